@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized matvec hot path (BASELINE.json's metric: achieved
+HBM GB/s of the dequant-in-kernel matvec).
+
+One JSON line on stdout.  A *step* is one pass of the hot path over one batch of
+synthetic input:
+
+* ``--gpus 1`` — workload ``c1_q6k_ffn_pair``: the Q6_K matvec [14336, 4096]
+  followed by the companion Q6_K down-projection [4096, 14336] on its result.
+  Weights are resident; successive steps walk distinct device copies of the two
+  matrices whose total exceeds L2 several times over, so every step reads HBM.
+* ``--gpus N`` (N > 1, under torchrun) — workload ``c4_70b_layer_matvec``: the
+  seven matrices of one Llama-3-70B-shaped block, output rows split evenly over
+  the ranks, followed by an NCCL all-gather of each output vector.
+
+``value`` is device-timed (CUDA events on the launching stream, max over ranks);
+``e2e`` goes through the host-buffer entry point ``matvec_resident`` with pinned
+host activations (host<->device copies inside the timed region).
+``--impl reference`` times the CPU restatement of the reference's path (the
+oracle port, OpenMP over rows) on the host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from ullm_b200 import synth  # noqa: E402
+
+C1_UP = (14336, 4096)
+C1_DOWN = (4096, 14336)
+C1_BYTES_PER_LAUNCH = 48_168_960 + 16_384 + 57_344  # weights + x + y (either launch)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
+# from the ncu capture summarised in profiles/ (None until captured).
+NCU_TRAFFIC_PER_LAUNCH = {"c1_q6k_ffn_pair": None}
+
+C4_MATS = [  # name, dtype, out, in   (one Llama-3-70B block)
+    ("q", synth.Q4_K, 8192, 8192), ("k", synth.Q4_K, 1024, 8192), ("v", synth.Q4_K, 1024, 8192),
+    ("o", synth.Q4_K, 8192, 8192), ("gate", synth.Q4_K, 28672, 8192), ("up", synth.Q4_K, 28672, 8192),
+    ("down", synth.Q6_K, 8192, 28672),
+]
+
+
+def weight_bytes(dtype, out, cols):
+    return out * (cols // 256) * (144 if dtype == synth.Q4_K else 210)
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])), mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# CPU restatement (oracle port) legs
+# ---------------------------------------------------------------------------
+def cpu_c1_step_factory(frac: float = 1.0):
+    """CPU step on the first ``frac`` of the rows of each matrix (bounded sample)."""
+    import oracle
+
+    ru, rd = max(8, int(C1_UP[0] * frac)), max(8, int(C1_DOWN[0] * frac))
+    up = oracle.Weight(oracle.Q6_K, synth.gen_q6k(ru, C1_UP[1], synth.seed_for(1, 0)), ru, C1_UP[1])
+    down = oracle.Weight(oracle.Q6_K, synth.gen_q6k(rd, C1_DOWN[1], synth.seed_for(1, 1)), rd, C1_DOWN[1])
+    x = synth.normal(synth.seed_for(1, 2), C1_UP[1])
+    h_full = np.zeros(C1_DOWN[1], np.float32)
+
+    def step():
+        h_full[:ru] = oracle.matvec_q(up, x)
+        return oracle.matvec_q(down, h_full)
+
+    nbytes = weight_bytes(synth.Q6_K, ru, C1_UP[1]) + weight_bytes(synth.Q6_K, rd, C1_DOWN[1]) + 4 * (ru + rd + sum(C1_UP[1:]) + C1_DOWN[1])
+    return step, oracle.max_threads(), nbytes, f"rows 0..{ru} of up and 0..{rd} of down"
+
+
+def cpu_c4_step_factory(frac: float = 1.0):
+    import oracle
+
+    ws, xs, nbytes = [], [], 0
+    for i, (name, dt, out, cols) in enumerate(C4_MATS):
+        r = max(8, int(out * frac))
+        ws.append(oracle.Weight(dt, synth.gen_weight(dt, r, cols, synth.seed_for(4, i)), r, cols))
+        xs.append(synth.normal(synth.seed_for(4, 8 + i), cols))
+        nbytes += weight_bytes(dt, r, cols) + 4 * (r + cols)
+
+    def step():
+        return [oracle.matvec_q(w, x) for w, x in zip(ws, xs)]
+
+    return step, oracle.max_threads(), nbytes, f"first {frac:.3f} of the rows of each of the 7 matrices"
+
+
+def run_reference(args):
+    """The reference's CPU path (oracle port) on the host cores, same workload and metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    factory = cpu_c1_step_factory if args.gpus == 1 else cpu_c4_step_factory
+    workload = "c1_q6k_ffn_pair" if args.gpus == 1 else "c4_70b_layer_matvec"
+    # Size the per-step sample so that warmup + steps end within ~2 minutes.
+    probe, cores, pbytes, _ = factory(1.0 / 16)
+    probe()
+    t0 = time.perf_counter()
+    probe()
+    t_probe = time.perf_counter() - t0
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    frac = min(1.0, (1.0 / 16) * budget / max(t_probe, 1e-6))
+    step, cores, nbytes, sample = factory(frac)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    gbs = args.steps * nbytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "quantized_matvec_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "note": "C restatement of ullm-model's CPU path (rayon -> OpenMP over rows); the Rust reference cannot be built here"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": f"{args.steps} steps, each over {sample}"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------
+# CUDA arm
+# ---------------------------------------------------------------------------
+def run_single(args):
+    import torch
+
+    from ullm_b200 import backend
+
+    torch.cuda.set_device(0)
+    ctx = backend.CudaContext(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    dev = torch.device("cuda:0")
+
+    w_up_h = synth.gen_q6k(*C1_UP, synth.seed_for(1, 0))
+    w_dn_h = synth.gen_q6k(*C1_DOWN, synth.seed_for(1, 1))
+    x_h = synth.normal(synth.seed_for(1, 2), C1_UP[1])
+    ncopies = args.copies  # 2 * 48 MB per copy; the walk must exceed L2 (126 MB) several times
+    ups = [torch.from_numpy(w_up_h.reshape(-1)).to(dev) for _ in range(ncopies)]
+    dns = [torch.from_numpy(w_dn_h.reshape(-1)).to(dev) for _ in range(ncopies)]
+    x = torch.from_numpy(x_h).to(dev)
+    h = torch.empty(C1_UP[0], dtype=torch.float32, device=dev)
+    y = torch.empty(C1_DOWN[0], dtype=torch.float32, device=dev)
+
+    def step(i):
+        c = i % ncopies
+        ctx.matvec_dev(backend.Q6_K, ups[c].data_ptr(), x.data_ptr(), h.data_ptr(), *C1_UP, stream=stream)
+        ctx.matvec_dev(backend.Q6_K, dns[c].data_ptr(), h.data_ptr(), y.data_ptr(), *C1_DOWN, stream=stream)
+
+    if args.pdl:
+        ctx.debug_set("pdl", 1)
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    plan = ctx.last_plan()
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    ev1.record()
+    torch.cuda.synchronize()
+    ctx.synchronize()  # surfaces a device-side timeout status
+    ms = ev0.elapsed_time(ev1)
+
+    # end to end: host buffers in, host buffers out, through matvec_resident
+    up_buf = [ctx.upload(w_up_h) for _ in range(ncopies)]
+    dn_buf = [ctx.upload(w_dn_h) for _ in range(ncopies)]
+    xp = torch.from_numpy(x_h).pin_memory().numpy()
+    hp = torch.empty(C1_UP[0], dtype=torch.float32).pin_memory().numpy()
+    yp = torch.empty(C1_DOWN[0], dtype=torch.float32).pin_memory().numpy()
+
+    def e2e_step(i):
+        c = i % ncopies
+        ctx.matvec_resident(backend.Q6_K, up_buf[c], xp, *C1_UP, out=hp)
+        ctx.matvec_resident(backend.Q6_K, dn_buf[c], hp, *C1_DOWN, out=yp)
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(args.warmup + i)
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+
+    # parity spot check of what was timed (64 rows of the final output)
+    y_host = y.cpu().numpy()
+    check = {"rel_err_vs_e2e": synth.rel_err(y_host, yp)}
+
+    step_bytes = 2 * C1_BYTES_PER_LAUNCH
+    value = args.steps * step_bytes / (ms * 1e-3) / 1e9
+    launch_us = ms * 1e3 / (2 * args.steps)
+    peak, peak_kind = measured_peak_gbs()
+    achieved = C1_BYTES_PER_LAUNCH / (launch_us * 1e-6) / 1e9
+
+    cpu = None
+    if not args.no_cpu:
+        cstep, cores, _, _ = cpu_c1_step_factory()
+        cstep()
+        t0 = time.perf_counter()
+        n = 0
+        while n < 3 or (time.perf_counter() - t0 < 10.0 and n < 200):
+            ref = cstep()
+            n += 1
+        cdt = (time.perf_counter() - t0) / n
+        check["rel_err_vs_cpu"] = synth.rel_err(y_host, ref)
+        cpu = {"value": step_bytes / cdt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+               "sample": f"{n} full steps of c1_q6k_ffn_pair, {cdt * 1e3:.1f} ms each"}
+
+    line = {
+        "metric": "quantized_matvec_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 dot products (16-bit fixed-point x) + f32 accumulate", "data": "synthetic",
+        "config": {"workload": "c1_q6k_ffn_pair", "shapes": "Q6_K [14336,4096] then Q6_K [4096,14336], batch 1",
+                   "l2": f"{ncopies} distinct weight copies ({ncopies * 96} MB) walked round-robin: inputs larger than L2",
+                   "plan": plan, "pdl": bool(args.pdl), "frac_of_8000": value / 8000.0},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_PER_LAUNCH["c1_q6k_ffn_pair"], "peak_kind": f"of {peak_kind}",
+                     "kernel": "matvec_stream_kernel<Q6_K>", "launch_us": launch_us,
+                     "algorithmic_bytes_per_launch": C1_BYTES_PER_LAUNCH},
+        "cpu_baseline": cpu,
+        "e2e": {"value": args.steps * step_bytes / e2e_s / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": 4 * (C1_UP[1] + C1_DOWN[1]), "d2h_bytes_per_step": 4 * (C1_UP[0] + C1_DOWN[0]),
+                "us_per_step": e2e_s / args.steps * 1e6, "api": "ullm_cuda_matvec_resident (pinned host x / y)"},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+        "check": check,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def run_multi(args):
+    import torch
+    import torch.distributed as dist
+
+    from ullm_b200 import backend
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    ctx = backend.CudaContext(local)
+    dev = torch.device(f"cuda:{local}")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    mats = []
+    for i, (name, dt, out, cols) in enumerate(C4_MATS):
+        assert out % world == 0
+        rows = out // world
+        # each rank generates only its own row slice (rows are self-contained byte ranges)
+        w = synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1))
+        xv = synth.normal(synth.seed_for(4, 8 + i), cols)
+        mats.append(dict(dt=dt, rows=rows, out=out, cols=cols, w=torch.from_numpy(w.reshape(-1)).to(dev),
+                         x=torch.from_numpy(xv).to(dev), y_local=torch.empty(rows, dtype=torch.float32, device=dev),
+                         y_full=torch.empty(out, dtype=torch.float32, device=dev)))
+
+    def step(_i):
+        for m in mats:
+            ctx.matvec_dev(m["dt"], m["w"].data_ptr(), m["x"].data_ptr(), m["y_local"].data_ptr(), m["rows"], m["cols"], stream=stream)
+        for m in mats:
+            dist.all_gather_into_tensor(m["y_full"], m["y_local"])
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ctx.synchronize()
+    ms_t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms = float(ms_t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    total_bytes = sum(weight_bytes(dt, o, c) + 4 * (o + c) for _, dt, o, c in C4_MATS)
+    if rank == 0:
+        value = args.steps * total_bytes / (ms * 1e-3) / 1e9
+        peak, peak_kind = measured_peak_gbs()
+        line = {
+            "metric": "quantized_matvec_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8 dot products (16-bit fixed-point x) + f32 accumulate", "data": "synthetic",
+            "config": {"workload": "c4_70b_layer_matvec", "shapes": "Q4_K q,o [8192,8192] k,v [1024,8192] gate,up [28672,8192]; Q6_K down [8192,28672]",
+                       "parallelism": f"rows/{world} + NCCL all-gather per output vector",
+                       "l2": "542 MB of weights per step: inputs larger than the aggregate L2 only at N<=4; per-rank slice at N=8 is 68 MB (L2-resident)"},
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                         "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "matvec_stream_kernel (per rank, incl. all-gather time)"},
+            "cpu_baseline": None,
+            "e2e": None,
+            "gpu_launches": 7 * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return run_multi(args)
+    return run_single(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,197 @@
+/*
+ * ullm_cuda.h — C ABI of the B200 (sm_100a) backend for uLLM's quantized
+ * matrix-product path.
+ *
+ * The reference has no C ABI: its GPU backend is the Rust crate `ullm-metal`,
+ * used concretely by `ullm-model`.  Every entry point below replaces one method
+ * of that crate's public surface (cited as file:line inside the reference
+ * project); a Rust `ullm-cuda` crate binds them one to one.
+ *
+ * Conventions
+ *  - All functions return an `ullm_status`; 0 is success.  A human-readable
+ *    message for the last failure on a context is kept by the context
+ *    (`ullm_cuda_last_error`).  UNSUPPORTED / FORMAT map onto
+ *    `ullm_core::Error::{Unsupported, Format}` (crates/ullm-core/src/error.rs:11-20).
+ *  - Host pointers are borrowed for the duration of the call only; the library
+ *    copies what it keeps (as `GpuForward::new` does, forward.rs:247-268).
+ *  - Calls taking host buffers are synchronous (the reference commits and waits,
+ *    forward.rs:513-515).  `*_dev` calls take device pointers plus a
+ *    `cudaStream_t` (as `void *`; NULL = the context's own stream), only enqueue,
+ *    and are the resident / graph-capturable form.
+ *  - A context is bound to one CUDA device and may be moved between threads but
+ *    not used concurrently (the reference's `unsafe impl Send`, forward.rs:221-225).
+ *  - There is no CPU fallback: without a CUDA device `ullm_cuda_ctx_create`
+ *    fails with ULLM_ERR_UNSUPPORTED ("no CUDA device available"), like
+ *    `MetalContext::new` (crates/ullm-metal/src/lib.rs:31-33).
+ *  - Matrices are row-major `[out, in]` in their on-disk quantized form
+ *    (`QWeight`, crates/ullm-model/src/lib.rs:49-61); activations are f32,
+ *    token-major `[s, in]`, outputs `[s, out]` (forward.rs:675-676).
+ */
+#ifndef ULLM_CUDA_H
+#define ULLM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    ULLM_OK = 0,
+    ULLM_ERR_UNSUPPORTED = 1, /* Error::Unsupported */
+    ULLM_ERR_FORMAT = 2,      /* Error::Format      */
+    ULLM_ERR_CUDA = 3,        /* a CUDA runtime call failed            */
+    ULLM_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up     */
+    ULLM_ERR_OOM = 5,
+    ULLM_ERR_INVALID = 6      /* NULL pointer / bad handle              */
+} ullm_status;
+
+/* Weight element types: ggml tensor type ids (crates/ullm-gguf/src/types.rs:7-29)
+ * plus a private id for MLX packed 4-bit words (`DType::U32`, dtype.rs:27). */
+typedef enum {
+    ULLM_DTYPE_F32 = 0,
+    ULLM_DTYPE_F16 = 1,
+    ULLM_DTYPE_Q4_K = 12,
+    ULLM_DTYPE_Q6_K = 14,
+    ULLM_DTYPE_BF16 = 30,
+    ULLM_DTYPE_MLX_U32 = 1000
+} ullm_dtype;
+
+typedef struct ullm_cuda_ctx ullm_cuda_ctx;
+typedef struct ullm_cuda_buf ullm_cuda_buf;
+typedef struct ullm_cuda_fwd ullm_cuda_fwd;
+typedef struct ullm_cuda_experts ullm_cuda_experts;
+
+/* ---- context: MetalContext::new / device_name (ullm-metal/src/lib.rs:31, :59) ---- */
+int ullm_cuda_ctx_create(int device, ullm_cuda_ctx **out);
+void ullm_cuda_ctx_destroy(ullm_cuda_ctx *ctx);
+const char *ullm_cuda_last_error(const ullm_cuda_ctx *ctx);
+int ullm_cuda_device_name(const ullm_cuda_ctx *ctx, char *name, size_t cap);
+int ullm_cuda_sm_count(const ullm_cuda_ctx *ctx);
+/* Blocks until everything enqueued on the context's stream has finished and
+ * reports a device-side status (ULLM_ERR_TIMEOUT if a kernel's bounded wait
+ * expired). */
+int ullm_cuda_synchronize(ullm_cuda_ctx *ctx);
+
+/* ---- resident buffers: MetalContext::upload (lib.rs:64) ---- */
+int ullm_cuda_upload(ullm_cuda_ctx *ctx, const void *bytes, size_t len, ullm_cuda_buf **out);
+int ullm_cuda_alloc(ullm_cuda_ctx *ctx, size_t len, ullm_cuda_buf **out);
+int ullm_cuda_download(ullm_cuda_ctx *ctx, const ullm_cuda_buf *buf, size_t offset, void *host, size_t len);
+void *ullm_cuda_buf_ptr(const ullm_cuda_buf *buf);
+size_t ullm_cuda_buf_len(const ullm_cuda_buf *buf);
+void ullm_cuda_buf_free(ullm_cuda_ctx *ctx, ullm_cuda_buf *buf);
+
+/* ---- dequantization (bit-exact against ullm_core::dequant) ----
+ * `dequantize` (dequant.rs:52-110): n elements of dtype from `data` (host) into
+ * `out` (host).  FORMAT when n is not a multiple of the block size or `data_len`
+ * is short (dequant.rs:65-77); UNSUPPORTED for other dtypes. */
+int ullm_cuda_dequantize(ullm_cuda_ctx *ctx, int dtype, const void *data, size_t data_len, float *out, size_t n);
+/* `dequantize_mlx_q4` (dequant.rs:297-317): f32 scale/bias tables. */
+int ullm_cuda_dequantize_mlx4(ullm_cuda_ctx *ctx, const uint32_t *weight, const float *scales, const float *biases,
+                              size_t out_dim, size_t in_dim, size_t group, float *y);
+
+/* ---- batch-1 matvec ----
+ * MetalContext::matvec_quant (lib.rs:83-94): raw GGUF block bytes on the host. */
+int ullm_cuda_matvec_quant(ullm_cuda_ctx *ctx, int dtype, const void *w_bytes, size_t w_len, const float *x, float *y,
+                           size_t out_dim, size_t in_dim);
+/* MetalContext::matvec_resident (lib.rs:97-107): weights already uploaded. */
+int ullm_cuda_matvec_resident(ullm_cuda_ctx *ctx, int dtype, const ullm_cuda_buf *w, const float *x, float *y,
+                              size_t out_dim, size_t in_dim);
+/* MetalContext::matvec_mlx4 (lib.rs:112-158): packed words + f32 group tables. */
+int ullm_cuda_matvec_mlx4(ullm_cuda_ctx *ctx, const void *w, const float *scales, const float *biases, const float *x,
+                          float *y, size_t out_dim, size_t in_dim, size_t group);
+/* GpuForward::matvec (forward.rs:639-673) on device pointers.  `d_w` must be
+ * 16-byte aligned.  For ULLM_DTYPE_MLX_U32 pass the tables and their element
+ * type (ULLM_DTYPE_F32, or ULLM_DTYPE_BF16 for the bits as stored on disk:
+ * widening bf16 is exact, dequant.rs:286); otherwise NULL/0. */
+int ullm_cuda_matvec_dev(ullm_cuda_ctx *ctx, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
+                         int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
+                         void *stream);
+
+/* ---- batched matmul (prefill) ----
+ * GpuForward::matmul (forward.rs:679-725; kernels matmul_q4k / matmul_q6k /
+ * matmul_mlx4) and MetalContext::matmul_mlx4 (lib.rs:212-266).
+ * x: [s, in] f32 token-major; y: [s, out] f32. */
+int ullm_cuda_matmul_quant(ullm_cuda_ctx *ctx, int dtype, const void *w_bytes, size_t w_len, const float *x, float *y,
+                           size_t out_dim, size_t in_dim, size_t s);
+int ullm_cuda_matmul_mlx4(ullm_cuda_ctx *ctx, const void *w, const float *scales, const float *biases, const float *x,
+                          float *y, size_t out_dim, size_t in_dim, size_t group, size_t s);
+int ullm_cuda_matmul_dev(ullm_cuda_ctx *ctx, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
+                         int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
+                         size_t s, void *stream);
+
+/* ---- mixture-of-experts FFN (MLX 4-bit stacked experts) ----
+ * GpuExperts (forward.rs:67-75): `n_experts` matrices concatenated, gate/up
+ * `[n_experts, inter, hidden/8]` words, down `[n_experts, hidden, inter/8]`,
+ * tables `[n_experts, out, in/group]` of `table_dtype`. */
+typedef struct {
+    const void *gate_w, *gate_scales, *gate_biases;
+    const void *up_w, *up_scales, *up_biases;
+    const void *down_w, *down_scales, *down_biases;
+    int table_dtype; /* ULLM_DTYPE_F32 or ULLM_DTYPE_BF16 */
+    size_t n_experts, hidden, inter, group;
+} ullm_moe_experts_input;
+int ullm_cuda_experts_create(ullm_cuda_ctx *ctx, const ullm_moe_experts_input *in, ullm_cuda_experts **out);
+void ullm_cuda_experts_destroy(ullm_cuda_ctx *ctx, ullm_cuda_experts *e);
+/* moe_topk + moe_gate_up_all + moe_down_all + moe_combine (forward.rs:484-494,
+ * shader.metal:301-444; CPU form crates/ullm-model/src/lib.rs:1453-1488) for
+ * `n_tok` tokens at once: x [n_tok, hidden], router logits [n_tok, n_experts],
+ * y [n_tok, hidden]; top-k by descending logit (ties: lower index first),
+ * softmax over the k selected, accumulation in that order.  Optional outputs
+ * `idx` [n_tok, k] (uint32) and `wts` [n_tok, k] may be NULL. */
+int ullm_cuda_moe_ffn(ullm_cuda_ctx *ctx, const ullm_cuda_experts *e, const float *x, const float *logits, size_t n_tok,
+                      size_t k, float *y, uint32_t *idx, float *wts);
+
+/* ---- full decode step: GpuForward (forward.rs:162-757) ---- */
+typedef struct { /* GpuParams, forward.rs:24-51 */
+    size_t n_embd, n_layer, n_head, n_kv_head, head_dim, n_ff, n_ctx, vocab;
+    float rope_theta, eps;
+    int rope_neox, qk_norm, sandwich_norm, geglu;
+    size_t n_experts, n_experts_used, moe_inter, sliding_window;
+    /* Not in the reference (its KV cache is f32, forward.rs:355-356): store K/V
+     * as IEEE half when non-zero. */
+    int kv_f16;
+} ullm_gpu_params;
+typedef struct { /* GpuWeight, forward.rs:56-64 */
+    int dtype;
+    const void *bytes;
+    size_t len, out, cols;
+    const float *mlx_scales, *mlx_biases;
+    size_t mlx_group;
+} ullm_gpu_weight;
+typedef struct { /* GpuLayerInput, forward.rs:78-100 (dense Llama fields) */
+    const float *attn_norm, *ffn_norm;
+    ullm_gpu_weight wq, wk, wv, wo, w_gate, w_up, w_down;
+} ullm_gpu_layer_input;
+typedef struct { /* GpuModelInput, forward.rs:105-110 */
+    ullm_gpu_params params;
+    ullm_gpu_weight output;
+    const float *final_norm;
+    const ullm_gpu_layer_input *layers; /* params.n_layer entries */
+} ullm_gpu_model_input;
+
+/* GpuForward::new (forward.rs:230).  UNSUPPORTED for flags no benchmark
+ * configuration uses (rope_neox, qk_norm, sandwich_norm, geglu, MoE layers,
+ * sliding window) instead of silently ignoring them. */
+int ullm_cuda_forward_create(ullm_cuda_ctx *ctx, const ullm_gpu_model_input *in, ullm_cuda_fwd **out);
+void ullm_cuda_forward_destroy(ullm_cuda_fwd *f);
+/* GpuForward::forward (forward.rs:384): one token at `pos`, returns vocab logits. */
+int ullm_cuda_forward(ullm_cuda_fwd *f, const float *x_init, size_t pos, float *logits);
+/* Fills KV cache positions [pos0, pos0+n) of every layer from host f32 arrays
+ * laid out [n_layer][n][kv_dim] (test / benchmark set-up: the reference fills
+ * the cache by running tokens). */
+int ullm_cuda_forward_set_kv(ullm_cuda_fwd *f, size_t pos0, size_t n, const float *k, const float *v);
+/* GpuForward::supports_batched_prefill (forward.rs:744). */
+int ullm_cuda_forward_supports_batched_prefill(const ullm_cuda_fwd *f);
+/* Greedy continuation kept on the device: runs `n` decode steps starting from
+ * token embedding lookups of `embd_table` (dtype rows, resident) — argmax
+ * (sample.rs:125-133, first index wins) feeds the next step without a host
+ * round trip.  tokens_out[n]. */
+int ullm_cuda_forward_greedy(ullm_cuda_fwd *f, const ullm_cuda_buf *embd_table, int embd_dtype, uint32_t first_token,
+                             size_t pos, size_t n, uint32_t *tokens_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ULLM_CUDA_H */

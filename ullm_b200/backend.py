@@ -1,0 +1,266 @@
+"""Host-side mirror of the reference's GPU backend surface over the C ABI.
+
+``CudaContext`` carries the method set of ``ullm_metal::MetalContext``
+(crates/ullm-metal/src/lib.rs:18-318): ``device_name``, ``upload``,
+``matvec_quant``, ``matvec_resident``, ``matvec_mlx4``, ``matmul_mlx4`` — same
+names, argument meaning and error behaviour (``Unsupported`` / ``Format``).
+Everything runs in ``libullm_cuda.so``; there is no Python or CPU compute path,
+and loading fails loudly when the library has not been built.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libullm_cuda.so")
+
+# ullm_status
+OK, ERR_UNSUPPORTED, ERR_FORMAT, ERR_CUDA, ERR_TIMEOUT, ERR_OOM, ERR_INVALID = range(7)
+# ullm_dtype (ggml ids, crates/ullm-gguf/src/types.rs:7-29)
+F32, F16, Q4_K, Q6_K, BF16, MLX_U32 = 0, 1, 12, 14, 30, 1000
+
+Q4K_BLOCK_BYTES, Q6K_BLOCK_BYTES, QK_K = 144, 210, 256
+
+
+class UllmError(Exception):
+    """ullm_core::Error (crates/ullm-core/src/error.rs:11-20) plus CUDA statuses."""
+
+    def __init__(self, code: int, msg: str):
+        names = {1: "unsupported", 2: "format error", 3: "cuda error", 4: "timeout", 5: "out of memory", 6: "invalid argument"}
+        super().__init__(f"{names.get(code, code)}: {msg}")
+        self.code = code
+
+
+class Unsupported(UllmError):
+    pass
+
+
+class FormatError(UllmError):
+    pass
+
+
+_lib = None
+
+_vp, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
+
+# name -> (restype, argtypes): every symbol include/ullm_cuda.h declares.
+SIGNATURES = {
+    "ullm_cuda_ctx_create": (_i, [_i, C.POINTER(_vp)]),
+    "ullm_cuda_ctx_destroy": (None, [_vp]),
+    "ullm_cuda_last_error": (C.c_char_p, [_vp]),
+    "ullm_cuda_device_name": (_i, [_vp, C.c_char_p, _sz]),
+    "ullm_cuda_sm_count": (_i, [_vp]),
+    "ullm_cuda_synchronize": (_i, [_vp]),
+    "ullm_cuda_upload": (_i, [_vp, _vp, _sz, C.POINTER(_vp)]),
+    "ullm_cuda_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
+    "ullm_cuda_download": (_i, [_vp, _vp, _sz, _vp, _sz]),
+    "ullm_cuda_buf_ptr": (_vp, [_vp]),
+    "ullm_cuda_buf_len": (_sz, [_vp]),
+    "ullm_cuda_buf_free": (None, [_vp, _vp]),
+    "ullm_cuda_dequantize": (_i, [_vp, _i, _vp, _sz, _vp, _sz]),
+    "ullm_cuda_dequantize_mlx4": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp]),
+    "ullm_cuda_matvec_quant": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _sz, _sz]),
+    "ullm_cuda_matvec_resident": (_i, [_vp, _i, _vp, _vp, _vp, _sz, _sz]),
+    "ullm_cuda_matvec_mlx4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "ullm_cuda_matvec_dev": (_i, [_vp, _i, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _sz, _vp]),
+    "ullm_cuda_matmul_quant": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
+    "ullm_cuda_matmul_mlx4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),
+    "ullm_cuda_matmul_dev": (_i, [_vp, _i, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _sz, _sz, _vp]),
+    "ullm_cuda_experts_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "ullm_cuda_experts_destroy": (None, [_vp, _vp]),
+    "ullm_cuda_moe_ffn": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp]),
+    "ullm_cuda_forward_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "ullm_cuda_forward_destroy": (None, [_vp]),
+    "ullm_cuda_forward": (_i, [_vp, _vp, _sz, _vp]),
+    "ullm_cuda_forward_set_kv": (_i, [_vp, _sz, _sz, _vp, _vp]),
+    "ullm_cuda_forward_supports_batched_prefill": (_i, [_vp]),
+    "ullm_cuda_forward_greedy": (_i, [_vp, _vp, _i, C.c_uint32, _sz, _sz, _vp]),
+}
+# Test / tuning knobs outside the mirrored surface.
+DEBUG_SIGNATURES = {
+    "ullm_cuda_debug_set": (_i, [_vp, C.c_char_p, _i]),
+    "ullm_cuda_debug_last_plan": (_i, [_vp, _vp, _i]),
+}
+
+
+def load_library() -> C.CDLL:
+    """Loads ``libullm_cuda.so``; raises if it has not been built (no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build the CUDA library first (python -m ullm_b200.build); there is no CPU fallback"
+            )
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in {**SIGNATURES, **DEBUG_SIGNATURES}.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def _ptr(a) -> int:
+    return a.ctypes.data if a is not None else None
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, np.float32)
+
+
+def _bytes(a) -> np.ndarray:
+    if isinstance(a, (bytes, bytearray, memoryview)):
+        return np.frombuffer(a, np.uint8)
+    return np.ascontiguousarray(a).view(np.uint8).reshape(-1)
+
+
+class Buffer:
+    """A resident device buffer (``metal::Buffer`` in the reference surface)."""
+
+    def __init__(self, ctx: "CudaContext", handle: int):
+        self._ctx, self._h = ctx, handle
+
+    @property
+    def ptr(self) -> int:
+        return load_library().ullm_cuda_buf_ptr(self._h)
+
+    def __len__(self) -> int:
+        return load_library().ullm_cuda_buf_len(self._h)
+
+    def download(self, offset: int = 0, length: int | None = None) -> np.ndarray:
+        n = len(self) - offset if length is None else length
+        out = np.empty(n, np.uint8)
+        self._ctx._check(load_library().ullm_cuda_download(self._ctx._h, self._h, offset, _ptr(out), n))
+        return out
+
+    def free(self):
+        if self._h:
+            load_library().ullm_cuda_buf_free(self._ctx._h, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class CudaContext:
+    """``MetalContext`` on a B200 (crates/ullm-metal/src/lib.rs:18-318)."""
+
+    def __init__(self, device: int = 0):
+        lib = load_library()
+        h = _vp()
+        rc = lib.ullm_cuda_ctx_create(device, C.byref(h))
+        if rc == ERR_UNSUPPORTED:
+            raise Unsupported(rc, "no CUDA device available")  # lib.rs:33
+        if rc != OK:
+            raise UllmError(rc, "context creation failed")
+        self._h = h.value
+        self._lib = lib
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.ullm_cuda_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc == OK:
+            return
+        msg = (self._lib.ullm_cuda_last_error(self._h) or b"").decode()
+        cls = {ERR_UNSUPPORTED: Unsupported, ERR_FORMAT: FormatError}.get(rc, UllmError)
+        raise cls(rc, msg)
+
+    # -- MetalContext surface ------------------------------------------------
+    def device_name(self) -> str:
+        buf = C.create_string_buffer(256)
+        self._check(self._lib.ullm_cuda_device_name(self._h, buf, 256))
+        return buf.value.decode()
+
+    def sm_count(self) -> int:
+        return self._lib.ullm_cuda_sm_count(self._h)
+
+    def synchronize(self):
+        self._check(self._lib.ullm_cuda_synchronize(self._h))
+
+    def upload(self, data) -> Buffer:
+        b = _bytes(data)
+        h = _vp()
+        self._check(self._lib.ullm_cuda_upload(self._h, _ptr(b), b.size, C.byref(h)))
+        return Buffer(self, h.value)
+
+    def alloc(self, nbytes: int) -> Buffer:
+        h = _vp()
+        self._check(self._lib.ullm_cuda_alloc(self._h, nbytes, C.byref(h)))
+        return Buffer(self, h.value)
+
+    def dequantize(self, dtype: int, data, n: int) -> np.ndarray:
+        b = _bytes(data)
+        out = np.empty(n, np.float32)
+        self._check(self._lib.ullm_cuda_dequantize(self._h, dtype, _ptr(b), b.size, _ptr(out), n))
+        return out
+
+    def dequantize_mlx_q4(self, weight, scales, biases, out_dim: int, in_dim: int, group: int) -> np.ndarray:
+        w = np.ascontiguousarray(weight, np.uint32)
+        s, b = _f32(scales), _f32(biases)
+        y = np.empty((out_dim, in_dim), np.float32)
+        self._check(self._lib.ullm_cuda_dequantize_mlx4(self._h, _ptr(w), _ptr(s), _ptr(b), out_dim, in_dim, group, _ptr(y)))
+        return y
+
+    def matvec_quant(self, dtype: int, w_bytes, x, out_dim: int, in_dim: int) -> np.ndarray:
+        w, x = _bytes(w_bytes), _f32(x)
+        y = np.empty(out_dim, np.float32)
+        self._check(self._lib.ullm_cuda_matvec_quant(self._h, dtype, _ptr(w), w.size, _ptr(x), _ptr(y), out_dim, in_dim))
+        return y
+
+    def matvec_resident(self, dtype: int, wbuf: Buffer, x, out_dim: int, in_dim: int, out: np.ndarray | None = None) -> np.ndarray:
+        x = _f32(x)
+        y = np.empty(out_dim, np.float32) if out is None else out
+        self._check(self._lib.ullm_cuda_matvec_resident(self._h, dtype, wbuf._h, _ptr(x), _ptr(y), out_dim, in_dim))
+        return y
+
+    def matvec_mlx4(self, w, scales, biases, x, out_dim: int, in_dim: int, group_size: int) -> np.ndarray:
+        w, s, b, x = _bytes(w), _f32(scales), _f32(biases), _f32(x)
+        y = np.empty(out_dim, np.float32)
+        self._check(self._lib.ullm_cuda_matvec_mlx4(self._h, _ptr(w), _ptr(s), _ptr(b), _ptr(x), _ptr(y), out_dim, in_dim, group_size))
+        return y
+
+    def matmul_quant(self, dtype: int, w_bytes, x, out_dim: int, in_dim: int, s: int) -> np.ndarray:
+        w, x = _bytes(w_bytes), _f32(x)
+        y = np.empty((s, out_dim), np.float32)
+        self._check(self._lib.ullm_cuda_matmul_quant(self._h, dtype, _ptr(w), w.size, _ptr(x), _ptr(y), out_dim, in_dim, s))
+        return y
+
+    def matmul_mlx4(self, w, scales, biases, x, out_dim: int, in_dim: int, group_size: int, s: int) -> np.ndarray:
+        w, sc, b, x = _bytes(w), _f32(scales), _f32(biases), _f32(x)
+        y = np.empty((s, out_dim), np.float32)
+        self._check(self._lib.ullm_cuda_matmul_mlx4(self._h, _ptr(w), _ptr(sc), _ptr(b), _ptr(x), _ptr(y), out_dim, in_dim, group_size, s))
+        return y
+
+    # -- device-pointer forms (resident pipelines, benchmarks) ------------------
+    def matvec_dev(self, dtype, d_w, d_x, d_y, out_dim, in_dim, stream=None, d_scales=None, d_biases=None, table_dtype=0, group=0):
+        self._check(
+            self._lib.ullm_cuda_matvec_dev(self._h, dtype, d_w, d_scales, d_biases, table_dtype, group, d_x, d_y, out_dim, in_dim, stream)
+        )
+
+    def matmul_dev(self, dtype, d_w, d_x, d_y, out_dim, in_dim, s, stream=None, d_scales=None, d_biases=None, table_dtype=0, group=0):
+        self._check(
+            self._lib.ullm_cuda_matmul_dev(self._h, dtype, d_w, d_scales, d_biases, table_dtype, group, d_x, d_y, out_dim, in_dim, s, stream)
+        )
+
+    # -- knobs used by tests and benchmarks ---------------------------------
+    def debug_set(self, key: str, value: int):
+        self._check(self._lib.ullm_cuda_debug_set(self._h, key.encode(), value))
+
+    def last_plan(self) -> dict:
+        v = (C.c_int * 6)()
+        self._lib.ullm_cuda_debug_last_plan(self._h, v, 6)
+        return dict(zip(("streamed", "rows_per_tile", "warps", "stages", "smem_bytes", "grid"), list(v)))

@@ -1,0 +1,375 @@
+// C ABI of the backend (see include/ullm_cuda.h).  Thin, validating wrappers:
+// shapes and pointers are checked on the host before anything is launched, CUDA
+// failures are turned into status codes with a message, and nothing here ever
+// computes on the CPU.
+#include "../../include/ullm_cuda.h"
+#include "engine.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+using namespace ullm;
+
+// ---- context ---------------------------------------------------------------
+int ullm_cuda_ctx_create(int device, ullm_cuda_ctx **out) {
+    if (!out) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return ULLM_ERR_UNSUPPORTED; // "no CUDA device available"
+    }
+    if (device < 0 || device >= n) return ULLM_ERR_INVALID;
+    ullm_cuda_ctx *c = new (std::nothrow) ullm_cuda_ctx();
+    if (!c) return ULLM_ERR_OOM;
+    c->device = device;
+    cudaDeviceProp prop;
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        delete c;
+        return ULLM_ERR_CUDA;
+    }
+    if (prop.major != 10) { // the kernels are sm_100a only; no other path exists
+        delete c;
+        return ULLM_ERR_UNSUPPORTED;
+    }
+    snprintf(c->name, sizeof c->name, "%s", prop.name);
+    c->dev.sm_count = prop.multiProcessorCount;
+    c->dev.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaHostAlloc((void **)&c->h_status, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void **)&c->d_status, (void *)c->h_status, 0) != cudaSuccess) {
+        ullm_cuda_ctx_destroy(c);
+        return ULLM_ERR_CUDA;
+    }
+    *c->h_status = 0;
+    *out = c;
+    return ULLM_OK;
+}
+
+void ullm_cuda_ctx_destroy(ullm_cuda_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) {
+        cudaStreamSynchronize(c->stream);
+        cudaStreamDestroy(c->stream);
+    }
+    if (c->h_status) cudaFreeHost((void *)c->h_status);
+    for (auto &s : c->scratch)
+        if (s.ptr) cudaFree(s.ptr);
+    delete c;
+}
+
+const char *ullm_cuda_last_error(const ullm_cuda_ctx *c) { return c ? c->err : "null context"; }
+
+int ullm_cuda_device_name(const ullm_cuda_ctx *c, char *name, size_t cap) {
+    if (!c || !name || cap == 0) return ULLM_ERR_INVALID;
+    snprintf(name, cap, "%s", c->name);
+    return ULLM_OK;
+}
+int ullm_cuda_sm_count(const ullm_cuda_ctx *c) { return c ? c->dev.sm_count : 0; }
+
+int ullm_cuda_synchronize(ullm_cuda_ctx *c) {
+    if (!c) return ULLM_ERR_INVALID;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ctx_check_status(c);
+}
+
+// ---- buffers ---------------------------------------------------------------
+int ullm_cuda_alloc(ullm_cuda_ctx *c, size_t len, ullm_cuda_buf **out) {
+    if (!c || !out) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    ullm_cuda_buf *b = new (std::nothrow) ullm_cuda_buf();
+    if (!b) return ULLM_ERR_OOM;
+    b->len = len;
+    cudaError_t e = cudaMalloc(&b->ptr, len ? len : 16);
+    if (e != cudaSuccess) {
+        delete b;
+        cudaGetLastError();
+        return ctx_fail(c, e == cudaErrorMemoryAllocation ? ULLM_ERR_OOM : ULLM_ERR_CUDA, "cudaMalloc(%zu): %s", len,
+                        cudaGetErrorString(e));
+    }
+    *out = b;
+    return ULLM_OK;
+}
+int ullm_cuda_upload(ullm_cuda_ctx *c, const void *bytes, size_t len, ullm_cuda_buf **out) {
+    if (!c || !out || (!bytes && len)) return ULLM_ERR_INVALID;
+    int rc = ullm_cuda_alloc(c, len, out);
+    if (rc) return rc;
+    if (len) {
+        cudaError_t e = cudaMemcpyAsync((*out)->ptr, bytes, len, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e != cudaSuccess) {
+            ullm_cuda_buf_free(c, *out);
+            *out = nullptr;
+            return ctx_fail(c, ULLM_ERR_CUDA, "upload: %s", cudaGetErrorString(e));
+        }
+    }
+    return ULLM_OK;
+}
+int ullm_cuda_download(ullm_cuda_ctx *c, const ullm_cuda_buf *b, size_t offset, void *host, size_t len) {
+    if (!c || !b || (!host && len)) return ULLM_ERR_INVALID;
+    if (offset > b->len || len > b->len - offset) return ctx_fail(c, ULLM_ERR_FORMAT, "download: range outside buffer");
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(host, (const uint8_t *)b->ptr + offset, len, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ULLM_OK;
+}
+void *ullm_cuda_buf_ptr(const ullm_cuda_buf *b) { return b ? b->ptr : nullptr; }
+size_t ullm_cuda_buf_len(const ullm_cuda_buf *b) { return b ? b->len : 0; }
+void ullm_cuda_buf_free(ullm_cuda_ctx *c, ullm_cuda_buf *b) {
+    if (!b) return;
+    if (c) cudaSetDevice(c->device);
+    if (b->ptr) cudaFree(b->ptr);
+    delete b;
+}
+
+// ---- helpers ---------------------------------------------------------------
+static int fmt_of(int dtype) {
+    switch (dtype) {
+    case ULLM_DTYPE_Q4_K: return FMT_Q4K;
+    case ULLM_DTYPE_Q6_K: return FMT_Q6K;
+    case ULLM_DTYPE_MLX_U32: return FMT_MLX4;
+    default: return -1;
+    }
+}
+static size_t weight_bytes(int fmt, size_t out_dim, size_t in_dim) {
+    if (fmt == FMT_Q4K) return out_dim * (in_dim / QK_K) * Q4K_BYTES;
+    if (fmt == FMT_Q6K) return out_dim * (in_dim / QK_K) * Q6K_BYTES;
+    return out_dim * (in_dim / 8) * 4;
+}
+
+// ---- dequantization --------------------------------------------------------
+int ullm_cuda_dequantize(ullm_cuda_ctx *c, int dtype, const void *data, size_t data_len, float *out, size_t n) {
+    if (!c || (!data && data_len) || (!out && n)) return ULLM_ERR_INVALID;
+    size_t block, ts;
+    switch (dtype) {
+    case ULLM_DTYPE_F32: block = 1, ts = 4; break;
+    case ULLM_DTYPE_F16: case ULLM_DTYPE_BF16: block = 1, ts = 2; break;
+    case ULLM_DTYPE_Q4_K: block = QK_K, ts = Q4K_BYTES; break;
+    case ULLM_DTYPE_Q6_K: block = QK_K, ts = Q6K_BYTES; break;
+    default: return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "dequantization of dtype %d is not implemented", dtype);
+    }
+    // crates/ullm-core/src/dequant.rs:65-77
+    if (n % block) return ctx_fail(c, ULLM_ERR_FORMAT, "element count %zu is not a multiple of block size %zu", n, block);
+    size_t need = n / block * ts;
+    if (data_len < need) return ctx_fail(c, ULLM_ERR_FORMAT, "need %zu bytes, have %zu", need, data_len);
+    if (n == 0) return ULLM_OK;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    void *d_in = nullptr, *d_out = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 0, need, &d_in)) || (rc = ctx_scratch(c, 1, n * 4, &d_out))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_in, data, need, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, launch_dequant(dtype, d_in, (float *)d_out, n, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(out, d_out, n * 4, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ULLM_OK;
+}
+
+int ullm_cuda_dequantize_mlx4(ullm_cuda_ctx *c, const uint32_t *weight, const float *scales, const float *biases,
+                              size_t out_dim, size_t in_dim, size_t group, float *y) {
+    if (!c || !weight || !scales || !biases || !y) return ULLM_ERR_INVALID;
+    if (const char *m = matvec_shape_error(FMT_MLX4, out_dim, in_dim, group)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    size_t wb = out_dim * (in_dim / 8) * 4, tb = out_dim * (in_dim / group) * 4, yb = out_dim * in_dim * 4;
+    void *d_w = nullptr, *d_s = nullptr, *d_b = nullptr, *d_y = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 0, wb, &d_w)) || (rc = ctx_scratch(c, 1, yb, &d_y)) || (rc = ctx_scratch(c, 2, tb, &d_s)) ||
+        (rc = ctx_scratch(c, 3, tb, &d_b)))
+        return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_w, weight, wb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_s, scales, tb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_b, biases, tb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, launch_dequant_mlx4((const uint32_t *)d_w, (const float *)d_s, (const float *)d_b, (float *)d_y,
+                                         out_dim, in_dim, group, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ULLM_OK;
+}
+
+// ---- matvec ----------------------------------------------------------------
+int ullm_cuda_matvec_dev(ullm_cuda_ctx *c, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
+                         int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
+                         void *stream) {
+    if (!c || !d_w || !d_x || !d_y) return ULLM_ERR_INVALID;
+    int fmt = fmt_of(dtype);
+    if (fmt < 0) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "no CUDA kernel for dtype %d yet", dtype);
+    MlxTables tb;
+    if (fmt == FMT_MLX4) {
+        if (!d_scales || !d_biases) return ULLM_ERR_INVALID;
+        if (table_dtype != ULLM_DTYPE_F32 && table_dtype != ULLM_DTYPE_BF16)
+            return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MLX tables must be f32 or bf16");
+        tb.scales = d_scales, tb.biases = d_biases, tb.group = group;
+        tb.elem_bytes = table_dtype == ULLM_DTYPE_F32 ? 4 : 2;
+    }
+    if (const char *m = matvec_shape_error(fmt, out_dim, in_dim, group)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    if ((uintptr_t)d_w % 16 || (uintptr_t)d_x % 16 || (uintptr_t)d_y % 4)
+        return ctx_fail(c, ULLM_ERR_FORMAT, "device pointers must be 16-byte aligned");
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    ULLM_CUDA_TRY(c, launch_matvec(c->dev, fmt, d_w, tb, d_x, d_y, out_dim, in_dim, c->d_status, st, c->force_generic,
+                                   c->use_pdl, &c->last_plan));
+    return ULLM_OK;
+}
+
+// x (host) -> device scratch, run, y -> host, wait.
+static int matvec_host(ullm_cuda_ctx *c, int dtype, const void *d_w, const void *d_s, const void *d_b, int tdt,
+                       size_t group, const float *x, float *y, size_t out_dim, size_t in_dim) {
+    void *d_x = nullptr, *d_y = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 4, in_dim * 4, &d_x)) || (rc = ctx_scratch(c, 5, out_dim * 4, &d_y))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_x, x, in_dim * 4, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = ullm_cuda_matvec_dev(c, dtype, d_w, d_s, d_b, tdt, group, (const float *)d_x, (float *)d_y, out_dim, in_dim,
+                                   nullptr)))
+        return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, out_dim * 4, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ctx_check_status(c);
+}
+
+int ullm_cuda_matvec_resident(ullm_cuda_ctx *c, int dtype, const ullm_cuda_buf *w, const float *x, float *y,
+                              size_t out_dim, size_t in_dim) {
+    if (!c || !w || !x || !y) return ULLM_ERR_INVALID;
+    int fmt = fmt_of(dtype);
+    // MetalContext::pso_for (crates/ullm-metal/src/lib.rs:268-276): only the k-quants
+    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "no CUDA kernel for dtype %d yet", dtype);
+    if (const char *m = matvec_shape_error(fmt, out_dim, in_dim, 0)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    if (w->len < weight_bytes(fmt, out_dim, in_dim))
+        return ctx_fail(c, ULLM_ERR_FORMAT, "need %zu weight bytes, have %zu", weight_bytes(fmt, out_dim, in_dim), w->len);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    return matvec_host(c, dtype, w->ptr, nullptr, nullptr, 0, 0, x, y, out_dim, in_dim);
+}
+
+int ullm_cuda_matvec_quant(ullm_cuda_ctx *c, int dtype, const void *w_bytes, size_t w_len, const float *x, float *y,
+                           size_t out_dim, size_t in_dim) {
+    if (!c || !w_bytes || !x || !y) return ULLM_ERR_INVALID;
+    int fmt = fmt_of(dtype);
+    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "no CUDA kernel for dtype %d yet", dtype);
+    if (const char *m = matvec_shape_error(fmt, out_dim, in_dim, 0)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    size_t need = weight_bytes(fmt, out_dim, in_dim);
+    if (w_len < need) return ctx_fail(c, ULLM_ERR_FORMAT, "need %zu weight bytes, have %zu", need, w_len);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    void *d_w = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 0, need, &d_w))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_w, w_bytes, need, cudaMemcpyHostToDevice, c->stream));
+    return matvec_host(c, dtype, d_w, nullptr, nullptr, 0, 0, x, y, out_dim, in_dim);
+}
+
+int ullm_cuda_matvec_mlx4(ullm_cuda_ctx *c, const void *w, const float *scales, const float *biases, const float *x,
+                          float *y, size_t out_dim, size_t in_dim, size_t group) {
+    if (!c || !w || !scales || !biases || !x || !y) return ULLM_ERR_INVALID;
+    if (const char *m = matvec_shape_error(FMT_MLX4, out_dim, in_dim, group)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    size_t wb = weight_bytes(FMT_MLX4, out_dim, in_dim), tb = out_dim * (in_dim / group) * 4;
+    void *d_w = nullptr, *d_s = nullptr, *d_b = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 0, wb, &d_w)) || (rc = ctx_scratch(c, 2, tb, &d_s)) || (rc = ctx_scratch(c, 3, tb, &d_b)))
+        return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_w, w, wb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_s, scales, tb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_b, biases, tb, cudaMemcpyHostToDevice, c->stream));
+    return matvec_host(c, ULLM_DTYPE_MLX_U32, d_w, d_s, d_b, ULLM_DTYPE_F32, group, x, y, out_dim, in_dim);
+}
+
+// ---- batched matmul --------------------------------------------------------
+int ullm_cuda_matmul_dev(ullm_cuda_ctx *c, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
+                         int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
+                         size_t s, void *stream) {
+    if (!c || !d_w || !d_x || !d_y) return ULLM_ERR_INVALID;
+    // Until the tensor-core kernel takes a shape, the product is formed one token
+    // column at a time with the matvec kernel (same arithmetic, weights re-read).
+    for (size_t t = 0; t < s; ++t) {
+        int rc = ullm_cuda_matvec_dev(c, dtype, d_w, d_scales, d_biases, table_dtype, group, d_x + t * in_dim,
+                                      d_y + t * out_dim, out_dim, in_dim, stream);
+        if (rc) return rc;
+    }
+    return ULLM_OK;
+}
+
+static int matmul_host(ullm_cuda_ctx *c, int dtype, const void *d_w, const void *d_s, const void *d_b, int tdt,
+                       size_t group, const float *x, float *y, size_t out_dim, size_t in_dim, size_t s) {
+    void *d_x = nullptr, *d_y = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 4, s * in_dim * 4, &d_x)) || (rc = ctx_scratch(c, 5, s * out_dim * 4, &d_y))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_x, x, s * in_dim * 4, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = ullm_cuda_matmul_dev(c, dtype, d_w, d_s, d_b, tdt, group, (const float *)d_x, (float *)d_y, out_dim, in_dim,
+                                   s, nullptr)))
+        return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, s * out_dim * 4, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ctx_check_status(c);
+}
+
+int ullm_cuda_matmul_quant(ullm_cuda_ctx *c, int dtype, const void *w_bytes, size_t w_len, const float *x, float *y,
+                           size_t out_dim, size_t in_dim, size_t s) {
+    if (!c || !w_bytes || (s && (!x || !y))) return ULLM_ERR_INVALID;
+    int fmt = fmt_of(dtype);
+    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "no CUDA kernel for dtype %d yet", dtype);
+    if (const char *m = matvec_shape_error(fmt, out_dim, in_dim, 0)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    size_t need = weight_bytes(fmt, out_dim, in_dim);
+    if (w_len < need) return ctx_fail(c, ULLM_ERR_FORMAT, "need %zu weight bytes, have %zu", need, w_len);
+    if (s == 0) return ULLM_OK;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    void *d_w = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 0, need, &d_w))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_w, w_bytes, need, cudaMemcpyHostToDevice, c->stream));
+    return matmul_host(c, dtype, d_w, nullptr, nullptr, 0, 0, x, y, out_dim, in_dim, s);
+}
+
+int ullm_cuda_matmul_mlx4(ullm_cuda_ctx *c, const void *w, const float *scales, const float *biases, const float *x,
+                          float *y, size_t out_dim, size_t in_dim, size_t group, size_t s) {
+    if (!c || !w || !scales || !biases || (s && (!x || !y))) return ULLM_ERR_INVALID;
+    if (const char *m = matvec_shape_error(FMT_MLX4, out_dim, in_dim, group)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    if (s == 0) return ULLM_OK;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    size_t wb = weight_bytes(FMT_MLX4, out_dim, in_dim), tb = out_dim * (in_dim / group) * 4;
+    void *d_w = nullptr, *d_s = nullptr, *d_b = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 0, wb, &d_w)) || (rc = ctx_scratch(c, 2, tb, &d_s)) || (rc = ctx_scratch(c, 3, tb, &d_b)))
+        return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_w, w, wb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_s, scales, tb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_b, biases, tb, cudaMemcpyHostToDevice, c->stream));
+    return matmul_host(c, ULLM_DTYPE_MLX_U32, d_w, d_s, d_b, ULLM_DTYPE_F32, group, x, y, out_dim, in_dim, s);
+}
+
+// ---- test / tuning knobs (not part of the mirrored surface) ------------------
+extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value) {
+    if (!c || !key) return ULLM_ERR_INVALID;
+    if (!strcmp(key, "force_generic")) c->force_generic = value != 0;
+    else if (!strcmp(key, "pdl")) c->use_pdl = value != 0;
+    else return ULLM_ERR_INVALID;
+    return ULLM_OK;
+}
+extern "C" int ullm_cuda_debug_last_plan(const ullm_cuda_ctx *c, int *vals, int n) {
+    if (!c || !vals) return ULLM_ERR_INVALID;
+    const int v[6] = {c->last_plan.streamed, c->last_plan.rows_per_tile, c->last_plan.warps,
+                      c->last_plan.stages,   c->last_plan.smem_bytes,    c->last_plan.grid};
+    for (int i = 0; i < n && i < 6; ++i) vals[i] = v[i];
+    return ULLM_OK;
+}
+
+// ---- not built yet -----------------------------------------------------------
+int ullm_cuda_experts_create(ullm_cuda_ctx *c, const ullm_moe_experts_input *, ullm_cuda_experts **) {
+    return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MoE experts are not built yet");
+}
+void ullm_cuda_experts_destroy(ullm_cuda_ctx *, ullm_cuda_experts *) {}
+int ullm_cuda_moe_ffn(ullm_cuda_ctx *c, const ullm_cuda_experts *, const float *, const float *, size_t, size_t, float *,
+                      uint32_t *, float *) {
+    return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MoE FFN is not built yet");
+}
+int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *, ullm_cuda_fwd **) {
+    return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "decode step is not built yet");
+}
+void ullm_cuda_forward_destroy(ullm_cuda_fwd *) {}
+int ullm_cuda_forward(ullm_cuda_fwd *, const float *, size_t, float *) { return ULLM_ERR_UNSUPPORTED; }
+int ullm_cuda_forward_set_kv(ullm_cuda_fwd *, size_t, size_t, const float *, const float *) { return ULLM_ERR_UNSUPPORTED; }
+int ullm_cuda_forward_supports_batched_prefill(const ullm_cuda_fwd *) { return 0; }
+int ullm_cuda_forward_greedy(ullm_cuda_fwd *, const ullm_cuda_buf *, int, uint32_t, size_t, size_t, uint32_t *) {
+    return ULLM_ERR_UNSUPPORTED;
+}

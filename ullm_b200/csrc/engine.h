@@ -1,0 +1,84 @@
+// Host-side objects behind the opaque handles of the C ABI.
+#pragma once
+
+#include "common.cuh"
+#include "kernels.h"
+
+#include <cstdarg>
+#include <cstdio>
+
+struct ullm_cuda_buf {
+    void *ptr = nullptr;
+    size_t len = 0;
+};
+
+struct ullm_cuda_ctx {
+    int device = 0;
+    char name[256] = {0};
+    ullm::DeviceInfo dev;
+    cudaStream_t stream = nullptr;
+    // Status word the kernels write when a bounded wait expires: mapped pinned
+    // host memory, so the host reads it without a copy.
+    volatile int *h_status = nullptr;
+    int *d_status = nullptr;
+    char err[512] = {0};
+    // Grow-only device staging areas for the host-buffer entry points.
+    struct Scratch {
+        void *ptr = nullptr;
+        size_t cap = 0;
+    } scratch[8];
+    bool force_generic = false;
+    bool use_pdl = false;
+    ullm::MatvecPlan last_plan;
+};
+
+inline int ctx_fail(ullm_cuda_ctx *c, int code, const char *fmt, ...) {
+    if (c) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(c->err, sizeof c->err, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define ULLM_CUDA_TRY(ctx, expr)                                                                   \
+    do {                                                                                           \
+        cudaError_t e__ = (expr);                                                                  \
+        if (e__ != cudaSuccess) {                                                                  \
+            cudaGetLastError();                                                                    \
+            return ctx_fail((ctx), e__ == cudaErrorMemoryAllocation ? 5 /*OOM*/ : 3 /*CUDA*/,      \
+                            "%s failed: %s", #expr, cudaGetErrorString(e__));                      \
+        }                                                                                          \
+    } while (0)
+
+// Device staging area `slot`, at least `bytes` large (never shrinks).
+inline int ctx_scratch(ullm_cuda_ctx *c, int slot, size_t bytes, void **out) {
+    auto &s = c->scratch[slot];
+    if (s.cap < bytes) {
+        if (s.ptr) {
+            cudaStreamSynchronize(c->stream);
+            cudaFree(s.ptr);
+            s.ptr = nullptr, s.cap = 0;
+        }
+        size_t cap = bytes < 4096 ? 4096 : bytes;
+        cudaError_t e = cudaMalloc(&s.ptr, cap);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            s.ptr = nullptr;
+            return ctx_fail(c, 5, "cudaMalloc(%zu) for staging failed: %s", cap, cudaGetErrorString(e));
+        }
+        s.cap = cap;
+    }
+    *out = s.ptr;
+    return 0;
+}
+
+// After a synchronize: turns a device-side timeout into ULLM_ERR_TIMEOUT.
+inline int ctx_check_status(ullm_cuda_ctx *c) {
+    if (c->h_status && *c->h_status != ullm::DEV_OK) {
+        *c->h_status = ullm::DEV_OK;
+        return ctx_fail(c, 4, "a device-side bounded wait expired (kernel gave up instead of hanging)");
+    }
+    return 0;
+}

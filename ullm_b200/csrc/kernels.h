@@ -1,0 +1,42 @@
+// Host-callable launchers of the CUDA kernels (internal C++ interface between
+// the kernel translation units and the C ABI in api.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace ullm {
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int max_smem_optin = 0; // bytes of dynamic shared memory a CTA may opt in to
+};
+
+// Where the scale / bias tables of an MLX matrix live and how wide they are.
+struct MlxTables {
+    const void *scales = nullptr;
+    const void *biases = nullptr;
+    int elem_bytes = 4; // 4 = f32, 2 = bf16 bits
+    size_t group = 0;
+};
+
+// dequant.cu
+cudaError_t launch_dequant(int dtype, const void *d_data, float *d_out, size_t n, cudaStream_t st);
+cudaError_t launch_dequant_mlx4(const uint32_t *d_w, const float *d_s, const float *d_b, float *d_y, size_t out_dim,
+                                size_t in_dim, size_t group, cudaStream_t st);
+
+// matvec.cu — y[o] = sum_i W[o,i] x[i].  fmt: 0 Q4_K, 1 Q6_K, 2 MLX4.
+// `status` is a device int the kernels set to non-zero when a bounded wait
+// expires.  `force_generic` selects the plain fallback kernel (tests).
+struct MatvecPlan {
+    bool streamed = false;
+    int rows_per_tile = 0, warps = 0, stages = 0, smem_bytes = 0, grid = 0;
+};
+cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const MlxTables &tb, const float *d_x,
+                          float *d_y, size_t out_dim, size_t in_dim, int *d_status, cudaStream_t st,
+                          bool force_generic = false, bool pdl = false, MatvecPlan *plan_out = nullptr);
+// Returns a static message when the shape cannot be computed at all.
+const char *matvec_shape_error(int fmt, size_t out_dim, size_t in_dim, size_t group);
+
+} // namespace ullm
