@@ -142,6 +142,9 @@ void ullm_cuda_experts_destroy(ullm_cuda_ctx *ctx, ullm_cuda_experts *e);
  * `idx` [n_tok, k] (uint32) and `wts` [n_tok, k] may be NULL. */
 int ullm_cuda_moe_ffn(ullm_cuda_ctx *ctx, const ullm_cuda_experts *e, const float *x, const float *logits, size_t n_tok,
                       size_t k, float *y, uint32_t *idx, float *wts);
+/* The same on device pointers, enqueued on `stream` (NULL = the context's). */
+int ullm_cuda_moe_ffn_dev(ullm_cuda_ctx *ctx, const ullm_cuda_experts *e, const float *d_x, const float *d_logits,
+                          size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *stream);
 
 /* ---- full decode step: GpuForward (forward.rs:162-757) ---- */
 typedef struct { /* GpuParams, forward.rs:24-51 */

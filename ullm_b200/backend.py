@@ -72,6 +72,7 @@ SIGNATURES = {
     "ullm_cuda_experts_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "ullm_cuda_experts_destroy": (None, [_vp, _vp]),
     "ullm_cuda_moe_ffn": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp]),
+    "ullm_cuda_moe_ffn_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     "ullm_cuda_forward_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "ullm_cuda_forward_destroy": (None, [_vp]),
     "ullm_cuda_forward": (_i, [_vp, _vp, _sz, _vp]),
@@ -264,3 +265,56 @@ class CudaContext:
         v = (C.c_int * 6)()
         self._lib.ullm_cuda_debug_last_plan(self._h, v, 6)
         return dict(zip(("streamed", "rows_per_tile", "warps", "stages", "smem_bytes", "grid"), list(v)))
+
+
+class MoeExpertsInput(C.Structure):
+    """``ullm_moe_experts_input`` (GpuExperts x3, crates/ullm-metal/src/forward.rs:67-75)."""
+
+    _fields_ = [(n, _vp) for n in ("gate_w", "gate_scales", "gate_biases", "up_w", "up_scales", "up_biases", "down_w", "down_scales", "down_biases")] + [
+        ("table_dtype", _i), ("n_experts", _sz), ("hidden", _sz), ("inter", _sz), ("group", _sz)]
+
+
+class Experts:
+    """Stacked MLX 4-bit experts resident on the device.  ``gate``/``up``/``down``
+    are ``(words u32, scales, biases)``; tables either f32 or bf16 bit patterns
+    (uint16), kept on the device in the type given."""
+
+    def __init__(self, ctx: CudaContext, gate, up, down, n_experts: int, hidden: int, inter: int, group: int):
+        self._ctx = ctx
+        bf16 = np.asarray(gate[1]).dtype == np.uint16
+        tdt = np.uint16 if bf16 else np.float32
+        keep, ptrs = [], []
+        for w, s, b in (gate, up, down):
+            arrs = [np.ascontiguousarray(w, np.uint32), np.ascontiguousarray(s, tdt), np.ascontiguousarray(b, tdt)]
+            keep += arrs
+            ptrs += [a.ctypes.data for a in arrs]
+        inp = MoeExpertsInput(*ptrs, BF16 if bf16 else F32, n_experts, hidden, inter, group)
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_experts_create(ctx._h, C.byref(inp), C.byref(h)))
+        self._h, self.n_experts, self.hidden, self.inter = h.value, n_experts, hidden, inter
+
+    def moe_ffn(self, x, logits, k: int, want_routing: bool = False):
+        """``moe_ffn`` for every token of x [n_tok, hidden] (crates/ullm-model/src/lib.rs:1453-1488)."""
+        x, lg = _f32(x).reshape(-1, self.hidden), _f32(logits).reshape(-1, self.n_experts)
+        n_tok = x.shape[0]
+        y = np.empty_like(x)
+        idx = np.empty((n_tok, k), np.uint32)
+        wts = np.empty((n_tok, k), np.float32)
+        c = self._ctx
+        c._check(c._lib.ullm_cuda_moe_ffn(c._h, self._h, _ptr(x), _ptr(lg), n_tok, k, _ptr(y), _ptr(idx), _ptr(wts)))
+        return (y, idx, wts) if want_routing else y
+
+    def moe_ffn_dev(self, d_x, d_logits, n_tok, k, d_y, stream=None):
+        c = self._ctx
+        c._check(c._lib.ullm_cuda_moe_ffn_dev(c._h, self._h, d_x, d_logits, n_tok, k, d_y, None, None, stream))
+
+    def free(self):
+        if self._h:
+            self._ctx._lib.ullm_cuda_experts_destroy(self._ctx._h, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

@@ -355,14 +355,103 @@ extern "C" int ullm_cuda_debug_last_plan(const ullm_cuda_ctx *c, int *vals, int 
 }
 
 // ---- not built yet -----------------------------------------------------------
-int ullm_cuda_experts_create(ullm_cuda_ctx *c, const ullm_moe_experts_input *, ullm_cuda_experts **) {
-    return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MoE experts are not built yet");
+// ---- mixture of experts ------------------------------------------------------
+struct ullm_cuda_experts {
+    MoeExperts e;
+    void *blob = nullptr;    // one allocation holding the nine arrays
+    void *scratch = nullptr; // routing table + per-pair intermediates
+};
+
+int ullm_cuda_experts_create(ullm_cuda_ctx *c, const ullm_moe_experts_input *in, ullm_cuda_experts **out) {
+    if (!c || !in || !out) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    const void *src[9] = {in->gate_w, in->gate_scales, in->gate_biases, in->up_w,       in->up_scales,
+                          in->up_biases, in->down_w,   in->down_scales, in->down_biases};
+    for (auto p : src)
+        if (!p) return ULLM_ERR_INVALID;
+    if (in->table_dtype != ULLM_DTYPE_F32 && in->table_dtype != ULLM_DTYPE_BF16)
+        return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MLX tables must be f32 or bf16");
+    MoeExperts e;
+    e.table_bytes = in->table_dtype == ULLM_DTYPE_F32 ? 4 : 2;
+    e.n_experts = in->n_experts, e.hidden = in->hidden, e.inter = in->inter, e.group = in->group;
+    if (const char *m = moe_shape_error(e, 1, 1)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    const size_t wb = e.n_experts * e.inter * e.hidden / 2; // same for gate, up and down
+    const size_t tb = e.n_experts * e.inter * (e.hidden / e.group) * e.table_bytes;
+    const size_t tbd = e.n_experts * e.hidden * (e.inter / e.group) * e.table_bytes;
+    const size_t sizes[9] = {wb, tb, tb, wb, tb, tb, wb, tbd, tbd};
+    size_t offs[9], total = 0;
+    for (int i = 0; i < 9; ++i) {
+        offs[i] = total;
+        total += (sizes[i] + 255) / 256 * 256;
+    }
+    ullm_cuda_experts *x = new (std::nothrow) ullm_cuda_experts();
+    if (!x) return ULLM_ERR_OOM;
+    cudaError_t err = cudaMalloc(&x->blob, total);
+    if (err == cudaSuccess) err = cudaMalloc(&x->scratch, moe_scratch_bytes(e));
+    for (int i = 0; i < 9 && err == cudaSuccess; ++i)
+        err = cudaMemcpyAsync((uint8_t *)x->blob + offs[i], src[i], sizes[i], cudaMemcpyHostToDevice, c->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(c->stream);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        ullm_cuda_experts_destroy(c, x);
+        return ctx_fail(c, err == cudaErrorMemoryAllocation ? ULLM_ERR_OOM : ULLM_ERR_CUDA, "experts upload: %s",
+                        cudaGetErrorString(err));
+    }
+    const uint8_t *b = (const uint8_t *)x->blob;
+    e.gate_w = b + offs[0], e.gate_s = b + offs[1], e.gate_b = b + offs[2];
+    e.up_w = b + offs[3], e.up_s = b + offs[4], e.up_b = b + offs[5];
+    e.down_w = b + offs[6], e.down_s = b + offs[7], e.down_b = b + offs[8];
+    x->e = e;
+    *out = x;
+    return ULLM_OK;
 }
-void ullm_cuda_experts_destroy(ullm_cuda_ctx *, ullm_cuda_experts *) {}
-int ullm_cuda_moe_ffn(ullm_cuda_ctx *c, const ullm_cuda_experts *, const float *, const float *, size_t, size_t, float *,
-                      uint32_t *, float *) {
-    return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MoE FFN is not built yet");
+
+void ullm_cuda_experts_destroy(ullm_cuda_ctx *c, ullm_cuda_experts *x) {
+    if (!x) return;
+    if (c) cudaSetDevice(c->device);
+    if (x->blob) cudaFree(x->blob);
+    if (x->scratch) cudaFree(x->scratch);
+    delete x;
 }
+
+int ullm_cuda_moe_ffn_dev(ullm_cuda_ctx *c, const ullm_cuda_experts *x, const float *d_x, const float *d_logits,
+                          size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *stream) {
+    if (!c || !x || !d_x || !d_logits || !d_y) return ULLM_ERR_INVALID;
+    if (const char *m = moe_shape_error(x->e, n_tok, k)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    int streamed = 0;
+    ULLM_CUDA_TRY(c, launch_moe_ffn(c->dev, x->e, d_x, d_logits, n_tok, k, d_y, d_idx, d_wts, x->scratch, c->d_status, st,
+                                    c->force_generic, c->use_pdl, &streamed));
+    c->last_plan = MatvecPlan();
+    c->last_plan.streamed = streamed != 0;
+    return ULLM_OK;
+}
+
+int ullm_cuda_moe_ffn(ullm_cuda_ctx *c, const ullm_cuda_experts *x, const float *xs, const float *logits, size_t n_tok,
+                      size_t k, float *y, uint32_t *idx, float *wts) {
+    if (!c || !x || !xs || !logits || !y) return ULLM_ERR_INVALID;
+    if (const char *m = moe_shape_error(x->e, n_tok, k)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    const size_t xb = n_tok * x->e.hidden * 4, lb = n_tok * x->e.n_experts * 4, kb = n_tok * k * 4;
+    void *d_x = nullptr, *d_l = nullptr, *d_y = nullptr, *d_i = nullptr, *d_w = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 4, xb, &d_x)) || (rc = ctx_scratch(c, 5, xb, &d_y)) || (rc = ctx_scratch(c, 6, lb, &d_l)) ||
+        (rc = ctx_scratch(c, 2, kb, &d_i)) || (rc = ctx_scratch(c, 3, kb, &d_w)))
+        return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_x, xs, xb, cudaMemcpyHostToDevice, c->stream));
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_l, logits, lb, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = ullm_cuda_moe_ffn_dev(c, x, (const float *)d_x, (const float *)d_l, n_tok, k, (float *)d_y, (uint32_t *)d_i,
+                                    (float *)d_w, nullptr)))
+        return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, xb, cudaMemcpyDeviceToHost, c->stream));
+    if (idx) ULLM_CUDA_TRY(c, cudaMemcpyAsync(idx, d_i, kb, cudaMemcpyDeviceToHost, c->stream));
+    if (wts) ULLM_CUDA_TRY(c, cudaMemcpyAsync(wts, d_w, kb, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ctx_check_status(c);
+}
+
 int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *, ullm_cuda_fwd **) {
     return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "decode step is not built yet");
 }

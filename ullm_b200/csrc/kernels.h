@@ -39,4 +39,21 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
 // Returns a static message when the shape cannot be computed at all.
 const char *matvec_shape_error(int fmt, size_t out_dim, size_t in_dim, size_t group);
 
+// moe.cu — stacked MLX 4-bit experts resident on the device.
+struct MoeExperts {
+    const void *gate_w = nullptr, *gate_s = nullptr, *gate_b = nullptr;
+    const void *up_w = nullptr, *up_s = nullptr, *up_b = nullptr;
+    const void *down_w = nullptr, *down_s = nullptr, *down_b = nullptr;
+    int table_bytes = 4; // 4 = f32 tables, 2 = bf16 bits
+    size_t n_experts = 0, hidden = 0, inter = 0, group = 0;
+};
+// Bytes of scratch (routing table + per-pair intermediates) one call needs.
+size_t moe_scratch_bytes(const MoeExperts &e);
+const char *moe_shape_error(const MoeExperts &e, size_t n_tok, size_t k);
+// x [n_tok, hidden], logits [n_tok, n_experts] -> y [n_tok, hidden]; d_idx / d_wts
+// ([n_tok, k]) may be null.  Everything is a device pointer.
+cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const float *d_x, const float *d_logits,
+                           size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *d_scratch,
+                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out);
+
 } // namespace ullm

@@ -1,0 +1,483 @@
+// Mixture-of-experts SwiGLU FFN on MLX 4-bit stacked experts, for a few tokens
+// at once (CPU form: crates/ullm-model/src/lib.rs:1453-1488; GPU form:
+// crates/ullm-metal/src/forward.rs:484-494 with shader.metal:301-444).
+//
+// Four launches:
+//   1. route   : per token, top-k experts by descending router logit (ties: lower
+//                index first) and softmax over the selected logits; then the
+//                (token, slot) pairs are grouped by expert so each distinct
+//                expert's weights are read from HBM once for all tokens that
+//                picked it.
+//   2. gate_up : expert-gathered  hidden[pair] = silu(W_gate[e] x_t) * (W_up[e] x_t)
+//   3. down    : expert-gathered  down[pair]   = W_down[e] hidden[pair]
+//   4. combine : y[t] = sum over slots, in descending-logit order, of w * down
+//                (the order the reference accumulates in, lib.rs:1479-1488).
+// Kernels 2 and 3 are streamed like the dense matvec: persistent CTAs, each
+// owning a contiguous range of (expert, row-tile) units so that it meets one or
+// two experts only, weights and group tables arriving through a TMA-bulk ring;
+// activations are re-expressed as 16-bit fixed point in shared memory per CTA
+// and the products are integer dp4a sums scaled in fp32 (see matvec.cu).
+// A plain gather kernel covers shapes the streamed layout rules exclude.
+#include "kernels.h"
+#include "matvec_core.cuh"
+
+#include <algorithm>
+
+namespace ullm {
+
+constexpr int MOE_MAX_TOK = 8;   // tokens per launch group
+constexpr int MOE_MAX_K = 16;    // experts per token (reference kernel cap, shader.metal:310)
+constexpr int MOE_MAX_EXPERTS = 1024;
+
+// Layout of the routing scratch (ints): [0] D = number of distinct experts,
+// [1 .. 1+E) expert ids ascending, [1+E .. 2+2E) pair offsets, then pair ids.
+__host__ __device__ inline int route_off_list() { return 1; }
+__host__ __device__ inline int route_off_offs(int E) { return 1 + E; }
+__host__ __device__ inline int route_off_pairs(int E) { return 2 + 2 * E; }
+
+// ---------------------------------------------------------------------------
+// 1. routing
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict__ logits, int n_tok, int n_exp, int k,
+                                                       uint32_t *__restrict__ idx, float *__restrict__ wts,
+                                                       int *__restrict__ route) {
+    __shared__ float lg[MOE_MAX_EXPERTS];
+    __shared__ int sel[MOE_MAX_TOK * MOE_MAX_K];
+    __shared__ int cnt[MOE_MAX_EXPERTS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    pdl_wait_prior();
+    for (int t = 0; t < n_tok; ++t) {
+        // token t is handled by warp t % nwarp; logits staged per warp would need
+        // nwarp copies, so tokens are simply processed one after another by warp 0..:
+        // n_tok <= 8 and n_exp <= 1024, this kernel is a few microseconds.
+        __syncthreads();
+        for (int i = threadIdx.x; i < n_exp; i += blockDim.x) lg[i] = logits[(size_t)t * n_exp + i];
+        __syncthreads();
+        if (warp == 0) {
+            float selv[MOE_MAX_K];
+            for (int j = 0; j < k; ++j) {
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                for (int i = lane; i < n_exp; i += 32) {
+                    float v = lg[i];
+                    if (v > bv || (v == bv && i < bi)) bv = v, bi = i; // first index wins
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+                }
+                selv[j] = bv;
+                if (lane == 0) {
+                    sel[t * k + j] = bi;
+                    lg[bi] = -INFINITY; // taken (a logit of -inf itself can then be picked twice only if k > finite count)
+                }
+                __syncwarp();
+            }
+            if (lane == 0) {
+                // softmax over the k selected logits (lib.rs:1460-1475): max is the first
+                float mx = selv[0], wsum = 0.f, e[MOE_MAX_K];
+                for (int j = 0; j < k; ++j) {
+                    e[j] = expf(selv[j] - mx);
+                    wsum += e[j];
+                }
+                for (int j = 0; j < k; ++j) {
+                    wts[t * k + j] = e[j] / wsum;
+                    idx[t * k + j] = (uint32_t)sel[t * k + j];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // group the pairs by expert (ascending expert id, pairs in (token, slot) order)
+    const int npairs = n_tok * k;
+    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) {
+        int c = 0;
+        for (int p = 0; p < npairs; ++p) c += sel[p] == e;
+        cnt[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int D = 0, off = 0;
+        int *list = route + route_off_list(), *offs = route + route_off_offs(n_exp), *pairs = route + route_off_pairs(n_exp);
+        for (int e = 0; e < n_exp; ++e) {
+            if (!cnt[e]) continue;
+            list[D] = e;
+            offs[D] = off;
+            for (int p = 0; p < npairs; ++p)
+                if (sel[p] == e) pairs[off++] = p;
+            ++D;
+        }
+        offs[D] = off;
+        route[0] = D;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 2/3. streamed expert-gathered kernels
+// ---------------------------------------------------------------------------
+struct MoeStreamParams {
+    // matrices of this launch: NM = 2 (gate, up) or 1 (down); stacked over experts
+    const uint8_t *w[2], *sc[2], *bi[2];
+    const float *act;  // gate_up: x [n_tok, in]; down: hidden [n_pairs, in]
+    float *out;        // gate_up: hidden [n_pairs, rows]; down: down_out [n_pairs, rows]
+    const int *route;
+    int *status;
+    uint32_t n_exp, k, n_tok;
+    uint32_t rows, in_dim, group; // per-expert matrix [rows, in_dim]
+    uint32_t row_bytes, tbl_row_bytes;
+    uint32_t R, NW, S, tiles_per_expert, ncg;
+    uint32_t w_stage_bytes, tbl_stage_bytes, stage_bytes; // one matrix' regions; stage = NM * (w + 2 tbl)
+    uint32_t off_q, off_ring;
+};
+
+// GATE_UP: two matrices, x indexed by token, epilogue silu(g)*u.
+template <bool GATE_UP, int G, typename TBL>
+__global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParams p) {
+    constexpr int XR = XREGS_MLX, NM = GATE_UP ? 2 : 1;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = (uint64_t *)smem;
+    uint64_t *empty = full + p.S;
+    uint32_t *qimg = (uint32_t *)(smem + p.off_q); // [vec][cg][XR][32]
+    uint8_t *ring = smem + p.off_ring;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool producer = warp == p.NW;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < p.S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], p.NW);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_wait_prior(); // the routing table and the activations come from earlier kernels
+
+    const int D = p.route[0];
+    const int *ex_list = p.route + route_off_list(), *ex_off = p.route + route_off_offs(p.n_exp),
+              *pairs = p.route + route_off_pairs(p.n_exp);
+    const uint32_t U = (uint32_t)D * p.tiles_per_expert;
+    const uint32_t u0 = (uint32_t)(((uint64_t)U * blockIdx.x) / gridDim.x),
+                   u1 = (uint32_t)(((uint64_t)U * (blockIdx.x + 1)) / gridDim.x);
+
+    if (producer) {
+        if (lane == 0) {
+            uint32_t kk = 0;
+            for (uint32_t u = u0; u < u1; ++u, ++kk) {
+                const uint32_t s = kk % p.S;
+                if (kk >= p.S && !wait_or_timeout(&empty[s], ((kk / p.S) - 1) & 1)) {
+                    *(volatile int *)p.status = DEV_TIMEOUT;
+                    break;
+                }
+                const uint32_t d = u / p.tiles_per_expert, rt = u % p.tiles_per_expert;
+                const uint32_t e = (uint32_t)ex_list[d], r0 = rt * p.R;
+                const uint32_t nrows = min(p.R, p.rows - r0);
+                const uint32_t wb = nrows * p.row_bytes, tb = nrows * p.tbl_row_bytes;
+                const size_t grow = (size_t)e * p.rows + r0;
+                uint8_t *dst = ring + (size_t)s * p.stage_bytes;
+                mbar_arrive_expect_tx(&full[s], NM * (wb + 2 * tb));
+#pragma unroll
+                for (int m = 0; m < NM; ++m) {
+                    uint8_t *dm = dst + m * (p.w_stage_bytes + 2 * p.tbl_stage_bytes);
+                    bulk_g2s(dm, p.w[m] + grow * p.row_bytes, wb, &full[s]);
+                    bulk_g2s(dm + p.w_stage_bytes, p.sc[m] + grow * p.tbl_row_bytes, tb, &full[s]);
+                    bulk_g2s(dm + p.w_stage_bytes + p.tbl_stage_bytes, p.bi[m] + grow * p.tbl_row_bytes, tb, &full[s]);
+                }
+            }
+        }
+        return;
+    }
+
+    const uint32_t nthr_c = p.NW * 32; // consumer threads (named barrier 1)
+    if (GATE_UP) {
+        // every token's x, once per CTA
+        for (uint32_t sl = tid; sl < p.n_tok * p.ncg * 32u; sl += nthr_c) {
+            const uint32_t t = sl / (p.ncg * 32u), rem = sl % (p.ncg * 32u);
+            prep_slot<FMT_MLX4>(p.act + (size_t)t * p.in_dim, p.in_dim, rem >> 5, rem & 31u,
+                                qimg + ((size_t)(t * p.ncg + (rem >> 5)) * XR) * 32 + (rem & 31u));
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
+    }
+
+    bool aborted = false;
+    int cur_d = -1;
+    uint32_t kk = 0;
+    const uint32_t RW = p.R / p.NW;
+    for (uint32_t u = u0; u < u1; ++u, ++kk) {
+        const uint32_t s = kk % p.S;
+        const uint32_t d = u / p.tiles_per_expert, rt = u % p.tiles_per_expert, r0 = rt * p.R;
+        const int pb = ex_off[d], np = ex_off[d + 1] - pb;
+        if (!GATE_UP && (int)d != cur_d) {
+            // new expert: fixed-point images of the hidden vectors of its pairs
+            asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // everyone done with the previous images
+            for (uint32_t sl = tid; sl < (uint32_t)np * p.ncg * 32u; sl += nthr_c) {
+                const uint32_t j = sl / (p.ncg * 32u), rem = sl % (p.ncg * 32u);
+                prep_slot<FMT_MLX4>(p.act + (size_t)pairs[pb + j] * p.in_dim, p.in_dim, rem >> 5, rem & 31u,
+                                    qimg + ((size_t)(j * p.ncg + (rem >> 5)) * XR) * 32 + (rem & 31u));
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
+        }
+        cur_d = (int)d;
+        if (!aborted && !wait_or_timeout(&full[s], (kk / p.S) & 1)) aborted = true;
+        const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
+        const uint32_t mstride = p.w_stage_bytes + 2 * p.tbl_stage_bytes;
+        for (int j = 0; j < np && !aborted; ++j) {
+            const int pair = pairs[pb + j];
+            const uint32_t vec = GATE_UP ? (uint32_t)pair / p.k : (uint32_t)j;
+            uint32_t X[G][XR];
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+                for (int q = 0; q < XR; ++q)
+                    X[g][q] = (uint32_t)g < p.ncg ? qimg[((size_t)(vec * p.ncg + g) * XR + q) * 32 + lane] : 0u;
+            for (uint32_t rr = 0; rr < RW; ++rr) {
+                const uint32_t rl = warp * RW + rr;
+                if (r0 + rl >= p.rows) break;
+                float acc[NM];
+#pragma unroll
+                for (int m = 0; m < NM; ++m) {
+                    acc[m] = 0.f;
+                    const uint32_t base = stage + m * mstride;
+                    const uint32_t ts = base + p.w_stage_bytes + rl * p.tbl_row_bytes;
+#pragma unroll
+                    for (int g = 0; g < G; ++g)
+                        if ((uint32_t)g < p.ncg && (g * 32u + lane) * 32u < p.in_dim)
+                            acc[m] += row_partial<FMT_MLX4, TBL>(base + rl * p.row_bytes, X[g], g, lane, ts,
+                                                                 ts + p.tbl_stage_bytes, p.group);
+                    acc[m] = warp_sum(acc[m]);
+                }
+                if (lane == 0) {
+                    float v;
+                    if (GATE_UP) v = acc[0] / (1.0f + expf(-acc[0])) * acc[NM - 1]; // math.rs:103-105, lib.rs:1482
+                    else v = acc[0];
+                    p.out[(size_t)pair * p.rows + r0 + rl] = v;
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
+}
+
+// ---------------------------------------------------------------------------
+// Plain gather kernels (any shape the format allows): one warp per (pair, row)
+// ---------------------------------------------------------------------------
+template <typename TBL>
+__device__ __forceinline__ float mlx_row_dot(const uint32_t *__restrict__ row, const TBL *__restrict__ sc,
+                                             const TBL *__restrict__ bi, const float *__restrict__ x, uint32_t in_dim,
+                                             uint32_t group, uint32_t lane) {
+    float acc = 0.f;
+    const uint32_t words = in_dim / 8;
+    for (uint32_t wi = lane; wi < words; wi += 32) {
+        uint32_t q = row[wi];
+        uint32_t g = (wi * 8) / group;
+        float s = tbl_load<TBL>(sc + g), b = tbl_load<TBL>(bi + g);
+        const float4 xa = *(const float4 *)(x + wi * 8), xb = *(const float4 *)(x + wi * 8 + 4);
+        float dot = (float)(q & 15) * xa.x + (float)((q >> 4) & 15) * xa.y + (float)((q >> 8) & 15) * xa.z +
+                    (float)((q >> 12) & 15) * xa.w + (float)((q >> 16) & 15) * xb.x + (float)((q >> 20) & 15) * xb.y +
+                    (float)((q >> 24) & 15) * xb.z + (float)(q >> 28) * xb.w;
+        acc += s * dot + b * (xa.x + xa.y + xa.z + xa.w + xb.x + xb.y + xb.z + xb.w);
+    }
+    return warp_sum(acc);
+}
+
+template <bool GATE_UP, typename TBL>
+__global__ void __launch_bounds__(256) moe_gather_kernel(const uint32_t *__restrict__ w0, const TBL *__restrict__ s0,
+                                                        const TBL *__restrict__ b0, const uint32_t *__restrict__ w1,
+                                                        const TBL *__restrict__ s1, const TBL *__restrict__ b1,
+                                                        const float *__restrict__ act, float *__restrict__ out,
+                                                        const uint32_t *__restrict__ idx, uint32_t k, uint32_t rows,
+                                                        uint32_t in_dim, uint32_t group) {
+    const uint32_t lane = threadIdx.x & 31, pair = blockIdx.y;
+    const uint32_t o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (o >= rows) return;
+    const uint32_t e = idx[pair];
+    const size_t grow = (size_t)e * rows + o, words = in_dim / 8, groups = in_dim / group;
+    const float *x = act + (size_t)(GATE_UP ? pair / k : pair) * in_dim;
+    float a = mlx_row_dot<TBL>(w0 + grow * words, s0 + grow * groups, b0 + grow * groups, x, in_dim, group, lane);
+    if (GATE_UP) {
+        float u = mlx_row_dot<TBL>(w1 + grow * words, s1 + grow * groups, b1 + grow * groups, x, in_dim, group, lane);
+        a = a / (1.0f + expf(-a)) * u;
+    }
+    if (lane == 0) out[(size_t)pair * rows + o] = a;
+}
+
+// 4. y[t][o] = sum_slot wts[t][slot] * down[t*k+slot][o]   (lib.rs:1484-1487)
+__global__ void moe_combine_kernel(const float *__restrict__ down, const float *__restrict__ wts, float *__restrict__ y,
+                                   uint32_t n_tok, uint32_t k, uint32_t hidden) {
+    pdl_wait_prior();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tok * hidden) return;
+    const uint32_t t = i / hidden, o = i % hidden;
+    float acc = 0.f;
+    for (uint32_t s = 0; s < k; ++s) acc += wts[t * k + s] * down[((size_t)t * k + s) * hidden + o];
+    y[i] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+static inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+struct MoePlanInt {
+    bool ok = false;
+    MoeStreamParams p{};
+    int g = 1, grid = 0, threads = 0;
+    uint32_t smem = 0;
+};
+
+static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, uint32_t in_dim, uint32_t group,
+                           int tbl_bytes, uint32_t n_vec) {
+    MoePlanInt best;
+    if (in_dim % 32 || group % 32 || in_dim % group) return best;
+    const uint32_t NM = gate_up ? 2 : 1;
+    const uint32_t row_bytes = in_dim / 2, tbl_row_bytes = (in_dim / group) * tbl_bytes;
+    const uint32_t ncg = (in_dim + 1023) / 1024;
+    if (ncg > 4) return best;
+    const uint32_t G = ncg <= 1 ? 1 : (ncg <= 2 ? 2 : 4);
+    const uint32_t NW = 16;
+    const int budget = dev.max_smem_optin - 1024;
+    const uint32_t off_q = 128;
+    const uint32_t off_ring = align_up(off_q + n_vec * ncg * XREGS_MLX * 32 * 4, 128);
+    for (uint32_t RW = 1; RW <= 4; RW *= 2) {
+        const uint32_t R = NW * RW;
+        if ((R * row_bytes) % 16 || (R * tbl_row_bytes) % 16) continue;
+        if (rows % R && ((row_bytes % 16) || (tbl_row_bytes % 16))) continue;
+        const uint32_t wst = align_up(R * row_bytes, 128), tst = align_up(R * tbl_row_bytes, 128);
+        const uint32_t stage = NM * (wst + 2 * tst);
+        if (stage > 40 * 1024 && best.ok) continue;
+        if ((int)(off_ring + 2 * stage) > budget) continue;
+        const uint32_t S = std::min<uint32_t>(8, (budget - off_ring) / stage);
+        // prefer ~16-36 KB stages
+        if (best.ok && stage > 36 * 1024) continue;
+        best.ok = true;
+        best.g = (int)G;
+        best.threads = (int)(NW + 1) * 32;
+        best.grid = dev.sm_count;
+        best.smem = off_ring + S * stage;
+        MoeStreamParams &p = best.p;
+        p.rows = rows, p.in_dim = in_dim, p.group = group, p.row_bytes = row_bytes, p.tbl_row_bytes = tbl_row_bytes;
+        p.R = R, p.NW = NW, p.S = S, p.tiles_per_expert = (rows + R - 1) / R, p.ncg = ncg;
+        p.w_stage_bytes = wst, p.tbl_stage_bytes = tst, p.stage_bytes = stage;
+        p.off_q = off_q, p.off_ring = off_ring;
+    }
+    return best;
+}
+
+template <bool GATE_UP, int G, typename TBL> static cudaError_t launch_moe_t(const MoePlanInt &pl, cudaStream_t st, bool pdl) {
+    auto kfn = moe_stream_kernel<GATE_UP, G, TBL>;
+    static bool attr_set[64] = {};
+    int devid = 0;
+    cudaGetDevice(&devid);
+    if (devid < 64 && !attr_set[devid]) {
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[devid] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.grid), cfg.blockDim = dim3(pl.threads), cfg.dynamicSmemBytes = pl.smem, cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kfn, pl.p);
+}
+template <bool GATE_UP, typename TBL> static cudaError_t launch_moe_g(const MoePlanInt &pl, cudaStream_t st, bool pdl) {
+    if (pl.g == 1) return launch_moe_t<GATE_UP, 1, TBL>(pl, st, pdl);
+    if (pl.g == 2) return launch_moe_t<GATE_UP, 2, TBL>(pl, st, pdl);
+    return launch_moe_t<GATE_UP, 4, TBL>(pl, st, pdl);
+}
+
+size_t moe_scratch_bytes(const MoeExperts &e) {
+    const size_t pairs = (size_t)MOE_MAX_TOK * MOE_MAX_K;
+    size_t route = (size_t)(route_off_pairs((int)e.n_experts) + pairs) * 4;
+    route = (route + 255) / 256 * 256;
+    return route + pairs * e.inter * 4 + pairs * e.hidden * 4 + pairs * 8 + 1024;
+}
+
+const char *moe_shape_error(const MoeExperts &e, size_t n_tok, size_t k) {
+    if (e.n_experts == 0 || e.n_experts > MOE_MAX_EXPERTS) return "number of experts must be 1..1024";
+    if (k == 0 || k > MOE_MAX_K || k > e.n_experts) return "experts per token must be 1..16 and <= n_experts";
+    if (n_tok == 0) return "no tokens";
+    if (e.hidden % 8 || e.inter % 8 || e.group == 0 || e.group % 8 || e.hidden % e.group || e.inter % e.group)
+        return "hidden / inter must be multiples of the group size, group a multiple of 8";
+    return nullptr;
+}
+
+cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const float *d_x, const float *d_logits,
+                           size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *d_scratch,
+                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out) {
+    // scratch carve-up
+    const size_t pairs_cap = (size_t)MOE_MAX_TOK * MOE_MAX_K;
+    uint8_t *sp = (uint8_t *)d_scratch;
+    int *route = (int *)sp;
+    size_t route_b = ((size_t)(route_off_pairs((int)e.n_experts) + pairs_cap) * 4 + 255) / 256 * 256;
+    float *hidden = (float *)(sp + route_b);
+    float *down = hidden + pairs_cap * e.inter;
+    uint32_t *idx_s = (uint32_t *)(down + pairs_cap * e.hidden);
+    float *wts_s = (float *)(idx_s + pairs_cap);
+    const uint32_t tb = (uint32_t)e.table_bytes;
+    const bool aligned = ((uintptr_t)d_x % 16 == 0);
+    if (streamed_out) *streamed_out = 0;
+
+    for (size_t t0 = 0; t0 < n_tok; t0 += MOE_MAX_TOK) {
+        const uint32_t nt = (uint32_t)std::min<size_t>(MOE_MAX_TOK, n_tok - t0), npairs = nt * (uint32_t)k;
+        const float *x = d_x + t0 * e.hidden;
+        uint32_t *idx = d_idx ? d_idx + t0 * k : idx_s;
+        float *wts = d_wts ? d_wts + t0 * k : wts_s;
+        moe_route_kernel<<<1, 256, 0, st>>>(d_logits + t0 * e.n_experts, (int)nt, (int)e.n_experts, (int)k, idx, wts, route);
+        cudaError_t err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+
+        MoePlanInt pg, pd;
+        if (!force_generic && aligned) {
+            pg = plan_moe(dev, true, (uint32_t)e.inter, (uint32_t)e.hidden, (uint32_t)e.group, (int)tb, nt);
+            pd = plan_moe(dev, false, (uint32_t)e.hidden, (uint32_t)e.inter, (uint32_t)e.group, (int)tb, nt);
+        }
+        if (pg.ok && pd.ok) {
+            if (streamed_out) *streamed_out = 1;
+            MoeStreamParams &a = pg.p;
+            a.w[0] = (const uint8_t *)e.gate_w, a.sc[0] = (const uint8_t *)e.gate_s, a.bi[0] = (const uint8_t *)e.gate_b;
+            a.w[1] = (const uint8_t *)e.up_w, a.sc[1] = (const uint8_t *)e.up_s, a.bi[1] = (const uint8_t *)e.up_b;
+            a.act = x, a.out = hidden, a.route = route, a.status = d_status;
+            a.n_exp = (uint32_t)e.n_experts, a.k = (uint32_t)k, a.n_tok = nt;
+            err = tb == 2 ? launch_moe_g<true, uint16_t>(pg, st, pdl) : launch_moe_g<true, float>(pg, st, pdl);
+            if (err != cudaSuccess) return err;
+            MoeStreamParams &b = pd.p;
+            b.w[0] = (const uint8_t *)e.down_w, b.sc[0] = (const uint8_t *)e.down_s, b.bi[0] = (const uint8_t *)e.down_b;
+            b.w[1] = nullptr, b.sc[1] = nullptr, b.bi[1] = nullptr;
+            b.act = hidden, b.out = down, b.route = route, b.status = d_status;
+            b.n_exp = (uint32_t)e.n_experts, b.k = (uint32_t)k, b.n_tok = nt;
+            err = tb == 2 ? launch_moe_g<false, uint16_t>(pd, st, pdl) : launch_moe_g<false, float>(pd, st, pdl);
+            if (err != cudaSuccess) return err;
+        } else {
+            dim3 g1((unsigned)((e.inter + 7) / 8), npairs), g2((unsigned)((e.hidden + 7) / 8), npairs);
+            if (tb == 2) {
+                moe_gather_kernel<true, uint16_t><<<g1, 256, 0, st>>>(
+                    (const uint32_t *)e.gate_w, (const uint16_t *)e.gate_s, (const uint16_t *)e.gate_b,
+                    (const uint32_t *)e.up_w, (const uint16_t *)e.up_s, (const uint16_t *)e.up_b, x, hidden, idx,
+                    (uint32_t)k, (uint32_t)e.inter, (uint32_t)e.hidden, (uint32_t)e.group);
+                moe_gather_kernel<false, uint16_t><<<g2, 256, 0, st>>>(
+                    (const uint32_t *)e.down_w, (const uint16_t *)e.down_s, (const uint16_t *)e.down_b, nullptr, nullptr,
+                    nullptr, hidden, down, idx, (uint32_t)k, (uint32_t)e.hidden, (uint32_t)e.inter, (uint32_t)e.group);
+            } else {
+                moe_gather_kernel<true, float><<<g1, 256, 0, st>>>(
+                    (const uint32_t *)e.gate_w, (const float *)e.gate_s, (const float *)e.gate_b,
+                    (const uint32_t *)e.up_w, (const float *)e.up_s, (const float *)e.up_b, x, hidden, idx, (uint32_t)k,
+                    (uint32_t)e.inter, (uint32_t)e.hidden, (uint32_t)e.group);
+                moe_gather_kernel<false, float><<<g2, 256, 0, st>>>(
+                    (const uint32_t *)e.down_w, (const float *)e.down_s, (const float *)e.down_b, nullptr, nullptr, nullptr,
+                    hidden, down, idx, (uint32_t)k, (uint32_t)e.hidden, (uint32_t)e.inter, (uint32_t)e.group);
+            }
+            if ((err = cudaGetLastError()) != cudaSuccess) return err;
+        }
+        const uint32_t n = nt * (uint32_t)e.hidden;
+        moe_combine_kernel<<<(n + 255) / 256, 256, 0, st>>>(down, wts, d_y + t0 * e.hidden, nt, (uint32_t)k, (uint32_t)e.hidden);
+        if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    }
+    return cudaSuccess;
+}
+
+} // namespace ullm
