@@ -46,7 +46,7 @@ def test_moe_golden_fixture(ctx):
 @pytest.mark.parametrize("ne,hid,inter,gs,ntok,k", [
     (8, 256, 128, 64, 3, 2),     # small
     (16, 1024, 96, 32, 8, 4),    # inter not a multiple of the row tile; group 32
-    (6, 2048, 64, 128, 11, 3),   # more than 8 tokens: two launch groups; two column groups
+    (6, 2048, 128, 128, 11, 3),  # more than 8 tokens: two launch groups; two column groups
     (5, 64, 64, 64, 1, 5),       # every expert chosen by the one token
 ])
 def test_moe_matches_oracle(ctx, ne, hid, inter, gs, ntok, k, f32_tables, generic):

@@ -50,9 +50,24 @@ __device__ __forceinline__ int quant16(float v, float inv) {
 
 // Fills the persistent register image of (column group cg, lane ln) at
 // slot[k * 32] (k = 0..XREGS-1; the caller passes slot already offset by lane).
+// The vector a matvec consumes: x itself, or rmsnorm(x) = x[i] * inv * norm_w[i]
+// (crates/ullm-model/src/math.rs:82-86) when norm_w is given.
+struct ActSrc {
+    const float *x;
+    const float *norm_w; // may be null
+    float inv;           // 1 / sqrt(mean(x^2) + eps) when norm_w is set
+};
+__device__ __forceinline__ float4 act_load4(const ActSrc &a, uint32_t i) {
+    float4 t = __ldg((const float4 *)(a.x + i));
+    if (a.norm_w) {
+        float4 w = __ldg((const float4 *)(a.norm_w + i));
+        t.x = t.x * a.inv * w.x, t.y = t.y * a.inv * w.y, t.z = t.z * a.inv * w.z, t.w = t.w * a.inv * w.w;
+    }
+    return t;
+}
+
 template <int FMT>
-__device__ __forceinline__ void prep_slot(const float *__restrict__ x, uint32_t in_dim, uint32_t cg, uint32_t ln,
-                                          uint32_t *slot) {
+__device__ __forceinline__ void prep_slot(const ActSrc &src, uint32_t in_dim, uint32_t cg, uint32_t ln, uint32_t *slot) {
     constexpr int XR = FmtTraits<FMT>::XREGS;
     if constexpr (FMT == FMT_Q4K) {
         // lane: block 8cg + ln/4, chunk c = ln%4: low nibbles = elements [64c,64c+32),
@@ -66,10 +81,9 @@ __device__ __forceinline__ void prep_slot(const float *__restrict__ x, uint32_t 
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             float v[32];
-            const float4 *xp = (const float4 *)(x + e0 + 32 * half);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                float4 t = __ldg(xp + i);
+                float4 t = act_load4(src, e0 + 32 * half + 4 * i);
                 v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
             }
             float mx = 0.f, sum = 0.f;
@@ -105,8 +119,7 @@ __device__ __forceinline__ void prep_slot(const float *__restrict__ x, uint32_t 
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             float v[8];
-            const float4 *xp = (const float4 *)(x + e0 + 32 * g);
-            float4 t0 = __ldg(xp), t1 = __ldg(xp + 1);
+            float4 t0 = act_load4(src, e0 + 32 * g), t1 = act_load4(src, e0 + 32 * g + 4);
             v[0] = t0.x, v[1] = t0.y, v[2] = t0.z, v[3] = t0.w, v[4] = t1.x, v[5] = t1.y, v[6] = t1.z, v[7] = t1.w;
             float mx = 0.f;
 #pragma unroll
@@ -140,10 +153,9 @@ __device__ __forceinline__ void prep_slot(const float *__restrict__ x, uint32_t 
             return;
         }
         float v[32];
-        const float4 *xp = (const float4 *)(x + e0);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            float4 t = __ldg(xp + i);
+            float4 t = act_load4(src, e0 + 4 * i);
             v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
         }
         float mx = 0.f, sum = 0.f;

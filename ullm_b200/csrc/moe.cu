@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         // every token's x, once per CTA
         for (uint32_t sl = tid; sl < p.n_tok * p.ncg * 32u; sl += nthr_c) {
             const uint32_t t = sl / (p.ncg * 32u), rem = sl % (p.ncg * 32u);
-            prep_slot<FMT_MLX4>(p.act + (size_t)t * p.in_dim, p.in_dim, rem >> 5, rem & 31u,
+            prep_slot<FMT_MLX4>(ActSrc{p.act + (size_t)t * p.in_dim, nullptr, 0.f}, p.in_dim, rem >> 5, rem & 31u,
                                 qimg + ((size_t)(t * p.ncg + (rem >> 5)) * XR) * 32 + (rem & 31u));
         }
         asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
             asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // everyone done with the previous images
             for (uint32_t sl = tid; sl < (uint32_t)np * p.ncg * 32u; sl += nthr_c) {
                 const uint32_t j = sl / (p.ncg * 32u), rem = sl % (p.ncg * 32u);
-                prep_slot<FMT_MLX4>(p.act + (size_t)pairs[pb + j] * p.in_dim, p.in_dim, rem >> 5, rem & 31u,
+                prep_slot<FMT_MLX4>(ActSrc{p.act + (size_t)pairs[pb + j] * p.in_dim, nullptr, 0.f}, p.in_dim, rem >> 5, rem & 31u,
                                     qimg + ((size_t)(j * p.ncg + (rem >> 5)) * XR) * 32 + (rem & 31u));
             }
             asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
