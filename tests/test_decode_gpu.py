@@ -1,0 +1,109 @@
+"""GPU parity tests for the resident decode step against the oracle's restatement
+of ``forward_llama`` (crates/ullm-model/src/lib.rs:807-969)."""
+import numpy as np
+import pytest
+
+import oracle
+from ullm_b200 import backend, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_model(m, kv_f16):
+    mk = lambda t: oracle.Weight(t[0], t[1], t[2], t[3])
+    layers = [{k: (mk(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in m["layers"]]
+    return oracle.LlamaModel(m["params"], mk(m["tok_embd"]), mk(m["output"]), m["final_norm"], layers, kv_f16)
+
+
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_tiny_decode_logits_match_oracle(ctx, kv_f16):
+    p = dict(synth.LLAMA_TINY)
+    m = synth.gen_llama_model(p, 3)
+    om = oracle_model(m, kv_f16)
+    gf = backend.GpuForward(ctx, m, kv_f16=kv_f16)
+    assert not gf.supports_batched_prefill()
+    tok = 7
+    for pos in range(6):
+        ref = om.forward(tok, pos)
+        got = gf.forward(om.embed(tok), pos)
+        assert synth.rel_err(got, ref) < 1e-3, pos
+        assert int(np.argmax(got)) == oracle.argmax(ref)
+        tok = oracle.argmax(ref)
+    gf.free()
+
+
+def test_tiny_decode_with_prefilled_cache_and_greedy(ctx):
+    """Prefilled f16 cache, then a greedy continuation kept on the device; every
+    step is also checked teacher-forced so a near-tie cannot hide later steps."""
+    p = dict(synth.LLAMA_TINY)
+    p["n_ctx"] = 256
+    m = synth.gen_llama_model(p, 5)
+    n_pre, n_gen = 100, 24
+    k, v = synth.gen_kv_prefill(p, n_pre, 77)
+    om = oracle_model(m, True)
+    om.key_cache[:, :n_pre] = k
+    om.val_cache[:, :n_pre] = v
+    gf = backend.GpuForward(ctx, m, kv_f16=True)
+    gf.set_kv(0, k, v)
+    embd = ctx.upload(m["tok_embd"][1])
+    first = 11
+    ref_tokens, margins = [], []
+    tok = first
+    for i in range(n_gen):
+        lg = om.forward(tok, n_pre + i)
+        s = np.sort(lg)
+        margins.append(float(s[-1] - s[-2]))
+        tok = oracle.argmax(lg)
+        ref_tokens.append(tok)
+    got = gf.greedy(embd, m["tok_embd"][0], first, n_pre, n_gen)
+    assert got.tolist() == ref_tokens, (got.tolist(), ref_tokens, margins)
+    gf.free()
+
+
+def test_decode_rejects_unbuilt_variants(ctx):
+    p = dict(synth.LLAMA_TINY)
+    m = synth.gen_llama_model(p, 3)
+    for flag in ("rope_neox", "qk_norm", "sandwich_norm", "geglu", "sliding_window", "n_experts"):
+        with pytest.raises(backend.Unsupported):
+            backend.GpuForward(ctx, m, **{flag: 1})
+    bad = dict(m)
+    bad["output"] = (backend.F32, m["output"][1], m["output"][2], m["output"][3])
+    with pytest.raises(backend.Unsupported):  # forward.rs:376-378
+        backend.GpuForward(ctx, bad)
+    gf = backend.GpuForward(ctx, m)
+    with pytest.raises(backend.FormatError):
+        gf.forward(np.zeros(p["n_embd"], np.float32), p["n_ctx"])
+    gf.free()
+
+
+def test_llama_1b_shape_greedy_sequence(ctx):
+    """Benchmark configuration 3: Llama-3.2-1B-shaped, Q4_K_M mix, f16 KV prefilled
+    with 1024 positions, 16-token prompt processed token by token, then greedy
+    tokens; the CUDA sequence must equal the oracle's (f16-rounding KV)."""
+    p = dict(synth.LLAMA_1B)
+    m = synth.gen_llama_model(p, synth.seed_for(3, 0))
+    n_pre, n_prompt, n_gen = 1024, 16, 16
+    k, v = synth.gen_kv_prefill(p, n_pre, synth.seed_for(3, 1))
+    prompt = synth.rand_ints(synth.seed_for(3, 2), n_prompt, 0, p["vocab"] - 1)
+    om = oracle_model(m, True)
+    om.key_cache[:, :n_pre] = k
+    om.val_cache[:, :n_pre] = v
+    gf = backend.GpuForward(ctx, m, kv_f16=True)
+    gf.set_kv(0, k, v)
+    for i, t in enumerate(prompt):
+        ref = om.forward(int(t), n_pre + i)
+        got = gf.forward(om.embed(int(t)), n_pre + i)
+        assert synth.rel_err(got, ref) < 1e-3, i
+    tok = oracle.argmax(ref)
+    assert int(np.argmax(got)) == tok
+    embd = ctx.upload(m["tok_embd"][1])
+    ref_tokens, margins, t = [], [], tok
+    for i in range(n_gen):
+        lg = om.forward(t, n_pre + n_prompt + i)
+        s = np.partition(lg, -2)
+        margins.append(float(s[-1] - s[-2]))
+        t = oracle.argmax(lg)
+        ref_tokens.append(t)
+    got_tokens = gf.greedy(embd, m["tok_embd"][0], tok, n_pre + n_prompt, n_gen)
+    assert got_tokens.tolist() == ref_tokens, (got_tokens.tolist(), ref_tokens, margins)
+    gf.free()

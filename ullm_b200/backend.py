@@ -318,3 +318,99 @@ class Experts:
             self.free()
         except Exception:
             pass
+
+
+# ---- full decode step: GpuForward (crates/ullm-metal/src/forward.rs:162-757) ----
+class GpuParams(C.Structure):
+    """``GpuParams`` (forward.rs:24-51) plus ``kv_f16``."""
+
+    _fields_ = ([(n, _sz) for n in ("n_embd", "n_layer", "n_head", "n_kv_head", "head_dim", "n_ff", "n_ctx", "vocab")]
+                + [("rope_theta", C.c_float), ("eps", C.c_float)]
+                + [(n, _i) for n in ("rope_neox", "qk_norm", "sandwich_norm", "geglu")]
+                + [(n, _sz) for n in ("n_experts", "n_experts_used", "moe_inter", "sliding_window")]
+                + [("kv_f16", _i)])
+
+
+class GpuWeight(C.Structure):
+    """``GpuWeight`` (forward.rs:56-64)."""
+
+    _fields_ = [("dtype", _i), ("bytes", _vp), ("len", _sz), ("out", _sz), ("cols", _sz), ("mlx_scales", _vp), ("mlx_biases", _vp), ("mlx_group", _sz)]
+
+
+class GpuLayerInput(C.Structure):
+    _fields_ = [("attn_norm", _vp), ("ffn_norm", _vp)] + [(n, GpuWeight) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")]
+
+
+class GpuModelInput(C.Structure):
+    _fields_ = [("params", GpuParams), ("output", GpuWeight), ("final_norm", _vp), ("layers", _vp)]
+
+
+class GpuForward:
+    """``GpuForward::{new, forward, supports_batched_prefill}`` on the B200.
+
+    ``model`` is the dict :func:`ullm_b200.synth.gen_llama_model` builds (or the
+    same structure filled from a real file): weights as ``(dtype, bytes, out,
+    cols)`` tuples, norms as f32 arrays."""
+
+    def __init__(self, ctx: CudaContext, model: dict, kv_f16: bool = False, **flags):
+        self._ctx, p = ctx, model["params"]
+        self.params = dict(p)
+        keep = []
+
+        def gw(t):
+            dtype, data, out, cols = t
+            b = _bytes(data)
+            keep.append(b)
+            return GpuWeight(dtype, b.ctypes.data, b.size, out, cols, None, None, 0)
+
+        def f32p(a):
+            a = _f32(a)
+            keep.append(a)
+            return a.ctypes.data
+
+        layers = (GpuLayerInput * len(model["layers"]))()
+        for i, l in enumerate(model["layers"]):
+            layers[i].attn_norm, layers[i].ffn_norm = f32p(l["attn_norm"]), f32p(l["ffn_norm"])
+            for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down"):
+                setattr(layers[i], n, gw(l[n]))
+        gp = GpuParams(p["n_embd"], p["n_layer"], p["n_head"], p["n_kv_head"], p["head_dim"], p["n_ff"], p["n_ctx"], p["vocab"],
+                       p["rope_theta"], p["eps"], flags.get("rope_neox", 0), flags.get("qk_norm", 0), flags.get("sandwich_norm", 0),
+                       flags.get("geglu", 0), flags.get("n_experts", 0), flags.get("n_experts_used", 0), flags.get("moe_inter", 0),
+                       flags.get("sliding_window", 0), 1 if kv_f16 else 0)
+        inp = GpuModelInput(gp, gw(model["output"]), f32p(model["final_norm"]), C.addressof(layers))
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_forward_create(ctx._h, C.byref(inp), C.byref(h)))
+        self._h = h.value
+        self._logits = np.empty(p["vocab"], np.float32)
+
+    def forward(self, x_init, pos: int) -> np.ndarray:
+        """One token: ``x_init`` is its embedding row; returns the vocab logits (forward.rs:384)."""
+        x = _f32(x_init)
+        out = np.empty(self.params["vocab"], np.float32)
+        self._ctx._check(self._ctx._lib.ullm_cuda_forward(self._h, _ptr(x), pos, _ptr(out)))
+        return out
+
+    def set_kv(self, pos0: int, k, v):
+        k, v = _f32(k), _f32(v)
+        n = k.shape[1]
+        self._ctx._check(self._ctx._lib.ullm_cuda_forward_set_kv(self._h, pos0, n, _ptr(k), _ptr(v)))
+
+    def supports_batched_prefill(self) -> bool:
+        return bool(self._ctx._lib.ullm_cuda_forward_supports_batched_prefill(self._h))
+
+    def greedy(self, embd: Buffer, embd_dtype: int, first_token: int, pos: int, n: int) -> np.ndarray:
+        """``n`` greedy tokens kept on the device: argmax feeds the next embedding lookup."""
+        out = np.empty(n, np.uint32)
+        self._ctx._check(self._ctx._lib.ullm_cuda_forward_greedy(self._h, embd._h, embd_dtype, first_token, pos, n, _ptr(out)))
+        return out
+
+    def free(self):
+        if getattr(self, "_h", None):
+            self._ctx._lib.ullm_cuda_forward_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

@@ -3,6 +3,7 @@
 // failures are turned into status codes with a message, and nothing here ever
 // computes on the CPU.
 #include "../../include/ullm_cuda.h"
+#include "decode.h"
 #include "engine.h"
 
 #include <cstdarg>
@@ -210,8 +211,9 @@ int ullm_cuda_matvec_dev(ullm_cuda_ctx *c, int dtype, const void *d_w, const voi
         return ctx_fail(c, ULLM_ERR_FORMAT, "device pointers must be 16-byte aligned");
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
     cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
-    ULLM_CUDA_TRY(c, launch_matvec(c->dev, fmt, d_w, tb, d_x, d_y, out_dim, in_dim, c->d_status, st, c->force_generic,
-                                   c->use_pdl, &c->last_plan));
+    MatvecOpts mo;
+    mo.force_generic = c->force_generic, mo.pdl = c->use_pdl, mo.plan_out = &c->last_plan;
+    ULLM_CUDA_TRY(c, launch_matvec(c->dev, fmt, d_w, tb, d_x, d_y, out_dim, in_dim, c->d_status, st, mo));
     return ULLM_OK;
 }
 
@@ -452,13 +454,116 @@ int ullm_cuda_moe_ffn(ullm_cuda_ctx *c, const ullm_cuda_experts *x, const float 
     return ctx_check_status(c);
 }
 
-int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *, ullm_cuda_fwd **) {
-    return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "decode step is not built yet");
+// ---- decode step -------------------------------------------------------------
+struct ullm_cuda_fwd {
+    ullm_cuda_ctx *ctx = nullptr;
+    Forward f;
+};
+
+static int fwd_fail(ullm_cuda_fwd *f, cudaError_t e, const char *what) {
+    cudaGetLastError();
+    return ctx_fail(f->ctx, e == cudaErrorMemoryAllocation ? ULLM_ERR_OOM : ULLM_ERR_CUDA, "%s: %s", what,
+                    cudaGetErrorString(e));
 }
-void ullm_cuda_forward_destroy(ullm_cuda_fwd *) {}
-int ullm_cuda_forward(ullm_cuda_fwd *, const float *, size_t, float *) { return ULLM_ERR_UNSUPPORTED; }
-int ullm_cuda_forward_set_kv(ullm_cuda_fwd *, size_t, size_t, const float *, const float *) { return ULLM_ERR_UNSUPPORTED; }
+static int fwd_status(ullm_cuda_fwd *f) {
+    if (f->f.h_status && *f->f.h_status != DEV_OK) {
+        *f->f.h_status = DEV_OK;
+        return ctx_fail(f->ctx, ULLM_ERR_TIMEOUT, "a device-side bounded wait expired during the decode step");
+    }
+    return ULLM_OK;
+}
+
+int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, ullm_cuda_fwd **out) {
+    if (!c || !in || !out || !in->layers || !in->final_norm) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    const ullm_gpu_params &gp = in->params;
+    // Flags no benchmark configuration uses are refused, not ignored.
+    if (gp.rope_neox) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "NeoX RoPE is not built");
+    if (gp.qk_norm) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "per-head Q/K RMSNorm is not built");
+    if (gp.sandwich_norm) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "sandwich norms are not built");
+    if (gp.geglu) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "GeGLU is not built");
+    if (gp.n_experts || gp.n_experts_used || gp.moe_inter) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MoE layers inside the decode step are not built");
+    if (gp.sliding_window) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "sliding-window attention is not built");
+    ForwardParams P;
+    P.n_embd = gp.n_embd, P.n_layer = gp.n_layer, P.n_head = gp.n_head, P.n_kv_head = gp.n_kv_head, P.head_dim = gp.head_dim;
+    P.n_ff = gp.n_ff, P.n_ctx = gp.n_ctx, P.vocab = gp.vocab, P.rope_theta = gp.rope_theta, P.eps = gp.eps, P.kv_f16 = gp.kv_f16;
+    if (const char *m = Forward::check_params(P)) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s", m);
+    const size_t qd = P.n_head * P.head_dim, kvd = P.n_kv_head * P.head_dim;
+    auto conv = [&](const ullm_gpu_weight &w, size_t out_dim, size_t cols, HostWeight *hw, const char *name) -> int {
+        if (w.mlx_scales || w.mlx_biases) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s: MLX weights inside the decode step are not built", name);
+        if (w.dtype != ULLM_DTYPE_Q4_K && w.dtype != ULLM_DTYPE_Q6_K)
+            return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s: no CUDA forward kernel for dtype %d", name, w.dtype); // forward.rs:376-378
+        if (!w.bytes || w.out != out_dim || w.cols != cols) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: expected shape [%zu, %zu]", name, out_dim, cols);
+        const size_t need = out_dim * (cols / QK_K) * (w.dtype == ULLM_DTYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES);
+        if (w.len < need) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: need %zu bytes, have %zu", name, need, w.len);
+        hw->dtype = w.dtype, hw->bytes = w.bytes, hw->out = out_dim, hw->cols = cols;
+        return ULLM_OK;
+    };
+    HostModel hm;
+    int rc;
+    if ((rc = conv(in->output, P.vocab, P.n_embd, &hm.output, "output"))) return rc;
+    hm.final_norm = in->final_norm;
+    hm.layers.resize(P.n_layer);
+    for (size_t l = 0; l < P.n_layer; ++l) {
+        const ullm_gpu_layer_input &li = in->layers[l];
+        HostLayer &hl = hm.layers[l];
+        if (!li.attn_norm || !li.ffn_norm) return ULLM_ERR_INVALID;
+        hl.attn_norm = li.attn_norm, hl.ffn_norm = li.ffn_norm;
+        if ((rc = conv(li.wq, qd, P.n_embd, &hl.wq, "wq")) || (rc = conv(li.wk, kvd, P.n_embd, &hl.wk, "wk")) ||
+            (rc = conv(li.wv, kvd, P.n_embd, &hl.wv, "wv")) || (rc = conv(li.wo, P.n_embd, qd, &hl.wo, "wo")) ||
+            (rc = conv(li.w_gate, P.n_ff, P.n_embd, &hl.w_gate, "w_gate")) ||
+            (rc = conv(li.w_up, P.n_ff, P.n_embd, &hl.w_up, "w_up")) ||
+            (rc = conv(li.w_down, P.n_embd, P.n_ff, &hl.w_down, "w_down")))
+            return rc;
+    }
+    ullm_cuda_fwd *f = new (std::nothrow) ullm_cuda_fwd();
+    if (!f) return ULLM_ERR_OOM;
+    f->ctx = c;
+    f->f.use_pdl = c->use_pdl;
+    cudaError_t e = f->f.init(c->dev, c->device, P, hm);
+    if (e != cudaSuccess) {
+        int code = fwd_fail(f, e, "uploading the model");
+        delete f;
+        return code;
+    }
+    *out = f;
+    return ULLM_OK;
+}
+
+void ullm_cuda_forward_destroy(ullm_cuda_fwd *f) { delete f; }
+
+int ullm_cuda_forward(ullm_cuda_fwd *f, const float *x_init, size_t pos, float *logits) {
+    if (!f || !x_init || !logits) return ULLM_ERR_INVALID;
+    if (pos >= f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "position %zu is outside the context of %zu", pos, f->f.P.n_ctx);
+    cudaError_t e = f->f.forward(x_init, pos, logits);
+    if (e == cudaErrorNotSupported) return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "a layer shape is outside the fused decode path");
+    if (e != cudaSuccess) return fwd_fail(f, e, "decode step");
+    return fwd_status(f);
+}
+
+int ullm_cuda_forward_set_kv(ullm_cuda_fwd *f, size_t pos0, size_t n, const float *k, const float *v) {
+    if (!f || !k || !v) return ULLM_ERR_INVALID;
+    if (pos0 + n > f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "positions beyond the context");
+    cudaError_t e = f->f.set_kv(pos0, n, k, v);
+    if (e != cudaSuccess) return fwd_fail(f, e, "filling the KV cache");
+    return ULLM_OK;
+}
+
+// GpuForward::supports_batched_prefill (forward.rs:744-749): the batched prefill
+// pass is not built, so callers take the token-by-token path (lib.rs:1287-1295).
 int ullm_cuda_forward_supports_batched_prefill(const ullm_cuda_fwd *) { return 0; }
-int ullm_cuda_forward_greedy(ullm_cuda_fwd *, const ullm_cuda_buf *, int, uint32_t, size_t, size_t, uint32_t *) {
-    return ULLM_ERR_UNSUPPORTED;
+
+int ullm_cuda_forward_greedy(ullm_cuda_fwd *f, const ullm_cuda_buf *embd, int embd_dtype, uint32_t first_token, size_t pos,
+                             size_t n, uint32_t *tokens_out) {
+    if (!f || !embd || (n && !tokens_out)) return ULLM_ERR_INVALID;
+    if (embd_dtype != ULLM_DTYPE_Q4_K && embd_dtype != ULLM_DTYPE_Q6_K)
+        return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "embedding table dtype %d has no device lookup", embd_dtype);
+    const size_t rb = (f->f.P.n_embd / QK_K) * (embd_dtype == ULLM_DTYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES);
+    if (embd->len < f->f.P.vocab * rb) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "embedding table is shorter than vocab rows");
+    if (first_token >= f->f.P.vocab) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "token id outside the vocabulary");
+    if (pos + n > f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "positions beyond the context");
+    cudaError_t e = f->f.greedy(embd->ptr, embd_dtype, first_token, pos, n, tokens_out);
+    if (e == cudaErrorNotSupported) return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "a layer shape is outside the fused decode path");
+    if (e != cudaSuccess) return fwd_fail(f, e, "greedy decode");
+    return fwd_status(f);
 }

@@ -1,0 +1,582 @@
+// One decode step of a dense Llama-family model with every weight resident and
+// quantized (CPU form: crates/ullm-model/src/lib.rs:807-969; GPU surface:
+// crates/ullm-metal/src/forward.rs:384-526).
+//
+// Per layer the step is six launches, all HBM-streaming matvecs except the
+// attention:
+//   [rmsnorm ->] W_qk x      (Q and K projections stored as one matrix)
+//   [rmsnorm ->] W_v  x
+//   rope(q), rope(k), K/V cache write, split-KV attention, split combine
+//   W_o attn  (+ residual, in the epilogue)
+//   [rmsnorm ->] W_gate|up x (rows interleaved at upload; silu(g)*u in the epilogue)
+//   W_down h  (+ residual)
+// and norm + output projection at the end.  The position and the current token
+// live in device memory, so the same CUDA graph is replayed for every token: one
+// submission per decoded token, and greedy decoding (argmax -> embedding lookup)
+// needs no host round trip at all.
+#include "decode.h"
+
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+namespace ullm {
+
+// ---------------------------------------------------------------------------
+// Attention for one new token
+// ---------------------------------------------------------------------------
+constexpr int ATT_CHUNK = 64; // cache positions per CTA
+
+template <typename T> __device__ __forceinline__ float kv_load(const T *p);
+template <> __device__ __forceinline__ float kv_load<float>(const float *p) { return __ldcg(p); }
+template <> __device__ __forceinline__ float kv_load<__half>(const __half *p) { return __half2float(__ldcg(p)); }
+template <typename T> __device__ __forceinline__ T kv_make(float v);
+template <> __device__ __forceinline__ float kv_make<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half kv_make<__half>(float v) { return __float2half_rn(v); }
+
+struct AttnParams {
+    const float *q, *knew, *vnew; // projections of the new token (before RoPE)
+    void *kcache, *vcache;        // this layer: [n_ctx][kv_dim]
+    const float2 *rope;           // [n_ctx][HD/2] (cos, sin) of pos * theta^(-2i/HD)
+    const int *pos_ptr;
+    float scale;
+    float *partial;               // [n_kv_head][n_split][KVMUL][HD + 2]
+    unsigned *counters;           // [n_kv_head], zero between launches
+    float *out;                   // [n_head * HD]
+    int kv_dim, n_split;
+};
+
+// Sums each of the 32 values over the warp; on return lane L holds the total of
+// value index L.
+__device__ __forceinline__ float warp_transpose_sum32(float (&v)[32], int lane) {
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool up = lane & half;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            float send = up ? v[i] : v[i + half];
+            float keep = up ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+    }
+    return v[0];
+}
+
+// grid (n_kv_head, n_split), 128 threads.  CTA (h, s) owns cache positions
+// [s*64, s*64+64) of kv head h for its KVMUL query heads; the CTA that owns `pos`
+// applies RoPE to the new K, rounds K and V to the cache type and stores them;
+// the last CTA of a head to finish merges the per-split softmax partials.
+template <int HD, int KVMUL, typename KV_T>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
+    constexpr int E = HD / 32;     // dims per lane
+    constexpr int PB = 32 / KVMUL; // positions per transposed-reduction batch
+    __shared__ float qs[KVMUL][HD];
+    __shared__ float sc[KVMUL][ATT_CHUNK];
+    __shared__ float red[4][KVMUL][HD];
+    __shared__ float ml[KVMUL][2];
+    __shared__ bool is_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.x, sp = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int pos = *p.pos_ptr;
+    const int n_active = pos / ATT_CHUNK + 1;
+    if (sp >= n_active) return;
+    const int p0 = sp * ATT_CHUNK, p1 = min(p0 + ATT_CHUNK, pos + 1), np = p1 - p0;
+    KV_T *kc = (KV_T *)p.kcache, *vc = (KV_T *)p.vcache;
+    const float2 *rp = p.rope + (size_t)pos * (HD / 2);
+
+    // RoPE, interleaved pairs, products and sums kept unfused as in math.rs:130-132
+    for (int i = tid; i < KVMUL * (HD / 2); i += 128) {
+        const int h = i / (HD / 2), j = i % (HD / 2);
+        const float *qp = p.q + (size_t)(kvh * KVMUL + h) * HD + 2 * j;
+        const float a = qp[0], b = qp[1];
+        const float2 cs = rp[j];
+        qs[h][2 * j] = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+        qs[h][2 * j + 1] = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+    }
+    if (sp == n_active - 1) {
+        for (int j = tid; j < HD / 2; j += 128) {
+            const float *kp = p.knew + (size_t)kvh * HD + 2 * j;
+            const float a = kp[0], b = kp[1];
+            const float2 cs = rp[j];
+            KV_T *dst = kc + (size_t)pos * p.kv_dim + kvh * HD + 2 * j;
+            dst[0] = kv_make<KV_T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
+            dst[1] = kv_make<KV_T>(__fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)));
+        }
+        for (int j = tid; j < HD; j += 128)
+            vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(p.vnew[(size_t)kvh * HD + j]);
+    }
+    __syncthreads();
+
+    // scores: lane owns dims [lane*E, lane*E+E) of every head
+    float qr[KVMUL][E];
+#pragma unroll
+    for (int h = 0; h < KVMUL; ++h)
+#pragma unroll
+        for (int e = 0; e < E; ++e) qr[h][e] = qs[h][lane * E + e];
+    for (int b0 = warp * PB; b0 < np; b0 += 4 * PB) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < PB; ++j) {
+            const int pp = min(p0 + b0 + j, p1 - 1);
+            const KV_T *kp = kc + (size_t)pp * p.kv_dim + kvh * HD + lane * E;
+            float kk[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) kk[e] = kv_load<KV_T>(kp + e);
+#pragma unroll
+            for (int h = 0; h < KVMUL; ++h) {
+                float s = 0.f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) s += qr[h][e] * kk[e];
+                v[j * KVMUL + h] = s;
+            }
+        }
+        const float tot = warp_transpose_sum32(v, lane);
+        const int j = lane / KVMUL, h = lane % KVMUL;
+        if (b0 + j < np) sc[h][b0 + j] = tot * p.scale;
+    }
+    __syncthreads();
+
+    // per-head softmax partials over this CTA's positions
+    for (int h = warp; h < KVMUL; h += 4) {
+        float m = -INFINITY;
+        for (int i = lane; i < np; i += 32) m = fmaxf(m, sc[h][i]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int i = lane; i < np; i += 32) {
+            const float e = expf(sc[h][i] - m);
+            sc[h][i] = e;
+            l += e;
+        }
+        l = warp_sum(l);
+        if (lane == 0) ml[h][0] = m, ml[h][1] = l;
+    }
+    __syncthreads();
+
+    // P V: positions split over the warps, dims over the lanes
+    float acc[KVMUL][E];
+#pragma unroll
+    for (int h = 0; h < KVMUL; ++h)
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[h][e] = 0.f;
+    for (int i = warp; i < np; i += 4) {
+        const KV_T *vp = vc + (size_t)(p0 + i) * p.kv_dim + kvh * HD + lane * E;
+        float vv[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) vv[e] = kv_load<KV_T>(vp + e);
+#pragma unroll
+        for (int h = 0; h < KVMUL; ++h) {
+            const float a = sc[h][i];
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[h][e] += a * vv[e];
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < KVMUL; ++h)
+#pragma unroll
+        for (int e = 0; e < E; ++e) red[warp][h][lane * E + e] = acc[h][e];
+    __syncthreads();
+    float *mine = p.partial + ((size_t)(kvh * p.n_split + sp) * KVMUL) * (HD + 2);
+    for (int i = tid; i < KVMUL * HD; i += 128) {
+        const int h = i / HD, d = i % HD;
+        mine[(size_t)h * (HD + 2) + d] = red[0][h][d] + red[1][h][d] + red[2][h][d] + red[3][h][d];
+    }
+    if (tid < KVMUL) {
+        mine[(size_t)tid * (HD + 2) + HD] = ml[tid][0];
+        mine[(size_t)tid * (HD + 2) + HD + 1] = ml[tid][1];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned t = atomicAdd(&p.counters[kvh], 1u);
+        is_last = t == (unsigned)(n_active - 1);
+        if (is_last) p.counters[kvh] = 0u; // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float *base = p.partial + ((size_t)kvh * p.n_split * KVMUL) * (HD + 2);
+    for (int i = tid; i < KVMUL * HD; i += 128) {
+        const int h = i / HD, d = i % HD;
+        float M = -INFINITY;
+        for (int s = 0; s < n_active; ++s) M = fmaxf(M, __ldcg(base + ((size_t)s * KVMUL + h) * (HD + 2) + HD));
+        float L = 0.f, o = 0.f;
+        for (int s = 0; s < n_active; ++s) {
+            const float *ps = base + ((size_t)s * KVMUL + h) * (HD + 2);
+            const float w = expf(__ldcg(ps + HD) - M);
+            L += __ldcg(ps + HD + 1) * w;
+            o += __ldcg(ps + d) * w;
+        }
+        p.out[(size_t)(kvh * KVMUL + h) * HD + d] = o / L;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Small kernels
+// ---------------------------------------------------------------------------
+// Greedy sampling (crates/ullm-model/src/sample.rs:125-133: first index wins ties)
+// and the bookkeeping that lets the next graph replay run without the host.
+__global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restrict__ logits, int n, uint32_t *token,
+                                                          int *pos, int *step, uint32_t *tokens_out, int max_steps) {
+    __shared__ float bvs[32];
+    __shared__ int bis[32];
+    pdl_wait_prior();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < n; i += 1024) {
+        const float v = logits[i];
+        if (v > bv || (v == bv && i < bi)) bv = v, bi = i;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+    }
+    if (lane == 0) bvs[warp] = bv, bis[warp] = bi;
+    __syncthreads();
+    if (warp == 0) {
+        bv = bvs[lane], bi = bis[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+        }
+        if (lane == 0) {
+            if (bi == 0x7fffffff) bi = 0; // all NaN / -inf: the reference keeps index 0
+            *token = (uint32_t)bi;
+            const int s = *step;
+            if (s < max_steps) tokens_out[s] = (uint32_t)bi;
+            *step = s + 1;
+            *pos = *pos + 1;
+        }
+    }
+}
+
+__global__ void kv_fill_kernel(const float *__restrict__ src, void *dst, size_t n, int f16) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (f16) ((__half *)dst)[i] = __float2half_rn(src[i]);
+    else ((float *)dst)[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------
+// Engine
+// ---------------------------------------------------------------------------
+static int fmt_of_dtype(int dtype) { return dtype == 12 ? FMT_Q4K : (dtype == 14 ? FMT_Q6K : -1); }
+static size_t qbytes(int fmt, size_t out, size_t cols) {
+    return out * (cols / QK_K) * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+}
+
+template <int HD, int KVMUL> static cudaError_t launch_attn_t(const AttnParams &p, int n_kv_head, bool f16, cudaStream_t st, bool pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_kv_head, p.n_split), cfg.blockDim = dim3(128), cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
+    if (f16) return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, KVMUL, __half>, p);
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, KVMUL, float>, p);
+}
+static cudaError_t launch_attn(const AttnParams &p, int hd, int kvmul, int n_kv_head, bool f16, cudaStream_t st, bool pdl) {
+#define ULLM_ATT(H, K) \
+    if (hd == H && kvmul == K) return launch_attn_t<H, K>(p, n_kv_head, f16, st, pdl);
+    ULLM_ATT(64, 1) ULLM_ATT(64, 2) ULLM_ATT(64, 4) ULLM_ATT(64, 8)
+    ULLM_ATT(128, 1) ULLM_ATT(128, 2) ULLM_ATT(128, 4) ULLM_ATT(128, 8)
+#undef ULLM_ATT
+    return cudaErrorNotSupported;
+}
+
+const char *Forward::check_params(const ForwardParams &p) {
+    if (!p.n_embd || !p.n_layer || !p.n_head || !p.n_kv_head || !p.head_dim || !p.n_ff || !p.n_ctx || !p.vocab)
+        return "zero hyperparameter";
+    if (p.n_head % p.n_kv_head) return "n_head is not a multiple of n_kv_head";
+    const size_t kvmul = p.n_head / p.n_kv_head;
+    if (p.head_dim != 64 && p.head_dim != 128) return "head_dim must be 64 or 128";
+    if (kvmul != 1 && kvmul != 2 && kvmul != 4 && kvmul != 8) return "n_head / n_kv_head must be 1, 2, 4 or 8";
+    if (p.n_embd % QK_K || p.n_ff % QK_K || (p.n_head * p.head_dim) % QK_K) return "dimensions must be multiples of 256";
+    return nullptr;
+}
+
+Forward::~Forward() {
+    cudaSetDevice(device);
+    if (graph_exec[0]) cudaGraphExecDestroy(graph_exec[0]);
+    if (graph_exec[1]) cudaGraphExecDestroy(graph_exec[1]);
+    for (void *q : owned)
+        if (q) cudaFree(q);
+    if (h_pin) cudaFreeHost(h_pin);
+    if (h_status) cudaFreeHost((void *)h_status);
+    if (stream) cudaStreamDestroy(stream);
+}
+
+cudaError_t Forward::dev_alloc(void **out, size_t bytes) {
+    cudaError_t e = cudaMalloc(out, bytes ? bytes : 16);
+    if (e == cudaSuccess) owned.push_back(*out);
+    return e;
+}
+
+cudaError_t Forward::upload(const void *host, size_t bytes, void **out) {
+    cudaError_t e = dev_alloc(out, bytes);
+    if (e != cudaSuccess) return e;
+    return cudaMemcpyAsync(*out, host, bytes, cudaMemcpyHostToDevice, stream);
+}
+
+// Two matrices of the same type stacked (`interleave` = false: rows of a then rows
+// of b) or row-interleaved (a0 b0 a1 b1 ...) into one resident matrix.
+cudaError_t Forward::upload_pair(const HostWeight &a, const HostWeight &b, bool interleave, Mat *out) {
+    const int fmt = fmt_of_dtype(a.dtype);
+    const size_t rb = (a.cols / QK_K) * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    std::vector<uint8_t> tmp((a.out + b.out) * rb);
+    if (!interleave) {
+        memcpy(tmp.data(), a.bytes, a.out * rb);
+        memcpy(tmp.data() + a.out * rb, b.bytes, b.out * rb);
+    } else {
+        for (size_t r = 0; r < a.out; ++r) {
+            memcpy(tmp.data() + (2 * r) * rb, (const uint8_t *)a.bytes + r * rb, rb);
+            memcpy(tmp.data() + (2 * r + 1) * rb, (const uint8_t *)b.bytes + r * rb, rb);
+        }
+    }
+    out->fmt = fmt, out->out = a.out + b.out, out->cols = a.cols;
+    cudaError_t e = upload(tmp.data(), tmp.size(), &out->w);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream); // tmp dies at scope exit
+    return e;
+}
+
+cudaError_t Forward::upload_one(const HostWeight &a, Mat *out) {
+    out->fmt = fmt_of_dtype(a.dtype), out->out = a.out, out->cols = a.cols;
+    return upload(a.bytes, qbytes(out->fmt, a.out, a.cols), &out->w);
+}
+
+cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardParams &params, const HostModel &m) {
+    dev = devinfo, device = device_, P = params;
+    cudaError_t e;
+#define TRY(x) \
+    if ((e = (x)) != cudaSuccess) return e;
+    TRY(cudaSetDevice(device));
+    TRY(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    const size_t hd = P.head_dim, qd = P.n_head * hd, kvd = P.n_kv_head * hd;
+    layers.resize(P.n_layer);
+    for (size_t l = 0; l < P.n_layer; ++l) {
+        const HostLayer &h = m.layers[l];
+        Layer &L = layers[l];
+        TRY(upload(h.attn_norm, P.n_embd * 4, (void **)&L.attn_norm));
+        TRY(upload(h.ffn_norm, P.n_embd * 4, (void **)&L.ffn_norm));
+        L.qk_fused = h.wq.dtype == h.wk.dtype;
+        if (L.qk_fused) {
+            TRY(upload_pair(h.wq, h.wk, false, &L.wqk));
+        } else {
+            TRY(upload_one(h.wq, &L.wq));
+            TRY(upload_one(h.wk, &L.wk));
+        }
+        TRY(upload_one(h.wv, &L.wv));
+        TRY(upload_one(h.wo, &L.wo));
+        L.gu_fused = h.w_gate.dtype == h.w_up.dtype &&
+                     matvec_is_streamed(dev, fmt_of_dtype(h.w_gate.dtype), 2 * P.n_ff, P.n_embd, 0, 4, EPI_SWIGLU);
+        if (L.gu_fused) {
+            TRY(upload_pair(h.w_gate, h.w_up, true, &L.wgu));
+        } else {
+            TRY(upload_one(h.w_gate, &L.wg));
+            TRY(upload_one(h.w_up, &L.wu));
+        }
+        TRY(upload_one(h.w_down, &L.wd));
+    }
+    TRY(upload_one(m.output, &output));
+    TRY(upload(m.final_norm, P.n_embd * 4, (void **)&final_norm));
+
+    // RoPE table with the host libm, as the CPU path computes it (math.rs:128-129)
+    {
+        std::vector<float2> tab(P.n_ctx * (hd / 2));
+        for (size_t pos = 0; pos < P.n_ctx; ++pos)
+            for (size_t j = 0; j < hd / 2; ++j) {
+                const float freq = 1.0f / powf(P.rope_theta, (float)(2 * j) / (float)hd);
+                const float ang = (float)pos * freq;
+                tab[pos * (hd / 2) + j] = make_float2(cosf(ang), sinf(ang));
+            }
+        TRY(upload(tab.data(), tab.size() * sizeof(float2), (void **)&rope));
+        TRY(cudaStreamSynchronize(stream));
+    }
+    const size_t kvb = P.kv_f16 ? 2 : 4;
+    TRY(dev_alloc(&kcache, P.n_layer * P.n_ctx * kvd * kvb));
+    TRY(dev_alloc(&vcache, P.n_layer * P.n_ctx * kvd * kvb));
+    TRY(cudaMemsetAsync(kcache, 0, P.n_layer * P.n_ctx * kvd * kvb, stream));
+    TRY(cudaMemsetAsync(vcache, 0, P.n_layer * P.n_ctx * kvd * kvb, stream));
+    n_split = (int)((P.n_ctx + ATT_CHUNK - 1) / ATT_CHUNK);
+    TRY(dev_alloc((void **)&x, P.n_embd * 4));
+    TRY(dev_alloc((void **)&xb, P.n_embd * 4));
+    TRY(dev_alloc((void **)&qk, (qd + kvd) * 4));
+    TRY(dev_alloc((void **)&vbuf, kvd * 4));
+    TRY(dev_alloc((void **)&attn, qd * 4));
+    TRY(dev_alloc((void **)&hidden, P.n_ff * 4));
+    TRY(dev_alloc((void **)&gate, P.n_ff * 4));
+    TRY(dev_alloc((void **)&up, P.n_ff * 4));
+    TRY(dev_alloc((void **)&logits, P.vocab * 4));
+    TRY(dev_alloc((void **)&partial, P.n_kv_head * n_split * (P.n_head / P.n_kv_head) * (hd + 2) * 4));
+    TRY(dev_alloc((void **)&counters, P.n_kv_head * 4));
+    TRY(cudaMemsetAsync(counters, 0, P.n_kv_head * 4, stream));
+    TRY(dev_alloc((void **)&state, 64)); // [0] pos, [1] token, [2] step
+    TRY(cudaMemsetAsync(state, 0, 64, stream));
+    TRY(dev_alloc((void **)&tokens_out, MAX_GREEDY * 4));
+    TRY(cudaHostAlloc((void **)&h_pin, 64, cudaHostAllocDefault));
+    TRY(cudaHostAlloc((void **)&h_status, sizeof(int), cudaHostAllocMapped));
+    owned_host = true;
+    *h_status = 0;
+    TRY(cudaHostGetDevicePointer((void **)&d_status, (void *)h_status, 0));
+    TRY(cudaStreamSynchronize(stream));
+#undef TRY
+    return cudaSuccess;
+}
+
+cudaError_t Forward::mv(const Mat &m, const float *in, float *out, const float *norm_w, int epi, const float *res) {
+    MatvecOpts o;
+    o.pdl = use_pdl, o.norm_w = norm_w, o.eps = P.eps, o.epi = epi, o.res = res;
+    MlxTables tb;
+    cudaError_t e = launch_matvec(dev, m.fmt, m.w, tb, in, out, m.out, m.cols, d_status, stream, o);
+    ++launches;
+    return e;
+}
+
+// Enqueues one token step on `stream`.  mode 0: x already holds the embedding,
+// logits are left in `logits`.  mode 1 (greedy): embedding lookup of state.token
+// first, argmax + bookkeeping last.
+cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dtype) {
+    cudaError_t e;
+#define TRY(x) \
+    if ((e = (x)) != cudaSuccess) return e;
+    const size_t hd = P.head_dim, qd = P.n_head * hd, kvd = P.n_kv_head * hd;
+    int *pos_ptr = (int *)state;
+    uint32_t *tok_ptr = (uint32_t *)state + 1;
+    int *step_ptr = (int *)state + 2;
+    launches = 0;
+    if (mode == 1) {
+        TRY(launch_dequant_row(embd_dtype, embd_table, tok_ptr, P.n_embd, x, stream));
+        ++launches;
+    }
+    const size_t kvb = P.kv_f16 ? 2 : 4;
+    for (size_t l = 0; l < P.n_layer; ++l) {
+        Layer &L = layers[l];
+        if (L.qk_fused) {
+            TRY(mv(L.wqk, x, qk, L.attn_norm, EPI_STORE, nullptr));
+        } else {
+            TRY(mv(L.wq, x, qk, L.attn_norm, EPI_STORE, nullptr));
+            TRY(mv(L.wk, x, qk + qd, L.attn_norm, EPI_STORE, nullptr));
+        }
+        TRY(mv(L.wv, x, vbuf, L.attn_norm, EPI_STORE, nullptr));
+        AttnParams ap;
+        ap.q = qk, ap.knew = qk + qd, ap.vnew = vbuf;
+        ap.kcache = (uint8_t *)kcache + l * P.n_ctx * kvd * kvb;
+        ap.vcache = (uint8_t *)vcache + l * P.n_ctx * kvd * kvb;
+        ap.rope = rope, ap.pos_ptr = pos_ptr, ap.scale = 1.0f / sqrtf((float)hd);
+        ap.partial = partial, ap.counters = counters, ap.out = attn, ap.kv_dim = (int)kvd, ap.n_split = n_split;
+        TRY(launch_attn(ap, (int)hd, (int)(P.n_head / P.n_kv_head), (int)P.n_kv_head, P.kv_f16 != 0, stream, use_pdl));
+        ++launches;
+        TRY(mv(L.wo, attn, x, nullptr, EPI_RESIDUAL, x));
+        if (L.gu_fused) {
+            TRY(mv(L.wgu, x, hidden, L.ffn_norm, EPI_SWIGLU, nullptr));
+        } else {
+            return cudaErrorNotSupported;
+        }
+        TRY(mv(L.wd, hidden, x, nullptr, EPI_RESIDUAL, x));
+    }
+    TRY(mv(output, x, logits, final_norm, EPI_STORE, nullptr));
+    if (mode == 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1), cfg.blockDim = dim3(1024), cfg.stream = stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
+        TRY(cudaLaunchKernelEx(&cfg, argmax_step_kernel, (const float *)logits, (int)P.vocab, tok_ptr, pos_ptr, step_ptr,
+                               tokens_out, (int)MAX_GREEDY));
+        ++launches;
+    }
+#undef TRY
+    return cudaSuccess;
+}
+
+// Captures the step into a graph once per mode and replays it afterwards.
+cudaError_t Forward::run_step(int mode, const void *embd_table, int embd_dtype) {
+    if (!use_graph) return enqueue_step(mode, embd_table, embd_dtype);
+    if (graph_exec[mode] && (mode == 0 || (graph_table == embd_table && graph_dtype == embd_dtype)))
+        return cudaGraphLaunch(graph_exec[mode], stream);
+    if (graph_exec[mode]) {
+        cudaGraphExecDestroy(graph_exec[mode]);
+        graph_exec[mode] = nullptr;
+    }
+    cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return e;
+    cudaError_t body = enqueue_step(mode, embd_table, embd_dtype);
+    cudaGraph_t g = nullptr;
+    e = cudaStreamEndCapture(stream, &g);
+    if (body != cudaSuccess) {
+        if (g) cudaGraphDestroy(g);
+        return body;
+    }
+    if (e != cudaSuccess) return e;
+    e = cudaGraphInstantiate(&graph_exec[mode], g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return e;
+    graph_launches = launches;
+    if (mode == 1) graph_table = embd_table, graph_dtype = embd_dtype;
+    return cudaGraphLaunch(graph_exec[mode], stream);
+}
+
+cudaError_t Forward::forward(const float *x_init, size_t pos, float *logits_host) {
+    cudaError_t e;
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return e;
+    ((int *)h_pin)[0] = (int)pos;
+    if ((e = cudaMemcpyAsync(state, h_pin, 4, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
+    if ((e = cudaMemcpyAsync(x, x_init, P.n_embd * 4, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
+    if ((e = run_step(0, nullptr, 0)) != cudaSuccess) return e;
+    if ((e = cudaMemcpyAsync(logits_host, logits, P.vocab * 4, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
+    return cudaStreamSynchronize(stream);
+}
+
+cudaError_t Forward::greedy(const void *embd_table, int embd_dtype, uint32_t first_token, size_t pos, size_t n,
+                            uint32_t *tokens_host) {
+    cudaError_t e;
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return e;
+    size_t done = 0;
+    uint32_t tok = first_token;
+    while (done < n) {
+        const size_t chunk = n - done < MAX_GREEDY ? n - done : MAX_GREEDY;
+        ((int *)h_pin)[0] = (int)(pos + done), ((uint32_t *)h_pin)[1] = tok, ((int *)h_pin)[2] = 0;
+        if ((e = cudaMemcpyAsync(state, h_pin, 12, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
+        for (size_t i = 0; i < chunk; ++i)
+            if ((e = run_step(1, embd_table, embd_dtype)) != cudaSuccess) return e;
+        if ((e = cudaMemcpyAsync(tokens_host + done, tokens_out, chunk * 4, cudaMemcpyDeviceToHost, stream)) != cudaSuccess)
+            return e;
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return e;
+        tok = tokens_host[done + chunk - 1];
+        done += chunk;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t Forward::set_kv(size_t pos0, size_t n, const float *k, const float *v) {
+    cudaError_t e;
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return e;
+    const size_t kvd = P.n_kv_head * P.head_dim, kvb = P.kv_f16 ? 2 : 4;
+    float *tmp = nullptr;
+    if ((e = cudaMalloc((void **)&tmp, n * kvd * 4)) != cudaSuccess) return e;
+    for (int which = 0; which < 2 && e == cudaSuccess; ++which) {
+        const float *src = which ? v : k;
+        uint8_t *cache = (uint8_t *)(which ? vcache : kcache);
+        for (size_t l = 0; l < P.n_layer && e == cudaSuccess; ++l) {
+            e = cudaMemcpyAsync(tmp, src + l * n * kvd, n * kvd * 4, cudaMemcpyHostToDevice, stream);
+            if (e != cudaSuccess) break;
+            const size_t cnt = n * kvd;
+            kv_fill_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, stream>>>(tmp, cache + (l * P.n_ctx + pos0) * kvd * kvb, cnt,
+                                                                             P.kv_f16);
+            e = cudaGetLastError();
+        }
+    }
+    cudaError_t e2 = cudaStreamSynchronize(stream);
+    cudaFree(tmp);
+    return e != cudaSuccess ? e : e2;
+}
+
+} // namespace ullm

@@ -1,0 +1,88 @@
+// Resident dense-Llama decode engine (see decode.cu).
+#pragma once
+
+#include "common.cuh"
+#include "kernels.h"
+
+#include <vector>
+
+namespace ullm {
+
+struct ForwardParams { // GpuParams, crates/ullm-metal/src/forward.rs:24-51 (dense subset)
+    size_t n_embd = 0, n_layer = 0, n_head = 0, n_kv_head = 0, head_dim = 0, n_ff = 0, n_ctx = 0, vocab = 0;
+    float rope_theta = 10000.f, eps = 1e-5f;
+    int kv_f16 = 0;
+};
+struct HostWeight { // GpuWeight, forward.rs:56-64
+    int dtype = 0;
+    const void *bytes = nullptr;
+    size_t out = 0, cols = 0;
+};
+struct HostLayer {
+    const float *attn_norm = nullptr, *ffn_norm = nullptr;
+    HostWeight wq, wk, wv, wo, w_gate, w_up, w_down;
+};
+struct HostModel {
+    HostWeight output;
+    const float *final_norm = nullptr;
+    std::vector<HostLayer> layers;
+};
+
+struct Forward {
+    static constexpr size_t MAX_GREEDY = 4096; // tokens kept on the device between host reads
+    struct Mat {
+        int fmt = 0;
+        void *w = nullptr;
+        size_t out = 0, cols = 0;
+    };
+    struct Layer {
+        float *attn_norm = nullptr, *ffn_norm = nullptr;
+        bool qk_fused = false, gu_fused = false;
+        Mat wqk, wq, wk, wv, wo, wgu, wg, wu, wd;
+    };
+
+    DeviceInfo dev;
+    int device = 0;
+    ForwardParams P;
+    cudaStream_t stream = nullptr;
+    std::vector<Layer> layers;
+    Mat output;
+    float *final_norm = nullptr;
+    float2 *rope = nullptr;
+    void *kcache = nullptr, *vcache = nullptr;
+    int n_split = 0;
+    float *x = nullptr, *xb = nullptr, *qk = nullptr, *vbuf = nullptr, *attn = nullptr, *hidden = nullptr, *gate = nullptr,
+          *up = nullptr, *logits = nullptr, *partial = nullptr;
+    unsigned *counters = nullptr;
+    void *state = nullptr; // device ints: [0] pos, [1] token, [2] step
+    uint32_t *tokens_out = nullptr;
+    void *h_pin = nullptr;
+    volatile int *h_status = nullptr;
+    int *d_status = nullptr;
+    bool owned_host = false;
+    std::vector<void *> owned;
+    bool use_graph = true, use_pdl = false;
+    cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
+    const void *graph_table = nullptr;
+    int graph_dtype = 0;
+    int launches = 0, graph_launches = 0;
+
+    ~Forward();
+    static const char *check_params(const ForwardParams &p);
+    cudaError_t init(const DeviceInfo &devinfo, int device, const ForwardParams &params, const HostModel &m);
+    cudaError_t forward(const float *x_init, size_t pos, float *logits_host);
+    cudaError_t greedy(const void *embd_table, int embd_dtype, uint32_t first_token, size_t pos, size_t n,
+                       uint32_t *tokens_host);
+    cudaError_t set_kv(size_t pos0, size_t n, const float *k, const float *v);
+
+  private:
+    cudaError_t dev_alloc(void **out, size_t bytes);
+    cudaError_t upload(const void *host, size_t bytes, void **out);
+    cudaError_t upload_pair(const HostWeight &a, const HostWeight &b, bool interleave, Mat *out);
+    cudaError_t upload_one(const HostWeight &a, Mat *out);
+    cudaError_t mv(const Mat &m, const float *in, float *out, const float *norm_w, int epi, const float *res);
+    cudaError_t enqueue_step(int mode, const void *embd_table, int embd_dtype);
+    cudaError_t run_step(int mode, const void *embd_table, int embd_dtype);
+};
+
+} // namespace ullm

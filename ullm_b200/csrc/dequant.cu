@@ -13,10 +13,12 @@ namespace ullm {
 
 // One thread per qs byte: byte l of chunk c gives element 64c+l (low nibble)
 // and 64c+32+l (high nibble)  (dequant.rs:188-217).
-__global__ void dequant_q4k_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, size_t nblocks) {
+__global__ void dequant_q4k_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, size_t nblocks,
+                                   const uint32_t *__restrict__ row_sel, size_t row_bytes) {
     size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t b = gid >> 7;
     if (b >= nblocks) return;
+    if (row_sel) data += (size_t)(*row_sel) * row_bytes;
     int t = (int)(gid & 127), c = t >> 5, l = t & 31;
     const uint8_t *blk = data + b * Q4K_BYTES;
     float d = f16_bits_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
@@ -34,10 +36,12 @@ __global__ void dequant_q4k_kernel(const uint8_t *__restrict__ data, float *__re
 
 // One thread per (half nh, l): four elements l, l+32, l+64, l+96 of the half
 // (dequant.rs:255-282).
-__global__ void dequant_q6k_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, size_t nblocks) {
+__global__ void dequant_q6k_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, size_t nblocks,
+                                   const uint32_t *__restrict__ row_sel, size_t row_bytes) {
     size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t b = gid >> 6;
     if (b >= nblocks) return;
+    if (row_sel) data += (size_t)(*row_sel) * row_bytes;
     int t = (int)(gid & 63), nh = t >> 5, l = t & 31, is = l >> 4;
     const uint8_t *blk = data + b * Q6K_BYTES;
     const uint8_t *ql = blk + 64 * nh, *qh = blk + 128 + 32 * nh;
@@ -88,13 +92,25 @@ static inline unsigned nblk(size_t n, unsigned t) { return (unsigned)((n + t - 1
 cudaError_t launch_dequant(int dtype, const void *d_data, float *d_out, size_t n, cudaStream_t st) {
     if (n == 0) return cudaSuccess;
     switch (dtype) {
-    case 12: dequant_q4k_kernel<<<nblk(n / QK_K * 128, 256), 256, 0, st>>>((const uint8_t *)d_data, d_out, n / QK_K); break;
-    case 14: dequant_q6k_kernel<<<nblk(n / QK_K * 64, 256), 256, 0, st>>>((const uint8_t *)d_data, d_out, n / QK_K); break;
+    case 12: dequant_q4k_kernel<<<nblk(n / QK_K * 128, 256), 256, 0, st>>>((const uint8_t *)d_data, d_out, n / QK_K, nullptr, 0); break;
+    case 14: dequant_q6k_kernel<<<nblk(n / QK_K * 64, 256), 256, 0, st>>>((const uint8_t *)d_data, d_out, n / QK_K, nullptr, 0); break;
     case 1: widen_f16_kernel<<<nblk(n, 256), 256, 0, st>>>((const uint16_t *)d_data, d_out, n); break;
     case 30: widen_bf16_kernel<<<nblk(n, 256), 256, 0, st>>>((const uint16_t *)d_data, d_out, n); break;
     case 0: return cudaMemcpyAsync(d_out, d_data, n * 4, cudaMemcpyDeviceToDevice, st);
     default: return cudaErrorInvalidValue;
     }
+    return cudaGetLastError();
+}
+
+// Row `*d_row` of a [rows, cols] Q4_K / Q6_K table -> cols f32 (the embedding
+// lookup of crates/ullm-model/src/lib.rs:692-710 with the token id on the device).
+cudaError_t launch_dequant_row(int dtype, const void *d_table, const uint32_t *d_row, size_t cols, float *d_out,
+                               cudaStream_t st) {
+    if (cols % QK_K) return cudaErrorInvalidValue;
+    size_t nb = cols / QK_K;
+    if (dtype == 12) dequant_q4k_kernel<<<nblk(nb * 128, 256), 256, 0, st>>>((const uint8_t *)d_table, d_out, nb, d_row, nb * Q4K_BYTES);
+    else if (dtype == 14) dequant_q6k_kernel<<<nblk(nb * 64, 256), 256, 0, st>>>((const uint8_t *)d_table, d_out, nb, d_row, nb * Q6K_BYTES);
+    else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }
 

@@ -23,6 +23,8 @@ struct MlxTables {
 
 // dequant.cu
 cudaError_t launch_dequant(int dtype, const void *d_data, float *d_out, size_t n, cudaStream_t st);
+cudaError_t launch_dequant_row(int dtype, const void *d_table, const uint32_t *d_row, size_t cols, float *d_out,
+                               cudaStream_t st);
 cudaError_t launch_dequant_mlx4(const uint32_t *d_w, const float *d_s, const float *d_b, float *d_y, size_t out_dim,
                                 size_t in_dim, size_t group, cudaStream_t st);
 
@@ -33,9 +35,24 @@ struct MatvecPlan {
     bool streamed = false;
     int rows_per_tile = 0, warps = 0, stages = 0, smem_bytes = 0, grid = 0;
 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
+struct MatvecOpts {
+    bool force_generic = false;
+    bool pdl = false; // launch with programmatic stream serialization
+    MatvecPlan *plan_out = nullptr;
+    // Fusions (streamed kernel only; cudaErrorNotSupported when the shape needs the
+    // plain kernel):
+    const float *norm_w = nullptr; // x <- rmsnorm(x, norm_w, eps) before the product
+    float eps = 0.f;
+    int epi = EPI_STORE;           // EPI_RESIDUAL: y = res + W x;  EPI_SWIGLU: rows are
+                                   // interleaved (gate, up) pairs, y[j] = silu(Wx[2j]) * Wx[2j+1]
+    const float *res = nullptr;
+};
 cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const MlxTables &tb, const float *d_x,
                           float *d_y, size_t out_dim, size_t in_dim, int *d_status, cudaStream_t st,
-                          bool force_generic = false, bool pdl = false, MatvecPlan *plan_out = nullptr);
+                          const MatvecOpts &opts = MatvecOpts());
+bool matvec_is_streamed(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
+                        int epi);
 // Returns a static message when the shape cannot be computed at all.
 const char *matvec_shape_error(int fmt, size_t out_dim, size_t in_dim, size_t group);
 

@@ -126,6 +126,10 @@ struct StreamParams {
     const float *x;
     float *y;
     int *status;
+    const float *norm_w; // prologue: x <- rmsnorm(x, norm_w, eps) when set
+    float eps;
+    int epi;             // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU
+    const float *res;    // EPI_RESIDUAL: y[o] = res[o] + (W x)[o]  (res may alias y)
     uint32_t out_dim, in_dim, group;
     uint32_t row_bytes, tbl_row_bytes;
     uint32_t R, WC, WR, NW, S;
@@ -147,6 +151,9 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool producer = warp == p.NW;
 
+    // Under programmatic dependent launch the next kernel may be scheduled as soon
+    // as SMs free up; it only prefetches its own weights until this grid is done.
+    pdl_launch_dependents();
     if (tid == 0) {
         for (uint32_t s = 0; s < p.S; ++s) {
             mbar_init(&full[s], 1);
@@ -177,9 +184,26 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
     }
     pdl_wait_prior();
 
+    // Optional fused RMSNorm of the input (crates/ullm-model/src/math.rs:82-86):
+    // every CTA recomputes the mean square of x (a few KB from L2).
+    ActSrc src{p.x, p.norm_w, 0.f};
+    if (p.norm_w) {
+        float ss = 0.f;
+        for (uint32_t i = tid * 4; i < p.in_dim; i += blockDim.x * 4) {
+            float4 t = __ldg((const float4 *)(p.x + i));
+            ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) part[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (uint32_t w = 0; w <= p.NW; ++w) tot += part[w];
+        src.inv = 1.0f / sqrtf(tot / (float)p.in_dim + p.eps);
+        __syncthreads(); // part is reused by the row reduction below
+    }
     // x -> fixed-point register images, built once per CTA in shared memory
     for (uint32_t sl = tid; sl < p.ncg * 32u; sl += blockDim.x)
-        prep_slot<FMT>(p.x, p.in_dim, sl >> 5, sl & 31u, prep + (size_t)(sl >> 5) * XR * 32 + (sl & 31u));
+        prep_slot<FMT>(src, p.in_dim, sl >> 5, sl & 31u, prep + (size_t)(sl >> 5) * XR * 32 + (sl & 31u));
     __syncthreads();
 
     if (producer) {
@@ -242,7 +266,16 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
         float r = warp_reduce_rows<RW>(v, lane, myrow);
         const uint32_t rl = rs * RW + myrow;
         if (p.WC == 1) {
-            if ((lane & 7) == 0 && (RW == 4 || (lane & 8) == 0) && r0 + rl < p.out_dim && !aborted) p.y[r0 + rl] = r;
+            // SwiGLU on interleaved rows: even row = gate, odd row = up, held by the
+            // lane group that differs in the lowest row bit
+            float other = 0.f;
+            if (RW >= 2) other = __shfl_xor_sync(0xffffffffu, r, RW == 2 ? 16 : 8);
+            const bool writer = (lane & 7) == 0 && (RW == 4 || (lane & 8) == 0) && (RW > 1 || lane == 0);
+            if (writer && r0 + rl < p.out_dim && !aborted) {
+                if (p.epi == EPI_STORE) p.y[r0 + rl] = r;
+                else if (p.epi == EPI_RESIDUAL) p.y[r0 + rl] = p.res[r0 + rl] + r;
+                else if ((myrow & 1) == 0) p.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
+            }
         } else {
             float *pt = part + (size_t)(k & 1) * p.R * p.WC;
             if ((lane & 7) == 0 && (RW == 4 || (lane & 8) == 0)) pt[rl * p.WC + cgw] = r;
@@ -252,7 +285,15 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
                 const uint32_t row = rs * RW + sl;
                 float acc = 0.f;
                 for (uint32_t c = 0; c < p.WC; ++c) acc += pt[row * p.WC + c];
-                if (r0 + row < p.out_dim && !aborted) p.y[r0 + row] = acc;
+                if (r0 + row < p.out_dim && !aborted) {
+                    if (p.epi == EPI_STORE) p.y[r0 + row] = acc;
+                    else if (p.epi == EPI_RESIDUAL) p.y[r0 + row] = p.res[r0 + row] + acc;
+                    else if ((sl & 1) == 0) {
+                        float up = 0.f;
+                        for (uint32_t c = 0; c < p.WC; ++c) up += pt[(row + 1) * p.WC + c];
+                        p.y[(r0 + row) >> 1] = acc / (1.0f + expf(-acc)) * up;
+                    }
+                }
             }
         }
     }
@@ -287,7 +328,8 @@ struct Plan {
     double score = 0;
 };
 
-static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes) {
+static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
+                        int epi) {
     Plan best;
     const uint32_t cg_elems = fmt == FMT_Q4K ? 2048u : 1024u;
     const uint32_t xregs = fmt == FMT_Q4K ? XREGS_Q4K : (fmt == FMT_Q6K ? XREGS_Q6K : XREGS_MLX);
@@ -308,7 +350,7 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
     for (uint32_t WR = 1; WR <= 16; WR *= 2) {
         if (WC * WR > 16) break;
         if (WC > 1 && WR > 8) break; // named barriers 1..8
-        for (uint32_t RW = 1; RW <= 4; RW *= 2) {
+        for (uint32_t RW = (epi == EPI_SWIGLU ? 2 : 1); RW <= 4; RW *= 2) {
             const uint32_t R = WR * RW;
             if ((R * row_bytes) % 16 || (R * tbl_row_bytes) % 16) continue;
             if (out_dim % R && ((row_bytes % 16) || (tbl_row_bytes % 16))) continue;
@@ -391,28 +433,33 @@ static cudaError_t launch_generic_t(const void *d_w, const MlxTables &tb, const 
 }
 
 cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const MlxTables &tb, const float *d_x,
-                          float *d_y, size_t out_dim, size_t in_dim, int *d_status, cudaStream_t st, bool force_generic,
-                          bool pdl, MatvecPlan *plan_out) {
+                          float *d_y, size_t out_dim, size_t in_dim, int *d_status, cudaStream_t st,
+                          const MatvecOpts &o) {
     Plan pl;
+    const bool fused = o.norm_w || o.epi != EPI_STORE;
     const bool aligned = ((uintptr_t)d_w % 16 == 0) && ((uintptr_t)d_x % 16 == 0) &&
+                         (!o.norm_w || (uintptr_t)o.norm_w % 16 == 0) &&
                          (fmt != FMT_MLX4 || ((uintptr_t)tb.scales % 16 == 0 && (uintptr_t)tb.biases % 16 == 0));
-    if (!force_generic && aligned) pl = plan_stream(dev, fmt, out_dim, in_dim, tb.group, tb.elem_bytes);
-    if (plan_out) {
-        plan_out->streamed = pl.ok;
-        plan_out->rows_per_tile = pl.ok ? (int)pl.p.R : 8;
-        plan_out->warps = pl.ok ? (int)pl.p.NW : 8;
-        plan_out->stages = pl.ok ? (int)pl.p.S : 0;
-        plan_out->smem_bytes = pl.ok ? (int)pl.smem : 0;
-        plan_out->grid = pl.ok ? pl.grid : (int)((out_dim + 7) / 8);
+    if (o.epi == EPI_SWIGLU && (out_dim & 1)) return cudaErrorInvalidValue;
+    if (!o.force_generic && aligned) pl = plan_stream(dev, fmt, out_dim, in_dim, tb.group, tb.elem_bytes, o.epi);
+    if (o.plan_out) {
+        o.plan_out->streamed = pl.ok;
+        o.plan_out->rows_per_tile = pl.ok ? (int)pl.p.R : 8;
+        o.plan_out->warps = pl.ok ? (int)pl.p.NW : 8;
+        o.plan_out->stages = pl.ok ? (int)pl.p.S : 0;
+        o.plan_out->smem_bytes = pl.ok ? (int)pl.smem : 0;
+        o.plan_out->grid = pl.ok ? pl.grid : (int)((out_dim + 7) / 8);
     }
     if (pl.ok) {
         pl.p.w = (const uint8_t *)d_w, pl.p.scales = (const uint8_t *)tb.scales, pl.p.biases = (const uint8_t *)tb.biases;
         pl.p.x = d_x, pl.p.y = d_y, pl.p.status = d_status;
-        if (fmt == FMT_Q4K) return launch_stream_f<FMT_Q4K, float>(pl, st, pdl);
-        if (fmt == FMT_Q6K) return launch_stream_f<FMT_Q6K, float>(pl, st, pdl);
-        if (tb.elem_bytes == 2) return launch_stream_f<FMT_MLX4, uint16_t>(pl, st, pdl);
-        return launch_stream_f<FMT_MLX4, float>(pl, st, pdl);
+        pl.p.norm_w = o.norm_w, pl.p.eps = o.eps, pl.p.epi = o.epi, pl.p.res = o.res;
+        if (fmt == FMT_Q4K) return launch_stream_f<FMT_Q4K, float>(pl, st, o.pdl);
+        if (fmt == FMT_Q6K) return launch_stream_f<FMT_Q6K, float>(pl, st, o.pdl);
+        if (tb.elem_bytes == 2) return launch_stream_f<FMT_MLX4, uint16_t>(pl, st, o.pdl);
+        return launch_stream_f<FMT_MLX4, float>(pl, st, o.pdl);
     }
+    if (fused) return cudaErrorNotSupported; // the plain kernel has no fused prologue / epilogue
     if (fmt == FMT_Q4K) return launch_generic_t<FMT_Q4K, float>(d_w, tb, d_x, d_y, 0, out_dim, in_dim, st);
     if (fmt == FMT_Q6K) return launch_generic_t<FMT_Q6K, float>(d_w, tb, d_x, d_y, 0, out_dim, in_dim, st);
     if (fmt == FMT_MLX4) {
@@ -420,6 +467,11 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
         return launch_generic_t<FMT_MLX4, float>(d_w, tb, d_x, d_y, 0, out_dim, in_dim, st);
     }
     return cudaErrorInvalidValue;
+}
+
+bool matvec_is_streamed(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
+                        int epi) {
+    return plan_stream(dev, fmt, out_dim, in_dim, group, tbl_bytes, epi).ok;
 }
 
 } // namespace ullm

@@ -152,6 +152,7 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
     pdl_wait_prior(); // the routing table and the activations come from earlier kernels
 
     const int D = p.route[0];
