@@ -146,6 +146,26 @@ int ullm_cuda_moe_ffn(ullm_cuda_ctx *ctx, const ullm_cuda_experts *e, const floa
 int ullm_cuda_moe_ffn_dev(ullm_cuda_ctx *ctx, const ullm_cuda_experts *e, const float *d_x, const float *d_logits,
                           size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *stream);
 
+/* No counterpart in the reference.  The same FFN for callers that must not
+ * allocate device memory: programs whose own memory pool owns the whole GPU (a
+ * cudaMalloc behind its back fails or steals from it) and latency-critical loops
+ * that cannot take cudaMalloc's device-wide synchronisation.  Every array of
+ * `dev_experts`, and `d_x` / `d_logits` / `d_y`, are device pointers the caller
+ * owns (16-byte aligned); the kernels' scratch lives in a fixed array inside the
+ * library, ULLM_CUDA_MOE_NOALLOC_SCRATCH_BYTES on every GPU that loads it.
+ *  - Problems needing more scratch (roughly 128*(hidden+inter)*4 bytes + 16 KB)
+ *    are rejected with ULLM_ERR_FORMAT.
+ *  - The first call on a device performs a one-time address look-up: make it at
+ *    start-up, before any stream capture.
+ *  - The array is shared by all calls and keeps the previous call's contents;
+ *    calls whose kernels overlap on the GPU race on it — serialise them.
+ *  - Blocks until the result is in `d_y`.  Never calls cudaMalloc / cudaFree.
+ * `err` (may be NULL) receives a message on failure. */
+#define ULLM_CUDA_MOE_NOALLOC_SCRATCH_BYTES (4u << 20)
+int ullm_cuda_moe_ffn_noalloc(int device, const ullm_moe_experts_input *dev_experts, const float *d_x,
+                              const float *d_logits, size_t n_tok, size_t k, float *d_y, void *stream, char *err,
+                              size_t err_cap);
+
 /* ---- full decode step: GpuForward (forward.rs:162-757) ---- */
 typedef struct { /* GpuParams, forward.rs:24-51 */
     size_t n_embd, n_layer, n_head, n_kv_head, head_dim, n_ff, n_ctx, vocab;

@@ -73,6 +73,7 @@ SIGNATURES = {
     "ullm_cuda_experts_destroy": (None, [_vp, _vp]),
     "ullm_cuda_moe_ffn": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp]),
     "ullm_cuda_moe_ffn_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
+    "ullm_cuda_moe_ffn_noalloc": (_i, [_i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, C.c_char_p, _sz]),
     "ullm_cuda_forward_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "ullm_cuda_forward_destroy": (None, [_vp]),
     "ullm_cuda_forward": (_i, [_vp, _vp, _sz, _vp]),
