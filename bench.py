@@ -14,8 +14,8 @@ synthetic input:
   the ranks, followed by an NCCL all-gather of each output vector.
 
 ``value`` is device-timed (CUDA events on the launching stream, max over ranks);
-``e2e`` goes through the host-buffer entry point ``matvec_resident`` with pinned
-host activations (host<->device copies inside the timed region).
+``e2e`` goes through the host-buffer entry point ``ullm_cuda_weight_matvec`` with
+pinned host activations (host<->device copies inside the timed region).
 ``--impl reference`` times the CPU restatement of the reference's path (the
 oracle port, OpenMP over rows) on the host cores for the same workload.
 """
@@ -197,16 +197,17 @@ def run_single(args):
     w_dn_h = synth.gen_q6k(*C1_DOWN, synth.seed_for(1, 1))
     x_h = synth.normal(synth.seed_for(1, 2), C1_UP[1])
     ncopies = args.copies  # 2 * 48 MB per copy; the walk must exceed L2 (126 MB) several times
-    ups = [torch.from_numpy(w_up_h.reshape(-1)).to(dev) for _ in range(ncopies)]
-    dns = [torch.from_numpy(w_dn_h.reshape(-1)).to(dev) for _ in range(ncopies)]
+    # resident weight objects (what GpuForward::new builds from a GpuWeight): one device copy each
+    ups = [backend.Weight(ctx, backend.Q6_K, w_up_h, *C1_UP) for _ in range(ncopies)]
+    dns = [backend.Weight(ctx, backend.Q6_K, w_dn_h, *C1_DOWN) for _ in range(ncopies)]
     x = torch.from_numpy(x_h).to(dev)
     h = torch.empty(C1_UP[0], dtype=torch.float32, device=dev)
     y = torch.empty(C1_DOWN[0], dtype=torch.float32, device=dev)
 
     def step(i):
         c = i % ncopies
-        ctx.matvec_dev(backend.Q6_K, ups[c].data_ptr(), x.data_ptr(), h.data_ptr(), *C1_UP, stream=stream)
-        ctx.matvec_dev(backend.Q6_K, dns[c].data_ptr(), h.data_ptr(), y.data_ptr(), *C1_DOWN, stream=stream)
+        ups[c].matvec_dev(x.data_ptr(), h.data_ptr(), stream)
+        dns[c].matvec_dev(h.data_ptr(), y.data_ptr(), stream)
 
     if args.pdl:
         ctx.debug_set("pdl", 1)
@@ -215,30 +216,46 @@ def run_single(args):
     torch.cuda.synchronize()
     plan = ctx.last_plan()
 
+    # The K timed steps are captured into one CUDA graph and replayed, so the host's
+    # launch rate (a few microseconds per call from Python) is not what is measured.
+    side = torch.cuda.Stream()
+    graph = None
+    if not args.eager:
+        stream = side.cuda_stream
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(args.steps):
+                step(args.warmup + i)
+        graph.replay()  # one untimed replay
+        torch.cuda.synchronize()
+
     sampler = ClockSampler(0)
     sampler.start()
     time.sleep(0.3)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
-    ev0.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    ev1.record()
+    with torch.cuda.stream(side):
+        ev0.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            stream = side.cuda_stream
+            for i in range(args.steps):
+                step(args.warmup + i)
+        ev1.record()
     torch.cuda.synchronize()
     ctx.synchronize()  # surfaces a device-side timeout status
     ms = ev0.elapsed_time(ev1)
 
     # end to end: host buffers in, host buffers out, through matvec_resident
-    up_buf = [ctx.upload(w_up_h) for _ in range(ncopies)]
-    dn_buf = [ctx.upload(w_dn_h) for _ in range(ncopies)]
     xp = torch.from_numpy(x_h).pin_memory().numpy()
     hp = torch.empty(C1_UP[0], dtype=torch.float32).pin_memory().numpy()
     yp = torch.empty(C1_DOWN[0], dtype=torch.float32).pin_memory().numpy()
 
     def e2e_step(i):
         c = i % ncopies
-        ctx.matvec_resident(backend.Q6_K, up_buf[c], xp, *C1_UP, out=hp)
-        ctx.matvec_resident(backend.Q6_K, dn_buf[c], hp, *C1_DOWN, out=yp)
+        ups[c].matvec(xp, out=hp)
+        dns[c].matvec(hp, out=yp)
 
     for i in range(args.warmup):
         e2e_step(i)
@@ -278,20 +295,134 @@ def run_single(args):
         "vs_baseline": None, "dtype": "int8 dot products (16-bit fixed-point x) + f32 accumulate", "data": "synthetic",
         "config": {"workload": "c1_q6k_ffn_pair", "shapes": "Q6_K [14336,4096] then Q6_K [4096,14336], batch 1",
                    "l2": f"{ncopies} distinct weight copies ({ncopies * 96} MB) walked round-robin: inputs larger than L2",
-                   "plan": plan, "pdl": bool(args.pdl), "frac_of_8000": value / 8000.0},
+                   "plan": plan, "pdl": bool(args.pdl), "launch": "eager" if args.eager else "one CUDA graph of all timed steps",
+                   "frac_of_8000": value / 8000.0},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_PER_LAUNCH["c1_q6k_ffn_pair"], "peak_kind": f"of {peak_kind}",
-                     "kernel": "matvec_stream_kernel<Q6_K>", "launch_us": launch_us,
+                     "kernel": "matvec_stream_kernel<Q6_K prepared>", "launch_us": launch_us,
                      "algorithmic_bytes_per_launch": C1_BYTES_PER_LAUNCH},
         "cpu_baseline": cpu,
         "e2e": {"value": args.steps * step_bytes / e2e_s / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": 4 * (C1_UP[1] + C1_DOWN[1]), "d2h_bytes_per_step": 4 * (C1_UP[0] + C1_DOWN[0]),
-                "us_per_step": e2e_s / args.steps * 1e6, "api": "ullm_cuda_matvec_resident (pinned host x / y)"},
+                "us_per_step": e2e_s / args.steps * 1e6, "api": "ullm_cuda_weight_matvec (resident weight, pinned host x / y)"},
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
         "check": check,
     }
     print(json.dumps(line), flush=True)
+    return 0
+
+
+def _time_steps(torch, step, steps, warmup):
+    """step(i, stream) enqueues step i; the timed steps run as one CUDA graph."""
+    cur = torch.cuda.current_stream().cuda_stream
+    for i in range(warmup):
+        step(i, cur)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(steps):
+            step(warmup + i, side.cuda_stream)
+    graph.replay()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(side):
+        ev0.record()
+        graph.replay()
+        ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1)
+
+
+def run_other(args):
+    """Single-GPU measurements of the other benchmark configurations (parity-test
+    cases; reported for the design notes, not the headline line)."""
+    import torch
+
+    from ullm_b200 import backend
+
+    torch.cuda.set_device(0)
+    ctx = backend.CudaContext(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    dev = torch.device("cuda:0")
+    peak, peak_kind = measured_peak_gbs()
+    if args.pdl:
+        ctx.debug_set("pdl", 1)
+    out = {"workload": args.workload, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "pdl": bool(args.pdl)}
+
+    if args.workload == "c0":
+        shape = (4096, 4096)
+        w = synth.gen_q4k(*shape, synth.seed_for(0, 0))
+        n = 40  # 9.4 MB each: 377 MB walked round-robin
+        ws = [backend.Weight(ctx, backend.Q4_K, w, *shape) for _ in range(n)]
+        x = torch.from_numpy(synth.normal(synth.seed_for(0, 1), shape[1])).to(dev)
+        y = torch.empty(shape[0], dtype=torch.float32, device=dev)
+        ms = _time_steps(torch, lambda i, st: ws[i % n].matvec_dev(x.data_ptr(), y.data_ptr(), st), args.steps, args.warmup)
+        nbytes = weight_bytes(synth.Q4_K, *shape) + 4 * sum(shape)
+        out.update(us_per_launch=ms * 1e3 / args.steps, gbs=args.steps * nbytes / ms / 1e6, bytes_per_launch=nbytes, plan=ctx.last_plan())
+    elif args.workload == "c4":
+        mats = []
+        for i, (name, dt, o, c) in enumerate(C4_MATS):
+            w = synth.gen_weight(dt, o, c, synth.seed_for(4, i))
+            mats.append((backend.Weight(ctx, dt, w, o, c), torch.from_numpy(synth.normal(synth.seed_for(4, 8 + i), c)).to(dev),
+                         torch.empty(o, dtype=torch.float32, device=dev)))
+
+        def step(_i, st):
+            for w, xv, yv in mats:
+                w.matvec_dev(xv.data_ptr(), yv.data_ptr(), st)
+
+        ms = _time_steps(torch, step, args.steps, args.warmup)
+        nbytes = sum(weight_bytes(dt, o, c) + 4 * (o + c) for _, dt, o, c in C4_MATS)
+        out.update(us_per_step=ms * 1e3 / args.steps, gbs=args.steps * nbytes / ms / 1e6, bytes_per_step=nbytes)
+    elif args.workload == "c2":
+        ne, hid, inter, gs, ntok, k = 128, 2048, 768, 64, 8, 8
+        g = synth.gen_mlx4(ne * inter, hid, gs, synth.seed_for(2, 0))
+        u = synth.gen_mlx4(ne * inter, hid, gs, synth.seed_for(2, 1))
+        d = synth.gen_mlx4(ne * hid, inter, gs, synth.seed_for(2, 2))
+        exs = [backend.Experts(ctx, g, u, d, ne, hid, inter, gs) for _ in range(2)]  # 2 x 340 MB
+        x = torch.from_numpy(synth.normal(synth.seed_for(2, 4), ntok * hid)).to(dev)
+        lgs, dist = [], []
+        for j in range(4):
+            lg = synth.router_logits(ntok, ne, k, synth.seed_for(2, 5) + 977 * j)
+            dist.append(len(np.unique(np.argsort(-lg, axis=1)[:, :k])))
+            lgs.append(torch.from_numpy(lg).to(dev))
+        y = torch.empty(ntok * hid, dtype=torch.float32, device=dev)
+        ms = _time_steps(torch, lambda i, st: exs[i % 2].moe_ffn_dev(x.data_ptr(), lgs[i % 4].data_ptr(), ntok, k, y.data_ptr(), stream=st), args.steps, args.warmup)
+        D = sum(dist) / len(dist)
+        nbytes = D * 2_654_208 + 131_072
+        out.update(us_per_step=ms * 1e3 / args.steps, distinct_experts=D, gbs=args.steps * nbytes / ms / 1e6,
+                   bytes_per_step=nbytes, launches_per_step=4)
+    elif args.workload == "c3":
+        p = dict(synth.LLAMA_1B)
+        m = synth.gen_llama_model(p, synth.seed_for(3, 0))
+        kk, vv = synth.gen_kv_prefill(p, 1024, synth.seed_for(3, 1))
+        gf = backend.GpuForward(ctx, m, kv_f16=True)
+        gf.set_kv(0, kk, vv)
+        embd = ctx.upload(m["tok_embd"][1])
+        prompt = synth.rand_ints(synth.seed_for(3, 2), 16, 0, p["vocab"] - 1)
+        import oracle  # embedding rows for the prompt (host-side lookup, as the reference does)
+
+        emb_w = oracle.Weight(m["tok_embd"][0], m["tok_embd"][1], p["vocab"], p["n_embd"])
+        t0 = time.perf_counter()
+        for i, t in enumerate(prompt):
+            row = oracle.dequantize(m["tok_embd"][0], m["tok_embd"][1][int(t)], p["n_embd"])
+            lg = gf.forward(row, 1024 + i)
+        t_prompt = time.perf_counter() - t0
+        tok = int(np.argmax(lg))
+        n_gen = 128 if args.steps == 500 else args.steps  # 128 tokens unless --steps is given
+        gf.greedy(embd, m["tok_embd"][0], tok, 1040, min(8, n_gen))  # warm the greedy graph
+        t0 = time.perf_counter()
+        toks = gf.greedy(embd, m["tok_embd"][0], tok, 1040, n_gen)
+        dt = time.perf_counter() - t0
+        wbytes = 16 * 38_805_504 + 215_470_080
+        kvbytes = 32_768 * (1040 + 64)
+        out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, prompt_ms_per_token=t_prompt / 16 * 1e3, tokens=n_gen,
+                   bytes_per_token=wbytes + kvbytes + 513_024, gbs=(wbytes + kvbytes + 513_024) * n_gen / dt / 1e9,
+                   first_tokens=toks[:8].tolist())
+    out["frac_of_measured_peak"] = out["gbs"] / peak
+    out["peak_kind"] = peak_kind
+    print(json.dumps(out), flush=True)
     return 0
 
 
@@ -316,18 +447,25 @@ def run_multi(args):
         # each rank generates only its own row slice (rows are self-contained byte ranges)
         w = synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1))
         xv = synth.normal(synth.seed_for(4, 8 + i), cols)
-        mats.append(dict(dt=dt, rows=rows, out=out, cols=cols, w=torch.from_numpy(w.reshape(-1)).to(dev),
+        mats.append(dict(dt=dt, rows=rows, out=out, cols=cols, w=backend.Weight(ctx, dt, w, rows, cols),
                          x=torch.from_numpy(xv).to(dev), y_local=torch.empty(rows, dtype=torch.float32, device=dev),
                          y_full=torch.empty(out, dtype=torch.float32, device=dev)))
 
+    # Kernels and NCCL collectives share one non-default stream: a NULL stream handle
+    # would send the kernels to the context's own stream, unordered with NCCL.
+    side = torch.cuda.Stream()
+    stream = side.cuda_stream
+
     def step(_i):
         for m in mats:
-            ctx.matvec_dev(m["dt"], m["w"].data_ptr(), m["x"].data_ptr(), m["y_local"].data_ptr(), m["rows"], m["cols"], stream=stream)
+            m["w"].matvec_dev(m["x"].data_ptr(), m["y_local"].data_ptr(), stream)
         for m in mats:
             dist.all_gather_into_tensor(m["y_full"], m["y_local"])
 
-    for i in range(args.warmup):
-        step(i)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        for i in range(args.warmup):
+            step(i)
     torch.cuda.synchronize()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -336,10 +474,11 @@ def run_multi(args):
     dist.barrier()
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        step(i)
-    ev1.record()
+    with torch.cuda.stream(side):
+        ev0.record()
+        for i in range(args.steps):
+            step(i)
+        ev1.record()
     torch.cuda.synchronize()
     dist.barrier()
     ctx.synchronize()
@@ -380,11 +519,16 @@ def main():
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--pdl", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
+    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"],
+                    help="single-GPU only: c1 is the headline workload, the others are auxiliary measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         return run_multi(args)
+    if args.workload != "c1":
+        return run_other(args)
     return run_single(args)
 
 

@@ -62,6 +62,7 @@ typedef struct ullm_cuda_ctx ullm_cuda_ctx;
 typedef struct ullm_cuda_buf ullm_cuda_buf;
 typedef struct ullm_cuda_fwd ullm_cuda_fwd;
 typedef struct ullm_cuda_experts ullm_cuda_experts;
+typedef struct ullm_cuda_weight ullm_cuda_weight;
 
 /* ---- context: MetalContext::new / device_name (ullm-metal/src/lib.rs:31, :59) ---- */
 int ullm_cuda_ctx_create(int device, ullm_cuda_ctx **out);
@@ -108,6 +109,27 @@ int ullm_cuda_matvec_mlx4(ullm_cuda_ctx *ctx, const void *w, const float *scales
 int ullm_cuda_matvec_dev(ullm_cuda_ctx *ctx, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
                          int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
                          void *stream);
+
+/* ---- resident weight matrices ----
+ * A weight made resident for the kernels: the `WBuf` that `GpuForward::new` builds
+ * from a `GpuWeight` (forward.rs:119-126, :253-268).  The bytes are copied; Q6_K
+ * rows whose length is a multiple of 16 bytes are re-ordered on the device into an
+ * aligned layout of the same size (`ullm_cuda_weight_export` returns the original
+ * bytes, so nothing is lost).  `w` is a `ullm_gpu_weight` (declared below); for MLX
+ * weights `mlx_table_dtype` says whether `mlx_scales` / `mlx_biases` point at f32
+ * values (ULLM_DTYPE_F32, as the reference passes them) or at the bf16 bits stored
+ * on disk (ULLM_DTYPE_BF16, kept as such). */
+struct ullm_gpu_weight_s;
+int ullm_cuda_weight_create(ullm_cuda_ctx *ctx, const struct ullm_gpu_weight_s *w, int mlx_table_dtype,
+                            ullm_cuda_weight **out);
+void ullm_cuda_weight_destroy(ullm_cuda_ctx *ctx, ullm_cuda_weight *w);
+/* GpuForward::matvec (forward.rs:639-673): y = W x, host vectors, blocking. */
+int ullm_cuda_weight_matvec(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *x, float *y);
+/* The same on device vectors, enqueued on `stream` (NULL = the context's). */
+int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *d_x, float *d_y, void *stream);
+/* The weight's original on-disk bytes (`len` = ullm_cuda_weight_bytes). */
+int ullm_cuda_weight_export(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, void *bytes, size_t len);
+size_t ullm_cuda_weight_bytes(const ullm_cuda_weight *w);
 
 /* ---- batched matmul (prefill) ----
  * GpuForward::matmul (forward.rs:679-725; kernels matmul_q4k / matmul_q6k /
@@ -176,7 +198,7 @@ typedef struct { /* GpuParams, forward.rs:24-51 */
      * as IEEE half when non-zero. */
     int kv_f16;
 } ullm_gpu_params;
-typedef struct { /* GpuWeight, forward.rs:56-64 */
+typedef struct ullm_gpu_weight_s { /* GpuWeight, forward.rs:56-64 */
     int dtype;
     const void *bytes;
     size_t len, out, cols;

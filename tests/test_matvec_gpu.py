@@ -246,3 +246,65 @@ def test_matmul_mlx4_pattern(ctx):  # crates/ullm-metal/src/lib.rs:474-515: abs 
     cpu = oracle.matmul_q(oracle.Weight(oracle.MLX_U32, w, 96, 256, sc, b, 64), x.reshape(s, 256), s)
     gpu = ctx.matmul_mlx4(w, sc, b, x, 96, 256, 64, s)
     assert np.max(np.abs(gpu - cpu)) < 1e-3
+
+
+# ---- resident weight objects (prepared layouts) -----------------------------------
+WEIGHT_SHAPES = [
+    (backend.Q6_K, 14336, 4096),   # config 1 up: rows prepared (in % 2048 == 0)
+    (backend.Q6_K, 4096, 14336),   # config 1 down
+    (backend.Q6_K, 2048, 8192),
+    (backend.Q6_K, 37, 2048),      # ragged row count, one column group partly filled
+    (backend.Q6_K, 64, 28672),     # two column groups per warp
+    (backend.Q6_K, 24, 768),       # rows not 16-byte multiples: stays verbatim
+    (backend.Q4_K, 4096, 4096),
+    (backend.Q4_K, 1000, 512),
+]
+
+
+@pytest.mark.parametrize("dtype,out,cols", WEIGHT_SHAPES)
+def test_weight_object_matvec_and_lossless_export(ctx, dtype, out, cols):
+    w = GEN[dtype](out, cols, synth.seed_for(1, out % 7))
+    x = synth.normal(synth.seed_for(1, 3), cols)
+    wt = backend.Weight(ctx, dtype, w, out, cols)
+    got = wt.matvec(x)
+    cpu = oracle.matvec_q(oracle.Weight(dtype, w, out, cols), x)
+    assert synth.rel_err(got, cpu) < TOL, ctx.last_plan()
+    assert np.array_equal(wt.export(), w.reshape(-1))  # the prepared layout loses nothing
+    assert np.array_equal(got, wt.matvec(x))
+    wt.free()
+
+
+def test_weight_object_mlx_and_errors(ctx):
+    w, s, b = synth.gen_mlx4(768, 2048, 64, 9)
+    x = synth.normal(10, 2048)
+    cpu = oracle.matvec_q(oracle.Weight(oracle.MLX_U32, w, 768, 2048, synth.bf16_to_f32(s), synth.bf16_to_f32(b), 64), x)
+    for tables in ((s, b), (synth.bf16_to_f32(s), synth.bf16_to_f32(b))):
+        wt = backend.Weight(ctx, backend.MLX_U32, w, 768, 2048, tables[0], tables[1], 64)
+        assert synth.rel_err(wt.matvec(x), cpu) < TOL
+        wt.free()
+    with pytest.raises(backend.Unsupported):
+        backend.Weight(ctx, backend.F32, np.zeros(16, np.float32), 4, 4)
+    with pytest.raises(backend.FormatError):
+        backend.Weight(ctx, backend.Q4_K, np.zeros(100, np.uint8), 4, 256)
+
+
+@pytest.mark.parametrize("wr,rw", [(1, 1), (2, 2), (3, 4), (6, 1), (12, 1)])
+def test_streamed_plan_variants_agree(ctx, wr, rw):
+    """Every tile shape the planner may pick computes the same product."""
+    out, cols = 1111 * 0 + 1024, 4096
+    for dtype in (backend.Q6_K, backend.Q4_K):
+        w = GEN[dtype](out, cols, 51)
+        x = synth.normal(52, cols)
+        cpu = oracle.matvec_q(oracle.Weight(dtype, w, out, cols), x)
+        wt = backend.Weight(ctx, dtype, w, out, cols)
+        ctx.debug_set("plan_wr", wr)
+        ctx.debug_set("plan_rw", rw)
+        try:
+            got = wt.matvec(x)
+            plan = ctx.last_plan()
+        finally:
+            ctx.debug_set("plan_wr", 0)
+            ctx.debug_set("plan_rw", 0)
+        assert plan["streamed"] == 1 and plan["rows_per_tile"] == wr * rw, plan
+        assert synth.rel_err(got, cpu) < TOL
+        wt.free()

@@ -66,6 +66,12 @@ SIGNATURES = {
     "ullm_cuda_matvec_resident": (_i, [_vp, _i, _vp, _vp, _vp, _sz, _sz]),
     "ullm_cuda_matvec_mlx4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ullm_cuda_matvec_dev": (_i, [_vp, _i, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _sz, _vp]),
+    "ullm_cuda_weight_create": (_i, [_vp, _vp, _i, C.POINTER(_vp)]),
+    "ullm_cuda_weight_destroy": (None, [_vp, _vp]),
+    "ullm_cuda_weight_matvec": (_i, [_vp, _vp, _vp, _vp]),
+    "ullm_cuda_weight_matvec_dev": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "ullm_cuda_weight_export": (_i, [_vp, _vp, _vp, _sz]),
+    "ullm_cuda_weight_bytes": (_sz, [_vp]),
     "ullm_cuda_matmul_quant": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "ullm_cuda_matmul_mlx4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),
     "ullm_cuda_matmul_dev": (_i, [_vp, _i, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _sz, _sz, _vp]),
@@ -268,6 +274,58 @@ class CudaContext:
         return dict(zip(("streamed", "rows_per_tile", "warps", "stages", "smem_bytes", "grid"), list(v)))
 
 
+class GpuWeight(C.Structure):
+    """``GpuWeight`` (forward.rs:56-64)."""
+
+    _fields_ = [("dtype", _i), ("bytes", _vp), ("len", _sz), ("out", _sz), ("cols", _sz), ("mlx_scales", _vp), ("mlx_biases", _vp), ("mlx_group", _sz)]
+
+
+class Weight:
+    """A resident weight matrix (``WBuf``, crates/ullm-metal/src/forward.rs:119-126):
+    built from a ``GpuWeight`` the way ``GpuForward::new`` does (forward.rs:253-268)."""
+
+    def __init__(self, ctx: CudaContext, dtype: int, data, out_dim: int, cols: int, scales=None, biases=None, group: int = 0):
+        self._ctx = ctx
+        b = _bytes(data)
+        tdt = F32
+        s = bi = None
+        if scales is not None:
+            if np.asarray(scales).dtype == np.uint16:
+                tdt, s, bi = BF16, np.ascontiguousarray(scales, np.uint16), np.ascontiguousarray(biases, np.uint16)
+            else:
+                s, bi = _f32(scales), _f32(biases)
+        gw = GpuWeight(dtype, b.ctypes.data, b.size, out_dim, cols, _ptr(s), _ptr(bi), group)
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_weight_create(ctx._h, C.byref(gw), tdt, C.byref(h)))
+        self._h, self.out, self.cols, self.dtype = h.value, out_dim, cols, dtype
+
+    def matvec(self, x, out: np.ndarray | None = None) -> np.ndarray:
+        x = _f32(x)
+        y = np.empty(self.out, np.float32) if out is None else out
+        self._ctx._check(self._ctx._lib.ullm_cuda_weight_matvec(self._ctx._h, self._h, _ptr(x), _ptr(y)))
+        return y
+
+    def matvec_dev(self, d_x: int, d_y: int, stream=None):
+        self._ctx._check(self._ctx._lib.ullm_cuda_weight_matvec_dev(self._ctx._h, self._h, d_x, d_y, stream))
+
+    def export(self) -> np.ndarray:
+        n = self._ctx._lib.ullm_cuda_weight_bytes(self._h)
+        out = np.empty(n, np.uint8)
+        self._ctx._check(self._ctx._lib.ullm_cuda_weight_export(self._ctx._h, self._h, _ptr(out), n))
+        return out
+
+    def free(self):
+        if getattr(self, "_h", None):
+            self._ctx._lib.ullm_cuda_weight_destroy(self._ctx._h, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class MoeExpertsInput(C.Structure):
     """``ullm_moe_experts_input`` (GpuExperts x3, crates/ullm-metal/src/forward.rs:67-75)."""
 
@@ -330,12 +388,6 @@ class GpuParams(C.Structure):
                 + [(n, _i) for n in ("rope_neox", "qk_norm", "sandwich_norm", "geglu")]
                 + [(n, _sz) for n in ("n_experts", "n_experts_used", "moe_inter", "sliding_window")]
                 + [("kv_f16", _i)])
-
-
-class GpuWeight(C.Structure):
-    """``GpuWeight`` (forward.rs:56-64)."""
-
-    _fields_ = [("dtype", _i), ("bytes", _vp), ("len", _sz), ("out", _sz), ("cols", _sz), ("mlx_scales", _vp), ("mlx_biases", _vp), ("mlx_group", _sz)]
 
 
 class GpuLayerInput(C.Structure):

@@ -277,6 +277,118 @@ int ullm_cuda_matvec_mlx4(ullm_cuda_ctx *c, const void *w, const float *scales, 
     return matvec_host(c, ULLM_DTYPE_MLX_U32, d_w, d_s, d_b, ULLM_DTYPE_F32, group, x, y, out_dim, in_dim);
 }
 
+// ---- resident weights ------------------------------------------------------
+struct ullm_cuda_weight {
+    int fmt = 0;          // kernel format, FMT_Q6KR when the rows were prepared
+    int dtype = 0;        // ullm_dtype the caller gave
+    void *w = nullptr;
+    void *scales = nullptr, *biases = nullptr;
+    int table_bytes = 4;
+    size_t group = 0, out = 0, cols = 0, nbytes = 0, tbytes = 0;
+};
+
+int ullm_cuda_weight_create(ullm_cuda_ctx *c, const ullm_gpu_weight *gw, int mlx_table_dtype, ullm_cuda_weight **out) {
+    if (!c || !gw || !out || !gw->bytes) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    int fmt = fmt_of(gw->dtype);
+    if (fmt < 0) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "no CUDA forward kernel for dtype %d", gw->dtype); // forward.rs:376-378
+    if (const char *m = matvec_shape_error(fmt, gw->out, gw->cols, gw->mlx_group)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    const size_t need = weight_bytes(fmt, gw->out, gw->cols);
+    if (gw->len < need) return ctx_fail(c, ULLM_ERR_FORMAT, "need %zu weight bytes, have %zu", need, gw->len);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    ullm_cuda_weight *w = new (std::nothrow) ullm_cuda_weight();
+    if (!w) return ULLM_ERR_OOM;
+    w->fmt = fmt, w->dtype = gw->dtype, w->out = gw->out, w->cols = gw->cols, w->nbytes = need, w->group = gw->mlx_group;
+    cudaError_t e = cudaMalloc(&w->w, need);
+    if (e == cudaSuccess && fmt == FMT_MLX4) {
+        if (!gw->mlx_scales || !gw->mlx_biases || (mlx_table_dtype != ULLM_DTYPE_F32 && mlx_table_dtype != ULLM_DTYPE_BF16)) {
+            ullm_cuda_weight_destroy(c, w);
+            return ctx_fail(c, ULLM_ERR_FORMAT, "MLX weights need scale and bias tables (f32 or bf16)");
+        }
+        w->table_bytes = mlx_table_dtype == ULLM_DTYPE_F32 ? 4 : 2;
+        w->tbytes = gw->out * (gw->cols / gw->mlx_group) * w->table_bytes;
+        e = cudaMalloc(&w->scales, w->tbytes);
+        if (e == cudaSuccess) e = cudaMalloc(&w->biases, w->tbytes);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(w->scales, gw->mlx_scales, w->tbytes, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(w->biases, gw->mlx_biases, w->tbytes, cudaMemcpyHostToDevice, c->stream);
+    }
+    if (e == cudaSuccess && fmt == FMT_Q6K && q6k_can_prepare(gw->cols) && !c->no_prepare) {
+        void *tmp = nullptr; // raw bytes land in staging, the prepared rows in the weight
+        int rc = ctx_scratch(c, 0, need, &tmp);
+        if (rc) {
+            ullm_cuda_weight_destroy(c, w);
+            return rc;
+        }
+        e = cudaMemcpyAsync(tmp, gw->bytes, need, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess) e = launch_q6k_prepare(tmp, w->w, gw->out, gw->cols, false, c->stream);
+        w->fmt = FMT_Q6KR;
+    } else if (e == cudaSuccess) {
+        e = cudaMemcpyAsync(w->w, gw->bytes, need, cudaMemcpyHostToDevice, c->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        ullm_cuda_weight_destroy(c, w);
+        return ctx_fail(c, e == cudaErrorMemoryAllocation ? ULLM_ERR_OOM : ULLM_ERR_CUDA, "weight upload: %s", cudaGetErrorString(e));
+    }
+    *out = w;
+    return ULLM_OK;
+}
+
+void ullm_cuda_weight_destroy(ullm_cuda_ctx *c, ullm_cuda_weight *w) {
+    if (!w) return;
+    if (c) cudaSetDevice(c->device);
+    if (w->w) cudaFree(w->w);
+    if (w->scales) cudaFree(w->scales);
+    if (w->biases) cudaFree(w->biases);
+    delete w;
+}
+
+size_t ullm_cuda_weight_bytes(const ullm_cuda_weight *w) { return w ? w->nbytes : 0; }
+
+int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const float *d_x, float *d_y, void *stream) {
+    if (!c || !w || !d_x || !d_y) return ULLM_ERR_INVALID;
+    if ((uintptr_t)d_x % 16 || (uintptr_t)d_y % 4) return ctx_fail(c, ULLM_ERR_FORMAT, "device pointers must be 16-byte aligned");
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    MlxTables tb;
+    tb.scales = w->scales, tb.biases = w->biases, tb.elem_bytes = w->table_bytes, tb.group = w->group;
+    MatvecOpts mo;
+    mo.force_generic = c->force_generic && w->fmt != FMT_Q6KR, mo.pdl = c->use_pdl, mo.plan_out = &c->last_plan;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    ULLM_CUDA_TRY(c, launch_matvec(c->dev, w->fmt, w->w, tb, d_x, d_y, w->out, w->cols, c->d_status, st, mo));
+    return ULLM_OK;
+}
+
+int ullm_cuda_weight_matvec(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const float *x, float *y) {
+    if (!c || !w || !x || !y) return ULLM_ERR_INVALID;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    void *d_x = nullptr, *d_y = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 4, w->cols * 4, &d_x)) || (rc = ctx_scratch(c, 5, w->out * 4, &d_y))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_x, x, w->cols * 4, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = ullm_cuda_weight_matvec_dev(c, w, (const float *)d_x, (float *)d_y, nullptr))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, w->out * 4, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ctx_check_status(c);
+}
+
+int ullm_cuda_weight_export(ullm_cuda_ctx *c, const ullm_cuda_weight *w, void *bytes, size_t len) {
+    if (!c || !w || !bytes) return ULLM_ERR_INVALID;
+    if (len < w->nbytes) return ctx_fail(c, ULLM_ERR_FORMAT, "need room for %zu bytes, have %zu", w->nbytes, len);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    const void *src = w->w;
+    if (w->fmt == FMT_Q6KR) {
+        void *tmp = nullptr;
+        int rc = ctx_scratch(c, 0, w->nbytes, &tmp);
+        if (rc) return rc;
+        ULLM_CUDA_TRY(c, launch_q6k_prepare(w->w, tmp, w->out, w->cols, true, c->stream));
+        src = tmp;
+    }
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(bytes, src, w->nbytes, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ULLM_OK;
+}
+
 // ---- batched matmul --------------------------------------------------------
 int ullm_cuda_matmul_dev(ullm_cuda_ctx *c, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
                          int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
@@ -345,6 +457,10 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     if (!c || !key) return ULLM_ERR_INVALID;
     if (!strcmp(key, "force_generic")) c->force_generic = value != 0;
     else if (!strcmp(key, "pdl")) c->use_pdl = value != 0;
+    else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
+    else if (!strcmp(key, "plan_wr")) c->plan_wr = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
+    else if (!strcmp(key, "plan_rw")) c->plan_rw = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
+    else if (!strcmp(key, "plan_stages")) c->plan_stages = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
     else return ULLM_ERR_INVALID;
     return ULLM_OK;
 }

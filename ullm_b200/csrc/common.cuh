@@ -16,7 +16,10 @@ constexpr int QK_K = 256;
 constexpr int Q4K_BYTES = 144; // f16 d @0, f16 dmin @2, u8 scales[12] @4, u8 qs[128] @16
 constexpr int Q6K_BYTES = 210; // u8 ql[128] @0, u8 qh[64] @128, i8 scales[16] @192, f16 d @208
 
-enum Fmt : int { FMT_Q4K = 0, FMT_Q6K = 1, FMT_MLX4 = 2 };
+// FMT_Q6KR is the prepared form of Q6_K used by resident weight objects: the same
+// 210 bytes per super-block, re-ordered per row so that every access is an aligned
+// 128-bit load and three of every four 6-bit values need one mask (prepare.cu).
+enum Fmt : int { FMT_Q4K = 0, FMT_Q6K = 1, FMT_MLX4 = 2, FMT_Q6KR = 3 };
 
 // Device-side status word values (kept in a per-context int in global memory).
 constexpr int DEV_OK = 0;

@@ -325,6 +325,28 @@ cudaError_t Forward::upload(const void *host, size_t bytes, void **out) {
     return cudaMemcpyAsync(*out, host, bytes, cudaMemcpyHostToDevice, stream);
 }
 
+// Makes `bytes` (rows of `fmt`) resident; Q6_K rows are prepared on the device
+// (prepare.cu) when their length allows it.
+cudaError_t Forward::upload_rows(const void *bytes, int fmt, size_t out_dim, size_t cols, Mat *out) {
+    const size_t n = qbytes(fmt, out_dim, cols);
+    out->fmt = fmt, out->out = out_dim, out->cols = cols;
+    cudaError_t e = dev_alloc(&out->w, n);
+    if (e != cudaSuccess) return e;
+    if (fmt == FMT_Q6K && q6k_can_prepare(cols)) {
+        void *tmp = nullptr;
+        if ((e = cudaMalloc(&tmp, n)) != cudaSuccess) return e;
+        e = cudaMemcpyAsync(tmp, bytes, n, cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess) e = launch_q6k_prepare(tmp, out->w, out_dim, cols, false, stream);
+        cudaError_t e2 = cudaStreamSynchronize(stream);
+        cudaFree(tmp);
+        out->fmt = FMT_Q6KR;
+        return e != cudaSuccess ? e : e2;
+    }
+    e = cudaMemcpyAsync(out->w, bytes, n, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream); // the caller's bytes may be a temporary
+    return e;
+}
+
 // Two matrices of the same type stacked (`interleave` = false: rows of a then rows
 // of b) or row-interleaved (a0 b0 a1 b1 ...) into one resident matrix.
 cudaError_t Forward::upload_pair(const HostWeight &a, const HostWeight &b, bool interleave, Mat *out) {
@@ -340,15 +362,11 @@ cudaError_t Forward::upload_pair(const HostWeight &a, const HostWeight &b, bool 
             memcpy(tmp.data() + (2 * r + 1) * rb, (const uint8_t *)b.bytes + r * rb, rb);
         }
     }
-    out->fmt = fmt, out->out = a.out + b.out, out->cols = a.cols;
-    cudaError_t e = upload(tmp.data(), tmp.size(), &out->w);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream); // tmp dies at scope exit
-    return e;
+    return upload_rows(tmp.data(), fmt, a.out + b.out, a.cols, out);
 }
 
 cudaError_t Forward::upload_one(const HostWeight &a, Mat *out) {
-    out->fmt = fmt_of_dtype(a.dtype), out->out = a.out, out->cols = a.cols;
-    return upload(a.bytes, qbytes(out->fmt, a.out, a.cols), &out->w);
+    return upload_rows(a.bytes, fmt_of_dtype(a.dtype), a.out, a.cols, out);
 }
 
 cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardParams &params, const HostModel &m) {
@@ -374,8 +392,9 @@ cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardP
         }
         TRY(upload_one(h.wv, &L.wv));
         TRY(upload_one(h.wo, &L.wo));
-        L.gu_fused = h.w_gate.dtype == h.w_up.dtype &&
-                     matvec_is_streamed(dev, fmt_of_dtype(h.w_gate.dtype), 2 * P.n_ff, P.n_embd, 0, 4, EPI_SWIGLU);
+        int gfmt = fmt_of_dtype(h.w_gate.dtype);
+        if (gfmt == FMT_Q6K && q6k_can_prepare(P.n_embd)) gfmt = FMT_Q6KR;
+        L.gu_fused = h.w_gate.dtype == h.w_up.dtype && matvec_is_streamed(dev, gfmt, 2 * P.n_ff, P.n_embd, 0, 4, EPI_SWIGLU);
         if (L.gu_fused) {
             TRY(upload_pair(h.w_gate, h.w_up, true, &L.wgu));
         } else {

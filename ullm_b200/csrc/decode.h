@@ -78,6 +78,7 @@ struct Forward {
   private:
     cudaError_t dev_alloc(void **out, size_t bytes);
     cudaError_t upload(const void *host, size_t bytes, void **out);
+    cudaError_t upload_rows(const void *bytes, int fmt, size_t out_dim, size_t cols, Mat *out);
     cudaError_t upload_pair(const HostWeight &a, const HostWeight &b, bool interleave, Mat *out);
     cudaError_t upload_one(const HostWeight &a, Mat *out);
     cudaError_t mv(const Mat &m, const float *in, float *out, const float *norm_w, int epi, const float *res);

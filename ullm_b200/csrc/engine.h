@@ -29,6 +29,8 @@ struct ullm_cuda_ctx {
     } scratch[8];
     bool force_generic = false;
     bool use_pdl = false;
+    bool no_prepare = false; // keep Q6_K weights in their verbatim bytes (tests)
+    int plan_wr = 0, plan_rw = 0, plan_stages = 0;
     ullm::MatvecPlan last_plan;
 };
 

@@ -51,6 +51,12 @@ struct MatvecOpts {
 cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const MlxTables &tb, const float *d_x,
                           float *d_y, size_t out_dim, size_t in_dim, int *d_status, cudaStream_t st,
                           const MatvecOpts &opts = MatvecOpts());
+// Tuning override for tests / sweeps: force the row-slice count, rows per warp and
+// ring depth of the streamed plan (0 = automatic).
+void matvec_set_plan_override(int wr, int rw, int stages);
+// prepare.cu — Q6_K rows <-> the prepared layout (FMT_Q6KR)
+bool q6k_can_prepare(size_t in_dim);
+cudaError_t launch_q6k_prepare(const void *d_src, void *d_dst, size_t rows, size_t in_dim, bool inverse, cudaStream_t st);
 bool matvec_is_streamed(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
                         int epi);
 // Returns a static message when the shape cannot be computed at all.

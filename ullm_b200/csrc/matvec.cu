@@ -132,14 +132,17 @@ struct StreamParams {
     const float *res;    // EPI_RESIDUAL: y[o] = res[o] + (W x)[o]  (res may alias y)
     uint32_t out_dim, in_dim, group;
     uint32_t row_bytes, tbl_row_bytes;
+    uint32_t gran;       // CTA row ranges start at multiples of this many rows (16-byte alignment)
     uint32_t R, WC, WR, NW, S;
     uint32_t w_stage_bytes, tbl_stage_bytes, stage_bytes; // regions inside one stage (128-B multiples)
-    uint32_t ntiles, ncg;
+    uint32_t ncg;
     uint32_t off_part, off_prep, off_ring; // byte offsets in dynamic smem
 };
 
+constexpr int STREAM_MAX_THREADS = 800; // 24 consumer warps + the producer warp
+
 template <int FMT, int RW, int G, typename TBL>
-__global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParams p) {
+__global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(const StreamParams p) {
     constexpr int XR = FmtTraits<FMT>::XREGS;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = (uint64_t *)smem;
@@ -150,6 +153,14 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool producer = warp == p.NW;
+
+    // Rows are dealt to the CTAs as contiguous, balanced ranges (to within `gran`
+    // rows); each CTA walks its range in tiles of R rows, the last one ragged.
+    const uint32_t units = p.out_dim / p.gran;
+    const uint32_t rbeg = (uint32_t)(((uint64_t)units * blockIdx.x) / gridDim.x) * p.gran;
+    const uint32_t rend = blockIdx.x + 1 == gridDim.x ? p.out_dim
+                                                      : (uint32_t)(((uint64_t)units * (blockIdx.x + 1)) / gridDim.x) * p.gran;
+    const uint32_t ntiles = (rend - rbeg + p.R - 1) / p.R;
 
     // Under programmatic dependent launch the next kernel may be scheduled as soon
     // as SMs free up; it only prefetches its own weights until this grid is done.
@@ -163,10 +174,10 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
     }
     __syncthreads();
 
-    auto issue = [&](uint32_t tile, uint32_t s) {
-        uint32_t r0 = tile * p.R;
-        uint32_t rows = min(p.R, p.out_dim - r0);
-        uint32_t wb = rows * p.row_bytes, tb = rows * p.tbl_row_bytes;
+    auto issue = [&](uint32_t k, uint32_t s) {
+        const uint32_t r0 = rbeg + k * p.R;
+        const uint32_t rows = min(p.R, rend - r0);
+        const uint32_t wb = rows * p.row_bytes, tb = rows * p.tbl_row_bytes;
         uint8_t *dst = ring + (size_t)s * p.stage_bytes;
         mbar_arrive_expect_tx(&full[s], wb + 2 * tb);
         bulk_g2s(dst, p.w + (size_t)r0 * p.row_bytes, wb, &full[s]);
@@ -178,10 +189,8 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
 
     // Weights do not depend on the previous kernel in the stream: start the first
     // S tiles now, before waiting for it.
-    if (producer && lane == 0) {
-        uint32_t k = 0;
-        for (uint32_t tile = blockIdx.x; tile < p.ntiles && k < p.S; tile += gridDim.x, ++k) issue(tile, k);
-    }
+    if (producer && lane == 0)
+        for (uint32_t k = 0; k < ntiles && k < p.S; ++k) issue(k, k);
     pdl_wait_prior();
 
     // Optional fused RMSNorm of the input (crates/ullm-model/src/math.rs:82-86):
@@ -202,21 +211,18 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
         __syncthreads(); // part is reused by the row reduction below
     }
     // x -> fixed-point register images, built once per CTA in shared memory
-    for (uint32_t sl = tid; sl < p.ncg * 32u; sl += blockDim.x)
-        prep_slot<FMT>(src, p.in_dim, sl >> 5, sl & 31u, prep + (size_t)(sl >> 5) * XR * 32 + (sl & 31u));
+    prep_image<FMT>(src, p.in_dim, prep, tid, blockDim.x);
     __syncthreads();
 
     if (producer) {
         if (lane == 0) {
-            uint32_t k = 0;
-            for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++k) {
-                if (k < p.S) continue;
-                uint32_t s = k % p.S;
+            for (uint32_t k = p.S; k < ntiles; ++k) {
+                const uint32_t s = k % p.S;
                 if (!wait_or_timeout(&empty[s], ((k / p.S) - 1) & 1)) {
                     *(volatile int *)p.status = DEV_TIMEOUT;
                     break;
                 }
-                issue(tile, s);
+                issue(k, s);
             }
         }
         return;
@@ -224,39 +230,38 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
 
     const uint32_t rs = warp / p.WC, cgw = warp % p.WC;
     uint32_t X[G][XR];
+    bool live[G]; // lanes past the end of the row must not read beyond the stage
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        uint32_t cg = cgw + g * p.WC;
+        const uint32_t cg = cgw + g * p.WC;
+        live[g] = cg < p.ncg;
+        if (FMT == FMT_Q4K || FMT == FMT_Q6KR) live[g] = live[g] && (cg * 8u + (lane >> 2)) * QK_K < p.in_dim;
+        if (FMT == FMT_Q6K) live[g] = live[g] && (cg * 4u + (lane >> 3)) * QK_K < p.in_dim;
+        if (FMT == FMT_MLX4) live[g] = live[g] && (cg * 32u + lane) * 32u < p.in_dim;
 #pragma unroll
-        for (int k = 0; k < XR; ++k) X[g][k] = cg < p.ncg ? prep[((size_t)cg * XR + k) * 32 + lane] : 0u;
+        for (int k = 0; k < XR; ++k) X[g][k] = live[g] ? prep[((size_t)cg * XR + k) * 32 + lane] : 0u;
     }
+    const uint32_t nb = p.in_dim / QK_K;
 
     bool aborted = false;
-    uint32_t k = 0;
-    for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++k) {
+    for (uint32_t k = 0; k < ntiles; ++k) {
         const uint32_t s = k % p.S;
         if (!aborted && !wait_or_timeout(&full[s], (k / p.S) & 1)) aborted = true;
         const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
-        const uint32_t r0 = tile * p.R;
+        const uint32_t r0 = rbeg + k * p.R;
         float v[RW];
 #pragma unroll
         for (int rr = 0; rr < RW; ++rr) {
             v[rr] = 0.f;
             const uint32_t rl = rs * RW + rr;
-            if (!aborted && r0 + rl < p.out_dim) {
+            if (!aborted && r0 + rl < rend) {
                 const uint32_t row_addr = stage + rl * p.row_bytes;
-                const uint32_t ts = stage + p.w_stage_bytes + rl * p.tbl_row_bytes;
+                uint32_t ts, tb2;
+                if (FMT == FMT_Q6KR) ts = row_addr + 192u * nb, tb2 = row_addr + 208u * nb;
+                else ts = stage + p.w_stage_bytes + rl * p.tbl_row_bytes, tb2 = ts + p.tbl_stage_bytes;
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const uint32_t cg = cgw + g * p.WC;
-                    // lanes past the end of the row hold a zero register image but must
-                    // not read beyond the stage
-                    bool live = cg < p.ncg;
-                    if (FMT == FMT_Q4K) live = live && (cg * 8u + (lane >> 2)) * QK_K < p.in_dim;
-                    if (FMT == FMT_Q6K) live = live && (cg * 4u + (lane >> 3)) * QK_K < p.in_dim;
-                    if (FMT == FMT_MLX4) live = live && (cg * 32u + lane) * 32u < p.in_dim;
-                    if (live) v[rr] += row_partial<FMT, TBL>(row_addr, X[g], cg, lane, ts, ts + p.tbl_stage_bytes, p.group);
-                }
+                for (int g = 0; g < G; ++g)
+                    if (live[g]) v[rr] += row_partial<FMT, TBL>(row_addr, X[g], cgw + g * p.WC, lane, ts, tb2, p.group);
             }
         }
         __syncwarp();
@@ -271,7 +276,7 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
             float other = 0.f;
             if (RW >= 2) other = __shfl_xor_sync(0xffffffffu, r, RW == 2 ? 16 : 8);
             const bool writer = (lane & 7) == 0 && (RW == 4 || (lane & 8) == 0) && (RW > 1 || lane == 0);
-            if (writer && r0 + rl < p.out_dim && !aborted) {
+            if (writer && r0 + rl < rend && !aborted) {
                 if (p.epi == EPI_STORE) p.y[r0 + rl] = r;
                 else if (p.epi == EPI_RESIDUAL) p.y[r0 + rl] = p.res[r0 + rl] + r;
                 else if ((myrow & 1) == 0) p.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
@@ -285,7 +290,7 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
                 const uint32_t row = rs * RW + sl;
                 float acc = 0.f;
                 for (uint32_t c = 0; c < p.WC; ++c) acc += pt[row * p.WC + c];
-                if (r0 + row < p.out_dim && !aborted) {
+                if (r0 + row < rend && !aborted) {
                     if (p.epi == EPI_STORE) p.y[r0 + row] = acc;
                     else if (p.epi == EPI_RESIDUAL) p.y[r0 + row] = p.res[r0 + row] + acc;
                     else if ((sl & 1) == 0) {
@@ -306,8 +311,9 @@ __global__ void __launch_bounds__(544, 1) matvec_stream_kernel(const StreamParam
 const char *matvec_shape_error(int fmt, size_t out_dim, size_t in_dim, size_t group) {
     if (out_dim == 0 || in_dim == 0) return "empty matrix";
     if (out_dim > 0x7fffffffull || in_dim > 0x7fffffffull) return "dimension too large";
-    if (fmt == FMT_Q4K || fmt == FMT_Q6K) {
+    if (fmt == FMT_Q4K || fmt == FMT_Q6K || fmt == FMT_Q6KR) {
         if (in_dim % QK_K) return "in_dim is not a multiple of the 256-element super-block";
+        if (fmt == FMT_Q6KR && in_dim % 2048) return "prepared Q6_K rows need in_dim to be a multiple of 2048";
     } else if (fmt == FMT_MLX4) {
         if (in_dim % 8) return "in_dim is not a multiple of 8 (one packed word)";
         if (group == 0 || in_dim % group) return "in_dim is not a multiple of the MLX group size";
@@ -319,6 +325,13 @@ const char *matvec_shape_error(int fmt, size_t out_dim, size_t in_dim, size_t gr
 }
 
 static inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+static inline uint32_t gcd_u32(uint32_t a, uint32_t b) {
+    while (b) {
+        uint32_t t = a % b;
+        a = b, b = t;
+    }
+    return a;
+}
 
 struct Plan {
     bool ok = false;
@@ -328,11 +341,15 @@ struct Plan {
     double score = 0;
 };
 
+// Tuning overrides (tests / sweeps): 0 = choose automatically.
+static int g_force_wr = 0, g_force_rw = 0, g_force_stages = 0;
+void matvec_set_plan_override(int wr, int rw, int stages) { g_force_wr = wr, g_force_rw = rw, g_force_stages = stages; }
+
 static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
                         int epi) {
     Plan best;
-    const uint32_t cg_elems = fmt == FMT_Q4K ? 2048u : 1024u;
-    const uint32_t xregs = fmt == FMT_Q4K ? XREGS_Q4K : (fmt == FMT_Q6K ? XREGS_Q6K : XREGS_MLX);
+    const uint32_t cg_elems = (fmt == FMT_Q4K || fmt == FMT_Q6KR) ? 2048u : 1024u;
+    const uint32_t xregs = fmt == FMT_Q4K ? XREGS_Q4K : (fmt == FMT_Q6K ? XREGS_Q6K : (fmt == FMT_Q6KR ? XREGS_Q6KR : XREGS_MLX));
     uint32_t row_bytes, tbl_row_bytes = 0;
     if (fmt == FMT_MLX4) {
         if (in_dim % 32 || group % 32) return best; // a lane owns 32 consecutive weights of one group
@@ -341,36 +358,45 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
     } else {
         row_bytes = (uint32_t)(in_dim / QK_K) * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
     }
+    if (fmt == FMT_Q6KR && in_dim % 2048) return best;
+    // rows at which a 16-byte aligned copy may start
+    uint32_t gran = 16 / gcd_u32(row_bytes, 16);
+    if (tbl_row_bytes) gran = std::max(gran, 16 / gcd_u32(tbl_row_bytes, 16)); // both powers of two
+    if (epi == EPI_SWIGLU) gran = std::max(gran, 2u);
+    if (out_dim % gran) return best;
     const uint32_t ncg = (uint32_t)((in_dim + cg_elems - 1) / cg_elems);
-    const uint32_t gmax = 2;
+    const uint32_t max_warps = 24;
     const uint32_t G = (ncg + 15) / 16;
-    if (G > gmax) return best;
+    if (G > 2) return best;
     const uint32_t WC = (ncg + G - 1) / G;
     const int budget = dev.max_smem_optin - 1024;
-    for (uint32_t WR = 1; WR <= 16; WR *= 2) {
-        if (WC * WR > 16) break;
-        if (WC > 1 && WR > 8) break; // named barriers 1..8
+    const uint32_t units = (uint32_t)(out_dim / gran);
+    const uint32_t grid = std::min<uint32_t>((uint32_t)dev.sm_count, units);
+    const uint32_t rows_cta = ((units + grid - 1) / grid) * gran; // the largest range
+    for (uint32_t WR = 1; WR <= 15; ++WR) {
+        if (WC * WR > max_warps) break;
+        if (WC == 1 && WR > 24) break;
+        if (g_force_wr && (int)WR != g_force_wr) continue;
         for (uint32_t RW = (epi == EPI_SWIGLU ? 2 : 1); RW <= 4; RW *= 2) {
+            if (g_force_rw && (int)RW != g_force_rw) continue;
             const uint32_t R = WR * RW;
-            if ((R * row_bytes) % 16 || (R * tbl_row_bytes) % 16) continue;
-            if (out_dim % R && ((row_bytes % 16) || (tbl_row_bytes % 16))) continue;
+            if (R % gran) continue;
             const uint32_t wst = align_up(R * row_bytes, 128), tst = align_up(R * tbl_row_bytes, 128);
             const uint32_t stage = wst + 2 * tst;
-            if (stage > 48 * 1024) continue;
-            const uint32_t ntiles = (uint32_t)((out_dim + R - 1) / R);
-            const uint32_t grid = std::min<uint32_t>((uint32_t)dev.sm_count, ntiles);
-            const uint32_t per = (ntiles + grid - 1) / grid;
+            if (stage > 64 * 1024) continue;
             const uint32_t off_part = 128;
-            const uint32_t off_prep = align_up(off_part + 2 * R * WC * 4, 128);
+            const uint32_t off_prep = align_up(off_part + std::max(2 * R * WC * 4, 128u), 128);
             const uint32_t off_ring = align_up(off_prep + ncg * xregs * 32 * 4, 128);
             if ((int)off_ring + 2 * (int)stage > budget) continue;
+            const uint32_t tiles = (rows_cta + R - 1) / R;
             uint32_t S = std::min<uint32_t>(8, (budget - off_ring) / stage);
-            S = std::min(S, std::max(2u, per));
-            const double eff = (double)ntiles / ((double)per * grid);
-            const double fill = std::min(1.0, (double)(S * stage) / 49152.0);
-            const double score = eff * std::pow(std::min(1.0, stage / 8192.0), 0.25) *
-                                 std::sqrt(std::min(1.0, WC * WR / 8.0)) * (1.0 + 0.03 * std::log2((double)RW)) *
-                                 (0.5 + 0.5 * fill);
+            S = std::min(S, std::max(2u, tiles));
+            if (g_force_stages) S = std::min<uint32_t>(S, (uint32_t)g_force_stages);
+            const double eff = (double)rows_cta / ((double)tiles * R);      // idle warps in the ragged tile
+            const double warps = std::min(1.0, (WC * WR) / 20.0);           // latency hiding
+            const double inflight = std::min(1.0, (double)(S * stage) / 65536.0);
+            const double pipe = tiles >= 3 ? 1.0 : 0.85;                    // something to overlap with
+            const double score = eff * (0.4 + 0.6 * warps) * (0.6 + 0.4 * inflight) * pipe * (1.0 + 0.02 * std::log2((double)RW));
             if (score > best.score) {
                 best.ok = true;
                 best.score = score;
@@ -381,10 +407,10 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
                 best.smem = off_ring + S * stage;
                 StreamParams &p = best.p;
                 p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.group = (uint32_t)group;
-                p.row_bytes = row_bytes, p.tbl_row_bytes = tbl_row_bytes;
+                p.row_bytes = row_bytes, p.tbl_row_bytes = tbl_row_bytes, p.gran = gran;
                 p.R = R, p.WC = WC, p.WR = WR, p.NW = WC * WR, p.S = S;
                 p.w_stage_bytes = wst, p.tbl_stage_bytes = tst, p.stage_bytes = stage;
-                p.ntiles = ntiles, p.ncg = ncg;
+                p.ncg = ncg;
                 p.off_part = off_part, p.off_prep = off_prep, p.off_ring = off_ring;
             }
         }
@@ -456,10 +482,11 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
         pl.p.norm_w = o.norm_w, pl.p.eps = o.eps, pl.p.epi = o.epi, pl.p.res = o.res;
         if (fmt == FMT_Q4K) return launch_stream_f<FMT_Q4K, float>(pl, st, o.pdl);
         if (fmt == FMT_Q6K) return launch_stream_f<FMT_Q6K, float>(pl, st, o.pdl);
+        if (fmt == FMT_Q6KR) return launch_stream_f<FMT_Q6KR, float>(pl, st, o.pdl);
         if (tb.elem_bytes == 2) return launch_stream_f<FMT_MLX4, uint16_t>(pl, st, o.pdl);
         return launch_stream_f<FMT_MLX4, float>(pl, st, o.pdl);
     }
-    if (fused) return cudaErrorNotSupported; // the plain kernel has no fused prologue / epilogue
+    if (fused || fmt == FMT_Q6KR) return cudaErrorNotSupported; // the plain kernel has no fused prologue / epilogue
     if (fmt == FMT_Q4K) return launch_generic_t<FMT_Q4K, float>(d_w, tb, d_x, d_y, 0, out_dim, in_dim, st);
     if (fmt == FMT_Q6K) return launch_generic_t<FMT_Q6K, float>(d_w, tb, d_x, d_y, 0, out_dim, in_dim, st);
     if (fmt == FMT_MLX4) {

@@ -34,11 +34,12 @@ template <typename T> __device__ __forceinline__ float tbl_load(const T *p);
 template <> __device__ __forceinline__ float tbl_load<float>(const float *p) { return *p; }
 template <> __device__ __forceinline__ float tbl_load<uint16_t>(const uint16_t *p) { return bf16_bits_to_f32(*p); }
 
-constexpr int XREGS_Q4K = 36, XREGS_Q6K = 24, XREGS_MLX = 18;
+constexpr int XREGS_Q4K = 36, XREGS_Q6K = 24, XREGS_MLX = 18, XREGS_Q6KR = 37;
 template <int FMT> struct FmtTraits;
 template <> struct FmtTraits<FMT_Q4K> { static constexpr int XREGS = XREGS_Q4K, CG_ELEMS = 2048; };
 template <> struct FmtTraits<FMT_Q6K> { static constexpr int XREGS = XREGS_Q6K, CG_ELEMS = 1024; };
 template <> struct FmtTraits<FMT_MLX4> { static constexpr int XREGS = XREGS_MLX, CG_ELEMS = 1024; };
+template <> struct FmtTraits<FMT_Q6KR> { static constexpr int XREGS = XREGS_Q6KR, CG_ELEMS = 2048; };
 
 
 // 16-bit fixed point of up to 32 values sharing one scale.  X = rint(v/s) with
@@ -66,117 +67,135 @@ __device__ __forceinline__ float4 act_load4(const ActSrc &a, uint32_t i) {
     return t;
 }
 
+// Builds the persistent register images of one activation vector in shared
+// memory: img[(cg * XREGS + k) * 32 + lane] is register k of (column group cg,
+// lane).  Work is split in tasks of 8 consecutive elements so that all `nthr`
+// threads take part (blockDim-uniform loop; nthr must be a multiple of 32 and all
+// threads of the participating warps must call this).
+//
+// Register image layouts (what row_partial expects):
+//  Q4_K  lane (cg, ln): block 8cg + ln/4, chunk c = ln%4.  Low nibbles are elements
+//        [64c, 64c+32) of the block, high nibbles [64c+32, 64c+64) (dequant.rs:200-214).
+//        k = 16*half + j: high byte plane of word j (elements 4j..4j+3) of that half,
+//        16*half + 8 + j: low byte plane, 32+half: x scale (half 1 carries 1/16 because
+//        high nibbles are used in place), 34+half: fp32 sum of the 32 x values.
+//  Q6_K  lane (cg, ln): block 4cg + ln/8, nh = (ln%8)/4, l0 = 8*(ln%4); group g = 0..3 is
+//        elements 128nh + 32g + l0 + [0,8) (dequant.rs:264-279).  k = 4g + j: high plane of
+//        word j, 4g + 2 + j: low plane, 16+g: x scale, 20+g: 32 * sum of the fixed-point x
+//        (folds the -32 offset of the 6-bit values).
+//  Q6KR  lane (cg, ln): block 8cg + ln/4, nh = (ln/2)%2, t' = ln%2: the 16 positions
+//        l = 16t' .. 16t'+15 of half nh in all four groups g (elements 128nh + 32g + l).
+//        One x scale for the 64 values.  k = 8g + j: high plane of word j (l = 16t'+4j..+3)
+//        of group g, 8g + 4 + j: low plane, 32: x scale, 33+g: -32 * sum of the fixed-point
+//        x of group g (the accumulator's start value: folds the -32 offset).
+//  MLX4  lane (cg, ln): words 4*(32cg+ln)..+3 = elements 32*(32cg+ln) + [0,32); nibble n of
+//        word j is element 8j+n (dequant.rs:310-311).  k = j: high plane of the even
+//        nibbles of word j, 4+j: their low plane, 8+j / 12+j: the odd nibbles (used in
+//        place, value*16), 16: x scale / 16, 17: fp32 sum of the 32 x values.
 template <int FMT>
-__device__ __forceinline__ void prep_slot(const ActSrc &src, uint32_t in_dim, uint32_t cg, uint32_t ln, uint32_t *slot) {
+__device__ __forceinline__ void prep_image(const ActSrc &src, uint32_t in_dim, uint32_t *img, uint32_t tid, uint32_t nthr) {
     constexpr int XR = FmtTraits<FMT>::XREGS;
-    if constexpr (FMT == FMT_Q4K) {
-        // lane: block 8cg + ln/4, chunk c = ln%4: low nibbles = elements [64c,64c+32),
-        // high nibbles = [64c+32, 64c+64)   (dequant.rs:200-214)
-        uint32_t e0 = cg * 2048u + (ln >> 2) * 256u + (ln & 3) * 64u;
-        if (e0 >= in_dim) {
+    const uint32_t ntasks = in_dim >> 3;
+    for (uint32_t base = 0; base < ntasks; base += nthr) {
+        const uint32_t t = base + tid;
+        const bool act = t < ntasks;
+        const uint32_t e = (act ? t : 0u) << 3;
+        float4 t0 = act_load4(src, e), t1 = act_load4(src, e + 4);
+        const float v[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+        float mx = 0.f, sum = 0.f;
 #pragma unroll
-            for (int k = 0; k < XR; ++k) slot[k * 32] = 0u;
-            return;
+        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i])), sum += v[i];
+        if (FMT == FMT_Q6KR) { // 64 values share a scale: task bits 0 (8 of 16), 2-3 (group)
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        } else if (FMT != FMT_Q6K) { // 32 values share a scale: four neighbouring tasks
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         }
+        const float inv = mx > 0.f ? 32767.f / mx : 0.f, sc = mx * (1.f / 32767.f);
+        int q[8];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            float v[32];
+        for (int i = 0; i < 8; ++i) q[i] = quant16(v[i], inv);
+        int isum8 = 0;
+        if (FMT == FMT_Q6KR) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float4 t = act_load4(src, e0 + 32 * half + 4 * i);
-                v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
-            }
-            float mx = 0.f, sum = 0.f;
+            for (int i = 0; i < 8; ++i) isum8 += q[i];
+            isum8 += __shfl_xor_sync(0xffffffffu, isum8, 1); // the 16 positions of this group
+        }
+        if (!act) continue;
+        if constexpr (FMT == FMT_Q4K) {
+            const uint32_t b = e >> 8, r = e & 255u, c = r >> 6, half = (r >> 5) & 1u, sub = (r >> 3) & 3u;
+            uint32_t *slot = img + ((b >> 3) * XR) * 32 + (((b & 7u) << 2) | c);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fabsf(v[i])), sum += v[i];
-            float inv = mx > 0.f ? 32767.f / mx : 0.f, s = mx * (1.f / 32767.f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 2; ++j) {
                 uint32_t hi = 0, lo = 0;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    int q = quant16(v[4 * j + k], inv);
-                    hi |= (uint32_t)((q >> 8) & 0xff) << (8 * k);
-                    lo |= (uint32_t)(q & 0xff) << (8 * k);
+                    hi |= (uint32_t)((q[4 * j + k] >> 8) & 0xff) << (8 * k);
+                    lo |= (uint32_t)(q[4 * j + k] & 0xff) << (8 * k);
                 }
-                slot[(16 * half + j) * 32] = hi;
-                slot[(16 * half + 8 + j) * 32] = lo;
+                slot[(16 * half + 2 * sub + j) * 32] = hi;
+                slot[(16 * half + 8 + 2 * sub + j) * 32] = lo;
             }
-            // high nibbles are used in place (value * 16): fold the 1/16 here
-            slot[(32 + half) * 32] = __float_as_uint(half ? s * 0.0625f : s);
-            slot[(34 + half) * 32] = __float_as_uint(sum);
-        }
-    } else if constexpr (FMT == FMT_Q6K) {
-        // lane: block 4cg + ln/8, half nh = (ln%8)/4, l0 = 8*(ln%4); group g = 0..3 is
-        // the element range 128nh + 32g + l0 + [0,8)   (dequant.rs:264-279)
-        uint32_t r = ln & 7;
-        uint32_t e0 = cg * 1024u + (ln >> 3) * 256u + (r >> 2) * 128u + (r & 3) * 8u;
-        if (e0 >= in_dim) {
-#pragma unroll
-            for (int k = 0; k < XR; ++k) slot[k * 32] = 0u;
-            return;
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            float v[8];
-            float4 t0 = act_load4(src, e0 + 32 * g), t1 = act_load4(src, e0 + 32 * g + 4);
-            v[0] = t0.x, v[1] = t0.y, v[2] = t0.z, v[3] = t0.w, v[4] = t1.x, v[5] = t1.y, v[6] = t1.z, v[7] = t1.w;
-            float mx = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
-            float inv = mx > 0.f ? 32767.f / mx : 0.f, s = mx * (1.f / 32767.f);
+            if (sub == 0) {
+                slot[(32 + half) * 32] = __float_as_uint(half ? sc * 0.0625f : sc);
+                slot[(34 + half) * 32] = __float_as_uint(sum);
+            }
+        } else if constexpr (FMT == FMT_Q6K) {
+            const uint32_t b = e >> 8, r = e & 255u, nh = r >> 7, g = (r >> 5) & 3u, tt = (r >> 3) & 3u;
+            uint32_t *slot = img + ((b >> 2) * XR) * 32 + (((b & 3u) << 3) | (nh << 2) | tt);
             int isum = 0;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 uint32_t hi = 0, lo = 0;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    int q = quant16(v[4 * j + k], inv);
-                    isum += q;
-                    hi |= (uint32_t)((q >> 8) & 0xff) << (8 * k);
-                    lo |= (uint32_t)(q & 0xff) << (8 * k);
+                    isum += q[4 * j + k];
+                    hi |= (uint32_t)((q[4 * j + k] >> 8) & 0xff) << (8 * k);
+                    lo |= (uint32_t)(q[4 * j + k] & 0xff) << (8 * k);
                 }
                 slot[(4 * g + j) * 32] = hi;
                 slot[(4 * g + 2 + j) * 32] = lo;
             }
-            slot[(16 + g) * 32] = __float_as_uint(s);
-            slot[(20 + g) * 32] = (uint32_t)(32 * isum); // sum (q-32) X = sum q X - 32 sum X
-        }
-    } else {
-        // lane: words 4*(32cg+ln) .. +3 = elements 32*(32cg+ln) + [0,32); nibble k of
-        // word j is element 8j+k (dequant.rs:310-311).  Even nibbles are taken with
-        // the mask 0x0f0f0f0f, odd ones in place (value*16) with 0xf0f0f0f0.
-        uint32_t e0 = (cg * 32u + ln) * 32u;
-        if (e0 >= in_dim) {
+            slot[(16 + g) * 32] = __float_as_uint(sc);
+            slot[(20 + g) * 32] = (uint32_t)(32 * isum);
+        } else if constexpr (FMT == FMT_Q6KR) {
+            const uint32_t b = e >> 8, r = e & 255u, nh = r >> 7, g = (r >> 5) & 3u, l8 = (r >> 3) & 3u;
+            const uint32_t tp = l8 >> 1, jj = (l8 & 1u) * 2u;
+            uint32_t *slot = img + ((b >> 3) * XR) * 32 + (((b & 7u) << 2) | (nh << 1) | tp);
 #pragma unroll
-            for (int k = 0; k < XR; ++k) slot[k * 32] = 0u;
-            return;
-        }
-        float v[32];
+            for (int j = 0; j < 2; ++j) {
+                uint32_t hi = 0, lo = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float4 t = act_load4(src, e0 + 4 * i);
-            v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
-        }
-        float mx = 0.f, sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fabsf(v[i])), sum += v[i];
-        float inv = mx > 0.f ? 32767.f / mx : 0.f, s = mx * (1.f / 32767.f);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
+                for (int k = 0; k < 4; ++k) {
+                    hi |= (uint32_t)((q[4 * j + k] >> 8) & 0xff) << (8 * k);
+                    lo |= (uint32_t)(q[4 * j + k] & 0xff) << (8 * k);
+                }
+                slot[(8 * g + jj + j) * 32] = hi;
+                slot[(8 * g + 4 + jj + j) * 32] = lo;
+            }
+            if ((l8 & 1u) == 0) slot[(33 + g) * 32] = (uint32_t)(-32 * isum8);
+            if (g == 0 && (l8 & 1u) == 0) slot[32 * 32] = __float_as_uint(sc);
+        } else {
+            const uint32_t widx = e >> 5, j = (e >> 3) & 3u;
+            uint32_t *slot = img + ((widx >> 5) * XR) * 32 + (widx & 31u);
             uint32_t he = 0, le = 0, ho = 0, lo = 0;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                int qe = quant16(v[8 * j + 2 * k], inv), qo = quant16(v[8 * j + 2 * k + 1], inv);
-                he |= (uint32_t)((qe >> 8) & 0xff) << (8 * k);
-                le |= (uint32_t)(qe & 0xff) << (8 * k);
-                ho |= (uint32_t)((qo >> 8) & 0xff) << (8 * k);
-                lo |= (uint32_t)(qo & 0xff) << (8 * k);
+                he |= (uint32_t)((q[2 * k] >> 8) & 0xff) << (8 * k);
+                le |= (uint32_t)(q[2 * k] & 0xff) << (8 * k);
+                ho |= (uint32_t)((q[2 * k + 1] >> 8) & 0xff) << (8 * k);
+                lo |= (uint32_t)(q[2 * k + 1] & 0xff) << (8 * k);
             }
             slot[j * 32] = he, slot[(4 + j) * 32] = le, slot[(8 + j) * 32] = ho, slot[(12 + j) * 32] = lo;
+            if (j == 0) {
+                slot[16 * 32] = __float_as_uint(sc * 0.0625f);
+                slot[17 * 32] = __float_as_uint(sum);
+            }
         }
-        slot[16 * 32] = __float_as_uint(s * 0.0625f);
-        slot[17 * 32] = __float_as_uint(sum);
     }
 }
 
@@ -258,6 +277,35 @@ __device__ __forceinline__ float row_partial(uint32_t row_addr, const uint32_t (
         uint32_t dbits;
         asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits) : "r"(blk + 208));
         return f16_bits_to_f32((uint16_t)dbits) * s;
+    } else if constexpr (FMT == FMT_Q6KR) {
+        // prepared row: [records 48 B x 4 x nb][scales 4 B x 4 x nb][d 2 B x nb];
+        // tbl_s / tbl_b carry the addresses of the scale and d planes of this row
+        const uint32_t ri = cg * 32u + ln; // record = (block, nh, t')
+        const uint32_t rec = row_addr + ri * 48u;
+        const uint4 w1 = lds128(rec), w2 = lds128(rec + 16), w3 = lds128(rec + 32);
+        const uint32_t sc4 = lds32(tbl_s + ri * 4u);
+        uint32_t dbits;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits) : "r"(tbl_b + (ri >> 2) * 2u));
+        const uint32_t a1[4] = {w1.x, w1.y, w1.z, w1.w}, a2[4] = {w2.x, w2.y, w2.z, w2.w}, a3[4] = {w3.x, w3.y, w3.z, w3.w};
+        int ah[4] = {0, 0, 0, 0};
+        int al[4] = {(int)X[33], (int)X[34], (int)X[35], (int)X[36]};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t q0 = a1[j] & 0x3f3f3f3fu, q3 = a3[j] & 0x3f3f3f3fu;
+            const uint32_t q1 = (a2[j] & 0x0f0f0f0fu) | ((a1[j] >> 2) & 0x30303030u);
+            const uint32_t q2 = ((a2[j] >> 4) & 0x0f0f0f0fu) | ((a3[j] >> 2) & 0x30303030u);
+            ah[0] = dp4a_su(q0, X[j], ah[0]), al[0] = dp4a_uu(q0, X[4 + j], al[0]);
+            ah[1] = dp4a_su(q1, X[8 + j], ah[1]), al[1] = dp4a_uu(q1, X[12 + j], al[1]);
+            ah[2] = dp4a_su(q2, X[16 + j], ah[2]), al[2] = dp4a_uu(q2, X[20 + j], al[2]);
+            ah[3] = dp4a_su(q3, X[24 + j], ah[3]), al[3] = dp4a_uu(q3, X[28 + j], al[3]);
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int sc = (int)(sc4 << (24 - 8 * g)) >> 24; // int8 scale of group g
+            s += (float)sc * (float)(ah[g] * 256 + al[g]);
+        }
+        return f16_bits_to_f32((uint16_t)dbits) * __uint_as_float(X[32]) * s;
     } else {
         const uint32_t widx = cg * 32u + ln; // 16-byte unit inside the row
         uint4 qw = lds128(row_addr + widx * 16u);

@@ -193,11 +193,9 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     const uint32_t nthr_c = p.NW * 32; // consumer threads (named barrier 1)
     if (GATE_UP) {
         // every token's x, once per CTA
-        for (uint32_t sl = tid; sl < p.n_tok * p.ncg * 32u; sl += nthr_c) {
-            const uint32_t t = sl / (p.ncg * 32u), rem = sl % (p.ncg * 32u);
-            prep_slot<FMT_MLX4>(ActSrc{p.act + (size_t)t * p.in_dim, nullptr, 0.f}, p.in_dim, rem >> 5, rem & 31u,
-                                qimg + ((size_t)(t * p.ncg + (rem >> 5)) * XR) * 32 + (rem & 31u));
-        }
+        for (uint32_t t = 0; t < p.n_tok; ++t)
+            prep_image<FMT_MLX4>(ActSrc{p.act + (size_t)t * p.in_dim, nullptr, 0.f}, p.in_dim,
+                                 qimg + (size_t)t * p.ncg * XR * 32, tid, nthr_c);
         asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
     }
 
@@ -212,11 +210,9 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         if (!GATE_UP && (int)d != cur_d) {
             // new expert: fixed-point images of the hidden vectors of its pairs
             asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // everyone done with the previous images
-            for (uint32_t sl = tid; sl < (uint32_t)np * p.ncg * 32u; sl += nthr_c) {
-                const uint32_t j = sl / (p.ncg * 32u), rem = sl % (p.ncg * 32u);
-                prep_slot<FMT_MLX4>(ActSrc{p.act + (size_t)pairs[pb + j] * p.in_dim, nullptr, 0.f}, p.in_dim, rem >> 5, rem & 31u,
-                                    qimg + ((size_t)(j * p.ncg + (rem >> 5)) * XR) * 32 + (rem & 31u));
-            }
+            for (int j = 0; j < np; ++j)
+                prep_image<FMT_MLX4>(ActSrc{p.act + (size_t)pairs[pb + j] * p.in_dim, nullptr, 0.f}, p.in_dim,
+                                     qimg + (size_t)j * p.ncg * XR * 32, tid, nthr_c);
             asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
         }
         cur_d = (int)d;
