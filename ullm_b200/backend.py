@@ -91,6 +91,7 @@ SIGNATURES = {
 DEBUG_SIGNATURES = {
     "ullm_cuda_debug_set": (_i, [_vp, C.c_char_p, _i]),
     "ullm_cuda_debug_last_plan": (_i, [_vp, _vp, _i]),
+    "ullm_cuda_debug_trace": (_i, [_vp]),
 }
 
 

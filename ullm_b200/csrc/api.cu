@@ -38,6 +38,7 @@ int ullm_cuda_ctx_create(int device, ullm_cuda_ctx **out) {
     snprintf(c->name, sizeof c->name, "%s", prop.name);
     c->dev.sm_count = prop.multiProcessorCount;
     c->dev.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    c->dev.max_smem_sm = (int)prop.sharedMemPerMultiprocessor;
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaHostAlloc((void **)&c->h_status, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer((void **)&c->d_status, (void *)c->h_status, 0) != cudaSuccess) {
@@ -458,10 +459,18 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     if (!strcmp(key, "force_generic")) c->force_generic = value != 0;
     else if (!strcmp(key, "pdl")) c->use_pdl = value != 0;
     else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
+    else if (!strcmp(key, "skip_compute")) matvec_set_skip_compute(value);
+    else if (!strcmp(key, "chunk")) matvec_set_chunk(value);
+    else if (!strcmp(key, "stagger")) matvec_set_stagger(value);
+    else if (!strcmp(key, "ctas_per_sm")) matvec_set_ctas_per_sm(value);
     else if (!strcmp(key, "plan_wr")) c->plan_wr = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
     else if (!strcmp(key, "plan_rw")) c->plan_rw = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
     else if (!strcmp(key, "plan_stages")) c->plan_stages = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
     else return ULLM_ERR_INVALID;
+    return ULLM_OK;
+}
+extern "C" int ullm_cuda_debug_trace(void *d_buf) {
+    matvec_set_trace(d_buf);
     return ULLM_OK;
 }
 extern "C" int ullm_cuda_debug_last_plan(const ullm_cuda_ctx *c, int *vals, int n) {

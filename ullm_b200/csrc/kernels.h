@@ -11,6 +11,7 @@ namespace ullm {
 struct DeviceInfo {
     int sm_count = 0;
     int max_smem_optin = 0; // bytes of dynamic shared memory a CTA may opt in to
+    int max_smem_sm = 0;    // bytes of shared memory per SM
 };
 
 // Where the scale / bias tables of an MLX matrix live and how wide they are.
@@ -54,6 +55,16 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
 // Tuning override for tests / sweeps: force the row-slice count, rows per warp and
 // ring depth of the streamed plan (0 = automatic).
 void matvec_set_plan_override(int wr, int rw, int stages);
+// Tuning aid: device buffer (64 x u64 per CTA) receiving %globaltimer stamps of CTA
+// thread 0 (start, before / after x prep, before / after each tile wait, end); null = off.
+void matvec_set_trace(void *d_buf);
+// Tuning aid: stream the weight tiles but skip the arithmetic (memory-side ceiling).
+void matvec_set_skip_compute(int v);
+// Tuning aid: bytes per bulk copy of the tile stream (0 = default).
+void matvec_set_chunk(int v);
+void matvec_set_stagger(int v);
+// Tuning override: CTAs per SM of the streamed plan (0 = automatic, 1 or 2).
+void matvec_set_ctas_per_sm(int v);
 // prepare.cu — Q6_K rows <-> the prepared layout (FMT_Q6KR)
 bool q6k_can_prepare(size_t in_dim);
 cudaError_t launch_q6k_prepare(const void *d_src, void *d_dst, size_t rows, size_t in_dim, bool inverse, cudaStream_t st);

@@ -137,6 +137,11 @@ struct StreamParams {
     uint32_t w_stage_bytes, tbl_stage_bytes, stage_bytes; // regions inside one stage (128-B multiples)
     uint32_t ncg;
     uint32_t off_part, off_prep, off_ring; // byte offsets in dynamic smem
+    unsigned long long *trace; // optional per-CTA timestamps (tuning aid), 64 slots per CTA
+    int skip_compute;          // tuning aid: stream the tiles but skip the arithmetic
+    uint32_t chunk;            // bytes per bulk copy (multiple of 16)
+    int pdl;                   // launched with programmatic stream serialization
+    int stagger;               // request the first S tiles one after the other
 };
 
 constexpr int STREAM_MAX_THREADS = 800; // 24 consumer warps + the producer warp
@@ -153,6 +158,15 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool producer = warp == p.NW;
+    uint32_t tr = 0;
+    auto stamp = [&]() {
+        if (p.trace && tid == 0 && tr < 64) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[(size_t)blockIdx.x * 64 + tr++] = t;
+        }
+    };
+    stamp();
 
     // Rows are dealt to the CTAs as contiguous, balanced ranges (to within `gran`
     // rows); each CTA walks its range in tiles of R rows, the last one ragged.
@@ -165,6 +179,11 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
     // Under programmatic dependent launch the next kernel may be scheduled as soon
     // as SMs free up; it only prefetches its own weights until this grid is done.
     pdl_launch_dependents();
+    // Without a programmatic dependency x is ready now: fetch it before the weight
+    // stream starts, or these few KB wait behind megabytes of queued weight traffic.
+    const uint32_t nthr_c = p.NW * 32; // consumer threads
+    PrepPre pre;
+    if (!p.pdl && !producer) prep_preload(pre, p.x, p.norm_w, p.in_dim, tid, nthr_c);
     if (tid == 0) {
         for (uint32_t s = 0; s < p.S; ++s) {
             mbar_init(&full[s], 1);
@@ -174,59 +193,76 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
     }
     __syncthreads();
 
-    auto issue = [&](uint32_t k, uint32_t s) {
-        const uint32_t r0 = rbeg + k * p.R;
-        const uint32_t rows = min(p.R, rend - r0);
-        const uint32_t wb = rows * p.row_bytes, tb = rows * p.tbl_row_bytes;
-        uint8_t *dst = ring + (size_t)s * p.stage_bytes;
-        mbar_arrive_expect_tx(&full[s], wb + 2 * tb);
-        bulk_g2s(dst, p.w + (size_t)r0 * p.row_bytes, wb, &full[s]);
-        if (FMT == FMT_MLX4) {
-            bulk_g2s(dst + p.w_stage_bytes, p.scales + (size_t)r0 * p.tbl_row_bytes, tb, &full[s]);
-            bulk_g2s(dst + p.w_stage_bytes + p.tbl_stage_bytes, p.biases + (size_t)r0 * p.tbl_row_bytes, tb, &full[s]);
+    if (producer) {
+        // One tile = one contiguous byte range (plus two table ranges for MLX).  The
+        // whole producer warp issues it, in chunks of p.chunk bytes spread over the
+        // lanes; all chunks complete on the tile's barrier.  Weights do not depend on
+        // the previous kernel in the stream, so the stream starts at once.  The first
+        // ring revolution is staggered (tile k is requested when tile k-1 has landed):
+        // requested together, all S tiles would arrive together and the first row
+        // could only be computed when most of the ring had been filled.
+        for (uint32_t k = 0; k < ntiles; ++k) {
+            const uint32_t s = k % p.S;
+            bool ok = true;
+            if (lane == 0) {
+                if (k >= p.S) ok = wait_or_timeout(&empty[s], ((k / p.S) - 1) & 1);
+                else if (k > 0 && p.stagger) ok = wait_or_timeout(&full[k - 1], 0);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
+                break;
+            }
+            const uint32_t r0 = rbeg + k * p.R;
+            const uint32_t rows = min(p.R, rend - r0);
+            const uint32_t wb = rows * p.row_bytes, tb = rows * p.tbl_row_bytes;
+            uint8_t *dst = ring + (size_t)s * p.stage_bytes;
+            if (lane == 0) mbar_arrive_expect_tx(&full[s], wb + 2 * tb);
+            __syncwarp();
+            const uint8_t *src = p.w + (size_t)r0 * p.row_bytes;
+            for (uint32_t off = lane * p.chunk; off < wb; off += 32 * p.chunk)
+                bulk_g2s(dst + off, src + off, min(p.chunk, wb - off), &full[s]);
+            if (FMT == FMT_MLX4 && lane < 2) {
+                const uint8_t *t = (lane ? p.biases : p.scales) + (size_t)r0 * p.tbl_row_bytes;
+                bulk_g2s(dst + p.w_stage_bytes + lane * p.tbl_stage_bytes, t, tb, &full[s]);
+            }
         }
-    };
+        return;
+    }
 
-    // Weights do not depend on the previous kernel in the stream: start the first
-    // S tiles now, before waiting for it.
-    if (producer && lane == 0)
-        for (uint32_t k = 0; k < ntiles && k < p.S; ++k) issue(k, k);
+    // ---- consumer warps (named barrier 2 = all of them) ----
     pdl_wait_prior();
+    if (p.pdl) prep_preload(pre, p.x, p.norm_w, p.in_dim, tid, nthr_c);
 
     // Optional fused RMSNorm of the input (crates/ullm-model/src/math.rs:82-86):
     // every CTA recomputes the mean square of x (a few KB from L2).
     ActSrc src{p.x, p.norm_w, 0.f};
     if (p.norm_w) {
         float ss = 0.f;
-        for (uint32_t i = tid * 4; i < p.in_dim; i += blockDim.x * 4) {
-            float4 t = __ldg((const float4 *)(p.x + i));
-            ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+        const uint32_t ntasks = p.in_dim >> 3;
+#pragma unroll
+        for (int ps = 0; ps < PREP_NPRE; ++ps)
+            if (ps * nthr_c + tid < ntasks) {
+                const float4 a = pre.x[ps][0], b = pre.x[ps][1];
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+            }
+        for (uint32_t t = PREP_NPRE * nthr_c + tid; t < ntasks; t += nthr_c) {
+            const float4 a = __ldg((const float4 *)(p.x + 8 * t)), b = __ldg((const float4 *)(p.x + 8 * t + 4));
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
         }
         ss = warp_sum(ss);
         if (lane == 0) part[warp] = ss;
-        __syncthreads();
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
         float tot = 0.f;
-        for (uint32_t w = 0; w <= p.NW; ++w) tot += part[w];
+        for (uint32_t w = 0; w < p.NW; ++w) tot += part[w];
         src.inv = 1.0f / sqrtf(tot / (float)p.in_dim + p.eps);
-        __syncthreads(); // part is reused by the row reduction below
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // part is reused by the row reduction below
     }
     // x -> fixed-point register images, built once per CTA in shared memory
-    prep_image<FMT>(src, p.in_dim, prep, tid, blockDim.x);
-    __syncthreads();
-
-    if (producer) {
-        if (lane == 0) {
-            for (uint32_t k = p.S; k < ntiles; ++k) {
-                const uint32_t s = k % p.S;
-                if (!wait_or_timeout(&empty[s], ((k / p.S) - 1) & 1)) {
-                    *(volatile int *)p.status = DEV_TIMEOUT;
-                    break;
-                }
-                issue(k, s);
-            }
-        }
-        return;
-    }
+    stamp();
+    prep_image<FMT>(src, p.in_dim, prep, tid, nthr_c, &pre);
+    asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+    stamp();
 
     const uint32_t rs = warp / p.WC, cgw = warp % p.WC;
     uint32_t X[G][XR];
@@ -244,9 +280,31 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
     const uint32_t nb = p.in_dim / QK_K;
 
     bool aborted = false;
+    // Sums the per-column-group partials of tile kt and writes its rows.  Run by the
+    // first warp of each row slice, one tile-ring revolution late: by then every
+    // warp has released the tile's stage (and written its partials before doing
+    // so), so no barrier between the warps of a slice is needed per tile.
+    auto flush = [&](uint32_t kt) {
+        if (cgw != 0 || lane >= RW) return;
+        const float *pt = part + ((size_t)(((kt / p.S) & 1) * p.S + kt % p.S) * p.R) * p.WC;
+        const uint32_t row = rs * RW + lane, gr = rbeg + kt * p.R + row;
+        if (gr >= rend || aborted) return;
+        float acc = 0.f;
+        for (uint32_t c = 0; c < p.WC; ++c) acc += pt[row * p.WC + c];
+        if (p.epi == EPI_STORE) p.y[gr] = acc;
+        else if (p.epi == EPI_RESIDUAL) p.y[gr] = p.res[gr] + acc;
+        else if ((lane & 1) == 0) {
+            float up = 0.f;
+            for (uint32_t c = 0; c < p.WC; ++c) up += pt[(row + 1) * p.WC + c];
+            p.y[gr >> 1] = acc / (1.0f + expf(-acc)) * up;
+        }
+    };
     for (uint32_t k = 0; k < ntiles; ++k) {
         const uint32_t s = k % p.S;
+        stamp();
         if (!aborted && !wait_or_timeout(&full[s], (k / p.S) & 1)) aborted = true;
+        stamp();
+        if (p.WC > 1 && k >= p.S) flush(k - p.S);
         const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
         const uint32_t r0 = rbeg + k * p.R;
         float v[RW];
@@ -254,7 +312,7 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
         for (int rr = 0; rr < RW; ++rr) {
             v[rr] = 0.f;
             const uint32_t rl = rs * RW + rr;
-            if (!aborted && r0 + rl < rend) {
+            if (!aborted && !p.skip_compute && r0 + rl < rend) {
                 const uint32_t row_addr = stage + rl * p.row_bytes;
                 uint32_t ts, tb2;
                 if (FMT == FMT_Q6KR) ts = row_addr + 192u * nb, tb2 = row_addr + 208u * nb;
@@ -264,9 +322,6 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
                     if (live[g]) v[rr] += row_partial<FMT, TBL>(row_addr, X[g], cgw + g * p.WC, lane, ts, tb2, p.group);
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]); // stage may be refilled
-
         uint32_t myrow;
         float r = warp_reduce_rows<RW>(v, lane, myrow);
         const uint32_t rl = rs * RW + myrow;
@@ -282,26 +337,18 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
                 else if ((myrow & 1) == 0) p.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
             }
         } else {
-            float *pt = part + (size_t)(k & 1) * p.R * p.WC;
+            float *pt = part + ((size_t)(((k / p.S) & 1) * p.S + s) * p.R) * p.WC;
             if ((lane & 7) == 0 && (RW == 4 || (lane & 8) == 0)) pt[rl * p.WC + cgw] = r;
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + rs), "r"(p.WC * 32) : "memory");
-            const uint32_t sl = cgw * 32 + lane;
-            if (sl < RW) {
-                const uint32_t row = rs * RW + sl;
-                float acc = 0.f;
-                for (uint32_t c = 0; c < p.WC; ++c) acc += pt[row * p.WC + c];
-                if (r0 + row < rend && !aborted) {
-                    if (p.epi == EPI_STORE) p.y[r0 + row] = acc;
-                    else if (p.epi == EPI_RESIDUAL) p.y[r0 + row] = p.res[r0 + row] + acc;
-                    else if ((sl & 1) == 0) {
-                        float up = 0.f;
-                        for (uint32_t c = 0; c < p.WC; ++c) up += pt[(row + 1) * p.WC + c];
-                        p.y[(r0 + row) >> 1] = acc / (1.0f + expf(-acc)) * up;
-                    }
-                }
-            }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]); // partials written, stage may be refilled
     }
+    stamp();
+    if (p.WC > 1) {
+        asm volatile("bar.sync 1, %0;" ::"r"(p.NW * 32) : "memory"); // all partials of the last tiles are in
+        for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt);
+    }
+    stamp();
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
 }
 
@@ -342,7 +389,16 @@ struct Plan {
 };
 
 // Tuning overrides (tests / sweeps): 0 = choose automatically.
-static int g_force_wr = 0, g_force_rw = 0, g_force_stages = 0;
+static int g_force_wr = 0, g_force_rw = 0, g_force_stages = 0, g_force_cpsm = 0;
+void matvec_set_ctas_per_sm(int v) { g_force_cpsm = v; }
+static unsigned long long *g_trace = nullptr;
+static int g_skip_compute = 0;
+static int g_chunk = 0;
+static int g_stagger = 1;
+void matvec_set_stagger(int v) { g_stagger = v; }
+void matvec_set_chunk(int v) { g_chunk = v; }
+void matvec_set_trace(void *p) { g_trace = (unsigned long long *)p; }
+void matvec_set_skip_compute(int v) { g_skip_compute = v; }
 void matvec_set_plan_override(int wr, int rw, int stages) { g_force_wr = wr, g_force_rw = rw, g_force_stages = stages; }
 
 static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
@@ -365,13 +421,17 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
     if (epi == EPI_SWIGLU) gran = std::max(gran, 2u);
     if (out_dim % gran) return best;
     const uint32_t ncg = (uint32_t)((in_dim + cg_elems - 1) / cg_elems);
-    const uint32_t max_warps = 24;
+    // Two CTAs per SM (half the warps and half the ring each) let the CTAs of the next
+    // kernel of a programmatic-dependent chain move in and prefetch while this one runs.
+    const uint32_t cpsm = g_force_cpsm ? (uint32_t)g_force_cpsm : 1u;
+    const uint32_t max_warps = cpsm == 2 ? 12 : 24;
     const uint32_t G = (ncg + 15) / 16;
     if (G > 2) return best;
     const uint32_t WC = (ncg + G - 1) / G;
-    const int budget = dev.max_smem_optin - 1024;
+    if (WC > max_warps) return best;
+    const int budget = cpsm == 2 ? (dev.max_smem_sm - 2048) / 2 - 1024 : dev.max_smem_optin - 1024;
     const uint32_t units = (uint32_t)(out_dim / gran);
-    const uint32_t grid = std::min<uint32_t>((uint32_t)dev.sm_count, units);
+    const uint32_t grid = std::min<uint32_t>((uint32_t)dev.sm_count * cpsm, units);
     const uint32_t rows_cta = ((units + grid - 1) / grid) * gran; // the largest range
     for (uint32_t WR = 1; WR <= 15; ++WR) {
         if (WC * WR > max_warps) break;
@@ -385,18 +445,22 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
             const uint32_t stage = wst + 2 * tst;
             if (stage > 64 * 1024) continue;
             const uint32_t off_part = 128;
-            const uint32_t off_prep = align_up(off_part + std::max(2 * R * WC * 4, 128u), 128);
+            const uint32_t off_prep = align_up(off_part + std::max(2 * 8 * R * WC * 4, 128u), 128);
             const uint32_t off_ring = align_up(off_prep + ncg * xregs * 32 * 4, 128);
             if ((int)off_ring + 2 * (int)stage > budget) continue;
             const uint32_t tiles = (rows_cta + R - 1) / R;
             uint32_t S = std::min<uint32_t>(8, (budget - off_ring) / stage);
             S = std::min(S, std::max(2u, tiles));
             if (g_force_stages) S = std::min<uint32_t>(S, (uint32_t)g_force_stages);
-            const double eff = (double)rows_cta / ((double)tiles * R);      // idle warps in the ragged tile
-            const double warps = std::min(1.0, (WC * WR) / 20.0);           // latency hiding
-            const double inflight = std::min(1.0, (double)(S * stage) / 65536.0);
-            const double pipe = tiles >= 3 ? 1.0 : 0.85;                    // something to overlap with
-            const double score = eff * (0.4 + 0.6 * warps) * (0.6 + 0.4 * inflight) * pipe * (1.0 + 0.02 * std::log2((double)RW));
+            // Measured on B200: rows-per-warp 2 beats 1 (more independent work per tile
+            // wait), tiles of 40-64 KB beat small ones, three or more stages unless the
+            // CTA's whole range fits in two.
+            const double eff = (double)rows_cta / ((double)tiles * R); // idle warps in the ragged tile
+            const double f_warps = std::sqrt(std::min(1.0, (WC * WR) / (cpsm == 2 ? 10.0 : 16.0)));
+            const double f_rw = RW == 1 ? 0.85 : (RW == 2 ? 1.0 : 0.97);
+            const double f_stage = std::sqrt(std::min(1.0, stage / (cpsm == 2 ? 28672.0 : 45056.0)));
+            const double f_depth = (S >= 3 || tiles <= S) ? 1.0 : 0.85;
+            const double score = eff * f_warps * f_rw * f_stage * f_depth;
             if (score > best.score) {
                 best.ok = true;
                 best.score = score;
@@ -480,6 +544,10 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
         pl.p.w = (const uint8_t *)d_w, pl.p.scales = (const uint8_t *)tb.scales, pl.p.biases = (const uint8_t *)tb.biases;
         pl.p.x = d_x, pl.p.y = d_y, pl.p.status = d_status;
         pl.p.norm_w = o.norm_w, pl.p.eps = o.eps, pl.p.epi = o.epi, pl.p.res = o.res;
+        pl.p.trace = g_trace, pl.p.skip_compute = g_skip_compute;
+        pl.p.pdl = o.pdl ? 1 : 0;
+        pl.p.stagger = g_stagger;
+        pl.p.chunk = g_chunk > 0 ? (uint32_t)g_chunk / 16 * 16 : 4096u;
         if (fmt == FMT_Q4K) return launch_stream_f<FMT_Q4K, float>(pl, st, o.pdl);
         if (fmt == FMT_Q6K) return launch_stream_f<FMT_Q6K, float>(pl, st, o.pdl);
         if (fmt == FMT_Q6KR) return launch_stream_f<FMT_Q6KR, float>(pl, st, o.pdl);

@@ -92,15 +92,59 @@ __device__ __forceinline__ float4 act_load4(const ActSrc &a, uint32_t i) {
 //        word j is element 8j+n (dequant.rs:310-311).  k = j: high plane of the even
 //        nibbles of word j, 4+j: their low plane, 8+j / 12+j: the odd nibbles (used in
 //        place, value*16), 16: x scale / 16, 17: fp32 sum of the 32 x values.
+// Raw x values a thread fetched early (before the weight stream was started, so that
+// these small loads do not queue behind megabytes of weight traffic): pass ps of the
+// task loop below, i.e. elements 8 * (ps * nthr + tid) .. +7.
+constexpr int PREP_NPRE = 3;
+struct PrepPre {
+    float4 x[PREP_NPRE][2];
+    float4 w0[2]; // norm weights of pass 0
+    bool valid = false;
+};
+__device__ __forceinline__ void prep_preload(PrepPre &pre, const float *x, const float *norm_w, uint32_t in_dim, uint32_t tid,
+                                             uint32_t nthr) {
+    const uint32_t ntasks = in_dim >> 3;
+#pragma unroll
+    for (int ps = 0; ps < PREP_NPRE; ++ps) {
+        const uint32_t t = ps * nthr + tid;
+        const uint32_t e = (t < ntasks ? t : 0u) << 3;
+        pre.x[ps][0] = __ldg((const float4 *)(x + e));
+        pre.x[ps][1] = __ldg((const float4 *)(x + e + 4));
+    }
+    if (norm_w) {
+        const uint32_t e = (tid < ntasks ? tid : 0u) << 3;
+        pre.w0[0] = __ldg((const float4 *)(norm_w + e));
+        pre.w0[1] = __ldg((const float4 *)(norm_w + e + 4));
+    }
+    pre.valid = true;
+}
+__device__ __forceinline__ float4 norm4(float4 t, float inv, float4 w) {
+    t.x = t.x * inv * w.x, t.y = t.y * inv * w.y, t.z = t.z * inv * w.z, t.w = t.w * inv * w.w;
+    return t;
+}
+
 template <int FMT>
-__device__ __forceinline__ void prep_image(const ActSrc &src, uint32_t in_dim, uint32_t *img, uint32_t tid, uint32_t nthr) {
+__device__ __forceinline__ void prep_image(const ActSrc &src, uint32_t in_dim, uint32_t *img, uint32_t tid, uint32_t nthr,
+                                           const PrepPre *pre = nullptr) {
     constexpr int XR = FmtTraits<FMT>::XREGS;
     const uint32_t ntasks = in_dim >> 3;
-    for (uint32_t base = 0; base < ntasks; base += nthr) {
+    int pass = 0;
+    for (uint32_t base = 0; base < ntasks; base += nthr, ++pass) {
         const uint32_t t = base + tid;
         const bool act = t < ntasks;
         const uint32_t e = (act ? t : 0u) << 3;
-        float4 t0 = act_load4(src, e), t1 = act_load4(src, e + 4);
+        float4 t0, t1;
+        if (pre && pass < PREP_NPRE) {
+            t0 = pass == 0 ? pre->x[0][0] : (pass == 1 ? pre->x[1][0] : pre->x[2][0]);
+            t1 = pass == 0 ? pre->x[0][1] : (pass == 1 ? pre->x[1][1] : pre->x[2][1]);
+            if (src.norm_w) {
+                float4 w0 = pass == 0 ? pre->w0[0] : __ldg((const float4 *)(src.norm_w + e));
+                float4 w1 = pass == 0 ? pre->w0[1] : __ldg((const float4 *)(src.norm_w + e + 4));
+                t0 = norm4(t0, src.inv, w0), t1 = norm4(t1, src.inv, w1);
+            }
+        } else {
+            t0 = act_load4(src, e), t1 = act_load4(src, e + 4);
+        }
         const float v[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
         float mx = 0.f, sum = 0.f;
 #pragma unroll

@@ -110,6 +110,7 @@ extern "C" int ullm_cuda_moe_ffn_noalloc(int device, const ullm_moe_experts_inpu
             pd.scratch = (unsigned char *)p;
             pd.info.sm_count = prop.multiProcessorCount;
             pd.info.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+            pd.info.max_smem_sm = (int)prop.sharedMemPerMultiprocessor;
             pd.ready = true;
         }
     }
