@@ -35,7 +35,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from ullm_b200 import synth  # noqa: E402
+from ullm_b200 import shard, synth  # noqa: E402
 
 C1_UP = (14336, 4096)
 C1_DOWN = (4096, 14336)
@@ -440,33 +440,57 @@ def run_multi(args):
     dev = torch.device(f"cuda:{local}")
     stream = torch.cuda.current_stream().cuda_stream
 
-    mats = []
+    # Row slices: rank r owns rows [r*out/N, (r+1)*out/N) of every matrix and generates
+    # only those (rows are self-contained byte ranges).  Enough distinct device copies of
+    # the slice set are walked round-robin that a step never finds its weights in L2.
+    slice_bytes = sum(weight_bytes(dt, o // world, c) for _, dt, o, c in C4_MATS)
+    ncopies = max(1, -(-400_000_000 // slice_bytes))
+    rows_total = shard.local_offsets([o for _, _, o, _ in C4_MATS], world)[-1]
+    y_cat = torch.empty(rows_total, dtype=torch.float32, device=dev)       # this rank's rows of all 7 outputs
+    y_all = torch.empty(world * rows_total, dtype=torch.float32, device=dev)  # [rank][matrix][rows]
+    mats, off = [], 0
     for i, (name, dt, out, cols) in enumerate(C4_MATS):
         assert out % world == 0
         rows = out // world
-        # each rank generates only its own row slice (rows are self-contained byte ranges)
         w = synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1))
         xv = synth.normal(synth.seed_for(4, 8 + i), cols)
-        mats.append(dict(dt=dt, rows=rows, out=out, cols=cols, w=backend.Weight(ctx, dt, w, rows, cols),
-                         x=torch.from_numpy(xv).to(dev), y_local=torch.empty(rows, dtype=torch.float32, device=dev),
-                         y_full=torch.empty(out, dtype=torch.float32, device=dev)))
+        mats.append(dict(rows=rows, cols=cols, off=off, ws=[backend.Weight(ctx, dt, w, rows, cols) for _ in range(ncopies)],
+                         x=torch.from_numpy(xv).to(dev), xh=torch.from_numpy(xv).pin_memory()))
+        off += rows
+    y_host = torch.empty(world * rows_total, dtype=torch.float32).pin_memory()
 
-    # Kernels and NCCL collectives share one non-default stream: a NULL stream handle
-    # would send the kernels to the context's own stream, unordered with NCCL.
+    # Kernels and the NCCL collective share one non-default stream (a NULL handle would
+    # send the kernels to the context's own stream, unordered with NCCL).
     side = torch.cuda.Stream()
     stream = side.cuda_stream
+    use_pdl = bool(args.pdl) and args.multi_graph
+    ctx.debug_set("pdl", 1 if use_pdl else 0)
+    batches = [backend.WeightBatch(ctx, [m["ws"][c] for m in mats], [m["x"].data_ptr() for m in mats],
+                                   [y_cat.data_ptr() + 4 * m["off"] for m in mats]) for c in range(ncopies)]
 
-    def step(_i):
-        for m in mats:
-            m["w"].matvec_dev(m["x"].data_ptr(), m["y_local"].data_ptr(), stream)
-        for m in mats:
-            dist.all_gather_into_tensor(m["y_full"], m["y_local"])
+    def step(i):
+        batches[i % ncopies].launch(stream)  # the seven matvecs of this rank, one host call
+        # the one exchange of the path: every rank's output rows to every rank
+        dist.all_gather_into_tensor(y_all, y_cat)
 
     torch.cuda.synchronize()
     with torch.cuda.stream(side):
-        for i in range(args.warmup):
+        for i in range(max(args.warmup, 3)):
             step(i)
     torch.cuda.synchronize()
+    graph = None
+    if args.multi_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(args.steps):
+                    step(args.warmup + i)
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as e:  # fall back to host launches, say so in the line
+            graph = None
+            print(f"graph capture failed on rank {rank}: {e}", file=sys.stderr)
+            torch.cuda.synchronize()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -476,12 +500,35 @@ def run_multi(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(side):
         ev0.record()
-        for i in range(args.steps):
-            step(i)
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(args.steps):
+                step(args.warmup + i)
         ev1.record()
     torch.cuda.synchronize()
     dist.barrier()
     ctx.synchronize()
+
+    # end to end: x vectors from pinned host memory, gathered outputs back to the host
+    def e2e_step(i):
+        with torch.cuda.stream(side):
+            for m in mats:
+                m["x"].copy_(m["xh"], non_blocking=True)
+            step(i)
+            y_host.copy_(y_all, non_blocking=True)
+        side.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    dist.barrier()
+    t0 = time.perf_counter()
+    n_e2e = min(args.steps, 200)
+    for i in range(n_e2e):
+        e2e_step(i)
+    e2e_t = torch.tensor([time.perf_counter() - t0], device=dev)
+    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_s = float(e2e_t.item()) / n_e2e
     ms_t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
     dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
     ms = float(ms_t.item())
@@ -496,12 +543,15 @@ def run_multi(args):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8 dot products (16-bit fixed-point x) + f32 accumulate", "data": "synthetic",
             "config": {"workload": "c4_70b_layer_matvec", "shapes": "Q4_K q,o [8192,8192] k,v [1024,8192] gate,up [28672,8192]; Q6_K down [8192,28672]",
-                       "parallelism": f"rows/{world} + NCCL all-gather per output vector",
-                       "l2": "542 MB of weights per step: inputs larger than the aggregate L2 only at N<=4; per-rank slice at N=8 is 68 MB (L2-resident)"},
+                       "parallelism": f"rows/{world} per matrix, one NCCL all-gather of the ranks' output rows per step",
+                       "l2": f"{ncopies} distinct copies of the per-rank slice set ({slice_bytes // 1000000} MB each) walked round-robin: inputs larger than L2",
+                       "launch": "one CUDA graph of all timed steps" if graph is not None else "host launches (one C call per step) + NCCL", "pdl": use_pdl},
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
                          "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "matvec_stream_kernel (per rank, incl. all-gather time)"},
             "cpu_baseline": None,
-            "e2e": None,
+            "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * sum(c for _, _, _, c in C4_MATS),
+                    "d2h_bytes_per_step": 4 * world * rows_total, "us_per_step": e2e_s * 1e6,
+                    "api": "pinned host x -> ullm_cuda_weight_matvec_dev x7 -> NCCL all-gather -> pinned host y"},
             "gpu_launches": 7 * args.steps,
             "clocks": clocks,
         }
@@ -519,6 +569,7 @@ def main():
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--pdl", type=int, default=1, help="launch the kernels with programmatic dependent launch (weight prefetch of the next kernel overlaps the tail of the previous one)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--multi-graph", action="store_true", help="N>1: capture kernels + NCCL in a CUDA graph (off by default)")
     ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
     ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"],
                     help="single-GPU only: c1 is the headline workload, the others are auxiliary measurements")

@@ -127,6 +127,10 @@ void ullm_cuda_weight_destroy(ullm_cuda_ctx *ctx, ullm_cuda_weight *w);
 int ullm_cuda_weight_matvec(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *x, float *y);
 /* The same on device vectors, enqueued on `stream` (NULL = the context's). */
 int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *d_x, float *d_y, void *stream);
+/* `n` independent matvecs enqueued by one call (the projections of one layer that
+ * share no data: q/k/v, gate/up): y[i] = W[i] x[i], device vectors. */
+int ullm_cuda_weight_matvec_batch_dev(ullm_cuda_ctx *ctx, size_t n, const ullm_cuda_weight *const *w,
+                                      const float *const *d_x, float *const *d_y, void *stream);
 /* The weight's original on-disk bytes (`len` = ullm_cuda_weight_bytes). */
 int ullm_cuda_weight_export(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, void *bytes, size_t len);
 size_t ullm_cuda_weight_bytes(const ullm_cuda_weight *w);

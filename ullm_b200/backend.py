@@ -70,6 +70,7 @@ SIGNATURES = {
     "ullm_cuda_weight_destroy": (None, [_vp, _vp]),
     "ullm_cuda_weight_matvec": (_i, [_vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_dev": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "ullm_cuda_weight_matvec_batch_dev": (_i, [_vp, _sz, _vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_export": (_i, [_vp, _vp, _vp, _sz]),
     "ullm_cuda_weight_bytes": (_sz, [_vp]),
     "ullm_cuda_matmul_quant": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
@@ -325,6 +326,22 @@ class Weight:
             self.free()
         except Exception:
             pass
+
+
+class WeightBatch:
+    """A fixed list of independent matvecs (weights, device x, device y) launched by one
+    call of ``ullm_cuda_weight_matvec_batch_dev``."""
+
+    def __init__(self, ctx: CudaContext, weights, d_xs, d_ys):
+        n = len(weights)
+        self._ctx, self._n, self._keep = ctx, n, weights
+        self._w = (_vp * n)(*[w._h for w in weights])
+        self._x = (_vp * n)(*d_xs)
+        self._y = (_vp * n)(*d_ys)
+
+    def launch(self, stream=None):
+        c = self._ctx
+        c._check(c._lib.ullm_cuda_weight_matvec_batch_dev(c._h, self._n, self._w, self._x, self._y, stream))
 
 
 class MoeExpertsInput(C.Structure):

@@ -360,6 +360,16 @@ int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *c, const ullm_cuda_weight *w, con
     return ULLM_OK;
 }
 
+int ullm_cuda_weight_matvec_batch_dev(ullm_cuda_ctx *c, size_t n, const ullm_cuda_weight *const *w, const float *const *d_x,
+                                      float *const *d_y, void *stream) {
+    if (!c || (n && (!w || !d_x || !d_y))) return ULLM_ERR_INVALID;
+    for (size_t i = 0; i < n; ++i) {
+        int rc = ullm_cuda_weight_matvec_dev(c, w[i], d_x[i], d_y[i], stream);
+        if (rc) return rc;
+    }
+    return ULLM_OK;
+}
+
 int ullm_cuda_weight_matvec(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const float *x, float *y) {
     if (!c || !w || !x || !y) return ULLM_ERR_INVALID;
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
@@ -644,7 +654,7 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, u
     ullm_cuda_fwd *f = new (std::nothrow) ullm_cuda_fwd();
     if (!f) return ULLM_ERR_OOM;
     f->ctx = c;
-    f->f.use_pdl = c->use_pdl;
+    f->f.use_pdl = !c->force_generic; // programmatic dependent launch between the kernels of a step
     cudaError_t e = f->f.init(c->dev, c->device, P, hm);
     if (e != cudaSuccess) {
         int code = fwd_fail(f, e, "uploading the model");

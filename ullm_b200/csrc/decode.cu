@@ -26,7 +26,7 @@ namespace ullm {
 // ---------------------------------------------------------------------------
 // Attention for one new token
 // ---------------------------------------------------------------------------
-constexpr int ATT_CHUNK = 64; // cache positions per CTA
+constexpr int ATT_CHUNK = 128; // cache positions per CTA
 
 template <typename T> __device__ __forceinline__ float kv_load(const T *p);
 template <> __device__ __forceinline__ float kv_load<float>(const float *p) { return __ldcg(p); }
@@ -161,6 +161,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     for (int h = 0; h < KVMUL; ++h)
 #pragma unroll
         for (int e = 0; e < E; ++e) acc[h][e] = 0.f;
+#pragma unroll 4
     for (int i = warp; i < np; i += 4) {
         const KV_T *vp = vc + (size_t)(p0 + i) * p.kv_dim + kvh * HD + lane * E;
         float vv[E];
@@ -197,19 +198,33 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // merge the splits: w[h][s] = exp(m_s - M) / L first (all loads independent), then
+    // one pass over the partial outputs
     const float *base = p.partial + ((size_t)kvh * p.n_split * KVMUL) * (HD + 2);
+    __shared__ float wgt[KVMUL][64]; // up to 64 splits (8192 positions)
+    for (int i = tid; i < KVMUL * n_active; i += 128) {
+        const int h = i / n_active, s2 = i % n_active;
+        wgt[h][s2] = __ldcg(base + ((size_t)s2 * KVMUL + h) * (HD + 2) + HD);
+    }
+    __syncthreads();
+    if (tid < KVMUL) {
+        float M = -INFINITY, L = 0.f;
+        for (int s2 = 0; s2 < n_active; ++s2) M = fmaxf(M, wgt[tid][s2]);
+        for (int s2 = 0; s2 < n_active; ++s2) {
+            const float w = expf(wgt[tid][s2] - M);
+            L += __ldcg(base + ((size_t)s2 * KVMUL + tid) * (HD + 2) + HD + 1) * w;
+            wgt[tid][s2] = w;
+        }
+        const float invL = 1.0f / L;
+        for (int s2 = 0; s2 < n_active; ++s2) wgt[tid][s2] *= invL;
+    }
+    __syncthreads();
     for (int i = tid; i < KVMUL * HD; i += 128) {
         const int h = i / HD, d = i % HD;
-        float M = -INFINITY;
-        for (int s = 0; s < n_active; ++s) M = fmaxf(M, __ldcg(base + ((size_t)s * KVMUL + h) * (HD + 2) + HD));
-        float L = 0.f, o = 0.f;
-        for (int s = 0; s < n_active; ++s) {
-            const float *ps = base + ((size_t)s * KVMUL + h) * (HD + 2);
-            const float w = expf(__ldcg(ps + HD) - M);
-            L += __ldcg(ps + HD + 1) * w;
-            o += __ldcg(ps + d) * w;
-        }
-        p.out[(size_t)(kvh * KVMUL + h) * HD + d] = o / L;
+        float o = 0.f;
+#pragma unroll 8
+        for (int s2 = 0; s2 < n_active; ++s2) o += __ldcg(base + ((size_t)s2 * KVMUL + h) * (HD + 2) + d) * wgt[h][s2];
+        p.out[(size_t)(kvh * KVMUL + h) * HD + d] = o;
     }
 }
 
@@ -295,6 +310,7 @@ const char *Forward::check_params(const ForwardParams &p) {
     if (!p.n_embd || !p.n_layer || !p.n_head || !p.n_kv_head || !p.head_dim || !p.n_ff || !p.n_ctx || !p.vocab)
         return "zero hyperparameter";
     if (p.n_head % p.n_kv_head) return "n_head is not a multiple of n_kv_head";
+    if (p.n_ctx > 8192) return "context longer than 8192 positions"; // the reference caps it there too (lib.rs:236)
     const size_t kvmul = p.n_head / p.n_kv_head;
     if (p.head_dim != 64 && p.head_dim != 128) return "head_dim must be 64 or 128";
     if (kvmul != 1 && kvmul != 2 && kvmul != 4 && kvmul != 8) return "n_head / n_kv_head must be 1, 2, 4 or 8";

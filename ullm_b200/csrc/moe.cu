@@ -41,52 +41,47 @@ __host__ __device__ inline int route_off_pairs(int E) { return 2 + 2 * E; }
 __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict__ logits, int n_tok, int n_exp, int k,
                                                        uint32_t *__restrict__ idx, float *__restrict__ wts,
                                                        int *__restrict__ route) {
-    __shared__ float lg[MOE_MAX_EXPERTS];
+    __shared__ float lg[MOE_MAX_TOK][MOE_MAX_EXPERTS];
     __shared__ int sel[MOE_MAX_TOK * MOE_MAX_K];
     __shared__ int cnt[MOE_MAX_EXPERTS];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    __shared__ int offs_s[MOE_MAX_EXPERTS + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
     pdl_wait_prior();
-    for (int t = 0; t < n_tok; ++t) {
-        // token t is handled by warp t % nwarp; logits staged per warp would need
-        // nwarp copies, so tokens are simply processed one after another by warp 0..:
-        // n_tok <= 8 and n_exp <= 1024, this kernel is a few microseconds.
-        __syncthreads();
-        for (int i = threadIdx.x; i < n_exp; i += blockDim.x) lg[i] = logits[(size_t)t * n_exp + i];
-        __syncthreads();
-        if (warp == 0) {
-            float selv[MOE_MAX_K];
-            for (int j = 0; j < k; ++j) {
-                float bv = -INFINITY;
-                int bi = 0x7fffffff;
-                for (int i = lane; i < n_exp; i += 32) {
-                    float v = lg[i];
-                    if (v > bv || (v == bv && i < bi)) bv = v, bi = i; // first index wins
-                }
+    // one warp per token (n_tok <= 8 = warps of the block)
+    if (warp < n_tok) {
+        const int t = warp;
+        float *l = lg[t];
+        for (int i = lane; i < n_exp; i += 32) l[i] = logits[(size_t)t * n_exp + i];
+        __syncwarp();
+        float mx = 0.f, wsum = 0.f, mine = 0.f;
+        for (int j = 0; j < k; ++j) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int i = lane; i < n_exp; i += 32) {
+                const float v = l[i];
+                if (v > bv || (v == bv && i < bi)) bv = v, bi = i; // first index wins
+            }
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                    if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
-                }
-                selv[j] = bv;
-                if (lane == 0) {
-                    sel[t * k + j] = bi;
-                    lg[bi] = -INFINITY; // taken (a logit of -inf itself can then be picked twice only if k > finite count)
-                }
-                __syncwarp();
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
             }
+            // softmax over the k selected logits (lib.rs:1460-1475): the first is the max
+            if (j == 0) mx = bv;
+            const float e = expf(bv - mx);
+            wsum += e; // summed in selection order, identically in every lane
+            if (lane == j) mine = e;
             if (lane == 0) {
-                // softmax over the k selected logits (lib.rs:1460-1475): max is the first
-                float mx = selv[0], wsum = 0.f, e[MOE_MAX_K];
-                for (int j = 0; j < k; ++j) {
-                    e[j] = expf(selv[j] - mx);
-                    wsum += e[j];
-                }
-                for (int j = 0; j < k; ++j) {
-                    wts[t * k + j] = e[j] / wsum;
-                    idx[t * k + j] = (uint32_t)sel[t * k + j];
-                }
+                sel[t * k + j] = bi;
+                l[bi] = -INFINITY; // taken
             }
+            __syncwarp();
+        }
+        if (lane < k) {
+            wts[t * k + lane] = mine / wsum;
+            idx[t * k + lane] = (uint32_t)sel[t * k + lane];
         }
     }
     __syncthreads();
@@ -98,19 +93,40 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
         cnt[e] = c;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int D = 0, off = 0;
-        int *list = route + route_off_list(), *offs = route + route_off_offs(n_exp), *pairs = route + route_off_pairs(n_exp);
-        for (int e = 0; e < n_exp; ++e) {
-            if (!cnt[e]) continue;
-            list[D] = e;
-            offs[D] = off;
-            for (int p = 0; p < npairs; ++p)
-                if (sel[p] == e) pairs[off++] = p;
-            ++D;
+    int *list = route + route_off_list(), *offs = route + route_off_offs(n_exp), *pairs = route + route_off_pairs(n_exp);
+    if (warp == 0) {
+        // exclusive scan of the counts and of the "used" flags, 32 experts at a time
+        int base_off = 0, base_d = 0;
+        for (int e0 = 0; e0 < n_exp; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < n_exp ? cnt[e] : 0, u = c > 0;
+            int so = c, sd = u;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int a = __shfl_up_sync(0xffffffffu, so, o), b2 = __shfl_up_sync(0xffffffffu, sd, o);
+                if (lane >= o) so += a, sd += b2;
+            }
+            if (u) {
+                const int d = base_d + sd - 1;
+                list[d] = e;
+                offs[d] = base_off + so - c;
+                offs_s[e] = base_off + so - c;
+            }
+            base_off += __shfl_sync(0xffffffffu, so, 31);
+            base_d += __shfl_sync(0xffffffffu, sd, 31);
         }
-        offs[D] = off;
-        route[0] = D;
+        if (lane == 0) {
+            offs[base_d] = base_off;
+            route[0] = base_d;
+        }
+    }
+    __syncthreads();
+    // each used expert writes its pairs, in (token, slot) order
+    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) {
+        if (!cnt[e]) continue;
+        int o = offs_s[e];
+        for (int p = 0; p < npairs; ++p)
+            if (sel[p] == e) pairs[o++] = p;
     }
 }
 

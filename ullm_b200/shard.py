@@ -1,0 +1,56 @@
+"""Row sharding of a quantized matrix over the ranks of one node.
+
+Output rows of ``y = W x`` are independent (the reference parallelises its CPU
+matvec over them, crates/ullm-model/src/math.rs:11-21), and a row of a GGUF /
+MLX matrix is a self-contained byte range, so rank ``r`` of ``N`` keeps rows
+``[r*out/N, (r+1)*out/N)`` and the path has one exchange: an all-gather of the
+ranks' output rows.  Several matrices that share a step are gathered together:
+each rank concatenates its rows of all of them, one all-gather produces the
+``[rank][matrix][rows]`` layout, and :func:`split_gathered` gives the per-matrix
+vectors back.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+BLOCK_BYTES = {12: 144, 14: 210}  # ggml ids -> bytes per 256-element super-block
+
+
+def row_range(out_dim: int, world: int, rank: int) -> tuple[int, int]:
+    if out_dim % world:
+        raise ValueError(f"{out_dim} rows do not split evenly over {world} ranks")
+    n = out_dim // world
+    return rank * n, (rank + 1) * n
+
+
+def row_bytes(dtype: int, cols: int) -> int:
+    return cols // 256 * BLOCK_BYTES[dtype]
+
+
+def slice_rows(dtype: int, w_bytes, out_dim: int, cols: int, world: int, rank: int) -> np.ndarray:
+    """The bytes of this rank's rows of a row-major quantized matrix."""
+    rb = row_bytes(dtype, cols)
+    b = np.ascontiguousarray(w_bytes).view(np.uint8).reshape(-1)
+    if b.size < out_dim * rb:
+        raise ValueError("weight buffer shorter than out_dim rows")
+    lo, hi = row_range(out_dim, world, rank)
+    return b[lo * rb : hi * rb]
+
+
+def local_offsets(out_dims, world: int) -> list[int]:
+    """Offsets of each matrix' rows inside a rank's concatenated output."""
+    offs, o = [], 0
+    for d in out_dims:
+        if d % world:
+            raise ValueError(f"{d} rows do not split evenly over {world} ranks")
+        offs.append(o)
+        o += d // world
+    return offs + [o]
+
+
+def split_gathered(y_all, out_dims, world: int) -> list[np.ndarray]:
+    """``y_all`` is the all-gathered ``[rank][matrix][rows]`` buffer; returns the full
+    output vector of every matrix (rank-major rows, i.e. original row order)."""
+    offs = local_offsets(out_dims, world)
+    per_rank = np.asarray(y_all).reshape(world, offs[-1])
+    return [per_rank[:, offs[i] : offs[i + 1]].reshape(-1) for i in range(len(out_dims))]
