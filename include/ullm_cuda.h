@@ -131,6 +131,12 @@ int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, c
  * share no data: q/k/v, gate/up): y[i] = W[i] x[i], device vectors. */
 int ullm_cuda_weight_matvec_batch_dev(ullm_cuda_ctx *ctx, size_t n, const ullm_cuda_weight *const *w,
                                       const float *const *d_x, float *const *d_y, void *stream);
+/* GpuForward::matmul (forward.rs:679-725) on a resident weight: x [s, in] f32
+ * token-major -> y [s, out].  Prefill-sized batches run on the tensor cores
+ * (activations and dequantized weights rounded to bf16, f32 accumulation). */
+int ullm_cuda_weight_matmul(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *x, float *y, size_t s);
+int ullm_cuda_weight_matmul_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *d_x, float *d_y, size_t s,
+                                void *stream);
 /* The weight's original on-disk bytes (`len` = ullm_cuda_weight_bytes). */
 int ullm_cuda_weight_export(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, void *bytes, size_t len);
 size_t ullm_cuda_weight_bytes(const ullm_cuda_weight *w);

@@ -71,6 +71,8 @@ SIGNATURES = {
     "ullm_cuda_weight_matvec": (_i, [_vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_dev": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_batch_dev": (_i, [_vp, _sz, _vp, _vp, _vp, _vp]),
+    "ullm_cuda_weight_matmul": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "ullm_cuda_weight_matmul_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "ullm_cuda_weight_export": (_i, [_vp, _vp, _vp, _sz]),
     "ullm_cuda_weight_bytes": (_sz, [_vp]),
     "ullm_cuda_matmul_quant": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
@@ -309,6 +311,16 @@ class Weight:
 
     def matvec_dev(self, d_x: int, d_y: int, stream=None):
         self._ctx._check(self._ctx._lib.ullm_cuda_weight_matvec_dev(self._ctx._h, self._h, d_x, d_y, stream))
+
+    def matmul(self, xs, s: int) -> np.ndarray:
+        """``[s, in]`` token-major activations -> ``[s, out]`` (GpuForward::matmul, forward.rs:679)."""
+        xs = _f32(xs)
+        y = np.empty((s, self.out), np.float32)
+        self._ctx._check(self._ctx._lib.ullm_cuda_weight_matmul(self._ctx._h, self._h, _ptr(xs), _ptr(y), s))
+        return y
+
+    def matmul_dev(self, d_x: int, d_y: int, s: int, stream=None):
+        self._ctx._check(self._ctx._lib.ullm_cuda_weight_matmul_dev(self._ctx._h, self._h, d_x, d_y, s, stream))
 
     def export(self) -> np.ndarray:
         n = self._ctx._lib.ullm_cuda_weight_bytes(self._h)

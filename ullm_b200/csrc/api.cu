@@ -401,18 +401,86 @@ int ullm_cuda_weight_export(ullm_cuda_ctx *c, const ullm_cuda_weight *w, void *b
 }
 
 // ---- batched matmul --------------------------------------------------------
+// Runs the tensor-core GEMM on weights in kernel format `fmt` (FMT_Q4K verbatim or
+// FMT_Q6KR prepared); ULLM_ERR_UNSUPPORTED (silently, no message) when the shape or
+// the batch is outside what it takes, so callers can fall back to per-token matvecs.
+static int gemm_try(ullm_cuda_ctx *c, int fmt, const void *d_w, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
+                    size_t s, cudaStream_t st) {
+    if (c->force_generic || s < (size_t)c->gemm_min_s || !gemm_tc_supported(fmt, out_dim, in_dim, s)) return ULLM_ERR_UNSUPPORTED;
+    void *xb = nullptr;
+    int rc = ctx_scratch(c, 7, gemm_tc_scratch_bytes(in_dim, s), &xb);
+    if (rc) return rc;
+    cudaError_t e = launch_gemm_tc(fmt, d_w, d_x, d_y, xb, out_dim, in_dim, s, c->d_status, st);
+    if (e == cudaErrorNotSupported) {
+        cudaGetLastError();
+        return ULLM_ERR_UNSUPPORTED;
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return ctx_fail(c, ULLM_ERR_CUDA, "tensor-core GEMM launch: %s", cudaGetErrorString(e));
+    }
+    c->last_plan = MatvecPlan();
+    c->last_plan.streamed = true, c->last_plan.warps = 10, c->last_plan.rows_per_tile = 128, c->last_plan.stages = 4;
+    c->last_plan.grid = -1; // marks the GEMM kernel
+    return ULLM_OK;
+}
+
 int ullm_cuda_matmul_dev(ullm_cuda_ctx *c, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
                          int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
                          size_t s, void *stream) {
     if (!c || !d_w || !d_x || !d_y) return ULLM_ERR_INVALID;
-    // Until the tensor-core kernel takes a shape, the product is formed one token
-    // column at a time with the matvec kernel (same arithmetic, weights re-read).
+    int fmt = fmt_of(dtype);
+    if (fmt < 0) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "no CUDA kernel for dtype %d yet", dtype);
+    if (const char *m = matvec_shape_error(fmt, out_dim, in_dim, group)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    // Prefill-sized batches go to the tcgen05 GEMM (dequantize to bf16 in shared memory,
+    // accumulate in TMEM); Q6_K rows are first re-ordered into the prepared layout.
+    if (fmt == FMT_Q4K || (fmt == FMT_Q6K && q6k_can_prepare(in_dim))) {
+        const void *gw = d_w;
+        int gfmt = fmt, rc = ULLM_OK;
+        if (fmt == FMT_Q6K && s >= (size_t)c->gemm_min_s && !c->force_generic) {
+            void *prep = nullptr;
+            if ((rc = ctx_scratch(c, 6, weight_bytes(fmt, out_dim, in_dim), &prep))) return rc;
+            ULLM_CUDA_TRY(c, launch_q6k_prepare(d_w, prep, out_dim, in_dim, false, st));
+            gw = prep, gfmt = FMT_Q6KR;
+        }
+        rc = gemm_try(c, gfmt, gw, d_x, d_y, out_dim, in_dim, s, st);
+        if (rc != ULLM_ERR_UNSUPPORTED) return rc;
+    }
+    // Otherwise the product is formed one token column at a time with the matvec kernel
+    // (same arithmetic, weights re-read per token).
     for (size_t t = 0; t < s; ++t) {
         int rc = ullm_cuda_matvec_dev(c, dtype, d_w, d_scales, d_biases, table_dtype, group, d_x + t * in_dim,
                                       d_y + t * out_dim, out_dim, in_dim, stream);
         if (rc) return rc;
     }
     return ULLM_OK;
+}
+
+int ullm_cuda_weight_matmul_dev(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const float *d_x, float *d_y, size_t s, void *stream) {
+    if (!c || !w || !d_x || !d_y) return ULLM_ERR_INVALID;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    int rc = gemm_try(c, w->fmt, w->w, d_x, d_y, w->out, w->cols, s, st);
+    if (rc != ULLM_ERR_UNSUPPORTED) return rc;
+    for (size_t t = 0; t < s; ++t)
+        if ((rc = ullm_cuda_weight_matvec_dev(c, w, d_x + t * w->cols, d_y + t * w->out, stream))) return rc;
+    return ULLM_OK;
+}
+
+int ullm_cuda_weight_matmul(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const float *x, float *y, size_t s) {
+    if (!c || !w || (s && (!x || !y))) return ULLM_ERR_INVALID;
+    if (s == 0) return ULLM_OK;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    void *d_x = nullptr, *d_y = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 4, s * w->cols * 4, &d_x)) || (rc = ctx_scratch(c, 5, s * w->out * 4, &d_y))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_x, x, s * w->cols * 4, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = ullm_cuda_weight_matmul_dev(c, w, (const float *)d_x, (float *)d_y, s, nullptr))) return rc;
+    ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, s * w->out * 4, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ctx_check_status(c);
 }
 
 static int matmul_host(ullm_cuda_ctx *c, int dtype, const void *d_w, const void *d_s, const void *d_b, int tdt,
@@ -469,6 +537,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     if (!strcmp(key, "force_generic")) c->force_generic = value != 0;
     else if (!strcmp(key, "pdl")) c->use_pdl = value != 0;
     else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
+    else if (!strcmp(key, "gemm_min_s")) c->gemm_min_s = value;
     else if (!strcmp(key, "skip_compute")) matvec_set_skip_compute(value);
     else if (!strcmp(key, "chunk")) matvec_set_chunk(value);
     else if (!strcmp(key, "stagger")) matvec_set_stagger(value);

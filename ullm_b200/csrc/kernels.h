@@ -68,6 +68,11 @@ void matvec_set_ctas_per_sm(int v);
 // prepare.cu — Q6_K rows <-> the prepared layout (FMT_Q6KR)
 bool q6k_can_prepare(size_t in_dim);
 cudaError_t launch_q6k_prepare(const void *d_src, void *d_dst, size_t rows, size_t in_dim, bool inverse, cudaStream_t st);
+// gemm.cu — tcgen05 / TMEM prefill GEMM on Q4_K (verbatim) or prepared Q6_K rows.
+bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s);
+size_t gemm_tc_scratch_bytes(size_t in_dim, size_t s);
+cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_xb16, size_t out_dim, size_t in_dim,
+                           size_t s, int *d_status, cudaStream_t st);
 bool matvec_is_streamed(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
                         int epi);
 // Returns a static message when the shape cannot be computed at all.
