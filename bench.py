@@ -55,6 +55,15 @@ def weight_bytes(dtype, out, cols):
     return out * (cols // 256) * (144 if dtype == synth.Q4_K else 210)
 
 
+def measured_peak_tflops():
+    """Dense bf16 cuBLAS burst throughput measured on this pool (else the earlier measurement)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
 def measured_peak_gbs():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -375,6 +384,26 @@ def run_other(args):
         ms = _time_steps(torch, step, args.steps, args.warmup)
         nbytes = sum(weight_bytes(dt, o, c) + 4 * (o + c) for _, dt, o, c in C4_MATS)
         out.update(us_per_step=ms * 1e3 / args.steps, gbs=args.steps * nbytes / ms / 1e6, bytes_per_step=nbytes)
+    elif args.workload == "c4gemm":
+        # the same block as a prefill GEMM: 512 tokens through every matrix (tcgen05 path)
+        S = args.tokens
+        tf_peak = measured_peak_tflops()
+        per, total_ms, total_flop = {}, 0.0, 0.0
+        for i, (name, dt, o, c) in enumerate(C4_MATS):
+            w = backend.Weight(ctx, dt, synth.gen_weight(dt, o, c, synth.seed_for(4, i)), o, c)
+            xs = torch.randn(S * c, dtype=torch.float32, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i))
+            ys = torch.empty(S * o, dtype=torch.float32, device=dev)
+            ms = _time_steps(torch, lambda _i, st: w.matmul_dev(xs.data_ptr(), ys.data_ptr(), S, st), args.steps, args.warmup)
+            flop = 2.0 * S * o * c
+            per[name] = {"us": round(ms * 1e3 / args.steps, 2), "tflops": round(args.steps * flop / ms / 1e9, 1)}
+            total_ms += ms / args.steps
+            total_flop += flop
+            assert ctx.last_plan()["grid"] == -1, "tensor-core GEMM did not run"
+            w.free()
+            del xs, ys
+        out.update(tokens=S, us_per_step=total_ms * 1e3, tflops=total_flop / total_ms / 1e9, peak_tflops=tf_peak,
+                   frac=total_flop / total_ms / 1e9 / tf_peak, per_matrix=per,
+                   note="includes the f32->bf16 activation cast kernel of every call")
     elif args.workload == "c2":
         ne, hid, inter, gs, ntok, k = 128, 2048, 768, 64, 8, 8
         g = synth.gen_mlx4(ne * inter, hid, gs, synth.seed_for(2, 0))
@@ -420,7 +449,8 @@ def run_other(args):
         out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, prompt_ms_per_token=t_prompt / 16 * 1e3, tokens=n_gen,
                    bytes_per_token=wbytes + kvbytes + 513_024, gbs=(wbytes + kvbytes + 513_024) * n_gen / dt / 1e9,
                    first_tokens=toks[:8].tolist())
-    out["frac_of_measured_peak"] = out["gbs"] / peak
+    if "gbs" in out:
+        out["frac_of_measured_peak"] = out["gbs"] / peak
     out["peak_kind"] = peak_kind
     print(json.dumps(out), flush=True)
     return 0
@@ -567,11 +597,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--tokens", type=int, default=512, help="prefill length of the c4gemm workload")
     ap.add_argument("--pdl", type=int, default=1, help="launch the kernels with programmatic dependent launch (weight prefetch of the next kernel overlaps the tail of the previous one)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--multi-graph", action="store_true", help="N>1: capture kernels + NCCL in a CUDA graph (off by default)")
     ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"],
+    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4", "c4gemm"],
                     help="single-GPU only: c1 is the headline workload, the others are auxiliary measurements")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -538,6 +538,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     else if (!strcmp(key, "pdl")) c->use_pdl = value != 0;
     else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
     else if (!strcmp(key, "gemm_min_s")) c->gemm_min_s = value;
+    else if (!strcmp(key, "gemm_mode")) gemm_set_debug_mode(value);
     else if (!strcmp(key, "skip_compute")) matvec_set_skip_compute(value);
     else if (!strcmp(key, "chunk")) matvec_set_chunk(value);
     else if (!strcmp(key, "stagger")) matvec_set_stagger(value);
@@ -550,6 +551,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
 }
 extern "C" int ullm_cuda_debug_trace(void *d_buf) {
     matvec_set_trace(d_buf);
+    gemm_set_trace(d_buf);
     return ULLM_OK;
 }
 extern "C" int ullm_cuda_debug_last_plan(const ullm_cuda_ctx *c, int *vals, int n) {

@@ -12,26 +12,31 @@
 // that recycle the operand slots.  The epilogue reads the accumulator back with
 // tcgen05.ld and stores token-major f32.
 //
-// Roles in a CTA of 10 warps:
-//   warp 0      TMA: activation tile [256 tokens x 64 k] per k-chunk, 4 slots
+// Roles in a CTA of 11 warps:
+//   warp 0      TMA: activation tile [256 tokens x 64 k] per k-chunk, 3 stages
+//   warp 10     TMA: the packed weight bytes of [128 rows x 256 k] per block, 2-3 stages
 //   warp 1      TMEM allocation, MMA issue, commits
-//   warps 2-9   dequantization (thread = (row, half of the 256-k block)), then epilogue
+//   warps 2-9   dequantization from the staged bytes, all 256 threads on one 64-k chunk
+//               at a time into the same 3 stages, then the epilogue
 // Every mbarrier wait is bounded; on expiry the CTA records a status, stops issuing
 // work, still frees its TMEM and leaves.
 #include "kernels.h"
 #include "matvec_core.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 namespace ullm {
 
 constexpr int GM = 128;  // weight rows per CTA (MMA M)
 constexpr int GN = 256;  // tokens per CTA (MMA N, TMEM columns)
 constexpr int GKC = 64;  // k per chunk: 64 bf16 = one 128-byte swizzle row
-constexpr int G_SLOTS = 4;
+constexpr int G_STAGES = 3;  // operand stages in flight: one dequantized weight chunk + one activation chunk each
 constexpr int G_A_BYTES = GM * GKC * 2;  // 16 KB
 constexpr int G_B_BYTES = GN * GKC * 2;  // 32 KB
-constexpr int G_THREADS = 320;
+constexpr int G_THREADS = 352;
+constexpr int G_DEQ_THREADS = 256;
+constexpr int G_RAW_WARP = 10;
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B apart
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -75,146 +80,180 @@ __device__ __forceinline__ void st_a_sw128(uint32_t tile, uint32_t row, uint32_t
 }
 
 struct GemmParams {
-    const uint8_t *w;  // FMT_Q4K verbatim rows or FMT_Q6KR prepared rows
-    float *y;          // [s, out]
+    float *y;  // [s, out]
     int *status;
     uint32_t out_dim, in_dim, s;
+    long long *trace; // measurement only: cycle stamps of CTA (0, 0)
+    uint32_t mode; // measurement only: bit 0 skips the dequantization, bit 1 the activation loads, bit 2 the MMAs
+};
+// x: bf16 activations [s, in], 128-byte swizzle.  w0..w2: the packed weight bytes as plain
+// 2-D byte tensors [out rows, row bytes] — Q4_K: w0 = whole 144-byte blocks; prepared
+// Q6_K: w0 = 48-byte records, w1 = the 16 scale bytes of a block, w2 = eight blocks' f16 d.
+struct GemmMaps {
+    CUtensorMap x, w0, w1, w2;
 };
 
-// ---- raw bytes one dequant thread needs for (row, 256-k block, half h) ----------
-struct RawQ4K {
-    uint4 hdr;     // d, dmin, 12 packed scale bytes
-    uint4 qs[4];   // qs[64h .. 64h+63]: chunks 2h and 2h+1
+template <int FMT> struct GemmCfg;
+template <> struct GemmCfg<FMT_Q4K> {
+    static constexpr int RAW_BYTES = GM * Q4K_BYTES; // [128 rows][144 B]: 16-byte reads one row apart hit distinct banks
+    static constexpr int RAW_STAGES = 3;
 };
-struct RawQ6KR {
-    uint4 rec[6];  // records (h, t'=0) and (h, t'=1): W1, W2, W3 each
-    uint2 sc;      // their 2 x 4 int8 scales
-    uint32_t d;    // f16 bits
+template <> struct GemmCfg<FMT_Q6KR> {
+    static constexpr int REC_BYTES = GM * 48;                  // one record of every row: [128][48 B], conflict-free as well
+    static constexpr int RAW_BYTES = 4 * REC_BYTES + 2 * GM * 16; // 4 records, [128][16 B] scales, [128][16 B] d
+    static constexpr int RAW_STAGES = 2;
 };
 
-__device__ __forceinline__ void raw_load(RawQ4K &r, const uint8_t *w, uint32_t row, uint32_t nb, uint32_t kb, uint32_t h) {
-    const uint4 *blk = (const uint4 *)(w + ((size_t)row * nb + kb) * Q4K_BYTES);
-    r.hdr = __ldg(blk);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) r.qs[i] = __ldg(blk + 1 + 4 * h + i);
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
 }
-__device__ __forceinline__ void raw_load(RawQ6KR &r, const uint8_t *w, uint32_t row, uint32_t nb, uint32_t kb, uint32_t h) {
-    const uint8_t *rw = w + (size_t)row * nb * Q6K_BYTES;
-    const uint32_t ri = kb * 4 + h * 2;
-    const uint4 *rec = (const uint4 *)(rw + (size_t)ri * 48);
-#pragma unroll
-    for (int i = 0; i < 6; ++i) r.rec[i] = __ldg(rec + i);
-    r.sc = __ldg((const uint2 *)(rw + (size_t)nb * 192 + (size_t)ri * 4));
-    r.d = __ldg((const uint16_t *)(rw + (size_t)nb * 208 + (size_t)kb * 2));
-}
-__device__ __forceinline__ void raw_zero(RawQ4K &r) {
-    r.hdr = make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) r.qs[i] = make_uint4(0, 0, 0, 0);
-}
-__device__ __forceinline__ void raw_zero(RawQ6KR &r) {
-#pragma unroll
-    for (int i = 0; i < 6; ++i) r.rec[i] = make_uint4(0, 0, 0, 0);
-    r.sc = make_uint2(0, 0), r.d = 0;
-}
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
-__device__ __forceinline__ uint32_t byte_of(const uint4 &v, int i) {
-    const uint32_t w = i < 4 ? v.x : (i < 8 ? v.y : (i < 12 ? v.z : v.w));
-    return (w >> (8 * (i & 3))) & 0xffu;
-}
+// Integer -> float without the conversion unit: a 16-bit lane holding 0x6400 | v is the
+// half-precision number 1024 + v exactly (v < 1024), so one logic op places two packed
+// integers into a half2 and one half2 subtract (exact) turns them into the values; the
+// half -> float widening is exact as well.
+__device__ __forceinline__ __half2 h2_bits(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ __half2 h2_const(float v) { return __float2half2_rn(v); }
 
-// Writes the two k-chunks (2h, 2h+1) of one row into their A tiles, values computed as
-// crates/ullm-core/src/dequant.rs:203-210 does (d*sc exact, (d*sc)*q exact, one rounding
-// at the subtraction) and then rounded once more to bf16.
-__device__ __forceinline__ void dequant_store(const RawQ4K &r, uint32_t h, uint32_t row, uint32_t tile_c0, uint32_t tile_c1) {
-    const float d = f16_bits_to_f32((uint16_t)(r.hdr.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(r.hdr.x >> 16));
+// ---- what one dequantization thread keeps of a 256-k block of its row -----------------
+// Q4_K: thread (row, q) owns qs bytes [16q, 16q+16) of each of the four 64-k chunks.
+struct BlkQ4K {
+    uint4 hdr;   // d, dmin, 12 packed scale bytes
+    uint4 qs[4];
+};
+__device__ __forceinline__ void blk_load(BlkQ4K &b, uint32_t raw, uint32_t row, uint32_t q, uint32_t) {
+    const uint32_t a = raw + row * Q4K_BYTES;
+    b.hdr = lds128(a);
 #pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-        int sA, mA, sB, mB;
-        q4k_pair(r.hdr.y, r.hdr.z, r.hdr.w, (int)(2 * h + cc), sA, mA, sB, mB);
-        const float d1 = __fmul_rn(d, (float)sA), m1 = __fmul_rn(dmin, (float)mA);
-        const float d2 = __fmul_rn(d, (float)sB), m2 = __fmul_rn(dmin, (float)mB);
-        const uint32_t tile = cc ? tile_c1 : tile_c0;
+    for (int c = 0; c < 4; ++c) b.qs[c] = lds128(a + 16 + 32 * c + 16 * q);
+}
+// Writes the thread's 32 values of chunk c (low nibbles -> k 16q.., high -> k 32+16q..),
+// computed as crates/ullm-core/src/dequant.rs:203-210 does (d*sc exact, (d*sc)*q exact,
+// one rounding at the subtraction) and then rounded once more to bf16.
+__device__ __forceinline__ void chunk_store(const BlkQ4K &b, int c, uint32_t q, uint32_t row, uint32_t tile) {
+    const float d = f16_bits_to_f32((uint16_t)(b.hdr.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(b.hdr.x >> 16));
+    const __half2 k1024 = h2_const(1024.f), k16th = h2_const(0.0625f), km64 = h2_const(-64.f);
+    int sA, mA, sB, mB;
+    q4k_pair(b.hdr.y, b.hdr.z, b.hdr.w, c, sA, mA, sB, mB);
+    const float d1 = __fmul_rn(d, (float)sA), m1 = __fmul_rn(dmin, (float)mA);
+    const float d2 = __fmul_rn(d, (float)sB), m2 = __fmul_rn(dmin, (float)mB);
+    uint32_t lo[8], hi[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { // 8 qs bytes -> 8 low-nibble and 8 high-nibble values
-            const uint4 &q = r.qs[2 * cc + (j >> 1)];
-            const uint32_t w0 = (j & 1) ? q.z : q.x, w1 = (j & 1) ? q.w : q.y;
-            float lo[8], hi[8];
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                const uint32_t byte = ((b < 4 ? w0 : w1) >> (8 * (b & 3))) & 0xffu;
-                lo[b] = __fsub_rn(__fmul_rn(d1, (float)(byte & 15u)), m1);
-                hi[b] = __fsub_rn(__fmul_rn(d2, (float)(byte >> 4)), m2);
-            }
-            st_a_sw128(tile, row, j, make_uint4(pack_bf16x2(lo[0], lo[1]), pack_bf16x2(lo[2], lo[3]), pack_bf16x2(lo[4], lo[5]), pack_bf16x2(lo[6], lo[7])));
-            st_a_sw128(tile, row, 4 + j, make_uint4(pack_bf16x2(hi[0], hi[1]), pack_bf16x2(hi[2], hi[3]), pack_bf16x2(hi[4], hi[5]), pack_bf16x2(hi[6], hi[7])));
-        }
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w = word_of(b.qs[c], i), w8 = w >> 8;
+        // bytes (0, 2) and (1, 3) of the word: low nibbles, then high nibbles (held as 16 * q)
+        const __half2 l02 = __hsub2(h2_bits((w & 0x000f000fu) | 0x64006400u), k1024);
+        const __half2 l13 = __hsub2(h2_bits((w8 & 0x000f000fu) | 0x64006400u), k1024);
+        const __half2 h02 = __hfma2(h2_bits((w & 0x00f000f0u) | 0x64006400u), k16th, km64);
+        const __half2 h13 = __hfma2(h2_bits((w8 & 0x00f000f0u) | 0x64006400u), k16th, km64);
+        lo[2 * i] = pack_bf16x2(__fsub_rn(__fmul_rn(d1, __low2float(l02)), m1), __fsub_rn(__fmul_rn(d1, __low2float(l13)), m1));
+        lo[2 * i + 1] = pack_bf16x2(__fsub_rn(__fmul_rn(d1, __high2float(l02)), m1), __fsub_rn(__fmul_rn(d1, __high2float(l13)), m1));
+        hi[2 * i] = pack_bf16x2(__fsub_rn(__fmul_rn(d2, __low2float(h02)), m2), __fsub_rn(__fmul_rn(d2, __low2float(h13)), m2));
+        hi[2 * i + 1] = pack_bf16x2(__fsub_rn(__fmul_rn(d2, __high2float(h02)), m2), __fsub_rn(__fmul_rn(d2, __high2float(h13)), m2));
     }
+    st_a_sw128(tile, row, 2 * q, make_uint4(lo[0], lo[1], lo[2], lo[3]));
+    st_a_sw128(tile, row, 2 * q + 1, make_uint4(lo[4], lo[5], lo[6], lo[7]));
+    st_a_sw128(tile, row, 4 + 2 * q, make_uint4(hi[0], hi[1], hi[2], hi[3]));
+    st_a_sw128(tile, row, 5 + 2 * q, make_uint4(hi[4], hi[5], hi[6], hi[7]));
 }
 
-// Prepared Q6_K (prepare.cu): value = (d * sc) * (q - 32), left to right as
-// dequant.rs:275-278.  Half h of the block is k-chunks 2h (groups 0, 1) and 2h+1 (2, 3).
-__device__ __forceinline__ void dequant_store(const RawQ6KR &r, uint32_t h, uint32_t row, uint32_t tile_c0, uint32_t tile_c1) {
-    const float d = f16_bits_to_f32((uint16_t)r.d);
+// Prepared Q6_K (prepare.cu): thread (row, tp) owns records (h, tp), h = 0, 1: positions
+// l = 16tp..16tp+15 of all four groups of half h.  Chunk c = 2h + gp holds groups 2gp, 2gp+1.
+struct BlkQ6KR {
+    uint4 rec[2][3]; // W1, W2, W3
+    uint32_t sc[2];  // the record's four int8 scales
+    uint32_t d;      // f16 bits
+};
+__device__ __forceinline__ void blk_load(BlkQ6KR &b, uint32_t raw, uint32_t row, uint32_t tp, uint32_t kb) {
+    constexpr uint32_t REC = GemmCfg<FMT_Q6KR>::REC_BYTES;
 #pragma unroll
-    for (int tp = 0; tp < 2; ++tp) {
-        const uint4 &W1 = r.rec[3 * tp], &W2 = r.rec[3 * tp + 1], &W3 = r.rec[3 * tp + 2];
-        const uint32_t scw = tp ? r.sc.y : r.sc.x;
-        float ds[4];
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t a = raw + (2 * h + tp) * REC + row * 48;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) ds[g] = __fmul_rn(d, (float)((int)(scw << (24 - 8 * g)) >> 24));
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) { // positions l = 16tp + 8hf .. +7
-            float v[4][8];
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                const uint32_t w1 = byte_of(W1, 8 * hf + b), w2 = byte_of(W2, 8 * hf + b), w3 = byte_of(W3, 8 * hf + b);
-                const int q0 = (int)(w1 & 0x3f), q1 = (int)((w2 & 0xf) | ((w1 >> 6) << 4));
-                const int q2 = (int)((w2 >> 4) | ((w3 >> 6) << 4)), q3 = (int)(w3 & 0x3f);
-                v[0][b] = __fmul_rn(ds[0], (float)(q0 - 32));
-                v[1][b] = __fmul_rn(ds[1], (float)(q1 - 32));
-                v[2][b] = __fmul_rn(ds[2], (float)(q2 - 32));
-                v[3][b] = __fmul_rn(ds[3], (float)(q3 - 32));
-            }
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const uint32_t tile = g < 2 ? tile_c0 : tile_c1;
-                const uint32_t c16 = 4 * (g & 1) + 2 * tp + hf;
-                st_a_sw128(tile, row, c16, make_uint4(pack_bf16x2(v[g][0], v[g][1]), pack_bf16x2(v[g][2], v[g][3]), pack_bf16x2(v[g][4], v[g][5]), pack_bf16x2(v[g][6], v[g][7])));
-            }
-        }
+        for (int k = 0; k < 3; ++k) b.rec[h][k] = lds128(a + 16 * k);
+        b.sc[h] = lds32(raw + 4 * REC + row * 16 + (2 * h + tp) * 4);
     }
+    b.d = lds_u16(raw + 4 * REC + GM * 16 + row * 16 + (kb & 7u) * 2);
+}
+// value = (d * sc) * (q - 32), left to right as dequant.rs:275-278, then rounded to bf16
+__device__ __forceinline__ void chunk_store(const BlkQ6KR &b, int c, uint32_t tp, uint32_t row, uint32_t tile) {
+    const int h = c >> 1, gp = c & 1;
+    const float d = f16_bits_to_f32((uint16_t)b.d);
+    const __half2 k1056 = h2_const(1056.f); // 1024 + the format's offset of 32
+    const uint32_t scw = b.sc[h];
+    const float dsA = __fmul_rn(d, (float)((int)(scw << (24 - 16 * gp)) >> 24));
+    const float dsB = __fmul_rn(d, (float)((int)(scw << (16 - 16 * gp)) >> 24));
+    uint32_t oA[8], oB[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w1 = word_of(b.rec[h][0], i), w2 = word_of(b.rec[h][1], i), w3 = word_of(b.rec[h][2], i);
+        // four 6-bit values per word, one per byte, for the chunk's two groups
+        const uint32_t qa = gp ? (((w2 >> 4) & 0x0f0f0f0fu) | ((w3 >> 2) & 0x30303030u)) : (w1 & 0x3f3f3f3fu);
+        const uint32_t qb = gp ? (w3 & 0x3f3f3f3fu) : ((w2 & 0x0f0f0f0fu) | ((w1 >> 2) & 0x30303030u));
+        const __half2 a02 = __hsub2(h2_bits((qa & 0x00ff00ffu) | 0x64006400u), k1056);
+        const __half2 a13 = __hsub2(h2_bits(((qa >> 8) & 0x00ff00ffu) | 0x64006400u), k1056);
+        const __half2 b02 = __hsub2(h2_bits((qb & 0x00ff00ffu) | 0x64006400u), k1056);
+        const __half2 b13 = __hsub2(h2_bits(((qb >> 8) & 0x00ff00ffu) | 0x64006400u), k1056);
+        oA[2 * i] = pack_bf16x2(__fmul_rn(dsA, __low2float(a02)), __fmul_rn(dsA, __low2float(a13)));
+        oA[2 * i + 1] = pack_bf16x2(__fmul_rn(dsA, __high2float(a02)), __fmul_rn(dsA, __high2float(a13)));
+        oB[2 * i] = pack_bf16x2(__fmul_rn(dsB, __low2float(b02)), __fmul_rn(dsB, __low2float(b13)));
+        oB[2 * i + 1] = pack_bf16x2(__fmul_rn(dsB, __high2float(b02)), __fmul_rn(dsB, __high2float(b13)));
+    }
+    st_a_sw128(tile, row, 2 * tp, make_uint4(oA[0], oA[1], oA[2], oA[3]));
+    st_a_sw128(tile, row, 2 * tp + 1, make_uint4(oA[4], oA[5], oA[6], oA[7]));
+    st_a_sw128(tile, row, 4 + 2 * tp, make_uint4(oB[0], oB[1], oB[2], oB[3]));
+    st_a_sw128(tile, row, 5 + 2 * tp, make_uint4(oB[4], oB[5], oB[6], oB[7]));
 }
 
-template <int FMT> struct RawOf;
-template <> struct RawOf<FMT_Q4K> { using type = RawQ4K; };
-template <> struct RawOf<FMT_Q6KR> { using type = RawQ6KR; };
+// A whole warp waits on an mbarrier with one polling lane: 256 threads spinning on
+// try_wait crowd the shared-memory pipe the MMA-issuing thread's own waits go through.
+// Every lane then observes the completed phase itself (one try_wait that succeeds at
+// once), which orders its following accesses after the barrier.
+__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32_t lane) {
+    int ok = 1;
+    if (lane == 0) ok = wait_or_timeout(bar, parity) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) (void)mbar_try_wait(bar, parity);
+    return ok != 0;
+}
 
-// grid (ceil(out / 128), ceil(s / 256)), 320 threads, dynamic smem: 4 x (16 KB A + 32 KB B)
+template <int FMT> struct BlkOf;
+template <> struct BlkOf<FMT_Q4K> { using type = BlkQ4K; };
+template <> struct BlkOf<FMT_Q6KR> { using type = BlkQ6KR; };
+
+// grid (ceil(out / 128), ceil(s / 256)), 352 threads
 template <int FMT>
-__global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
-    using Raw = typename RawOf<FMT>::type;
+__global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
+    using Cfg = GemmCfg<FMT>;
+    using Blk = typename BlkOf<FMT>::type;
+    constexpr int RS = Cfg::RAW_STAGES;
     extern __shared__ __align__(1024) uint8_t gsm[];
     // dynamic smem is only guaranteed 16-byte aligned: round up to the 1024 B the swizzle atoms need
     uint8_t *base = (uint8_t *)(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
-    uint8_t *a_tiles = base;                       // G_SLOTS x 16 KB
-    uint8_t *b_tiles = base + G_SLOTS * G_A_BYTES; // G_SLOTS x 32 KB
-    __shared__ uint64_t a_full[G_SLOTS], b_full[G_SLOTS], slot_free[G_SLOTS], acc_full;
+    uint8_t *a_tiles = base;                                 // G_STAGES x 16 KB
+    uint8_t *b_tiles = base + G_STAGES * G_A_BYTES;          // G_STAGES x 32 KB
+    uint8_t *raw = b_tiles + G_STAGES * G_B_BYTES;           // RS x packed bytes of [128 rows x 256 k]
+    // full: 256 dequantization threads + the TMA thread's expect_tx arrival; free: one tcgen05.commit
+    __shared__ uint64_t full[G_STAGES], freeb[G_STAGES], raw_full[RS], raw_free[RS], acc_full;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_s;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t m0 = blockIdx.x * GM, n0 = blockIdx.y * GN;
     const uint32_t nb = p.in_dim / QK_K, nchunks = nb * 4;
 
     if (tid == 0) {
-        for (int i = 0; i < G_SLOTS; ++i) {
-            mbar_init(&a_full[i], 128); // the 128 threads that own this chunk's half
-            mbar_init(&b_full[i], 1);
-            mbar_init(&slot_free[i], 1);
+        for (int i = 0; i < G_STAGES; ++i) {
+            mbar_init(&full[i], G_DEQ_THREADS + 1);
+            mbar_init(&freeb[i], 1);
+        }
+        for (int i = 0; i < RS; ++i) {
+            mbar_init(&raw_full[i], 1);
+            mbar_init(&raw_free[i], G_DEQ_THREADS);
         }
         mbar_init(&acc_full, 1);
-        abort_s = 0;
         mbar_fence_init();
     }
     if (warp == 1) { // TMEM: 256 columns of 128 lanes x 32 bit
@@ -231,64 +270,98 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParam
         // ---- TMA producer: activation tile of every k-chunk ----
         if (lane == 0) {
             for (uint32_t g = 0; g < nchunks; ++g) {
-                const uint32_t c = g % G_SLOTS;
-                if (g >= G_SLOTS && !wait_or_timeout(&slot_free[c], ((g / G_SLOTS) - 1) & 1)) {
-                    abort_s = 1;
+                const uint32_t c = g % G_STAGES;
+                if (g >= G_STAGES && !wait_or_timeout(&freeb[c], ((g / G_STAGES) - 1) & 1)) {
                     *(volatile int *)p.status = DEV_TIMEOUT;
                     break;
                 }
-                mbar_arrive_expect_tx(&b_full[c], G_B_BYTES);
-                tma_load_2d(b_tiles + c * G_B_BYTES, &xmap, (int)(g * GKC), (int)n0, &b_full[c]);
+                if (p.mode & 2u) {
+                    mbar_arrive(&full[c]);
+                    continue;
+                }
+                mbar_arrive_expect_tx(&full[c], G_B_BYTES);
+                tma_load_2d(b_tiles + c * G_B_BYTES, &maps.x, (int)(g * GKC), (int)n0, &full[c]);
+            }
+        }
+    } else if (warp == G_RAW_WARP) {
+        // ---- TMA producer: packed weight bytes of every 256-k block (rows past the matrix read as zero) ----
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < nb; ++kb) {
+                const uint32_t st = kb % RS;
+                if (kb >= RS && !wait_or_timeout(&raw_free[st], ((kb / RS) - 1) & 1)) {
+                    *(volatile int *)p.status = DEV_TIMEOUT;
+                    break;
+                }
+                uint8_t *dst = raw + st * Cfg::RAW_BYTES;
+                mbar_arrive_expect_tx(&raw_full[st], Cfg::RAW_BYTES);
+                if constexpr (FMT == FMT_Q4K) {
+                    tma_load_2d(dst, &maps.w0, (int)(kb * Q4K_BYTES), (int)m0, &raw_full[st]);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        tma_load_2d(dst + r * Cfg::REC_BYTES, &maps.w0, (int)((kb * 4 + r) * 48), (int)m0, &raw_full[st]);
+                    tma_load_2d(dst + 4 * Cfg::REC_BYTES, &maps.w1, (int)(kb * 16), (int)m0, &raw_full[st]);
+                    tma_load_2d(dst + 4 * Cfg::REC_BYTES + GM * 16, &maps.w2, (int)((kb >> 3) * 16), (int)m0, &raw_full[st]);
+                }
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
+        // The issuing thread blocks while the tensor pipe's short queue is full, so whatever
+        // it does between two chunks is time the pipe can run dry: it waits for the NEXT
+        // chunk's operands before issuing the current chunk's MMAs (they are ready long
+        // before in steady state, and depend only on MMAs issued earlier), and each chunk
+        // costs one wait and one commit.
         if (lane == 0) {
             const uint32_t idesc = umma_idesc();
-            bool ok = true;
+            bool ok = wait_or_timeout(&full[0], 0);
             for (uint32_t g = 0; g < nchunks && ok; ++g) {
-                const uint32_t c = g % G_SLOTS, par = (g / G_SLOTS) & 1;
-                ok = wait_or_timeout(&a_full[c], par) && wait_or_timeout(&b_full[c], par);
+                const uint32_t c = g % G_STAGES;
+                const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && g < 1024;
+                if (tr) p.trace[4 * g] = clock64();
+                if (g + 1 < nchunks) ok = wait_or_timeout(&full[(g + 1) % G_STAGES], ((g + 1) / G_STAGES) & 1);
+                if (tr) p.trace[4 * g + 1] = clock64();
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t ad = umma_desc_sw128(smem_u32(a_tiles + c * G_A_BYTES));
                 const uint64_t bd = umma_desc_sw128(smem_u32(b_tiles + c * G_B_BYTES));
 #pragma unroll
                 for (uint32_t k = 0; k < GKC / 16; ++k) // K = 16 per instruction: 32 bytes along the swizzle row
-                    umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, (g | k) != 0);
-                umma_commit(&slot_free[c]); // operands of this slot may be overwritten once these MMAs are done
+                    if (!(p.mode & 4u)) umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, (g | k) != 0);
+                umma_commit(&freeb[c]); // this stage may be overwritten once these MMAs are done
+                if (tr) p.trace[4 * g + 3] = clock64();
             }
             if (ok) umma_commit(&acc_full);
-            else {
-                abort_s = 1;
-                *(volatile int *)p.status = DEV_TIMEOUT;
-            }
+            else *(volatile int *)p.status = DEV_TIMEOUT;
         }
     } else {
-        // ---- dequantization: thread = (row, half of each 256-k block) ----
-        const uint32_t dt = tid - 64, row = dt & 127, h = dt >> 7;
-        const bool in_range = m0 + row < p.out_dim;
-        Raw cur, nxt;
-        if (in_range) raw_load(cur, p.w, m0 + row, nb, 0, h);
-        else raw_zero(cur);
+        // ---- dequantization: all 256 threads work on one 64-k chunk at a time ----
+        const uint32_t dt = tid - 64, row = dt & 127, part = dt >> 7;
         bool ok = true;
         for (uint32_t kb = 0; kb < nb && ok; ++kb) {
-            if (kb + 1 < nb && in_range) raw_load(nxt, p.w, m0 + row, nb, kb + 1, h); // overlaps the math below
-            const uint32_t c0 = 2 * h, c1 = 2 * h + 1;
-            if (kb >= 1) ok = wait_or_timeout(&slot_free[c0], (kb - 1) & 1) && wait_or_timeout(&slot_free[c1], (kb - 1) & 1);
+            const uint32_t st = kb % RS;
+            ok = warp_wait(&raw_full[st], (kb / RS) & 1, lane);
             if (!ok) break;
-            dequant_store(cur, h, row, smem_u32(a_tiles + c0 * G_A_BYTES), smem_u32(a_tiles + c1 * G_A_BYTES));
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the MMA
-            mbar_arrive(&a_full[c0]);
-            mbar_arrive(&a_full[c1]);
-            if (in_range) cur = nxt;
+            Blk blk;
+            blk_load(blk, smem_u32(raw + st * Cfg::RAW_BYTES), row, part, kb);
+            mbar_arrive(&raw_free[st]); // the block's bytes are in registers: its stage can be refilled
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t g = 4 * kb + c, ca = g % G_STAGES;
+                const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && g < 1024 && dt == 0;
+                if (tr) p.trace[4096 + 4 * g] = clock64();
+                if (g >= G_STAGES) ok = ok && warp_wait(&freeb[ca], ((g / G_STAGES) - 1) & 1, lane);
+                if (tr) p.trace[4096 + 4 * g + 1] = clock64();
+                if (!ok) break;
+                if (!(p.mode & 1u)) chunk_store(blk, c, part, row, smem_u32(a_tiles + ca * G_A_BYTES));
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the MMA
+                mbar_arrive(&full[ca]);
+                if (tr) p.trace[4096 + 4 * g + 2] = clock64();
+            }
         }
-        if (!ok) {
-            abort_s = 1;
-            *(volatile int *)p.status = DEV_TIMEOUT;
-        }
+        if (!ok) *(volatile int *)p.status = DEV_TIMEOUT;
         // ---- epilogue: TMEM -> registers -> Y[token, row] ----
-        if (ok && wait_or_timeout(&acc_full, 0)) {
+        if (ok && warp_wait(&acc_full, 0, lane)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t q = warp & 3, colh = (warp - 2) >> 2; // TMEM lane quarter of this warp, column half
             const uint32_t orow = m0 + q * 32 + lane;
@@ -314,7 +387,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParam
                 }
             }
         } else if (ok) {
-            abort_s = 1;
             *(volatile int *)p.status = DEV_TIMEOUT;
         }
     }
@@ -355,54 +427,70 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// 2-D row-major tensor [rows, inner elements], box [box_rows, box_inner]
+static bool encode_2d(EncodeTiledFn enc, CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t rows,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw) {
+    const cuuint64_t gdim[2] = {inner, rows};
+    const cuuint64_t gstride[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows}, estr[2] = {1, 1};
+    return enc(map, dt, 2, const_cast<void *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static uint32_t g_gemm_mode = 0;
+static long long *g_gemm_trace = nullptr;
+void gemm_set_trace(void *d_buf) { g_gemm_trace = (long long *)d_buf; }
+void gemm_set_debug_mode(int mode) { g_gemm_mode = (uint32_t)mode; }
+
 bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s) {
     if (fmt != FMT_Q4K && fmt != FMT_Q6KR) return false;
     if (in_dim % QK_K || in_dim < QK_K || out_dim == 0 || s == 0) return false;
     if (fmt == FMT_Q6KR && in_dim % 2048) return false;
-    return in_dim <= (1u << 30) && out_dim <= (1u << 30) && s <= (1u << 30);
+    return in_dim <= (1u << 24) && out_dim <= (1u << 30) && s <= (1u << 30);
 }
 
 size_t gemm_tc_scratch_bytes(size_t in_dim, size_t s) { return s * in_dim * 2; }
 
-// d_w: FMT_Q4K verbatim rows or FMT_Q6KR prepared rows.  d_x f32 [s, in], d_y f32 [s, out],
-// d_xb16: scratch of gemm_tc_scratch_bytes (256-byte aligned).
+template <int FMT> static cudaError_t launch_one(const GemmParams &p, const GemmMaps &maps, dim3 grid, cudaStream_t st) {
+    using Cfg = GemmCfg<FMT>;
+    const size_t smem = (size_t)G_STAGES * (G_A_BYTES + G_B_BYTES) + (size_t)Cfg::RAW_STAGES * Cfg::RAW_BYTES + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    gemm_q_tc_kernel<FMT><<<grid, G_THREADS, smem, st>>>(p, maps);
+    return cudaGetLastError();
+}
+
+// d_w: FMT_Q4K verbatim rows or FMT_Q6KR prepared rows (16-byte aligned).  d_x f32 [s, in],
+// d_y f32 [s, out], d_xb16: scratch of gemm_tc_scratch_bytes (256-byte aligned).
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_xb16, size_t out_dim, size_t in_dim,
                            size_t s, int *d_status, cudaStream_t st) {
-    if (!gemm_tc_supported(fmt, out_dim, in_dim, s)) return cudaErrorNotSupported;
+    if (!gemm_tc_supported(fmt, out_dim, in_dim, s) || ((uintptr_t)d_w & 15)) return cudaErrorNotSupported;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
-    const size_t n = s * in_dim;
+    const size_t n = s * in_dim, nb = in_dim / QK_K;
     cast_bf16_kernel<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, st>>>(d_x, (__nv_bfloat16 *)d_xb16, n);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    CUtensorMap map;
-    const cuuint64_t gdim[2] = {(cuuint64_t)in_dim, (cuuint64_t)s};
-    const cuuint64_t gstride[1] = {(cuuint64_t)in_dim * 2};
-    const cuuint32_t box[2] = {GKC, GN}, estr[2] = {1, 1};
-    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d_xb16, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
-    GemmParams p;
-    p.w = (const uint8_t *)d_w, p.y = d_y, p.status = d_status;
-    p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
-    const dim3 grid((unsigned)((out_dim + GM - 1) / GM), (unsigned)((s + GN - 1) / GN));
-    const size_t smem = (size_t)G_SLOTS * (G_A_BYTES + G_B_BYTES) + 1024;
+    GemmMaps maps;
+    bool ok = encode_2d(enc, &maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_xb16, in_dim, s, in_dim * 2, GKC, GN, CU_TENSOR_MAP_SWIZZLE_128B);
+    const uint8_t *w = (const uint8_t *)d_w;
     if (fmt == FMT_Q4K) {
-        static bool set = false;
-        if (!set) {
-            if ((e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-            set = true;
-        }
-        gemm_q_tc_kernel<FMT_Q4K><<<grid, G_THREADS, smem, st>>>(p, map);
+        const size_t rb = nb * Q4K_BYTES;
+        ok = ok && encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, rb, out_dim, rb, Q4K_BYTES, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
+        maps.w1 = maps.w0, maps.w2 = maps.w0;
     } else {
-        static bool set = false;
-        if (!set) {
-            if ((e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT_Q6KR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-            set = true;
-        }
-        gemm_q_tc_kernel<FMT_Q6KR><<<grid, G_THREADS, smem, st>>>(p, map);
+        const size_t rb = nb * Q6K_BYTES; // prepared rows: records | scales | d planes
+        ok = ok && encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, nb * 192, out_dim, rb, 48, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
+        ok = ok && encode_2d(enc, &maps.w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, w + nb * 192, nb * 16, out_dim, rb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
+        ok = ok && encode_2d(enc, &maps.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, w + nb * 208, nb * 2, out_dim, rb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
-    return cudaGetLastError();
+    if (!ok) return cudaErrorInvalidValue;
+    GemmParams p;
+    p.y = d_y, p.status = d_status;
+    p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
+    p.mode = g_gemm_mode, p.trace = g_gemm_trace;
+    const dim3 grid((unsigned)((out_dim + GM - 1) / GM), (unsigned)((s + GN - 1) / GN));
+    return fmt == FMT_Q4K ? launch_one<FMT_Q4K>(p, maps, grid, st) : launch_one<FMT_Q6KR>(p, maps, grid, st);
 }
 
 } // namespace ullm

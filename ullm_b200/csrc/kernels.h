@@ -69,6 +69,8 @@ void matvec_set_ctas_per_sm(int v);
 bool q6k_can_prepare(size_t in_dim);
 cudaError_t launch_q6k_prepare(const void *d_src, void *d_dst, size_t rows, size_t in_dim, bool inverse, cudaStream_t st);
 // gemm.cu — tcgen05 / TMEM prefill GEMM on Q4_K (verbatim) or prepared Q6_K rows.
+void gemm_set_trace(void *d_buf); // >= 8192 int64: cycle stamps of CTA (0, 0)'s MMA and dequantization loops
+void gemm_set_debug_mode(int mode); // measurement only: stages of the GEMM kernel switched off
 bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s);
 size_t gemm_tc_scratch_bytes(size_t in_dim, size_t s);
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_xb16, size_t out_dim, size_t in_dim,

@@ -415,6 +415,7 @@ template <int N> __device__ __forceinline__ float warp_reduce_rows(float (&v)[N]
 }
 
 __device__ __forceinline__ bool wait_or_timeout(uint64_t *bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true; // already complete: no timer needed
     // ~2^31 cycles (about a second) of polling before giving up
     long long t0 = clock64();
     for (;;) {
