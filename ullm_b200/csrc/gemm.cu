@@ -28,14 +28,15 @@
 
 namespace ullm {
 
-constexpr int GM = 128;  // weight rows per CTA (MMA M)
-constexpr int GN = 256;  // tokens per CTA (MMA N, TMEM columns)
-constexpr int GKC = 64;  // k per chunk: 64 bf16 = one 128-byte swizzle row
-constexpr int G_STAGES = 3;  // operand stages in flight: one dequantized weight chunk + one activation chunk each
-constexpr int G_A_BYTES = GM * GKC * 2;  // 16 KB
-constexpr int G_B_BYTES = GN * GKC * 2;  // 32 KB
+constexpr int GM = 128;   // weight rows per CTA; a CTA pair covers 256 (MMA M)
+constexpr int GN = 256;   // tokens per CTA pair (MMA N, TMEM columns); each CTA stages 128 of them
+constexpr int GNH = GN / 2;
+constexpr int GKC = 64;   // k per chunk: 64 bf16 = one 128-byte swizzle row
+constexpr int G_STAGES = 5;  // operand stages in flight: one dequantized weight chunk + one activation chunk each
+constexpr int G_A_BYTES = GM * GKC * 2;   // 16 KB
+constexpr int G_B_BYTES = GNH * GKC * 2;  // 16 KB
 constexpr int G_THREADS = 352;
-constexpr int G_DEQ_THREADS = 256;
+constexpr int G_DEQ_WARPS = 8;
 constexpr int G_RAW_WARP = 10;
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B apart
@@ -48,24 +49,76 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
     return d;
 }
-// instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = 256
+// instruction descriptor: D f32, A/B bf16, both K-major, M = 256 (two CTAs x 128), N = 256
 __host__ __device__ constexpr uint32_t umma_idesc() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GN >> 3) << 17) | ((uint32_t)(GM >> 4) << 24);
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GN >> 3) << 17) | ((uint32_t)((2 * GM) >> 4) << 24);
 }
 
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+// shared::cluster address of `local` (an address in this CTA's shared window) inside CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on an mbarrier of any CTA of the cluster (address from mapa_u32)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// bounded like wait_or_timeout, observing arrivals made by the peer CTA
+__device__ __forceinline__ bool wait_cluster_or_timeout(uint64_t *bar, uint32_t parity) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (clock64() - t0 > (1ll << 31)) return false;
+    }
+}
+
+// Tiled TMA load into this CTA's own shared memory, completion counted on an mbarrier
+// given by its shared::cluster address (this CTA's or the pair leader's).
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                      smem_u32(smem_dst)),
-                 "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
                  : "memory");
 }
+// One MMA over the CTA pair: D[256 x 256] (+)= A[256 x 16] * B[256 x 16]^T, each CTA supplying
+// its 128 rows of A and its 128 of B's tokens from the same shared-memory offsets, and
+// holding its 128 rows of D in its own tensor memory.
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
                  "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+// the same with D always accumulated (no predicate to set up)
+__device__ __forceinline__ void umma_bf16_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d), "l"(adesc),
+                 "l"(bdesc), "r"(idesc)
+                 : "memory");
+}
+// Arrives (once the MMAs issued so far are complete) on the mbarrier at the same offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+                 "h"((uint16_t)3)
+                 : "memory");
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
@@ -75,7 +128,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // 16 bytes of row `row`, 16-byte column `c16` (0..7) of a [rows x 128 B] tile with the
 // 128-byte swizzle: the column index is XORed with the row index modulo 8.
 __device__ __forceinline__ void st_a_sw128(uint32_t tile, uint32_t row, uint32_t c16, uint4 v) {
-    const uint32_t addr = tile + row * 128u + ((c16 ^ (row & 7u)) << 4);
+    const uint32_t addr = tile + row * 128u + ((c16 << 4) ^ ((row & 7u) << 4));
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
@@ -130,16 +183,17 @@ __device__ __forceinline__ void blk_load(BlkQ4K &b, uint32_t raw, uint32_t row, 
 #pragma unroll
     for (int c = 0; c < 4; ++c) b.qs[c] = lds128(a + 16 + 32 * c + 16 * q);
 }
-// Writes the thread's 32 values of chunk c (low nibbles -> k 16q.., high -> k 32+16q..),
-// computed as crates/ullm-core/src/dequant.rs:203-210 does (d*sc exact, (d*sc)*q exact,
-// one rounding at the subtraction) and then rounded once more to bf16.
+// Writes the thread's 32 values of chunk c (low nibbles -> k 16q.., high -> k 32+16q..):
+// d*sc and dmin*m as crates/ullm-core/src/dequant.rs:203-210 forms them, then
+// (d*sc)*q - dmin*m — the product is exact in f32 (q < 16), so the fused multiply-subtract
+// rounds exactly where the reference's subtraction does — and one more rounding to bf16.
 __device__ __forceinline__ void chunk_store(const BlkQ4K &b, int c, uint32_t q, uint32_t row, uint32_t tile) {
     const float d = f16_bits_to_f32((uint16_t)(b.hdr.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(b.hdr.x >> 16));
     const __half2 k1024 = h2_const(1024.f), k16th = h2_const(0.0625f), km64 = h2_const(-64.f);
     int sA, mA, sB, mB;
     q4k_pair(b.hdr.y, b.hdr.z, b.hdr.w, c, sA, mA, sB, mB);
-    const float d1 = __fmul_rn(d, (float)sA), m1 = __fmul_rn(dmin, (float)mA);
-    const float d2 = __fmul_rn(d, (float)sB), m2 = __fmul_rn(dmin, (float)mB);
+    const float d1 = __fmul_rn(d, (float)sA), nm1 = -__fmul_rn(dmin, (float)mA);
+    const float d2 = __fmul_rn(d, (float)sB), nm2 = -__fmul_rn(dmin, (float)mB);
     uint32_t lo[8], hi[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -149,10 +203,10 @@ __device__ __forceinline__ void chunk_store(const BlkQ4K &b, int c, uint32_t q, 
         const __half2 l13 = __hsub2(h2_bits((w8 & 0x000f000fu) | 0x64006400u), k1024);
         const __half2 h02 = __hfma2(h2_bits((w & 0x00f000f0u) | 0x64006400u), k16th, km64);
         const __half2 h13 = __hfma2(h2_bits((w8 & 0x00f000f0u) | 0x64006400u), k16th, km64);
-        lo[2 * i] = pack_bf16x2(__fsub_rn(__fmul_rn(d1, __low2float(l02)), m1), __fsub_rn(__fmul_rn(d1, __low2float(l13)), m1));
-        lo[2 * i + 1] = pack_bf16x2(__fsub_rn(__fmul_rn(d1, __high2float(l02)), m1), __fsub_rn(__fmul_rn(d1, __high2float(l13)), m1));
-        hi[2 * i] = pack_bf16x2(__fsub_rn(__fmul_rn(d2, __low2float(h02)), m2), __fsub_rn(__fmul_rn(d2, __low2float(h13)), m2));
-        hi[2 * i + 1] = pack_bf16x2(__fsub_rn(__fmul_rn(d2, __high2float(h02)), m2), __fsub_rn(__fmul_rn(d2, __high2float(h13)), m2));
+        lo[2 * i] = pack_bf16x2(__fmaf_rn(d1, __low2float(l02), nm1), __fmaf_rn(d1, __low2float(l13), nm1));
+        lo[2 * i + 1] = pack_bf16x2(__fmaf_rn(d1, __high2float(l02), nm1), __fmaf_rn(d1, __high2float(l13), nm1));
+        hi[2 * i] = pack_bf16x2(__fmaf_rn(d2, __low2float(h02), nm2), __fmaf_rn(d2, __low2float(h13), nm2));
+        hi[2 * i + 1] = pack_bf16x2(__fmaf_rn(d2, __high2float(h02), nm2), __fmaf_rn(d2, __high2float(h13), nm2));
     }
     st_a_sw128(tile, row, 2 * q, make_uint4(lo[0], lo[1], lo[2], lo[3]));
     st_a_sw128(tile, row, 2 * q + 1, make_uint4(lo[4], lo[5], lo[6], lo[7]));
@@ -208,13 +262,34 @@ __device__ __forceinline__ void chunk_store(const BlkQ6KR &b, int c, uint32_t tp
     st_a_sw128(tile, row, 5 + 2 * tp, make_uint4(oB[4], oB[5], oB[6], oB[7]));
 }
 
+// try_wait that may suspend the thread in hardware for up to `ns` while the phase is
+// incomplete (it still wakes when the phase completes), so a waiting thread does not fill
+// issue slots with polls.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool wait_sleepy_or_timeout(uint64_t *bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+        if (clock64() - t0 > (1ll << 31)) return false; // about a second
+    }
+}
 // A whole warp waits on an mbarrier with one polling lane: 256 threads spinning on
 // try_wait crowd the shared-memory pipe the MMA-issuing thread's own waits go through.
 // Every lane then observes the completed phase itself (one try_wait that succeeds at
 // once), which orders its following accesses after the barrier.
 __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32_t lane) {
     int ok = 1;
-    if (lane == 0) ok = wait_or_timeout(bar, parity) ? 1 : 0;
+    if (lane == 0) ok = wait_sleepy_or_timeout(bar, parity) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (ok) (void)mbar_try_wait(bar, parity);
     return ok != 0;
@@ -224,63 +299,71 @@ template <int FMT> struct BlkOf;
 template <> struct BlkOf<FMT_Q4K> { using type = BlkQ4K; };
 template <> struct BlkOf<FMT_Q6KR> { using type = BlkQ6KR; };
 
-// grid (ceil(out / 128), ceil(s / 256)), 352 threads
-template <int FMT>
-__global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
+// grid (2 * ceil(out / 256), ceil(s / 256)) in clusters of 2 along x, 352 threads
+template <int FMT, bool DBG>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
+    gemm_q_tc_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
     using Cfg = GemmCfg<FMT>;
     using Blk = typename BlkOf<FMT>::type;
     constexpr int RS = Cfg::RAW_STAGES;
     extern __shared__ __align__(1024) uint8_t gsm[];
     // dynamic smem is only guaranteed 16-byte aligned: round up to the 1024 B the swizzle atoms need
+    // (the same amount in both CTAs of the pair, so operand offsets agree)
     uint8_t *base = (uint8_t *)(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
-    uint8_t *a_tiles = base;                                 // G_STAGES x 16 KB
-    uint8_t *b_tiles = base + G_STAGES * G_A_BYTES;          // G_STAGES x 32 KB
+    uint8_t *a_tiles = base;                                 // G_STAGES x 16 KB: this CTA's 128 rows
+    uint8_t *b_tiles = base + G_STAGES * G_A_BYTES;          // G_STAGES x 16 KB: this CTA's 128 tokens
     uint8_t *raw = b_tiles + G_STAGES * G_B_BYTES;           // RS x packed bytes of [128 rows x 256 k]
-    // full: 256 dequantization threads + the TMA thread's expect_tx arrival; free: one tcgen05.commit
+    // full (used in the leader only): 16 dequantization warps of the pair + the leader's expect_tx arrival;
+    // freeb / acc_full: one multicast tcgen05.commit each
     __shared__ uint64_t full[G_STAGES], freeb[G_STAGES], raw_full[RS], raw_free[RS], acc_full;
     __shared__ uint32_t tmem_base_s;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();
     const uint32_t m0 = blockIdx.x * GM, n0 = blockIdx.y * GN;
     const uint32_t nb = p.in_dim / QK_K, nchunks = nb * 4;
+    const bool traced = DBG && p.trace && blockIdx.x == 0 && blockIdx.y == 0;
+    const uint32_t mode = DBG ? p.mode : 0u; // stages switched off for measurement
 
     if (tid == 0) {
         for (int i = 0; i < G_STAGES; ++i) {
-            mbar_init(&full[i], G_DEQ_THREADS + 1);
+            mbar_init(&full[i], 2 * G_DEQ_WARPS + 1);
             mbar_init(&freeb[i], 1);
         }
         for (int i = 0; i < RS; ++i) {
             mbar_init(&raw_full[i], 1);
-            mbar_init(&raw_free[i], G_DEQ_THREADS);
+            mbar_init(&raw_free[i], G_DEQ_WARPS);
         }
         mbar_init(&acc_full, 1);
         mbar_fence_init();
     }
-    if (warp == 1) { // TMEM: 256 columns of 128 lanes x 32 bit
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)GN)
+    if (warp == 1) { // tensor memory: 256 columns of 128 lanes x 32 bit in each CTA of the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)GN)
                      : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    cluster_sync_all(); // the peer's barriers exist before anything signals them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = tmem_base_s;
 
     if (warp == 0) {
-        // ---- TMA producer: activation tile of every k-chunk ----
+        // ---- TMA producer: this CTA's half of the activation tile of every k-chunk ----
         if (lane == 0) {
             for (uint32_t g = 0; g < nchunks; ++g) {
                 const uint32_t c = g % G_STAGES;
-                if (g >= G_STAGES && !wait_or_timeout(&freeb[c], ((g / G_STAGES) - 1) & 1)) {
+                if (g >= G_STAGES && !(mode & 16u) && !wait_sleepy_or_timeout(&freeb[c], ((g / G_STAGES) - 1) & 1)) {
                     *(volatile int *)p.status = DEV_TIMEOUT;
                     break;
                 }
-                if (p.mode & 2u) {
-                    mbar_arrive(&full[c]);
+                const uint32_t lead_full = mapa_u32(smem_u32(&full[c]), 0);
+                if (mode & 2u) {
+                    if (rank == 0) mbar_arrive(&full[c]);
                     continue;
                 }
-                mbar_arrive_expect_tx(&full[c], G_B_BYTES);
-                tma_load_2d(b_tiles + c * G_B_BYTES, &maps.x, (int)(g * GKC), (int)n0, &full[c]);
+                if (rank == 0) mbar_arrive_expect_tx(&full[c], 2 * G_B_BYTES); // both halves land on the leader's barrier
+                tma_load_2d(b_tiles + c * G_B_BYTES, &maps.x, (int)(g * GKC), (int)(n0 + rank * GNH), lead_full);
             }
         }
     } else if (warp == G_RAW_WARP) {
@@ -288,50 +371,87 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParam
         if (lane == 0) {
             for (uint32_t kb = 0; kb < nb; ++kb) {
                 const uint32_t st = kb % RS;
-                if (kb >= RS && !wait_or_timeout(&raw_free[st], ((kb / RS) - 1) & 1)) {
+                if (kb >= RS && !wait_sleepy_or_timeout(&raw_free[st], ((kb / RS) - 1) & 1)) {
                     *(volatile int *)p.status = DEV_TIMEOUT;
                     break;
                 }
                 uint8_t *dst = raw + st * Cfg::RAW_BYTES;
+                const uint32_t bar = smem_u32(&raw_full[st]);
                 mbar_arrive_expect_tx(&raw_full[st], Cfg::RAW_BYTES);
                 if constexpr (FMT == FMT_Q4K) {
-                    tma_load_2d(dst, &maps.w0, (int)(kb * Q4K_BYTES), (int)m0, &raw_full[st]);
+                    tma_load_2d(dst, &maps.w0, (int)(kb * Q4K_BYTES), (int)m0, bar);
                 } else {
 #pragma unroll
-                    for (int r = 0; r < 4; ++r)
-                        tma_load_2d(dst + r * Cfg::REC_BYTES, &maps.w0, (int)((kb * 4 + r) * 48), (int)m0, &raw_full[st]);
-                    tma_load_2d(dst + 4 * Cfg::REC_BYTES, &maps.w1, (int)(kb * 16), (int)m0, &raw_full[st]);
-                    tma_load_2d(dst + 4 * Cfg::REC_BYTES + GM * 16, &maps.w2, (int)((kb >> 3) * 16), (int)m0, &raw_full[st]);
+                    for (int r = 0; r < 4; ++r) tma_load_2d(dst + r * Cfg::REC_BYTES, &maps.w0, (int)((kb * 4 + r) * 48), (int)m0, bar);
+                    tma_load_2d(dst + 4 * Cfg::REC_BYTES, &maps.w1, (int)(kb * 16), (int)m0, bar);
+                    tma_load_2d(dst + 4 * Cfg::REC_BYTES + GM * 16, &maps.w2, (int)((kb >> 3) * 16), (int)m0, bar);
                 }
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issuer ----
-        // The issuing thread blocks while the tensor pipe's short queue is full, so whatever
-        // it does between two chunks is time the pipe can run dry: it waits for the NEXT
-        // chunk's operands before issuing the current chunk's MMAs (they are ready long
-        // before in steady state, and depend only on MMAs issued earlier), and each chunk
-        // costs one wait and one commit.
-        if (lane == 0) {
+        // ---- MMA issuer: one thread of the pair's leader CTA ----
+        // Issuing four MMAs costs this thread most of the time the tensor pipe needs to run
+        // them, so everything else is kept off its path: the test of the NEXT chunk's barrier
+        // is started before the current chunk's MMAs are issued and only read afterwards (its
+        // shared-memory latency overlaps the issue), the stage index is a compile-time
+        // constant (operand descriptors differ by constants), and only the first MMA of the
+        // tile carries the "overwrite" predicate.
+        if (lane == 0 && rank == 0) {
             const uint32_t idesc = umma_idesc();
-            bool ok = wait_or_timeout(&full[0], 0);
-            for (uint32_t g = 0; g < nchunks && ok; ++g) {
-                const uint32_t c = g % G_STAGES;
-                const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && g < 1024;
-                if (tr) p.trace[4 * g] = clock64();
-                if (g + 1 < nchunks) ok = wait_or_timeout(&full[(g + 1) % G_STAGES], ((g + 1) / G_STAGES) & 1);
-                if (tr) p.trace[4 * g + 1] = clock64();
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t ad = umma_desc_sw128(smem_u32(a_tiles + c * G_A_BYTES));
-                const uint64_t bd = umma_desc_sw128(smem_u32(b_tiles + c * G_B_BYTES));
+            const uint64_t ad0 = umma_desc_sw128(smem_u32(a_tiles)), bd0 = umma_desc_sw128(smem_u32(b_tiles));
+            bool ok = (mode & 8u) ? true : wait_cluster_or_timeout(&full[0], 0);
+            for (uint32_t g0 = 0, it = 0; g0 < nchunks && ok; g0 += G_STAGES, ++it) {
 #pragma unroll
-                for (uint32_t k = 0; k < GKC / 16; ++k) // K = 16 per instruction: 32 bytes along the swizzle row
-                    if (!(p.mode & 4u)) umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, (g | k) != 0);
-                umma_commit(&freeb[c]); // this stage may be overwritten once these MMAs are done
-                if (tr) p.trace[4 * g + 3] = clock64();
+                for (uint32_t c = 0; c < G_STAGES; ++c) {
+                    const uint32_t g = g0 + c;
+                    if (g >= nchunks || !ok) break;
+                    const bool tr = traced && g < 1024;
+                    if (tr) p.trace[4 * g] = clock64();
+                    const uint32_t cn = (c + 1) % G_STAGES, parn = (c + 1 == G_STAGES ? it + 1 : it) & 1;
+                    const bool has_next = g + 1 < nchunks && !(mode & 8u);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t ad = ad0 + (uint64_t)(c * (G_A_BYTES >> 4)), bd = bd0 + (uint64_t)(c * (G_B_BYTES >> 4));
+                    // One instruction sequence: start the test of the next chunk's barrier, issue the four
+                    // MMAs (K = 16 each: 32 bytes along the swizzle row) and the commit, and only then read
+                    // the test's result, so that nothing issued in between waits for it.
+                    uint32_t next_ready;
+                    if (DBG && (mode & 28u)) { // measurement variants: pieces of the sequence left out
+                        next_ready = (mode & 8u) ? 1u : (uint32_t)mbar_try_wait_cluster(&full[cn], parn);
+                        if (!(mode & 4u)) {
+                            umma_bf16(tmem_d, ad, bd, idesc, g != 0);
+                            umma_bf16_acc(tmem_d, ad + 2, bd + 2, idesc);
+                            umma_bf16_acc(tmem_d, ad + 4, bd + 4, idesc);
+                            umma_bf16_acc(tmem_d, ad + 6, bd + 6, idesc);
+                        }
+                        if (!(mode & 16u)) umma_commit_pair(&freeb[c]);
+                    } else
+                    asm volatile(
+                        "{\n"
+                        ".reg .pred pw, pa, pt;\n"
+                        ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+                        "setp.ne.b32 pa, %7, 0;\n"
+                        "setp.eq.b32 pt, 0, 0;\n"
+                        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 pw, [%1], %2;\n"
+                        "add.u64 a1, %4, 2;\n add.u64 a2, %4, 4;\n add.u64 a3, %4, 6;\n"
+                        "add.u64 b1, %5, 2;\n add.u64 b2, %5, 4;\n add.u64 b3, %5, 6;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], %4, %5, %6, pa;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], a1, b1, %6, pt;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], a2, b2, %6, pt;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], a3, b3, %6, pt;\n"
+                        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %9;\n"
+                        "selp.u32 %0, 1, 0, pw;\n"
+                        "}"
+                        : "=r"(next_ready)
+                        : "r"(smem_u32(&full[cn])), "r"(parn), "r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"((uint32_t)(g != 0)),
+                          "r"(smem_u32(&freeb[c])), "h"((uint16_t)3)
+                        : "memory");
+                    if (!has_next) next_ready = 1;
+                    if (tr) p.trace[4 * g + 1] = clock64();
+                    if (!next_ready) ok = wait_cluster_or_timeout(&full[cn], parn);
+                    if (tr) p.trace[4 * g + 3] = clock64();
+                }
             }
-            if (ok) umma_commit(&acc_full);
+            if (ok) umma_commit_pair(&acc_full);
             else *(volatile int *)p.status = DEV_TIMEOUT;
         }
     } else {
@@ -344,18 +464,20 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParam
             if (!ok) break;
             Blk blk;
             blk_load(blk, smem_u32(raw + st * Cfg::RAW_BYTES), row, part, kb);
-            mbar_arrive(&raw_free[st]); // the block's bytes are in registers: its stage can be refilled
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_free[st]); // the block's bytes are in registers: its stage can be refilled
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const uint32_t g = 4 * kb + c, ca = g % G_STAGES;
-                const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && g < 1024 && dt == 0;
+                const bool tr = traced && g < 1024 && dt == 0;
                 if (tr) p.trace[4096 + 4 * g] = clock64();
-                if (g >= G_STAGES) ok = ok && warp_wait(&freeb[ca], ((g / G_STAGES) - 1) & 1, lane);
+                if (g >= G_STAGES && !(mode & 16u)) ok = ok && warp_wait(&freeb[ca], ((g / G_STAGES) - 1) & 1, lane);
                 if (tr) p.trace[4096 + 4 * g + 1] = clock64();
                 if (!ok) break;
-                if (!(p.mode & 1u)) chunk_store(blk, c, part, row, smem_u32(a_tiles + ca * G_A_BYTES));
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the MMA
-                mbar_arrive(&full[ca]);
+                if (!(mode & 1u)) chunk_store(blk, c, part, row, smem_u32(a_tiles + ca * G_A_BYTES));
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the MMA (issued by the leader)
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&full[ca]), 0));
                 if (tr) p.trace[4096 + 4 * g + 2] = clock64();
             }
         }
@@ -390,12 +512,14 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_q_tc_kernel(const GemmParam
             *(volatile int *)p.status = DEV_TIMEOUT;
         }
     }
+    // Neither CTA leaves, or frees tensor memory, while the other may still read its shared
+    // memory (the leader's MMAs), signal its barriers or hold accumulator rows.
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    cluster_sync_all();
     if (warp == 1) {
-        __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)GN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)GN) : "memory");
     }
 }
 
@@ -451,12 +575,12 @@ bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s) {
 
 size_t gemm_tc_scratch_bytes(size_t in_dim, size_t s) { return s * in_dim * 2; }
 
-template <int FMT> static cudaError_t launch_one(const GemmParams &p, const GemmMaps &maps, dim3 grid, cudaStream_t st) {
+template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, const GemmMaps &maps, dim3 grid, cudaStream_t st) {
     using Cfg = GemmCfg<FMT>;
     const size_t smem = (size_t)G_STAGES * (G_A_BYTES + G_B_BYTES) + (size_t)Cfg::RAW_STAGES * Cfg::RAW_BYTES + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gemm_q_tc_kernel<FMT><<<grid, G_THREADS, smem, st>>>(p, maps);
+    gemm_q_tc_kernel<FMT, DBG><<<grid, G_THREADS, smem, st>>>(p, maps);
     return cudaGetLastError();
 }
 
@@ -472,7 +596,7 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     GemmMaps maps;
-    bool ok = encode_2d(enc, &maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_xb16, in_dim, s, in_dim * 2, GKC, GN, CU_TENSOR_MAP_SWIZZLE_128B);
+    bool ok = encode_2d(enc, &maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_xb16, in_dim, s, in_dim * 2, GKC, GNH, CU_TENSOR_MAP_SWIZZLE_128B);
     const uint8_t *w = (const uint8_t *)d_w;
     if (fmt == FMT_Q4K) {
         const size_t rb = nb * Q4K_BYTES;
@@ -489,8 +613,9 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
     p.y = d_y, p.status = d_status;
     p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
     p.mode = g_gemm_mode, p.trace = g_gemm_trace;
-    const dim3 grid((unsigned)((out_dim + GM - 1) / GM), (unsigned)((s + GN - 1) / GN));
-    return fmt == FMT_Q4K ? launch_one<FMT_Q4K>(p, maps, grid, st) : launch_one<FMT_Q6KR>(p, maps, grid, st);
+    const dim3 grid(2 * (unsigned)((out_dim + 2 * GM - 1) / (2 * GM)), (unsigned)((s + GN - 1) / GN));
+    if (p.mode || p.trace) return fmt == FMT_Q4K ? launch_one<FMT_Q4K, true>(p, maps, grid, st) : launch_one<FMT_Q6KR, true>(p, maps, grid, st);
+    return fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
 }
 
 } // namespace ullm
