@@ -408,9 +408,9 @@ static int gemm_try(ullm_cuda_ctx *c, int fmt, const void *d_w, const float *d_x
                     size_t s, cudaStream_t st) {
     if (c->force_generic || s < (size_t)c->gemm_min_s || !gemm_tc_supported(fmt, out_dim, in_dim, s)) return ULLM_ERR_UNSUPPORTED;
     void *xb = nullptr;
-    int rc = ctx_scratch(c, 7, gemm_tc_scratch_bytes(in_dim, s), &xb);
+    int rc = ctx_scratch(c, 7, gemm_tc_scratch_bytes(out_dim, in_dim, s, c->dev.sm_count), &xb);
     if (rc) return rc;
-    cudaError_t e = launch_gemm_tc(fmt, d_w, d_x, d_y, xb, out_dim, in_dim, s, c->d_status, st);
+    cudaError_t e = launch_gemm_tc(fmt, d_w, d_x, d_y, xb, out_dim, in_dim, s, c->dev.sm_count, c->d_status, st);
     if (e == cudaErrorNotSupported) {
         cudaGetLastError();
         return ULLM_ERR_UNSUPPORTED;

@@ -2,24 +2,33 @@
 // tokens at once (CPU form: matmul_q, crates/ullm-model/src/math.rs:38-63; Metal form:
 // matmul_q4k / matmul_q6k, crates/ullm-metal/src/shader.metal:620-740).
 //
-// A dense contraction, so it runs on the 5th-generation tensor cores: per CTA a
-// [128 weight rows x 256 tokens] fp32 accumulator lives in tensor memory (TMEM);
-// producer warps dequantize the packed weight blocks to bf16 (values rounded once,
-// from the exact f32 dequantization) straight into the 128-byte-swizzled K-major
-// shared-memory layout `tcgen05.mma` reads, the bf16 activation tile arrives by
-// tiled TMA with the same swizzle, one elected thread issues the MMAs
-// (kind::f16, M=128, N=256, K=16, cta_group::1) and commits them onto the mbarriers
-// that recycle the operand slots.  The epilogue reads the accumulator back with
-// tcgen05.ld and stores token-major f32.
+// A dense contraction, so it runs on the 5th-generation tensor cores.  A pair of CTAs
+// (cta_group::2) owns a [256 weight rows x 256 tokens] tile; each CTA keeps its 128 rows of
+// the fp32 accumulator in its tensor memory (TMEM).  The packed weight bytes arrive in shared
+// memory by tiled TMA, dequantization threads turn them into bf16 (values rounded once, from
+// the exact f32 dequantization) and write them with tcgen05.st straight into tensor memory,
+// where tcgen05.mma reads its A operand — the weights never pass through shared memory in
+// bf16 form, which keeps its bandwidth for the B operand: the bf16 activation tile, loaded
+// by tiled TMA with the 128-byte swizzle, half of the tokens into each CTA.  One elected
+// thread of the pair issues the MMAs (kind::f16, M=256, N=256, K=16) and commits them onto
+// the mbarriers that recycle the operand stages in both CTAs.  The epilogue reads the
+// accumulator back with tcgen05.ld and stores token-major f32.
 //
-// Roles in a CTA of 11 warps:
-//   warp 0      TMA: activation tile [256 tokens x 64 k] per k-chunk, 3 stages
-//   warp 10     TMA: the packed weight bytes of [128 rows x 256 k] per block, 2-3 stages
-//   warp 1      TMEM allocation, MMA issue, commits
-//   warps 2-9   dequantization from the staged bytes, all 256 threads on one 64-k chunk
-//               at a time into the same 3 stages, then the epilogue
+// Roles in a CTA of 12 warps (a pair of CTAs on neighbouring SMs works on one tile):
+//   warp 0      TMA: this CTA's half of the activation tile of every k-chunk, 8 stages
+//   warp 10     TMA: the packed weight bytes of [128 rows x 256 k] per block, 3-4 stages
+//   warp 1      tensor-memory allocation
+//   warp 11     MMA issue and commits (leader CTA of the pair only)
+//   warps 2-9   dequantization from the staged bytes into tensor memory (thread = one row
+//               = one TMEM lane; all 256 threads on one 64-k chunk at a time), then the epilogue
 // Every mbarrier wait is bounded; on expiry the CTA records a status, stops issuing
-// work, still frees its TMEM and leaves.
+// work, still frees its tensor memory and leaves.
+//
+// Measured on B200 (cycle stamps of every warp's arrival): the two dequantization warps that
+// share a warp scheduler with the MMA-issuing thread finish each chunk last — issuing four
+// MMAs per chunk costs that scheduler about as many cycles as the warps' own work — and
+// set the pace; the schedulers hosting the TMA threads lose less.  The service warps are
+// therefore spread over three schedulers.
 #include "kernels.h"
 #include "matvec_core.cuh"
 
@@ -32,10 +41,12 @@ constexpr int GM = 128;   // weight rows per CTA; a CTA pair covers 256 (MMA M)
 constexpr int GN = 256;   // tokens per CTA pair (MMA N, TMEM columns); each CTA stages 128 of them
 constexpr int GNH = GN / 2;
 constexpr int GKC = 64;   // k per chunk: 64 bf16 = one 128-byte swizzle row
-constexpr int G_STAGES = 5;  // operand stages in flight: one dequantized weight chunk + one activation chunk each
-constexpr int G_A_BYTES = GM * GKC * 2;   // 16 KB
+constexpr int G_STAGES = 8;  // operand stages in flight: one dequantized weight chunk (tensor memory) + one activation chunk (shared memory) each
+constexpr int G_A_COLS = GKC / 2;         // a weight chunk in tensor memory: 64 bf16 per row = 32 columns of 32 bit
+constexpr int G_TMEM_COLS = 512;          // accumulator (256) + 8 weight chunks (8 x 32)
 constexpr int G_B_BYTES = GNH * GKC * 2;  // 16 KB
-constexpr int G_THREADS = 352;
+constexpr int G_THREADS = 384;
+constexpr int G_MMA_WARP = 11;
 constexpr int G_DEQ_WARPS = 8;
 constexpr int G_RAW_WARP = 10;
 
@@ -72,26 +83,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok)
-                 : "r"(smem_u32(bar)), "r"(parity)
-                 : "memory");
-    return ok != 0;
-}
-// bounded like wait_or_timeout, observing arrivals made by the peer CTA
-__device__ __forceinline__ bool wait_cluster_or_timeout(uint64_t *bar, uint32_t parity) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait_cluster(bar, parity)) return true;
-        if (clock64() - t0 > (1ll << 31)) return false;
-    }
-}
-
 // Tiled TMA load into this CTA's own shared memory, completion counted on an mbarrier
 // given by its shared::cluster address (this CTA's or the pair leader's).
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
@@ -100,17 +91,18 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
                  "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
                  : "memory");
 }
-// One MMA over the CTA pair: D[256 x 256] (+)= A[256 x 16] * B[256 x 16]^T, each CTA supplying
-// its 128 rows of A and its 128 of B's tokens from the same shared-memory offsets, and
-// holding its 128 rows of D in its own tensor memory.
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
-                 "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+// One MMA over the CTA pair: D[256 x 256] (+)= A[256 x 16] * B[256 x 16]^T.  Each CTA supplies its
+// 128 rows of A from its own tensor memory (lane = row, one 32-bit column = two consecutive k),
+// its 128 of B's tokens from shared memory (same offsets in both CTAs), and holds its 128 rows
+// of D in its own tensor memory.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tmem_d),
+                 "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
 // the same with D always accumulated (no predicate to set up)
-__device__ __forceinline__ void umma_bf16_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
-    asm volatile("{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d), "l"(adesc),
+__device__ __forceinline__ void umma_bf16_acc(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tmem_d), "r"(tmem_a),
                  "l"(bdesc), "r"(idesc)
                  : "memory");
 }
@@ -125,17 +117,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
-// 16 bytes of row `row`, 16-byte column `c16` (0..7) of a [rows x 128 B] tile with the
-// 128-byte swizzle: the column index is XORed with the row index modulo 8.
-__device__ __forceinline__ void st_a_sw128(uint32_t tile, uint32_t row, uint32_t c16, uint4 v) {
-    const uint32_t addr = tile + row * 128u + ((c16 << 4) ^ ((row & 7u) << 4));
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+// Eight consecutive 32-bit columns of this thread's tensor-memory lane (the warp's lane quarter is in taddr)
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
 }
 
 struct GemmParams {
     float *y;  // [s, out]
     int *status;
     uint32_t out_dim, in_dim, s;
+    uint32_t blocks_per_split; // 256-k blocks handled by one grid.z slice (split-K for matrices with few row tiles)
     long long *trace; // measurement only: cycle stamps of CTA (0, 0)
     uint32_t mode; // measurement only: bit 0 skips the dequantization, bit 1 the activation loads, bit 2 the MMAs
 };
@@ -149,12 +142,12 @@ struct GemmMaps {
 template <int FMT> struct GemmCfg;
 template <> struct GemmCfg<FMT_Q4K> {
     static constexpr int RAW_BYTES = GM * Q4K_BYTES; // [128 rows][144 B]: 16-byte reads one row apart hit distinct banks
-    static constexpr int RAW_STAGES = 3;
+    static constexpr int RAW_STAGES = 4;
 };
 template <> struct GemmCfg<FMT_Q6KR> {
     static constexpr int REC_BYTES = GM * 48;                  // one record of every row: [128][48 B], conflict-free as well
     static constexpr int RAW_BYTES = 4 * REC_BYTES + 2 * GM * 16; // 4 records, [128][16 B] scales, [128][16 B] d
-    static constexpr int RAW_STAGES = 2;
+    static constexpr int RAW_STAGES = 3;
 };
 
 __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
@@ -187,7 +180,7 @@ __device__ __forceinline__ void blk_load(BlkQ4K &b, uint32_t raw, uint32_t row, 
 // d*sc and dmin*m as crates/ullm-core/src/dequant.rs:203-210 forms them, then
 // (d*sc)*q - dmin*m — the product is exact in f32 (q < 16), so the fused multiply-subtract
 // rounds exactly where the reference's subtraction does — and one more rounding to bf16.
-__device__ __forceinline__ void chunk_store(const BlkQ4K &b, int c, uint32_t q, uint32_t row, uint32_t tile) {
+__device__ __forceinline__ void chunk_store(const BlkQ4K &b, int c, uint32_t q, uint32_t ta) {
     const float d = f16_bits_to_f32((uint16_t)(b.hdr.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(b.hdr.x >> 16));
     const __half2 k1024 = h2_const(1024.f), k16th = h2_const(0.0625f), km64 = h2_const(-64.f);
     int sA, mA, sB, mB;
@@ -208,10 +201,8 @@ __device__ __forceinline__ void chunk_store(const BlkQ4K &b, int c, uint32_t q, 
         hi[2 * i] = pack_bf16x2(__fmaf_rn(d2, __low2float(h02), nm2), __fmaf_rn(d2, __low2float(h13), nm2));
         hi[2 * i + 1] = pack_bf16x2(__fmaf_rn(d2, __high2float(h02), nm2), __fmaf_rn(d2, __high2float(h13), nm2));
     }
-    st_a_sw128(tile, row, 2 * q, make_uint4(lo[0], lo[1], lo[2], lo[3]));
-    st_a_sw128(tile, row, 2 * q + 1, make_uint4(lo[4], lo[5], lo[6], lo[7]));
-    st_a_sw128(tile, row, 4 + 2 * q, make_uint4(hi[0], hi[1], hi[2], hi[3]));
-    st_a_sw128(tile, row, 5 + 2 * q, make_uint4(hi[4], hi[5], hi[6], hi[7]));
+    tmem_st8(ta + 8 * q, lo);       // k 16q .. 16q+15
+    tmem_st8(ta + 16 + 8 * q, hi);  // k 32+16q .. 32+16q+15
 }
 
 // Prepared Q6_K (prepare.cu): thread (row, tp) owns records (h, tp), h = 0, 1: positions
@@ -233,7 +224,7 @@ __device__ __forceinline__ void blk_load(BlkQ6KR &b, uint32_t raw, uint32_t row,
     b.d = lds_u16(raw + 4 * REC + GM * 16 + row * 16 + (kb & 7u) * 2);
 }
 // value = (d * sc) * (q - 32), left to right as dequant.rs:275-278, then rounded to bf16
-__device__ __forceinline__ void chunk_store(const BlkQ6KR &b, int c, uint32_t tp, uint32_t row, uint32_t tile) {
+__device__ __forceinline__ void chunk_store(const BlkQ6KR &b, int c, uint32_t tp, uint32_t ta) {
     const int h = c >> 1, gp = c & 1;
     const float d = f16_bits_to_f32((uint16_t)b.d);
     const __half2 k1056 = h2_const(1056.f); // 1024 + the format's offset of 32
@@ -256,31 +247,32 @@ __device__ __forceinline__ void chunk_store(const BlkQ6KR &b, int c, uint32_t tp
         oB[2 * i] = pack_bf16x2(__fmul_rn(dsB, __low2float(b02)), __fmul_rn(dsB, __low2float(b13)));
         oB[2 * i + 1] = pack_bf16x2(__fmul_rn(dsB, __high2float(b02)), __fmul_rn(dsB, __high2float(b13)));
     }
-    st_a_sw128(tile, row, 2 * tp, make_uint4(oA[0], oA[1], oA[2], oA[3]));
-    st_a_sw128(tile, row, 2 * tp + 1, make_uint4(oA[4], oA[5], oA[6], oA[7]));
-    st_a_sw128(tile, row, 4 + 2 * tp, make_uint4(oB[0], oB[1], oB[2], oB[3]));
-    st_a_sw128(tile, row, 5 + 2 * tp, make_uint4(oB[4], oB[5], oB[6], oB[7]));
+    tmem_st8(ta + 8 * tp, oA);       // first group of the chunk, positions 16tp .. 16tp+15
+    tmem_st8(ta + 16 + 8 * tp, oB);  // second group
 }
 
-// try_wait that may suspend the thread in hardware for up to `ns` while the phase is
-// incomplete (it still wakes when the phase completes), so a waiting thread does not fill
-// issue slots with polls.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parity, uint32_t ns) {
+// A waiting thread must stay off the warp scheduler: a thread parked in try_wait (or spinning on
+// it) takes issue slots from the dequantization warps of its scheduler, which then finish last and
+// make everyone wait longer.  So waits test the barrier once (test_wait never blocks) and sleep
+// between tests.  Bounded: about a second.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
                  : "=r"(ok)
-                 : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+                 : "r"(smem_u32(bar)), "r"(parity)
                  : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool wait_sleepy_or_timeout(uint64_t *bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool wait_polite_or_timeout(uint64_t *bar, uint32_t parity) {
+    if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
-        if (clock64() - t0 > (1ll << 31)) return false; // about a second
+        for (int i = 0; i < 64; ++i) {
+            asm volatile("nanosleep.u32 64;" ::: "memory");
+            if (mbar_test_wait(bar, parity)) return true;
+        }
+        if (clock64() - t0 > (1ll << 31)) return false;
     }
 }
 // A whole warp waits on an mbarrier with one polling lane: 256 threads spinning on
@@ -289,9 +281,9 @@ __device__ __forceinline__ bool wait_sleepy_or_timeout(uint64_t *bar, uint32_t p
 // once), which orders its following accesses after the barrier.
 __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32_t lane) {
     int ok = 1;
-    if (lane == 0) ok = wait_sleepy_or_timeout(bar, parity) ? 1 : 0;
+    if (lane == 0) ok = wait_polite_or_timeout(bar, parity) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (ok) (void)mbar_try_wait(bar, parity);
+    if (ok) (void)mbar_test_wait(bar, parity);
     return ok != 0;
 }
 
@@ -310,8 +302,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
     // dynamic smem is only guaranteed 16-byte aligned: round up to the 1024 B the swizzle atoms need
     // (the same amount in both CTAs of the pair, so operand offsets agree)
     uint8_t *base = (uint8_t *)(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
-    uint8_t *a_tiles = base;                                 // G_STAGES x 16 KB: this CTA's 128 rows
-    uint8_t *b_tiles = base + G_STAGES * G_A_BYTES;          // G_STAGES x 16 KB: this CTA's 128 tokens
+    uint8_t *b_tiles = base;                                 // G_STAGES x 16 KB: this CTA's 128 tokens
     uint8_t *raw = b_tiles + G_STAGES * G_B_BYTES;           // RS x packed bytes of [128 rows x 256 k]
     // full (used in the leader only): 16 dequantization warps of the pair + the leader's expect_tx arrival;
     // freeb / acc_full: one multicast tcgen05.commit each
@@ -321,8 +312,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_ctarank();
     const uint32_t m0 = blockIdx.x * GM, n0 = blockIdx.y * GN;
-    const uint32_t nb = p.in_dim / QK_K, nchunks = nb * 4;
-    const bool traced = DBG && p.trace && blockIdx.x == 0 && blockIdx.y == 0;
+    // this CTA's share of k: blocks [kb0, kb0 + nb); with split-K, slice z writes its partial sums to y + z * s * out
+    const uint32_t kb0 = blockIdx.z * p.blocks_per_split;
+    const uint32_t nb = min(p.blocks_per_split, p.in_dim / QK_K - kb0), nchunks = nb * 4;
+    float *const yout = p.y + (size_t)blockIdx.z * p.s * p.out_dim;
+    const bool traced = DBG && p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
     const uint32_t mode = DBG ? p.mode : 0u; // stages switched off for measurement
 
     if (tid == 0) {
@@ -337,8 +331,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         mbar_init(&acc_full, 1);
         mbar_fence_init();
     }
-    if (warp == 1) { // tensor memory: 256 columns of 128 lanes x 32 bit in each CTA of the pair
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)GN)
+    if (warp == 1) { // all of tensor memory in each CTA of the pair: accumulator columns 0-255, weight chunks 256-511
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)G_TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
@@ -353,7 +347,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         if (lane == 0) {
             for (uint32_t g = 0; g < nchunks; ++g) {
                 const uint32_t c = g % G_STAGES;
-                if (g >= G_STAGES && !(mode & 16u) && !wait_sleepy_or_timeout(&freeb[c], ((g / G_STAGES) - 1) & 1)) {
+                if (g >= G_STAGES && !(mode & 16u) && !wait_polite_or_timeout(&freeb[c], ((g / G_STAGES) - 1) & 1)) {
                     *(volatile int *)p.status = DEV_TIMEOUT;
                     break;
                 }
@@ -363,7 +357,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                     continue;
                 }
                 if (rank == 0) mbar_arrive_expect_tx(&full[c], 2 * G_B_BYTES); // both halves land on the leader's barrier
-                tma_load_2d(b_tiles + c * G_B_BYTES, &maps.x, (int)(g * GKC), (int)(n0 + rank * GNH), lead_full);
+                tma_load_2d(b_tiles + c * G_B_BYTES, &maps.x, (int)((kb0 * 4 + g) * GKC), (int)(n0 + rank * GNH), lead_full);
+                if (traced && g < 500) p.trace[6000 + g] = clock64();
             }
         }
     } else if (warp == G_RAW_WARP) {
@@ -371,24 +366,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         if (lane == 0) {
             for (uint32_t kb = 0; kb < nb; ++kb) {
                 const uint32_t st = kb % RS;
-                if (kb >= RS && !wait_sleepy_or_timeout(&raw_free[st], ((kb / RS) - 1) & 1)) {
+                if (kb >= RS && !wait_polite_or_timeout(&raw_free[st], ((kb / RS) - 1) & 1)) {
                     *(volatile int *)p.status = DEV_TIMEOUT;
                     break;
                 }
                 uint8_t *dst = raw + st * Cfg::RAW_BYTES;
-                const uint32_t bar = smem_u32(&raw_full[st]);
+                const uint32_t bar = smem_u32(&raw_full[st]), kg = kb0 + kb;
                 mbar_arrive_expect_tx(&raw_full[st], Cfg::RAW_BYTES);
                 if constexpr (FMT == FMT_Q4K) {
-                    tma_load_2d(dst, &maps.w0, (int)(kb * Q4K_BYTES), (int)m0, bar);
+                    tma_load_2d(dst, &maps.w0, (int)(kg * Q4K_BYTES), (int)m0, bar);
                 } else {
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) tma_load_2d(dst + r * Cfg::REC_BYTES, &maps.w0, (int)((kb * 4 + r) * 48), (int)m0, bar);
-                    tma_load_2d(dst + 4 * Cfg::REC_BYTES, &maps.w1, (int)(kb * 16), (int)m0, bar);
-                    tma_load_2d(dst + 4 * Cfg::REC_BYTES + GM * 16, &maps.w2, (int)((kb >> 3) * 16), (int)m0, bar);
+                    for (int r = 0; r < 4; ++r) tma_load_2d(dst + r * Cfg::REC_BYTES, &maps.w0, (int)((kg * 4 + r) * 48), (int)m0, bar);
+                    tma_load_2d(dst + 4 * Cfg::REC_BYTES, &maps.w1, (int)(kg * 16), (int)m0, bar);
+                    tma_load_2d(dst + 4 * Cfg::REC_BYTES + GM * 16, &maps.w2, (int)((kg >> 3) * 16), (int)m0, bar);
                 }
             }
         }
     } else if (warp == 1) {
+        // (tensor-memory allocation warp: nothing in the main loop)
+    } else if (warp == G_MMA_WARP) {
         // ---- MMA issuer: one thread of the pair's leader CTA ----
         // Issuing four MMAs costs this thread most of the time the tensor pipe needs to run
         // them, so everything else is kept off its path: the test of the NEXT chunk's barrier
@@ -398,8 +395,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         // tile carries the "overwrite" predicate.
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = umma_idesc();
-            const uint64_t ad0 = umma_desc_sw128(smem_u32(a_tiles)), bd0 = umma_desc_sw128(smem_u32(b_tiles));
-            bool ok = (mode & 8u) ? true : wait_cluster_or_timeout(&full[0], 0);
+            const uint32_t ta0 = tmem_d + GN; // weight chunks follow the accumulator
+            const uint64_t bd0 = umma_desc_sw128(smem_u32(b_tiles));
+            bool ok = (mode & 8u) ? true : wait_polite_or_timeout(&full[0], 0);
             for (uint32_t g0 = 0, it = 0; g0 < nchunks && ok; g0 += G_STAGES, ++it) {
 #pragma unroll
                 for (uint32_t c = 0; c < G_STAGES; ++c) {
@@ -407,47 +405,54 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                     if (g >= nchunks || !ok) break;
                     const bool tr = traced && g < 1024;
                     if (tr) p.trace[4 * g] = clock64();
+                    if (tr && g >= 96 && g < 112) {
+                        unsigned long long gt;
+                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+                        p.trace[7000 + 16 * 32 + (g - 96)] = (long long)gt;
+                    }
                     const uint32_t cn = (c + 1) % G_STAGES, parn = (c + 1 == G_STAGES ? it + 1 : it) & 1;
                     const bool has_next = g + 1 < nchunks && !(mode & 8u);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t ad = ad0 + (uint64_t)(c * (G_A_BYTES >> 4)), bd = bd0 + (uint64_t)(c * (G_B_BYTES >> 4));
+                    const uint32_t ad = ta0 + c * G_A_COLS;
+                    const uint64_t bd = bd0 + (uint64_t)(c * (G_B_BYTES >> 4));
                     // One instruction sequence: start the test of the next chunk's barrier, issue the four
                     // MMAs (K = 16 each: 32 bytes along the swizzle row) and the commit, and only then read
                     // the test's result, so that nothing issued in between waits for it.
                     uint32_t next_ready;
                     if (DBG && (mode & 28u)) { // measurement variants: pieces of the sequence left out
-                        next_ready = (mode & 8u) ? 1u : (uint32_t)mbar_try_wait_cluster(&full[cn], parn);
+                        next_ready = (mode & 8u) ? 1u : (uint32_t)mbar_test_wait(&full[cn], parn);
                         if (!(mode & 4u)) {
                             umma_bf16(tmem_d, ad, bd, idesc, g != 0);
-                            umma_bf16_acc(tmem_d, ad + 2, bd + 2, idesc);
-                            umma_bf16_acc(tmem_d, ad + 4, bd + 4, idesc);
-                            umma_bf16_acc(tmem_d, ad + 6, bd + 6, idesc);
+                            umma_bf16_acc(tmem_d, ad + 8, bd + 2, idesc);
+                            umma_bf16_acc(tmem_d, ad + 16, bd + 4, idesc);
+                            umma_bf16_acc(tmem_d, ad + 24, bd + 6, idesc);
                         }
                         if (!(mode & 16u)) umma_commit_pair(&freeb[c]);
                     } else
                     asm volatile(
                         "{\n"
                         ".reg .pred pw, pa, pt;\n"
-                        ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+                        ".reg .b32 a1, a2, a3;\n"
+                        ".reg .b64 b1, b2, b3;\n"
                         "setp.ne.b32 pa, %7, 0;\n"
                         "setp.eq.b32 pt, 0, 0;\n"
-                        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 pw, [%1], %2;\n"
-                        "add.u64 a1, %4, 2;\n add.u64 a2, %4, 4;\n add.u64 a3, %4, 6;\n"
+                        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 pw, [%1], %2;\n"
+                        "add.u32 a1, %4, 8;\n add.u32 a2, %4, 16;\n add.u32 a3, %4, 24;\n"
                         "add.u64 b1, %5, 2;\n add.u64 b2, %5, 4;\n add.u64 b3, %5, 6;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], %4, %5, %6, pa;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], a1, b1, %6, pt;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], a2, b2, %6, pt;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], a3, b3, %6, pt;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [%4], %5, %6, pa;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [a1], b1, %6, pt;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [a2], b2, %6, pt;\n"
+                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [a3], b3, %6, pt;\n"
                         "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %9;\n"
                         "selp.u32 %0, 1, 0, pw;\n"
                         "}"
                         : "=r"(next_ready)
-                        : "r"(smem_u32(&full[cn])), "r"(parn), "r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"((uint32_t)(g != 0)),
+                        : "r"(smem_u32(&full[cn])), "r"(parn), "r"(tmem_d), "r"(ad), "l"(bd), "r"(idesc), "r"((uint32_t)(g != 0)),
                           "r"(smem_u32(&freeb[c])), "h"((uint16_t)3)
                         : "memory");
                     if (!has_next) next_ready = 1;
                     if (tr) p.trace[4 * g + 1] = clock64();
-                    if (!next_ready) ok = wait_cluster_or_timeout(&full[cn], parn);
+                    if (!next_ready) ok = wait_polite_or_timeout(&full[cn], parn);
                     if (tr) p.trace[4 * g + 3] = clock64();
                 }
             }
@@ -456,14 +461,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         }
     } else {
         // ---- dequantization: all 256 threads work on one 64-k chunk at a time ----
-        const uint32_t dt = tid - 64, row = dt & 127, part = dt >> 7;
+        // a warp reaches only its own quarter of the tensor-memory lanes: row = lane of that quarter
+        const uint32_t dt = tid - 64, lq = warp & 3, row = lq * 32 + lane, part = (warp - 2) >> 2;
+        const uint32_t ta_lane = tmem_d + ((lq * 32u) << 16) + GN;
         bool ok = true;
         for (uint32_t kb = 0; kb < nb && ok; ++kb) {
             const uint32_t st = kb % RS;
             ok = warp_wait(&raw_full[st], (kb / RS) & 1, lane);
             if (!ok) break;
             Blk blk;
-            blk_load(blk, smem_u32(raw + st * Cfg::RAW_BYTES), row, part, kb);
+            blk_load(blk, smem_u32(raw + st * Cfg::RAW_BYTES), row, part, kb0 + kb);
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_free[st]); // the block's bytes are in registers: its stage can be refilled
 #pragma unroll
@@ -474,10 +481,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                 if (g >= G_STAGES && !(mode & 16u)) ok = ok && warp_wait(&freeb[ca], ((g / G_STAGES) - 1) & 1, lane);
                 if (tr) p.trace[4096 + 4 * g + 1] = clock64();
                 if (!ok) break;
-                if (!(mode & 1u)) chunk_store(blk, c, part, row, smem_u32(a_tiles + ca * G_A_BYTES));
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the MMA (issued by the leader)
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); // the MMAs that read this stage are done
+                if (!(mode & 1u)) chunk_store(blk, c, part, ta_lane + ca * G_A_COLS);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); // the chunk is in tensor memory
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&full[ca]), 0));
+                if (DBG && p.trace && blockIdx.x < 2 && blockIdx.y == 0 && lane == 0 && g >= 96 && g < 112) {
+                    unsigned long long gt;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+                    p.trace[7000 + (g - 96) * 32 + rank * 16 + (warp - 2)] = (long long)gt;
+                }
                 if (tr) p.trace[4096 + 4 * g + 2] = clock64();
             }
         }
@@ -504,7 +518,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t tok = n0 + col0 + j;
-                        if (tok < p.s) p.y[(size_t)tok * p.out_dim + orow] = __uint_as_float(v[j]);
+                        if (tok < p.s) yout[(size_t)tok * p.out_dim + orow] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -519,7 +533,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
     cluster_sync_all();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)GN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)G_TMEM_COLS) : "memory");
     }
 }
 
@@ -533,6 +547,25 @@ __global__ void cast_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__r
         *(uint2 *)(y + i) = o;
     } else {
         for (size_t j = i; j < n; ++j) y[j] = __float2bfloat16_rn(x[j]);
+    }
+}
+
+// split-K: y[i] = part[0][i] + part[1][i] + ... in slice order (deterministic)
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, float *__restrict__ y, size_t n, int splits) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        float4 a = *(const float4 *)(part + i);
+        for (int z = 1; z < splits; ++z) {
+            const float4 b = *(const float4 *)(part + (size_t)z * n + i);
+            a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+        }
+        *(float4 *)(y + i) = a;
+    } else {
+        for (size_t j = i; j < n; ++j) {
+            float a = part[j];
+            for (int z = 1; z < splits; ++z) a += part[(size_t)z * n + j];
+            y[j] = a;
+        }
     }
 }
 
@@ -573,11 +606,26 @@ bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s) {
     return in_dim <= (1u << 24) && out_dim <= (1u << 30) && s <= (1u << 30);
 }
 
-size_t gemm_tc_scratch_bytes(size_t in_dim, size_t s) { return s * in_dim * 2; }
+// Matrices with few row tiles leave most SMs idle: their k range is split over grid.z slices
+// (whole 256-k blocks each), partial sums go to scratch and are added in slice order.
+static int gemm_splits(size_t out_dim, size_t in_dim, size_t s, int sm_count) {
+    const size_t ctas = 2 * ((out_dim + 2 * GM - 1) / (2 * GM)) * ((s + GN - 1) / GN), nb = in_dim / QK_K;
+    if (ctas * 2 > (size_t)sm_count) return 1;
+    size_t z = (size_t)sm_count / ctas;
+    if (z > nb / 2) z = nb / 2; // at least two blocks per slice
+    if (z > 16) z = 16;
+    return z < 2 ? 1 : (int)z;
+}
+static size_t x16_bytes(size_t in_dim, size_t s) { return (s * in_dim * 2 + 255) & ~(size_t)255; }
+
+size_t gemm_tc_scratch_bytes(size_t out_dim, size_t in_dim, size_t s, int sm_count) {
+    const int z = gemm_splits(out_dim, in_dim, s, sm_count);
+    return x16_bytes(in_dim, s) + (z > 1 ? (size_t)z * s * out_dim * 4 : 0);
+}
 
 template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, const GemmMaps &maps, dim3 grid, cudaStream_t st) {
     using Cfg = GemmCfg<FMT>;
-    const size_t smem = (size_t)G_STAGES * (G_A_BYTES + G_B_BYTES) + (size_t)Cfg::RAW_STAGES * Cfg::RAW_BYTES + 1024;
+    const size_t smem = (size_t)G_STAGES * G_B_BYTES + (size_t)Cfg::RAW_STAGES * Cfg::RAW_BYTES + 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     gemm_q_tc_kernel<FMT, DBG><<<grid, G_THREADS, smem, st>>>(p, maps);
@@ -587,7 +635,7 @@ template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, 
 // d_w: FMT_Q4K verbatim rows or FMT_Q6KR prepared rows (16-byte aligned).  d_x f32 [s, in],
 // d_y f32 [s, out], d_xb16: scratch of gemm_tc_scratch_bytes (256-byte aligned).
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_xb16, size_t out_dim, size_t in_dim,
-                           size_t s, int *d_status, cudaStream_t st) {
+                           size_t s, int sm_count, int *d_status, cudaStream_t st) {
     if (!gemm_tc_supported(fmt, out_dim, in_dim, s) || ((uintptr_t)d_w & 15)) return cudaErrorNotSupported;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
@@ -609,13 +657,22 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
         ok = ok && encode_2d(enc, &maps.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, w + nb * 208, nb * 2, out_dim, rb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (!ok) return cudaErrorInvalidValue;
+    const int splits = gemm_splits(out_dim, in_dim, s, sm_count);
+    float *part = (float *)((uint8_t *)d_xb16 + x16_bytes(in_dim, s));
     GemmParams p;
-    p.y = d_y, p.status = d_status;
+    p.blocks_per_split = (uint32_t)((nb + splits - 1) / splits);
+    const unsigned gz = (unsigned)((nb + p.blocks_per_split - 1) / p.blocks_per_split);
+    p.y = gz > 1 ? part : d_y, p.status = d_status;
     p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
     p.mode = g_gemm_mode, p.trace = g_gemm_trace;
-    const dim3 grid(2 * (unsigned)((out_dim + 2 * GM - 1) / (2 * GM)), (unsigned)((s + GN - 1) / GN));
-    if (p.mode || p.trace) return fmt == FMT_Q4K ? launch_one<FMT_Q4K, true>(p, maps, grid, st) : launch_one<FMT_Q6KR, true>(p, maps, grid, st);
-    return fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
+    const dim3 grid(2 * (unsigned)((out_dim + 2 * GM - 1) / (2 * GM)), (unsigned)((s + GN - 1) / GN),
+                    gz);
+    if (p.mode || p.trace) e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, true>(p, maps, grid, st) : launch_one<FMT_Q6KR, true>(p, maps, grid, st);
+    else e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
+    if (e != cudaSuccess || grid.z == 1) return e;
+    const size_t ny = s * out_dim;
+    splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, d_y, ny, (int)grid.z);
+    return cudaGetLastError();
 }
 
 } // namespace ullm
