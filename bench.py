@@ -42,7 +42,7 @@ C1_DOWN = (4096, 14336)
 C1_BYTES_PER_LAUNCH = 48_168_960 + 16_384 + 57_344  # weights + x + y (either launch)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_PER_LAUNCH = {"c1_q6k_ffn_pair": (48_208_384 + 6_400 + 48_252_672 + 1_536) // 2}
+NCU_TRAFFIC_PER_LAUNCH = {"c1_q6k_ffn_pair": (48_224_768 + 48_265_728) // 2}  # dram read + write of the two launches, ncu capture under profiles/
 
 C4_MATS = [  # name, dtype, out, in   (one Llama-3-70B block)
     ("q", synth.Q4_K, 8192, 8192), ("k", synth.Q4_K, 1024, 8192), ("v", synth.Q4_K, 1024, 8192),
@@ -390,6 +390,8 @@ def run_other(args):
         tf_peak = measured_peak_tflops()
         per, total_ms, total_flop = {}, 0.0, 0.0
         for i, (name, dt, o, c) in enumerate(C4_MATS):
+            if args.only and name != args.only:
+                continue
             w = backend.Weight(ctx, dt, synth.gen_weight(dt, o, c, synth.seed_for(4, i)), o, c)
             xs = torch.randn(S * c, dtype=torch.float32, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i))
             ys = torch.empty(S * o, dtype=torch.float32, device=dev)
@@ -598,6 +600,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=512, help="prefill length of the c4gemm workload")
+    ap.add_argument("--only", default="", help="c4gemm: run just this matrix of the block (q, k, v, o, gate, up, down)")
     ap.add_argument("--pdl", type=int, default=1, help="launch the kernels with programmatic dependent launch (weight prefetch of the next kernel overlaps the tail of the previous one)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--multi-graph", action="store_true", help="N>1: capture kernels + NCCL in a CUDA graph (off by default)")
