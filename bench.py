@@ -458,6 +458,69 @@ def run_other(args):
     return 0
 
 
+def run_multi_gemm(args):
+    """N>1, --workload c4gemm: the 70B block as a 512-token prefill GEMM, rows/N of every matrix per
+    rank (tcgen05 kernel on the slice), one all-gather of the ranks' [tokens, rows/N] outputs per step."""
+    import torch
+    import torch.distributed as dist
+
+    from ullm_b200 import backend
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    ctx = backend.CudaContext(local)
+    dev = torch.device(f"cuda:{local}")
+    S = args.tokens
+    rows_total = shard.local_offsets([o for _, _, o, _ in C4_MATS], world)[-1]
+    y_cat = torch.empty(S * rows_total, dtype=torch.float32, device=dev)            # [matrix][token][rows/N]
+    y_all = torch.empty(world * S * rows_total, dtype=torch.float32, device=dev)    # [rank][matrix][token][rows/N]
+    mats, off = [], 0
+    for i, (name, dt, out, cols) in enumerate(C4_MATS):
+        rows = out // world
+        w = backend.Weight(ctx, dt, synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1)), rows, cols)
+        xs = torch.randn(S * cols, dtype=torch.float32, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i))
+        mats.append((w, xs, y_cat.data_ptr() + 4 * S * off))
+        off += rows
+    side = torch.cuda.Stream()
+    ctx.debug_set("pdl", 0)
+
+    def step():
+        for w, xs, yp in mats:
+            w.matmul_dev(xs.data_ptr(), yp, S, side.cuda_stream)
+        dist.all_gather_into_tensor(y_all, y_cat)
+
+    with torch.cuda.stream(side):
+        for _ in range(max(args.warmup, 3)):
+            step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(side):
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms_t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms = float(ms_t.item()) / args.steps
+    if rank == 0:
+        flop = 2.0 * S * sum(o * c for _, _, o, c in C4_MATS)
+        tf = flop / ms / 1e9
+        print(json.dumps({"workload": "c4gemm", "n_gpus": world, "tokens": S, "steps": args.steps, "us_per_step": ms * 1e3,
+                          "tflops": tf, "tflops_per_gpu": tf / world, "peak_tflops": measured_peak_tflops(),
+                          "frac_per_gpu": tf / world / measured_peak_tflops(), "scaling": "strong",
+                          "gather_bytes_per_step": 4 * world * S * rows_total,
+                          "parallelism": f"rows/{world} per matrix, one NCCL all-gather of [rank][matrix][token][rows] per step",
+                          "launch": "host launches + NCCL"}), flush=True)
+    dist.destroy_process_group()
+    return 0
+
+
 def run_multi(args):
     import torch
     import torch.distributed as dist
@@ -611,7 +674,7 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        return run_multi(args)
+        return run_multi_gemm(args) if args.workload == "c4gemm" else run_multi(args)
     if args.workload != "c1":
         return run_other(args)
     return run_single(args)

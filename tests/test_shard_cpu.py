@@ -73,3 +73,22 @@ def test_shard_index_math():
     y_all = np.arange(2 * 5, dtype=np.float32)  # world 2, matrices of 4 and 6 rows
     a, b = shard.split_gathered(y_all, [4, 6], 2)
     assert a.tolist() == [0, 1, 5, 6] and b.tolist() == [2, 3, 4, 7, 8, 9]
+
+
+def test_prefill_gather_layout_matches_the_unsharded_matmul():
+    """Each rank's token-major [tokens, rows/N] products, concatenated per matrix and gathered
+    as [rank][matrix][token][rows], must split back into the unsharded [tokens, out] products."""
+    world, tokens = 2, 5
+    outs, parts = [m[1] for m in MATS], [[] for _ in range(world)]
+    refs = []
+    for i, (dt, out, cols) in enumerate(MATS):
+        gen = synth.gen_q4k if dt == oracle.Q4_K else synth.gen_q6k
+        full = gen(out, cols, 300 + i)
+        xs = synth.normal(400 + i, tokens * cols)
+        refs.append(oracle.matmul_q(oracle.Weight(dt, full, out, cols), xs, tokens))
+        for r in range(world):
+            mine = shard.slice_rows(dt, full, out, cols, world, r)
+            parts[r].append(oracle.matmul_q(oracle.Weight(dt, mine, out // world, cols), xs, tokens).reshape(-1))
+    y_all = np.concatenate([np.concatenate(p) for p in parts])
+    for got, ref in zip(shard.split_gathered_tokens(y_all, outs, world, tokens), refs):
+        assert np.array_equal(got, ref)

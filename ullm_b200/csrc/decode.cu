@@ -26,7 +26,8 @@ namespace ullm {
 // ---------------------------------------------------------------------------
 // Attention for one new token
 // ---------------------------------------------------------------------------
-constexpr int ATT_CHUNK = 128; // cache positions per CTA
+constexpr int ATT_CHUNK = 32; // cache positions per CTA: a 1024-position context is 33 x n_kv_head CTAs, each with one batch per warp
+constexpr int ATT_MAX_CTX = 8192;
 
 template <typename T> __device__ __forceinline__ float kv_load(const T *p);
 template <> __device__ __forceinline__ float kv_load<float>(const float *p) { return __ldcg(p); }
@@ -64,7 +65,7 @@ __device__ __forceinline__ float warp_transpose_sum32(float (&v)[32], int lane) 
 }
 
 // grid (n_kv_head, n_split), 128 threads.  CTA (h, s) owns cache positions
-// [s*64, s*64+64) of kv head h for its KVMUL query heads; the CTA that owns `pos`
+// [s*ATT_CHUNK, (s+1)*ATT_CHUNK) of kv head h for its KVMUL query heads; the CTA that owns `pos`
 // applies RoPE to the new K, rounds K and V to the cache type and stores them;
 // the last CTA of a head to finish merges the per-split softmax partials.
 template <int HD, int KVMUL, typename KV_T>
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     // merge the splits: w[h][s] = exp(m_s - M) / L first (all loads independent), then
     // one pass over the partial outputs
     const float *base = p.partial + ((size_t)kvh * p.n_split * KVMUL) * (HD + 2);
-    __shared__ float wgt[KVMUL][64]; // up to 64 splits (8192 positions)
+    __shared__ float wgt[KVMUL][ATT_MAX_CTX / ATT_CHUNK];
     for (int i = tid; i < KVMUL * n_active; i += 128) {
         const int h = i / n_active, s2 = i % n_active;
         wgt[h][s2] = __ldcg(base + ((size_t)s2 * KVMUL + h) * (HD + 2) + HD);
@@ -294,6 +295,14 @@ template <int HD, int KVMUL> static cudaError_t launch_attn_t(const AttnParams &
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
+    // Same shared-memory carve-out as the streamed matvecs around it: a kernel that prefers a
+    // different L1 / shared split makes the SMs drain and reconfigure between launches.
+    static bool carved = false;
+    if (!carved) {
+        cudaFuncSetAttribute(attn_decode_kernel<HD, KVMUL, __half>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(attn_decode_kernel<HD, KVMUL, float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carved = true;
+    }
     if (f16) return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, KVMUL, __half>, p);
     return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, KVMUL, float>, p);
 }
@@ -524,6 +533,7 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
+        cudaFuncSetAttribute(argmax_step_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         TRY(cudaLaunchKernelEx(&cfg, argmax_step_kernel, (const float *)logits, (int)P.vocab, tok_ptr, pos_ptr, step_ptr,
                                tokens_out, (int)MAX_GREEDY));
         ++launches;

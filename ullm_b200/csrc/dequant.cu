@@ -108,6 +108,12 @@ cudaError_t launch_dequant_row(int dtype, const void *d_table, const uint32_t *d
                                cudaStream_t st) {
     if (cols % QK_K) return cudaErrorInvalidValue;
     size_t nb = cols / QK_K;
+    static bool carved = false; // runs between streamed matvecs: keep their shared-memory carve-out
+    if (!carved) {
+        cudaFuncSetAttribute(dequant_q4k_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(dequant_q6k_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carved = true;
+    }
     if (dtype == 12) dequant_q4k_kernel<<<nblk(nb * 128, 256), 256, 0, st>>>((const uint8_t *)d_table, d_out, nb, d_row, nb * Q4K_BYTES);
     else if (dtype == 14) dequant_q6k_kernel<<<nblk(nb * 64, 256), 256, 0, st>>>((const uint8_t *)d_table, d_out, nb, d_row, nb * Q6K_BYTES);
     else return cudaErrorInvalidValue;

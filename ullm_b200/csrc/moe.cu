@@ -174,9 +174,21 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     const int D = p.route[0];
     const int *ex_list = p.route + route_off_list(), *ex_off = p.route + route_off_offs(p.n_exp),
               *pairs = p.route + route_off_pairs(p.n_exp);
-    const uint32_t U = (uint32_t)D * p.tiles_per_expert;
-    const uint32_t u0 = (uint32_t)(((uint64_t)U * blockIdx.x) / gridDim.x),
-                   u1 = (uint32_t)(((uint64_t)U * (blockIdx.x + 1)) / gridDim.x);
+    // Units (expert d, row tile rt), in that order, are dealt to the CTAs by COST, not by count: a
+    // tile of an expert picked by np pairs costs np row passes (the arithmetic per pair is about
+    // what the tile's transfer takes, so popular experts are compute-bound).  Unit (d, rt) sits at
+    // cost position ex_off[d] * T + rt * np(d); CTA b owns the units whose position falls in its
+    // equal share of the total npairs * T.
+    const uint32_t T = p.tiles_per_expert;
+    const uint64_t C = (uint64_t)ex_off[D] * T;
+    auto first_unit_at = [&](uint64_t c) -> uint32_t {
+        for (int d = 0; d < D; ++d) {
+            const uint64_t base = (uint64_t)ex_off[d] * T, np = (uint64_t)(ex_off[d + 1] - ex_off[d]);
+            if (c <= base + (T - 1) * np) return (uint32_t)d * T + (c <= base ? 0u : (uint32_t)((c - base + np - 1) / np));
+        }
+        return (uint32_t)D * T;
+    };
+    const uint32_t u0 = first_unit_at(C * blockIdx.x / gridDim.x), u1 = first_unit_at(C * (blockIdx.x + 1) / gridDim.x);
 
     if (producer) {
         if (lane == 0) {

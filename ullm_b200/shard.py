@@ -54,3 +54,16 @@ def split_gathered(y_all, out_dims, world: int) -> list[np.ndarray]:
     offs = local_offsets(out_dims, world)
     per_rank = np.asarray(y_all).reshape(world, offs[-1])
     return [per_rank[:, offs[i] : offs[i + 1]].reshape(-1) for i in range(len(out_dims))]
+
+
+def split_gathered_tokens(y_all, out_dims, world: int, tokens: int) -> list[np.ndarray]:
+    """Prefill form: ``y_all`` is ``[rank][matrix][token][rows/N]`` (each rank's token-major GEMM
+    outputs on its row slices, concatenated, then all-gathered); returns ``[tokens, out]`` per matrix."""
+    offs = local_offsets(out_dims, world)
+    per_rank = np.asarray(y_all).reshape(world, tokens * offs[-1])
+    res = []
+    for i, d in enumerate(out_dims):
+        n = d // world
+        blk = per_rank[:, tokens * offs[i] : tokens * offs[i + 1]].reshape(world, tokens, n)
+        res.append(np.ascontiguousarray(blk.transpose(1, 0, 2)).reshape(tokens, d))
+    return res
