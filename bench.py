@@ -213,10 +213,17 @@ def run_single(args):
     h = torch.empty(C1_UP[0], dtype=torch.float32, device=dev)
     y = torch.empty(C1_DOWN[0], dtype=torch.float32, device=dev)
 
+    # the pair as one persistent launch (up, then down behind a grid barrier) or as two launches
+    chains = [backend.WeightChain(ctx, [dict(w=ups[c], x=x.data_ptr(), y=h.data_ptr()),
+                                        dict(w=dns[c], x=h.data_ptr(), y=y.data_ptr(), dep=True)]) for c in range(ncopies)]
+
     def step(i):
         c = i % ncopies
-        ups[c].matvec_dev(x.data_ptr(), h.data_ptr(), stream)
-        dns[c].matvec_dev(h.data_ptr(), y.data_ptr(), stream)
+        if args.chain:
+            chains[c].launch(stream)
+        else:
+            ups[c].matvec_dev(x.data_ptr(), h.data_ptr(), stream)
+            dns[c].matvec_dev(h.data_ptr(), y.data_ptr(), stream)
 
     if args.pdl:
         ctx.debug_set("pdl", 1)
@@ -280,9 +287,10 @@ def run_single(args):
 
     step_bytes = 2 * C1_BYTES_PER_LAUNCH
     value = args.steps * step_bytes / (ms * 1e-3) / 1e9
-    launch_us = ms * 1e3 / (2 * args.steps)
+    per_launch = 2 if args.chain else 1  # matrices streamed by one launch
+    launch_us = ms * 1e3 / (2 * args.steps) * per_launch
     peak, peak_kind = measured_peak_gbs()
-    achieved = C1_BYTES_PER_LAUNCH / (launch_us * 1e-6) / 1e9
+    achieved = per_launch * C1_BYTES_PER_LAUNCH / (launch_us * 1e-6) / 1e9
 
     cpu = None
     if not args.no_cpu:
@@ -307,14 +315,14 @@ def run_single(args):
                    "plan": plan, "pdl": bool(args.pdl), "launch": "eager" if args.eager else "one CUDA graph of all timed steps",
                    "frac_of_8000": value / 8000.0},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_PER_LAUNCH["c1_q6k_ffn_pair"], "peak_kind": f"of {peak_kind}",
-                     "kernel": "matvec_stream_kernel<Q6_K prepared>", "launch_us": launch_us,
-                     "algorithmic_bytes_per_launch": C1_BYTES_PER_LAUNCH},
+                     "traffic": per_launch * NCU_TRAFFIC_PER_LAUNCH["c1_q6k_ffn_pair"], "peak_kind": f"of {peak_kind}",
+                     "kernel": "matvec_chain_kernel (both matrices, one persistent launch)" if args.chain else "matvec_stream_kernel<Q6_K prepared>",
+                     "launch_us": launch_us, "algorithmic_bytes_per_launch": per_launch * C1_BYTES_PER_LAUNCH},
         "cpu_baseline": cpu,
         "e2e": {"value": args.steps * step_bytes / e2e_s / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": 4 * (C1_UP[1] + C1_DOWN[1]), "d2h_bytes_per_step": 4 * (C1_UP[0] + C1_DOWN[0]),
                 "us_per_step": e2e_s / args.steps * 1e6, "api": "ullm_cuda_weight_matvec (resident weight, pinned host x / y)"},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": (1 if args.chain else 2) * args.steps,
         "clocks": clocks,
         "check": check,
     }
@@ -474,22 +482,25 @@ def run_multi_gemm(args):
     dev = torch.device(f"cuda:{local}")
     S = args.tokens
     rows_total = shard.local_offsets([o for _, _, o, _ in C4_MATS], world)[-1]
-    y_cat = torch.empty(S * rows_total, dtype=torch.float32, device=dev)            # [matrix][token][rows/N]
-    y_all = torch.empty(world * S * rows_total, dtype=torch.float32, device=dev)    # [rank][matrix][token][rows/N]
-    mats, off = [], 0
+    mats = []
     for i, (name, dt, out, cols) in enumerate(C4_MATS):
         rows = out // world
         w = backend.Weight(ctx, dt, synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1)), rows, cols)
         xs = torch.randn(S * cols, dtype=torch.float32, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i))
-        mats.append((w, xs, y_cat.data_ptr() + 4 * S * off))
-        off += rows
+        y_r = torch.empty(S * rows, dtype=torch.float32, device=dev)             # this rank's [token][rows/N]
+        y_g = torch.empty(world * S * rows, dtype=torch.float32, device=dev)     # [rank][token][rows/N]
+        mats.append((w, xs, y_r, y_g))
     side = torch.cuda.Stream()
     ctx.debug_set("pdl", 0)
 
     def step():
-        for w, xs, yp in mats:
-            w.matmul_dev(xs.data_ptr(), yp, S, side.cuda_stream)
-        dist.all_gather_into_tensor(y_all, y_cat)
+        # the gather of one matrix' output overlaps the GEMM of the next (NCCL runs on its own stream)
+        works = []
+        for w, xs, y_r, y_g in mats:
+            w.matmul_dev(xs.data_ptr(), y_r.data_ptr(), S, side.cuda_stream)
+            works.append(dist.all_gather_into_tensor(y_g, y_r, async_op=True))
+        for wk in works:
+            wk.wait()
 
     with torch.cuda.stream(side):
         for _ in range(max(args.warmup, 3)):
@@ -515,7 +526,7 @@ def run_multi_gemm(args):
                           "tflops": tf, "tflops_per_gpu": tf / world, "peak_tflops": measured_peak_tflops(),
                           "frac_per_gpu": tf / world / measured_peak_tflops(), "scaling": "strong",
                           "gather_bytes_per_step": 4 * world * S * rows_total,
-                          "parallelism": f"rows/{world} per matrix, one NCCL all-gather of [rank][matrix][token][rows] per step",
+                          "parallelism": f"rows/{world} per matrix; each matrix' [token][rows/N] output is all-gathered while the next matrix is multiplied",
                           "launch": "host launches + NCCL"}), flush=True)
     dist.destroy_process_group()
     return 0
@@ -666,6 +677,9 @@ def main():
     ap.add_argument("--only", default="", help="c4gemm: run just this matrix of the block (q, k, v, o, gate, up, down)")
     ap.add_argument("--pdl", type=int, default=1, help="launch the kernels with programmatic dependent launch (weight prefetch of the next kernel overlaps the tail of the previous one)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--chain", type=int, default=0,
+                    help="c1: run the pair as one persistent launch (ullm_cuda_weight_matvec_chain_dev); measured slower than "
+                         "two programmatically chained launches for this pair, so off by default")
     ap.add_argument("--multi-graph", action="store_true", help="N>1: capture kernels + NCCL in a CUDA graph (off by default)")
     ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
     ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4", "c4gemm"],

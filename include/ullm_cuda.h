@@ -131,6 +131,27 @@ int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, c
  * share no data: q/k/v, gate/up): y[i] = W[i] x[i], device vectors. */
 int ullm_cuda_weight_matvec_batch_dev(ullm_cuda_ctx *ctx, size_t n, const ullm_cuda_weight *const *w,
                                       const float *const *d_x, float *const *d_y, void *stream);
+/* A list of matvecs on resident weights run as ONE persistent launch: the weight stream
+ * of op i+1 follows that of op i without a gap, and the grid synchronises only where
+ * `dep` says an op consumes what an earlier op of the list produced (x or res).  With the
+ * optional prologue x <- rmsnorm(x, d_norm_w, eps) (math.rs:82-86) and the epilogues
+ * y = W x | y = d_res + W x | y[j] = silu((W x)[2j]) * (W x)[2j+1] (rows stored as
+ * interleaved gate/up pairs; math.rs:103-105) this is the dense FFN / attention-projection
+ * chain of one decode step (lib.rs:807-969).  Q4_K and prepared Q6_K weights; other
+ * weights, or `no_chain` contexts, run the same ops as separate launches.  No counterpart
+ * in the reference (Metal encodes one compute pass per op, forward.rs:384-526). */
+enum { ULLM_EPI_STORE = 0, ULLM_EPI_RESIDUAL = 1, ULLM_EPI_SWIGLU = 2 };
+typedef struct ullm_chain_op {
+    const ullm_cuda_weight *w;
+    const float *d_x;      /* [in] device */
+    float *d_y;            /* [out] device ([out/2] for ULLM_EPI_SWIGLU) */
+    const float *d_norm_w; /* NULL = no RMSNorm prologue */
+    float eps;
+    int epi;
+    const float *d_res;    /* ULLM_EPI_RESIDUAL only; may alias d_y */
+    int dep;               /* non-zero: d_x / d_res were written by an earlier op of this list */
+} ullm_chain_op;
+int ullm_cuda_weight_matvec_chain_dev(ullm_cuda_ctx *ctx, size_t n, const ullm_chain_op *ops, void *stream);
 /* GpuForward::matmul (forward.rs:679-725) on a resident weight: x [s, in] f32
  * token-major -> y [s, out].  Prefill-sized batches run on the tensor cores
  * (activations and dequantized weights rounded to bf16, f32 accumulation). */

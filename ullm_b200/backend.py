@@ -71,6 +71,7 @@ SIGNATURES = {
     "ullm_cuda_weight_matvec": (_i, [_vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_dev": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_batch_dev": (_i, [_vp, _sz, _vp, _vp, _vp, _vp]),
+    "ullm_cuda_weight_matvec_chain_dev": (_i, [_vp, _sz, _vp, _vp]),
     "ullm_cuda_weight_matmul": (_i, [_vp, _vp, _vp, _vp, _sz]),
     "ullm_cuda_weight_matmul_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "ullm_cuda_weight_export": (_i, [_vp, _vp, _vp, _sz]),
@@ -354,6 +355,33 @@ class WeightBatch:
     def launch(self, stream=None):
         c = self._ctx
         c._check(c._lib.ullm_cuda_weight_matvec_batch_dev(c._h, self._n, self._w, self._x, self._y, stream))
+
+
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+
+
+class ChainOpC(C.Structure):
+    """``ullm_chain_op``."""
+
+    _fields_ = [("w", _vp), ("d_x", _vp), ("d_y", _vp), ("d_norm_w", _vp), ("eps", C.c_float), ("epi", _i), ("d_res", _vp), ("dep", _i)]
+
+
+class WeightChain:
+    """A fixed list of matvecs on resident weights run as one persistent launch
+    (``ullm_cuda_weight_matvec_chain_dev``).  ``ops``: dicts with ``w`` (:class:`Weight`), ``x``,
+    ``y`` (device addresses) and optionally ``norm_w``, ``eps``, ``epi``, ``res``, ``dep``."""
+
+    def __init__(self, ctx: CudaContext, ops):
+        self._ctx, self._n, self._keep = ctx, len(ops), [o["w"] for o in ops]
+        self._ops = (ChainOpC * len(ops))()
+        for c, o in zip(self._ops, ops):
+            c.w, c.d_x, c.d_y = o["w"]._h, o["x"], o["y"]
+            c.d_norm_w, c.eps, c.epi = o.get("norm_w"), o.get("eps", 0.0), o.get("epi", EPI_STORE)
+            c.d_res, c.dep = o.get("res"), 1 if o.get("dep") else 0
+
+    def launch(self, stream=None):
+        c = self._ctx
+        c._check(c._lib.ullm_cuda_weight_matvec_chain_dev(c._h, self._n, self._ops, stream))
 
 
 class MoeExpertsInput(C.Structure):

@@ -6,6 +6,9 @@
 #include "decode.h"
 #include "engine.h"
 
+#include <algorithm>
+#include <vector>
+
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -58,6 +61,7 @@ void ullm_cuda_ctx_destroy(ullm_cuda_ctx *c) {
         cudaStreamDestroy(c->stream);
     }
     if (c->h_status) cudaFreeHost((void *)c->h_status);
+    if (c->d_sync) cudaFree(c->d_sync);
     for (auto &s : c->scratch)
         if (s.ptr) cudaFree(s.ptr);
     delete c;
@@ -360,14 +364,94 @@ int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *c, const ullm_cuda_weight *w, con
     return ULLM_OK;
 }
 
+// The grid barrier counter of the chain kernel (one unsigned per context, allocated on first use).
+static int ctx_sync_word(ullm_cuda_ctx *c, unsigned **out) {
+    if (!c->d_sync) {
+        cudaError_t e = cudaMalloc((void **)&c->d_sync, 256);
+        if (e == cudaSuccess) e = cudaMemset(c->d_sync, 0, 256);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            c->d_sync = nullptr;
+            return ctx_fail(c, ULLM_ERR_OOM, "cudaMalloc for the chain barrier failed: %s", cudaGetErrorString(e));
+        }
+    }
+    *out = c->d_sync;
+    return ULLM_OK;
+}
+
+int ullm_cuda_weight_matvec_chain_dev(ullm_cuda_ctx *c, size_t n, const ullm_chain_op *ops, void *stream) {
+    if (!c || (n && !ops)) return ULLM_ERR_INVALID;
+    if (n == 0) return ULLM_OK;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    std::vector<MatvecChainOp> v(n);
+    bool chain_ok = !c->force_generic && !c->no_chain;
+    for (size_t i = 0; i < n; ++i) {
+        const ullm_chain_op &o = ops[i];
+        if (!o.w || !o.d_x || !o.d_y) return ULLM_ERR_INVALID;
+        if (o.epi < ULLM_EPI_STORE || o.epi > ULLM_EPI_SWIGLU) return ctx_fail(c, ULLM_ERR_INVALID, "op %zu: unknown epilogue %d", i, o.epi);
+        if (o.epi == ULLM_EPI_RESIDUAL && !o.d_res) return ctx_fail(c, ULLM_ERR_INVALID, "op %zu: residual epilogue without d_res", i);
+        MatvecChainOp &m = v[i];
+        m.fmt = o.w->fmt, m.w = o.w->w, m.x = o.d_x, m.y = o.d_y, m.out_dim = o.w->out, m.in_dim = o.w->cols;
+        m.norm_w = o.d_norm_w, m.eps = o.eps, m.epi = o.epi, m.res = o.d_res, m.dep = o.dep != 0;
+        chain_ok = chain_ok && matvec_chain_supported(m.fmt, m.out_dim, m.in_dim, m.epi);
+    }
+    // one persistent launch per run of at most 12 ops; anything it cannot take goes op by op
+    if (chain_ok) {
+        unsigned *d_sync = nullptr;
+        int rc = ctx_sync_word(c, &d_sync);
+        if (rc) return rc;
+        size_t i = 0;
+        bool fell_back = false;
+        while (i < n) {
+            const size_t m = std::min<size_t>(12, n - i);
+            if (i > 0) v[i].dep = false; // ordered after the previous launch by the stream
+            cudaError_t e = launch_matvec_chain(c->dev, (int)m, v.data() + i, d_sync, c->d_status, st, c->use_pdl);
+            if (e == cudaErrorNotSupported) {
+                cudaGetLastError();
+                fell_back = true;
+                break;
+            }
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return ctx_fail(c, ULLM_ERR_CUDA, "matvec chain launch: %s", cudaGetErrorString(e));
+            }
+            i += m;
+        }
+        if (!fell_back) {
+            c->last_plan = MatvecPlan();
+            c->last_plan.streamed = true, c->last_plan.warps = 16, c->last_plan.grid = -2; // marks the chain kernel
+            return ULLM_OK;
+        }
+        if (i > 0) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "matvec chain: ops %zu.. cannot be streamed", i);
+    }
+    for (size_t i = 0; i < n; ++i) {
+        const ullm_chain_op &o = ops[i];
+        MlxTables tb;
+        tb.scales = o.w->scales, tb.biases = o.w->biases, tb.group = o.w->group, tb.elem_bytes = o.w->table_bytes;
+        MatvecOpts mo;
+        mo.force_generic = c->force_generic && o.w->fmt != FMT_Q6KR, mo.pdl = c->use_pdl, mo.plan_out = &c->last_plan;
+        mo.norm_w = o.d_norm_w, mo.eps = o.eps, mo.epi = o.epi, mo.res = o.d_res;
+        cudaError_t e = launch_matvec(c->dev, o.w->fmt, o.w->w, tb, o.d_x, o.d_y, o.w->out, o.w->cols, c->d_status, st, mo);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return ctx_fail(c, e == cudaErrorNotSupported ? ULLM_ERR_UNSUPPORTED : ULLM_ERR_CUDA, "matvec %zu of the chain: %s", i,
+                            cudaGetErrorString(e));
+        }
+    }
+    return ULLM_OK;
+}
+
 int ullm_cuda_weight_matvec_batch_dev(ullm_cuda_ctx *c, size_t n, const ullm_cuda_weight *const *w, const float *const *d_x,
                                       float *const *d_y, void *stream) {
     if (!c || (n && (!w || !d_x || !d_y))) return ULLM_ERR_INVALID;
+    std::vector<ullm_chain_op> ops(n);
     for (size_t i = 0; i < n; ++i) {
-        int rc = ullm_cuda_weight_matvec_dev(c, w[i], d_x[i], d_y[i], stream);
-        if (rc) return rc;
+        if (!w[i]) return ULLM_ERR_INVALID;
+        ops[i] = ullm_chain_op{};
+        ops[i].w = w[i], ops[i].d_x = d_x[i], ops[i].d_y = d_y[i];
     }
-    return ULLM_OK;
+    return ullm_cuda_weight_matvec_chain_dev(c, n, ops.data(), stream);
 }
 
 int ullm_cuda_weight_matvec(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const float *x, float *y) {
@@ -538,6 +622,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     else if (!strcmp(key, "pdl")) c->use_pdl = value != 0;
     else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
     else if (!strcmp(key, "gemm_min_s")) c->gemm_min_s = value;
+    else if (!strcmp(key, "no_chain")) c->no_chain = value != 0;
     else if (!strcmp(key, "gemm_mode")) gemm_set_debug_mode(value);
     else if (!strcmp(key, "skip_compute")) matvec_set_skip_compute(value);
     else if (!strcmp(key, "chunk")) matvec_set_chunk(value);

@@ -30,6 +30,8 @@ struct ullm_cuda_ctx {
     bool force_generic = false;
     bool use_pdl = false;
     bool no_prepare = false; // keep Q6_K weights in their verbatim bytes (tests)
+    bool no_chain = false;   // run op lists one kernel per op (tests, comparisons)
+    unsigned *d_sync = nullptr; // grid-barrier counter of the chain kernel
     int plan_wr = 0, plan_rw = 0, plan_stages = 0;
     int gemm_min_s = 32; // batches below this many tokens use per-token matvecs
     ullm::MatvecPlan last_plan;
@@ -81,6 +83,7 @@ inline int ctx_scratch(ullm_cuda_ctx *c, int slot, size_t bytes, void **out) {
 inline int ctx_check_status(ullm_cuda_ctx *c) {
     if (c->h_status && *c->h_status != ullm::DEV_OK) {
         *c->h_status = ullm::DEV_OK;
+        if (c->d_sync) cudaMemset(c->d_sync, 0, 256); // a chain that gave up may have left its barrier half-way
         return ctx_fail(c, 4, "a device-side bounded wait expired (kernel gave up instead of hanging)");
     }
     return 0;

@@ -52,6 +52,23 @@ struct MatvecOpts {
 cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const MlxTables &tb, const float *d_x,
                           float *d_y, size_t out_dim, size_t in_dim, int *d_status, cudaStream_t st,
                           const MatvecOpts &opts = MatvecOpts());
+// A list of matvecs in one persistent launch (matvec_chain.cu).  `dep` marks an op whose x or
+// res was written by an earlier op of the same list.  d_sync: one zero-able unsigned in device memory.
+struct MatvecChainOp {
+    int fmt = 0; // FMT_Q4K or FMT_Q6KR
+    const void *w = nullptr;
+    const float *x = nullptr;
+    float *y = nullptr;
+    size_t out_dim = 0, in_dim = 0;
+    const float *norm_w = nullptr;
+    float eps = 0.f;
+    int epi = EPI_STORE;
+    const float *res = nullptr;
+    bool dep = false;
+};
+bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi);
+cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainOp *ops, unsigned *d_sync, int *d_status,
+                                cudaStream_t st, bool pdl);
 // Tuning override for tests / sweeps: force the row-slice count, rows per warp and
 // ring depth of the streamed plan (0 = automatic).
 void matvec_set_plan_override(int wr, int rw, int stages);

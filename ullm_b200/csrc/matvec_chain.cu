@@ -1,0 +1,353 @@
+// A list of matvecs in ONE persistent launch (Q4_K and prepared Q6_K weights).
+//
+// A decode step is a chain of small dependent matvecs: W_o, gate|up, down, the next layer's
+// q|k and v ... (crates/ullm-model/src/lib.rs:807-969).  Launched one kernel each, every
+// link pays the fixed cost of a launch: the grid drains, the next grid starts, its first
+// weight tiles take a DRAM round trip, and only then does the stream run — 4-5 us against
+// 0.5-3 us of streaming for matrices of 2-19 MB.  Here the grid stays resident (one CTA per
+// SM) and walks the whole list:
+//   * the producer warp of every CTA streams the tiles of op 0, op 1, ... back to back
+//     through one shared-memory ring — weights do not depend on activations, so the stream
+//     never stops at an op boundary;
+//   * the consumer warps do, per op, what matvec_stream_kernel does (matvec.cu): fixed-point
+//     image of x in registers, dp4a row sums, optional RMSNorm prologue and residual / SwiGLU
+//     epilogue — and wait at a grid-wide barrier only where an op reads what an earlier op
+//     of the same launch wrote;
+//   * that barrier is an atomic counter in global memory with a bounded, sleeping spin
+//     (the grid never exceeds the SM count and every CTA takes a whole SM, so all CTAs are
+//     resident; if the wait still expires the kernel records DEV_TIMEOUT, stops computing
+//     and walks out through its barriers).
+#include "kernels.h"
+#include "matvec_core.cuh"
+
+#include <algorithm>
+
+namespace ullm {
+
+constexpr int CHAIN_MAX_OPS = 12;
+
+struct ChainOpDev {
+    const uint8_t *w;
+    const float *x;      // [in_dim]
+    float *y;            // [out_dim] (EPI_SWIGLU: [out_dim / 2])
+    const float *norm_w; // prologue: x <- rmsnorm(x, norm_w, eps) when set
+    const float *res;    // EPI_RESIDUAL
+    float eps;
+    int epi, fmt;
+    int dep;             // x / res come from an earlier op of this launch: grid barrier first
+    uint32_t out_dim, in_dim, row_bytes, gran, ncg;
+    uint32_t R, WC, WR, rw, g; // tile rows, column-group warps, row-slice warps, rows per warp, groups per warp
+};
+struct ChainParams {
+    ChainOpDev op[CHAIN_MAX_OPS];
+    int n_ops;
+    unsigned *sync; // {arrival count, generation}: zero once, self-restoring
+    int *status;
+    uint32_t NW, S, stage_bytes, off_part, off_prep, off_ring, chunk;
+};
+
+__device__ __forceinline__ void chain_row_range(const ChainOpDev &o, uint32_t &rbeg, uint32_t &rend) {
+    const uint32_t units = o.out_dim / o.gran;
+    rbeg = (uint32_t)(((uint64_t)units * blockIdx.x) / gridDim.x) * o.gran;
+    rend = blockIdx.x + 1 == gridDim.x ? o.out_dim : (uint32_t)(((uint64_t)units * (blockIdx.x + 1)) / gridDim.x) * o.gran;
+}
+
+// Grid-wide barrier of the consumer threads.  sync[0] counts arrivals, sync[1] is the generation:
+// the last CTA to arrive clears the count and then bumps the generation, the others wait for the
+// bump.  The words return to (0, g+1), so launches need no reset between them (after a timeout
+// the host clears them).  Bounded: about a second of sleeping polls.
+__device__ __forceinline__ bool chain_grid_sync(unsigned *sync, uint32_t nthr_c, uint32_t tid, int *ok_s) {
+    asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // this CTA's stores of the earlier ops are issued
+    if (tid == 0) {
+        unsigned g;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(sync + 1) : "memory");
+        __threadfence();
+        int ok = 1;
+        if (atomicAdd(sync, 1u) == gridDim.x - 1) {
+            atomicExch(sync, 0u);
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sync + 1), "r"(g + 1) : "memory");
+        } else {
+            const long long t0 = clock64();
+            for (;;) {
+                unsigned v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sync + 1) : "memory");
+                if (v != g) break;
+                asm volatile("nanosleep.u32 40;" ::: "memory");
+                if (clock64() - t0 > (1ll << 31)) {
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+        *ok_s = ok;
+        __threadfence();
+    }
+    asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+    return *ok_s != 0;
+}
+
+// One op, consumer side.  kbase = number of tiles this CTA has streamed before this op.
+template <int FMT, int RW, int G>
+__device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainParams &p, uint8_t *smem, uint32_t kbase,
+                                              uint32_t tid, bool &aborted) {
+    constexpr int XR = FmtTraits<FMT>::XREGS;
+    uint64_t *full = (uint64_t *)smem, *empty = full + p.S;
+    float *part = (float *)(smem + p.off_part);
+    uint32_t *prep = (uint32_t *)(smem + p.off_prep);
+    uint8_t *ring = smem + p.off_ring;
+    const uint32_t warp = tid >> 5, lane = tid & 31, nthr_c = p.NW * 32;
+    uint32_t rbeg, rend;
+    chain_row_range(o, rbeg, rend);
+    const uint32_t ntiles = (rend - rbeg + o.R - 1) / o.R;
+
+    // ---- x: optional RMSNorm (math.rs:82-86), then the fixed-point register image ----
+    ActSrc src{o.x, o.norm_w, 0.f};
+    if (o.norm_w) {
+        float ss = 0.f;
+        for (uint32_t t = tid; t < (o.in_dim >> 3); t += nthr_c) {
+            const float4 a = __ldcg((const float4 *)(o.x + 8 * t)), b = __ldcg((const float4 *)(o.x + 8 * t + 4));
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) part[warp] = ss;
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+        float tot = 0.f;
+        for (uint32_t w = 0; w < p.NW; ++w) tot += part[w];
+        src.inv = 1.0f / sqrtf(tot / (float)o.in_dim + o.eps);
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // part is reused below
+    }
+    prep_image<FMT>(src, o.in_dim, prep, tid, nthr_c);
+    asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+
+    const bool active = warp < o.WC * o.WR; // the op may use fewer warps than the launch has
+    const uint32_t rs = warp / o.WC, cgw = warp % o.WC;
+    uint32_t X[G][XR];
+    bool live[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const uint32_t cg = cgw + g * o.WC;
+        live[g] = active && cg < o.ncg && (cg * 8u + (lane >> 2)) * QK_K < o.in_dim;
+#pragma unroll
+        for (int k = 0; k < XR; ++k) X[g][k] = live[g] ? prep[((size_t)cg * XR + k) * 32 + lane] : 0u;
+    }
+    const uint32_t nb = o.in_dim / QK_K;
+
+    auto flush = [&](uint32_t kt) { // sums the column-group partials of tile kt (see matvec.cu)
+        if (!active || cgw != 0 || lane >= RW) return;
+        const float *pt = part + ((size_t)(((kt / p.S) & 1) * p.S + kt % p.S) * o.R) * o.WC;
+        const uint32_t row = rs * RW + lane, gr = rbeg + kt * o.R + row;
+        if (gr >= rend || aborted) return;
+        float acc = 0.f;
+        for (uint32_t c = 0; c < o.WC; ++c) acc += pt[row * o.WC + c];
+        if (o.epi == EPI_STORE) o.y[gr] = acc;
+        else if (o.epi == EPI_RESIDUAL) o.y[gr] = __ldcg(o.res + gr) + acc;
+        else if ((lane & 1) == 0) {
+            float up = 0.f;
+            for (uint32_t c = 0; c < o.WC; ++c) up += pt[(row + 1) * o.WC + c];
+            o.y[gr >> 1] = acc / (1.0f + expf(-acc)) * up;
+        }
+    };
+    for (uint32_t k = 0; k < ntiles; ++k) {
+        const uint32_t kg = kbase + k, s = kg % p.S;
+        if (!aborted && !wait_or_timeout(&full[s], (kg / p.S) & 1)) aborted = true;
+        if (o.WC > 1 && k >= p.S) flush(k - p.S);
+        const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
+        const uint32_t r0 = rbeg + k * o.R;
+        if (active) {
+            float v[RW];
+#pragma unroll
+            for (int rr = 0; rr < RW; ++rr) {
+                v[rr] = 0.f;
+                const uint32_t rl = rs * RW + rr;
+                if (!aborted && r0 + rl < rend) {
+                    const uint32_t row_addr = stage + rl * o.row_bytes;
+                    const uint32_t ts = row_addr + 192u * nb, tb2 = row_addr + 208u * nb; // prepared Q6_K planes
+#pragma unroll
+                    for (int g = 0; g < G; ++g)
+                        if (live[g]) v[rr] += row_partial<FMT, float>(row_addr, X[g], cgw + g * o.WC, lane, ts, tb2, 0u);
+                }
+            }
+            uint32_t myrow;
+            const float r = warp_reduce_rows<RW>(v, lane, myrow);
+            const uint32_t rl = rs * RW + myrow;
+            if (o.WC == 1) {
+                float other = 0.f;
+                if (RW >= 2) other = __shfl_xor_sync(0xffffffffu, r, RW == 2 ? 16 : 8);
+                const bool writer = (lane & 7) == 0 && (RW == 4 || (lane & 8) == 0) && (RW > 1 || lane == 0);
+                if (writer && r0 + rl < rend && !aborted) {
+                    if (o.epi == EPI_STORE) o.y[r0 + rl] = r;
+                    else if (o.epi == EPI_RESIDUAL) o.y[r0 + rl] = __ldcg(o.res + r0 + rl) + r;
+                    else if ((myrow & 1) == 0) o.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
+                }
+            } else {
+                float *pt = part + ((size_t)(((k / p.S) & 1) * p.S + k % p.S) * o.R) * o.WC;
+                if ((lane & 7) == 0 && (RW == 4 || (lane & 8) == 0)) pt[rl * o.WC + cgw] = r;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]); // partials written, stage may be refilled
+    }
+    if (o.WC > 1) {
+        asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // all partials of the last tiles are in
+        for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt);
+    }
+}
+
+constexpr int CHAIN_MAX_THREADS = 17 * 32; // 16 consumer warps + the producer warp
+
+__global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(const __grid_constant__ ChainParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = (uint64_t *)smem, *empty = full + p.S;
+    int &sync_ok = *(int *)(smem + 128); // after the 2 x 8 mbarriers; static shared memory would eat into the opt-in maximum
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool producer = warp == p.NW;
+    pdl_launch_dependents();
+    if (tid == 0) {
+        for (uint32_t s = 0; s < p.S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], p.NW);
+        }
+        sync_ok = 1;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (producer) {
+        // the weight tiles of every op, back to back: one tile = one contiguous byte range
+        uint8_t *ring = smem + p.off_ring;
+        uint32_t kg = 0;
+        for (int i = 0; i < p.n_ops; ++i) {
+            const ChainOpDev &o = p.op[i];
+            uint32_t rbeg, rend;
+            chain_row_range(o, rbeg, rend);
+            const uint32_t ntiles = (rend - rbeg + o.R - 1) / o.R;
+            for (uint32_t k = 0; k < ntiles; ++k, ++kg) {
+                const uint32_t s = kg % p.S;
+                bool ok = true;
+                if (lane == 0 && kg >= p.S) ok = wait_or_timeout(&empty[s], ((kg / p.S) - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
+                    return;
+                }
+                const uint32_t r0 = rbeg + k * o.R, rows = min(o.R, rend - r0), wb = rows * o.row_bytes;
+                uint8_t *dst = ring + (size_t)s * p.stage_bytes;
+                if (lane == 0) mbar_arrive_expect_tx(&full[s], wb);
+                __syncwarp();
+                const uint8_t *src = o.w + (size_t)r0 * o.row_bytes;
+                for (uint32_t off = lane * p.chunk; off < wb; off += 32 * p.chunk)
+                    bulk_g2s(dst + off, src + off, min(p.chunk, wb - off), &full[s]);
+            }
+        }
+        return;
+    }
+
+    // ---- consumer warps ----
+    pdl_wait_prior(); // activations may come from the previous kernel in the stream
+    const uint32_t nthr_c = p.NW * 32;
+    bool aborted = false;
+    uint32_t kbase = 0;
+    for (int i = 0; i < p.n_ops; ++i) {
+        const ChainOpDev &o = p.op[i];
+        if (o.dep && !chain_grid_sync(p.sync, nthr_c, tid, &sync_ok)) aborted = true;
+#define ULLM_CHAIN_CASE(F, RWv, Gv) \
+    if (o.fmt == F && o.rw == RWv && o.g == Gv) chain_consume<F, RWv, Gv>(o, p, smem, kbase, tid, aborted);
+        ULLM_CHAIN_CASE(FMT_Q4K, 1, 1) ULLM_CHAIN_CASE(FMT_Q4K, 2, 1) ULLM_CHAIN_CASE(FMT_Q4K, 4, 1)
+        ULLM_CHAIN_CASE(FMT_Q6KR, 1, 1) ULLM_CHAIN_CASE(FMT_Q6KR, 2, 1) ULLM_CHAIN_CASE(FMT_Q6KR, 4, 1)
+#undef ULLM_CHAIN_CASE
+        uint32_t rbeg, rend;
+        chain_row_range(o, rbeg, rend);
+        kbase += (rend - rbeg + o.R - 1) / o.R;
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // prep / part areas are free for the next op
+    }
+    if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+static inline uint32_t align_up_u32(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+static inline uint32_t gcd_u(uint32_t a, uint32_t b) {
+    while (b) {
+        const uint32_t t = a % b;
+        a = b, b = t;
+    }
+    return a;
+}
+
+bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi) {
+    if (fmt != FMT_Q4K && fmt != FMT_Q6KR) return false;
+    if (in_dim % QK_K || in_dim == 0 || out_dim == 0 || out_dim > 0x7fffffffull) return false;
+    if (fmt == FMT_Q6KR && in_dim % 2048) return false;
+    if (epi == EPI_SWIGLU && (out_dim & 1)) return false;
+    return (in_dim + 2047) / 2048 <= 16; // one column group (2048 columns) per warp, 16 warps
+}
+
+cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainOp *ops, unsigned *d_sync, int *d_status,
+                                cudaStream_t st, bool pdl) {
+    if (n <= 0 || n > CHAIN_MAX_OPS) return cudaErrorInvalidValue;
+    ChainParams p{};
+    p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 16, p.chunk = 4096;
+    const int budget = dev.max_smem_optin - 1024;
+    uint32_t max_stage = 0, max_part = 128, max_prep = 0;
+    const uint32_t grid = (uint32_t)dev.sm_count;
+    for (int i = 0; i < n; ++i) {
+        const MatvecChainOp &h = ops[i];
+        if (!matvec_chain_supported(h.fmt, h.out_dim, h.in_dim, h.epi)) return cudaErrorNotSupported;
+        if (((uintptr_t)h.w | (uintptr_t)h.x) & 15 || (h.norm_w && ((uintptr_t)h.norm_w & 15))) return cudaErrorNotSupported;
+        ChainOpDev &o = p.op[i];
+        o.w = (const uint8_t *)h.w, o.x = h.x, o.y = h.y, o.norm_w = h.norm_w, o.res = h.res, o.eps = h.eps, o.epi = h.epi;
+        o.fmt = h.fmt, o.dep = h.dep ? 1 : 0, o.out_dim = (uint32_t)h.out_dim, o.in_dim = (uint32_t)h.in_dim;
+        o.row_bytes = (uint32_t)(h.in_dim / QK_K) * (h.fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+        o.gran = 16 / gcd_u(o.row_bytes, 16);
+        if (h.epi == EPI_SWIGLU) o.gran = std::max(o.gran, 2u);
+        if (o.out_dim % o.gran) return cudaErrorNotSupported;
+        o.ncg = (uint32_t)((h.in_dim + 2047) / 2048);
+        o.g = (o.ncg + 15) / 16;
+        o.WC = (o.ncg + o.g - 1) / o.g;
+        o.WR = p.NW / o.WC;
+        // rows per warp: the largest of 4, 2, 1 whose tile stays within 56 KB, unless a tile of
+        // half the rows already covers this CTA's whole share (then the rest would be padding)
+        const uint32_t rows_cta = (o.out_dim / o.gran + grid - 1) / grid * o.gran;
+        const uint32_t rw_min = h.epi == EPI_SWIGLU ? 2u : 1u;
+        o.rw = 0;
+        for (uint32_t rw = 4; rw >= rw_min; rw /= 2) {
+            const uint32_t R = o.WR * rw;
+            if (R % o.gran || (uint64_t)R * o.row_bytes > 57344) continue;
+            if (rw > rw_min && o.WR * (rw / 2) >= rows_cta && (o.WR * (rw / 2)) % o.gran == 0) continue;
+            o.rw = rw;
+            break;
+        }
+        if (!o.rw) return cudaErrorNotSupported;
+        o.R = o.WR * o.rw;
+        max_stage = std::max(max_stage, align_up_u32(o.R * o.row_bytes, 128));
+        max_part = std::max(max_part, 2u * 8u * o.R * o.WC * 4u);
+        max_prep = std::max(max_prep, o.ncg * (uint32_t)(h.fmt == FMT_Q4K ? XREGS_Q4K : XREGS_Q6KR) * 32u * 4u);
+    }
+    // CTAs whose share of an op is empty stream nothing for it, but still take part in the barriers
+    p.off_part = 256;
+    p.off_prep = align_up_u32(p.off_part + max_part, 128);
+    p.off_ring = align_up_u32(p.off_prep + max_prep, 128);
+    p.stage_bytes = max_stage;
+    if ((int)p.off_ring + 2 * (int)max_stage > budget) return cudaErrorNotSupported;
+    p.S = std::min<uint32_t>(8, (uint32_t)(budget - (int)p.off_ring) / max_stage);
+    const uint32_t smem = p.off_ring + p.S * max_stage;
+    static bool attr_set[64] = {};
+    int devid = 0;
+    cudaGetDevice(&devid);
+    if (devid < 64 && !attr_set[devid]) {
+        cudaError_t e = cudaFuncSetAttribute(matvec_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[devid] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid), cfg.blockDim = dim3((p.NW + 1) * 32), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, matvec_chain_kernel, p);
+}
+
+} // namespace ullm
