@@ -107,3 +107,50 @@ def test_llama_1b_shape_greedy_sequence(ctx):
     got_tokens = gf.greedy(embd, m["tok_embd"][0], tok, n_pre + n_prompt, n_gen)
     assert got_tokens.tolist() == ref_tokens, (got_tokens.tolist(), ref_tokens, margins)
     gf.free()
+
+
+def test_engine_built_from_a_gguf_file_equals_the_one_built_from_arrays(ctx, tmp_path):
+    """The GGUF feed (include/ullm_gguf.h -> ullm_cuda_forward_create_gguf): same weights through a
+    .gguf file on disk must give bit-identical logits, and a file with tied embeddings or with a
+    tensor of an unbuilt variant behaves as LlamaModel::from_gguf says (lib.rs:270-304)."""
+    import os
+
+    from ullm_b200 import gguf
+
+    p = dict(synth.LLAMA_TINY)
+    m = synth.gen_llama_model(p, 11)
+    path = os.path.join(tmp_path, "tiny.gguf")
+    with open(path, "wb") as f:
+        f.write(gguf.llama_to_gguf(m, alignment=64))
+    g = gguf.Gguf(path)
+    a, b = backend.GpuForward(ctx, m, kv_f16=True), backend.GpuForward.from_gguf(ctx, g, kv_f16=True)
+    om = oracle_model(m, True)
+    tok = 3
+    for pos in range(4):
+        x = om.embed(tok)
+        la, lb = a.forward(x, pos), b.forward(x, pos)
+        assert np.array_equal(la, lb), pos
+        assert synth.rel_err(lb, om.forward(tok, pos)) < 1e-3
+        tok = int(np.argmax(lb))
+    # greedy continuation with the embedding table taken from the file
+    t = g.tensor("token_embd.weight")
+    embd = ctx.upload(t["data"])
+    assert np.array_equal(a.greedy(embd, t["dtype"], tok, 4, 6), b.greedy(embd, t["dtype"], tok, 4, 6))
+    a.free(), b.free()
+    # a Qwen2-style bias tensor: this decode variant is not built -> Unsupported, not ignored
+    md = [(k, ty, v) for k, ty, v in [("general.architecture", gguf.T_STRING, "llama")]]
+    blob = gguf.llama_to_gguf(m)
+    g2 = gguf.Gguf(blob)
+    ts = [(x["name"], x["dtype"], x["shape"], x["data"].copy()) for x in g2.tensors()]
+    ts.append(("blk.0.attn_q.bias", 0, (p["n_head"] * p["head_dim"],), np.zeros(p["n_head"] * p["head_dim"], np.float32)))
+    keys = [(k, gguf.T_STRING if isinstance(g2.get(k), str) else (gguf.T_F32 if isinstance(g2.get(k), float) else gguf.T_U32), g2.get(k)) for k in g2.keys()]
+    with pytest.raises(backend.Unsupported):
+        backend.GpuForward.from_gguf(ctx, gguf.Gguf(gguf.write_gguf(keys, ts)))
+    # tied embeddings: no output.weight -> the embedding matrix is the output projection
+    ts_tied = [x for x in ts[:-1] if x[0] != "output.weight"]
+    tied = backend.GpuForward.from_gguf(ctx, gguf.Gguf(gguf.write_gguf(keys, ts_tied)))
+    m_tied = dict(m, output=m["tok_embd"])
+    ref = backend.GpuForward(ctx, m_tied)
+    x = om.embed(5)
+    assert np.array_equal(tied.forward(x, 0), ref.forward(x, 0))
+    tied.free(), ref.free()

@@ -85,6 +85,7 @@ SIGNATURES = {
     "ullm_cuda_moe_ffn_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     "ullm_cuda_moe_ffn_noalloc": (_i, [_i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, C.c_char_p, _sz]),
     "ullm_cuda_forward_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "ullm_cuda_forward_create_gguf": (_i, [_vp, _vp, _i, C.POINTER(_vp)]),
     "ullm_cuda_forward_destroy": (None, [_vp]),
     "ullm_cuda_forward": (_i, [_vp, _vp, _sz, _vp]),
     "ullm_cuda_forward_set_kv": (_i, [_vp, _sz, _sz, _vp, _vp]),
@@ -493,6 +494,19 @@ class GpuForward:
         ctx._check(ctx._lib.ullm_cuda_forward_create(ctx._h, C.byref(inp), C.byref(h)))
         self._h = h.value
         self._logits = np.empty(p["vocab"], np.float32)
+
+    @classmethod
+    def from_gguf(cls, ctx: CudaContext, gguf, kv_f16: bool = False) -> "GpuForward":
+        """Builds the engine from an open :class:`ullm_b200.gguf.Gguf` (``ullm_cuda_forward_create_gguf``)."""
+        self = cls.__new__(cls)
+        self._ctx = ctx
+        lp = gguf.llama_params()
+        self.params = dict(lp)
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_forward_create_gguf(ctx._h, gguf._h, 1 if kv_f16 else 0, C.byref(h)))
+        self._h = h.value
+        self._logits = np.empty(lp["vocab"], np.float32)
+        return self
 
     def forward(self, x_init, pos: int) -> np.ndarray:
         """One token: ``x_init`` is its embedding row; returns the vocab logits (forward.rs:384)."""

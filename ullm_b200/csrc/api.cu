@@ -3,10 +3,12 @@
 // failures are turned into status codes with a message, and nothing here ever
 // computes on the CPU.
 #include "../../include/ullm_cuda.h"
+#include "../../include/ullm_gguf.h"
 #include "decode.h"
 #include "engine.h"
 
 #include <algorithm>
+#include <string>
 #include <vector>
 
 #include <cstdarg>
@@ -857,4 +859,100 @@ int ullm_cuda_forward_greedy(ullm_cuda_fwd *f, const ullm_cuda_buf *embd, int em
     if (e == cudaErrorNotSupported) return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "a layer shape is outside the fused decode path");
     if (e != cudaSuccess) return fwd_fail(f, e, "greedy decode");
     return fwd_status(f);
+}
+
+// ---------------------------------------------------------------------------
+// GpuForward straight from a GGUF file (LlamaModel::from_gguf + build_gpu,
+// crates/ullm-model/src/lib.rs:174-301 and :712-805)
+// ---------------------------------------------------------------------------
+static float half_bits_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, mant = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (mant == 0) bits = sign;
+        else { // subnormal: mant * 2^-24 (crates/ullm-core/src/dequant.rs:20)
+            float f = (float)mant * 5.9604644775390625e-8f;
+            memcpy(&bits, &f, 4);
+            bits |= sign;
+        }
+    } else if (exp == 31) bits = sign | 0x7f800000u | (mant << 13);
+    else bits = sign | ((exp + 112u) << 23) | (mant << 13);
+    float out;
+    memcpy(&out, &bits, 4);
+    return out;
+}
+
+int ullm_cuda_forward_create_gguf(ullm_cuda_ctx *c, const ullm_gguf *g, int kv_f16, ullm_cuda_fwd **out) {
+    if (!c || !g || !out) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    char msg[256] = {0};
+    ullm_gguf_llama_params lp;
+    int rc = ullm_gguf_llama_params_get(g, &lp, msg, sizeof msg);
+    if (rc == ULLM_GGUF_ERR_UNSUPPORTED) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s", msg);
+    if (rc) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", msg);
+    const size_t qd = lp.n_head * lp.head_dim, kvd = lp.n_kv_head * lp.head_dim;
+    // f32 view of a norm vector (tensor_f32: F32 as is, F16 / BF16 widened)
+    std::vector<std::vector<float>> norms;
+    norms.reserve(2 * lp.n_layer + 1);
+    auto norm = [&](const std::string &name, size_t n, const float **dst) -> int {
+        ullm_gguf_tensor t;
+        if (ullm_gguf_tensor_find(g, name.c_str(), &t)) return ctx_fail(c, ULLM_ERR_FORMAT, "missing tensor '%s'", name.c_str());
+        uint64_t cnt = 1;
+        for (uint32_t d = 0; d < t.n_dims; ++d) cnt *= t.shape[d];
+        if (cnt != n) return ctx_fail(c, ULLM_ERR_FORMAT, "tensor '%s' has %llu elements, expected %zu", name.c_str(), (unsigned long long)cnt, n);
+        norms.emplace_back(n);
+        std::vector<float> &v = norms.back();
+        if (t.dtype == ULLM_DTYPE_F32) memcpy(v.data(), t.data, n * 4);
+        else if (t.dtype == ULLM_DTYPE_F16)
+            for (size_t i = 0; i < n; ++i) v[i] = half_bits_to_float(((const uint16_t *)t.data)[i]);
+        else if (t.dtype == ULLM_DTYPE_BF16)
+            for (size_t i = 0; i < n; ++i) {
+                const uint32_t b = (uint32_t)((const uint16_t *)t.data)[i] << 16;
+                memcpy(&v[i], &b, 4);
+            }
+        else return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "tensor '%s': norm weights of ggml type %d", name.c_str(), t.dtype);
+        *dst = v.data();
+        return ULLM_OK;
+    };
+    auto weight = [&](const std::string &name, size_t out_dim, size_t cols, ullm_gpu_weight *w, bool optional) -> int {
+        ullm_gguf_tensor t;
+        if (ullm_gguf_tensor_find(g, name.c_str(), &t)) return optional ? -1 : ctx_fail(c, ULLM_ERR_FORMAT, "missing tensor '%s'", name.c_str());
+        if (t.n_dims != 2 || t.shape[0] != out_dim || t.shape[1] != cols)
+            return ctx_fail(c, ULLM_ERR_FORMAT, "tensor '%s' is not [%zu, %zu]", name.c_str(), out_dim, cols);
+        memset(w, 0, sizeof *w);
+        w->dtype = t.dtype, w->bytes = t.data, w->len = (size_t)t.nbytes, w->out = out_dim, w->cols = cols;
+        return ULLM_OK;
+    };
+    std::vector<ullm_gpu_layer_input> layers(lp.n_layer);
+    for (size_t i = 0; i < lp.n_layer; ++i) {
+        const std::string b = "blk." + std::to_string(i) + ".";
+        ullm_gpu_layer_input &l = layers[i];
+        memset(&l, 0, sizeof l);
+        if ((rc = norm(b + "attn_norm.weight", lp.n_embd, &l.attn_norm)) || (rc = norm(b + "ffn_norm.weight", lp.n_embd, &l.ffn_norm)) ||
+            (rc = weight(b + "attn_q.weight", qd, lp.n_embd, &l.wq, false)) || (rc = weight(b + "attn_k.weight", kvd, lp.n_embd, &l.wk, false)) ||
+            (rc = weight(b + "attn_v.weight", kvd, lp.n_embd, &l.wv, false)) || (rc = weight(b + "attn_output.weight", lp.n_embd, qd, &l.wo, false)) ||
+            (rc = weight(b + "ffn_gate.weight", lp.n_ff, lp.n_embd, &l.w_gate, false)) ||
+            (rc = weight(b + "ffn_up.weight", lp.n_ff, lp.n_embd, &l.w_up, false)) ||
+            (rc = weight(b + "ffn_down.weight", lp.n_embd, lp.n_ff, &l.w_down, false)))
+            return rc;
+        // tensors this backend has no kernel for are refused, not ignored
+        for (const char *extra : {"attn_q.bias", "attn_k.bias", "attn_v.bias", "attn_q_norm.weight", "attn_k_norm.weight",
+                                  "post_attention_norm.weight", "post_ffw_norm.weight"}) {
+            ullm_gguf_tensor t;
+            if (ullm_gguf_tensor_find(g, (b + extra).c_str(), &t) == ULLM_GGUF_OK)
+                return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "tensor '%s%s': this variant of the decode step is not built", b.c_str(), extra);
+        }
+    }
+    ullm_gpu_model_input in;
+    memset(&in, 0, sizeof in);
+    in.params.n_embd = lp.n_embd, in.params.n_layer = lp.n_layer, in.params.n_head = lp.n_head, in.params.n_kv_head = lp.n_kv_head;
+    in.params.head_dim = lp.head_dim, in.params.n_ff = lp.n_ff, in.params.n_ctx = lp.n_ctx, in.params.vocab = lp.vocab;
+    in.params.rope_theta = lp.rope_theta, in.params.eps = lp.eps, in.params.kv_f16 = kv_f16 ? 1 : 0;
+    if ((rc = norm("output_norm.weight", lp.n_embd, &in.final_norm))) return rc;
+    // some models tie the output projection to the input embeddings (lib.rs:303-304)
+    rc = weight("output.weight", lp.vocab, lp.n_embd, &in.output, true);
+    if (rc == -1) rc = weight("token_embd.weight", lp.vocab, lp.n_embd, &in.output, false);
+    if (rc) return rc;
+    in.layers = layers.data();
+    return ullm_cuda_forward_create(c, &in, out);
 }

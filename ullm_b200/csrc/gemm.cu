@@ -393,17 +393,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         // shared-memory latency overlaps the issue), the stage index is a compile-time
         // constant (operand descriptors differ by constants), and only the first MMA of the
         // tile carries the "overwrite" predicate.
-        if (lane == 0 && rank == 0) {
+        // The whole warp runs the loop with uniform control flow and one elected lane issues:
+        // operands that are warp-uniform can then live in uniform registers, which is what the
+        // MMA and commit instructions read.
+        if (rank == 0) {
             const uint32_t idesc = umma_idesc();
             const uint32_t ta0 = tmem_d + GN; // weight chunks follow the accumulator
             const uint64_t bd0 = umma_desc_sw128(smem_u32(b_tiles));
-            bool ok = (mode & 8u) ? true : wait_polite_or_timeout(&full[0], 0);
+            bool ok = (mode & 8u) ? true : warp_wait(&full[0], 0, lane);
             for (uint32_t g0 = 0, it = 0; g0 < nchunks && ok; g0 += G_STAGES, ++it) {
 #pragma unroll
                 for (uint32_t c = 0; c < G_STAGES; ++c) {
                     const uint32_t g = g0 + c;
                     if (g >= nchunks || !ok) break;
-                    const bool tr = traced && g < 1024;
+                    const bool tr = traced && g < 1024 && lane == 0;
                     if (tr) p.trace[4 * g] = clock64();
                     if (tr && g >= 96 && g < 112) {
                         unsigned long long gt;
@@ -421,29 +424,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                     uint32_t next_ready;
                     if (DBG && (mode & 28u)) { // measurement variants: pieces of the sequence left out
                         next_ready = (mode & 8u) ? 1u : (uint32_t)mbar_test_wait(&full[cn], parn);
-                        if (!(mode & 4u)) {
+                        if (!(mode & 4u) && lane == 0) {
                             umma_bf16(tmem_d, ad, bd, idesc, g != 0);
                             umma_bf16_acc(tmem_d, ad + 8, bd + 2, idesc);
                             umma_bf16_acc(tmem_d, ad + 16, bd + 4, idesc);
                             umma_bf16_acc(tmem_d, ad + 24, bd + 6, idesc);
                         }
-                        if (!(mode & 16u)) umma_commit_pair(&freeb[c]);
+                        if (!(mode & 16u) && lane == 0) umma_commit_pair(&freeb[c]);
                     } else
                     asm volatile(
                         "{\n"
-                        ".reg .pred pw, pa, pt;\n"
+                        ".reg .pred pw, pa, pt, pe;\n"
                         ".reg .b32 a1, a2, a3;\n"
                         ".reg .b64 b1, b2, b3;\n"
                         "setp.ne.b32 pa, %7, 0;\n"
                         "setp.eq.b32 pt, 0, 0;\n"
+                        "elect.sync _|pe, 0xffffffff;\n"
                         "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 pw, [%1], %2;\n"
                         "add.u32 a1, %4, 8;\n add.u32 a2, %4, 16;\n add.u32 a3, %4, 24;\n"
                         "add.u64 b1, %5, 2;\n add.u64 b2, %5, 4;\n add.u64 b3, %5, 6;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [%4], %5, %6, pa;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [a1], b1, %6, pt;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [a2], b2, %6, pt;\n"
-                        "tcgen05.mma.cta_group::2.kind::f16 [%3], [a3], b3, %6, pt;\n"
-                        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %9;\n"
+                        "@pe tcgen05.mma.cta_group::2.kind::f16 [%3], [%4], %5, %6, pa;\n"
+                        "@pe tcgen05.mma.cta_group::2.kind::f16 [%3], [a1], b1, %6, pt;\n"
+                        "@pe tcgen05.mma.cta_group::2.kind::f16 [%3], [a2], b2, %6, pt;\n"
+                        "@pe tcgen05.mma.cta_group::2.kind::f16 [%3], [a3], b3, %6, pt;\n"
+                        "@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %9;\n"
                         "selp.u32 %0, 1, 0, pw;\n"
                         "}"
                         : "=r"(next_ready)
@@ -452,12 +456,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                         : "memory");
                     if (!has_next) next_ready = 1;
                     if (tr) p.trace[4 * g + 1] = clock64();
-                    if (!next_ready) ok = wait_polite_or_timeout(&full[cn], parn);
+                    if (!__all_sync(0xffffffffu, next_ready != 0)) ok = warp_wait(&full[cn], parn, lane);
                     if (tr) p.trace[4 * g + 3] = clock64();
                 }
             }
-            if (ok) umma_commit_pair(&acc_full);
-            else *(volatile int *)p.status = DEV_TIMEOUT;
+            if (lane == 0) {
+                if (ok) umma_commit_pair(&acc_full);
+                else *(volatile int *)p.status = DEV_TIMEOUT;
+            }
         }
     } else {
         // ---- dequantization: all 256 threads work on one 64-k chunk at a time ----
