@@ -459,6 +459,30 @@ def run_other(args):
         out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, prompt_ms_per_token=t_prompt / 16 * 1e3, tokens=n_gen,
                    bytes_per_token=wbytes + kvbytes + 513_024, gbs=(wbytes + kvbytes + 513_024) * n_gen / dt / 1e9,
                    first_tokens=toks[:8].tolist())
+    elif args.workload == "c3prefill":
+        # time to first token on the Llama-3.2-1B shape: all prompt tokens in one batched pass
+        # (tensor-core GEMMs on the quantized weights), against the same prompt token by token
+        p = dict(synth.LLAMA_1B)
+        m = synth.gen_llama_model(p, synth.seed_for(3, 0))
+        gf = backend.GpuForward(ctx, m, kv_f16=True)
+        S = args.tokens
+        emb = synth.normal(synth.seed_for(3, 5), S * p["n_embd"]).reshape(S, p["n_embd"]) * np.float32(0.02)
+        gf.forward_batch(emb, S)  # allocates the chunk buffers
+        reps = max(3, min(args.steps, 20))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            lg = gf.forward_batch(emb, S)
+        dt = (time.perf_counter() - t0) / reps
+        n_seq = min(S, 32)
+        t0 = time.perf_counter()
+        for i in range(n_seq):
+            gf.forward(emb[i], i)
+        dt_seq = (time.perf_counter() - t0) / n_seq
+        params = 16 * (2560 * 2048 + 512 * 2048 + 2048 * 2048 + 2 * 8192 * 2048 + 2048 * 8192)
+        flop = 2.0 * S * params
+        out.update(tokens=S, ms_prefill=dt * 1e3, prefill_tok_per_s=S / dt, gemm_tflops=flop / dt / 1e12,
+                   ms_per_token_stepwise=dt_seq * 1e3, speedup_vs_stepwise=dt_seq * S / dt, last_logit_argmax=int(np.argmax(lg)),
+                   note="host embeddings in, last-token logits out; projections as bf16 tensor-core GEMMs, attention f32")
     if "gbs" in out:
         out["frac_of_measured_peak"] = out["gbs"] / peak
     out["peak_kind"] = peak_kind
@@ -682,7 +706,7 @@ def main():
                          "two programmatically chained launches for this pair, so off by default")
     ap.add_argument("--multi-graph", action="store_true", help="N>1: capture kernels + NCCL in a CUDA graph (off by default)")
     ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4", "c4gemm"],
+    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c3prefill", "c4", "c4gemm"],
                     help="single-GPU only: c1 is the headline workload, the others are auxiliary measurements")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -266,8 +266,14 @@ int ullm_cuda_forward(ullm_cuda_fwd *f, const float *x_init, size_t pos, float *
  * laid out [n_layer][n][kv_dim] (test / benchmark set-up: the reference fills
  * the cache by running tokens). */
 int ullm_cuda_forward_set_kv(ullm_cuda_fwd *f, size_t pos0, size_t n, const float *k, const float *v);
-/* GpuForward::supports_batched_prefill (forward.rs:744). */
+/* GpuForward::supports_batched_prefill (forward.rs:744): 1 when every layer's matrices can go
+ * through the tensor-core GEMM (Q4_K, or Q6_K with in % 2048 == 0). */
 int ullm_cuda_forward_supports_batched_prefill(const ullm_cuda_fwd *f);
+/* GpuForward::forward_batch (forward.rs:757-909): embeds [s, n_embd] f32 token-major for
+ * positions 0..s-1 in one pass; fills the KV cache for those positions and returns the
+ * LAST token's logits [vocab].  The projections run as bf16 tensor-core GEMMs, so logits
+ * agree with s calls of ullm_cuda_forward to the bf16 tolerance (2e-2), not to 1e-3. */
+int ullm_cuda_forward_batch(ullm_cuda_fwd *f, const float *embeds, size_t s, float *logits);
 /* Greedy continuation kept on the device: runs `n` decode steps starting from
  * token embedding lookups of `embd_table` (dtype rows, resident) — argmax
  * (sample.rs:125-133, first index wins) feeds the next step without a host

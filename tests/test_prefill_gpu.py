@@ -1,0 +1,164 @@
+"""GPU parity tests of the batched prefill (``ullm_cuda_forward_batch``, the counterpart of
+``GpuForward::forward_batch``, crates/ullm-metal/src/forward.rs:757-909) against the oracle's
+token-by-token ``forward_llama`` (crates/ullm-model/src/lib.rs:807-969).  The projections run as
+bf16 tensor-core GEMMs, so the bar is the bf16 one: ``rel_err < 2e-2`` on the logits."""
+import numpy as np
+import pytest
+
+import oracle
+from ullm_b200 import backend, synth
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2  # BASELINE north_star tolerance for bf16 tensor-core products
+SMALL = dict(n_embd=2048, n_layer=2, n_head=8, n_kv_head=2, head_dim=64, n_ff=2048, n_ctx=640, vocab=1024, rope_theta=500000.0,
+             eps=1e-5)
+
+
+def oracle_model(m, kv_f16):
+    mk = lambda t: oracle.Weight(t[0], t[1], t[2], t[3])
+    layers = [{k: (mk(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in m["layers"]]
+    return oracle.LlamaModel(m["params"], mk(m["tok_embd"]), mk(m["output"]), m["final_norm"], layers, kv_f16)
+
+
+def conditioned(m):
+    """The benchmark's weight distributions give every projection a gain of ~200 (weights of magnitude
+    several units over 2048 inputs), which makes attention scores of the order of 1e4 and the softmax a
+    hard arg-max: a bf16-sized perturbation then flips the winning key of some tokens and changes their
+    logits by tens of percent.  That is a property of the random model, not of the arithmetic, so the
+    prefill parity model scales the f16 super-block scales down to a gain of ~1 (same formats, same
+    code paths, realistic magnitudes)."""
+    def scale(t):
+        dtype, data, out, cols = t
+        b = np.array(data, np.uint8).reshape(-1, 144 if dtype == backend.Q4_K else 210)
+        offs, k = ((0, 2), 1 / 128.0) if dtype == backend.Q4_K else ((208,), 1 / 256.0)
+        for o in offs:
+            d = b[:, o : o + 2].copy().view(np.float16).astype(np.float32)
+            b[:, o : o + 2] = (d * np.float32(k)).astype(np.float16).view(np.uint8)
+        return (dtype, b.reshape(out, -1), out, cols)
+
+    out = dict(m, tok_embd=scale(m["tok_embd"]), output=scale(m["output"]))
+    out["layers"] = [{k: (scale(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in m["layers"]]
+    return out
+
+
+def bf16(a):
+    return synth.bf16_to_f32(synth.f32_to_bf16(np.ascontiguousarray(a, np.float32)))
+
+
+def prefill_reference(m, embeds, kv_f16, round_bf16):
+    """forward_llama (crates/ullm-model/src/lib.rs:807-969) for all prompt tokens at once in numpy.
+    With ``round_bf16`` the five projections of a layer see weights and activations rounded to bf16,
+    exactly what the tensor-core path computes (f64 accumulation here), so only the accumulation
+    order is left to differ; without it this is the f32 meaning of the model.  Returns the last
+    token's logits (final norm + output projection through the oracle's f32 matvec)."""
+    p = m["params"]
+    E, hd, nh, nkv = p["n_embd"], p["head_dim"], p["n_head"], p["n_kv_head"]
+    qd, kvd, s = nh * hd, nkv * hd, embeds.shape[0]
+
+    def W(t):
+        w = oracle.dequantize(t[0], t[1], t[2] * t[3]).reshape(t[2], t[3])
+        return (bf16(w) if round_bf16 else w).astype(np.float64)
+
+    def proj(t, x):
+        return ((bf16(x) if round_bf16 else x).astype(np.float64) @ W(t).T).astype(np.float32)
+
+    def rms(x, w):
+        inv = (1.0 / np.sqrt((x.astype(np.float32) ** 2).mean(axis=1, dtype=np.float32) + np.float32(p["eps"]))).astype(np.float32)
+        return x * inv[:, None] * w[None, :]
+
+    j = np.arange(hd // 2, dtype=np.float32)
+    freq = (1.0 / np.power(np.float32(p["rope_theta"]), (2 * j) / np.float32(hd))).astype(np.float32)
+    ang = np.arange(s, dtype=np.float32)[:, None] * freq[None, :]
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+    def rope(v, heads):
+        v = v.reshape(s, heads, hd // 2, 2)
+        a, b = v[..., 0], v[..., 1]
+        return np.stack([a * cos[:, None, :] - b * sin[:, None, :], a * sin[:, None, :] + b * cos[:, None, :]], axis=-1).reshape(s, heads * hd)
+
+    x = embeds.astype(np.float32).copy()
+    for l in m["layers"]:
+        xn = rms(x, l["attn_norm"])
+        q, k, v = rope(proj(l["wq"], xn), nh), rope(proj(l["wk"], xn), nkv), proj(l["wv"], xn)
+        if kv_f16:
+            k, v = k.astype(np.float16).astype(np.float32), v.astype(np.float16).astype(np.float32)
+        att = np.zeros((s, qd), np.float32)
+        for h in range(nh):
+            kh = h // (nh // nkv)
+            sc = (q[:, h * hd : (h + 1) * hd].astype(np.float64) @ k[:, kh * hd : (kh + 1) * hd].astype(np.float64).T) / np.sqrt(hd)
+            sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
+            pr = np.exp(sc - sc.max(axis=1, keepdims=True))
+            pr /= pr.sum(axis=1, keepdims=True)
+            att[:, h * hd : (h + 1) * hd] = (pr @ v[:, kh * hd : (kh + 1) * hd].astype(np.float64)).astype(np.float32)
+        x = x + proj(l["wo"], att)
+        xn = rms(x, l["ffn_norm"])
+        g, u = proj(l["w_gate"], xn), proj(l["w_up"], xn)
+        x = x + proj(l["w_down"], (g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u)
+    o = m["output"]
+    return oracle.matvec_q(oracle.Weight(o[0], o[1], o[2], o[3]), rms(x[-1:], m["final_norm"])[0])
+
+
+@pytest.fixture(scope="module")
+def small():
+    return conditioned(synth.gen_llama_model(dict(SMALL), 21))
+
+
+def test_tiny_shapes_do_not_claim_batched_prefill(ctx):
+    # Q6_K rows of 256 columns cannot take the prepared layout the GEMM reads
+    gf = backend.GpuForward(ctx, synth.gen_llama_model(dict(synth.LLAMA_TINY), 3))
+    assert not gf.supports_batched_prefill()
+    with pytest.raises(backend.Unsupported):
+        gf.forward_batch(np.zeros((2, 256), np.float32), 2)
+    gf.free()
+
+
+@pytest.mark.parametrize("kv_f16,s", [(True, 40), (False, 1), (True, 7), (False, 28), (True, 48), (False, 16)])
+def test_prefill_data_path_and_model_parity(ctx, small, kv_f16, s):
+    """(1) Against the same computation with bf16-rounded projection operands: 3e-3 — pins every kernel of
+    the pass (one wrong element, position or mask shows).  (2) Against the oracle's f32 token-by-token
+    forward.  A single bf16 GEMM is within 2e-2 of f32 (tests/test_gemm_gpu.py); a whole model is only as
+    close as its conditioning allows — where a token's attention is nearly tied between two keys, the
+    bf16 rounding of q and k alone moves tens of percent of the weight (the (True, 48) case: 27 %, in
+    numpy as on the GPU).  So the f32 comparison asks that the GPU be no further from f32 than bf16
+    arithmetic itself is, measured by the numpy restatement with rounded operands."""
+    om = oracle_model(small, kv_f16)
+    gf = backend.GpuForward(ctx, small, kv_f16=kv_f16)
+    assert gf.supports_batched_prefill()
+    toks = synth.rand_ints(5, s + 1, 0, SMALL["vocab"] - 1)
+    embeds = np.stack([om.embed(int(t)) for t in toks[:s]])
+    got = gf.forward_batch(embeds, s)
+    assert synth.rel_err(got, prefill_reference(small, embeds, kv_f16, True)) < 3e-3
+    ref = None
+    for pos in range(s):
+        ref = om.forward(int(toks[pos]), pos)
+    # the numpy restatement is the oracle's model (f64 vs sequential f32 sums, libm differences, f16 cache rounding)
+    assert synth.rel_err(prefill_reference(small, embeds, kv_f16, False), ref) < 5e-3
+    bf16_effect = synth.rel_err(prefill_reference(small, embeds, kv_f16, True), ref)
+    assert synth.rel_err(got, ref) < bf16_effect + 5e-3
+    # the cache the prefill left behind serves the next decode step: same logits as a decode step on a
+    # cache built token by token by a second engine, to the effect of the bf16 K/V projections
+    step = backend.GpuForward(ctx, small, kv_f16=kv_f16)
+    for pos in range(s):
+        step.forward(embeds[pos], pos)
+    nxt = om.embed(int(toks[s]))
+    a, b = gf.forward(nxt, s), step.forward(nxt, s)
+    assert synth.rel_err(a, b) < max(10 * bf16_effect, 2e-2)
+    step.free()
+    gf.free()
+
+
+def test_chunked_prefill_equals_token_by_token_on_the_gpu(ctx, small):
+    """600 tokens = one full chunk of 512 + 88: the second chunk attends to the first through the cache."""
+    s = 600
+    a, b = backend.GpuForward(ctx, small, kv_f16=True), backend.GpuForward(ctx, small, kv_f16=True)
+    om = oracle_model(small, True)
+    toks = synth.rand_ints(6, s, 0, SMALL["vocab"] - 1)
+    embeds = np.stack([om.embed(int(t)) for t in toks])
+    step = None
+    for pos in range(s):
+        step = a.forward(embeds[pos], pos)
+    got = b.forward_batch(embeds, s)
+    ref16 = prefill_reference(small, embeds, True, True)
+    assert synth.rel_err(got, ref16) < 3e-3
+    assert synth.rel_err(got, step) < synth.rel_err(ref16, step) + 5e-3
+    a.free(), b.free()

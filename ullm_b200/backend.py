@@ -86,6 +86,7 @@ SIGNATURES = {
     "ullm_cuda_moe_ffn_noalloc": (_i, [_i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, C.c_char_p, _sz]),
     "ullm_cuda_forward_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "ullm_cuda_forward_create_gguf": (_i, [_vp, _vp, _i, C.POINTER(_vp)]),
+    "ullm_cuda_forward_batch": (_i, [_vp, _vp, _sz, _vp]),
     "ullm_cuda_forward_destroy": (None, [_vp]),
     "ullm_cuda_forward": (_i, [_vp, _vp, _sz, _vp]),
     "ullm_cuda_forward_set_kv": (_i, [_vp, _sz, _sz, _vp, _vp]),
@@ -519,6 +520,14 @@ class GpuForward:
         k, v = _f32(k), _f32(v)
         n = k.shape[1]
         self._ctx._check(self._ctx._lib.ullm_cuda_forward_set_kv(self._h, pos0, n, _ptr(k), _ptr(v)))
+
+    def forward_batch(self, embeds, s: int) -> np.ndarray:
+        """All ``s`` prompt tokens in one pass (``forward_batch``, forward.rs:757): fills the KV cache for
+        positions 0..s-1 and returns the last token's logits."""
+        e = _f32(embeds)
+        out = np.empty(self.params["vocab"], np.float32)
+        self._ctx._check(self._ctx._lib.ullm_cuda_forward_batch(self._h, _ptr(e), s, _ptr(out)))
+        return out
 
     def supports_batched_prefill(self) -> bool:
         return bool(self._ctx._lib.ullm_cuda_forward_supports_batched_prefill(self._h))

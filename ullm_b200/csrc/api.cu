@@ -842,9 +842,22 @@ int ullm_cuda_forward_set_kv(ullm_cuda_fwd *f, size_t pos0, size_t n, const floa
     return ULLM_OK;
 }
 
-// GpuForward::supports_batched_prefill (forward.rs:744-749): the batched prefill
-// pass is not built, so callers take the token-by-token path (lib.rs:1287-1295).
-int ullm_cuda_forward_supports_batched_prefill(const ullm_cuda_fwd *) { return 0; }
+// GpuForward::supports_batched_prefill (forward.rs:744-749)
+int ullm_cuda_forward_supports_batched_prefill(const ullm_cuda_fwd *f) { return f && f->f.batch_supported() ? 1 : 0; }
+
+// GpuForward::forward_batch (forward.rs:757-909): positions 0..s-1, last token's logits
+int ullm_cuda_forward_batch(ullm_cuda_fwd *f, const float *embeds, size_t s, float *logits) {
+    if (!f || !embeds || !logits) return ULLM_ERR_INVALID;
+    if (s == 0) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "empty prompt");
+    if (s > f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "%zu prompt tokens exceed the context of %zu", s, f->f.P.n_ctx);
+    if (!f->f.batch_supported()) return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "batched prefill is not available for this model's weight types");
+    cudaError_t e = f->f.forward_batch(embeds, s, logits);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return ctx_fail(f->ctx, e == cudaErrorMemoryAllocation ? ULLM_ERR_OOM : ULLM_ERR_CUDA, "forward_batch: %s", cudaGetErrorString(e));
+    }
+    return fwd_status(f);
+}
 
 int ullm_cuda_forward_greedy(ullm_cuda_fwd *f, const ullm_cuda_buf *embd, int embd_dtype, uint32_t first_token, size_t pos,
                              size_t n, uint32_t *tokens_out) {

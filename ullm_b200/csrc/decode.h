@@ -74,6 +74,12 @@ struct Forward {
     cudaError_t greedy(const void *embd_table, int embd_dtype, uint32_t first_token, size_t pos, size_t n,
                        uint32_t *tokens_host);
     cudaError_t set_kv(size_t pos0, size_t n, const float *k, const float *v);
+    // batched prefill (prefill.cu): all s prompt tokens in one pass, KV cache filled for 0..s-1,
+    // logits of the last token
+    bool batch_supported() const;
+    cudaError_t forward_batch(const float *embeds_host, size_t s, float *logits_host);
+    float *bx = nullptr, *bxn = nullptr, *bqk = nullptr, *bv = nullptr, *bgu = nullptr, *bh = nullptr, *bt = nullptr;
+    void *bscratch = nullptr;
 
   private:
     cudaError_t dev_alloc(void **out, size_t bytes);
