@@ -78,7 +78,7 @@ struct Forward {
     // logits of the last token
     bool batch_supported() const;
     cudaError_t forward_batch(const float *embeds_host, size_t s, float *logits_host);
-    float *bx = nullptr, *bxn = nullptr, *bqk = nullptr, *bv = nullptr, *bgu = nullptr, *bh = nullptr, *bt = nullptr;
+    float *bx = nullptr, *bxn = nullptr, *bqk = nullptr, *bv = nullptr, *bh = nullptr;
     void *bscratch = nullptr;
 
   private:

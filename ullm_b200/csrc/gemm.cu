@@ -129,6 +129,8 @@ struct GemmParams {
     int *status;
     uint32_t out_dim, in_dim, s;
     uint32_t blocks_per_split; // 256-k blocks handled by one grid.z slice (split-K for matrices with few row tiles)
+    int epi;                   // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU, applied here only when there is one k slice
+    const float *res;          // EPI_RESIDUAL: y = res + W x (may alias y)
     long long *trace; // measurement only: cycle stamps of CTA (0, 0)
     uint32_t mode; // measurement only: bit 0 skips the dequantization, bit 1 the activation loads, bit 2 the MMAs
 };
@@ -520,11 +522,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                       "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                     : "r"(tmem_d + ((q * 32u) << 16) + col0));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (orow < p.out_dim) {
+                if (p.epi == EPI_SWIGLU) {
+                    // rows are interleaved (gate_j, up_j): neighbouring lanes hold the pair (math.rs:103-105)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float a = __uint_as_float(v[j]), o = __shfl_xor_sync(0xffffffffu, a, 1);
+                        const uint32_t tok = n0 + col0 + j;
+                        if (!(lane & 1) && orow < p.out_dim && tok < p.s)
+                            yout[(size_t)tok * (p.out_dim >> 1) + (orow >> 1)] = __fdividef(a, 1.0f + __expf(-a)) * o; // operands are bf16 products: fast exp / divide lose nothing that matters
+                    }
+                } else if (orow < p.out_dim) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t tok = n0 + col0 + j;
-                        if (tok < p.s) yout[(size_t)tok * p.out_dim + orow] = __uint_as_float(v[j]);
+                        if (tok < p.s) {
+                            const size_t at = (size_t)tok * p.out_dim + orow;
+                            yout[at] = p.epi == EPI_RESIDUAL ? p.res[at] + __uint_as_float(v[j]) : __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -556,22 +570,25 @@ __global__ void cast_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__r
     }
 }
 
-// split-K: y[i] = part[0][i] + part[1][i] + ... in slice order (deterministic)
-__global__ void splitk_reduce_kernel(const float *__restrict__ part, float *__restrict__ y, size_t n, int splits) {
+// split-K: y[i] = part[0][i] + part[1][i] + ... in slice order (deterministic), then the epilogue
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, float *y, size_t n, int splits, int epi, const float *res) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (i + 3 < n) {
-        float4 a = *(const float4 *)(part + i);
-        for (int z = 1; z < splits; ++z) {
+    if (i >= n) return;
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    const int cnt = i + 3 < n ? 4 : (int)(n - i);
+    if (cnt == 4) {
+        for (int z = 0; z < splits; ++z) {
             const float4 b = *(const float4 *)(part + (size_t)z * n + i);
-            a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+            a[0] += b.x, a[1] += b.y, a[2] += b.z, a[3] += b.w;
         }
-        *(float4 *)(y + i) = a;
     } else {
-        for (size_t j = i; j < n; ++j) {
-            float a = part[j];
-            for (int z = 1; z < splits; ++z) a += part[(size_t)z * n + j];
-            y[j] = a;
-        }
+        for (int z = 0; z < splits; ++z)
+            for (int k = 0; k < cnt; ++k) a[k] += part[(size_t)z * n + i + k];
+    }
+    if (epi == EPI_SWIGLU) { // n and the row length are even: pairs never straddle a thread's four values
+        for (int k = 0; k + 1 < cnt; k += 2) y[(i + k) >> 1] = a[k] / (1.0f + expf(-a[k])) * a[k + 1];
+    } else {
+        for (int k = 0; k < cnt; ++k) y[i + k] = epi == EPI_RESIDUAL ? res[i + k] + a[k] : a[k];
     }
 }
 
@@ -641,7 +658,9 @@ template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, 
 // d_w: FMT_Q4K verbatim rows or FMT_Q6KR prepared rows (16-byte aligned).  d_x f32 [s, in],
 // d_y f32 [s, out], d_xb16: scratch of gemm_tc_scratch_bytes (256-byte aligned).
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_xb16, size_t out_dim, size_t in_dim,
-                           size_t s, int sm_count, int *d_status, cudaStream_t st) {
+                           size_t s, int sm_count, int *d_status, cudaStream_t st, int epi, const float *d_res) {
+    if (epi == EPI_SWIGLU && (out_dim & 1)) return cudaErrorInvalidValue;
+    if (epi == EPI_RESIDUAL && !d_res) return cudaErrorInvalidValue;
     if (!gemm_tc_supported(fmt, out_dim, in_dim, s) || ((uintptr_t)d_w & 15)) return cudaErrorNotSupported;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
@@ -669,6 +688,7 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
     p.blocks_per_split = (uint32_t)((nb + splits - 1) / splits);
     const unsigned gz = (unsigned)((nb + p.blocks_per_split - 1) / p.blocks_per_split);
     p.y = gz > 1 ? part : d_y, p.status = d_status;
+    p.epi = gz > 1 ? EPI_STORE : epi, p.res = d_res;
     p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
     p.mode = g_gemm_mode, p.trace = g_gemm_trace;
     const dim3 grid(2 * (unsigned)((out_dim + 2 * GM - 1) / (2 * GM)), (unsigned)((s + GN - 1) / GN),
@@ -677,7 +697,7 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
     else e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
     if (e != cudaSuccess || grid.z == 1) return e;
     const size_t ny = s * out_dim;
-    splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, d_y, ny, (int)grid.z);
+    splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, d_y, ny, (int)grid.z, epi, d_res);
     return cudaGetLastError();
 }
 

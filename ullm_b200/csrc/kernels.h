@@ -90,8 +90,9 @@ void gemm_set_trace(void *d_buf); // >= 8192 int64: cycle stamps of CTA (0, 0)'s
 void gemm_set_debug_mode(int mode); // measurement only: stages of the GEMM kernel switched off
 bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s);
 size_t gemm_tc_scratch_bytes(size_t out_dim, size_t in_dim, size_t s, int sm_count); // bf16 activations + split-K partial sums
+// epi / d_res: the matvec's epilogues on the [s, out] result (EPI_SWIGLU writes [s, out / 2]; d_res may alias d_y)
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_scratch, size_t out_dim, size_t in_dim,
-                           size_t s, int sm_count, int *d_status, cudaStream_t st);
+                           size_t s, int sm_count, int *d_status, cudaStream_t st, int epi = EPI_STORE, const float *d_res = nullptr);
 bool matvec_is_streamed(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
                         int epi);
 // Returns a static message when the shape cannot be computed at all.

@@ -5,7 +5,7 @@
 // Per layer: rmsnorm of every token -> [q|k] and v projections as tensor-core GEMMs on the
 // quantized weights (gemm.cu) -> RoPE of q and k, K/V written to the cache -> causal
 // attention of the s new tokens over the cache -> W_o GEMM + residual -> rmsnorm ->
-// [gate|up] GEMM -> silu(g)*u -> W_down GEMM + residual.  Only the last token goes through
+// [gate|up] GEMM with silu(g)*u in its epilogue -> W_down GEMM + residual (epilogue).  Only the last token goes through
 // the final norm and the output projection (a matvec).  Prompts longer than PREFILL_CHUNK
 // tokens are processed in chunks; the attention reads earlier chunks from the cache.
 #include "decode.h"
@@ -68,18 +68,34 @@ __global__ void __launch_bounds__(256) rope_kv_batch_kernel(float *__restrict__ 
     for (int i = threadIdx.x; i < kvd; i += 256) vc[(size_t)pos * kvd + i] = kv_from<KV_T>(v[(size_t)t * kvd + i]);
 }
 
+// Eight consecutive cache values of one position -> f32 (one 16- or 32-byte load)
+__device__ __forceinline__ void kv_load8(const float *p, float (&o)[8]) {
+    const float4 a = *(const float4 *)p, b = *(const float4 *)(p + 4);
+    o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
+}
+__device__ __forceinline__ void kv_load8(const __half *p, float (&o)[8]) {
+    const uint4 v = *(const uint4 *)p;
+    const __half2 *h = (const __half2 *)&v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        o[2 * i] = f.x, o[2 * i + 1] = f.y;
+    }
+}
+
 // Causal attention of the chunk's queries over cache positions 0 .. pos0 + t (lib.rs:916-938: scores
 // q.k / sqrt(hd), softmax, weighted sum of v).  grid (n_head, ceil(s / 8)), 8 warps: one query per
-// warp; keys in blocks of 32 staged in shared memory for the CTA's 8 queries; lane j scores key j of
+// warp; keys in blocks of 32 staged in shared memory for the CTA's 8 queries (vector loads from the
+// cache, rows padded so that 128-bit reads one row apart hit distinct banks); lane j scores key j of
 // the block, the block's probabilities are then broadcast lane by lane for the P.V sum, where every
 // lane owns HD / 32 output dimensions.  Running max / sum as in any streaming softmax.
 template <int HD, typename KV_T>
 __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restrict__ qk, const KV_T *__restrict__ kc,
                                                           const KV_T *__restrict__ vc, float *__restrict__ out, int s, int pos0,
                                                           int qd, int kvd, int kvmul, float scale) {
-    constexpr int E = HD / 32;
-    __shared__ float ks[32][HD + 1];
-    __shared__ float vs[32][HD];
+    constexpr int E = HD / 32, KP = HD + 4; // padded K row: 16-byte aligned, 4 banks apart per row
+    __shared__ __align__(16) float ks[32][KP];
+    __shared__ __align__(16) float vs[32][HD];
     const int h = blockIdx.x, kvh = h / kvmul, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.y * 8 + warp;
     const bool valid = t < s;
@@ -87,25 +103,36 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
     const int last_q = pos0 + min(s - 1, (int)blockIdx.y * 8 + 7); // the CTA's keys end at its last query
     float q[HD];
     {
-        const float *qp = qk + (size_t)(valid ? t : 0) * (qd + kvd) + (size_t)h * HD;
+        const float4 *qp = (const float4 *)(qk + (size_t)(valid ? t : 0) * (qd + kvd) + (size_t)h * HD);
 #pragma unroll
-        for (int d = 0; d < HD; ++d) q[d] = qp[d] * scale;
+        for (int d = 0; d < HD / 4; ++d) {
+            const float4 v = qp[d];
+            q[4 * d] = v.x * scale, q[4 * d + 1] = v.y * scale, q[4 * d + 2] = v.z * scale, q[4 * d + 3] = v.w * scale;
+        }
     }
     float m = -INFINITY, l = 0.f, acc[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[e] = 0.f;
     for (int k0 = 0; k0 <= last_q; k0 += 32) {
         __syncthreads(); // the previous block's tiles are no longer read
-        for (int i = threadIdx.x; i < 32 * HD; i += 256) {
-            const int j = i / HD, d = i % HD, kp = min(k0 + j, last_q);
-            ks[j][d] = kv_to<KV_T>(kc[(size_t)kp * kvd + (size_t)kvh * HD + d]);
-            vs[j][d] = kv_to<KV_T>(vc[(size_t)kp * kvd + (size_t)kvh * HD + d]);
+        for (int i = threadIdx.x; i < 32 * (HD / 8); i += 256) { // 8 values per thread and matrix
+            const int j = i / (HD / 8), d = (i % (HD / 8)) * 8, kp = min(k0 + j, last_q);
+            float kk[8], vv[8];
+            kv_load8(kc + (size_t)kp * kvd + (size_t)kvh * HD + d, kk);
+            kv_load8(vc + (size_t)kp * kvd + (size_t)kvh * HD + d, vv);
+            *(float4 *)&ks[j][d] = make_float4(kk[0], kk[1], kk[2], kk[3]);
+            *(float4 *)&ks[j][d + 4] = make_float4(kk[4], kk[5], kk[6], kk[7]);
+            *(float4 *)&vs[j][d] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+            *(float4 *)&vs[j][d + 4] = make_float4(vv[4], vv[5], vv[6], vv[7]);
         }
         __syncthreads();
         if (k0 > qpos) continue; // this query's keys are exhausted (other warps of the CTA still need the tiles)
         float sc = 0.f;
 #pragma unroll
-        for (int d = 0; d < HD; ++d) sc += q[d] * ks[lane][d];
+        for (int d = 0; d < HD / 4; ++d) {
+            const float4 kv = *(const float4 *)&ks[lane][4 * d];
+            sc += q[4 * d] * kv.x + q[4 * d + 1] * kv.y + q[4 * d + 2] * kv.z + q[4 * d + 3] * kv.w;
+        }
         if (k0 + lane > qpos) sc = -INFINITY;
         const float mb = warp_max(sc), mn = fmaxf(m, mb);
         const float pj = expf(sc - mn), corr = expf(m - mn);
@@ -116,8 +143,13 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
 #pragma unroll 8
         for (int j = 0; j < 32; ++j) {
             const float pb = __shfl_sync(0xffffffffu, pj, j);
-#pragma unroll
-            for (int e = 0; e < E; ++e) acc[e] += pb * vs[j][lane * E + e];
+            if constexpr (E == 2) {
+                const float2 v2 = *(const float2 *)&vs[j][lane * 2];
+                acc[0] += pb * v2.x, acc[1] += pb * v2.y;
+            } else {
+                const float4 v4 = *(const float4 *)&vs[j][lane * 4];
+                acc[0] += pb * v4.x, acc[1] += pb * v4.y, acc[2] += pb * v4.z, acc[3] += pb * v4.w;
+            }
         }
     }
     if (valid) {
@@ -125,26 +157,6 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
 #pragma unroll
         for (int e = 0; e < E; ++e) out[(size_t)t * qd + (size_t)h * HD + lane * E + e] = acc[e] * inv;
     }
-}
-
-__global__ void add_inplace_kernel(float *__restrict__ x, const float *__restrict__ y, size_t n) {
-    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (i + 3 < n) {
-        float4 a = *(float4 *)(x + i);
-        const float4 b = *(const float4 *)(y + i);
-        a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
-        *(float4 *)(x + i) = a;
-    } else {
-        for (size_t j = i; j < n; ++j) x[j] += y[j];
-    }
-}
-
-// gu: [s, 2 * ff] with rows of the matrix interleaved (gate_j, up_j) -> h[s, ff] = silu(g) * u (math.rs:103-105)
-__global__ void swiglu_batch_kernel(const float *__restrict__ gu, float *__restrict__ h, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float2 p = *(const float2 *)(gu + 2 * i);
-    h[i] = p.x / (1.0f + expf(-p.x)) * p.y;
 }
 
 bool Forward::batch_supported() const {
@@ -177,14 +189,12 @@ cudaError_t Forward::forward_batch(const float *embeds_host, size_t s, float *lo
         TRY(dev_alloc((void **)&bxn, B * std::max(E, qd) * 4));
         TRY(dev_alloc((void **)&bqk, B * (qd + kvd) * 4));
         TRY(dev_alloc((void **)&bv, B * kvd * 4));
-        TRY(dev_alloc((void **)&bgu, B * 2 * F * 4));
         TRY(dev_alloc((void **)&bh, B * F * 4));
-        TRY(dev_alloc((void **)&bt, B * E * 4));
         TRY(dev_alloc(&bscratch, scratch));
     }
-    auto gemm = [&](const Mat &m, const float *in, float *out, size_t n) {
+    auto gemm = [&](const Mat &m, const float *in, float *out, size_t n, int epi = EPI_STORE, const float *res = nullptr) {
         ++launches;
-        return launch_gemm_tc(m.fmt, m.w, in, out, bscratch, m.out, m.cols, n, dev.sm_count, d_status, stream);
+        return launch_gemm_tc(m.fmt, m.w, in, out, bscratch, m.out, m.cols, n, dev.sm_count, d_status, stream, epi, res);
     };
     const float scale = 1.0f / sqrtf((float)hd);
     for (size_t c0 = 0; c0 < s; c0 += B) {
@@ -208,13 +218,11 @@ cudaError_t Forward::forward_batch(const float *embeds_host, size_t s, float *lo
                 else attn_prefill_kernel<128, float><<<ag, 256, 0, stream>>>(bqk, (const float *)kc, (const float *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
             }
             TRY(cudaGetLastError());
-            TRY(gemm(L.wo, bxn, bt, n)); // attention output [n, qd] sits in bxn
-            add_inplace_kernel<<<(unsigned)((n * E / 4 + 255) / 256 + 1), 256, 0, stream>>>(bx, bt, n * E);
+            // the attention output [n, qd] sits in bxn; residual adds and silu(g)*u happen in the GEMM epilogues
+            TRY(gemm(L.wo, bxn, bx, n, EPI_RESIDUAL, bx));
             rmsnorm_batch_kernel<<<(unsigned)n, 256, 0, stream>>>(bx, L.ffn_norm, P.eps, (int)E, bxn);
-            TRY(gemm(L.wgu, bxn, bgu, n));
-            swiglu_batch_kernel<<<(unsigned)((n * F + 255) / 256), 256, 0, stream>>>(bgu, bh, n * F);
-            TRY(gemm(L.wd, bh, bt, n));
-            add_inplace_kernel<<<(unsigned)((n * E / 4 + 255) / 256 + 1), 256, 0, stream>>>(bx, bt, n * E);
+            TRY(gemm(L.wgu, bxn, bh, n, EPI_SWIGLU));
+            TRY(gemm(L.wd, bh, bx, n, EPI_RESIDUAL, bx));
             TRY(cudaGetLastError());
         }
         if (c0 + n == s) { // the last token's hidden state -> final norm + output projection
