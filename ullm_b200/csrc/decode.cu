@@ -461,6 +461,8 @@ cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardP
     TRY(dev_alloc((void **)&partial, P.n_kv_head * n_split * (P.n_head / P.n_kv_head) * (hd + 2) * 4));
     TRY(dev_alloc((void **)&counters, P.n_kv_head * 4));
     TRY(cudaMemsetAsync(counters, 0, P.n_kv_head * 4, stream));
+    TRY(dev_alloc((void **)&chain_sync, 256));
+    TRY(cudaMemsetAsync(chain_sync, 0, 256, stream));
     TRY(dev_alloc((void **)&state, 64)); // [0] pos, [1] token, [2] step
     TRY(cudaMemsetAsync(state, 0, 64, stream));
     TRY(dev_alloc((void **)&tokens_out, MAX_GREEDY * 4));
@@ -502,13 +504,29 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
     const size_t kvb = P.kv_f16 ? 2 : 4;
     for (size_t l = 0; l < P.n_layer; ++l) {
         Layer &L = layers[l];
-        if (L.qk_fused) {
-            TRY(mv(L.wqk, x, qk, L.attn_norm, EPI_STORE, nullptr));
-        } else {
-            TRY(mv(L.wq, x, qk, L.attn_norm, EPI_STORE, nullptr));
-            TRY(mv(L.wk, x, qk + qd, L.attn_norm, EPI_STORE, nullptr));
+        // q|k and v read the same normed x and share nothing else: one persistent launch for both
+        // (matvec_chain.cu) when the formats allow it, else one launch each
+        bool chained = false;
+        if (L.qk_fused && use_chain && matvec_chain_supported(L.wqk.fmt, L.wqk.out, L.wqk.cols, EPI_STORE) &&
+            matvec_chain_supported(L.wv.fmt, L.wv.out, L.wv.cols, EPI_STORE)) {
+            MatvecChainOp ops[2];
+            ops[0].fmt = L.wqk.fmt, ops[0].w = L.wqk.w, ops[0].x = x, ops[0].y = qk, ops[0].out_dim = L.wqk.out, ops[0].in_dim = L.wqk.cols;
+            ops[1].fmt = L.wv.fmt, ops[1].w = L.wv.w, ops[1].x = x, ops[1].y = vbuf, ops[1].out_dim = L.wv.out, ops[1].in_dim = L.wv.cols;
+            ops[0].norm_w = ops[1].norm_w = L.attn_norm, ops[0].eps = ops[1].eps = P.eps;
+            e = launch_matvec_chain(dev, 2, ops, chain_sync, d_status, stream, use_pdl);
+            if (e == cudaSuccess) chained = true, ++launches;
+            else if (e != cudaErrorNotSupported) return e;
+            else cudaGetLastError();
         }
-        TRY(mv(L.wv, x, vbuf, L.attn_norm, EPI_STORE, nullptr));
+        if (!chained) {
+            if (L.qk_fused) {
+                TRY(mv(L.wqk, x, qk, L.attn_norm, EPI_STORE, nullptr));
+            } else {
+                TRY(mv(L.wq, x, qk, L.attn_norm, EPI_STORE, nullptr));
+                TRY(mv(L.wk, x, qk + qd, L.attn_norm, EPI_STORE, nullptr));
+            }
+            TRY(mv(L.wv, x, vbuf, L.attn_norm, EPI_STORE, nullptr));
+        }
         AttnParams ap;
         ap.q = qk, ap.knew = qk + qd, ap.vnew = vbuf;
         ap.kcache = (uint8_t *)kcache + l * P.n_ctx * kvd * kvb;

@@ -61,7 +61,8 @@ struct Forward {
     int *d_status = nullptr;
     bool owned_host = false;
     std::vector<void *> owned;
-    bool use_graph = true, use_pdl = false;
+    bool use_graph = true, use_pdl = false, use_chain = false; // use_chain: q|k and v of a layer in one persistent launch
+    unsigned *chain_sync = nullptr; // grid-barrier words of the chain kernel
     cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
     const void *graph_table = nullptr;
     int graph_dtype = 0;

@@ -231,6 +231,10 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     int cur_d = -1;
     uint32_t kk = 0;
     const uint32_t RW = p.R / p.NW;
+    // The register image of the current activation vector survives from tile to tile: most experts
+    // are picked by a single pair, and then all row tiles of the expert use the same vector.
+    uint32_t X[G][XR];
+    int loaded_vec = -1;
     for (uint32_t u = u0; u < u1; ++u, ++kk) {
         const uint32_t s = kk % p.S;
         const uint32_t d = u / p.tiles_per_expert, rt = u % p.tiles_per_expert, r0 = rt * p.R;
@@ -242,6 +246,7 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
                 prep_image<FMT_MLX4>(ActSrc{p.act + (size_t)pairs[pb + j] * p.in_dim, nullptr, 0.f}, p.in_dim,
                                      qimg + (size_t)j * p.ncg * XR * 32, tid, nthr_c);
             asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
+            loaded_vec = -1; // the images were rebuilt
         }
         cur_d = (int)d;
         if (!aborted && !wait_or_timeout(&full[s], (kk / p.S) & 1)) aborted = true;
@@ -250,12 +255,14 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         for (int j = 0; j < np && !aborted; ++j) {
             const int pair = pairs[pb + j];
             const uint32_t vec = GATE_UP ? (uint32_t)pair / p.k : (uint32_t)j;
-            uint32_t X[G][XR];
+            if ((int)vec != loaded_vec) {
 #pragma unroll
-            for (int g = 0; g < G; ++g)
+                for (int g = 0; g < G; ++g)
 #pragma unroll
-                for (int q = 0; q < XR; ++q)
-                    X[g][q] = (uint32_t)g < p.ncg ? qimg[((size_t)(vec * p.ncg + g) * XR + q) * 32 + lane] : 0u;
+                    for (int q = 0; q < XR; ++q)
+                        X[g][q] = (uint32_t)g < p.ncg ? qimg[((size_t)(vec * p.ncg + g) * XR + q) * 32 + lane] : 0u;
+                loaded_vec = (int)vec;
+            }
             for (uint32_t rr = 0; rr < RW; ++rr) {
                 const uint32_t rl = warp * RW + rr;
                 if (r0 + rl >= p.rows) break;
