@@ -236,9 +236,13 @@ typedef struct ullm_gpu_weight_s { /* GpuWeight, forward.rs:56-64 */
     const float *mlx_scales, *mlx_biases;
     size_t mlx_group;
 } ullm_gpu_weight;
-typedef struct { /* GpuLayerInput, forward.rs:78-100 (dense Llama fields) */
+typedef struct { /* GpuLayerInput, forward.rs:78-100 (dense fields) */
     const float *attn_norm, *ffn_norm;
     ullm_gpu_weight wq, wk, wv, wo, w_gate, w_up, w_down;
+    /* Option<&[f32]> of the reference, NULL = absent: projection biases [q_dim] / [kv_dim] / [kv_dim]
+     * (Qwen2) and the per-head Q / K RMSNorm weights [head_dim] applied before RoPE (Qwen3; used when
+     * params.qk_norm is set). */
+    const float *q_bias, *k_bias, *v_bias, *q_norm, *k_norm;
 } ullm_gpu_layer_input;
 typedef struct { /* GpuModelInput, forward.rs:105-110 */
     ullm_gpu_params params;
@@ -247,9 +251,9 @@ typedef struct { /* GpuModelInput, forward.rs:105-110 */
     const ullm_gpu_layer_input *layers; /* params.n_layer entries */
 } ullm_gpu_model_input;
 
-/* GpuForward::new (forward.rs:230).  UNSUPPORTED for flags no benchmark
- * configuration uses (rope_neox, qk_norm, sandwich_norm, geglu, MoE layers,
- * sliding window) instead of silently ignoring them. */
+/* GpuForward::new (forward.rs:230).  rope_neox, qk_norm and the q/k/v biases are built;
+ * sandwich_norm, geglu, MoE layers and the sliding window return UNSUPPORTED instead of
+ * being silently ignored. */
 int ullm_cuda_forward_create(ullm_cuda_ctx *ctx, const ullm_gpu_model_input *in, ullm_cuda_fwd **out);
 /* The same from an open GGUF file (include/ullm_gguf.h): hyperparameters and tensor
  * names as LlamaModel::from_gguf reads them (crates/ullm-model/src/lib.rs:174-301:

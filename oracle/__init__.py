@@ -47,14 +47,15 @@ class MoeExperts(C.Structure):
 class Layer(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p)] + [
         (n, QWeight) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")
-    ]
+    ] + [(n, C.c_void_p) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")]
 
 
 class Model(C.Structure):
     _fields_ = (
         [(n, C.c_size_t) for n in ("n_embd", "n_layer", "n_head", "n_kv_head", "head_dim", "n_ff", "n_ctx", "vocab")]
         + [("rope_theta", C.c_float), ("eps", C.c_float), ("tok_embeddings", QWeight), ("output", QWeight)]
-        + [("final_norm", C.c_void_p), ("layers", C.c_void_p), ("key_cache", C.c_void_p), ("val_cache", C.c_void_p), ("kv_f16", C.c_int)]
+        + [("final_norm", C.c_void_p), ("layers", C.c_void_p), ("key_cache", C.c_void_p), ("val_cache", C.c_void_p), ("kv_f16", C.c_int),
+           ("rope_neox", C.c_int)]
     )
 
 
@@ -255,7 +256,7 @@ class LlamaModel:
     """Dense Llama decode on the oracle (lib.rs:807-969).  ``layers`` is a list of
     dicts with f32 ``attn_norm``/``ffn_norm`` and :class:`Weight` projections."""
 
-    def __init__(self, params: dict, tok_embeddings: Weight, output: Weight, final_norm, layers, kv_f16: bool):
+    def __init__(self, params: dict, tok_embeddings: Weight, output: Weight, final_norm, layers, kv_f16: bool, rope_neox: bool = False):
         self.p = params
         self.keep = [tok_embeddings, output, layers]
         self.final_norm = np.ascontiguousarray(final_norm, np.float32)
@@ -267,6 +268,11 @@ class LlamaModel:
             arr[i].attn_norm, arr[i].ffn_norm = an.ctypes.data, fn.ctypes.data
             for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down"):
                 setattr(arr[i], n, l[n].c)
+            for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm"):  # optional variants (lib.rs:877-901)
+                if l.get(n) is not None:
+                    a = np.ascontiguousarray(l[n], np.float32)
+                    self.keep.append(a)
+                    setattr(arr[i], n, a.ctypes.data)
         self.layers = arr
         kv_dim = params["n_kv_head"] * params["head_dim"]
         self.key_cache = np.zeros((params["n_layer"], params["n_ctx"], kv_dim), np.float32)
@@ -275,7 +281,7 @@ class LlamaModel:
             params["n_embd"], params["n_layer"], params["n_head"], params["n_kv_head"], params["head_dim"],
             params["n_ff"], params["n_ctx"], params["vocab"], params["rope_theta"], params["eps"],
             tok_embeddings.c, output.c, self.final_norm.ctypes.data, C.addressof(arr),
-            self.key_cache.ctypes.data, self.val_cache.ctypes.data, 1 if kv_f16 else 0,
+            self.key_cache.ctypes.data, self.val_cache.ctypes.data, 1 if kv_f16 else 0, 1 if rope_neox else 0,
         )
 
     def embed(self, token: int) -> np.ndarray:

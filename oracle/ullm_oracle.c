@@ -278,6 +278,21 @@ void uo_rope(float *vec, size_t n_heads, size_t head_dim, size_t rotary_dim, siz
         }
     }
 }
+/* math.rs:140-162: rotate-half pairs; only the first rotary_dim of a head turns */
+void uo_rope_neox(float *vec, size_t n_heads, size_t head_dim, size_t rotary_dim, size_t pos, float theta) {
+    size_t half = rotary_dim / 2;
+    for (size_t h = 0; h < n_heads; h++) {
+        size_t off = h * head_dim;
+        for (size_t i = 0; i < half; i++) {
+            float freq = 1.0f / powf(theta, 2.0f * (float)i / (float)rotary_dim);
+            float ang = (float)pos * freq;
+            float sn = sinf(ang), cs = cosf(ang);
+            float a = vec[off + i], b = vec[off + i + half];
+            vec[off + i] = a * cs - b * sn;
+            vec[off + i + half] = a * sn + b * cs;
+        }
+    }
+}
 /* ---- crates/ullm-model/src/sample.rs:125-133 ---- */
 size_t uo_argmax(const float *x, size_t n) {
     size_t best = 0;
@@ -369,8 +384,30 @@ void uo_forward_llama_embd(uo_model *m, const float *x_init, size_t pos, float *
         uo_matvec_q(&lw->wq, xb, q);
         uo_matvec_q(&lw->wk, xb, k);
         uo_matvec_q(&lw->wv, xb, v);
-        uo_rope(q, m->n_head, hd, hd, pos, m->rope_theta);
-        uo_rope(k, m->n_kv_head, hd, hd, pos, m->rope_theta);
+        if (lw->q_bias) for (size_t i = 0; i < q_dim; i++) q[i] += lw->q_bias[i];   /* lib.rs:877-885 */
+        if (lw->k_bias) for (size_t i = 0; i < kv_dim; i++) k[i] += lw->k_bias[i];
+        if (lw->v_bias) for (size_t i = 0; i < kv_dim; i++) v[i] += lw->v_bias[i];
+        if (lw->q_norm) { /* lib.rs:887-901: per-head RMSNorm before RoPE */
+            float tmp[512];
+            for (size_t h = 0; h < m->n_head; h++) {
+                uo_rmsnorm(q + h * hd, lw->q_norm, hd, m->eps, tmp);
+                memcpy(q + h * hd, tmp, hd * 4);
+            }
+        }
+        if (lw->k_norm) {
+            float tmp[512];
+            for (size_t h = 0; h < m->n_kv_head; h++) {
+                uo_rmsnorm(k + h * hd, lw->k_norm, hd, m->eps, tmp);
+                memcpy(k + h * hd, tmp, hd * 4);
+            }
+        }
+        if (m->rope_neox) {
+            uo_rope_neox(q, m->n_head, hd, hd, pos, m->rope_theta);
+            uo_rope_neox(k, m->n_kv_head, hd, hd, pos, m->rope_theta);
+        } else {
+            uo_rope(q, m->n_head, hd, hd, pos, m->rope_theta);
+            uo_rope(k, m->n_kv_head, hd, hd, pos, m->rope_theta);
+        }
         size_t kv_base = l * m->n_ctx * kv_dim, off = kv_base + pos * kv_dim;
         for (size_t i = 0; i < kv_dim; i++) {
             m->key_cache[off + i] = m->kv_f16 ? uo_round_f16(k[i]) : k[i];

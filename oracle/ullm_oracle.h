@@ -82,7 +82,8 @@ void uo_matvec_q(const uo_qweight *w, const float *x, float *y);
 /* math.rs:38-63: xs token-major [s_len, cols] -> y token-major [s_len, out]. */
 void uo_matmul_q(const uo_qweight *w, const float *xs, size_t s_len, float *y);
 
-/* math.rs:82-86, :89-100, :103-105, :116-136 */
+/* math.rs:82-86, :89-100, :103-105, :116-136, :140-162 */
+void uo_rope_neox(float *vec, size_t n_heads, size_t head_dim, size_t rotary_dim, size_t pos, float theta);
 void uo_rmsnorm(const float *x, const float *weight, size_t n, float eps, float *y);
 void uo_softmax(float *x, size_t n);
 float uo_silu(float x);
@@ -109,6 +110,9 @@ void uo_moe_ffn(const uo_moe_experts *e, const float *logits, size_t k, const fl
 typedef struct {
     const float *attn_norm, *ffn_norm;
     uo_qweight wq, wk, wv, wo, w_gate, w_up, w_down;
+    /* optional (NULL = absent): Qwen2 projection biases (lib.rs:877-885) and the per-head
+     * Q/K RMSNorm weights [head_dim] applied before RoPE (lib.rs:887-901) */
+    const float *q_bias, *k_bias, *v_bias, *q_norm, *k_norm;
 } uo_layer;
 typedef struct {
     size_t n_embd, n_layer, n_head, n_kv_head, head_dim, n_ff, n_ctx, vocab;
@@ -118,6 +122,7 @@ typedef struct {
     const uo_layer *layers;
     float *key_cache, *val_cache; /* [n_layer][n_ctx][kv_dim] f32 */
     int kv_f16;
+    int rope_neox; /* rotate-half pairs (x[i], x[i + d/2]) instead of interleaved ones (lib.rs:903-909) */
 } uo_model;
 void uo_embed(const uo_model *m, uint32_t token, float *x);
 void uo_forward_llama(uo_model *m, uint32_t token, size_t pos, float *logits);

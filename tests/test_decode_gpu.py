@@ -63,9 +63,11 @@ def test_tiny_decode_with_prefilled_cache_and_greedy(ctx):
 def test_decode_rejects_unbuilt_variants(ctx):
     p = dict(synth.LLAMA_TINY)
     m = synth.gen_llama_model(p, 3)
-    for flag in ("rope_neox", "qk_norm", "sandwich_norm", "geglu", "sliding_window", "n_experts"):
+    for flag in ("sandwich_norm", "geglu", "sliding_window", "n_experts"):
         with pytest.raises(backend.Unsupported):
             backend.GpuForward(ctx, m, **{flag: 1})
+    with pytest.raises(backend.FormatError):  # qk_norm without the norm vectors
+        backend.GpuForward(ctx, m, qk_norm=1)
     bad = dict(m)
     bad["output"] = (backend.F32, m["output"][1], m["output"][2], m["output"][3])
     with pytest.raises(backend.Unsupported):  # forward.rs:376-378
@@ -154,3 +156,38 @@ def test_engine_built_from_a_gguf_file_equals_the_one_built_from_arrays(ctx, tmp
     x = om.embed(5)
     assert np.array_equal(tied.forward(x, 0), ref.forward(x, 0))
     tied.free(), ref.free()
+
+
+def variant_model(p, seed, bias, qk_norm):
+    m = synth.gen_llama_model(p, seed)
+    qd, kvd, hd = p["n_head"] * p["head_dim"], p["n_kv_head"] * p["head_dim"], p["head_dim"]
+    for i, l in enumerate(m["layers"]):
+        if bias:  # Qwen2-style projection biases (lib.rs:877-885)
+            l["q_bias"], l["k_bias"], l["v_bias"] = (synth.normal(900 + 10 * i + j, n) * np.float32(20.0) for j, n in enumerate((qd, kvd, kvd)))
+        if qk_norm:  # Qwen3-style per-head Q/K RMSNorm weights (lib.rs:887-901)
+            l["q_norm"] = (1.0 + 0.1 * synth.normal(950 + i, hd)).astype(np.float32)
+            l["k_norm"] = (1.0 + 0.1 * synth.normal(970 + i, hd)).astype(np.float32)
+    return m
+
+
+@pytest.mark.parametrize("bias,qk_norm,neox,kv_f16", [(True, False, False, True), (False, True, False, False), (False, False, True, True),
+                                                      (True, True, True, False)])
+def test_decode_variants_bias_qknorm_neox(ctx, bias, qk_norm, neox, kv_f16):
+    """The GpuParams / GpuLayerInput options of forward.rs:35-50,86-90 that the dense step carries:
+    q/k/v biases, per-head Q/K RMSNorm before RoPE, rotate-half RoPE — each against the oracle."""
+    p = dict(synth.LLAMA_TINY)
+    m = variant_model(p, 31, bias, qk_norm)
+    mk = lambda t: oracle.Weight(t[0], t[1], t[2], t[3])
+    layers = [{k: (mk(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in m["layers"]]
+    om = oracle.LlamaModel(m["params"], mk(m["tok_embd"]), mk(m["output"]), m["final_norm"], layers, kv_f16, rope_neox=neox)
+    gf = backend.GpuForward(ctx, m, kv_f16=kv_f16, rope_neox=1 if neox else 0, qk_norm=1 if qk_norm else 0)
+    base = backend.GpuForward(ctx, synth.gen_llama_model(p, 31), kv_f16=kv_f16)
+    tok, differs = 11, False
+    for pos in range(6):
+        ref = om.forward(tok, pos)
+        got = gf.forward(om.embed(tok), pos)
+        assert synth.rel_err(got, ref) < 1e-3, pos
+        differs = differs or synth.rel_err(base.forward(om.embed(tok), pos), ref) > 1e-2  # the option is not a no-op
+        tok = oracle.argmax(ref)
+    assert differs
+    gf.free(), base.free()

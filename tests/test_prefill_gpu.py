@@ -162,3 +162,27 @@ def test_chunked_prefill_equals_token_by_token_on_the_gpu(ctx, small):
     assert synth.rel_err(got, ref16) < 3e-3
     assert synth.rel_err(got, step) < synth.rel_err(ref16, step) + 5e-3
     a.free(), b.free()
+
+
+def test_prefill_variants_fill_the_cache_like_the_decode_path(ctx, small):
+    """Biases, per-head Q/K norm and rotate-half RoPE in the batched pass: a decode step on the cache it
+    leaves must agree with a decode step on a cache built token by token (same engine options)."""
+    m = dict(small)
+    p = m["params"]
+    qd, kvd, hd = p["n_head"] * p["head_dim"], p["n_kv_head"] * p["head_dim"], p["head_dim"]
+    m["layers"] = [dict(l) for l in small["layers"]]
+    for i, l in enumerate(m["layers"]):
+        l["q_bias"], l["k_bias"], l["v_bias"] = (synth.normal(800 + 10 * i + j, n) * np.float32(0.5) for j, n in enumerate((qd, kvd, kvd)))
+        l["q_norm"] = (1.0 + 0.1 * synth.normal(850 + i, hd)).astype(np.float32)
+        l["k_norm"] = (1.0 + 0.1 * synth.normal(870 + i, hd)).astype(np.float32)
+    om = oracle_model(small, True)
+    s = 19
+    toks = synth.rand_ints(9, s + 1, 0, SMALL["vocab"] - 1)
+    embeds = np.stack([om.embed(int(t)) for t in toks])
+    a, b = backend.GpuForward(ctx, m, kv_f16=True, rope_neox=1, qk_norm=1), backend.GpuForward(ctx, m, kv_f16=True, rope_neox=1, qk_norm=1)
+    for pos in range(s):
+        step = a.forward(embeds[pos], pos)
+    got = b.forward_batch(embeds[:s], s)
+    assert synth.rel_err(got, step) < 5e-2
+    assert synth.rel_err(b.forward(embeds[s], s), a.forward(embeds[s], s)) < 5e-2
+    a.free(), b.free()

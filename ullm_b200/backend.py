@@ -451,7 +451,8 @@ class GpuParams(C.Structure):
 
 
 class GpuLayerInput(C.Structure):
-    _fields_ = [("attn_norm", _vp), ("ffn_norm", _vp)] + [(n, GpuWeight) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")]
+    _fields_ = [("attn_norm", _vp), ("ffn_norm", _vp)] + [(n, GpuWeight) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")] + [
+        (n, _vp) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")]
 
 
 class GpuModelInput(C.Structure):
@@ -486,6 +487,9 @@ class GpuForward:
             layers[i].attn_norm, layers[i].ffn_norm = f32p(l["attn_norm"]), f32p(l["ffn_norm"])
             for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down"):
                 setattr(layers[i], n, gw(l[n]))
+            for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm"):
+                if l.get(n) is not None:
+                    setattr(layers[i], n, f32p(l[n]))
         gp = GpuParams(p["n_embd"], p["n_layer"], p["n_head"], p["n_kv_head"], p["head_dim"], p["n_ff"], p["n_ctx"], p["vocab"],
                        p["rope_theta"], p["eps"], flags.get("rope_neox", 0), flags.get("qk_norm", 0), flags.get("sandwich_norm", 0),
                        flags.get("geglu", 0), flags.get("n_experts", 0), flags.get("n_experts_used", 0), flags.get("moe_inter", 0),

@@ -771,8 +771,6 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, u
     *out = nullptr;
     const ullm_gpu_params &gp = in->params;
     // Flags no benchmark configuration uses are refused, not ignored.
-    if (gp.rope_neox) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "NeoX RoPE is not built");
-    if (gp.qk_norm) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "per-head Q/K RMSNorm is not built");
     if (gp.sandwich_norm) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "sandwich norms are not built");
     if (gp.geglu) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "GeGLU is not built");
     if (gp.n_experts || gp.n_experts_used || gp.moe_inter) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MoE layers inside the decode step are not built");
@@ -780,6 +778,7 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, u
     ForwardParams P;
     P.n_embd = gp.n_embd, P.n_layer = gp.n_layer, P.n_head = gp.n_head, P.n_kv_head = gp.n_kv_head, P.head_dim = gp.head_dim;
     P.n_ff = gp.n_ff, P.n_ctx = gp.n_ctx, P.vocab = gp.vocab, P.rope_theta = gp.rope_theta, P.eps = gp.eps, P.kv_f16 = gp.kv_f16;
+    P.rope_neox = gp.rope_neox != 0, P.qk_norm = gp.qk_norm != 0;
     if (const char *m = Forward::check_params(P)) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s", m);
     const size_t qd = P.n_head * P.head_dim, kvd = P.n_kv_head * P.head_dim;
     auto conv = [&](const ullm_gpu_weight &w, size_t out_dim, size_t cols, HostWeight *hw, const char *name) -> int {
@@ -802,6 +801,13 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, u
         HostLayer &hl = hm.layers[l];
         if (!li.attn_norm || !li.ffn_norm) return ULLM_ERR_INVALID;
         hl.attn_norm = li.attn_norm, hl.ffn_norm = li.ffn_norm;
+        hl.q_bias = li.q_bias, hl.k_bias = li.k_bias, hl.v_bias = li.v_bias;
+        if (P.qk_norm) {
+            if (!li.q_norm || !li.k_norm) return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: qk_norm is set but q_norm / k_norm are missing", l);
+            hl.q_norm = li.q_norm, hl.k_norm = li.k_norm;
+        } else if (li.q_norm || li.k_norm) {
+            return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: q_norm / k_norm given but params.qk_norm is not set", l);
+        }
         if ((rc = conv(li.wq, qd, P.n_embd, &hl.wq, "wq")) || (rc = conv(li.wk, kvd, P.n_embd, &hl.wk, "wk")) ||
             (rc = conv(li.wv, kvd, P.n_embd, &hl.wv, "wv")) || (rc = conv(li.wo, P.n_embd, qd, &hl.wo, "wo")) ||
             (rc = conv(li.w_gate, P.n_ff, P.n_embd, &hl.w_gate, "w_gate")) ||

@@ -46,7 +46,46 @@ struct AttnParams {
     unsigned *counters;           // [n_kv_head], zero between launches
     float *out;                   // [n_head * HD]
     int kv_dim, n_split;
+    // optional model variants (crates/ullm-model/src/lib.rs:877-909), null / 0 = absent
+    const float *q_bias, *k_bias, *v_bias; // added to the projections
+    const float *q_norm, *k_norm;          // per-head RMSNorm weights [HD], applied before RoPE
+    float eps;
+    int neox;                              // rotate-half pairs (i, i + HD/2) instead of (2i, 2i+1)
 };
+
+// One head's projection -> (+ bias) -> (per-head RMSNorm) -> RoPE, in shared memory `dst[HD]`, by one
+// warp (all 32 lanes call it).  Products and sums unfused as in math.rs:130-132 / :154-158; the norm
+// as math.rs:82-86 (x * inv * w, inv = 1 / sqrt(mean(x^2) + eps)).
+template <int HD>
+__device__ __forceinline__ void head_prepare(const float *__restrict__ src, const float *__restrict__ bias,
+                                             const float *__restrict__ norm_w, float eps, const float2 *__restrict__ rp, int neox,
+                                             float *dst, int lane) {
+    constexpr int E = HD / 32;
+    float v[E], ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const int d = lane + 32 * e;
+        v[e] = src[d] + (bias ? bias[d] : 0.f);
+        ss += v[e] * v[e];
+    }
+    if (norm_w) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[e] = v[e] * inv * norm_w[lane + 32 * e];
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) dst[lane + 32 * e] = v[e];
+    __syncwarp();
+    for (int j = lane; j < HD / 2; j += 32) {
+        const int ia = neox ? j : 2 * j, ib = neox ? j + HD / 2 : 2 * j + 1;
+        const float a = dst[ia], b = dst[ib];
+        const float2 cs = rp[j];
+        dst[ia] = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+        dst[ib] = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+    }
+    __syncwarp();
+}
 
 // Sums each of the 32 values over the warp; on return lane L holds the total of
 // value index L.
@@ -88,26 +127,19 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     KV_T *kc = (KV_T *)p.kcache, *vc = (KV_T *)p.vcache;
     const float2 *rp = p.rope + (size_t)pos * (HD / 2);
 
-    // RoPE, interleaved pairs, products and sums kept unfused as in math.rs:130-132
-    for (int i = tid; i < KVMUL * (HD / 2); i += 128) {
-        const int h = i / (HD / 2), j = i % (HD / 2);
-        const float *qp = p.q + (size_t)(kvh * KVMUL + h) * HD + 2 * j;
-        const float a = qp[0], b = qp[1];
-        const float2 cs = rp[j];
-        qs[h][2 * j] = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
-        qs[h][2 * j + 1] = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
-    }
-    if (sp == n_active - 1) {
-        for (int j = tid; j < HD / 2; j += 128) {
-            const float *kp = p.knew + (size_t)kvh * HD + 2 * j;
-            const float a = kp[0], b = kp[1];
-            const float2 cs = rp[j];
-            KV_T *dst = kc + (size_t)pos * p.kv_dim + kvh * HD + 2 * j;
-            dst[0] = kv_make<KV_T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
-            dst[1] = kv_make<KV_T>(__fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)));
+    // the new token's q heads of this kv head (and, in the CTA that owns `pos`, its k and v): bias,
+    // per-head norm and RoPE as the model asks, then the cache write
+    __shared__ float kn[HD];
+    for (int h = warp; h < KVMUL; h += 4)
+        head_prepare<HD>(p.q + (size_t)(kvh * KVMUL + h) * HD, p.q_bias ? p.q_bias + (size_t)(kvh * KVMUL + h) * HD : nullptr, p.q_norm,
+                         p.eps, rp, p.neox, qs[h], lane);
+    if (sp == n_active - 1 && warp == 3) {
+        head_prepare<HD>(p.knew + (size_t)kvh * HD, p.k_bias ? p.k_bias + (size_t)kvh * HD : nullptr, p.k_norm, p.eps, rp, p.neox, kn, lane);
+        for (int j = lane; j < HD; j += 32) {
+            kc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(kn[j]);
+            const float vv = p.vnew[(size_t)kvh * HD + j] + (p.v_bias ? p.v_bias[(size_t)kvh * HD + j] : 0.f);
+            vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(vv);
         }
-        for (int j = tid; j < HD; j += 128)
-            vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(p.vnew[(size_t)kvh * HD + j]);
     }
     __syncthreads();
 
@@ -408,6 +440,14 @@ cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardP
         Layer &L = layers[l];
         TRY(upload(h.attn_norm, P.n_embd * 4, (void **)&L.attn_norm));
         TRY(upload(h.ffn_norm, P.n_embd * 4, (void **)&L.ffn_norm));
+        {
+            const size_t qd_ = P.n_head * P.head_dim, kvd_ = P.n_kv_head * P.head_dim;
+            if (h.q_bias) TRY(upload(h.q_bias, qd_ * 4, (void **)&L.q_bias));
+            if (h.k_bias) TRY(upload(h.k_bias, kvd_ * 4, (void **)&L.k_bias));
+            if (h.v_bias) TRY(upload(h.v_bias, kvd_ * 4, (void **)&L.v_bias));
+            if (h.q_norm) TRY(upload(h.q_norm, P.head_dim * 4, (void **)&L.q_norm));
+            if (h.k_norm) TRY(upload(h.k_norm, P.head_dim * 4, (void **)&L.k_norm));
+        }
         L.qk_fused = h.wq.dtype == h.wk.dtype;
         if (L.qk_fused) {
             TRY(upload_pair(h.wq, h.wk, false, &L.wqk));
@@ -533,6 +573,8 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
         ap.vcache = (uint8_t *)vcache + l * P.n_ctx * kvd * kvb;
         ap.rope = rope, ap.pos_ptr = pos_ptr, ap.scale = 1.0f / sqrtf((float)hd);
         ap.partial = partial, ap.counters = counters, ap.out = attn, ap.kv_dim = (int)kvd, ap.n_split = n_split;
+        ap.q_bias = L.q_bias, ap.k_bias = L.k_bias, ap.v_bias = L.v_bias, ap.q_norm = L.q_norm, ap.k_norm = L.k_norm;
+        ap.eps = P.eps, ap.neox = P.rope_neox;
         TRY(launch_attn(ap, (int)hd, (int)(P.n_head / P.n_kv_head), (int)P.n_kv_head, P.kv_f16 != 0, stream, use_pdl));
         ++launches;
         TRY(mv(L.wo, attn, x, nullptr, EPI_RESIDUAL, x));

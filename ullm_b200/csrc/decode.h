@@ -12,6 +12,7 @@ struct ForwardParams { // GpuParams, crates/ullm-metal/src/forward.rs:24-51 (den
     size_t n_embd = 0, n_layer = 0, n_head = 0, n_kv_head = 0, head_dim = 0, n_ff = 0, n_ctx = 0, vocab = 0;
     float rope_theta = 10000.f, eps = 1e-5f;
     int kv_f16 = 0;
+    int rope_neox = 0, qk_norm = 0;
 };
 struct HostWeight { // GpuWeight, forward.rs:56-64
     int dtype = 0;
@@ -21,6 +22,7 @@ struct HostWeight { // GpuWeight, forward.rs:56-64
 struct HostLayer {
     const float *attn_norm = nullptr, *ffn_norm = nullptr;
     HostWeight wq, wk, wv, wo, w_gate, w_up, w_down;
+    const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr;
 };
 struct HostModel {
     HostWeight output;
@@ -37,6 +39,7 @@ struct Forward {
     };
     struct Layer {
         float *attn_norm = nullptr, *ffn_norm = nullptr;
+        float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr; // optional
         bool qk_fused = false, gu_fused = false;
         Mat wqk, wq, wk, wv, wo, wgu, wg, wu, wd;
     };

@@ -44,28 +44,71 @@ template <typename T> __device__ __forceinline__ float kv_to(T v);
 template <> __device__ __forceinline__ float kv_to<float>(float v) { return v; }
 template <> __device__ __forceinline__ float kv_to<__half>(__half v) { return __half2float(v); }
 
-// RoPE on interleaved pairs (math.rs:116-136, products and sums unfused) of q (in place) and of
-// k, which goes to the cache together with v.  qk: [s, qd + kvd], v: [s, kvd]; one CTA per token.
-template <typename KV_T>
-__global__ void __launch_bounds__(256) rope_kv_batch_kernel(float *__restrict__ qk, const float *__restrict__ v,
-                                                           const float2 *__restrict__ rope, KV_T *__restrict__ kc,
-                                                           KV_T *__restrict__ vc, int pos0, int hd, int qd, int kvd) {
-    const int t = blockIdx.x, pos = pos0 + t;
-    float *row = qk + (size_t)t * (qd + kvd);
-    const float2 *rp = rope + (size_t)pos * (hd / 2);
-    for (int i = threadIdx.x; i < (qd + kvd) / 2; i += 256) {
-        const int e = 2 * i, j = (e % hd) / 2; // heads are hd wide in both the q and the k part (qd is a multiple of hd)
-        const float a = row[e], b = row[e + 1];
-        const float2 cs = rp[j];
-        const float r0 = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)), r1 = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
-        if (e < qd) {
-            row[e] = r0, row[e + 1] = r1;
-        } else {
-            KV_T *dst = kc + (size_t)pos * kvd + (e - qd);
-            dst[0] = kv_from<KV_T>(r0), dst[1] = kv_from<KV_T>(r1);
-        }
+// One head: (+ bias) -> (per-head RMSNorm, math.rs:82-86) -> RoPE on interleaved or rotate-half pairs
+// (math.rs:116-162, products and sums unfused), in shared memory, by one warp.  Same steps as the
+// decode kernel's prologue (decode.cu), so both paths fill the cache with the same values.
+template <int HD>
+__device__ __forceinline__ void head_prepare_batch(const float *__restrict__ src, const float *__restrict__ bias,
+                                                   const float *__restrict__ norm_w, float eps, const float2 *__restrict__ rp, int neox,
+                                                   float *dst, int lane) {
+    constexpr int E = HD / 32;
+    float v[E], ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const int d = lane + 32 * e;
+        v[e] = src[d] + (bias ? bias[d] : 0.f);
+        ss += v[e] * v[e];
     }
-    for (int i = threadIdx.x; i < kvd; i += 256) vc[(size_t)pos * kvd + i] = kv_from<KV_T>(v[(size_t)t * kvd + i]);
+    if (norm_w) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[e] = v[e] * inv * norm_w[lane + 32 * e];
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) dst[lane + 32 * e] = v[e];
+    __syncwarp();
+    for (int j = lane; j < HD / 2; j += 32) {
+        const int ia = neox ? j : 2 * j, ib = neox ? j + HD / 2 : 2 * j + 1;
+        const float a = dst[ia], b = dst[ib];
+        const float2 cs = rp[j];
+        dst[ia] = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+        dst[ib] = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+    }
+    __syncwarp();
+}
+
+struct RopeBatchParams {
+    float *qk;            // [s, qd + kvd]: q heads then k heads of every token; q is rewritten in place
+    const float *v;       // [s, kvd]
+    const float2 *rope;
+    void *kc, *vc;        // this layer's cache
+    const float *q_bias, *k_bias, *v_bias, *q_norm, *k_norm; // optional
+    float eps;
+    int pos0, n_head, n_kv_head, neox;
+};
+
+// one CTA per token, one warp per head in turn; k and v go to the cache
+template <int HD, typename KV_T> __global__ void __launch_bounds__(256) rope_kv_batch_kernel(const RopeBatchParams p) {
+    __shared__ float buf[8][HD];
+    const int t = blockIdx.x, pos = p.pos0 + t, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qd = p.n_head * HD, kvd = p.n_kv_head * HD;
+    float *row = p.qk + (size_t)t * (qd + kvd);
+    const float2 *rp = p.rope + (size_t)pos * (HD / 2);
+    KV_T *kc = (KV_T *)p.kc, *vc = (KV_T *)p.vc;
+    for (int hh = warp; hh < p.n_head + p.n_kv_head; hh += 8) {
+        const bool is_q = hh < p.n_head;
+        const int hk = hh - p.n_head;
+        const float *bias = is_q ? (p.q_bias ? p.q_bias + (size_t)hh * HD : nullptr) : (p.k_bias ? p.k_bias + (size_t)hk * HD : nullptr);
+        head_prepare_batch<HD>(row + (size_t)hh * HD, bias, is_q ? p.q_norm : p.k_norm, p.eps, rp, p.neox, buf[warp], lane);
+        for (int d = lane; d < HD; d += 32) {
+            if (is_q) row[(size_t)hh * HD + d] = buf[warp][d];
+            else kc[(size_t)pos * kvd + (size_t)hk * HD + d] = kv_from<KV_T>(buf[warp][d]);
+        }
+        __syncwarp();
+    }
+    for (int i = threadIdx.x; i < kvd; i += 256)
+        vc[(size_t)pos * kvd + i] = kv_from<KV_T>(p.v[(size_t)t * kvd + i] + (p.v_bias ? p.v_bias[i] : 0.f));
 }
 
 // Eight consecutive cache values of one position -> f32 (one 16- or 32-byte load)
@@ -208,14 +251,26 @@ cudaError_t Forward::forward_batch(const float *embeds_host, size_t s, float *lo
             TRY(gemm(L.wv, bxn, bv, n));
             const dim3 ag((unsigned)P.n_head, (unsigned)((n + 7) / 8));
             const int kvmul = (int)(P.n_head / P.n_kv_head);
+            RopeBatchParams rb;
+            rb.qk = bqk, rb.v = bv, rb.rope = rope, rb.kc = kc, rb.vc = vc;
+            rb.q_bias = L.q_bias, rb.k_bias = L.k_bias, rb.v_bias = L.v_bias, rb.q_norm = L.q_norm, rb.k_norm = L.k_norm;
+            rb.eps = P.eps, rb.pos0 = (int)c0, rb.n_head = (int)P.n_head, rb.n_kv_head = (int)P.n_kv_head, rb.neox = P.rope_neox;
             if (P.kv_f16) {
-                rope_kv_batch_kernel<__half><<<(unsigned)n, 256, 0, stream>>>(bqk, bv, rope, (__half *)kc, (__half *)vc, (int)c0, (int)hd, (int)qd, (int)kvd);
-                if (hd == 64) attn_prefill_kernel<64, __half><<<ag, 256, 0, stream>>>(bqk, (const __half *)kc, (const __half *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
-                else attn_prefill_kernel<128, __half><<<ag, 256, 0, stream>>>(bqk, (const __half *)kc, (const __half *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
+                if (hd == 64) {
+                    rope_kv_batch_kernel<64, __half><<<(unsigned)n, 256, 0, stream>>>(rb);
+                    attn_prefill_kernel<64, __half><<<ag, 256, 0, stream>>>(bqk, (const __half *)kc, (const __half *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
+                } else {
+                    rope_kv_batch_kernel<128, __half><<<(unsigned)n, 256, 0, stream>>>(rb);
+                    attn_prefill_kernel<128, __half><<<ag, 256, 0, stream>>>(bqk, (const __half *)kc, (const __half *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
+                }
             } else {
-                rope_kv_batch_kernel<float><<<(unsigned)n, 256, 0, stream>>>(bqk, bv, rope, (float *)kc, (float *)vc, (int)c0, (int)hd, (int)qd, (int)kvd);
-                if (hd == 64) attn_prefill_kernel<64, float><<<ag, 256, 0, stream>>>(bqk, (const float *)kc, (const float *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
-                else attn_prefill_kernel<128, float><<<ag, 256, 0, stream>>>(bqk, (const float *)kc, (const float *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
+                if (hd == 64) {
+                    rope_kv_batch_kernel<64, float><<<(unsigned)n, 256, 0, stream>>>(rb);
+                    attn_prefill_kernel<64, float><<<ag, 256, 0, stream>>>(bqk, (const float *)kc, (const float *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
+                } else {
+                    rope_kv_batch_kernel<128, float><<<(unsigned)n, 256, 0, stream>>>(rb);
+                    attn_prefill_kernel<128, float><<<ag, 256, 0, stream>>>(bqk, (const float *)kc, (const float *)vc, bxn, (int)n, (int)c0, (int)qd, (int)kvd, kvmul, scale);
+                }
             }
             TRY(cudaGetLastError());
             // the attention output [n, qd] sits in bxn; residual adds and silu(g)*u happen in the GEMM epilogues
