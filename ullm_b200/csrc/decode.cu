@@ -17,6 +17,7 @@
 #include "decode.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -130,15 +131,40 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     // the new token's q heads of this kv head (and, in the CTA that owns `pos`, its k and v): bias,
     // per-head norm and RoPE as the model asks, then the cache write
     __shared__ float kn[HD];
-    for (int h = warp; h < KVMUL; h += 4)
-        head_prepare<HD>(p.q + (size_t)(kvh * KVMUL + h) * HD, p.q_bias ? p.q_bias + (size_t)(kvh * KVMUL + h) * HD : nullptr, p.q_norm,
-                         p.eps, rp, p.neox, qs[h], lane);
-    if (sp == n_active - 1 && warp == 3) {
-        head_prepare<HD>(p.knew + (size_t)kvh * HD, p.k_bias ? p.k_bias + (size_t)kvh * HD : nullptr, p.k_norm, p.eps, rp, p.neox, kn, lane);
-        for (int j = lane; j < HD; j += 32) {
-            kc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(kn[j]);
-            const float vv = p.vnew[(size_t)kvh * HD + j] + (p.v_bias ? p.v_bias[(size_t)kvh * HD + j] : 0.f);
-            vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(vv);
+    const bool plain = !p.q_bias && !p.k_bias && !p.v_bias && !p.q_norm && !p.k_norm && !p.neox;
+    if (plain) {
+        // plain Llama: interleaved RoPE only, all pairs in parallel (products and sums unfused, math.rs:130-132)
+        for (int i = tid; i < KVMUL * (HD / 2); i += 128) {
+            const int h = i / (HD / 2), j = i % (HD / 2);
+            const float *qp = p.q + (size_t)(kvh * KVMUL + h) * HD + 2 * j;
+            const float a = qp[0], b = qp[1];
+            const float2 cs = rp[j];
+            qs[h][2 * j] = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+            qs[h][2 * j + 1] = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+        }
+        if (sp == n_active - 1) {
+            for (int j = tid; j < HD / 2; j += 128) {
+                const float *kp = p.knew + (size_t)kvh * HD + 2 * j;
+                const float a = kp[0], b = kp[1];
+                const float2 cs = rp[j];
+                KV_T *dst = kc + (size_t)pos * p.kv_dim + kvh * HD + 2 * j;
+                dst[0] = kv_make<KV_T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
+                dst[1] = kv_make<KV_T>(__fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)));
+            }
+            for (int j = tid; j < HD; j += 128)
+                vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(p.vnew[(size_t)kvh * HD + j]);
+        }
+    } else {
+        for (int h = warp; h < KVMUL; h += 4)
+            head_prepare<HD>(p.q + (size_t)(kvh * KVMUL + h) * HD, p.q_bias ? p.q_bias + (size_t)(kvh * KVMUL + h) * HD : nullptr,
+                             p.q_norm, p.eps, rp, p.neox, qs[h], lane);
+        if (sp == n_active - 1 && warp == 3) {
+            head_prepare<HD>(p.knew + (size_t)kvh * HD, p.k_bias ? p.k_bias + (size_t)kvh * HD : nullptr, p.k_norm, p.eps, rp, p.neox, kn, lane);
+            for (int j = lane; j < HD; j += 32) {
+                kc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(kn[j]);
+                const float vv = p.vnew[(size_t)kvh * HD + j] + (p.v_bias ? p.v_bias[(size_t)kvh * HD + j] : 0.f);
+                vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(vv);
+            }
         }
     }
     __syncthreads();
@@ -428,6 +454,7 @@ cudaError_t Forward::upload_one(const HostWeight &a, Mat *out) {
 
 cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardParams &params, const HostModel &m) {
     dev = devinfo, device = device_, P = params;
+    if (const char *v = getenv("ULLM_DECODE_CHAIN")) use_chain = atoi(v) != 0; // comparison knob
     cudaError_t e;
 #define TRY(x) \
     if ((e = (x)) != cudaSuccess) return e;
