@@ -47,6 +47,8 @@ SHAPES = [
     (backend.Q6_K, 128, 2048, 64),
     (backend.Q6_K, 200, 4096, 33),
     (backend.Q6_K, 1024, 2048, 512),
+    (backend.Q4_K, 75 * 256 + 44, 512, 40),   # 76 row tiles on 74 CTA pairs: the last two go to a split-K launch
+    (backend.Q6_K, 38 * 256, 2048, 300),      # 76 tiles (38 x 2 token tiles), prepared Q6_K, split-K tail
 ]
 
 

@@ -131,6 +131,7 @@ struct GemmParams {
     uint32_t blocks_per_split; // 256-k blocks handled by one grid.z slice (split-K for matrices with few row tiles)
     int epi;                   // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU, applied here only when there is one k slice
     const float *res;          // EPI_RESIDUAL: y = res + W x (may alias y)
+    uint32_t ldy;              // elements between two tokens in y / res (the full matrix' rows when this launch covers a row range)
     long long *trace; // measurement only: cycle stamps of CTA (0, 0)
     uint32_t mode; // measurement only: bit 0 skips the dequantization, bit 1 the activation loads, bit 2 the MMAs
 };
@@ -529,14 +530,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                         const float a = __uint_as_float(v[j]), o = __shfl_xor_sync(0xffffffffu, a, 1);
                         const uint32_t tok = n0 + col0 + j;
                         if (!(lane & 1) && orow < p.out_dim && tok < p.s)
-                            yout[(size_t)tok * (p.out_dim >> 1) + (orow >> 1)] = __fdividef(a, 1.0f + __expf(-a)) * o; // operands are bf16 products: fast exp / divide lose nothing that matters
+                            yout[(size_t)tok * (p.ldy >> 1) + (orow >> 1)] = __fdividef(a, 1.0f + __expf(-a)) * o; // operands are bf16 products: fast exp / divide lose nothing that matters
                     }
                 } else if (orow < p.out_dim) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t tok = n0 + col0 + j;
                         if (tok < p.s) {
-                            const size_t at = (size_t)tok * p.out_dim + orow;
+                            const size_t at = (size_t)tok * p.ldy + orow;
                             yout[at] = p.epi == EPI_RESIDUAL ? p.res[at] + __uint_as_float(v[j]) : __uint_as_float(v[j]);
                         }
                     }
@@ -570,13 +571,15 @@ __global__ void cast_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__r
     }
 }
 
-// split-K: y[i] = part[0][i] + part[1][i] + ... in slice order (deterministic), then the epilogue
-__global__ void splitk_reduce_kernel(const float *__restrict__ part, float *y, size_t n, int splits, int epi, const float *res) {
-    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+// split-K: the [s, rows] partial sums of the k slices added in slice order (deterministic), then the
+// epilogue; y / res have `ldy` elements between tokens
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, float *y, size_t s, size_t rows, size_t ldy, int splits, int epi,
+                                     const float *res) {
+    const size_t n = s * rows, i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
     float a[4] = {0.f, 0.f, 0.f, 0.f};
     const int cnt = i + 3 < n ? 4 : (int)(n - i);
-    if (cnt == 4) {
+    if (cnt == 4 && rows % 4 == 0) {
         for (int z = 0; z < splits; ++z) {
             const float4 b = *(const float4 *)(part + (size_t)z * n + i);
             a[0] += b.x, a[1] += b.y, a[2] += b.z, a[3] += b.w;
@@ -585,10 +588,16 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ part, float *y, s
         for (int z = 0; z < splits; ++z)
             for (int k = 0; k < cnt; ++k) a[k] += part[(size_t)z * n + i + k];
     }
-    if (epi == EPI_SWIGLU) { // n and the row length are even: pairs never straddle a thread's four values
-        for (int k = 0; k + 1 < cnt; k += 2) y[(i + k) >> 1] = a[k] / (1.0f + expf(-a[k])) * a[k + 1];
+    if (epi == EPI_SWIGLU) { // rows is even and i a multiple of 4: a (gate, up) pair never straddles two threads or tokens
+        for (int k = 0; k + 1 < cnt; k += 2) {
+            const size_t tok = (i + k) / rows, r = (i + k) % rows;
+            y[tok * (ldy >> 1) + (r >> 1)] = __fdividef(a[k], 1.0f + __expf(-a[k])) * a[k + 1];
+        }
     } else {
-        for (int k = 0; k < cnt; ++k) y[i + k] = epi == EPI_RESIDUAL ? res[i + k] + a[k] : a[k];
+        for (int k = 0; k < cnt; ++k) {
+            const size_t tok = (i + k) / rows, r = (i + k) % rows, at = tok * ldy + r;
+            y[at] = epi == EPI_RESIDUAL ? res[at] + a[k] : a[k];
+        }
     }
 }
 
@@ -641,9 +650,36 @@ static int gemm_splits(size_t out_dim, size_t in_dim, size_t s, int sm_count) {
 }
 static size_t x16_bytes(size_t in_dim, size_t s) { return (s * in_dim * 2 + 255) & ~(size_t)255; }
 
+// How a product is launched.  When the tiles need more than one wave of CTA pairs and the last wave
+// would be less than half full, the rows of that last wave are cut off into a second launch with
+// split-K (a [256 x 256] tile per pair is 75 % efficiency at 3.03 waves, and k slices of two rows of
+// tiles fill the machine instead).
+struct GemmPlan {
+    size_t rows_main = 0, rows_tail = 0;
+    int z_main = 1, z_tail = 1;
+};
+static GemmPlan gemm_plan(size_t out_dim, size_t in_dim, size_t s, int sm_count) {
+    GemmPlan pl;
+    const size_t pairs = (size_t)sm_count / 2, row_tiles = (out_dim + 2 * GM - 1) / (2 * GM), tok_tiles = (s + GN - 1) / GN;
+    const size_t total = row_tiles * tok_tiles, rem = pairs ? total % pairs : 0;
+    pl.rows_main = out_dim;
+    if (total <= pairs) {
+        pl.z_main = gemm_splits(out_dim, in_dim, s, sm_count);
+    } else if (rem != 0 && rem * 2 <= pairs) {
+        const size_t tail_tiles = (rem + tok_tiles - 1) / tok_tiles;
+        if (tail_tiles < row_tiles) {
+            pl.rows_main = (row_tiles - tail_tiles) * 2 * GM;
+            pl.rows_tail = out_dim - pl.rows_main;
+            pl.z_tail = gemm_splits(pl.rows_tail, in_dim, s, sm_count);
+        }
+    }
+    return pl;
+}
+
 size_t gemm_tc_scratch_bytes(size_t out_dim, size_t in_dim, size_t s, int sm_count) {
-    const int z = gemm_splits(out_dim, in_dim, s, sm_count);
-    return x16_bytes(in_dim, s) + (z > 1 ? (size_t)z * s * out_dim * 4 : 0);
+    const GemmPlan pl = gemm_plan(out_dim, in_dim, s, sm_count);
+    const size_t pm = pl.z_main > 1 ? (size_t)pl.z_main * s * pl.rows_main * 4 : 0, pt = pl.z_tail > 1 ? (size_t)pl.z_tail * s * pl.rows_tail * 4 : 0;
+    return x16_bytes(in_dim, s) + std::max(pm, pt);
 }
 
 template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, const GemmMaps &maps, dim3 grid, cudaStream_t st) {
@@ -652,6 +688,40 @@ template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, 
     cudaError_t e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     gemm_q_tc_kernel<FMT, DBG><<<grid, G_THREADS, smem, st>>>(p, maps);
+    return cudaGetLastError();
+}
+
+// One launch (plus the split-K reduction) over `rows` weight rows starting at `w`; y / res point at the
+// first of these rows' outputs, `ldy` elements between tokens.
+static cudaError_t gemm_part(EncodeTiledFn enc, int fmt, const uint8_t *w, size_t rows, size_t in_dim, size_t s, int z, GemmMaps maps,
+                             float *y, const float *res, size_t ldy, int epi, float *part, int *d_status, cudaStream_t st) {
+    const size_t nb = in_dim / QK_K;
+    bool ok = true;
+    if (fmt == FMT_Q4K) {
+        const size_t rb = nb * Q4K_BYTES;
+        ok = encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, rb, rows, rb, Q4K_BYTES, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
+        maps.w1 = maps.w0, maps.w2 = maps.w0;
+    } else {
+        const size_t rb = nb * Q6K_BYTES; // prepared rows: records | scales | d planes
+        ok = encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, nb * 192, rows, rb, 48, GM, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+             encode_2d(enc, &maps.w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, w + nb * 192, nb * 16, rows, rb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+             encode_2d(enc, &maps.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, w + nb * 208, nb * 2, rows, rb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    }
+    if (!ok) return cudaErrorInvalidValue;
+    GemmParams p;
+    p.blocks_per_split = (uint32_t)((nb + z - 1) / z);
+    const unsigned gz = (unsigned)((nb + p.blocks_per_split - 1) / p.blocks_per_split);
+    p.y = gz > 1 ? part : y, p.status = d_status;
+    p.epi = gz > 1 ? EPI_STORE : epi, p.res = res, p.ldy = gz > 1 ? (uint32_t)rows : (uint32_t)ldy;
+    p.out_dim = (uint32_t)rows, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
+    p.mode = g_gemm_mode, p.trace = g_gemm_trace;
+    const dim3 grid(2 * (unsigned)((rows + 2 * GM - 1) / (2 * GM)), (unsigned)((s + GN - 1) / GN), gz);
+    cudaError_t e;
+    if (p.mode || p.trace) e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, true>(p, maps, grid, st) : launch_one<FMT_Q6KR, true>(p, maps, grid, st);
+    else e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
+    if (e != cudaSuccess || gz == 1) return e;
+    const size_t ny = s * rows;
+    splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, y, s, rows, ldy, (int)gz, epi, res);
     return cudaGetLastError();
 }
 
@@ -664,41 +734,21 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
     if (!gemm_tc_supported(fmt, out_dim, in_dim, s) || ((uintptr_t)d_w & 15)) return cudaErrorNotSupported;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
-    const size_t n = s * in_dim, nb = in_dim / QK_K;
+    const size_t n = s * in_dim, row_bytes = in_dim / QK_K * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
     cast_bf16_kernel<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, st>>>(d_x, (__nv_bfloat16 *)d_xb16, n);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     GemmMaps maps;
-    bool ok = encode_2d(enc, &maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_xb16, in_dim, s, in_dim * 2, GKC, GNH, CU_TENSOR_MAP_SWIZZLE_128B);
-    const uint8_t *w = (const uint8_t *)d_w;
-    if (fmt == FMT_Q4K) {
-        const size_t rb = nb * Q4K_BYTES;
-        ok = ok && encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, rb, out_dim, rb, Q4K_BYTES, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
-        maps.w1 = maps.w0, maps.w2 = maps.w0;
-    } else {
-        const size_t rb = nb * Q6K_BYTES; // prepared rows: records | scales | d planes
-        ok = ok && encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, nb * 192, out_dim, rb, 48, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
-        ok = ok && encode_2d(enc, &maps.w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, w + nb * 192, nb * 16, out_dim, rb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
-        ok = ok && encode_2d(enc, &maps.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, w + nb * 208, nb * 2, out_dim, rb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
-    }
-    if (!ok) return cudaErrorInvalidValue;
-    const int splits = gemm_splits(out_dim, in_dim, s, sm_count);
+    if (!encode_2d(enc, &maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_xb16, in_dim, s, in_dim * 2, GKC, GNH, CU_TENSOR_MAP_SWIZZLE_128B))
+        return cudaErrorInvalidValue;
     float *part = (float *)((uint8_t *)d_xb16 + x16_bytes(in_dim, s));
-    GemmParams p;
-    p.blocks_per_split = (uint32_t)((nb + splits - 1) / splits);
-    const unsigned gz = (unsigned)((nb + p.blocks_per_split - 1) / p.blocks_per_split);
-    p.y = gz > 1 ? part : d_y, p.status = d_status;
-    p.epi = gz > 1 ? EPI_STORE : epi, p.res = d_res;
-    p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
-    p.mode = g_gemm_mode, p.trace = g_gemm_trace;
-    const dim3 grid(2 * (unsigned)((out_dim + 2 * GM - 1) / (2 * GM)), (unsigned)((s + GN - 1) / GN),
-                    gz);
-    if (p.mode || p.trace) e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, true>(p, maps, grid, st) : launch_one<FMT_Q6KR, true>(p, maps, grid, st);
-    else e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
-    if (e != cudaSuccess || grid.z == 1) return e;
-    const size_t ny = s * out_dim;
-    splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, d_y, ny, (int)grid.z, epi, d_res);
-    return cudaGetLastError();
+    const GemmPlan pl = gemm_plan(out_dim, in_dim, s, sm_count);
+    const uint8_t *w = (const uint8_t *)d_w;
+    const size_t ydiv = epi == EPI_SWIGLU ? 2 : 1; // SwiGLU halves the output rows
+    e = gemm_part(enc, fmt, w, pl.rows_main, in_dim, s, pl.z_main, maps, d_y, d_res, out_dim, epi, part, d_status, st);
+    if (e != cudaSuccess || pl.rows_tail == 0) return e;
+    return gemm_part(enc, fmt, w + pl.rows_main * row_bytes, pl.rows_tail, in_dim, s, pl.z_tail, maps, d_y + pl.rows_main / ydiv,
+                     d_res ? d_res + pl.rows_main : nullptr, out_dim, epi, part, d_status, st);
 }
 
 } // namespace ullm
