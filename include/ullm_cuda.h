@@ -161,6 +161,13 @@ int ullm_cuda_weight_matmul_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, c
 /* The weight's original on-disk bytes (`len` = ullm_cuda_weight_bytes). */
 int ullm_cuda_weight_export(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, void *bytes, size_t len);
 size_t ullm_cuda_weight_bytes(const ullm_cuda_weight *w);
+/* A resident weight made from the MLX linear `<name>.weight / .scales / .biases` of an open
+ * SafeTensors model (include/ullm_safetensors.h): what mlx_qweight (crates/ullm-model/src/mlx.rs:30-56)
+ * followed by build_gpu's GpuWeight (lib.rs:739-749) produces, except that the tables stay the bf16 bits
+ * of the file instead of being widened to f32 on the host (widening is exact, dequant.rs:286). */
+struct ullm_st;
+int ullm_cuda_weight_create_st(ullm_cuda_ctx *ctx, const struct ullm_st *st, const char *name, size_t group,
+                               ullm_cuda_weight **out);
 
 /* ---- batched matmul (prefill) ----
  * GpuForward::matmul (forward.rs:679-725; kernels matmul_q4k / matmul_q6k /
@@ -186,6 +193,13 @@ typedef struct {
     size_t n_experts, hidden, inter, group;
 } ullm_moe_experts_input;
 int ullm_cuda_experts_create(ullm_cuda_ctx *ctx, const ullm_moe_experts_input *in, ullm_cuda_experts **out);
+/* The experts of one MoE layer from an open SafeTensors model: `<prefix>.gate_proj`, `.up_proj`,
+ * `.down_proj`, each a stacked MLX linear [n_experts, out, in/8] (mlx_experts, mlx.rs:58-88, sliced
+ * per expert there and concatenated again by build_gpu, lib.rs:751-771 — the on-disk stack already is
+ * that concatenation, so the bytes go to the device as they lie in the file).  `prefix` is e.g.
+ * "model.layers.3.mlp.switch_mlp". */
+int ullm_cuda_experts_create_st(ullm_cuda_ctx *ctx, const struct ullm_st *st, const char *prefix, size_t n_experts,
+                                size_t hidden, size_t inter, size_t group, ullm_cuda_experts **out);
 void ullm_cuda_experts_destroy(ullm_cuda_ctx *ctx, ullm_cuda_experts *e);
 /* moe_topk + moe_gate_up_all + moe_down_all + moe_combine (forward.rs:484-494,
  * shader.metal:301-444; CPU form crates/ullm-model/src/lib.rs:1453-1488) for

@@ -39,6 +39,18 @@ def test_gguf_header_and_library_agree():
     assert set(names) == set(gguf.SIGNATURES)
 
 
+def test_safetensors_header_and_library_agree():
+    from ullm_b200 import safetensors
+
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "ullm_safetensors.h")).read(), flags=re.S)
+    names = sorted(set(re.findall(r"\b(ullm_st_[a-z0-9_]+)\s*\(", text)))
+    lib = backend.load_library()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/ullm_safetensors.h but not exported"
+    assert set(names) == set(safetensors.SIGNATURES)
+
+
 def test_context_creation_without_device_is_unsupported():
     import torch  # only to learn whether this machine has a GPU
 

@@ -76,10 +76,12 @@ SIGNATURES = {
     "ullm_cuda_weight_matmul_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "ullm_cuda_weight_export": (_i, [_vp, _vp, _vp, _sz]),
     "ullm_cuda_weight_bytes": (_sz, [_vp]),
+    "ullm_cuda_weight_create_st": (_i, [_vp, _vp, C.c_char_p, _sz, C.POINTER(_vp)]),
     "ullm_cuda_matmul_quant": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "ullm_cuda_matmul_mlx4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),
     "ullm_cuda_matmul_dev": (_i, [_vp, _i, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _sz, _sz, _vp]),
     "ullm_cuda_experts_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "ullm_cuda_experts_create_st": (_i, [_vp, _vp, C.c_char_p, _sz, _sz, _sz, _sz, C.POINTER(_vp)]),
     "ullm_cuda_experts_destroy": (None, [_vp, _vp]),
     "ullm_cuda_moe_ffn": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp]),
     "ullm_cuda_moe_ffn_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
@@ -306,6 +308,17 @@ class Weight:
         ctx._check(ctx._lib.ullm_cuda_weight_create(ctx._h, C.byref(gw), tdt, C.byref(h)))
         self._h, self.out, self.cols, self.dtype = h.value, out_dim, cols, dtype
 
+    @classmethod
+    def from_safetensors(cls, ctx: CudaContext, st, name: str, group: int) -> "Weight":
+        """The MLX linear ``<name>.weight/.scales/.biases`` of an open :class:`ullm_b200.safetensors.SafeTensors`
+        (``ullm_cuda_weight_create_st``): bytes go from the mapped file to the device."""
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_weight_create_st(ctx._h, st._h, name.encode(), group, C.byref(h)))
+        t = st.tensor(name + ".weight")
+        self = cls.__new__(cls)
+        self._ctx, self._h, self.out, self.cols, self.dtype = ctx, h.value, t["shape"][0], t["shape"][1] * 8, MLX_U32
+        return self
+
     def matvec(self, x, out: np.ndarray | None = None) -> np.ndarray:
         x = _f32(x)
         y = np.empty(self.out, np.float32) if out is None else out
@@ -411,6 +424,16 @@ class Experts:
         h = _vp()
         ctx._check(ctx._lib.ullm_cuda_experts_create(ctx._h, C.byref(inp), C.byref(h)))
         self._h, self.n_experts, self.hidden, self.inter = h.value, n_experts, hidden, inter
+
+    @classmethod
+    def from_safetensors(cls, ctx: CudaContext, st, prefix: str, n_experts: int, hidden: int, inter: int, group: int) -> "Experts":
+        """The stacked experts ``<prefix>.gate_proj / .up_proj / .down_proj`` of an open
+        :class:`ullm_b200.safetensors.SafeTensors` (``ullm_cuda_experts_create_st``)."""
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_experts_create_st(ctx._h, st._h, prefix.encode(), n_experts, hidden, inter, group, C.byref(h)))
+        self = cls.__new__(cls)
+        self._ctx, self._h, self.n_experts, self.hidden, self.inter = ctx, h.value, n_experts, hidden, inter
+        return self
 
     def moe_ffn(self, x, logits, k: int, want_routing: bool = False):
         """``moe_ffn`` for every token of x [n_tok, hidden] (crates/ullm-model/src/lib.rs:1453-1488)."""

@@ -4,6 +4,7 @@
 // computes on the CPU.
 #include "../../include/ullm_cuda.h"
 #include "../../include/ullm_gguf.h"
+#include "../../include/ullm_safetensors.h"
 #include "decode.h"
 #include "engine.h"
 
@@ -340,6 +341,19 @@ int ullm_cuda_weight_create(ullm_cuda_ctx *c, const ullm_gpu_weight *gw, int mlx
     }
     *out = w;
     return ULLM_OK;
+}
+
+int ullm_cuda_weight_create_st(ullm_cuda_ctx *c, const ullm_st *st, const char *name, size_t group, ullm_cuda_weight **out) {
+    if (!c || !st || !name || !out) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    char msg[256] = {0};
+    ullm_st_mlx_weight mw;
+    if (ullm_st_mlx_weight_get(st, name, group, &mw, msg, sizeof msg)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", msg);
+    ullm_gpu_weight gw;
+    memset(&gw, 0, sizeof gw);
+    gw.dtype = ULLM_DTYPE_MLX_U32, gw.bytes = mw.weight, gw.len = (size_t)(mw.out * (mw.in / 8) * 4), gw.out = (size_t)mw.out, gw.cols = (size_t)mw.in;
+    gw.mlx_scales = (const float *)mw.scales, gw.mlx_biases = (const float *)mw.biases, gw.mlx_group = group; // bf16 bits, said so below
+    return ullm_cuda_weight_create(c, &gw, ULLM_DTYPE_BF16, out);
 }
 
 void ullm_cuda_weight_destroy(ullm_cuda_ctx *c, ullm_cuda_weight *w) {
@@ -700,6 +714,26 @@ int ullm_cuda_experts_create(ullm_cuda_ctx *c, const ullm_moe_experts_input *in,
     x->e = e;
     *out = x;
     return ULLM_OK;
+}
+
+int ullm_cuda_experts_create_st(ullm_cuda_ctx *c, const ullm_st *st, const char *prefix, size_t n_experts, size_t hidden, size_t inter,
+                                size_t group, ullm_cuda_experts **out) {
+    if (!c || !st || !prefix || !out) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    char msg[256] = {0};
+    ullm_st_mlx_weight g, u, d;
+    const std::string p(prefix);
+    if (ullm_st_mlx_experts_get(st, (p + ".gate_proj").c_str(), n_experts, inter, hidden, group, n_experts, &g, msg, sizeof msg) ||
+        ullm_st_mlx_experts_get(st, (p + ".up_proj").c_str(), n_experts, inter, hidden, group, n_experts, &u, msg, sizeof msg) ||
+        ullm_st_mlx_experts_get(st, (p + ".down_proj").c_str(), n_experts, hidden, inter, group, n_experts, &d, msg, sizeof msg))
+        return ctx_fail(c, ULLM_ERR_FORMAT, "%s", msg);
+    ullm_moe_experts_input in;
+    memset(&in, 0, sizeof in);
+    in.gate_w = g.weight, in.gate_scales = g.scales, in.gate_biases = g.biases;
+    in.up_w = u.weight, in.up_scales = u.scales, in.up_biases = u.biases;
+    in.down_w = d.weight, in.down_scales = d.scales, in.down_biases = d.biases;
+    in.table_dtype = ULLM_DTYPE_BF16, in.n_experts = n_experts, in.hidden = hidden, in.inter = inter, in.group = group;
+    return ullm_cuda_experts_create(c, &in, out);
 }
 
 void ullm_cuda_experts_destroy(ullm_cuda_ctx *c, ullm_cuda_experts *x) {
