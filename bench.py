@@ -459,6 +459,30 @@ def run_other(args):
         out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, prompt_ms_per_token=t_prompt / 16 * 1e3, tokens=n_gen,
                    bytes_per_token=wbytes + kvbytes + 513_024, gbs=(wbytes + kvbytes + 513_024) * n_gen / dt / 1e9,
                    first_tokens=toks[:8].tolist())
+    elif args.workload == "c2decode":
+        # Decode step of the Qwen3-30B-A3B shape (MLX 4-bit, 128 experts, 8 per token): the model the reference
+        # quotes its MoE decode rate on.  One seeded layer's weights are uploaded once per layer (separate device
+        # copies, so every layer streams its own bytes from HBM); tokens are produced by the on-device greedy loop.
+        p = dict(synth.QWEN3MOE_30B)
+        p["n_layer"] = args.layers or p["n_layer"]
+        one = synth.gen_qwen3moe_model(dict(p, n_layer=1), synth.seed_for(2, 8))
+        m = dict(one, params=p, layers=[one["layers"][0]] * p["n_layer"])
+        gf = backend.GpuForward(ctx, m, kv_f16=True, rope_neox=1, qk_norm=1)
+        t = m["tok_embd"]
+        embd = backend.Weight(ctx, t[0], t[1], t[2], t[3], t[4], t[5], t[6])
+        n_gen = 128 if args.steps == 500 else args.steps
+        gf.greedy_weight(embd, 11, 0, min(8, n_gen))  # warm the greedy graph
+        t0 = time.perf_counter()
+        toks = gf.greedy_weight(embd, 11, 0, n_gen)
+        dt = time.perf_counter() - t0
+        e, hd, g = p["n_embd"], p["head_dim"], p["group"]
+        qd, kvd, ne, k, mi = p["n_head"] * hd, p["n_kv_head"] * hd, p["n_experts"], p["n_experts_used"], p["moe_inter"]
+        mlx = lambda o, c: o * c // 2 + 2 * 2 * o * (c // g)  # packed words + bf16 scale and bias tables
+        layer = mlx(qd, e) + 2 * mlx(kvd, e) + mlx(e, qd) + mlx(ne, e) + k * (2 * mlx(mi, e) + mlx(e, mi))
+        nbytes = p["n_layer"] * layer + mlx(p["vocab"], e) + 2 * 2 * kvd * p["n_layer"] * (n_gen // 2)
+        out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, tokens=n_gen, layers=p["n_layer"], bytes_per_token=nbytes,
+                   gbs=nbytes * n_gen / dt / 1e9, first_tokens=toks[:8].tolist(),
+                   note="weights of one seeded layer repeated per layer (distinct device copies); greedy loop on the device")
     elif args.workload == "c3prefill":
         # time to first token on the Llama-3.2-1B shape: all prompt tokens in one batched pass
         # (tensor-core GEMMs on the quantized weights), against the same prompt token by token
@@ -698,6 +722,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=512, help="prefill length of the c4gemm workload")
+    ap.add_argument("--layers", type=int, default=0, help="c2decode: number of layers (default: the model's 48)")
     ap.add_argument("--only", default="", help="c4gemm: run just this matrix of the block (q, k, v, o, gate, up, down)")
     ap.add_argument("--pdl", type=int, default=1, help="launch the kernels with programmatic dependent launch (weight prefetch of the next kernel overlaps the tail of the previous one)")
     ap.add_argument("--no-cpu", action="store_true")
@@ -706,7 +731,7 @@ def main():
                          "two programmatically chained launches for this pair, so off by default")
     ap.add_argument("--multi-graph", action="store_true", help="N>1: capture kernels + NCCL in a CUDA graph (off by default)")
     ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c3prefill", "c4", "c4gemm"],
+    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c2decode", "c3", "c3prefill", "c4", "c4gemm"],
                     help="single-GPU only: c1 is the headline workload, the others are auxiliary measurements")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -257,17 +257,26 @@ typedef struct { /* GpuLayerInput, forward.rs:78-100 (dense fields) */
      * (Qwen2) and the per-head Q / K RMSNorm weights [head_dim] applied before RoPE (Qwen3; used when
      * params.qk_norm is set). */
     const float *q_bias, *k_bias, *v_bias, *q_norm, *k_norm;
+    /* Mixture-of-experts layer (GpuLayerInput::moe_gate / experts_gate / experts_up / experts_down,
+     * forward.rs:95-99): the router weight [n_experts, n_embd] and the stacked experts; `experts` NULL =
+     * dense layer.  On an MoE layer w_gate / w_up / w_down are not read. */
+    ullm_gpu_weight moe_gate;
+    const ullm_moe_experts_input *experts;
 } ullm_gpu_layer_input;
 typedef struct { /* GpuModelInput, forward.rs:105-110 */
     ullm_gpu_params params;
     ullm_gpu_weight output;
     const float *final_norm;
     const ullm_gpu_layer_input *layers; /* params.n_layer entries */
+    /* Element type of every `mlx_scales` / `mlx_biases` table above: ULLM_DTYPE_F32 (0, what the reference
+     * passes) or ULLM_DTYPE_BF16 for the bits as stored on disk, kept as such on the device.  The experts'
+     * tables carry their own `table_dtype`. */
+    int mlx_table_dtype;
 } ullm_gpu_model_input;
 
-/* GpuForward::new (forward.rs:230).  rope_neox, qk_norm and the q/k/v biases are built;
- * sandwich_norm, geglu, MoE layers and the sliding window return UNSUPPORTED instead of
- * being silently ignored. */
+/* GpuForward::new (forward.rs:230).  rope_neox, qk_norm, the q/k/v biases, MLX 4-bit matrices and
+ * mixture-of-experts layers (router matvec -> top-k -> routed experts, forward.rs:484-494) are built;
+ * sandwich_norm, geglu and the sliding window return UNSUPPORTED instead of being silently ignored. */
 int ullm_cuda_forward_create(ullm_cuda_ctx *ctx, const ullm_gpu_model_input *in, ullm_cuda_fwd **out);
 /* The same from an open GGUF file (include/ullm_gguf.h): hyperparameters and tensor
  * names as LlamaModel::from_gguf reads them (crates/ullm-model/src/lib.rs:174-301:
@@ -277,6 +286,13 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *ctx, const ullm_gpu_model_input *in,
  * bias, q/k-norm or sandwich-norm tensors are refused with UNSUPPORTED. */
 struct ullm_gguf;
 int ullm_cuda_forward_create_gguf(ullm_cuda_ctx *ctx, const struct ullm_gguf *g, int kv_f16, ullm_cuda_fwd **out);
+/* The same from an open MLX model directory (include/ullm_safetensors.h): hyperparameters and tensor
+ * names as LlamaModel::from_mlx reads them (crates/ullm-model/src/mlx.rs:103-232: config.json of a
+ * Qwen3MoeForCausalLM, lm_head, model.norm.weight, model.layers.N.{input_layernorm, self_attn.{q,k,v,o}_proj,
+ * self_attn.{q,k}_norm, post_attention_layernorm, mlp.gate, mlp.switch_mlp.{gate,up,down}_proj}), rotate-half
+ * RoPE and per-head Q/K norms on, then GpuForward::new as build_gpu calls it (lib.rs:712-805).  Packed words
+ * and bf16 tables go to the device as they lie in the mapped files. */
+int ullm_cuda_forward_create_st(ullm_cuda_ctx *ctx, const struct ullm_st *st, int kv_f16, ullm_cuda_fwd **out);
 void ullm_cuda_forward_destroy(ullm_cuda_fwd *f);
 /* GpuForward::forward (forward.rs:384): one token at `pos`, returns vocab logits. */
 int ullm_cuda_forward(ullm_cuda_fwd *f, const float *x_init, size_t pos, float *logits);
@@ -298,6 +314,12 @@ int ullm_cuda_forward_batch(ullm_cuda_fwd *f, const float *embeds, size_t s, flo
  * round trip.  tokens_out[n]. */
 int ullm_cuda_forward_greedy(ullm_cuda_fwd *f, const ullm_cuda_buf *embd_table, int embd_dtype, uint32_t first_token,
                              size_t pos, size_t n, uint32_t *tokens_out);
+/* The same with the embedding matrix given as a resident weight (ullm_cuda_weight_create / _create_st), which
+ * also covers MLX 4-bit tables (embedding row = dequant_mlx_row, crates/ullm-model/src/math.rs:68-79).  Q6_K
+ * weights whose rows were re-ordered for the matvec kernels are refused: upload those bytes with
+ * ullm_cuda_upload and use ullm_cuda_forward_greedy. */
+int ullm_cuda_forward_greedy_weight(ullm_cuda_fwd *f, const ullm_cuda_weight *embd_table, uint32_t first_token, size_t pos,
+                                    size_t n, uint32_t *tokens_out);
 
 #ifdef __cplusplus
 }

@@ -47,7 +47,8 @@ class MoeExperts(C.Structure):
 class Layer(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p)] + [
         (n, QWeight) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")
-    ] + [(n, C.c_void_p) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")]
+    ] + [(n, C.c_void_p) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")] + [
+        ("moe_gate", QWeight), ("experts", C.c_void_p), ("n_experts_used", C.c_size_t)]
 
 
 class Model(C.Structure):
@@ -267,7 +268,10 @@ class LlamaModel:
             self.keep += [an, fn]
             arr[i].attn_norm, arr[i].ffn_norm = an.ctypes.data, fn.ctypes.data
             for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down"):
-                setattr(arr[i], n, l[n].c)
+                if l.get(n) is not None:  # a mixture-of-experts layer has no dense FFN matrices
+                    setattr(arr[i], n, l[n].c)
+            if l.get("experts") is not None:  # router :class:`Weight`, :class:`Experts`, experts per token
+                arr[i].moe_gate, arr[i].experts, arr[i].n_experts_used = l["moe_gate"].c, C.addressof(l["experts"].c), l["n_experts_used"]
             for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm"):  # optional variants (lib.rs:877-901)
                 if l.get(n) is not None:
                     a = np.ascontiguousarray(l[n], np.float32)

@@ -375,7 +375,7 @@ void uo_forward_llama_embd(uo_model *m, const float *x_init, size_t pos, float *
     float *x = (float *)malloc(n_embd * 4), *xb = (float *)malloc(n_embd * 4);
     float *q = (float *)malloc(q_dim * 4), *k = (float *)malloc(kv_dim * 4), *v = (float *)malloc(kv_dim * 4);
     float *att = (float *)malloc(q_dim * 4), *proj = (float *)malloc(n_embd * 4);
-    float *gate = (float *)malloc(m->n_ff * 4), *up = (float *)malloc(m->n_ff * 4);
+    float *gate = (float *)malloc((m->n_ff + 1) * 4), *up = (float *)malloc((m->n_ff + 1) * 4);
     float *scores = (float *)malloc((pos + 1) * 4);
     memcpy(x, x_init, n_embd * 4);
     for (size_t l = 0; l < m->n_layer; l++) {
@@ -430,10 +430,17 @@ void uo_forward_llama_embd(uo_model *m, const float *x_init, size_t pos, float *
         uo_matvec_q(&lw->wo, att, proj);
         for (size_t i = 0; i < n_embd; i++) x[i] += proj[i];
         uo_rmsnorm(x, lw->ffn_norm, n_embd, m->eps, xb);
-        uo_matvec_q(&lw->w_gate, xb, gate);
-        uo_matvec_q(&lw->w_up, xb, up);
-        for (size_t i = 0; i < m->n_ff; i++) gate[i] = uo_silu(gate[i]) * up[i];
-        uo_matvec_q(&lw->w_down, gate, proj);
+        if (lw->experts) { /* lib.rs:953-955: router logits, then the routed experts (lib.rs:1453-1488) */
+            float *rl = (float *)malloc(lw->experts->n_experts * 4);
+            uo_matvec_q(&lw->moe_gate, xb, rl);
+            uo_moe_ffn(lw->experts, rl, lw->n_experts_used, xb, proj);
+            free(rl);
+        } else {
+            uo_matvec_q(&lw->w_gate, xb, gate);
+            uo_matvec_q(&lw->w_up, xb, up);
+            for (size_t i = 0; i < m->n_ff; i++) gate[i] = uo_silu(gate[i]) * up[i];
+            uo_matvec_q(&lw->w_down, gate, proj);
+        }
         for (size_t i = 0; i < n_embd; i++) x[i] += proj[i];
     }
     uo_rmsnorm(x, m->final_norm, n_embd, m->eps, xb);

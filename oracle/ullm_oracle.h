@@ -113,6 +113,11 @@ typedef struct {
     /* optional (NULL = absent): Qwen2 projection biases (lib.rs:877-885) and the per-head
      * Q/K RMSNorm weights [head_dim] applied before RoPE (lib.rs:887-901) */
     const float *q_bias, *k_bias, *v_bias, *q_norm, *k_norm;
+    /* mixture-of-experts layer (lib.rs:953-955, 1453-1488): router weight [n_experts, n_embd], stacked
+     * experts and experts per token; experts == NULL = dense layer (w_gate / w_up / w_down used) */
+    uo_qweight moe_gate;
+    const uo_moe_experts *experts;
+    size_t n_experts_used;
 } uo_layer;
 typedef struct {
     size_t n_embd, n_layer, n_head, n_kv_head, head_dim, n_ff, n_ctx, vocab;

@@ -88,12 +88,14 @@ SIGNATURES = {
     "ullm_cuda_moe_ffn_noalloc": (_i, [_i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, C.c_char_p, _sz]),
     "ullm_cuda_forward_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "ullm_cuda_forward_create_gguf": (_i, [_vp, _vp, _i, C.POINTER(_vp)]),
+    "ullm_cuda_forward_create_st": (_i, [_vp, _vp, _i, C.POINTER(_vp)]),
     "ullm_cuda_forward_batch": (_i, [_vp, _vp, _sz, _vp]),
     "ullm_cuda_forward_destroy": (None, [_vp]),
     "ullm_cuda_forward": (_i, [_vp, _vp, _sz, _vp]),
     "ullm_cuda_forward_set_kv": (_i, [_vp, _sz, _sz, _vp, _vp]),
     "ullm_cuda_forward_supports_batched_prefill": (_i, [_vp]),
     "ullm_cuda_forward_greedy": (_i, [_vp, _vp, _i, C.c_uint32, _sz, _sz, _vp]),
+    "ullm_cuda_forward_greedy_weight": (_i, [_vp, _vp, C.c_uint32, _sz, _sz, _vp]),
 }
 # Test / tuning knobs outside the mirrored surface.
 DEBUG_SIGNATURES = {
@@ -475,11 +477,11 @@ class GpuParams(C.Structure):
 
 class GpuLayerInput(C.Structure):
     _fields_ = [("attn_norm", _vp), ("ffn_norm", _vp)] + [(n, GpuWeight) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")] + [
-        (n, _vp) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")]
+        (n, _vp) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")] + [("moe_gate", GpuWeight), ("experts", _vp)]
 
 
 class GpuModelInput(C.Structure):
-    _fields_ = [("params", GpuParams), ("output", GpuWeight), ("final_norm", _vp), ("layers", _vp)]
+    _fields_ = [("params", GpuParams), ("output", GpuWeight), ("final_norm", _vp), ("layers", _vp), ("mlx_table_dtype", _i)]
 
 
 class GpuForward:
@@ -494,10 +496,23 @@ class GpuForward:
         self.params = dict(p)
         keep = []
 
+        tdt = [F32]  # element type of the MLX tables: bf16 bits when the arrays are uint16
+
+        def table(a):
+            if np.asarray(a).dtype == np.uint16:
+                tdt[0] = BF16
+                a = np.ascontiguousarray(a, np.uint16)
+            else:
+                a = _f32(a)
+            keep.append(a)
+            return a.ctypes.data
+
         def gw(t):
-            dtype, data, out, cols = t
+            dtype, data, out, cols = t[:4]
             b = _bytes(data)
             keep.append(b)
+            if len(t) > 4:  # MLX 4-bit: (MLX_U32, words, out, cols, scales, biases, group)
+                return GpuWeight(dtype, b.ctypes.data, b.size, out, cols, table(t[4]), table(t[5]), t[6])
             return GpuWeight(dtype, b.ctypes.data, b.size, out, cols, None, None, 0)
 
         def f32p(a):
@@ -509,15 +524,32 @@ class GpuForward:
         for i, l in enumerate(model["layers"]):
             layers[i].attn_norm, layers[i].ffn_norm = f32p(l["attn_norm"]), f32p(l["ffn_norm"])
             for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down"):
-                setattr(layers[i], n, gw(l[n]))
+                if l.get(n) is not None:
+                    setattr(layers[i], n, gw(l[n]))
             for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm"):
                 if l.get(n) is not None:
                     setattr(layers[i], n, f32p(l[n]))
+            if l.get("experts") is not None:  # MoE layer: router weight + stacked experts (gate, up, down) = (words, scales, biases)
+                x = l["experts"]
+                ptrs = []
+                for w, s_, b_ in (x["gate"], x["up"], x["down"]):
+                    bf = np.asarray(s_).dtype == np.uint16
+                    arrs = [np.ascontiguousarray(w, np.uint32), np.ascontiguousarray(s_, np.uint16 if bf else np.float32),
+                            np.ascontiguousarray(b_, np.uint16 if bf else np.float32)]
+                    keep.extend(arrs)
+                    ptrs += [a.ctypes.data for a in arrs]
+                xi = MoeExpertsInput(*ptrs, BF16 if bf else F32, x["n_experts"], x["hidden"], x["inter"], x["group"])
+                keep.append(xi)
+                layers[i].moe_gate, layers[i].experts = gw(l["moe_gate"]), C.addressof(xi)
+        for n in ("n_experts", "n_experts_used", "moe_inter"):
+            if p.get(n):
+                flags.setdefault(n, p[n])
         gp = GpuParams(p["n_embd"], p["n_layer"], p["n_head"], p["n_kv_head"], p["head_dim"], p["n_ff"], p["n_ctx"], p["vocab"],
                        p["rope_theta"], p["eps"], flags.get("rope_neox", 0), flags.get("qk_norm", 0), flags.get("sandwich_norm", 0),
                        flags.get("geglu", 0), flags.get("n_experts", 0), flags.get("n_experts_used", 0), flags.get("moe_inter", 0),
                        flags.get("sliding_window", 0), 1 if kv_f16 else 0)
-        inp = GpuModelInput(gp, gw(model["output"]), f32p(model["final_norm"]), C.addressof(layers))
+        out_w, fin = gw(model["output"]), f32p(model["final_norm"])
+        inp = GpuModelInput(gp, out_w, fin, C.addressof(layers), tdt[0])
         h = _vp()
         ctx._check(ctx._lib.ullm_cuda_forward_create(ctx._h, C.byref(inp), C.byref(h)))
         self._h = h.value
@@ -534,6 +566,20 @@ class GpuForward:
         ctx._check(ctx._lib.ullm_cuda_forward_create_gguf(ctx._h, gguf._h, 1 if kv_f16 else 0, C.byref(h)))
         self._h = h.value
         self._logits = np.empty(lp["vocab"], np.float32)
+        return self
+
+    @classmethod
+    def from_safetensors(cls, ctx: CudaContext, st, kv_f16: bool = False) -> "GpuForward":
+        """Builds the engine from an open MLX model directory (:class:`ullm_b200.safetensors.SafeTensors`,
+        ``ullm_cuda_forward_create_st``)."""
+        self = cls.__new__(cls)
+        self._ctx = ctx
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_forward_create_st(ctx._h, st._h, 1 if kv_f16 else 0, C.byref(h)))
+        mp = st.mlx_params()
+        self.params = dict(mp)
+        self._h = h.value
+        self._logits = np.empty(mp["vocab"], np.float32)
         return self
 
     def forward(self, x_init, pos: int) -> np.ndarray:
@@ -563,6 +609,12 @@ class GpuForward:
         """``n`` greedy tokens kept on the device: argmax feeds the next embedding lookup."""
         out = np.empty(n, np.uint32)
         self._ctx._check(self._ctx._lib.ullm_cuda_forward_greedy(self._h, embd._h, embd_dtype, first_token, pos, n, _ptr(out)))
+        return out
+
+    def greedy_weight(self, embd: "Weight", first_token: int, pos: int, n: int) -> np.ndarray:
+        """The same with the embedding matrix as a resident :class:`Weight` (MLX 4-bit tables included)."""
+        out = np.empty(n, np.uint32)
+        self._ctx._check(self._ctx._lib.ullm_cuda_forward_greedy_weight(self._h, embd._h, first_token, pos, n, _ptr(out)))
         return out
 
     def free(self):

@@ -807,25 +807,37 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, u
     // Flags no benchmark configuration uses are refused, not ignored.
     if (gp.sandwich_norm) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "sandwich norms are not built");
     if (gp.geglu) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "GeGLU is not built");
-    if (gp.n_experts || gp.n_experts_used || gp.moe_inter) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MoE layers inside the decode step are not built");
     if (gp.sliding_window) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "sliding-window attention is not built");
+    if (in->mlx_table_dtype != ULLM_DTYPE_F32 && in->mlx_table_dtype != ULLM_DTYPE_BF16)
+        return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MLX tables must be f32 or bf16");
     ForwardParams P;
     P.n_embd = gp.n_embd, P.n_layer = gp.n_layer, P.n_head = gp.n_head, P.n_kv_head = gp.n_kv_head, P.head_dim = gp.head_dim;
     P.n_ff = gp.n_ff, P.n_ctx = gp.n_ctx, P.vocab = gp.vocab, P.rope_theta = gp.rope_theta, P.eps = gp.eps, P.kv_f16 = gp.kv_f16;
     P.rope_neox = gp.rope_neox != 0, P.qk_norm = gp.qk_norm != 0;
+    P.n_experts = gp.n_experts, P.n_experts_used = gp.n_experts_used, P.moe_inter = gp.moe_inter;
     if (const char *m = Forward::check_params(P)) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s", m);
     const size_t qd = P.n_head * P.head_dim, kvd = P.n_kv_head * P.head_dim;
     auto conv = [&](const ullm_gpu_weight &w, size_t out_dim, size_t cols, HostWeight *hw, const char *name) -> int {
-        if (w.mlx_scales || w.mlx_biases) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s: MLX weights inside the decode step are not built", name);
+        if (!w.bytes || w.out != out_dim || w.cols != cols) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: expected shape [%zu, %zu]", name, out_dim, cols);
+        hw->dtype = w.dtype, hw->bytes = w.bytes, hw->out = out_dim, hw->cols = cols;
+        if (w.dtype == ULLM_DTYPE_MLX_U32) { // GpuWeight with mlx_scales / mlx_biases / mlx_group (forward.rs:56-64)
+            if (!w.mlx_scales || !w.mlx_biases) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: MLX weights need scale and bias tables", name);
+            if (const char *m = matvec_shape_error(FMT_MLX4, out_dim, cols, w.mlx_group)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: %s", name, m);
+            if (w.len < out_dim * cols / 2) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: need %zu bytes, have %zu", name, out_dim * cols / 2, w.len);
+            hw->scales = w.mlx_scales, hw->biases = w.mlx_biases, hw->group = w.mlx_group;
+            return ULLM_OK;
+        }
+        if (w.mlx_scales || w.mlx_biases) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: MLX tables on a weight of dtype %d", name, w.dtype);
         if (w.dtype != ULLM_DTYPE_Q4_K && w.dtype != ULLM_DTYPE_Q6_K)
             return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s: no CUDA forward kernel for dtype %d", name, w.dtype); // forward.rs:376-378
-        if (!w.bytes || w.out != out_dim || w.cols != cols) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: expected shape [%zu, %zu]", name, out_dim, cols);
+        if (cols % QK_K) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: in_dim is not a multiple of the 256-element super-block", name);
         const size_t need = out_dim * (cols / QK_K) * (w.dtype == ULLM_DTYPE_Q4_K ? Q4K_BYTES : Q6K_BYTES);
         if (w.len < need) return ctx_fail(c, ULLM_ERR_FORMAT, "%s: need %zu bytes, have %zu", name, need, w.len);
-        hw->dtype = w.dtype, hw->bytes = w.bytes, hw->out = out_dim, hw->cols = cols;
         return ULLM_OK;
     };
     HostModel hm;
+    hm.mlx_table_bytes = in->mlx_table_dtype == ULLM_DTYPE_BF16 ? 2 : 4;
+    std::vector<MoeExperts> experts(P.n_layer); // host-pointer descriptions, alive until init() has copied them
     int rc;
     if ((rc = conv(in->output, P.vocab, P.n_embd, &hm.output, "output"))) return rc;
     hm.final_norm = in->final_norm;
@@ -843,11 +855,34 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, u
             return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: q_norm / k_norm given but params.qk_norm is not set", l);
         }
         if ((rc = conv(li.wq, qd, P.n_embd, &hl.wq, "wq")) || (rc = conv(li.wk, kvd, P.n_embd, &hl.wk, "wk")) ||
-            (rc = conv(li.wv, kvd, P.n_embd, &hl.wv, "wv")) || (rc = conv(li.wo, P.n_embd, qd, &hl.wo, "wo")) ||
-            (rc = conv(li.w_gate, P.n_ff, P.n_embd, &hl.w_gate, "w_gate")) ||
+            (rc = conv(li.wv, kvd, P.n_embd, &hl.wv, "wv")) || (rc = conv(li.wo, P.n_embd, qd, &hl.wo, "wo")))
+            return rc;
+        if (li.experts) {
+            const ullm_moe_experts_input &xi = *li.experts;
+            if (!P.n_experts) return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: experts given but params.n_experts is 0", l);
+            if (xi.n_experts != P.n_experts || xi.hidden != P.n_embd || xi.inter != P.moe_inter)
+                return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: experts are not %zu x [%zu, %zu]", l, P.n_experts, P.moe_inter, P.n_embd);
+            if (xi.table_dtype != ULLM_DTYPE_F32 && xi.table_dtype != ULLM_DTYPE_BF16) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "MLX tables must be f32 or bf16");
+            const void *ptrs[9] = {xi.gate_w, xi.gate_scales, xi.gate_biases, xi.up_w, xi.up_scales, xi.up_biases, xi.down_w, xi.down_scales, xi.down_biases};
+            for (auto q : ptrs)
+                if (!q) return ULLM_ERR_INVALID;
+            MoeExperts &e = experts[l];
+            e.gate_w = xi.gate_w, e.gate_s = xi.gate_scales, e.gate_b = xi.gate_biases, e.up_w = xi.up_w, e.up_s = xi.up_scales, e.up_b = xi.up_biases;
+            e.down_w = xi.down_w, e.down_s = xi.down_scales, e.down_b = xi.down_biases;
+            e.table_bytes = xi.table_dtype == ULLM_DTYPE_F32 ? 4 : 2;
+            e.n_experts = xi.n_experts, e.hidden = xi.hidden, e.inter = xi.inter, e.group = xi.group;
+            if (const char *m = moe_shape_error(e, 1, P.n_experts_used)) return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: %s", l, m);
+            if ((rc = conv(li.moe_gate, P.n_experts, P.n_embd, &hl.moe_gate, "moe_gate"))) return rc;
+            hl.experts = &e;
+            continue;
+        }
+        if (!P.n_ff) return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: neither experts nor a dense FFN (n_ff is 0)", l);
+        if ((rc = conv(li.w_gate, P.n_ff, P.n_embd, &hl.w_gate, "w_gate")) ||
             (rc = conv(li.w_up, P.n_ff, P.n_embd, &hl.w_up, "w_up")) ||
             (rc = conv(li.w_down, P.n_embd, P.n_ff, &hl.w_down, "w_down")))
             return rc;
+        if (hl.w_gate.dtype == ULLM_DTYPE_MLX_U32 || hl.w_up.dtype == ULLM_DTYPE_MLX_U32 || hl.w_down.dtype == ULLM_DTYPE_MLX_U32)
+            return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "layer %zu: a dense FFN of MLX 4-bit matrices is not built", l);
     }
     ullm_cuda_fwd *f = new (std::nothrow) ullm_cuda_fwd();
     if (!f) return ULLM_ERR_OOM;
@@ -861,6 +896,79 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *c, const ullm_gpu_model_input *in, u
     }
     *out = f;
     return ULLM_OK;
+}
+
+int ullm_cuda_forward_create_st(ullm_cuda_ctx *c, const ullm_st *st, int kv_f16, ullm_cuda_fwd **out) {
+    if (!c || !st || !out) return ULLM_ERR_INVALID;
+    *out = nullptr;
+    char msg[256] = {0};
+    ullm_st_mlx_params mp;
+    int rc = ullm_st_mlx_params_get(st, &mp, msg, sizeof msg);
+    if (rc == ULLM_ST_ERR_UNSUPPORTED) return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "%s", msg);
+    if (rc) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", msg);
+    const size_t qd = mp.n_head * mp.head_dim, kvd = mp.n_kv_head * mp.head_dim, gs = (size_t)mp.group;
+    // read_bf16 (mlx.rs:14-24): a bf16 vector widened to f32
+    std::vector<std::vector<float>> norms;
+    norms.reserve(4 * mp.n_layer + 1);
+    auto norm = [&](const std::string &name, size_t n, const float **dst) -> int {
+        ullm_st_tensor t;
+        if (ullm_st_tensor_find(st, name.c_str(), &t)) return ctx_fail(c, ULLM_ERR_FORMAT, "missing tensor '%s'", name.c_str());
+        if (t.dtype != ULLM_DTYPE_BF16 || !t.data || t.nbytes != n * 2)
+            return ctx_fail(c, ULLM_ERR_FORMAT, "tensor '%s' is not %zu bf16 values", name.c_str(), n);
+        norms.emplace_back(n);
+        for (size_t i = 0; i < n; ++i) {
+            const uint32_t b = (uint32_t)((const uint16_t *)t.data)[i] << 16;
+            memcpy(&norms.back()[i], &b, 4);
+        }
+        *dst = norms.back().data();
+        return ULLM_OK;
+    };
+    auto weight = [&](const std::string &name, size_t out_dim, size_t cols, ullm_gpu_weight *w) -> int {
+        ullm_st_mlx_weight mw;
+        if (ullm_st_mlx_weight_get(st, name.c_str(), gs, &mw, msg, sizeof msg)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", msg);
+        if (mw.out != out_dim || mw.in != cols) return ctx_fail(c, ULLM_ERR_FORMAT, "'%s' is not [%zu, %zu]", name.c_str(), out_dim, cols);
+        memset(w, 0, sizeof *w);
+        w->dtype = ULLM_DTYPE_MLX_U32, w->bytes = mw.weight, w->len = out_dim * cols / 2, w->out = out_dim, w->cols = cols;
+        w->mlx_scales = (const float *)mw.scales, w->mlx_biases = (const float *)mw.biases, w->mlx_group = gs; // bf16 bits: mlx_table_dtype below
+        return ULLM_OK;
+    };
+    std::vector<ullm_gpu_layer_input> layers(mp.n_layer);
+    std::vector<ullm_moe_experts_input> experts(mp.n_layer);
+    for (size_t i = 0; i < mp.n_layer; ++i) {
+        const std::string p = "model.layers." + std::to_string(i);
+        ullm_gpu_layer_input &l = layers[i];
+        memset(&l, 0, sizeof l);
+        if ((rc = norm(p + ".input_layernorm.weight", mp.n_embd, &l.attn_norm)) ||
+            (rc = norm(p + ".post_attention_layernorm.weight", mp.n_embd, &l.ffn_norm)) ||
+            (rc = norm(p + ".self_attn.q_norm.weight", mp.head_dim, &l.q_norm)) || (rc = norm(p + ".self_attn.k_norm.weight", mp.head_dim, &l.k_norm)) ||
+            (rc = weight(p + ".self_attn.q_proj", qd, mp.n_embd, &l.wq)) || (rc = weight(p + ".self_attn.k_proj", kvd, mp.n_embd, &l.wk)) ||
+            (rc = weight(p + ".self_attn.v_proj", kvd, mp.n_embd, &l.wv)) || (rc = weight(p + ".self_attn.o_proj", mp.n_embd, qd, &l.wo)) ||
+            (rc = weight(p + ".mlp.gate", mp.n_experts, mp.n_embd, &l.moe_gate)))
+            return rc;
+        ullm_moe_experts_input &x = experts[i];
+        memset(&x, 0, sizeof x);
+        ullm_st_mlx_weight g, u, d;
+        const std::string sw = p + ".mlp.switch_mlp";
+        if (ullm_st_mlx_experts_get(st, (sw + ".gate_proj").c_str(), mp.n_experts, mp.moe_inter, mp.n_embd, gs, mp.n_experts, &g, msg, sizeof msg) ||
+            ullm_st_mlx_experts_get(st, (sw + ".up_proj").c_str(), mp.n_experts, mp.moe_inter, mp.n_embd, gs, mp.n_experts, &u, msg, sizeof msg) ||
+            ullm_st_mlx_experts_get(st, (sw + ".down_proj").c_str(), mp.n_experts, mp.n_embd, mp.moe_inter, gs, mp.n_experts, &d, msg, sizeof msg))
+            return ctx_fail(c, ULLM_ERR_FORMAT, "%s", msg);
+        x.gate_w = g.weight, x.gate_scales = g.scales, x.gate_biases = g.biases, x.up_w = u.weight, x.up_scales = u.scales, x.up_biases = u.biases;
+        x.down_w = d.weight, x.down_scales = d.scales, x.down_biases = d.biases;
+        x.table_dtype = ULLM_DTYPE_BF16, x.n_experts = mp.n_experts, x.hidden = mp.n_embd, x.inter = mp.moe_inter, x.group = gs;
+        l.experts = &x;
+    }
+    ullm_gpu_model_input in;
+    memset(&in, 0, sizeof in);
+    ullm_gpu_params &gp = in.params;
+    gp.n_embd = mp.n_embd, gp.n_layer = mp.n_layer, gp.n_head = mp.n_head, gp.n_kv_head = mp.n_kv_head, gp.head_dim = mp.head_dim;
+    gp.n_ff = 0, gp.n_ctx = mp.n_ctx, gp.vocab = mp.vocab, gp.rope_theta = mp.rope_theta, gp.eps = mp.eps, gp.kv_f16 = kv_f16 ? 1 : 0;
+    gp.rope_neox = 1, gp.qk_norm = 1; // mlx.rs:228, :197-198
+    gp.n_experts = mp.n_experts, gp.n_experts_used = mp.n_experts_used, gp.moe_inter = mp.moe_inter;
+    if ((rc = norm("model.norm.weight", mp.n_embd, &in.final_norm)) || (rc = weight("lm_head", mp.vocab, mp.n_embd, &in.output))) return rc;
+    in.layers = layers.data();
+    in.mlx_table_dtype = ULLM_DTYPE_BF16;
+    return ullm_cuda_forward_create(c, &in, out);
 }
 
 void ullm_cuda_forward_destroy(ullm_cuda_fwd *f) { delete f; }
@@ -909,6 +1017,21 @@ int ullm_cuda_forward_greedy(ullm_cuda_fwd *f, const ullm_cuda_buf *embd, int em
     if (first_token >= f->f.P.vocab) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "token id outside the vocabulary");
     if (pos + n > f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "positions beyond the context");
     cudaError_t e = f->f.greedy(embd->ptr, embd_dtype, first_token, pos, n, tokens_out);
+    if (e == cudaErrorNotSupported) return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "a layer shape is outside the fused decode path");
+    if (e != cudaSuccess) return fwd_fail(f, e, "greedy decode");
+    return fwd_status(f);
+}
+
+int ullm_cuda_forward_greedy_weight(ullm_cuda_fwd *f, const ullm_cuda_weight *embd, uint32_t first_token, size_t pos, size_t n,
+                                    uint32_t *tokens_out) {
+    if (!f || !embd || (n && !tokens_out)) return ULLM_ERR_INVALID;
+    if (embd->fmt != FMT_Q4K && embd->fmt != FMT_Q6K && embd->fmt != FMT_MLX4)
+        return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "embedding table: rows re-ordered for the matvec kernels have no device lookup");
+    if (embd->out < f->f.P.vocab || embd->cols != f->f.P.n_embd) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "embedding table is not [vocab, n_embd]");
+    if (first_token >= f->f.P.vocab) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "token id outside the vocabulary");
+    if (pos + n > f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "positions beyond the context");
+    f->f.embd_mlx.scales = embd->scales, f->f.embd_mlx.biases = embd->biases, f->f.embd_mlx.elem_bytes = embd->table_bytes, f->f.embd_mlx.group = embd->group;
+    cudaError_t e = f->f.greedy(embd->w, embd->dtype, first_token, pos, n, tokens_out);
     if (e == cudaErrorNotSupported) return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "a layer shape is outside the fused decode path");
     if (e != cudaSuccess) return fwd_fail(f, e, "greedy decode");
     return fwd_status(f);

@@ -341,7 +341,30 @@ __global__ void kv_fill_kernel(const float *__restrict__ src, void *dst, size_t 
 // ---------------------------------------------------------------------------
 // Engine
 // ---------------------------------------------------------------------------
-static int fmt_of_dtype(int dtype) { return dtype == 12 ? FMT_Q4K : (dtype == 14 ? FMT_Q6K : -1); }
+static int fmt_of_dtype(int dtype) { return dtype == 12 ? FMT_Q4K : (dtype == 14 ? FMT_Q6K : (dtype == 1000 ? FMT_MLX4 : -1)); }
+
+// x * (1 / sqrt(mean(x^2) + eps)) * w (math.rs:82-86) and a + b for one vector: the steps around a
+// mixture-of-experts FFN, whose kernels take the normalised vector from memory, and the unfused
+// fallback of Forward::mv
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps, int n,
+                                                         float *__restrict__ y) {
+    __shared__ float red[8];
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) ss += x[i] * x[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += 256) y[i] = x[i] * inv * w[i];
+}
+__global__ void add_vec_kernel(const float *__restrict__ a, const float *__restrict__ b, int n, float *__restrict__ y) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = a[i] + b[i];
+}
 static size_t qbytes(int fmt, size_t out, size_t cols) {
     return out * (cols / QK_K) * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
 }
@@ -374,8 +397,9 @@ static cudaError_t launch_attn(const AttnParams &p, int hd, int kvmul, int n_kv_
 }
 
 const char *Forward::check_params(const ForwardParams &p) {
-    if (!p.n_embd || !p.n_layer || !p.n_head || !p.n_kv_head || !p.head_dim || !p.n_ff || !p.n_ctx || !p.vocab)
+    if (!p.n_embd || !p.n_layer || !p.n_head || !p.n_kv_head || !p.head_dim || (!p.n_ff && !p.n_experts) || !p.n_ctx || !p.vocab)
         return "zero hyperparameter";
+    if (p.n_experts && (!p.n_experts_used || !p.moe_inter || p.n_experts_used > p.n_experts)) return "mixture-of-experts sizes";
     if (p.n_head % p.n_kv_head) return "n_head is not a multiple of n_kv_head";
     if (p.n_ctx > 8192) return "context longer than 8192 positions"; // the reference caps it there too (lib.rs:236)
     const size_t kvmul = p.n_head / p.n_kv_head;
@@ -449,11 +473,56 @@ cudaError_t Forward::upload_pair(const HostWeight &a, const HostWeight &b, bool 
 }
 
 cudaError_t Forward::upload_one(const HostWeight &a, Mat *out) {
-    return upload_rows(a.bytes, fmt_of_dtype(a.dtype), a.out, a.cols, out);
+    const int fmt = fmt_of_dtype(a.dtype);
+    if (fmt != FMT_MLX4) return upload_rows(a.bytes, fmt, a.out, a.cols, out);
+    // MLX 4-bit: packed words as they are, tables in the element type given (f32, or the bf16 bits of the file)
+    out->fmt = fmt, out->out = a.out, out->cols = a.cols, out->group = a.group, out->tbl_bytes = mlx_table_bytes;
+    const size_t tb = a.out * (a.cols / a.group) * (size_t)mlx_table_bytes;
+    cudaError_t e = upload(a.bytes, a.out * a.cols / 2, &out->w);
+    if (e == cudaSuccess) e = upload(a.scales, tb, &out->scales);
+    if (e == cudaSuccess) e = upload(a.biases, tb, &out->biases);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    return e;
+}
+
+// MLX matrices with the same row length and group size stacked row-wise: words after words, tables after tables.
+cudaError_t Forward::upload_mlx_stack(const HostWeight *const *ws, int n, Mat *out) {
+    const size_t cols = ws[0]->cols, group = ws[0]->group, tb = (size_t)mlx_table_bytes;
+    size_t rows = 0;
+    for (int i = 0; i < n; ++i) rows += ws[i]->out;
+    std::vector<uint8_t> w(rows * cols / 2), sc(rows * (cols / group) * tb), bi(sc.size());
+    size_t r = 0;
+    for (int i = 0; i < n; ++i) {
+        memcpy(w.data() + r * cols / 2, ws[i]->bytes, ws[i]->out * cols / 2);
+        memcpy(sc.data() + r * (cols / group) * tb, ws[i]->scales, ws[i]->out * (cols / group) * tb);
+        memcpy(bi.data() + r * (cols / group) * tb, ws[i]->biases, ws[i]->out * (cols / group) * tb);
+        r += ws[i]->out;
+    }
+    HostWeight h = *ws[0];
+    h.bytes = w.data(), h.scales = sc.data(), h.biases = bi.data(), h.out = rows;
+    return upload_one(h, out); // synchronises: the vectors may go
+}
+
+// Stacked experts of one layer: nine arrays made resident, the description re-pointed at them.
+cudaError_t Forward::upload_experts(const MoeExperts &h, MoeExperts *out) {
+    *out = h;
+    const size_t wb = h.n_experts * h.inter * h.hidden / 2;
+    const size_t tg = h.n_experts * h.inter * (h.hidden / h.group) * (size_t)h.table_bytes;
+    const size_t td = h.n_experts * h.hidden * (h.inter / h.group) * (size_t)h.table_bytes;
+    const void *src[9] = {h.gate_w, h.gate_s, h.gate_b, h.up_w, h.up_s, h.up_b, h.down_w, h.down_s, h.down_b};
+    const void **dst[9] = {&out->gate_w, &out->gate_s, &out->gate_b, &out->up_w, &out->up_s, &out->up_b, &out->down_w, &out->down_s, &out->down_b};
+    const size_t len[9] = {wb, tg, tg, wb, tg, tg, wb, td, td};
+    for (int i = 0; i < 9; ++i) {
+        void *d = nullptr;
+        cudaError_t e = upload(src[i], len[i], &d);
+        if (e != cudaSuccess) return e;
+        *dst[i] = d;
+    }
+    return cudaStreamSynchronize(stream);
 }
 
 cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardParams &params, const HostModel &m) {
-    dev = devinfo, device = device_, P = params;
+    dev = devinfo, device = device_, P = params, mlx_table_bytes = m.mlx_table_bytes;
     if (const char *v = getenv("ULLM_DECODE_CHAIN")) use_chain = atoi(v) != 0; // comparison knob
     cudaError_t e;
 #define TRY(x) \
@@ -475,18 +544,30 @@ cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardP
             if (h.q_norm) TRY(upload(h.q_norm, P.head_dim * 4, (void **)&L.q_norm));
             if (h.k_norm) TRY(upload(h.k_norm, P.head_dim * 4, (void **)&L.k_norm));
         }
-        L.qk_fused = h.wq.dtype == h.wk.dtype;
-        if (L.qk_fused) {
+        const bool mlx = fmt_of_dtype(h.wq.dtype) == FMT_MLX4; // no stacked q|k for MLX matrices (tables would need stacking too)
+        L.qk_fused = h.wq.dtype == h.wk.dtype && !mlx;
+        L.qkv_fused = mlx && fmt_of_dtype(h.wk.dtype) == FMT_MLX4 && fmt_of_dtype(h.wv.dtype) == FMT_MLX4 && h.wq.group == h.wk.group &&
+                      h.wq.group == h.wv.group;
+        if (L.qkv_fused) {
+            const HostWeight *ws[3] = {&h.wq, &h.wk, &h.wv};
+            TRY(upload_mlx_stack(ws, 3, &L.wqk));
+        } else if (L.qk_fused) {
             TRY(upload_pair(h.wq, h.wk, false, &L.wqk));
         } else {
             TRY(upload_one(h.wq, &L.wq));
             TRY(upload_one(h.wk, &L.wk));
         }
-        TRY(upload_one(h.wv, &L.wv));
+        if (!L.qkv_fused) TRY(upload_one(h.wv, &L.wv));
         TRY(upload_one(h.wo, &L.wo));
+        if (h.experts) {
+            L.moe = true;
+            TRY(upload_one(h.moe_gate, &L.moe_gate));
+            TRY(upload_experts(*h.experts, &L.experts));
+            continue;
+        }
         int gfmt = fmt_of_dtype(h.w_gate.dtype);
         if (gfmt == FMT_Q6K && q6k_can_prepare(P.n_embd)) gfmt = FMT_Q6KR;
-        L.gu_fused = h.w_gate.dtype == h.w_up.dtype && matvec_is_streamed(dev, gfmt, 2 * P.n_ff, P.n_embd, 0, 4, EPI_SWIGLU);
+        L.gu_fused = h.w_gate.dtype == h.w_up.dtype && gfmt != FMT_MLX4 && matvec_is_streamed(dev, gfmt, 2 * P.n_ff, P.n_embd, 0, 4, EPI_SWIGLU);
         if (L.gu_fused) {
             TRY(upload_pair(h.w_gate, h.w_up, true, &L.wgu));
         } else {
@@ -518,12 +599,22 @@ cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardP
     n_split = (int)((P.n_ctx + ATT_CHUNK - 1) / ATT_CHUNK);
     TRY(dev_alloc((void **)&x, P.n_embd * 4));
     TRY(dev_alloc((void **)&xb, P.n_embd * 4));
-    TRY(dev_alloc((void **)&qk, (qd + kvd) * 4));
+    TRY(dev_alloc((void **)&qk, (qd + 2 * kvd) * 4)); // q | k (| v when the three projections are one stacked matrix)
     TRY(dev_alloc((void **)&vbuf, kvd * 4));
     TRY(dev_alloc((void **)&attn, qd * 4));
     TRY(dev_alloc((void **)&hidden, P.n_ff * 4));
     TRY(dev_alloc((void **)&gate, P.n_ff * 4));
     TRY(dev_alloc((void **)&up, P.n_ff * 4));
+    TRY(dev_alloc((void **)&tmpn, std::max(std::max(P.n_embd, qd), P.n_ff) * 4));
+    TRY(dev_alloc((void **)&tmpo, std::max(P.n_embd, P.n_ff) * 4));
+    if (P.n_experts) {
+        size_t sb = 0;
+        for (const Layer &L : layers)
+            if (L.moe) sb = std::max(sb, moe_scratch_bytes(L.experts));
+        TRY(dev_alloc((void **)&moe_logits, P.n_experts * 4));
+        TRY(dev_alloc((void **)&moe_out, P.n_embd * 4));
+        TRY(dev_alloc(&moe_scratch, sb));
+    }
     TRY(dev_alloc((void **)&logits, P.vocab * 4));
     TRY(dev_alloc((void **)&partial, P.n_kv_head * n_split * (P.n_head / P.n_kv_head) * (hd + 2) * 4));
     TRY(dev_alloc((void **)&counters, P.n_kv_head * 4));
@@ -547,9 +638,25 @@ cudaError_t Forward::mv(const Mat &m, const float *in, float *out, const float *
     MatvecOpts o;
     o.pdl = use_pdl, o.norm_w = norm_w, o.eps = P.eps, o.epi = epi, o.res = res;
     MlxTables tb;
+    tb.scales = m.scales, tb.biases = m.biases, tb.elem_bytes = m.tbl_bytes, tb.group = m.group;
     cudaError_t e = launch_matvec(dev, m.fmt, m.w, tb, in, out, m.out, m.cols, d_status, stream, o);
     ++launches;
-    return e;
+    if (e != cudaErrorNotSupported || epi == EPI_SWIGLU) return e;
+    // A shape the streamed kernel does not take has no fused prologue / epilogue: normalise into
+    // memory first, add the residual afterwards.
+    --launches;
+    if (norm_w) {
+        rmsnorm_vec_kernel<<<1, 256, 0, stream>>>(in, norm_w, P.eps, (int)m.cols, tmpn);
+        in = tmpn, ++launches;
+    }
+    MatvecOpts plain;
+    e = launch_matvec(dev, m.fmt, m.w, tb, in, epi == EPI_RESIDUAL ? tmpo : out, m.out, m.cols, d_status, stream, plain);
+    ++launches;
+    if (e == cudaSuccess && epi == EPI_RESIDUAL) {
+        add_vec_kernel<<<(unsigned)((m.out + 255) / 256), 256, 0, stream>>>(res, tmpo, (int)m.out, out);
+        ++launches;
+    }
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // Enqueues one token step on `stream`.  mode 0: x already holds the embedding,
@@ -565,7 +672,11 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
     int *step_ptr = (int *)state + 2;
     launches = 0;
     if (mode == 1) {
-        TRY(launch_dequant_row(embd_dtype, embd_table, tok_ptr, P.n_embd, x, stream));
+        if (embd_dtype == 1000) {
+            TRY(launch_dequant_row_mlx4(embd_table, embd_mlx.scales, embd_mlx.biases, embd_mlx.elem_bytes, embd_mlx.group, tok_ptr, P.n_embd, x, stream));
+        } else {
+            TRY(launch_dequant_row(embd_dtype, embd_table, tok_ptr, P.n_embd, x, stream));
+        }
         ++launches;
     }
     const size_t kvb = P.kv_f16 ? 2 : 4;
@@ -574,7 +685,7 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
         // q|k and v read the same normed x and share nothing else: one persistent launch for both
         // (matvec_chain.cu) when the formats allow it, else one launch each
         bool chained = false;
-        if (L.qk_fused && use_chain && matvec_chain_supported(L.wqk.fmt, L.wqk.out, L.wqk.cols, EPI_STORE) &&
+        if (L.qk_fused && !L.qkv_fused && use_chain && matvec_chain_supported(L.wqk.fmt, L.wqk.out, L.wqk.cols, EPI_STORE) &&
             matvec_chain_supported(L.wv.fmt, L.wv.out, L.wv.cols, EPI_STORE)) {
             MatvecChainOp ops[2];
             ops[0].fmt = L.wqk.fmt, ops[0].w = L.wqk.w, ops[0].x = x, ops[0].y = qk, ops[0].out_dim = L.wqk.out, ops[0].in_dim = L.wqk.cols;
@@ -585,7 +696,9 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
             else if (e != cudaErrorNotSupported) return e;
             else cudaGetLastError();
         }
-        if (!chained) {
+        if (L.qkv_fused) {
+            TRY(mv(L.wqk, x, qk, L.attn_norm, EPI_STORE, nullptr));
+        } else if (!chained) {
             if (L.qk_fused) {
                 TRY(mv(L.wqk, x, qk, L.attn_norm, EPI_STORE, nullptr));
             } else {
@@ -595,7 +708,7 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
             TRY(mv(L.wv, x, vbuf, L.attn_norm, EPI_STORE, nullptr));
         }
         AttnParams ap;
-        ap.q = qk, ap.knew = qk + qd, ap.vnew = vbuf;
+        ap.q = qk, ap.knew = qk + qd, ap.vnew = L.qkv_fused ? qk + qd + kvd : vbuf;
         ap.kcache = (uint8_t *)kcache + l * P.n_ctx * kvd * kvb;
         ap.vcache = (uint8_t *)vcache + l * P.n_ctx * kvd * kvb;
         ap.rope = rope, ap.pos_ptr = pos_ptr, ap.scale = 1.0f / sqrtf((float)hd);
@@ -605,6 +718,18 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
         TRY(launch_attn(ap, (int)hd, (int)(P.n_head / P.n_kv_head), (int)P.n_kv_head, P.kv_f16 != 0, stream, use_pdl));
         ++launches;
         TRY(mv(L.wo, attn, x, nullptr, EPI_RESIDUAL, x));
+        if (L.moe) {
+            // forward.rs:484-494: normalised x -> router logits -> top-k -> the selected experts' SwiGLU FFNs,
+            // weighted by the softmax over the selected logits -> added to x
+            rmsnorm_vec_kernel<<<1, 256, 0, stream>>>(x, L.ffn_norm, P.eps, (int)P.n_embd, xb);
+            ++launches;
+            TRY(mv(L.moe_gate, xb, moe_logits, nullptr, EPI_STORE, nullptr));
+            TRY(launch_moe_ffn(dev, L.experts, xb, moe_logits, 1, P.n_experts_used, x, nullptr, nullptr, moe_scratch, d_status, stream, false,
+                               use_pdl, nullptr, x));
+            launches += 4; // route, gate|up, down, combine (+ residual)
+            TRY(cudaGetLastError());
+            continue;
+        }
         if (L.gu_fused) {
             TRY(mv(L.wgu, x, hidden, L.ffn_norm, EPI_SWIGLU, nullptr));
         } else {

@@ -13,18 +13,26 @@ struct ForwardParams { // GpuParams, crates/ullm-metal/src/forward.rs:24-51 (den
     float rope_theta = 10000.f, eps = 1e-5f;
     int kv_f16 = 0;
     int rope_neox = 0, qk_norm = 0;
+    size_t n_experts = 0, n_experts_used = 0, moe_inter = 0; // mixture-of-experts layers (n_ff may then be 0)
 };
 struct HostWeight { // GpuWeight, forward.rs:56-64
     int dtype = 0;
     const void *bytes = nullptr;
     size_t out = 0, cols = 0;
+    const void *scales = nullptr, *biases = nullptr; // MLX 4-bit: per-group tables (element type: HostModel::mlx_table_bytes)
+    size_t group = 0;
 };
 struct HostLayer {
     const float *attn_norm = nullptr, *ffn_norm = nullptr;
     HostWeight wq, wk, wv, wo, w_gate, w_up, w_down;
     const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    // mixture-of-experts layer (GpuLayerInput::moe_gate / experts_*, forward.rs:95-99): router [n_experts, n_embd] and the
+    // stacked experts as host pointers; `experts` null = dense layer
+    HostWeight moe_gate;
+    const MoeExperts *experts = nullptr;
 };
 struct HostModel {
+    int mlx_table_bytes = 4; // 4 = f32 tables (as the reference passes them), 2 = bf16 bits as stored on disk
     HostWeight output;
     const float *final_norm = nullptr;
     std::vector<HostLayer> layers;
@@ -36,12 +44,18 @@ struct Forward {
         int fmt = 0;
         void *w = nullptr;
         size_t out = 0, cols = 0;
+        void *scales = nullptr, *biases = nullptr; // MLX 4-bit tables
+        int tbl_bytes = 4;
+        size_t group = 0;
     };
     struct Layer {
         float *attn_norm = nullptr, *ffn_norm = nullptr;
         float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr; // optional
-        bool qk_fused = false, gu_fused = false;
+        bool qk_fused = false, gu_fused = false, qkv_fused = false; // qkv_fused: MLX q | k | v rows and tables stacked (wqk holds them)
         Mat wqk, wq, wk, wv, wo, wgu, wg, wu, wd;
+        bool moe = false; // router + routed experts instead of the dense FFN
+        Mat moe_gate;
+        MoeExperts experts;
     };
 
     DeviceInfo dev;
@@ -84,6 +98,12 @@ struct Forward {
     cudaError_t forward_batch(const float *embeds_host, size_t s, float *logits_host);
     float *bx = nullptr, *bxn = nullptr, *bqk = nullptr, *bv = nullptr, *bh = nullptr;
     void *bscratch = nullptr;
+    // mixture-of-experts step: router logits, experts' output, routing scratch; tmpn / tmpo serve the
+    // unfused fallback of mv() (normalised input, un-added output)
+    float *moe_logits = nullptr, *moe_out = nullptr, *tmpn = nullptr, *tmpo = nullptr;
+    void *moe_scratch = nullptr;
+    int mlx_table_bytes = 4;
+    MlxTables embd_mlx; // tables of the embedding matrix when greedy() is given an MLX 4-bit one (embd_dtype 1000)
 
   private:
     cudaError_t dev_alloc(void **out, size_t bytes);
@@ -91,6 +111,8 @@ struct Forward {
     cudaError_t upload_rows(const void *bytes, int fmt, size_t out_dim, size_t cols, Mat *out);
     cudaError_t upload_pair(const HostWeight &a, const HostWeight &b, bool interleave, Mat *out);
     cudaError_t upload_one(const HostWeight &a, Mat *out);
+    cudaError_t upload_mlx_stack(const HostWeight *const *ws, int n, Mat *out);
+    cudaError_t upload_experts(const MoeExperts &h, MoeExperts *out);
     cudaError_t mv(const Mat &m, const float *in, float *out, const float *norm_w, int epi, const float *res);
     cudaError_t enqueue_step(int mode, const void *embd_table, int embd_dtype);
     cudaError_t run_step(int mode, const void *embd_table, int embd_dtype);

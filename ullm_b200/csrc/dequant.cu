@@ -102,6 +102,35 @@ cudaError_t launch_dequant(int dtype, const void *d_data, float *d_out, size_t n
     return cudaGetLastError();
 }
 
+// Row `*d_row` of an MLX 4-bit table [rows, cols] -> cols f32, tables f32 or bf16 bits (dequant_mlx_row,
+// crates/ullm-model/src/math.rs:68-79: q * scale + bias, product and sum rounded separately).
+template <typename TBL>
+__global__ void dequant_row_mlx4_kernel(const uint32_t *__restrict__ w, const TBL *__restrict__ scales, const TBL *__restrict__ biases,
+                                        const uint32_t *__restrict__ d_row, size_t cols, size_t group, float *__restrict__ y) {
+    const size_t words = cols / 8, wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi >= words) return;
+    const size_t row = *d_row;
+    const uint32_t word = w[row * words + wi];
+    const size_t g = row * (cols / group) + wi * 8 / group; // a word never straddles a group (group % 8 == 0)
+    float sc, bi;
+    if (sizeof(TBL) == 2) sc = bf16_bits_to_f32((uint16_t)scales[g]), bi = bf16_bits_to_f32((uint16_t)biases[g]);
+    else sc = (float)scales[g], bi = (float)biases[g];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) y[wi * 8 + n] = __fadd_rn(__fmul_rn((float)((word >> (4 * n)) & 0xF), sc), bi);
+}
+cudaError_t launch_dequant_row_mlx4(const void *d_w, const void *d_scales, const void *d_biases, int tbl_bytes, size_t group,
+                                    const uint32_t *d_row, size_t cols, float *d_out, cudaStream_t st) {
+    if (cols % 8 || !group || group % 8 || cols % group) return cudaErrorInvalidValue;
+    const unsigned blocks = (unsigned)((cols / 8 + 255) / 256);
+    if (tbl_bytes == 2)
+        dequant_row_mlx4_kernel<uint16_t><<<blocks, 256, 0, st>>>((const uint32_t *)d_w, (const uint16_t *)d_scales, (const uint16_t *)d_biases, d_row,
+                                                                   cols, group, d_out);
+    else
+        dequant_row_mlx4_kernel<float><<<blocks, 256, 0, st>>>((const uint32_t *)d_w, (const float *)d_scales, (const float *)d_biases, d_row, cols,
+                                                               group, d_out);
+    return cudaGetLastError();
+}
+
 // Row `*d_row` of a [rows, cols] Q4_K / Q6_K table -> cols f32 (the embedding
 // lookup of crates/ullm-model/src/lib.rs:692-710 with the token id on the device).
 cudaError_t launch_dequant_row(int dtype, const void *d_table, const uint32_t *d_row, size_t cols, float *d_out,

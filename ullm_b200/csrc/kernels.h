@@ -26,6 +26,9 @@ struct MlxTables {
 cudaError_t launch_dequant(int dtype, const void *d_data, float *d_out, size_t n, cudaStream_t st);
 cudaError_t launch_dequant_row(int dtype, const void *d_table, const uint32_t *d_row, size_t cols, float *d_out,
                                cudaStream_t st);
+// The same for an MLX 4-bit table (tables f32 or bf16 bits).
+cudaError_t launch_dequant_row_mlx4(const void *d_w, const void *d_scales, const void *d_biases, int tbl_bytes, size_t group,
+                                    const uint32_t *d_row, size_t cols, float *d_out, cudaStream_t st);
 cudaError_t launch_dequant_mlx4(const uint32_t *d_w, const float *d_s, const float *d_b, float *d_y, size_t out_dim,
                                 size_t in_dim, size_t group, cudaStream_t st);
 
@@ -113,6 +116,7 @@ const char *moe_shape_error(const MoeExperts &e, size_t n_tok, size_t k);
 // ([n_tok, k]) may be null.  Everything is a device pointer.
 cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const float *d_x, const float *d_logits,
                            size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *d_scratch,
-                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out);
+                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out,
+                           const float *d_res = nullptr); // d_res: [n_tok, hidden] added to the result (may alias d_y)
 
 } // namespace ullm

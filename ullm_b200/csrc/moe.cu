@@ -338,14 +338,14 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const uint32_t *__restr
 
 // 4. y[t][o] = sum_slot wts[t][slot] * down[t*k+slot][o]   (lib.rs:1484-1487)
 __global__ void moe_combine_kernel(const float *__restrict__ down, const float *__restrict__ wts, float *__restrict__ y,
-                                   uint32_t n_tok, uint32_t k, uint32_t hidden) {
+                                   uint32_t n_tok, uint32_t k, uint32_t hidden, const float *__restrict__ res) {
     pdl_wait_prior();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_tok * hidden) return;
     const uint32_t t = i / hidden, o = i % hidden;
     float acc = 0.f;
     for (uint32_t s = 0; s < k; ++s) acc += wts[t * k + s] * down[((size_t)t * k + s) * hidden + o];
-    y[i] = acc;
+    y[i] = res ? res[i] + acc : acc; // the residual stream's `x += down` (lib.rs:959-961) when asked for
 }
 
 // ---------------------------------------------------------------------------
@@ -440,7 +440,7 @@ const char *moe_shape_error(const MoeExperts &e, size_t n_tok, size_t k) {
 
 cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const float *d_x, const float *d_logits,
                            size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *d_scratch,
-                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out) {
+                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out, const float *d_res) {
     // scratch carve-up
     const size_t pairs_cap = (size_t)MOE_MAX_TOK * MOE_MAX_K;
     uint8_t *sp = (uint8_t *)d_scratch;
@@ -506,7 +506,8 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
             if ((err = cudaGetLastError()) != cudaSuccess) return err;
         }
         const uint32_t n = nt * (uint32_t)e.hidden;
-        moe_combine_kernel<<<(n + 255) / 256, 256, 0, st>>>(down, wts, d_y + t0 * e.hidden, nt, (uint32_t)k, (uint32_t)e.hidden);
+        moe_combine_kernel<<<(n + 255) / 256, 256, 0, st>>>(down, wts, d_y + t0 * e.hidden, nt, (uint32_t)k, (uint32_t)e.hidden,
+                                                             d_res ? d_res + t0 * e.hidden : nullptr);
         if ((err = cudaGetLastError()) != cudaSuccess) return err;
     }
     return cudaSuccess;

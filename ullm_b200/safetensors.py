@@ -217,3 +217,42 @@ def write_model_dir(path, config: dict, shards: dict, index: bool = True):
     if index or len(shards) > 1:
         with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {}, "weight_map": weight_map}, f)
+
+
+def qwen3moe_to_dir(path, model: dict, shards: int = 2):
+    """Writes a model of :func:`ullm_b200.synth.gen_qwen3moe_model` as an MLX model directory with the tensor
+    names and the ``config.json`` keys ``LlamaModel::from_mlx`` reads (crates/ullm-model/src/mlx.rs:103-213)."""
+    from . import synth
+
+    p = model["params"]
+
+    def lin(name, t):
+        _, words, out, cols, sc, bi, _ = t
+        return mlx_linear_tensors(name, np.asarray(words).reshape(out, cols // 8), np.asarray(sc).reshape(out, -1), np.asarray(bi).reshape(out, -1))
+
+    def vec(name, a):
+        return [(name, "BF16", (len(a),), synth.f32_to_bf16(np.asarray(a, np.float32)))]
+
+    files = [[] for _ in range(shards)]
+    files[0] += lin("model.embed_tokens", model["tok_embd"])
+    files[-1] += lin("lm_head", model["output"]) + vec("model.norm.weight", model["final_norm"])
+    for i, l in enumerate(model["layers"]):
+        q, ts = f"model.layers.{i}", []
+        ts += vec(q + ".input_layernorm.weight", l["attn_norm"]) + vec(q + ".post_attention_layernorm.weight", l["ffn_norm"])
+        ts += vec(q + ".self_attn.q_norm.weight", l["q_norm"]) + vec(q + ".self_attn.k_norm.weight", l["k_norm"])
+        for n, k in (("q_proj", "wq"), ("k_proj", "wk"), ("v_proj", "wv"), ("o_proj", "wo")):
+            ts += lin(f"{q}.self_attn.{n}", l[k])
+        ts += lin(q + ".mlp.gate", l["moe_gate"])
+        x = l["experts"]
+        ne, hid, inter = x["n_experts"], x["hidden"], x["inter"]
+        for n, k, o, c in (("gate_proj", "gate", inter, hid), ("up_proj", "up", inter, hid), ("down_proj", "down", hid, inter)):
+            w, sc, bi = x[k]
+            ts += mlx_linear_tensors(f"{q}.mlp.switch_mlp.{n}", np.asarray(w).reshape(ne, o, c // 8), np.asarray(sc).reshape(ne, o, -1),
+                                     np.asarray(bi).reshape(ne, o, -1))
+        files[i * shards // max(1, len(model["layers"]))] += ts
+    config = {"architectures": ["Qwen3MoeForCausalLM"], "hidden_size": p["n_embd"], "num_attention_heads": p["n_head"],
+              "num_hidden_layers": p["n_layer"], "num_key_value_heads": p["n_kv_head"], "head_dim": p["head_dim"],
+              "num_experts": p["n_experts"], "num_experts_per_tok": p["n_experts_used"], "moe_intermediate_size": p["moe_inter"],
+              "max_position_embeddings": p["n_ctx"], "rope_theta": p["rope_theta"], "rms_norm_eps": p["eps"], "vocab_size": p["vocab"],
+              "quantization": {"group_size": p["group"], "bits": 4}}
+    write_model_dir(path, config, {f"model-{j + 1:05d}-of-{shards:05d}.safetensors": ts for j, ts in enumerate(files)})

@@ -221,3 +221,48 @@ def gen_kv_prefill(p: dict, n_pos: int, seed: int):
     k = normal(seed, n).astype(np.float16).astype(np.float32).reshape(p["n_layer"], n_pos, kvd)
     v = normal(seed + 1, n).astype(np.float16).astype(np.float32).reshape(p["n_layer"], n_pos, kvd)
     return k, v
+
+
+QWEN3MOE_TINY = dict(n_embd=256, n_layer=2, n_head=4, n_kv_head=2, head_dim=64, n_ff=0, n_ctx=64, vocab=512, rope_theta=1000000.0,
+                     eps=1e-6, n_experts=8, n_experts_used=2, moe_inter=128, group=64)
+# Qwen3-30B-A3B's shape (crates/ullm-model/src/mlx.rs:117-141 reads it from config.json), with fewer layers by default
+QWEN3MOE_30B = dict(n_embd=2048, n_layer=48, n_head=32, n_kv_head=4, head_dim=128, n_ff=0, n_ctx=1280, vocab=151936,
+                    rope_theta=1000000.0, eps=1e-6, n_experts=128, n_experts_used=8, moe_inter=768, group=64)
+
+
+def gen_qwen3moe_model(p: dict, seed: int) -> dict:
+    """Random MLX 4-bit Qwen3-MoE weights laid out as ``LlamaModel::from_mlx`` builds them
+    (crates/ullm-model/src/mlx.rs:143-213): every linear ``(MLX_U32, words, out, cols, scales, biases, group)``
+    with bf16 tables as bits, norms = bf16-exact 1 + 0.1 N(0,1), per layer a router ``moe_gate`` and the
+    stacked experts ``{"gate", "up", "down": (words, scales, biases), n_experts, hidden, inter, group}``."""
+    e, hd, g = p["n_embd"], p["head_dim"], p["group"]
+    qd, kvd, ne, mi = p["n_head"] * hd, p["n_kv_head"] * hd, p["n_experts"], p["moe_inter"]
+    s = [seed * 1000 + 0x77000]
+
+    def nxt():
+        s[0] += 7
+        return s[0]
+
+    def mlx(out, cols):
+        # biases near -7.5 * scale centre the 4-bit values: with the all-positive weights of gen_mlx4 every
+        # activation would be dominated by one common component and the logits would not depend on the position
+        words, sc, bi = gen_mlx4(out, cols, g, nxt())
+        bi = f32_to_bf16((np.float32(-7.5) * bf16_to_f32(sc) + np.float32(0.1) * bf16_to_f32(bi)).astype(np.float32))
+        return words, sc, bi
+
+    def w(out, cols):
+        words, sc, bi = mlx(out, cols)
+        return (1000, words, out, cols, sc, bi, g)
+
+    def norm(n):
+        return bf16_to_f32(f32_to_bf16((np.float32(1.0) + np.float32(0.1) * normal(nxt(), n)).astype(np.float32)))
+
+    layers = []
+    for _ in range(p["n_layer"]):
+        layers.append(dict(
+            attn_norm=norm(e), ffn_norm=norm(e), q_norm=norm(hd), k_norm=norm(hd),
+            wq=w(qd, e), wk=w(kvd, e), wv=w(kvd, e), wo=w(e, qd), moe_gate=w(ne, e),
+            experts=dict(gate=mlx(ne * mi, e), up=mlx(ne * mi, e), down=mlx(ne * e, mi),
+                         n_experts=ne, hidden=e, inter=mi, group=g),
+        ))
+    return dict(params=dict(p), tok_embd=w(p["vocab"], e), output=w(p["vocab"], e), final_norm=norm(e), layers=layers)
