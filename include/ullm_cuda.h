@@ -281,9 +281,9 @@ int ullm_cuda_forward_create(ullm_cuda_ctx *ctx, const ullm_gpu_model_input *in,
 /* The same from an open GGUF file (include/ullm_gguf.h): hyperparameters and tensor
  * names as LlamaModel::from_gguf reads them (crates/ullm-model/src/lib.rs:174-301:
  * <arch>.embedding_length ..., token_embd.weight, blk.N.attn_q.weight ..., output_norm.weight,
- * output.weight or the tied embeddings), then GpuForward::new as build_gpu calls it
- * (lib.rs:712-805).  "llama" architecture with Q4_K / Q6_K matrices; files that carry
- * bias, q/k-norm or sandwich-norm tensors are refused with UNSUPPORTED. */
+ * output.weight or the tied embeddings; optional blk.N.attn_{q,k,v}.bias and blk.N.attn_{q,k}_norm.weight),
+ * then GpuForward::new as build_gpu calls it (lib.rs:712-805).  "llama" and "qwen2" architectures with
+ * Q4_K / Q6_K matrices; files that carry sandwich-norm tensors are refused with UNSUPPORTED. */
 struct ullm_gguf;
 int ullm_cuda_forward_create_gguf(ullm_cuda_ctx *ctx, const struct ullm_gguf *g, int kv_f16, ullm_cuda_fwd **out);
 /* The same from an open MLX model directory (include/ullm_safetensors.h): hyperparameters and tensor

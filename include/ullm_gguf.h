@@ -72,7 +72,8 @@ int ullm_gguf_meta_array_str(const ullm_gguf *g, const char *key, size_t i, cons
  * defaults: head_count_kv = head_count, context_length 2048 capped at 8192, key_length =
  * embedding_length / head_count, rope.freq_base 10000, layer_norm_rms_epsilon 1e-5, vocab =
  * <arch>.vocab_size or the length of tokenizer.ggml.tokens (lib.rs:207-215).  ULLM_GGUF_ERR_FORMAT
- * when a required key is missing, ULLM_GGUF_ERR_UNSUPPORTED for architectures other than "llama". */
+ * when a required key is missing, ULLM_GGUF_ERR_UNSUPPORTED for architectures other than "llama" and "qwen2"
+ * (the reference also loads "gemma3", whose sandwich norms, GeGLU and sliding window this backend does not build). */
 typedef struct ullm_gguf_llama_params {
     uint64_t n_embd, n_layer, n_head, n_kv_head, head_dim, n_ff, n_ctx, vocab;
     float rope_theta, eps;

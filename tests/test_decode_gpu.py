@@ -139,12 +139,11 @@ def test_engine_built_from_a_gguf_file_equals_the_one_built_from_arrays(ctx, tmp
     embd = ctx.upload(t["data"])
     assert np.array_equal(a.greedy(embd, t["dtype"], tok, 4, 6), b.greedy(embd, t["dtype"], tok, 4, 6))
     a.free(), b.free()
-    # a Qwen2-style bias tensor: this decode variant is not built -> Unsupported, not ignored
-    md = [(k, ty, v) for k, ty, v in [("general.architecture", gguf.T_STRING, "llama")]]
+    # a sandwich-norm tensor (Gemma): that variant is not built -> Unsupported, not ignored
     blob = gguf.llama_to_gguf(m)
     g2 = gguf.Gguf(blob)
     ts = [(x["name"], x["dtype"], x["shape"], x["data"].copy()) for x in g2.tensors()]
-    ts.append(("blk.0.attn_q.bias", 0, (p["n_head"] * p["head_dim"],), np.zeros(p["n_head"] * p["head_dim"], np.float32)))
+    ts.append(("blk.0.post_attention_norm.weight", 0, (p["n_embd"],), np.ones(p["n_embd"], np.float32)))
     keys = [(k, gguf.T_STRING if isinstance(g2.get(k), str) else (gguf.T_F32 if isinstance(g2.get(k), float) else gguf.T_U32), g2.get(k)) for k in g2.keys()]
     with pytest.raises(backend.Unsupported):
         backend.GpuForward.from_gguf(ctx, gguf.Gguf(gguf.write_gguf(keys, ts)))
@@ -156,6 +155,39 @@ def test_engine_built_from_a_gguf_file_equals_the_one_built_from_arrays(ctx, tmp
     x = om.embed(5)
     assert np.array_equal(tied.forward(x, 0), ref.forward(x, 0))
     tied.free(), ref.free()
+
+
+def test_gguf_qwen2_biases_and_qk_norms(ctx):
+    """LlamaModel::from_gguf reads "qwen2" files and the optional bias / Q-K-norm tensors of any architecture
+    (lib.rs:200-209, 277-281); build_gpu turns qk_norm on when layer 0 has the weights (lib.rs:714)."""
+    from ullm_b200 import gguf
+
+    p = dict(synth.LLAMA_TINY)
+    m = variant_model(p, 31, True, True)
+    # the values a file holds: K bias stored as F16, K norm as BF16
+    for l in m["layers"]:
+        l["k_bias"] = l["k_bias"].astype(np.float16).astype(np.float32)
+        l["k_norm"] = synth.bf16_to_f32(synth.f32_to_bf16(l["k_norm"]))
+    g = gguf.Gguf(gguf.llama_to_gguf(m, arch="qwen2"))
+    assert g.architecture == "qwen2" and g.llama_params()["n_ff"] == p["n_ff"]
+    a, b = backend.GpuForward(ctx, m, kv_f16=True, qk_norm=1), backend.GpuForward.from_gguf(ctx, g, kv_f16=True)
+    mk = lambda t: oracle.Weight(t[0], t[1], t[2], t[3])
+    layers = [{k: (mk(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in m["layers"]]
+    om = oracle.LlamaModel(m["params"], mk(m["tok_embd"]), mk(m["output"]), m["final_norm"], layers, True)
+    tok = 11
+    for pos in range(4):
+        x = om.embed(tok)
+        la, lb = a.forward(x, pos), b.forward(x, pos)
+        assert np.array_equal(la, lb), pos
+        assert synth.rel_err(lb, om.forward(tok, pos)) < 1e-3
+        tok = int(np.argmax(lb))
+    a.free(), b.free()
+    # a file with the Q norm only, or with norms in some layers only, is malformed
+    ts = [(x["name"], x["dtype"], x["shape"], x["data"].copy()) for x in g.tensors()]
+    keys = [(k, gguf.T_STRING if isinstance(g.get(k), str) else (gguf.T_F32 if isinstance(g.get(k), float) else gguf.T_U32), g.get(k)) for k in g.keys()]
+    for dropped in (("blk.0.attn_k_norm.weight",), ("blk.1.attn_q_norm.weight", "blk.1.attn_k_norm.weight")):
+        with pytest.raises(backend.FormatError):
+            backend.GpuForward.from_gguf(ctx, gguf.Gguf(gguf.write_gguf(keys, [t for t in ts if t[0] not in dropped])))
 
 
 def variant_model(p, seed, bias, qk_norm):

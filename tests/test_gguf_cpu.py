@@ -155,6 +155,9 @@ def test_llama_defaults_and_required_keys():
     with pytest.raises(gguf.GgufError) as e:
         gguf.Gguf(gguf.write_gguf(base[:-1], [])).llama_params()
     assert e.value.code == gguf.ERR_FORMAT and "feed_forward_length" in str(e.value)
-    with pytest.raises(gguf.GgufError) as e:
-        gguf.Gguf(gguf.write_gguf([("general.architecture", T_STRING, "qwen3")], [])).llama_params()
-    assert e.value.code == gguf.ERR_UNSUPPORTED
+    for arch in ("qwen3", "gemma3", ""):  # lib.rs:200-209 reads llama, qwen2 and gemma3; gemma3's kernels are not built here
+        with pytest.raises(gguf.GgufError) as e:
+            gguf.Gguf(gguf.write_gguf([("general.architecture", T_STRING, arch)], [])).llama_params()
+        assert e.value.code == gguf.ERR_UNSUPPORTED
+    q2 = [(k.replace("llama.", "qwen2."), t, "qwen2" if k == "general.architecture" else v) for k, t, v in base]
+    assert gguf.Gguf(gguf.write_gguf(q2, [])).llama_params()["n_ff"] == 1024  # keys are namespaced by the architecture (lib.rs:212-219)

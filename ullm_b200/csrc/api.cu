@@ -1069,7 +1069,7 @@ int ullm_cuda_forward_create_gguf(ullm_cuda_ctx *c, const ullm_gguf *g, int kv_f
     const size_t qd = lp.n_head * lp.head_dim, kvd = lp.n_kv_head * lp.head_dim;
     // f32 view of a norm vector (tensor_f32: F32 as is, F16 / BF16 widened)
     std::vector<std::vector<float>> norms;
-    norms.reserve(2 * lp.n_layer + 1);
+    norms.reserve(7 * lp.n_layer + 1); // pointers into it are handed out: it must never reallocate
     auto norm = [&](const std::string &name, size_t n, const float **dst) -> int {
         ullm_gguf_tensor t;
         if (ullm_gguf_tensor_find(g, name.c_str(), &t)) return ctx_fail(c, ULLM_ERR_FORMAT, "missing tensor '%s'", name.c_str());
@@ -1111,12 +1111,24 @@ int ullm_cuda_forward_create_gguf(ullm_cuda_ctx *c, const ullm_gguf *g, int kv_f
             (rc = weight(b + "ffn_up.weight", lp.n_ff, lp.n_embd, &l.w_up, false)) ||
             (rc = weight(b + "ffn_down.weight", lp.n_embd, lp.n_ff, &l.w_down, false)))
             return rc;
+        // optional tensors (lib.rs:277-281: `.ok()`): Qwen2 projection biases, per-head Q/K norm weights
+        auto optional = [&](const char *suffix, size_t n, const float **dst) -> int {
+            ullm_gguf_tensor t;
+            if (ullm_gguf_tensor_find(g, (b + suffix).c_str(), &t) != ULLM_GGUF_OK) return ULLM_OK;
+            return norm(b + suffix, n, dst);
+        };
+        if ((rc = optional("attn_q.bias", qd, &l.q_bias)) || (rc = optional("attn_k.bias", kvd, &l.k_bias)) ||
+            (rc = optional("attn_v.bias", kvd, &l.v_bias)) || (rc = optional("attn_q_norm.weight", lp.head_dim, &l.q_norm)) ||
+            (rc = optional("attn_k_norm.weight", lp.head_dim, &l.k_norm)))
+            return rc;
+        if (!l.q_norm != !l.k_norm) return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: only one of attn_q_norm / attn_k_norm is present", i);
+        if (i > 0 && !l.q_norm != !layers[0].q_norm) // qk_norm is one flag for the model (build_gpu, lib.rs:714)
+            return ctx_fail(c, ULLM_ERR_FORMAT, "layer %zu: attn_q_norm present in some layers only", i);
         // tensors this backend has no kernel for are refused, not ignored
-        for (const char *extra : {"attn_q.bias", "attn_k.bias", "attn_v.bias", "attn_q_norm.weight", "attn_k_norm.weight",
-                                  "post_attention_norm.weight", "post_ffw_norm.weight"}) {
+        for (const char *extra : {"post_attention_norm.weight", "post_ffw_norm.weight"}) {
             ullm_gguf_tensor t;
             if (ullm_gguf_tensor_find(g, (b + extra).c_str(), &t) == ULLM_GGUF_OK)
-                return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "tensor '%s%s': this variant of the decode step is not built", b.c_str(), extra);
+                return ctx_fail(c, ULLM_ERR_UNSUPPORTED, "tensor '%s%s': sandwich norms are not built", b.c_str(), extra);
         }
     }
     ullm_gpu_model_input in;
@@ -1124,6 +1136,7 @@ int ullm_cuda_forward_create_gguf(ullm_cuda_ctx *c, const ullm_gguf *g, int kv_f
     in.params.n_embd = lp.n_embd, in.params.n_layer = lp.n_layer, in.params.n_head = lp.n_head, in.params.n_kv_head = lp.n_kv_head;
     in.params.head_dim = lp.head_dim, in.params.n_ff = lp.n_ff, in.params.n_ctx = lp.n_ctx, in.params.vocab = lp.vocab;
     in.params.rope_theta = lp.rope_theta, in.params.eps = lp.eps, in.params.kv_f16 = kv_f16 ? 1 : 0;
+    in.params.qk_norm = lp.n_layer && layers[0].q_norm ? 1 : 0; // rope_neox stays 0: GGUF Llama / Qwen weights are permuted for interleaved RoPE (lib.rs:313-315)
     if ((rc = norm("output_norm.weight", lp.n_embd, &in.final_norm))) return rc;
     // some models tie the output projection to the input embeddings (lib.rs:303-304)
     rc = weight("output.weight", lp.vocab, lp.n_embd, &in.output, true);

@@ -357,9 +357,9 @@ int ullm_gguf_meta_array_str(const ullm_gguf *g, const char *key, size_t i, cons
 
 int ullm_gguf_llama_params_get(const ullm_gguf *g, ullm_gguf_llama_params *out, char *err, size_t err_cap) {
     if (!g || !out) return ULLM_GGUF_ERR_INVALID;
-    if (g->arch != "llama") {
+    if (g->arch != "llama" && g->arch != "qwen2") { // lib.rs:200-209; "gemma3" needs kernels this backend does not have
         char m[160];
-        snprintf(m, sizeof m, "architecture '%s' is not supported by this backend (llama only)", g->arch.c_str());
+        snprintf(m, sizeof m, "architecture '%s' is not supported by this backend (llama, qwen2)", g->arch.c_str());
         put_err(err, err_cap, m);
         return ULLM_GGUF_ERR_UNSUPPORTED;
     }

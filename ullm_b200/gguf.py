@@ -219,16 +219,16 @@ def write_gguf(metadata, tensors, alignment: int | None = None, version: int = 3
     return bytes(out)
 
 
-def llama_to_gguf(model: dict, alignment: int | None = None) -> bytes:
+def llama_to_gguf(model: dict, alignment: int | None = None, arch: str = "llama") -> bytes:
     """The synthetic model of :func:`ullm_b200.synth.gen_llama_model` as a GGUF file with the keys and
     tensor names ``LlamaModel::from_gguf`` reads (crates/ullm-model/src/lib.rs:174-301)."""
     p = model["params"]
-    md = [("general.architecture", T_STRING, "llama"), ("llama.embedding_length", T_U32, p["n_embd"]),
-          ("llama.block_count", T_U32, p["n_layer"]), ("llama.attention.head_count", T_U32, p["n_head"]),
-          ("llama.attention.head_count_kv", T_U32, p["n_kv_head"]), ("llama.feed_forward_length", T_U32, p["n_ff"]),
-          ("llama.context_length", T_U32, p["n_ctx"]), ("llama.attention.key_length", T_U32, p["head_dim"]),
-          ("llama.rope.freq_base", T_F32, p["rope_theta"]), ("llama.attention.layer_norm_rms_epsilon", T_F32, p["eps"]),
-          ("llama.vocab_size", T_U32, p["vocab"])]
+    md = [("general.architecture", T_STRING, arch), (arch + ".embedding_length", T_U32, p["n_embd"]),
+          (arch + ".block_count", T_U32, p["n_layer"]), (arch + ".attention.head_count", T_U32, p["n_head"]),
+          (arch + ".attention.head_count_kv", T_U32, p["n_kv_head"]), (arch + ".feed_forward_length", T_U32, p["n_ff"]),
+          (arch + ".context_length", T_U32, p["n_ctx"]), (arch + ".attention.key_length", T_U32, p["head_dim"]),
+          (arch + ".rope.freq_base", T_F32, p["rope_theta"]), (arch + ".attention.layer_norm_rms_epsilon", T_F32, p["eps"]),
+          (arch + ".vocab_size", T_U32, p["vocab"])]
 
     def w(name, t):
         dtype, data, out, cols = t
@@ -242,5 +242,12 @@ def llama_to_gguf(model: dict, alignment: int | None = None) -> bytes:
                w(b + "attn_output.weight", l["wo"]),
                (b + "ffn_norm.weight", 0, (p["n_embd"],), np.asarray(l["ffn_norm"], np.float32)),
                w(b + "ffn_gate.weight", l["w_gate"]), w(b + "ffn_up.weight", l["w_up"]), w(b + "ffn_down.weight", l["w_down"])]
+        # optional tensors (lib.rs:277-281); the K bias goes out as F16 and the K norm as BF16 to exercise tensor_f32's widening
+        for key, name, dt in (("q_bias", "attn_q.bias", 0), ("k_bias", "attn_k.bias", 1), ("v_bias", "attn_v.bias", 0),
+                              ("q_norm", "attn_q_norm.weight", 0), ("k_norm", "attn_k_norm.weight", 30)):
+            if l.get(key) is not None:
+                a = np.asarray(l[key], np.float32)
+                data = a if dt == 0 else (a.astype(np.float16) if dt == 1 else (a.view(np.uint32) >> 16).astype(np.uint16))
+                ts.append((b + name, dt, (a.size,), data))
     ts += [("output_norm.weight", 0, (p["n_embd"],), np.asarray(model["final_norm"], np.float32)), w("output.weight", model["output"])]
     return write_gguf(md, ts, alignment)
