@@ -145,7 +145,7 @@ struct MoeStreamParams {
     uint32_t row_bytes, tbl_row_bytes;
     uint32_t R, NW, S, tiles_per_expert, ncg;
     uint32_t w_stage_bytes, tbl_stage_bytes, stage_bytes; // one matrix' regions; stage = NM * (w + 2 tbl)
-    uint32_t off_q, off_ring;
+    uint32_t off_route, off_q, off_ring; // byte offsets in dynamic shared memory
 };
 
 // GATE_UP: two matrices, x indexed by token, epilogue silu(g)*u.
@@ -167,28 +167,48 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         }
         mbar_fence_init();
     }
-    __syncthreads();
     pdl_launch_dependents();
     pdl_wait_prior(); // the routing table and the activations come from earlier kernels
 
-    const int D = p.route[0];
-    const int *ex_list = p.route + route_off_list(), *ex_off = p.route + route_off_offs(p.n_exp),
-              *pairs = p.route + route_off_pairs(p.n_exp);
+    // The routing table goes to shared memory in one sweep (one round trip to L2 instead of one per
+    // entry looked at): [0] D, expert ids, pair offsets, pair ids, then this CTA's first / end unit.
+    int *rt_s = (int *)(smem + p.off_route);
+    int *ex_list = rt_s + route_off_list(), *ex_off = rt_s + route_off_offs(p.n_exp), *pairs = rt_s + route_off_pairs(p.n_exp);
+    const uint32_t n_route = (uint32_t)route_off_pairs(p.n_exp) + p.n_tok * p.k;
+    uint32_t *u_s = (uint32_t *)(rt_s + route_off_pairs(p.n_exp) + MOE_MAX_TOK * MOE_MAX_K);
+    for (uint32_t i = tid; i < n_route; i += blockDim.x) rt_s[i] = p.route[i];
+    __syncthreads();
+    const int D = rt_s[0];
     // Units (expert d, row tile rt), in that order, are dealt to the CTAs by COST, not by count: a
     // tile of an expert picked by np pairs costs np row passes (the arithmetic per pair is about
     // what the tile's transfer takes, so popular experts are compute-bound).  Unit (d, rt) sits at
     // cost position ex_off[d] * T + rt * np(d); CTA b owns the units whose position falls in its
-    // equal share of the total npairs * T.
+    // equal share of the total npairs * T.  The first expert whose last tile lies at or beyond a cost
+    // is found by a ballot over the experts (the bound grows with d); warps 0 and 1 do one end each.
     const uint32_t T = p.tiles_per_expert;
-    const uint64_t C = (uint64_t)ex_off[D] * T;
-    auto first_unit_at = [&](uint64_t c) -> uint32_t {
-        for (int d = 0; d < D; ++d) {
-            const uint64_t base = (uint64_t)ex_off[d] * T, np = (uint64_t)(ex_off[d + 1] - ex_off[d]);
-            if (c <= base + (T - 1) * np) return (uint32_t)d * T + (c <= base ? 0u : (uint32_t)((c - base + np - 1) / np));
+    if (warp < 2) {
+        const uint64_t C = (uint64_t)ex_off[D] * T, c = C * (blockIdx.x + warp) / gridDim.x;
+        uint32_t unit = (uint32_t)D * T;
+        for (int d0 = 0; d0 < D; d0 += 32) {
+            const int d = d0 + (int)lane;
+            uint64_t base = 0, np = 1;
+            bool hit = false;
+            if (d < D) {
+                base = (uint64_t)ex_off[d] * T, np = (uint64_t)(ex_off[d + 1] - ex_off[d]);
+                hit = c <= base + (T - 1) * np;
+            }
+            const uint32_t m = __ballot_sync(0xffffffffu, hit);
+            if (m) {
+                const int first = __ffs(m) - 1;
+                const uint32_t mine = (uint32_t)d * T + (c <= base ? 0u : (uint32_t)((c - base + np - 1) / np));
+                unit = __shfl_sync(0xffffffffu, mine, first);
+                break;
+            }
         }
-        return (uint32_t)D * T;
-    };
-    const uint32_t u0 = first_unit_at(C * blockIdx.x / gridDim.x), u1 = first_unit_at(C * (blockIdx.x + 1) / gridDim.x);
+        if (lane == 0) u_s[warp] = unit;
+    }
+    __syncthreads();
+    const uint32_t u0 = u_s[0], u1 = u_s[1];
 
     if (producer) {
         if (lane == 0) {
@@ -219,11 +239,15 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     }
 
     const uint32_t nthr_c = p.NW * 32; // consumer threads (named barrier 1)
+    // Fixed-point images of several activation vectors are built side by side, one group of warps per
+    // vector, so that their loads are in flight together.
+    const uint32_t pg_thr = max(32u, (nthr_c / max(1u, GATE_UP ? p.n_tok : 4u)) & ~31u), pg_n = nthr_c / pg_thr;
+    const uint32_t pg = tid / pg_thr, pg_tid = tid % pg_thr; // pg >= pg_n: a leftover warp, idle here
     if (GATE_UP) {
         // every token's x, once per CTA
-        for (uint32_t t = 0; t < p.n_tok; ++t)
+        for (uint32_t t = pg; t < p.n_tok && pg < pg_n; t += pg_n)
             prep_image<FMT_MLX4>(ActSrc{p.act + (size_t)t * p.in_dim, nullptr, 0.f}, p.in_dim,
-                                 qimg + (size_t)t * p.ncg * XR * 32, tid, nthr_c);
+                                 qimg + (size_t)t * p.ncg * XR * 32, pg_tid, pg_thr);
         asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
     }
 
@@ -242,9 +266,9 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         if (!GATE_UP && (int)d != cur_d) {
             // new expert: fixed-point images of the hidden vectors of its pairs
             asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // everyone done with the previous images
-            for (int j = 0; j < np; ++j)
+            for (int j = (int)pg; j < np && pg < pg_n; j += (int)pg_n)
                 prep_image<FMT_MLX4>(ActSrc{p.act + (size_t)pairs[pb + j] * p.in_dim, nullptr, 0.f}, p.in_dim,
-                                     qimg + (size_t)j * p.ncg * XR * 32, tid, nthr_c);
+                                     qimg + (size_t)j * p.ncg * XR * 32, pg_tid, pg_thr);
             asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
             loaded_vec = -1; // the images were rebuilt
         }
@@ -361,7 +385,7 @@ struct MoePlanInt {
 };
 
 static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, uint32_t in_dim, uint32_t group,
-                           int tbl_bytes, uint32_t n_vec) {
+                           int tbl_bytes, uint32_t n_vec, uint32_t n_exp) {
     MoePlanInt best;
     if (in_dim % 32 || group % 32 || in_dim % group) return best;
     const uint32_t NM = gate_up ? 2 : 1;
@@ -371,7 +395,8 @@ static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, u
     const uint32_t G = ncg <= 1 ? 1 : (ncg <= 2 ? 2 : 4);
     const uint32_t NW = 16;
     const int budget = dev.max_smem_optin - 1024;
-    const uint32_t off_q = 128;
+    const uint32_t off_route = 128; // routing table + the CTA's two unit bounds
+    const uint32_t off_q = align_up(off_route + ((uint32_t)route_off_pairs((int)n_exp) + MOE_MAX_TOK * MOE_MAX_K + 2) * 4, 128);
     const uint32_t off_ring = align_up(off_q + n_vec * ncg * XREGS_MLX * 32 * 4, 128);
     for (uint32_t RW = 1; RW <= 4; RW *= 2) {
         const uint32_t R = NW * RW;
@@ -393,7 +418,7 @@ static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, u
         p.rows = rows, p.in_dim = in_dim, p.group = group, p.row_bytes = row_bytes, p.tbl_row_bytes = tbl_row_bytes;
         p.R = R, p.NW = NW, p.S = S, p.tiles_per_expert = (rows + R - 1) / R, p.ncg = ncg;
         p.w_stage_bytes = wst, p.tbl_stage_bytes = tst, p.stage_bytes = stage;
-        p.off_q = off_q, p.off_ring = off_ring;
+        p.off_route = off_route, p.off_q = off_q, p.off_ring = off_ring;
     }
     return best;
 }
@@ -465,8 +490,8 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
 
         MoePlanInt pg, pd;
         if (!force_generic && aligned) {
-            pg = plan_moe(dev, true, (uint32_t)e.inter, (uint32_t)e.hidden, (uint32_t)e.group, (int)tb, nt);
-            pd = plan_moe(dev, false, (uint32_t)e.hidden, (uint32_t)e.inter, (uint32_t)e.group, (int)tb, nt);
+            pg = plan_moe(dev, true, (uint32_t)e.inter, (uint32_t)e.hidden, (uint32_t)e.group, (int)tb, nt, (uint32_t)e.n_experts);
+            pd = plan_moe(dev, false, (uint32_t)e.hidden, (uint32_t)e.inter, (uint32_t)e.group, (int)tb, nt, (uint32_t)e.n_experts);
         }
         if (pg.ok && pd.ok) {
             if (streamed_out) *streamed_out = 1;
