@@ -663,7 +663,6 @@ extern "C" int ullm_cuda_debug_last_plan(const ullm_cuda_ctx *c, int *vals, int 
     return ULLM_OK;
 }
 
-// ---- not built yet -----------------------------------------------------------
 // ---- mixture of experts ------------------------------------------------------
 struct ullm_cuda_experts {
     MoeExperts e;

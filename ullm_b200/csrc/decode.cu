@@ -2,14 +2,17 @@
 // quantized (CPU form: crates/ullm-model/src/lib.rs:807-969; GPU surface:
 // crates/ullm-metal/src/forward.rs:384-526).
 //
-// Per layer the step is six launches, all HBM-streaming matvecs except the
+// Per layer the step is five launches, all HBM-streaming matvecs except the
 // attention:
 //   [rmsnorm ->] W_qk x      (Q and K projections stored as one matrix)
 //   [rmsnorm ->] W_v  x
-//   rope(q), rope(k), K/V cache write, split-KV attention, split combine
+//   bias / per-head norm / rope of q and k, K/V cache write, split-KV attention, split combine
 //   W_o attn  (+ residual, in the epilogue)
 //   [rmsnorm ->] W_gate|up x (rows interleaved at upload; silu(g)*u in the epilogue)
 //   W_down h  (+ residual)
+// A mixture-of-experts layer (MLX 4-bit) replaces the last two by rmsnorm, router matvec, routing,
+// the selected experts' gate|up and down kernels and the weighted combine (+ residual): moe.cu;
+// its q, k and v projections are one stacked MLX matrix.
 // and norm + output projection at the end.  The position and the current token
 // live in device memory, so the same CUDA graph is replayed for every token: one
 // submission per decoded token, and greedy decoding (argmax -> embedding lookup)
@@ -36,6 +39,27 @@ template <> __device__ __forceinline__ float kv_load<__half>(const __half *p) { 
 template <typename T> __device__ __forceinline__ T kv_make(float v);
 template <> __device__ __forceinline__ float kv_make<float>(float v) { return v; }
 template <> __device__ __forceinline__ __half kv_make<__half>(float v) { return __float2half_rn(v); }
+
+// E consecutive cache elements (E = 2 or 4) as one load
+template <typename T, int E> __device__ __forceinline__ void kv_load_vec(const T *p, float (&o)[E]);
+template <> __device__ __forceinline__ void kv_load_vec<float, 2>(const float *p, float (&o)[2]) {
+    const float2 v = __ldcg((const float2 *)p);
+    o[0] = v.x, o[1] = v.y;
+}
+template <> __device__ __forceinline__ void kv_load_vec<float, 4>(const float *p, float (&o)[4]) {
+    const float4 v = __ldcg((const float4 *)p);
+    o[0] = v.x, o[1] = v.y, o[2] = v.z, o[3] = v.w;
+}
+template <> __device__ __forceinline__ void kv_load_vec<__half, 2>(const __half *p, float (&o)[2]) {
+    const unsigned v = __ldcg((const unsigned *)p);
+    const float2 f = __half22float2(*(const __half2 *)&v);
+    o[0] = f.x, o[1] = f.y;
+}
+template <> __device__ __forceinline__ void kv_load_vec<__half, 4>(const __half *p, float (&o)[4]) {
+    const uint2 v = __ldcg((const uint2 *)p);
+    const float2 a = __half22float2(*(const __half2 *)&v.x), b = __half22float2(*(const __half2 *)&v.y);
+    o[0] = a.x, o[1] = a.y, o[2] = b.x, o[3] = b.y;
+}
 
 struct AttnParams {
     const float *q, *knew, *vnew; // projections of the new token (before RoPE)
@@ -175,6 +199,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     for (int h = 0; h < KVMUL; ++h)
 #pragma unroll
         for (int e = 0; e < E; ++e) qr[h][e] = qs[h][lane * E + e];
+    // The values of this warp's positions (warp, warp + 4, ...: at most ATT_CHUNK / 4) are requested now, beside the
+    // keys: they do not depend on the scores, and one trip to memory is saved.
+    constexpr int VPW = ATT_CHUNK / 4;
+    float vpre[VPW][E];
+#pragma unroll
+    for (int i = 0; i < VPW; ++i) {
+        const int pp = min(p0 + warp + 4 * i, p1 - 1);
+        kv_load_vec<KV_T, E>(vc + (size_t)pp * p.kv_dim + kvh * HD + lane * E, vpre[i]);
+    }
     for (int b0 = warp * PB; b0 < np; b0 += 4 * PB) {
         float v[32];
 #pragma unroll
@@ -182,8 +215,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
             const int pp = min(p0 + b0 + j, p1 - 1);
             const KV_T *kp = kc + (size_t)pp * p.kv_dim + kvh * HD + lane * E;
             float kk[E];
-#pragma unroll
-            for (int e = 0; e < E; ++e) kk[e] = kv_load<KV_T>(kp + e);
+            kv_load_vec<KV_T, E>(kp, kk);
 #pragma unroll
             for (int h = 0; h < KVMUL; ++h) {
                 float s = 0.f;
@@ -220,17 +252,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     for (int h = 0; h < KVMUL; ++h)
 #pragma unroll
         for (int e = 0; e < E; ++e) acc[h][e] = 0.f;
-#pragma unroll 4
-    for (int i = warp; i < np; i += 4) {
-        const KV_T *vp = vc + (size_t)(p0 + i) * p.kv_dim + kvh * HD + lane * E;
-        float vv[E];
 #pragma unroll
-        for (int e = 0; e < E; ++e) vv[e] = kv_load<KV_T>(vp + e);
+    for (int i = 0; i < VPW; ++i) {
+        if (warp + 4 * i < np) {
 #pragma unroll
-        for (int h = 0; h < KVMUL; ++h) {
-            const float a = sc[h][i];
+            for (int h = 0; h < KVMUL; ++h) {
+                const float a = sc[h][warp + 4 * i];
 #pragma unroll
-            for (int e = 0; e < E; ++e) acc[h][e] += a * vv[e];
+                for (int e = 0; e < E; ++e) acc[h][e] += a * vpre[i][e];
+            }
         }
     }
 #pragma unroll
@@ -238,6 +268,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
 #pragma unroll
         for (int e = 0; e < E; ++e) red[warp][h][lane * E + e] = acc[h][e];
     __syncthreads();
+    if (n_active == 1) {
+        // one split holds the whole context: its partial is the answer, no merge and no hand-over through memory
+        for (int i = tid; i < KVMUL * HD; i += 128) {
+            const int h = i / HD, d = i % HD;
+            p.out[(size_t)(kvh * KVMUL + h) * HD + d] = (red[0][h][d] + red[1][h][d] + red[2][h][d] + red[3][h][d]) * (1.0f / ml[h][1]);
+        }
+        return;
+    }
     float *mine = p.partial + ((size_t)(kvh * p.n_split + sp) * KVMUL) * (HD + 2);
     for (int i = tid; i < KVMUL * HD; i += 128) {
         const int h = i / HD, d = i % HD;
@@ -257,25 +295,29 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // merge the splits: w[h][s] = exp(m_s - M) / L first (all loads independent), then
-    // one pass over the partial outputs
+    // merge the splits: w[h][s] = exp(m_s - M) * (1 / L), L = sum_s l_s exp(m_s - M).  The (m, l) pairs of all
+    // splits come in with one 8-byte load each (all independent), one warp per head reduces them, then one
+    // pass over the partial outputs.
     const float *base = p.partial + ((size_t)kvh * p.n_split * KVMUL) * (HD + 2);
-    __shared__ float wgt[KVMUL][ATT_MAX_CTX / ATT_CHUNK];
+    __shared__ float wgt[KVMUL][ATT_MAX_CTX / ATT_CHUNK], lsum[KVMUL][ATT_MAX_CTX / ATT_CHUNK];
     for (int i = tid; i < KVMUL * n_active; i += 128) {
         const int h = i / n_active, s2 = i % n_active;
-        wgt[h][s2] = __ldcg(base + ((size_t)s2 * KVMUL + h) * (HD + 2) + HD);
+        const float2 v = __ldcg((const float2 *)(base + ((size_t)s2 * KVMUL + h) * (HD + 2) + HD));
+        wgt[h][s2] = v.x, lsum[h][s2] = v.y;
     }
     __syncthreads();
-    if (tid < KVMUL) {
+    for (int h = warp; h < KVMUL; h += 4) {
         float M = -INFINITY, L = 0.f;
-        for (int s2 = 0; s2 < n_active; ++s2) M = fmaxf(M, wgt[tid][s2]);
-        for (int s2 = 0; s2 < n_active; ++s2) {
-            const float w = expf(wgt[tid][s2] - M);
-            L += __ldcg(base + ((size_t)s2 * KVMUL + tid) * (HD + 2) + HD + 1) * w;
-            wgt[tid][s2] = w;
+        for (int s2 = lane; s2 < n_active; s2 += 32) M = fmaxf(M, wgt[h][s2]);
+        M = warp_max(M);
+        for (int s2 = lane; s2 < n_active; s2 += 32) {
+            const float w = expf(wgt[h][s2] - M);
+            L += lsum[h][s2] * w;
+            wgt[h][s2] = w;
         }
+        L = warp_sum(L);
         const float invL = 1.0f / L;
-        for (int s2 = 0; s2 < n_active; ++s2) wgt[tid][s2] *= invL;
+        for (int s2 = lane; s2 < n_active; s2 += 32) wgt[h][s2] *= invL;
     }
     __syncthreads();
     for (int i = tid; i < KVMUL * HD; i += 128) {
