@@ -320,12 +320,33 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
         for (int s2 = lane; s2 < n_active; s2 += 32) wgt[h][s2] *= invL;
     }
     __syncthreads();
-    for (int i = tid; i < KVMUL * HD; i += 128) {
-        const int h = i / HD, d = i % HD;
-        float o = 0.f;
-#pragma unroll 8
-        for (int s2 = 0; s2 < n_active; ++s2) o += __ldcg(base + ((size_t)s2 * KVMUL + h) * (HD + 2) + d) * wgt[h][s2];
-        p.out[(size_t)(kvh * KVMUL + h) * HD + d] = o;
+    // every thread's outputs together, SU splits per batch: OPT * SU independent loads in flight instead of 8
+    constexpr int NOUT = KVMUL * HD, OPT = (NOUT + 127) / 128, SU = OPT <= 2 ? 16 : 8;
+    float o[OPT];
+#pragma unroll
+    for (int k = 0; k < OPT; ++k) o[k] = 0.f;
+    for (int s0 = 0; s0 < n_active; s0 += SU) {
+        float v[OPT][SU];
+#pragma unroll
+        for (int u = 0; u < SU; ++u) {
+            const int s2 = min(s0 + u, n_active - 1);
+#pragma unroll
+            for (int k = 0; k < OPT; ++k) {
+                const int i = min(tid + 128 * k, NOUT - 1), h = i / HD, d = i % HD;
+                v[k][u] = __ldcg(base + ((size_t)s2 * KVMUL + h) * (HD + 2) + d);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < SU; ++u)
+            if (s0 + u < n_active) {
+#pragma unroll
+                for (int k = 0; k < OPT; ++k) o[k] += v[k][u] * wgt[min(tid + 128 * k, NOUT - 1) / HD][s0 + u];
+            }
+    }
+#pragma unroll
+    for (int k = 0; k < OPT; ++k) {
+        const int i = tid + 128 * k, h = i / HD, d = i % HD;
+        if (i < NOUT) p.out[(size_t)(kvh * KVMUL + h) * HD + d] = o[k];
     }
 }
 
