@@ -355,42 +355,61 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
 // ---------------------------------------------------------------------------
 // Greedy sampling (crates/ullm-model/src/sample.rs:125-133: first index wins ties)
 // and the bookkeeping that lets the next graph replay run without the host.
-__global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restrict__ logits, int n, uint32_t *token,
-                                                          int *pos, int *step, uint32_t *tokens_out, int max_steps) {
-    __shared__ float bvs[32];
-    __shared__ int bis[32];
+constexpr int ARGMAX_CTAS = 32;
+__global__ void __launch_bounds__(256) argmax_step_kernel(const float *__restrict__ logits, int n, uint32_t *token, int *pos, int *step,
+                                                         uint32_t *tokens_out, int max_steps, float2 *part, unsigned *counter) {
+    __shared__ float bvs[8];
+    __shared__ int bis[8];
+    __shared__ bool is_last;
     pdl_wait_prior();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < n; i += 1024) {
-        const float v = logits[i];
-        if (v > bv || (v == bv && i < bi)) bv = v, bi = i;
+    auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
+    // each CTA scans a contiguous slice; the candidates meet in memory and the last CTA to arrive decides
+    const int per = (n + gridDim.x - 1) / gridDim.x, i0 = blockIdx.x * per, i1 = min(n, i0 + per);
+    for (int i = i0 + tid; i < i1; i += 256) {
+        const float v = __ldcg(logits + i);
+        if (better(v, i, bv, bi)) bv = v, bi = i;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+        if (better(ov, oi, bv, bi)) bv = ov, bi = oi;
     }
     if (lane == 0) bvs[warp] = bv, bis[warp] = bi;
     __syncthreads();
-    if (warp == 0) {
-        bv = bvs[lane], bi = bis[lane];
+    if (tid == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (better(bvs[w], bis[w], bv, bi)) bv = bvs[w], bi = bis[w];
+        part[blockIdx.x] = make_float2(bv, __int_as_float(bi));
+        __threadfence();
+        const unsigned t = atomicAdd(counter, 1u);
+        is_last = t == gridDim.x - 1;
+        if (is_last) *counter = 0u; // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last || warp != 0) return;
+    __threadfence();
+    bv = -INFINITY, bi = 0x7fffffff;
+    for (int c = lane; c < (int)gridDim.x; c += 32) {
+        const float2 v = __ldcg(part + c);
+        if (better(v.x, __float_as_int(v.y), bv, bi)) bv = v.x, bi = __float_as_int(v.y);
+    }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
-        }
-        if (lane == 0) {
-            if (bi == 0x7fffffff) bi = 0; // all NaN / -inf: the reference keeps index 0
-            *token = (uint32_t)bi;
-            const int s = *step;
-            if (s < max_steps) tokens_out[s] = (uint32_t)bi;
-            *step = s + 1;
-            *pos = *pos + 1;
-        }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) bv = ov, bi = oi;
+    }
+    if (lane == 0) {
+        if (bi == 0x7fffffff) bi = 0; // all NaN / -inf: the reference keeps index 0
+        *token = (uint32_t)bi;
+        const int s = *step;
+        if (s < max_steps) tokens_out[s] = (uint32_t)bi;
+        *step = s + 1;
+        *pos = *pos + 1;
     }
 }
 
@@ -680,8 +699,9 @@ cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardP
     }
     TRY(dev_alloc((void **)&logits, P.vocab * 4));
     TRY(dev_alloc((void **)&partial, P.n_kv_head * n_split * (P.n_head / P.n_kv_head) * (hd + 2) * 4));
-    TRY(dev_alloc((void **)&counters, P.n_kv_head * 4));
-    TRY(cudaMemsetAsync(counters, 0, P.n_kv_head * 4, stream));
+    TRY(dev_alloc((void **)&counters, (P.n_kv_head + 1) * 4)); // one per kv head (attention) + one for the argmax
+    TRY(cudaMemsetAsync(counters, 0, (P.n_kv_head + 1) * 4, stream));
+    TRY(dev_alloc((void **)&argmax_part, ARGMAX_CTAS * sizeof(float2)));
     TRY(dev_alloc((void **)&chain_sync, 256));
     TRY(cudaMemsetAsync(chain_sync, 0, 256, stream));
     TRY(dev_alloc((void **)&state, 64)); // [0] pos, [1] token, [2] step
@@ -803,14 +823,14 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
     TRY(mv(output, x, logits, final_norm, EPI_STORE, nullptr));
     if (mode == 1) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(1), cfg.blockDim = dim3(1024), cfg.stream = stream;
+        cfg.gridDim = dim3(ARGMAX_CTAS), cfg.blockDim = dim3(256), cfg.stream = stream;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
         cudaFuncSetAttribute(argmax_step_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         TRY(cudaLaunchKernelEx(&cfg, argmax_step_kernel, (const float *)logits, (int)P.vocab, tok_ptr, pos_ptr, step_ptr,
-                               tokens_out, (int)MAX_GREEDY));
+                               tokens_out, (int)MAX_GREEDY, (float2 *)argmax_part, counters + P.n_kv_head));
         ++launches;
     }
 #undef TRY

@@ -71,6 +71,7 @@ struct Forward {
     float *x = nullptr, *xb = nullptr, *qk = nullptr, *vbuf = nullptr, *attn = nullptr, *hidden = nullptr, *gate = nullptr,
           *up = nullptr, *logits = nullptr, *partial = nullptr;
     unsigned *counters = nullptr;
+    void *argmax_part = nullptr; // per-CTA candidates of the greedy argmax
     void *state = nullptr; // device ints: [0] pos, [1] token, [2] step
     uint32_t *tokens_out = nullptr;
     void *h_pin = nullptr;
