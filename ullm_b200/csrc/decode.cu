@@ -61,6 +61,10 @@ template <> __device__ __forceinline__ void kv_load_vec<__half, 4>(const __half 
     o[0] = a.x, o[1] = a.y, o[2] = b.x, o[3] = b.y;
 }
 
+template <typename T> __device__ __forceinline__ float kv_f(T v);
+template <> __device__ __forceinline__ float kv_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float kv_f<__half>(__half v) { return __half2float(v); }
+
 struct AttnParams {
     const float *q, *knew, *vnew; // projections of the new token (before RoPE)
     void *kcache, *vcache;        // this layer: [n_ctx][kv_dim]
@@ -152,6 +156,27 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     KV_T *kc = (KV_T *)p.kcache, *vc = (KV_T *)p.vcache;
     const float2 *rp = p.rope + (size_t)pos * (HD / 2);
 
+    // The cache rows of this CTA's positions are requested before anything else: keys of the warp's score batches
+    // and values of the warp's positions (warp, warp + 4, ...), so that their trip to memory overlaps the work on
+    // the new token below.  The row of `pos` itself is written by this kernel: what is read of it here is stale and
+    // is replaced from shared memory (kn / vn, rounded as the cache rounds) where it is used.
+    constexpr int NB = (KVMUL + 3) / 4, VPW = ATT_CHUNK / 4; // score batches per warp, values per warp
+    float kpre[NB][PB][E], vpre[VPW][E];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int j = 0; j < PB; ++j) {
+            const int pp = min(p0 + (warp + 4 * nb) * PB + j, p1 - 1);
+            kv_load_vec<KV_T, E>(kc + (size_t)pp * p.kv_dim + kvh * HD + lane * E, kpre[nb][j]);
+        }
+#pragma unroll
+    for (int i = 0; i < VPW; ++i) {
+        const int pp = min(p0 + warp + 4 * i, p1 - 1);
+        kv_load_vec<KV_T, E>(vc + (size_t)pp * p.kv_dim + kvh * HD + lane * E, vpre[i]);
+    }
+    const bool owns_pos = sp == n_active - 1;
+    __shared__ float vn[HD];
+
     // the new token's q heads of this kv head (and, in the CTA that owns `pos`, its k and v): bias,
     // per-head norm and RoPE as the model asks, then the cache write
     __shared__ float kn[HD];
@@ -166,28 +191,37 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
             qs[h][2 * j] = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
             qs[h][2 * j + 1] = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
         }
-        if (sp == n_active - 1) {
+        if (owns_pos) {
             for (int j = tid; j < HD / 2; j += 128) {
                 const float *kp = p.knew + (size_t)kvh * HD + 2 * j;
                 const float a = kp[0], b = kp[1];
                 const float2 cs = rp[j];
                 KV_T *dst = kc + (size_t)pos * p.kv_dim + kvh * HD + 2 * j;
-                dst[0] = kv_make<KV_T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
-                dst[1] = kv_make<KV_T>(__fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)));
+                const KV_T r0 = kv_make<KV_T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
+                const KV_T r1 = kv_make<KV_T>(__fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)));
+                dst[0] = r0, dst[1] = r1;
+                kn[2 * j] = kv_f<KV_T>(r0), kn[2 * j + 1] = kv_f<KV_T>(r1);
             }
-            for (int j = tid; j < HD; j += 128)
-                vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(p.vnew[(size_t)kvh * HD + j]);
+            for (int j = tid; j < HD; j += 128) {
+                const KV_T r = kv_make<KV_T>(p.vnew[(size_t)kvh * HD + j]);
+                vc[(size_t)pos * p.kv_dim + kvh * HD + j] = r;
+                vn[j] = kv_f<KV_T>(r);
+            }
         }
     } else {
         for (int h = warp; h < KVMUL; h += 4)
             head_prepare<HD>(p.q + (size_t)(kvh * KVMUL + h) * HD, p.q_bias ? p.q_bias + (size_t)(kvh * KVMUL + h) * HD : nullptr,
                              p.q_norm, p.eps, rp, p.neox, qs[h], lane);
-        if (sp == n_active - 1 && warp == 3) {
+        if (owns_pos && warp == 3) {
             head_prepare<HD>(p.knew + (size_t)kvh * HD, p.k_bias ? p.k_bias + (size_t)kvh * HD : nullptr, p.k_norm, p.eps, rp, p.neox, kn, lane);
             for (int j = lane; j < HD; j += 32) {
-                kc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(kn[j]);
+                const KV_T rk = kv_make<KV_T>(kn[j]);
+                kc[(size_t)pos * p.kv_dim + kvh * HD + j] = rk;
+                kn[j] = kv_f<KV_T>(rk);
                 const float vv = p.vnew[(size_t)kvh * HD + j] + (p.v_bias ? p.v_bias[(size_t)kvh * HD + j] : 0.f);
-                vc[(size_t)pos * p.kv_dim + kvh * HD + j] = kv_make<KV_T>(vv);
+                const KV_T rv = kv_make<KV_T>(vv);
+                vc[(size_t)pos * p.kv_dim + kvh * HD + j] = rv;
+                vn[j] = kv_f<KV_T>(rv);
             }
         }
     }
@@ -199,23 +233,17 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     for (int h = 0; h < KVMUL; ++h)
 #pragma unroll
         for (int e = 0; e < E; ++e) qr[h][e] = qs[h][lane * E + e];
-    // The values of this warp's positions (warp, warp + 4, ...: at most ATT_CHUNK / 4) are requested now, beside the
-    // keys: they do not depend on the scores, and one trip to memory is saved.
-    constexpr int VPW = ATT_CHUNK / 4;
-    float vpre[VPW][E];
 #pragma unroll
-    for (int i = 0; i < VPW; ++i) {
-        const int pp = min(p0 + warp + 4 * i, p1 - 1);
-        kv_load_vec<KV_T, E>(vc + (size_t)pp * p.kv_dim + kvh * HD + lane * E, vpre[i]);
-    }
-    for (int b0 = warp * PB; b0 < np; b0 += 4 * PB) {
+    for (int nb = 0; nb < NB; ++nb) {
+        const int b0 = (warp + 4 * nb) * PB;
+        if (b0 >= np) break;
         float v[32];
 #pragma unroll
         for (int j = 0; j < PB; ++j) {
             const int pp = min(p0 + b0 + j, p1 - 1);
-            const KV_T *kp = kc + (size_t)pp * p.kv_dim + kvh * HD + lane * E;
             float kk[E];
-            kv_load_vec<KV_T, E>(kp, kk);
+#pragma unroll
+            for (int e = 0; e < E; ++e) kk[e] = owns_pos && pp == pos ? kn[lane * E + e] : kpre[nb][j][e];
 #pragma unroll
             for (int h = 0; h < KVMUL; ++h) {
                 float s = 0.f;
@@ -259,7 +287,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
             for (int h = 0; h < KVMUL; ++h) {
                 const float a = sc[h][warp + 4 * i];
 #pragma unroll
-                for (int e = 0; e < E; ++e) acc[h][e] += a * vpre[i][e];
+                for (int e = 0; e < E; ++e) acc[h][e] += a * (owns_pos && p0 + warp + 4 * i == pos ? vn[lane * E + e] : vpre[i][e]);
             }
         }
     }
@@ -321,7 +349,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     }
     __syncthreads();
     // every thread's outputs together, SU splits per batch: OPT * SU independent loads in flight instead of 8
-    constexpr int NOUT = KVMUL * HD, OPT = (NOUT + 127) / 128, SU = OPT <= 2 ? 16 : 8;
+    constexpr int NOUT = KVMUL * HD, OPT = (NOUT + 127) / 128, SU = OPT <= 2 ? 40 : 8;
     float o[OPT];
 #pragma unroll
     for (int k = 0; k < OPT; ++k) o[k] = 0.f;
