@@ -223,3 +223,29 @@ def test_decode_variants_bias_qknorm_neox(ctx, bias, qk_norm, neox, kv_f16):
         tok = oracle.argmax(ref)
     assert differs
     gf.free(), base.free()
+
+
+@pytest.mark.parametrize("hd,n_head,n_kv_head,variant", [(128, 8, 1, False), (128, 2, 2, False), (64, 4, 4, False), (64, 8, 1, False),
+                                                         (128, 4, 1, True), (128, 8, 1, True)])
+def test_attention_head_shapes_with_a_multi_split_context(ctx, hd, n_head, n_kv_head, variant):
+    """Every head geometry the attention kernel is instantiated for (head_dim 64 / 128, 1 to 8 query heads per
+    KV head), on a context that spans several 32-position splits, so that the split merge runs; ``variant`` adds
+    the per-head Q/K norm and rotate-half RoPE (the Qwen3 path)."""
+    p = dict(synth.LLAMA_TINY, head_dim=hd, n_head=n_head, n_kv_head=n_kv_head, n_ctx=160)
+    m = variant_model(p, 41, False, variant)
+    mk = lambda t: oracle.Weight(t[0], t[1], t[2], t[3])
+    layers = [{k: (mk(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in m["layers"]]
+    n_pre = 70
+    k, v = synth.gen_kv_prefill(p, n_pre, 77)
+    for kv_f16 in (True, False):
+        om = oracle.LlamaModel(m["params"], mk(m["tok_embd"]), mk(m["output"]), m["final_norm"], layers, kv_f16, rope_neox=variant)
+        om.key_cache[:, :n_pre], om.val_cache[:, :n_pre] = k, v  # values that are exact in f16
+        gf = backend.GpuForward(ctx, m, kv_f16=kv_f16, rope_neox=1 if variant else 0, qk_norm=1 if variant else 0)
+        gf.set_kv(0, k, v)
+        tok = 5
+        for pos in range(n_pre, n_pre + 5):
+            ref = om.forward(tok, pos)
+            got = gf.forward(om.embed(tok), pos)
+            assert synth.rel_err(got, ref) < 1e-3, (kv_f16, pos)
+            tok = oracle.argmax(ref)
+        gf.free()

@@ -832,11 +832,18 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
         if (L.moe) {
             // forward.rs:484-494: normalised x -> router logits -> top-k -> the selected experts' SwiGLU FFNs,
             // weighted by the softmax over the selected logits -> added to x
-            rmsnorm_vec_kernel<<<1, 256, 0, stream>>>(x, L.ffn_norm, P.eps, (int)P.n_embd, xb);
-            ++launches;
-            TRY(mv(L.moe_gate, xb, moe_logits, nullptr, EPI_STORE, nullptr));
-            TRY(launch_moe_ffn(dev, L.experts, xb, moe_logits, 1, P.n_experts_used, x, nullptr, nullptr, moe_scratch, d_status, stream, false,
-                               use_pdl, nullptr, x));
+            // router and experts both normalise x themselves (fused prologues); shapes outside the streamed kernels
+            // go through a normalised copy instead
+            TRY(mv(L.moe_gate, x, moe_logits, L.ffn_norm, EPI_STORE, nullptr));
+            e = launch_moe_ffn(dev, L.experts, x, moe_logits, 1, P.n_experts_used, x, nullptr, nullptr, moe_scratch, d_status, stream, false,
+                               use_pdl, nullptr, x, L.ffn_norm, P.eps);
+            if (e == cudaErrorNotSupported) {
+                rmsnorm_vec_kernel<<<1, 256, 0, stream>>>(x, L.ffn_norm, P.eps, (int)P.n_embd, xb);
+                ++launches;
+                e = launch_moe_ffn(dev, L.experts, xb, moe_logits, 1, P.n_experts_used, x, nullptr, nullptr, moe_scratch, d_status, stream,
+                                   false, use_pdl, nullptr, x);
+            }
+            TRY(e);
             launches += 4; // route, gate|up, down, combine (+ residual)
             TRY(cudaGetLastError());
             continue;

@@ -117,6 +117,8 @@ const char *moe_shape_error(const MoeExperts &e, size_t n_tok, size_t k);
 cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const float *d_x, const float *d_logits,
                            size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *d_scratch,
                            int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out,
-                           const float *d_res = nullptr); // d_res: [n_tok, hidden] added to the result (may alias d_y)
+                           const float *d_res = nullptr, // [n_tok, hidden] added to the result (may alias d_y)
+                           const float *d_norm_w = nullptr, float eps = 0.f); // RMSNorm of x inside the gate|up kernel (streamed path only:
+                                                                               // cudaErrorNotSupported otherwise, nothing launched but the routing)
 
 } // namespace ullm

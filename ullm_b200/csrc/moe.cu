@@ -137,6 +137,8 @@ struct MoeStreamParams {
     // matrices of this launch: NM = 2 (gate, up) or 1 (down); stacked over experts
     const uint8_t *w[2], *sc[2], *bi[2];
     const float *act;  // gate_up: x [n_tok, in]; down: hidden [n_pairs, in]
+    const float *norm_w; // gate_up only, may be null: RMSNorm weight applied to x first (x * inv * w, math.rs:82-86)
+    float eps;
     float *out;        // gate_up: hidden [n_pairs, rows]; down: down_out [n_pairs, rows]
     const int *route;
     int *status;
@@ -244,10 +246,32 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     const uint32_t pg_thr = max(32u, (nthr_c / max(1u, GATE_UP ? p.n_tok : 4u)) & ~31u), pg_n = nthr_c / pg_thr;
     const uint32_t pg = tid / pg_thr, pg_tid = tid % pg_thr; // pg >= pg_n: a leftover warp, idle here
     if (GATE_UP) {
-        // every token's x, once per CTA
-        for (uint32_t t = pg; t < p.n_tok && pg < pg_n; t += pg_n)
-            prep_image<FMT_MLX4>(ActSrc{p.act + (size_t)t * p.in_dim, nullptr, 0.f}, p.in_dim,
-                                 qimg + (size_t)t * p.ncg * XR * 32, pg_tid, pg_thr);
+        // every token's x, once per CTA; with a norm weight the vector is RMS-normalised on the way (every CTA
+        // recomputes the few KB's mean square, which saves a kernel in front of this one)
+        float *ss_s = (float *)(u_s + 2); // 32 floats behind the unit bounds
+        if (p.norm_w) {
+            float ss = 0.f;
+            for (uint32_t t = pg; t < p.n_tok && pg < pg_n; t += pg_n) { // n_tok <= pg_n: at most one token per group
+                const float4 *xv = (const float4 *)(p.act + (size_t)t * p.in_dim);
+                for (uint32_t i = pg_tid; i < p.in_dim / 4; i += pg_thr) {
+                    const float4 a = __ldg(xv + i);
+                    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) ss_s[warp] = ss;
+            asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
+        }
+        for (uint32_t t = pg; t < p.n_tok && pg < pg_n; t += pg_n) {
+            float inv = 0.f;
+            if (p.norm_w) {
+                float tot = 0.f;
+                for (uint32_t w = pg * (pg_thr / 32); w < (pg + 1) * (pg_thr / 32); ++w) tot += ss_s[w];
+                inv = 1.0f / sqrtf(tot / (float)p.in_dim + p.eps);
+            }
+            prep_image<FMT_MLX4>(ActSrc{p.act + (size_t)t * p.in_dim, p.norm_w, inv}, p.in_dim, qimg + (size_t)t * p.ncg * XR * 32, pg_tid,
+                                 pg_thr);
+        }
         asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
     }
 
@@ -396,7 +420,7 @@ static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, u
     const uint32_t NW = 16;
     const int budget = dev.max_smem_optin - 1024;
     const uint32_t off_route = 128; // routing table + the CTA's two unit bounds
-    const uint32_t off_q = align_up(off_route + ((uint32_t)route_off_pairs((int)n_exp) + MOE_MAX_TOK * MOE_MAX_K + 2) * 4, 128);
+    const uint32_t off_q = align_up(off_route + ((uint32_t)route_off_pairs((int)n_exp) + MOE_MAX_TOK * MOE_MAX_K + 2 + 32) * 4, 128); // + per-warp sums of squares
     const uint32_t off_ring = align_up(off_q + n_vec * ncg * XREGS_MLX * 32 * 4, 128);
     for (uint32_t RW = 1; RW <= 4; RW *= 2) {
         const uint32_t R = NW * RW;
@@ -465,7 +489,8 @@ const char *moe_shape_error(const MoeExperts &e, size_t n_tok, size_t k) {
 
 cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const float *d_x, const float *d_logits,
                            size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *d_scratch,
-                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out, const float *d_res) {
+                           int *d_status, cudaStream_t st, bool force_generic, bool pdl, int *streamed_out, const float *d_res,
+                           const float *d_norm_w, float eps) {
     // scratch carve-up
     const size_t pairs_cap = (size_t)MOE_MAX_TOK * MOE_MAX_K;
     uint8_t *sp = (uint8_t *)d_scratch;
@@ -498,18 +523,19 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
             MoeStreamParams &a = pg.p;
             a.w[0] = (const uint8_t *)e.gate_w, a.sc[0] = (const uint8_t *)e.gate_s, a.bi[0] = (const uint8_t *)e.gate_b;
             a.w[1] = (const uint8_t *)e.up_w, a.sc[1] = (const uint8_t *)e.up_s, a.bi[1] = (const uint8_t *)e.up_b;
-            a.act = x, a.out = hidden, a.route = route, a.status = d_status;
+            a.act = x, a.norm_w = d_norm_w, a.eps = eps, a.out = hidden, a.route = route, a.status = d_status;
             a.n_exp = (uint32_t)e.n_experts, a.k = (uint32_t)k, a.n_tok = nt;
             err = tb == 2 ? launch_moe_g<true, uint16_t>(pg, st, pdl) : launch_moe_g<true, float>(pg, st, pdl);
             if (err != cudaSuccess) return err;
             MoeStreamParams &b = pd.p;
             b.w[0] = (const uint8_t *)e.down_w, b.sc[0] = (const uint8_t *)e.down_s, b.bi[0] = (const uint8_t *)e.down_b;
             b.w[1] = nullptr, b.sc[1] = nullptr, b.bi[1] = nullptr;
-            b.act = hidden, b.out = down, b.route = route, b.status = d_status;
+            b.act = hidden, b.norm_w = nullptr, b.eps = 0.f, b.out = down, b.route = route, b.status = d_status;
             b.n_exp = (uint32_t)e.n_experts, b.k = (uint32_t)k, b.n_tok = nt;
             err = tb == 2 ? launch_moe_g<false, uint16_t>(pd, st, pdl) : launch_moe_g<false, float>(pd, st, pdl);
             if (err != cudaSuccess) return err;
         } else {
+            if (d_norm_w) return cudaErrorNotSupported; // the plain kernels take the vector as it is
             dim3 g1((unsigned)((e.inter + 7) / 8), npairs), g2((unsigned)((e.hidden + 7) / 8), npairs);
             if (tb == 2) {
                 moe_gather_kernel<true, uint16_t><<<g1, 256, 0, st>>>(
