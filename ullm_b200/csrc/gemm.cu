@@ -45,10 +45,14 @@ constexpr int G_STAGES = 8;  // operand stages in flight: one dequantized weight
 constexpr int G_A_COLS = GKC / 2;         // a weight chunk in tensor memory: 64 bf16 per row = 32 columns of 32 bit
 constexpr int G_TMEM_COLS = 512;          // accumulator (256) + 8 weight chunks (8 x 32)
 constexpr int G_B_BYTES = GNH * GKC * 2;  // 16 KB
-constexpr int G_THREADS = 384;
-constexpr int G_MMA_WARP = 11;
-constexpr int G_DEQ_WARPS = 8;
-constexpr int G_RAW_WARP = 10;
+// Warps: 0 activation TMA, 1 tensor-memory allocation, 2..17 dequantization, 18 weight-byte TMA, 19 MMA issue.
+// A warp reaches only the tensor-memory lanes 32 * (warp % 4) .., so every row quarter has four dequantization
+// warps: two column parts x two phases.  A phase takes every other 64-k chunk, which gives a warp two chunk
+// periods for its wait -> unpack -> tcgen05.st -> arrive chain instead of one.
+constexpr int G_THREADS = 640;
+constexpr int G_MMA_WARP = 19;
+constexpr int G_DEQ_WARPS = 16;
+constexpr int G_RAW_WARP = 18;
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B apart
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -324,7 +328,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
 
     if (tid == 0) {
         for (int i = 0; i < G_STAGES; ++i) {
-            mbar_init(&full[i], 2 * G_DEQ_WARPS + 1);
+            mbar_init(&full[i], G_DEQ_WARPS + 1); // per chunk one phase of both CTAs arrives: 2 x 8 warps, + the expect_tx arrival
             mbar_init(&freeb[i], 1);
         }
         for (int i = 0; i < RS; ++i) {
@@ -471,7 +475,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
     } else {
         // ---- dequantization: all 256 threads work on one 64-k chunk at a time ----
         // a warp reaches only its own quarter of the tensor-memory lanes: row = lane of that quarter
-        const uint32_t dt = tid - 64, lq = warp & 3, row = lq * 32 + lane, part = (warp - 2) >> 2;
+        const uint32_t dt = tid - 64, lq = warp & 3, row = lq * 32 + lane, part = ((warp - 2) >> 2) & 1, phase = (warp - 2) >> 3;
         const uint32_t ta_lane = tmem_d + ((lq * 32u) << 16) + GN;
         bool ok = true;
         for (uint32_t kb = 0; kb < nb && ok; ++kb) {
@@ -484,6 +488,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
             if (lane == 0) mbar_arrive(&raw_free[st]); // the block's bytes are in registers: its stage can be refilled
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
+                if ((uint32_t)(c & 1) != phase) continue; // the other phase's chunk
                 const uint32_t g = 4 * kb + c, ca = g % G_STAGES;
                 const bool tr = traced && g < 1024 && dt == 0;
                 if (tr) p.trace[4096 + 4 * g] = clock64();
@@ -508,11 +513,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         // ---- epilogue: TMEM -> registers -> Y[token, row] ----
         if (ok && warp_wait(&acc_full, 0, lane)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t q = warp & 3, colh = (warp - 2) >> 2; // TMEM lane quarter of this warp, column half
+            const uint32_t q = warp & 3, colq = (warp - 2) >> 2; // TMEM lane quarter of this warp, column quarter
             const uint32_t orow = m0 + q * 32 + lane;
 #pragma unroll 1
-            for (uint32_t cb = 0; cb < 4; ++cb) {
-                const uint32_t col0 = colh * 128 + cb * 32;
+            for (uint32_t cb = 0; cb < 2; ++cb) {
+                const uint32_t col0 = colq * 64 + cb * 32;
                 uint32_t v[32];
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
