@@ -14,21 +14,24 @@
 // the mbarriers that recycle the operand stages in both CTAs.  The epilogue reads the
 // accumulator back with tcgen05.ld and stores token-major f32.
 //
-// Roles in a CTA of 12 warps (a pair of CTAs on neighbouring SMs works on one tile):
+// Roles in a CTA of 20 warps (a pair of CTAs on neighbouring SMs works on one tile):
 //   warp 0      TMA: this CTA's half of the activation tile of every k-chunk, 8 stages
-//   warp 10     TMA: the packed weight bytes of [128 rows x 256 k] per block, 3-4 stages
 //   warp 1      tensor-memory allocation
-//   warp 11     MMA issue and commits (leader CTA of the pair only)
-//   warps 2-9   dequantization from the staged bytes into tensor memory (thread = one row
-//               = one TMEM lane; all 256 threads on one 64-k chunk at a time), then the epilogue
+//   warps 2-17  dequantization from the staged bytes into tensor memory (thread = one row = one TMEM
+//               lane; a warp reaches only lanes 32 * (warp % 4) .., so each row quarter has four warps:
+//               two column parts x two phases, a phase taking every other 64-k chunk), then the epilogue
+//   warp 18     TMA: the packed weight bytes of [128 rows x 256 k] per block, 3-4 stages
+//   warp 19     MMA issue and commits (leader CTA of the pair only)
 // Every mbarrier wait is bounded; on expiry the CTA records a status, stops issuing
 // work, still frees its tensor memory and leaves.
 //
-// Measured on B200 (cycle stamps of every warp's arrival): the two dequantization warps that
-// share a warp scheduler with the MMA-issuing thread finish each chunk last — issuing four
-// MMAs per chunk costs that scheduler about as many cycles as the warps' own work — and
-// set the pace; the schedulers hosting the TMA threads lose less.  The service warps are
-// therefore spread over three schedulers.
+// Measured on B200 (cycle stamps of every warp's arrival): with one warp per (row quarter, column part)
+// the two dequantization warps that share a warp scheduler with the MMA-issuing thread finished each
+// chunk last and set the pace: a warp's chain wait -> unpack -> tcgen05.st -> wait::st -> arrive is
+// long against the chunk period, and any slot lost to the service warp shows.  Two phases give every
+// warp two chunk periods for that chain (857 -> 938 TFLOP/s on the 70B block at 512 tokens); three
+// phases (Q4_K fits in 72 registers) bring nothing more.  The service warps sit on four different
+// schedulers.
 #include "kernels.h"
 #include "matvec_core.cuh"
 
@@ -45,14 +48,14 @@ constexpr int G_STAGES = 8;  // operand stages in flight: one dequantized weight
 constexpr int G_A_COLS = GKC / 2;         // a weight chunk in tensor memory: 64 bf16 per row = 32 columns of 32 bit
 constexpr int G_TMEM_COLS = 512;          // accumulator (256) + 8 weight chunks (8 x 32)
 constexpr int G_B_BYTES = GNH * GKC * 2;  // 16 KB
-// Warps: 0 activation TMA, 1 tensor-memory allocation, 2..17 dequantization, 18 weight-byte TMA, 19 MMA issue.
+// Warps: 0 activation TMA, 1 tensor-memory allocation, 2 .. 1 + 8 * PHASES dequantization, then weight-byte TMA, then MMA issue.
 // A warp reaches only the tensor-memory lanes 32 * (warp % 4) .., so every row quarter has four dequantization
-// warps: two column parts x two phases.  A phase takes every other 64-k chunk, which gives a warp two chunk
-// periods for its wait -> unpack -> tcgen05.st -> arrive chain instead of one.
-constexpr int G_THREADS = 640;
-constexpr int G_MMA_WARP = 19;
-constexpr int G_DEQ_WARPS = 16;
-constexpr int G_RAW_WARP = 18;
+// warps: two column parts x PHASES phases.  A phase takes every PHASES-th 64-k chunk, which gives a warp that many chunk
+// periods for its wait -> unpack -> tcgen05.st -> arrive chain instead of one (the format's register need caps it).
+constexpr int g_deq_warps(int phases) { return 8 * phases; }
+constexpr int g_raw_warp(int phases) { return 2 + 8 * phases; }
+constexpr int g_mma_warp(int phases) { return 3 + 8 * phases; }
+constexpr int g_threads(int phases) { return (4 + 8 * phases) * 32; }
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B apart
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -146,14 +149,19 @@ struct GemmMaps {
     CUtensorMap x, w0, w1, w2;
 };
 
+#ifndef PHASES_Q4K
+#define PHASES_Q4K 2
+#endif
 template <int FMT> struct GemmCfg;
 template <> struct GemmCfg<FMT_Q4K> {
     static constexpr int RAW_BYTES = GM * Q4K_BYTES; // [128 rows][144 B]: 16-byte reads one row apart hit distinct banks
+    static constexpr int PHASES = PHASES_Q4K;
     static constexpr int RAW_STAGES = 4;
 };
 template <> struct GemmCfg<FMT_Q6KR> {
     static constexpr int REC_BYTES = GM * 48;                  // one record of every row: [128][48 B], conflict-free as well
     static constexpr int RAW_BYTES = 4 * REC_BYTES + 2 * GM * 16; // 4 records, [128][16 B] scales, [128][16 B] d
+    static constexpr int PHASES = 2;
     static constexpr int RAW_STAGES = 3;
 };
 
@@ -300,11 +308,12 @@ template <> struct BlkOf<FMT_Q6KR> { using type = BlkQ6KR; };
 
 // grid (2 * ceil(out / 256), ceil(s / 256)) in clusters of 2 along x, 352 threads
 template <int FMT, bool DBG>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FMT>::PHASES), 1)
     gemm_q_tc_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
     using Cfg = GemmCfg<FMT>;
     using Blk = typename BlkOf<FMT>::type;
     constexpr int RS = Cfg::RAW_STAGES;
+    constexpr uint32_t PH = Cfg::PHASES;
     extern __shared__ __align__(1024) uint8_t gsm[];
     // dynamic smem is only guaranteed 16-byte aligned: round up to the 1024 B the swizzle atoms need
     // (the same amount in both CTAs of the pair, so operand offsets agree)
@@ -328,12 +337,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
 
     if (tid == 0) {
         for (int i = 0; i < G_STAGES; ++i) {
-            mbar_init(&full[i], G_DEQ_WARPS + 1); // per chunk one phase of both CTAs arrives: 2 x 8 warps, + the expect_tx arrival
+            mbar_init(&full[i], 16 + 1); // per chunk one phase of both CTAs arrives: 2 x 8 warps, + the expect_tx arrival
             mbar_init(&freeb[i], 1);
         }
         for (int i = 0; i < RS; ++i) {
             mbar_init(&raw_full[i], 1);
-            mbar_init(&raw_free[i], G_DEQ_WARPS);
+            mbar_init(&raw_free[i], g_deq_warps(PH));
         }
         mbar_init(&acc_full, 1);
         mbar_fence_init();
@@ -368,7 +377,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
                 if (traced && g < 500) p.trace[6000 + g] = clock64();
             }
         }
-    } else if (warp == G_RAW_WARP) {
+    } else if (warp == (uint32_t)g_raw_warp(PH)) {
         // ---- TMA producer: packed weight bytes of every 256-k block (rows past the matrix read as zero) ----
         if (lane == 0) {
             for (uint32_t kb = 0; kb < nb; ++kb) {
@@ -392,7 +401,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
         }
     } else if (warp == 1) {
         // (tensor-memory allocation warp: nothing in the main loop)
-    } else if (warp == G_MMA_WARP) {
+    } else if (warp == (uint32_t)g_mma_warp(PH)) {
         // ---- MMA issuer: one thread of the pair's leader CTA ----
         // Issuing four MMAs costs this thread most of the time the tensor pipe needs to run
         // them, so everything else is kept off its path: the test of the NEXT chunk's barrier
@@ -473,7 +482,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
             }
         }
     } else {
-        // ---- dequantization: all 256 threads work on one 64-k chunk at a time ----
+        // ---- dequantization: the 256 threads of a phase work on one 64-k chunk at a time ----
         // a warp reaches only its own quarter of the tensor-memory lanes: row = lane of that quarter
         const uint32_t dt = tid - 64, lq = warp & 3, row = lq * 32 + lane, part = ((warp - 2) >> 2) & 1, phase = (warp - 2) >> 3;
         const uint32_t ta_lane = tmem_d + ((lq * 32u) << 16) + GN;
@@ -488,8 +497,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
             if (lane == 0) mbar_arrive(&raw_free[st]); // the block's bytes are in registers: its stage can be refilled
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                if ((uint32_t)(c & 1) != phase) continue; // the other phase's chunk
                 const uint32_t g = 4 * kb + c, ca = g % G_STAGES;
+                if (g % PH != phase) continue; // another phase's chunk
                 const bool tr = traced && g < 1024 && dt == 0;
                 if (tr) p.trace[4096 + 4 * g] = clock64();
                 if (g >= G_STAGES && !(mode & 16u)) ok = ok && warp_wait(&freeb[ca], ((g / G_STAGES) - 1) & 1, lane);
@@ -516,7 +525,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
             const uint32_t q = warp & 3, colq = (warp - 2) >> 2; // TMEM lane quarter of this warp, column quarter
             const uint32_t orow = m0 + q * 32 + lane;
 #pragma unroll 1
-            for (uint32_t cb = 0; cb < 2; ++cb) {
+            for (uint32_t cb = 0; cb < 2 && colq < 4; ++cb) { // sixteen warps cover the 4 x 4 (lane quarter, column quarter) grid
                 const uint32_t col0 = colq * 64 + cb * 32;
                 uint32_t v[32];
                 asm volatile(
@@ -692,7 +701,7 @@ template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, 
     const size_t smem = (size_t)G_STAGES * G_B_BYTES + (size_t)Cfg::RAW_STAGES * Cfg::RAW_BYTES + 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_q_tc_kernel<FMT, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gemm_q_tc_kernel<FMT, DBG><<<grid, G_THREADS, smem, st>>>(p, maps);
+    gemm_q_tc_kernel<FMT, DBG><<<grid, g_threads(Cfg::PHASES), smem, st>>>(p, maps);
     return cudaGetLastError();
 }
 
