@@ -308,3 +308,28 @@ def test_streamed_plan_variants_agree(ctx, wr, rw):
         assert plan["streamed"] == 1 and plan["rows_per_tile"] == wr * rw, plan
         assert synth.rel_err(got, cpu) < TOL
         wt.free()
+
+
+def test_host_vectors_pinned_and_pageable_take_the_same_values(ctx):
+    """``ullm_cuda_weight_matvec`` moves page-locked host vectors with small kernels and pageable ones with
+    cudaMemcpyAsync: same results either way, odd lengths and unaligned views included."""
+    import torch
+
+    out, cols = 1030, 2048  # out not a multiple of 4: the copy kernel's scalar tail
+    wb = synth.gen_q4k(out, cols, 21)
+    w = backend.Weight(ctx, backend.Q4_K, wb, out, cols)
+    x = synth.normal(22, cols)
+    ref = oracle.matvec_q(oracle.Weight(backend.Q4_K, wb, out, cols), x)
+    y_pageable = w.matvec(x.copy())
+    xp = torch.from_numpy(x.copy()).pin_memory().numpy()
+    yp = torch.empty(out + 1, dtype=torch.float32).pin_memory().numpy()
+    y_pinned = w.matvec(xp, out=yp[:out]).copy()  # a copy: the next call writes the same buffer
+    y_unaligned = w.matvec(xp, out=yp[1:]).copy()  # destination 4 bytes off a 16-byte boundary
+    assert np.array_equal(y_pageable, y_pinned) and np.array_equal(y_pageable, y_unaligned)
+    assert synth.rel_err(y_pinned, ref) < 1e-3
+    ctx.debug_set("no_host_kernels", 1)
+    try:
+        assert np.array_equal(w.matvec(xp), y_pageable)
+    finally:
+        ctx.debug_set("no_host_kernels", 0)
+    w.free()

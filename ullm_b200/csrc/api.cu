@@ -470,15 +470,44 @@ int ullm_cuda_weight_matvec_batch_dev(ullm_cuda_ctx *c, size_t n, const ullm_cud
     return ullm_cuda_weight_matvec_chain_dev(c, n, ops.data(), stream);
 }
 
+// A batch-1 call from host vectors is a few KB in, a few KB out and a 10-20 us kernel: the copy engines' start-up
+// and the hand-overs between them and the compute engine cost as much as the kernel.  When the caller's vectors
+// are page-locked (and so addressable from the device), the vectors are therefore moved by two small kernels on
+// the same stream instead: one stream of compute work, no engine switch.  Pageable vectors take cudaMemcpyAsync.
+__global__ void __launch_bounds__(256) host_vec_copy_kernel(const float *__restrict__ src, float *__restrict__ dst, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0 && i + 3 < n) {
+        *(float4 *)(dst + i) = *(const float4 *)(src + i);
+    } else {
+        for (size_t j = i; j < n && j < i + 4; ++j) dst[j] = src[j];
+    }
+}
+static const float *device_view_of_host(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return a.type == cudaMemoryTypeHost ? (const float *)a.devicePointer : nullptr;
+}
+static cudaError_t vec_copy(const float *src, float *dst, size_t n, cudaStream_t st) {
+    host_vec_copy_kernel<<<(unsigned)((n + 1023) / 1024), 256, 0, st>>>(src, dst, n);
+    return cudaGetLastError();
+}
+
 int ullm_cuda_weight_matvec(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const float *x, float *y) {
     if (!c || !w || !x || !y) return ULLM_ERR_INVALID;
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
     void *d_x = nullptr, *d_y = nullptr;
     int rc;
     if ((rc = ctx_scratch(c, 4, w->cols * 4, &d_x)) || (rc = ctx_scratch(c, 5, w->out * 4, &d_y))) return rc;
-    ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_x, x, w->cols * 4, cudaMemcpyHostToDevice, c->stream));
+    const float *xv = c->no_host_kernels ? nullptr : device_view_of_host(x);
+    float *yv = c->no_host_kernels ? nullptr : (float *)device_view_of_host(y);
+    if (xv) ULLM_CUDA_TRY(c, vec_copy(xv, (float *)d_x, w->cols, c->stream));
+    else ULLM_CUDA_TRY(c, cudaMemcpyAsync(d_x, x, w->cols * 4, cudaMemcpyHostToDevice, c->stream));
     if ((rc = ullm_cuda_weight_matvec_dev(c, w, (const float *)d_x, (float *)d_y, nullptr))) return rc;
-    ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, w->out * 4, cudaMemcpyDeviceToHost, c->stream));
+    if (yv) ULLM_CUDA_TRY(c, vec_copy((const float *)d_y, yv, w->out, c->stream));
+    else ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, w->out * 4, cudaMemcpyDeviceToHost, c->stream));
     ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     return ctx_check_status(c);
 }
@@ -639,6 +668,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
     else if (!strcmp(key, "gemm_min_s")) c->gemm_min_s = value;
     else if (!strcmp(key, "no_chain")) c->no_chain = value != 0;
+    else if (!strcmp(key, "no_host_kernels")) c->no_host_kernels = value != 0;
     else if (!strcmp(key, "gemm_mode")) gemm_set_debug_mode(value);
     else if (!strcmp(key, "skip_compute")) matvec_set_skip_compute(value);
     else if (!strcmp(key, "chunk")) matvec_set_chunk(value);

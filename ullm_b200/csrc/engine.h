@@ -31,6 +31,7 @@ struct ullm_cuda_ctx {
     bool use_pdl = false;
     bool no_prepare = false; // keep Q6_K weights in their verbatim bytes (tests)
     bool no_chain = false;   // run op lists one kernel per op (tests, comparisons)
+    bool no_host_kernels = false; // host vectors always through cudaMemcpyAsync (comparisons)
     unsigned *d_sync = nullptr; // grid-barrier counter of the chain kernel
     int plan_wr = 0, plan_rw = 0, plan_stages = 0;
     int gemm_min_s = 32; // batches below this many tokens use per-token matvecs
