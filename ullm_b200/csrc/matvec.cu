@@ -443,7 +443,7 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
             if (R % gran) continue;
             const uint32_t wst = align_up(R * row_bytes, 128), tst = align_up(R * tbl_row_bytes, 128);
             const uint32_t stage = wst + 2 * tst;
-            if (stage > 64 * 1024) continue;
+            if (stage > 100 * 1024) continue;
             const uint32_t off_part = 128;
             const uint32_t off_prep = align_up(off_part + std::max(2 * 8 * R * WC * 4, 128u), 128);
             const uint32_t off_ring = align_up(off_prep + ncg * xregs * 32 * 4, 128);
@@ -452,14 +452,17 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
             uint32_t S = std::min<uint32_t>(8, (budget - off_ring) / stage);
             S = std::min(S, std::max(2u, tiles));
             if (g_force_stages) S = std::min<uint32_t>(S, (uint32_t)g_force_stages);
-            // Measured on B200: rows-per-warp 2 beats 1 (more independent work per tile
-            // wait), tiles of 40-64 KB beat small ones, three or more stages unless the
-            // CTA's whole range fits in two.
+            // Measured on B200 (plan sweeps on [28672,8192] and [8192,8192] Q4_K, [14336,4096] and [4096,14336]
+            // Q6_K): the kernels are bound by instruction issue, not by HBM (about 200 warp instructions per
+            // 2048 weights; streaming alone runs at 5.2 TB/s where the full kernel reached 3.9), so four rows per
+            // warp beat two (the register image of x and the per-tile bookkeeping are shared by more rows, and
+            // the transposed reduction costs less per row), as many warps as the tile allows beat fewer, and two
+            // stages of 70-95 KB are enough when that is what four rows per warp cost.
             const double eff = (double)rows_cta / ((double)tiles * R); // idle warps in the ragged tile
-            const double f_warps = std::sqrt(std::min(1.0, (WC * WR) / (cpsm == 2 ? 10.0 : 16.0)));
-            const double f_rw = RW == 1 ? 0.85 : (RW == 2 ? 1.0 : 0.97);
+            const double f_warps = std::sqrt(std::min(1.0, (WC * WR) / (cpsm == 2 ? 10.0 : 14.0)));
+            const double f_rw = RW == 1 ? 0.75 : (RW == 2 ? 0.84 : 1.0);
             const double f_stage = std::sqrt(std::min(1.0, stage / (cpsm == 2 ? 28672.0 : 45056.0)));
-            const double f_depth = (S >= 3 || tiles <= S) ? 1.0 : 0.85;
+            const double f_depth = (S >= 3 || tiles <= S) ? 1.0 : 0.97;
             const double score = eff * f_warps * f_rw * f_stage * f_depth;
             if (score > best.score) {
                 best.ok = true;
