@@ -284,9 +284,10 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
     // first warp of each row slice, one tile-ring revolution late: by then every
     // warp has released the tile's stage (and written its partials before doing
     // so), so no barrier between the warps of a slice is needed per tile.
-    auto flush = [&](uint32_t kt) {
+    // `slot` = kt mod 2S names the tile's partial area (the tile loop keeps it without dividing).
+    auto flush = [&](uint32_t kt, uint32_t slot) {
         if (cgw != 0 || lane >= RW) return;
-        const float *pt = part + ((size_t)(((kt / p.S) & 1) * p.S + kt % p.S) * p.R) * p.WC;
+        const float *pt = part + ((size_t)slot * p.R) * p.WC;
         const uint32_t row = rs * RW + lane, gr = rbeg + kt * p.R + row;
         if (gr >= rend || aborted) return;
         float acc = 0.f;
@@ -299,12 +300,13 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
             p.y[gr >> 1] = acc / (1.0f + expf(-acc)) * up;
         }
     };
-    for (uint32_t k = 0; k < ntiles; ++k) {
-        const uint32_t s = k % p.S;
+    uint32_t slot = 0; // k mod 2S: stage s = slot mod S, mbarrier phase = slot / S
+    for (uint32_t k = 0; k < ntiles; ++k, slot = slot + 1 == 2 * p.S ? 0 : slot + 1) {
+        const uint32_t ph = slot >= p.S ? 1u : 0u, s = slot - ph * p.S;
         stamp();
-        if (!aborted && !wait_or_timeout(&full[s], (k / p.S) & 1)) aborted = true;
+        if (!aborted && !wait_or_timeout(&full[s], ph)) aborted = true;
         stamp();
-        if (p.WC > 1 && k >= p.S) flush(k - p.S);
+        if (p.WC > 1 && k >= p.S) flush(k - p.S, ph ? s : s + p.S);
         const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
         const uint32_t r0 = rbeg + k * p.R;
         float v[RW];
@@ -337,7 +339,7 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
                 else if ((myrow & 1) == 0) p.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
             }
         } else {
-            float *pt = part + ((size_t)(((k / p.S) & 1) * p.S + s) * p.R) * p.WC;
+            float *pt = part + ((size_t)slot * p.R) * p.WC;
             if ((lane & 7) == 0 && (RW == 4 || (lane & 8) == 0)) pt[rl * p.WC + cgw] = r;
         }
         __syncwarp();
@@ -346,7 +348,7 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
     stamp();
     if (p.WC > 1) {
         asm volatile("bar.sync 1, %0;" ::"r"(p.NW * 32) : "memory"); // all partials of the last tiles are in
-        for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt);
+        for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt, kt % (2 * p.S));
     }
     stamp();
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;

@@ -283,9 +283,10 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     // are picked by a single pair, and then all row tiles of the expert use the same vector.
     uint32_t X[G][XR];
     int loaded_vec = -1;
-    for (uint32_t u = u0; u < u1; ++u, ++kk) {
-        const uint32_t s = kk % p.S;
-        const uint32_t d = u / p.tiles_per_expert, rt = u % p.tiles_per_expert, r0 = rt * p.R;
+    // the tile loop divides nothing: stage, mbarrier phase, expert and row tile are carried along
+    uint32_t s = 0, ph = 0, d = u0 / p.tiles_per_expert, rt = u0 % p.tiles_per_expert;
+    for (uint32_t u = u0; u < u1; ++u, ++kk, s = s + 1 == p.S ? 0 : s + 1, ph ^= (s == 0), rt = rt + 1 == p.tiles_per_expert ? 0 : rt + 1, d += (rt == 0)) {
+        const uint32_t r0 = rt * p.R;
         const int pb = ex_off[d], np = ex_off[d + 1] - pb;
         if (!GATE_UP && (int)d != cur_d) {
             // new expert: fixed-point images of the hidden vectors of its pairs
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
             loaded_vec = -1; // the images were rebuilt
         }
         cur_d = (int)d;
-        if (!aborted && !wait_or_timeout(&full[s], (kk / p.S) & 1)) aborted = true;
+        if (!aborted && !wait_or_timeout(&full[s], ph)) aborted = true;
         const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
         const uint32_t mstride = p.w_stage_bytes + 2 * p.tbl_stage_bytes;
         for (int j = 0; j < np && !aborted; ++j) {
