@@ -673,6 +673,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     else if (!strcmp(key, "skip_compute")) matvec_set_skip_compute(value);
     else if (!strcmp(key, "chunk")) matvec_set_chunk(value);
     else if (!strcmp(key, "stagger")) matvec_set_stagger(value);
+    else if (!strcmp(key, "slices")) matvec_set_slices(value);
     else if (!strcmp(key, "ctas_per_sm")) matvec_set_ctas_per_sm(value);
     else if (!strcmp(key, "plan_wr")) c->plan_wr = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
     else if (!strcmp(key, "plan_rw")) c->plan_rw = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);

@@ -83,6 +83,7 @@ void matvec_set_skip_compute(int v);
 // Tuning aid: bytes per bulk copy of the tile stream (0 = default).
 void matvec_set_chunk(int v);
 void matvec_set_stagger(int v);
+void matvec_set_slices(int v); // 0: one barrier pair per tile instead of one per row slice (comparisons)
 // Tuning override: CTAs per SM of the streamed plan (0 = automatic, 1 or 2).
 void matvec_set_ctas_per_sm(int v);
 // prepare.cu — Q6_K rows <-> the prepared layout (FMT_Q6KR)

@@ -134,6 +134,7 @@ struct StreamParams {
     uint32_t row_bytes, tbl_row_bytes;
     uint32_t gran;       // CTA row ranges start at multiples of this many rows (16-byte alignment)
     uint32_t R, WC, WR, NW, S;
+    uint32_t NSL;        // barrier slices per tile: WR (one per row slice of RW rows) or 1 (whole tile)
     uint32_t w_stage_bytes, tbl_stage_bytes, stage_bytes; // regions inside one stage (128-B multiples)
     uint32_t ncg;
     uint32_t off_part, off_prep, off_ring; // byte offsets in dynamic smem
@@ -150,8 +151,11 @@ template <int FMT, int RW, int G, typename TBL>
 __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(const StreamParams p) {
     constexpr int XR = FmtTraits<FMT>::XREGS;
     extern __shared__ __align__(128) uint8_t smem[];
+    // full / empty mbarriers, one pair per (stage, slice): a row slice (the RW rows of one warp row) is
+    // handed over as soon as its own bytes are in, and refilled as soon as its own warps are done with it,
+    // so a 90 KB tile does not have to land completely before the first row is computed.
     uint64_t *full = (uint64_t *)smem;
-    uint64_t *empty = full + p.S;
+    uint64_t *empty = full + p.S * p.NSL;
     float *part = (float *)(smem + p.off_part);
     uint32_t *prep = (uint32_t *)(smem + p.off_prep);
     uint8_t *ring = smem + p.off_ring;
@@ -185,47 +189,55 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
     PrepPre pre;
     if (!p.pdl && !producer) prep_preload(pre, p.x, p.norm_w, p.in_dim, tid, nthr_c);
     if (tid == 0) {
-        for (uint32_t s = 0; s < p.S; ++s) {
+        for (uint32_t s = 0; s < p.S * p.NSL; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], p.NW);
+            mbar_init(&empty[s], p.NW / p.NSL);
         }
         mbar_fence_init();
     }
     __syncthreads();
 
     if (producer) {
-        // One tile = one contiguous byte range (plus two table ranges for MLX).  The
-        // whole producer warp issues it, in chunks of p.chunk bytes spread over the
-        // lanes; all chunks complete on the tile's barrier.  Weights do not depend on
-        // the previous kernel in the stream, so the stream starts at once.  The first
-        // ring revolution is staggered (tile k is requested when tile k-1 has landed):
-        // requested together, all S tiles would arrive together and the first row
-        // could only be computed when most of the ring had been filled.
-        for (uint32_t k = 0; k < ntiles; ++k) {
-            const uint32_t s = k % p.S;
-            bool ok = true;
-            if (lane == 0) {
-                if (k >= p.S) ok = wait_or_timeout(&empty[s], ((k / p.S) - 1) & 1);
-                else if (k > 0 && p.stagger) ok = wait_or_timeout(&full[k - 1], 0);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) {
-                if (lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
-                break;
-            }
+        // One tile = one contiguous byte range (plus two table ranges for MLX), requested slice by
+        // slice (one slice = the whole tile unless the plan asks for one per warp row).  The whole
+        // producer warp issues a slice, in chunks of p.chunk bytes spread over the lanes; all chunks
+        // complete on the slice's barrier.  Weights do not depend on the previous kernel in the
+        // stream, so the stream starts at once.  The first ring revolution is staggered (tile k is
+        // requested when tile k-1 has landed): requested together, all S tiles would arrive together
+        // and the first row could only be computed when most of the ring had been filled.
+        const uint32_t srows = p.R / p.NSL; // rows per slice
+        uint32_t s = 0, ph = 0;             // stage and the phase of its previous use, carried along
+        bool ok = true;
+        for (uint32_t k = 0; k < ntiles && ok; ++k) {
             const uint32_t r0 = rbeg + k * p.R;
             const uint32_t rows = min(p.R, rend - r0);
-            const uint32_t wb = rows * p.row_bytes, tb = rows * p.tbl_row_bytes;
             uint8_t *dst = ring + (size_t)s * p.stage_bytes;
-            if (lane == 0) mbar_arrive_expect_tx(&full[s], wb + 2 * tb);
-            __syncwarp();
-            const uint8_t *src = p.w + (size_t)r0 * p.row_bytes;
-            for (uint32_t off = lane * p.chunk; off < wb; off += 32 * p.chunk)
-                bulk_g2s(dst + off, src + off, min(p.chunk, wb - off), &full[s]);
-            if (FMT == FMT_MLX4 && lane < 2) {
-                const uint8_t *t = (lane ? p.biases : p.scales) + (size_t)r0 * p.tbl_row_bytes;
-                bulk_g2s(dst + p.w_stage_bytes + lane * p.tbl_stage_bytes, t, tb, &full[s]);
+            for (uint32_t j = 0; j < p.NSL; ++j) {
+                uint64_t *fb = &full[s * p.NSL + j];
+                if (lane == 0) {
+                    if (k >= p.S) ok = wait_or_timeout(&empty[s * p.NSL + j], ph ^ 1u);
+                    else if (k > 0 && j == 0 && p.stagger) ok = wait_or_timeout(&full[(k - 1) * p.NSL + p.NSL - 1], 0);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
+                    break;
+                }
+                const uint32_t row0 = j * srows;
+                const uint32_t nrows = rows > row0 ? min(srows, rows - row0) : 0u; // 0: a slice past the ragged end
+                const uint32_t wb = nrows * p.row_bytes, tb = nrows * p.tbl_row_bytes;
+                if (lane == 0) mbar_arrive_expect_tx(fb, wb + 2 * tb);
+                __syncwarp();
+                const uint8_t *src = p.w + (size_t)(r0 + row0) * p.row_bytes;
+                uint8_t *d = dst + (size_t)row0 * p.row_bytes;
+                for (uint32_t off = lane * p.chunk; off < wb; off += 32 * p.chunk)
+                    bulk_g2s(d + off, src + off, min(p.chunk, wb - off), fb);
+                if (FMT == FMT_MLX4 && lane < 2 && tb) {
+                    const uint8_t *t = (lane ? p.biases : p.scales) + (size_t)(r0 + row0) * p.tbl_row_bytes;
+                    bulk_g2s(dst + p.w_stage_bytes + lane * p.tbl_stage_bytes + (size_t)row0 * p.tbl_row_bytes, t, tb, fb);
+                }
             }
+            if (++s == p.S) s = 0, ph ^= 1u;
         }
         return;
     }
@@ -300,11 +312,12 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
             p.y[gr >> 1] = acc / (1.0f + expf(-acc)) * up;
         }
     };
+    const uint32_t bslice = p.NSL > 1 ? rs : 0u; // the barrier pair of this warp's rows
     uint32_t slot = 0; // k mod 2S: stage s = slot mod S, mbarrier phase = slot / S
     for (uint32_t k = 0; k < ntiles; ++k, slot = slot + 1 == 2 * p.S ? 0 : slot + 1) {
         const uint32_t ph = slot >= p.S ? 1u : 0u, s = slot - ph * p.S;
         stamp();
-        if (!aborted && !wait_or_timeout(&full[s], ph)) aborted = true;
+        if (!aborted && !wait_or_timeout(&full[s * p.NSL + bslice], ph)) aborted = true;
         stamp();
         if (p.WC > 1 && k >= p.S) flush(k - p.S, ph ? s : s + p.S);
         const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
@@ -343,7 +356,7 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
             if ((lane & 7) == 0 && (RW == 4 || (lane & 8) == 0)) pt[rl * p.WC + cgw] = r;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]); // partials written, stage may be refilled
+        if (lane == 0) mbar_arrive(&empty[s * p.NSL + bslice]); // partials written, the slice may be refilled
     }
     stamp();
     if (p.WC > 1) {
@@ -397,6 +410,8 @@ static unsigned long long *g_trace = nullptr;
 static int g_skip_compute = 0;
 static int g_chunk = 0;
 static int g_stagger = 1;
+static int g_slices = 1;
+void matvec_set_slices(int v) { g_slices = v; }
 void matvec_set_stagger(int v) { g_stagger = v; }
 void matvec_set_chunk(int v) { g_chunk = v; }
 void matvec_set_trace(void *p) { g_trace = (unsigned long long *)p; }
@@ -446,7 +461,11 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
             const uint32_t wst = align_up(R * row_bytes, 128), tst = align_up(R * tbl_row_bytes, 128);
             const uint32_t stage = wst + 2 * tst;
             if (stage > 100 * 1024) continue;
-            const uint32_t off_part = 128;
+            // one barrier pair per row slice when the slices are large (measured: slices of 47 KB, [4096,14336]
+            // Q6_K, 13.7 -> 13.0 us; slices of 13-18 KB lose 10-20 %) and start 16-byte aligned, else one per tile
+            const uint32_t NSL = (g_slices && WR > 1 && RW * row_bytes >= 32768 && (RW * row_bytes) % 16 == 0 &&
+                                  (RW * tbl_row_bytes) % 16 == 0) ? WR : 1u;
+            const uint32_t off_part = align_up(2 * 8 * NSL * 8, 128); // up to 8 stages x NSL slices x (full, empty)
             const uint32_t off_prep = align_up(off_part + std::max(2 * 8 * R * WC * 4, 128u), 128);
             const uint32_t off_ring = align_up(off_prep + ncg * xregs * 32 * 4, 128);
             if ((int)off_ring + 2 * (int)stage > budget) continue;
@@ -477,7 +496,7 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
                 StreamParams &p = best.p;
                 p.out_dim = (uint32_t)out_dim, p.in_dim = (uint32_t)in_dim, p.group = (uint32_t)group;
                 p.row_bytes = row_bytes, p.tbl_row_bytes = tbl_row_bytes, p.gran = gran;
-                p.R = R, p.WC = WC, p.WR = WR, p.NW = WC * WR, p.S = S;
+                p.R = R, p.WC = WC, p.WR = WR, p.NW = WC * WR, p.S = S, p.NSL = NSL;
                 p.w_stage_bytes = wst, p.tbl_stage_bytes = tst, p.stage_bytes = stage;
                 p.ncg = ncg;
                 p.off_part = off_part, p.off_prep = off_prep, p.off_ring = off_ring;
