@@ -42,7 +42,7 @@ C1_DOWN = (4096, 14336)
 C1_BYTES_PER_LAUNCH = 48_168_960 + 16_384 + 57_344  # weights + x + y (either launch)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_PER_LAUNCH = {"c1_q6k_ffn_pair": (48_224_768 + 48_265_728) // 2}  # dram read + write of the two launches, ncu capture under profiles/
+NCU_TRAFFIC_PER_LAUNCH = {"c1_q6k_ffn_pair": (48_236_032 + 48_276_992) // 2}  # dram read + write of the two launches, ncu capture under profiles/
 
 C4_MATS = [  # name, dtype, out, in   (one Llama-3-70B block)
     ("q", synth.Q4_K, 8192, 8192), ("k", synth.Q4_K, 1024, 8192), ("v", synth.Q4_K, 1024, 8192),
