@@ -429,11 +429,11 @@ static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, u
         if (rows % R && ((row_bytes % 16) || (tbl_row_bytes % 16))) continue;
         const uint32_t wst = align_up(R * row_bytes, 128), tst = align_up(R * tbl_row_bytes, 128);
         const uint32_t stage = NM * (wst + 2 * tst);
-        if (stage > 40 * 1024 && best.ok) continue;
+        if (stage > 100 * 1024 && best.ok) continue;
         if ((int)(off_ring + 2 * stage) > budget) continue;
         const uint32_t S = std::min<uint32_t>(8, (budget - off_ring) / stage);
         // prefer ~16-36 KB stages
-        if (best.ok && stage > 36 * 1024) continue;
+        if (best.ok && stage > 100 * 1024) continue;
         best.ok = true;
         best.g = (int)G;
         best.threads = (int)(NW + 1) * 32;
