@@ -41,7 +41,7 @@ __host__ __device__ inline int route_off_pairs(int E) { return 2 + 2 * E; }
 __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict__ logits, int n_tok, int n_exp, int k,
                                                        uint32_t *__restrict__ idx, float *__restrict__ wts,
                                                        int *__restrict__ route) {
-    __shared__ float lg[MOE_MAX_TOK][MOE_MAX_EXPERTS];
+    __shared__ __align__(16) float lg[MOE_MAX_TOK][MOE_MAX_EXPERTS];
     __shared__ int sel[MOE_MAX_TOK * MOE_MAX_K];
     __shared__ int cnt[MOE_MAX_EXPERTS];
     __shared__ int offs_s[MOE_MAX_EXPERTS + 1];
@@ -85,13 +85,16 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
         }
     }
     __syncthreads();
-    // group the pairs by expert (ascending expert id, pairs in (token, slot) order)
+    // group the pairs by expert (ascending expert id, pairs in (token, slot) order): every pair sets its bit in
+    // its expert's 128-bit mask; an expert's count is the mask's population and its pairs are the set bits in
+    // ascending order, so nothing depends on the order in which the bits were set
     const int npairs = n_tok * k;
-    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) {
-        int c = 0;
-        for (int p = 0; p < npairs; ++p) c += sel[p] == e;
-        cnt[e] = c;
-    }
+    unsigned long long(*mask)[2] = reinterpret_cast<unsigned long long(*)[2]>(&lg[0][0]); // the logits are spent: their 32 KB hold the masks
+    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) mask[e][0] = 0ull, mask[e][1] = 0ull;
+    __syncthreads();
+    for (int p = threadIdx.x; p < npairs; p += blockDim.x) atomicOr(&mask[sel[p]][p >> 6], 1ull << (p & 63));
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) cnt[e] = __popcll(mask[e][0]) + __popcll(mask[e][1]);
     __syncthreads();
     int *list = route + route_off_list(), *offs = route + route_off_offs(n_exp), *pairs = route + route_off_pairs(n_exp);
     if (warp == 0) {
@@ -125,8 +128,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
     for (int e = threadIdx.x; e < n_exp; e += blockDim.x) {
         if (!cnt[e]) continue;
         int o = offs_s[e];
-        for (int p = 0; p < npairs; ++p)
-            if (sel[p] == e) pairs[o++] = p;
+        for (int h = 0; h < 2; ++h)
+            for (unsigned long long m = mask[e][h]; m; m &= m - 1) pairs[o++] = 64 * h + __ffsll((long long)m) - 1;
     }
 }
 
