@@ -10,10 +10,10 @@
 //   W_o attn  (+ residual, in the epilogue)
 //   [rmsnorm ->] W_gate|up x (rows interleaved at upload; silu(g)*u in the epilogue)
 //   W_down h  (+ residual)
-// A mixture-of-experts layer (MLX 4-bit) replaces the last two by rmsnorm, router matvec, routing,
-// the selected experts' gate|up and down kernels and the weighted combine (+ residual): moe.cu;
-// its q, k and v projections are one stacked MLX matrix.
-// and norm + output projection at the end.  The position and the current token
+// and norm + output projection at the end.  A mixture-of-experts layer (MLX 4-bit) replaces the
+// last two by the router matvec, the routing, the selected experts' gate|up and down kernels (x is
+// RMS-normalised in their prologues) and the weighted combine (+ residual): moe.cu; its q, k and v
+// projections are one stacked MLX matrix.  The position and the current token
 // live in device memory, so the same CUDA graph is replayed for every token: one
 // submission per decoded token, and greedy decoding (argmax -> embedding lookup)
 // needs no host round trip at all.
@@ -526,6 +526,8 @@ Forward::~Forward() {
     for (void *q : owned)
         if (q) cudaFree(q);
     if (h_pin) cudaFreeHost(h_pin);
+    if (h_x) cudaFreeHost(h_x);
+    if (h_logits) cudaFreeHost(h_logits);
     if (h_status) cudaFreeHost((void *)h_status);
     if (stream) cudaStreamDestroy(stream);
 }
@@ -736,6 +738,8 @@ cudaError_t Forward::init(const DeviceInfo &devinfo, int device_, const ForwardP
     TRY(cudaMemsetAsync(state, 0, 64, stream));
     TRY(dev_alloc((void **)&tokens_out, MAX_GREEDY * 4));
     TRY(cudaHostAlloc((void **)&h_pin, 64, cudaHostAllocDefault));
+    TRY(cudaHostAlloc((void **)&h_x, P.n_embd * 4, cudaHostAllocDefault));
+    TRY(cudaHostAlloc((void **)&h_logits, P.vocab * 4, cudaHostAllocDefault));
     TRY(cudaHostAlloc((void **)&h_status, sizeof(int), cudaHostAllocMapped));
     owned_host = true;
     *h_status = 0;
@@ -904,10 +908,15 @@ cudaError_t Forward::forward(const float *x_init, size_t pos, float *logits_host
     if ((e = cudaSetDevice(device)) != cudaSuccess) return e;
     ((int *)h_pin)[0] = (int)pos;
     if ((e = cudaMemcpyAsync(state, h_pin, 4, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
-    if ((e = cudaMemcpyAsync(x, x_init, P.n_embd * 4, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
+    // The caller's vectors are ordinary (pageable) memory as a rule: a direct copy would be staged by the driver in
+    // small pieces.  They go through this object's page-locked buffers instead: one DMA each way plus a host memcpy.
+    memcpy(h_x, x_init, P.n_embd * 4);
+    if ((e = cudaMemcpyAsync(x, h_x, P.n_embd * 4, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
     if ((e = run_step(0, nullptr, 0)) != cudaSuccess) return e;
-    if ((e = cudaMemcpyAsync(logits_host, logits, P.vocab * 4, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
-    return cudaStreamSynchronize(stream);
+    if ((e = cudaMemcpyAsync(h_logits, logits, P.vocab * 4, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return e;
+    memcpy(logits_host, h_logits, P.vocab * 4);
+    return cudaSuccess;
 }
 
 cudaError_t Forward::greedy(const void *embd_table, int embd_dtype, uint32_t first_token, size_t pos, size_t n,

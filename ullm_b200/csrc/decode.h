@@ -75,6 +75,7 @@ struct Forward {
     void *state = nullptr; // device ints: [0] pos, [1] token, [2] step
     uint32_t *tokens_out = nullptr;
     void *h_pin = nullptr;
+    float *h_x = nullptr, *h_logits = nullptr; // page-locked staging of forward()'s input row and logits
     volatile int *h_status = nullptr;
     int *d_status = nullptr;
     bool owned_host = false;

@@ -10,6 +10,8 @@
 // tokens are processed in chunks; the attention reads earlier chunks from the cache.
 #include "decode.h"
 
+#include <cstring>
+
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -285,9 +287,11 @@ cudaError_t Forward::forward_batch(const float *embeds_host, size_t s, float *lo
             TRY(mv(output, x, logits, final_norm, EPI_STORE, nullptr));
         }
     }
-    TRY(cudaMemcpyAsync(logits_host, logits, P.vocab * 4, cudaMemcpyDeviceToHost, stream));
+    TRY(cudaMemcpyAsync(h_logits, logits, P.vocab * 4, cudaMemcpyDeviceToHost, stream)); // page-locked staging, as in forward()
+    TRY(cudaStreamSynchronize(stream));
 #undef TRY
-    return cudaStreamSynchronize(stream);
+    memcpy(logits_host, h_logits, P.vocab * 4);
+    return cudaSuccess;
 }
 
 } // namespace ullm
