@@ -154,7 +154,9 @@ struct MoeStreamParams {
 };
 
 // GATE_UP: two matrices, x indexed by token, epilogue silu(g)*u.
-template <bool GATE_UP, int G, typename TBL>
+// RW = rows per warp and tile (p.R / p.NW), a template parameter so that the per-row sums of a tile are reduced
+// over the warp together (transposed butterfly) instead of one after the other.
+template <bool GATE_UP, int G, typename TBL, int RW>
 __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParams p) {
     constexpr int XR = XREGS_MLX, NM = GATE_UP ? 2 : 1;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -281,7 +283,6 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     bool aborted = false;
     int cur_d = -1;
     uint32_t kk = 0;
-    const uint32_t RW = p.R / p.NW;
     // The register image of the current activation vector survives from tile to tile: most experts
     // are picked by a single pair, and then all row tiles of the expert use the same vector.
     uint32_t X[G][XR];
@@ -315,27 +316,40 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
                         X[g][q] = (uint32_t)g < p.ncg ? qimg[((size_t)(vec * p.ncg + g) * XR + q) * 32 + lane] : 0u;
                 loaded_vec = (int)vec;
             }
-            for (uint32_t rr = 0; rr < RW; ++rr) {
+            constexpr int NV = RW * NM; // partial sums of this warp's rows (gate and up of a row side by side)
+            float v[NV];
+#pragma unroll
+            for (int rr = 0; rr < RW; ++rr) {
                 const uint32_t rl = warp * RW + rr;
-                if (r0 + rl >= p.rows) break;
-                float acc[NM];
 #pragma unroll
                 for (int m = 0; m < NM; ++m) {
-                    acc[m] = 0.f;
-                    const uint32_t base = stage + m * mstride;
-                    const uint32_t ts = base + p.w_stage_bytes + rl * p.tbl_row_bytes;
+                    float a = 0.f;
+                    if (r0 + rl < p.rows) {
+                        const uint32_t base = stage + m * mstride;
+                        const uint32_t ts = base + p.w_stage_bytes + rl * p.tbl_row_bytes;
 #pragma unroll
-                    for (int g = 0; g < G; ++g)
-                        if ((uint32_t)g < p.ncg && (g * 32u + lane) * 32u < p.in_dim)
-                            acc[m] += row_partial<FMT_MLX4, TBL>(base + rl * p.row_bytes, X[g], g, lane, ts,
-                                                                 ts + p.tbl_stage_bytes, p.group);
-                    acc[m] = warp_sum(acc[m]);
+                        for (int g = 0; g < G; ++g)
+                            if ((uint32_t)g < p.ncg && (g * 32u + lane) * 32u < p.in_dim)
+                                a += row_partial<FMT_MLX4, TBL>(base + rl * p.row_bytes, X[g], g, lane, ts, ts + p.tbl_stage_bytes, p.group);
+                    }
+                    v[rr * NM + m] = a;
                 }
-                if (lane == 0) {
-                    float v;
-                    if (GATE_UP) v = acc[0] / (1.0f + expf(-acc[0])) * acc[NM - 1]; // math.rs:103-105, lib.rs:1482
-                    else v = acc[0];
-                    p.out[(size_t)pair * p.rows + r0 + rl] = v;
+            }
+            if constexpr (NV <= 4) {
+                // after the call the lanes with (bit 4, bit 3) = (i / 2, i % 2) [NV = 4] or bit 4 = i [NV = 2] hold sum i
+                uint32_t idx;
+                const float r = warp_reduce_rows<NV>(v, lane, idx);
+                const float other = GATE_UP ? __shfl_xor_sync(0xffffffffu, r, NV == 4 ? 8 : 16) : 0.f; // the row's up sum
+                const uint32_t rr = GATE_UP ? idx >> 1 : idx, rl = warp * RW + rr;
+                const bool writer = (lane & (NV == 4 ? 7 : 15)) == 0 && (NV > 1 || lane == 0) && (!GATE_UP || (idx & 1) == 0);
+                if (writer && r0 + rl < p.rows)
+                    p.out[(size_t)pair * p.rows + r0 + rl] = GATE_UP ? r / (1.0f + expf(-r)) * other : r; // math.rs:103-105, lib.rs:1482
+            } else {
+#pragma unroll
+                for (int rr = 0; rr < RW; ++rr) {
+                    const float g0 = warp_sum(v[rr * NM]), u0 = NM > 1 ? warp_sum(v[rr * NM + NM - 1]) : 0.f;
+                    const uint32_t rl = warp * RW + rr;
+                    if (lane == 0 && r0 + rl < p.rows) p.out[(size_t)pair * p.rows + r0 + rl] = GATE_UP ? g0 / (1.0f + expf(-g0)) * u0 : g0;
                 }
             }
         }
@@ -451,8 +465,8 @@ static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, u
     return best;
 }
 
-template <bool GATE_UP, int G, typename TBL> static cudaError_t launch_moe_t(const MoePlanInt &pl, cudaStream_t st, bool pdl) {
-    auto kfn = moe_stream_kernel<GATE_UP, G, TBL>;
+template <bool GATE_UP, int G, typename TBL, int RW> static cudaError_t launch_moe_t(const MoePlanInt &pl, cudaStream_t st, bool pdl) {
+    auto kfn = moe_stream_kernel<GATE_UP, G, TBL, RW>;
     static bool attr_set[64] = {};
     int devid = 0;
     cudaGetDevice(&devid);
@@ -469,10 +483,16 @@ template <bool GATE_UP, int G, typename TBL> static cudaError_t launch_moe_t(con
     cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kfn, pl.p);
 }
+template <bool GATE_UP, int G, typename TBL> static cudaError_t launch_moe_r(const MoePlanInt &pl, cudaStream_t st, bool pdl) {
+    const uint32_t rw = pl.p.R / pl.p.NW;
+    if (rw == 1) return launch_moe_t<GATE_UP, G, TBL, 1>(pl, st, pdl);
+    if (rw == 2) return launch_moe_t<GATE_UP, G, TBL, 2>(pl, st, pdl);
+    return launch_moe_t<GATE_UP, G, TBL, 4>(pl, st, pdl);
+}
 template <bool GATE_UP, typename TBL> static cudaError_t launch_moe_g(const MoePlanInt &pl, cudaStream_t st, bool pdl) {
-    if (pl.g == 1) return launch_moe_t<GATE_UP, 1, TBL>(pl, st, pdl);
-    if (pl.g == 2) return launch_moe_t<GATE_UP, 2, TBL>(pl, st, pdl);
-    return launch_moe_t<GATE_UP, 4, TBL>(pl, st, pdl);
+    if (pl.g == 1) return launch_moe_r<GATE_UP, 1, TBL>(pl, st, pdl);
+    if (pl.g == 2) return launch_moe_r<GATE_UP, 2, TBL>(pl, st, pdl);
+    return launch_moe_r<GATE_UP, 4, TBL>(pl, st, pdl);
 }
 
 size_t moe_scratch_bytes(const MoeExperts &e) {
