@@ -133,9 +133,10 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
     }
     const uint32_t nb = o.in_dim / QK_K;
 
-    auto flush = [&](uint32_t kt) { // sums the column-group partials of tile kt (see matvec.cu)
+    // sums the column-group partials of tile kt (see matvec.cu); slot = kt mod 2S names its partial area
+    auto flush = [&](uint32_t kt, uint32_t slot) {
         if (!active || cgw != 0 || lane >= RW) return;
-        const float *pt = part + ((size_t)(((kt / p.S) & 1) * p.S + kt % p.S) * o.R) * o.WC;
+        const float *pt = part + ((size_t)slot * o.R) * o.WC;
         const uint32_t row = rs * RW + lane, gr = rbeg + kt * o.R + row;
         if (gr >= rend || aborted) return;
         float acc = 0.f;
@@ -148,10 +149,15 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
             o.y[gr >> 1] = acc / (1.0f + expf(-acc)) * up;
         }
     };
-    for (uint32_t k = 0; k < ntiles; ++k) {
-        const uint32_t kg = kbase + k, s = kg % p.S;
-        if (!aborted && !wait_or_timeout(&full[s], (kg / p.S) & 1)) aborted = true;
-        if (o.WC > 1 && k >= p.S) flush(k - p.S);
+    // ring stage and mbarrier phase of the op's first tile (the ring runs on across ops), then carried along;
+    // slot = k mod 2S for the partial areas, which are the op's own
+    uint32_t s = kbase % p.S, ph = (kbase / p.S) & 1u, slot = 0;
+    for (uint32_t k = 0; k < ntiles; ++k, slot = slot + 1 == 2 * p.S ? 0 : slot + 1) {
+        if (k) {
+            if (++s == p.S) s = 0, ph ^= 1u;
+        }
+        if (!aborted && !wait_or_timeout(&full[s], ph)) aborted = true;
+        if (o.WC > 1 && k >= p.S) flush(k - p.S, slot >= p.S ? slot - p.S : slot + p.S);
         const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
         const uint32_t r0 = rbeg + k * o.R;
         if (active) {
@@ -181,7 +187,7 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
                     else if ((myrow & 1) == 0) o.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
                 }
             } else {
-                float *pt = part + ((size_t)(((k / p.S) & 1) * p.S + k % p.S) * o.R) * o.WC;
+                float *pt = part + ((size_t)slot * o.R) * o.WC;
                 if ((lane & 7) == 0 && (RW == 4 || (lane & 8) == 0)) pt[rl * o.WC + cgw] = r;
             }
         }
@@ -190,7 +196,7 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
     }
     if (o.WC > 1) {
         asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // all partials of the last tiles are in
-        for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt);
+        for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt, kt % (2 * p.S));
     }
 }
 
@@ -216,16 +222,15 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
     if (producer) {
         // the weight tiles of every op, back to back: one tile = one contiguous byte range
         uint8_t *ring = smem + p.off_ring;
-        uint32_t kg = 0;
+        uint32_t kg = 0, s = 0, ph = 0; // tile count, ring stage and phase of the stage's current use, carried along
         for (int i = 0; i < p.n_ops; ++i) {
             const ChainOpDev &o = p.op[i];
             uint32_t rbeg, rend;
             chain_row_range(o, rbeg, rend);
             const uint32_t ntiles = (rend - rbeg + o.R - 1) / o.R;
-            for (uint32_t k = 0; k < ntiles; ++k, ++kg) {
-                const uint32_t s = kg % p.S;
+            for (uint32_t k = 0; k < ntiles; ++k, ++kg, s = s + 1 == p.S ? 0 : s + 1, ph ^= (s == 0)) {
                 bool ok = true;
-                if (lane == 0 && kg >= p.S) ok = wait_or_timeout(&empty[s], ((kg / p.S) - 1) & 1);
+                if (lane == 0 && kg >= p.S) ok = wait_or_timeout(&empty[s], ph ^ 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     if (lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
