@@ -200,7 +200,7 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
     }
 }
 
-constexpr int CHAIN_MAX_THREADS = 17 * 32; // 16 consumer warps + the producer warp
+constexpr int CHAIN_MAX_THREADS = 21 * 32; // 20 consumer warps + the producer warp
 
 __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(const __grid_constant__ ChainParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -286,14 +286,14 @@ bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi) {
     if (in_dim % QK_K || in_dim == 0 || out_dim == 0 || out_dim > 0x7fffffffull) return false;
     if (fmt == FMT_Q6KR && in_dim % 2048) return false;
     if (epi == EPI_SWIGLU && (out_dim & 1)) return false;
-    return (in_dim + 2047) / 2048 <= 16; // one column group (2048 columns) per warp, 16 warps
+    return (in_dim + 2047) / 2048 <= 16; // one column group (2048 columns) per warp; up to 16 of the 20 consumer warps form a row slice
 }
 
 cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainOp *ops, unsigned *d_sync, int *d_status,
                                 cudaStream_t st, bool pdl) {
     if (n <= 0 || n > CHAIN_MAX_OPS) return cudaErrorInvalidValue;
     ChainParams p{};
-    p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 16, p.chunk = 4096;
+    p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 20, p.chunk = 4096;
     const int budget = dev.max_smem_optin - 1024;
     uint32_t max_stage = 0, max_part = 128, max_prep = 0;
     const uint32_t grid = (uint32_t)dev.sm_count;
@@ -319,7 +319,7 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         o.rw = 0;
         for (uint32_t rw = 4; rw >= rw_min; rw /= 2) {
             const uint32_t R = o.WR * rw;
-            if (R % o.gran || (uint64_t)R * o.row_bytes > 57344) continue;
+            if (R % o.gran || (uint64_t)R * o.row_bytes > 100 * 1024) continue;
             if (rw > rw_min && o.WR * (rw / 2) >= rows_cta && (o.WR * (rw / 2)) % o.gran == 0) continue;
             o.rw = rw;
             break;
