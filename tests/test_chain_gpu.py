@@ -119,3 +119,26 @@ def test_unsupported_weights_fall_back_to_separate_launches(ctx):
     assert run(ctx, [dict(w=gw, x=xd.data_ptr(), y=y.data_ptr())]) != -2
     ref = oracle.matvec_q(oracle.Weight(backend.MLX_U32, w, 64, 256, synth.bf16_to_f32(s), synth.bf16_to_f32(b), 64), x)
     assert synth.rel_err(y.cpu().numpy(), ref) < TOL
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_rank_shares_of_the_70b_block_in_one_launch(ctx, world):
+    """What one rank of the row-sharded 70B-shaped block launches per step (bench.py, N > 1): its 1/N of the
+    rows of all seven matrices in one batch call.  At N = 8 the k / v shares are 128 rows: fewer rows than CTAs,
+    so most CTAs stream nothing for those ops but still walk the ring and the barriers."""
+    mats = [(backend.Q4_K, 8192, 8192), (backend.Q4_K, 1024, 8192), (backend.Q4_K, 1024, 8192), (backend.Q4_K, 8192, 8192),
+            (backend.Q4_K, 28672, 8192), (backend.Q4_K, 28672, 8192), (backend.Q6_K, 8192, 28672)]
+    ws, xs, ys, refs = [], [], [], []
+    for i, (dt, out, cols) in enumerate(mats):
+        rows = out // world
+        gw, ow = make(ctx, dt, rows, cols, 300 + i)
+        x = synth.normal(310 + i, cols)
+        ws.append(gw), xs.append(dev_f32(x)), ys.append(torch.zeros(rows, device="cuda"))
+        refs.append(oracle.matvec_q(ow, x))
+    st = torch.cuda.Stream()
+    backend.WeightBatch(ctx, ws, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys]).launch(st.cuda_stream)
+    st.synchronize()
+    ctx.synchronize()
+    assert ctx.last_plan()["grid"] == -2, "the chain kernel did not run"
+    for y, ref in zip(ys, refs):
+        assert synth.rel_err(y.cpu().numpy(), ref) < TOL

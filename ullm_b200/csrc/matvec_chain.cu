@@ -297,6 +297,10 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     const int budget = dev.max_smem_optin - 1024;
     uint32_t max_stage = 0, max_part = 128, max_prep = 0;
     const uint32_t grid = (uint32_t)dev.sm_count;
+    // tiles of up to 100 KB (four rows per warp on wide matrices) when ring, partials and activation images then
+    // still fit; else the plan is redone with tiles of up to 56 KB
+    for (uint32_t tile_cap : {100u * 1024u, 56u * 1024u}) {
+    max_stage = 0, max_part = 128, max_prep = 0;
     for (int i = 0; i < n; ++i) {
         const MatvecChainOp &h = ops[i];
         if (!matvec_chain_supported(h.fmt, h.out_dim, h.in_dim, h.epi)) return cudaErrorNotSupported;
@@ -319,7 +323,7 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         o.rw = 0;
         for (uint32_t rw = 4; rw >= rw_min; rw /= 2) {
             const uint32_t R = o.WR * rw;
-            if (R % o.gran || (uint64_t)R * o.row_bytes > 100 * 1024) continue;
+            if (R % o.gran || (uint64_t)R * o.row_bytes > tile_cap) continue;
             if (rw > rw_min && o.WR * (rw / 2) >= rows_cta && (o.WR * (rw / 2)) % o.gran == 0) continue;
             o.rw = rw;
             break;
@@ -335,7 +339,9 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     p.off_prep = align_up_u32(p.off_part + max_part, 128);
     p.off_ring = align_up_u32(p.off_prep + max_prep, 128);
     p.stage_bytes = max_stage;
-    if ((int)p.off_ring + 2 * (int)max_stage > budget) return cudaErrorNotSupported;
+    if ((int)p.off_ring + 2 * (int)max_stage <= budget) break;
+    if (tile_cap == 56u * 1024u) return cudaErrorNotSupported;
+    }
     p.S = std::min<uint32_t>(8, (uint32_t)(budget - (int)p.off_ring) / max_stage);
     const uint32_t smem = p.off_ring + p.S * max_stage;
     static bool attr_set[64] = {};
