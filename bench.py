@@ -632,6 +632,8 @@ def run_multi(args):
         for i in range(max(args.warmup, 3)):
             step(i)
     torch.cuda.synchronize()
+    # the batch call is one persistent launch when the chain kernel takes the list, else one launch per matrix
+    launches_per_step = 1 if ctx.last_plan()["grid"] == -2 else len(mats)
     graph = None
     if args.multi_graph:
         try:
@@ -706,7 +708,7 @@ def run_multi(args):
             "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * sum(c for _, _, _, c in C4_MATS),
                     "d2h_bytes_per_step": 4 * world * rows_total, "us_per_step": e2e_s * 1e6,
                     "api": "pinned host x -> ullm_cuda_weight_matvec_dev x7 -> NCCL all-gather -> pinned host y"},
-            "gpu_launches": 7 * args.steps,
+            "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
