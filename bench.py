@@ -159,6 +159,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; this arm is the CPU path with every host thread it can
+    # use, so the setting is lifted before the oracle library (and with it the OpenMP runtime) is loaded
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     factory = cpu_c1_step_factory if args.gpus == 1 else cpu_c4_step_factory
     workload = "c1_q6k_ffn_pair" if args.gpus == 1 else "c4_70b_layer_matvec"
     # Size the per-step sample so that warmup + steps end within ~2 minutes.
