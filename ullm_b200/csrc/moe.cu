@@ -533,8 +533,15 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
         const float *x = d_x + t0 * e.hidden;
         uint32_t *idx = d_idx ? d_idx + t0 * k : idx_s;
         float *wts = d_wts ? d_wts + t0 * k : wts_s;
-        moe_route_kernel<<<1, 256, 0, st>>>(d_logits + t0 * e.n_experts, (int)nt, (int)e.n_experts, (int)k, idx, wts, route);
-        cudaError_t err = cudaGetLastError();
+        // the small kernels take part in the programmatic-dependent chain as well (both wait for their
+        // predecessor with griddepcontrol.wait before they read anything it wrote)
+        cudaLaunchAttribute pat[1];
+        pat[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        pat[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t rc_cfg = {};
+        rc_cfg.gridDim = dim3(1), rc_cfg.blockDim = dim3(256), rc_cfg.stream = st, rc_cfg.attrs = pat, rc_cfg.numAttrs = pdl ? 1 : 0;
+        cudaError_t err = cudaLaunchKernelEx(&rc_cfg, moe_route_kernel, d_logits + t0 * e.n_experts, (int)nt, (int)e.n_experts, (int)k, idx,
+                                             wts, route);
         if (err != cudaSuccess) return err;
 
         MoePlanInt pg, pd;
@@ -581,9 +588,10 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
             if ((err = cudaGetLastError()) != cudaSuccess) return err;
         }
         const uint32_t n = nt * (uint32_t)e.hidden;
-        moe_combine_kernel<<<(n + 255) / 256, 256, 0, st>>>(down, wts, d_y + t0 * e.hidden, nt, (uint32_t)k, (uint32_t)e.hidden,
-                                                             d_res ? d_res + t0 * e.hidden : nullptr);
-        if ((err = cudaGetLastError()) != cudaSuccess) return err;
+        rc_cfg.gridDim = dim3((n + 255) / 256);
+        err = cudaLaunchKernelEx(&rc_cfg, moe_combine_kernel, (const float *)down, (const float *)wts, d_y + t0 * e.hidden, nt, (uint32_t)k,
+                                 (uint32_t)e.hidden, (const float *)(d_res ? d_res + t0 * e.hidden : nullptr));
+        if (err != cudaSuccess) return err;
     }
     return cudaSuccess;
 }
