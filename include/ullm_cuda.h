@@ -218,7 +218,7 @@ int ullm_cuda_moe_ffn_dev(ullm_cuda_ctx *ctx, const ullm_cuda_experts *e, const 
  * cudaMalloc behind its back fails or steals from it) and latency-critical loops
  * that cannot take cudaMalloc's device-wide synchronisation.  Every array of
  * `dev_experts`, and `d_x` / `d_logits` / `d_y`, are device pointers the caller
- * owns (16-byte aligned); the kernels' scratch lives in a fixed array inside the
+ * owns (the expert arrays and `d_x` 16-byte aligned, else ULLM_ERR_FORMAT); the kernels' scratch lives in a fixed array inside the
  * library, ULLM_CUDA_MOE_NOALLOC_SCRATCH_BYTES on every GPU that loads it.
  *  - Problems needing more scratch (roughly 128*(hidden+inter)*4 bytes + 16 KB)
  *    are rejected with ULLM_ERR_FORMAT.
@@ -226,7 +226,9 @@ int ullm_cuda_moe_ffn_dev(ullm_cuda_ctx *ctx, const ullm_cuda_experts *e, const 
  *    start-up, before any stream capture.
  *  - The array is shared by all calls and keeps the previous call's contents;
  *    calls whose kernels overlap on the GPU race on it — serialise them.
- *  - Blocks until the result is in `d_y`.  Never calls cudaMalloc / cudaFree.
+ *  - Blocks until the result is in `d_y` (waits for `stream` only, not for the
+ *    device), so it cannot be part of a stream capture.  Never calls cudaMalloc /
+ *    cudaFree.  The calling thread's current device is restored before returning.
  * `err` (may be NULL) receives a message on failure. */
 #define ULLM_CUDA_MOE_NOALLOC_SCRATCH_BYTES (4u << 20)
 int ullm_cuda_moe_ffn_noalloc(int device, const ullm_moe_experts_input *dev_experts, const float *d_x,

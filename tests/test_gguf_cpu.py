@@ -111,6 +111,10 @@ def test_alignment_shape_order_and_offsets():
         assert [x["name"] for x in g.tensors()] == ["w.f32", "w.q4k", "w.f16"]  # file order
     # general.alignment = 0 is raised to 1 (lib.rs:123-128)
     assert gguf.Gguf(gguf.write_gguf([("general.alignment", T_U32, 0)], [])).alignment == 1
+    # a negative i32 widens to a huge u64 (value.rs:49): rounding the data offset up to it must not wrap to 0
+    with pytest.raises(gguf.GgufError) as e:
+        gguf.Gguf(gguf.write_gguf([("general.alignment", T_I32, -32)], [("w", 0, (8,), np.zeros(8, np.float32))]))
+    assert e.value.code == gguf.ERR_FORMAT
 
 
 def test_tensor_past_the_end_and_ragged_block_counts():

@@ -33,7 +33,8 @@ def sources() -> list[str]:
 
 def _headers_mtime() -> float:
     hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
-    hs.append(os.path.join(os.path.dirname(HERE), "include", "ullm_cuda.h"))
+    inc = os.path.join(os.path.dirname(HERE), "include")
+    hs += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
     return max(os.path.getmtime(h) for h in hs)
 
 

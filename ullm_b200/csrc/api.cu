@@ -778,6 +778,8 @@ int ullm_cuda_moe_ffn_dev(ullm_cuda_ctx *c, const ullm_cuda_experts *x, const fl
                           size_t n_tok, size_t k, float *d_y, uint32_t *d_idx, float *d_wts, void *stream) {
     if (!c || !x || !d_x || !d_logits || !d_y) return ULLM_ERR_INVALID;
     if (const char *m = moe_shape_error(x->e, n_tok, k)) return ctx_fail(c, ULLM_ERR_FORMAT, "%s", m);
+    if ((uintptr_t)d_x % 16 || (uintptr_t)d_y % 4 || (uintptr_t)d_logits % 4 || (uintptr_t)d_idx % 4 || (uintptr_t)d_wts % 4)
+        return ctx_fail(c, ULLM_ERR_FORMAT, "d_x must be 16-byte aligned, d_logits / d_y / d_idx / d_wts 4-byte aligned");
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
     cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
     int streamed = 0;

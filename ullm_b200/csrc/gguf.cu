@@ -179,6 +179,8 @@ struct ullm_gguf {
             if (a->is_int()) alignment = a->u;
         if (alignment < 1) alignment = 1;
         const uint64_t info_end = r.pos;
+        // an alignment beyond the file (a negative i32 read as u64, say) would wrap the round-up below
+        if (alignment > len) fail(ULLM_GGUF_ERR_FORMAT, "general.alignment %llu exceeds the file size", (unsigned long long)alignment);
         data_start = (info_end + alignment - 1) / alignment * alignment;
         for (Raw &rw : raws) {
             Tensor &t = rw.t;
@@ -245,7 +247,12 @@ int ullm_gguf_open(const char *path, ullm_gguf **out, char *err, size_t err_cap)
         return ULLM_GGUF_ERR_IO;
     }
     struct stat st;
-    if (fstat(fd, &st) != 0 || st.st_size <= 0) {
+    if (fstat(fd, &st) != 0) {
+        close(fd);
+        put_err(err, err_cap, "cannot stat the file");
+        return ULLM_GGUF_ERR_IO;
+    }
+    if (st.st_size <= 0) {
         close(fd);
         put_err(err, err_cap, st.st_size == 0 ? "unexpected end of file" : "cannot stat the file");
         return st.st_size == 0 ? ULLM_GGUF_ERR_FORMAT : ULLM_GGUF_ERR_IO;

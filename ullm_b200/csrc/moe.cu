@@ -22,6 +22,7 @@
 #include "matvec_core.cuh"
 
 #include <algorithm>
+#include <climits>
 
 namespace ullm {
 
@@ -55,30 +56,36 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
         for (int i = lane; i < n_exp; i += 32) l[i] = logits[(size_t)t * n_exp + i];
         __syncwarp();
         float mx = 0.f, wsum = 0.f, mine = 0.f;
+        // Experts are ranked by the total order on f32 bit patterns (descending, lower index first among equal
+        // patterns): the order the reference sorts by (total_cmp, lib.rs:1457).  It also ranks NaN, so a token
+        // whose logits are all NaN still selects k distinct experts in range; its weights come out NaN, as in
+        // the reference.  `taken` marks this lane's experts (bit m = expert lane + 32 m) already selected.
+        uint32_t taken = 0u;
         for (int j = 0; j < k; ++j) {
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-            for (int i = lane; i < n_exp; i += 32) {
-                const float v = l[i];
-                if (v > bv || (v == bv && i < bi)) bv = v, bi = i; // first index wins
+            int bk = INT_MIN, bi = 0x7fffffff;
+            for (int i = lane, m = 0; i < n_exp; i += 32, ++m) {
+                if ((taken >> m) & 1u) continue;
+                int key = __float_as_int(l[i]);
+                key ^= (key >> 31) & 0x7fffffff;
+                if (key > bk || (key == bk && i < bi)) bk = key, bi = i;
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
                 const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+                if (ok > bk || (ok == bk && oi < bi)) bk = ok, bi = oi;
             }
+            // k <= n_exp (checked on the host), so an untaken expert always exists and bi is in range
+            if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+            const float bv = l[bi];
             // softmax over the k selected logits (lib.rs:1460-1475): the first is the max
             if (j == 0) mx = bv;
             const float e = expf(bv - mx);
             wsum += e; // summed in selection order, identically in every lane
             if (lane == j) mine = e;
-            if (lane == 0) {
-                sel[t * k + j] = bi;
-                l[bi] = -INFINITY; // taken
-            }
-            __syncwarp();
+            if (lane == 0) sel[t * k + j] = bi;
         }
+        __syncwarp();
         if (lane < k) {
             wts[t * k + lane] = mine / wsum;
             idx[t * k + lane] = (uint32_t)sel[t * k + lane];
@@ -525,7 +532,8 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
     uint32_t *idx_s = (uint32_t *)(down + pairs_cap * e.hidden);
     float *wts_s = (float *)(idx_s + pairs_cap);
     const uint32_t tb = (uint32_t)e.table_bytes;
-    const bool aligned = ((uintptr_t)d_x % 16 == 0);
+    // both the streamed and the plain kernels read x with 128-bit loads: callers check this before launching
+    if ((uintptr_t)d_x % 16 || (uintptr_t)d_y % 4 || (uintptr_t)d_logits % 4) return cudaErrorMisalignedAddress;
     if (streamed_out) *streamed_out = 0;
 
     for (size_t t0 = 0; t0 < n_tok; t0 += MOE_MAX_TOK) {
@@ -545,7 +553,7 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
         if (err != cudaSuccess) return err;
 
         MoePlanInt pg, pd;
-        if (!force_generic && aligned) {
+        if (!force_generic) {
             pg = plan_moe(dev, true, (uint32_t)e.inter, (uint32_t)e.hidden, (uint32_t)e.group, (int)tb, nt, (uint32_t)e.n_experts);
             pd = plan_moe(dev, false, (uint32_t)e.hidden, (uint32_t)e.inter, (uint32_t)e.group, (int)tb, nt, (uint32_t)e.n_experts);
         }

@@ -24,6 +24,10 @@
 //  * The first call on a device looks up the device address of the array (and
 //    sets the kernels' shared-memory attribute).  Make that first call during
 //    start-up, before any stream capture begins.
+//  * The call blocks: it waits for its kernels on `stream` and reads the status
+//    word back before it returns (only that stream is waited for, never the whole
+//    device).  The calling thread's current device is the same after the call as
+//    before it.
 //  * No cudaMalloc, cudaFree or allocating library routine is called on any path
 //    through this function.
 #include "../../include/ullm_cuda.h"
@@ -67,6 +71,8 @@ extern "C" int ullm_cuda_moe_ffn_noalloc(int device, const ullm_moe_experts_inpu
                                          char *err, size_t err_cap) {
     if (err && err_cap) err[0] = 0;
     if (!dev_experts || !d_x || !d_logits || !d_y) return fail(err, err_cap, ULLM_ERR_INVALID, "null argument");
+    if ((uintptr_t)d_x % 16 || (uintptr_t)d_logits % 4 || (uintptr_t)d_y % 4)
+        return fail(err, err_cap, ULLM_ERR_FORMAT, "d_x must be 16-byte aligned, d_logits and d_y 4-byte aligned");
     if (device < 0 || device >= kMaxDevices) return fail(err, err_cap, ULLM_ERR_INVALID, "device index out of range");
     const ullm_moe_experts_input &in = *dev_experts;
     const void *ptrs[9] = {in.gate_w, in.gate_scales, in.gate_biases, in.up_w,       in.up_scales,
@@ -91,6 +97,17 @@ extern "C" int ullm_cuda_moe_ffn_noalloc(int device, const ullm_moe_experts_inpu
                     "this problem needs %zu bytes of scratch, the built-in array holds %u: use ullm_cuda_moe_ffn_dev", need,
                     (unsigned)ULLM_CUDA_MOE_NOALLOC_SCRATCH_BYTES);
 
+    // the caller's current device is put back on every way out
+    struct DeviceGuard {
+        int prev = -1;
+        ~DeviceGuard() {
+            if (prev >= 0) cudaSetDevice(prev);
+        }
+    } guard;
+    if (cudaGetDevice(&guard.prev) != cudaSuccess) {
+        cudaGetLastError();
+        guard.prev = -1;
+    }
     cudaError_t ce = cudaSetDevice(device);
     if (ce != cudaSuccess) return fail(err, err_cap, ULLM_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(ce));
     PerDevice &pd = g_dev[device];
@@ -125,10 +142,11 @@ extern "C" int ullm_cuda_moe_ffn_noalloc(int device, const ullm_moe_experts_inpu
         return fail(err, err_cap, ULLM_ERR_CUDA, "launch: %s", cudaGetErrorString(ce));
     }
     // Blocks like the other host-facing calls, then reports a kernel that gave up on
-    // a bounded wait.  The copy lands in a stack variable: no allocation.
-    ce = cudaStreamSynchronize(st);
+    // a bounded wait.  The status word is copied on the same stream into a stack
+    // variable (no allocation), so only this stream is waited for.
     int status = 0;
-    if (ce == cudaSuccess) ce = cudaMemcpy(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    ce = cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
     if (ce != cudaSuccess) return fail(err, err_cap, ULLM_ERR_CUDA, "synchronize: %s", cudaGetErrorString(ce));
     if (status != DEV_OK) return fail(err, err_cap, ULLM_ERR_TIMEOUT, "a device-side bounded wait expired");
     return ULLM_OK;
