@@ -1,23 +1,27 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized matvec hot path (BASELINE.json's metric: achieved
-HBM GB/s of the dequant-in-kernel matvec).
+"""Benchmark of the quantized matvec hot path: achieved HBM GB/s of the dequant-in-kernel matvec,
+with decode tokens/s and prefill TFLOP/s as secondary figures.
 
-One JSON line on stdout.  A *step* is one pass of the hot path over one batch of
-synthetic input:
+One JSON line on stdout.  A *step* is one pass of the hot path over one batch of synthetic input.
+At every ``--gpus N`` the workload is ``c4_70b_layer_matvec``: the seven matrices of one
+Llama-3-70B-shaped block (Q4_K q, k, v, o, gate, up; Q6_K down) as batch-1 matvecs, each with its own
+seeded input vector — the largest configuration that fits one GPU and the one that shards.
 
-* ``--gpus 1`` — workload ``c1_q6k_ffn_pair``: the Q6_K matvec [14336, 4096]
-  followed by the companion Q6_K down-projection [4096, 14336] on its result.
-  Weights are resident; successive steps walk distinct device copies of the two
-  matrices whose total exceeds L2 several times over, so every step reads HBM.
-* ``--gpus N`` (N > 1, under torchrun) — workload ``c4_70b_layer_matvec``: the
-  seven matrices of one Llama-3-70B-shaped block, output rows split evenly over
-  the ranks, followed by an NCCL all-gather of each output vector.
+* N = 1: resident weight objects, seven launches per step through ``ullm_cuda_weight_matvec_dev``.
+* N > 1 (one process per GPU under torchrun): output rows split evenly over the ranks
+  (``ullm_cuda_shard_*``); each rank runs its slices as one persistent launch whose epilogue stores
+  the rows into every rank's gather buffer over NVLink, then publishes a step number and waits for
+  the others' (no NCCL on the data path).  ``--exchange nccl`` runs the comparison arm instead:
+  the same kernels followed by an ``ncclAllGather``.  torch.distributed only carries the set-up
+  (handle exchange) and the max-over-ranks of the timings.
 
-``value`` is device-timed (CUDA events on the launching stream, max over ranks);
-``e2e`` goes through the host-buffer entry point ``ullm_cuda_weight_matvec`` with
-pinned host activations (host<->device copies inside the timed region).
-``--impl reference`` times the CPU restatement of the reference's path (the
-oracle port, OpenMP over rows) on the host cores for the same workload.
+The K timed steps are captured in one CUDA graph, replayed ``--replays`` times with CUDA events
+between the replays on the launching stream; ``ms_per_step`` is the median replay (max over ranks),
+with the minimum and maximum beside it.  ``e2e`` goes through the host-buffer entry points
+(``ullm_cuda_weight_matvec_batch`` / ``ullm_cuda_shard_matvec``) with pinned host vectors, copies
+inside the timed region.  ``--impl reference`` times the CPU restatement of the reference's path
+(OpenMP over rows) on the host cores for the same workload.  At N = 1 the line also carries a
+``secondary`` object: the other benchmark configurations measured the same way.
 """
 from __future__ import annotations
 
@@ -40,19 +44,26 @@ from ullm_b200 import shard, synth  # noqa: E402
 C1_UP = (14336, 4096)
 C1_DOWN = (4096, 14336)
 C1_BYTES_PER_LAUNCH = 48_168_960 + 16_384 + 57_344  # weights + x + y (either launch)
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
-# from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_PER_LAUNCH = {"c1_q6k_ffn_pair": (48_236_032 + 48_276_992) // 2}  # dram read + write of the two launches, ncu capture under profiles/
 
 C4_MATS = [  # name, dtype, out, in   (one Llama-3-70B block)
     ("q", synth.Q4_K, 8192, 8192), ("k", synth.Q4_K, 1024, 8192), ("v", synth.Q4_K, 1024, 8192),
     ("o", synth.Q4_K, 8192, 8192), ("gate", synth.Q4_K, 28672, 8192), ("up", synth.Q4_K, 28672, 8192),
     ("down", synth.Q6_K, 8192, 28672),
 ]
+METRIC = "quantized_matvec_hbm_gbs"
+DTYPE = "u8 x s16 integer dot products (x as 16-bit fixed point per 32/64 values), f32 scale and accumulate"
+# dram__bytes_read.sum + dram__bytes_write.sum of one step's kernels at N = 1, from an ncu capture of this
+# workload (None until one has been taken)
+NCU_TRAFFIC_PER_STEP = {"c4_70b_layer_matvec": None}
 
 
 def weight_bytes(dtype, out, cols):
     return out * (cols // 256) * (144 if dtype == synth.Q4_K else 210)
+
+
+def c4_step_bytes():
+    """Algorithmic bytes of one step: packed weights + 4 bytes per input and per output element."""
+    return sum(weight_bytes(dt, o, c) + 4 * (o + c) for _, dt, o, c in C4_MATS)
 
 
 def measured_peak_tflops():
@@ -84,7 +95,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.idx)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -154,26 +165,28 @@ def cpu_c4_step_factory(frac: float = 1.0):
     return step, oracle.max_threads(), nbytes, f"first {frac:.3f} of the rows of each of the 7 matrices"
 
 
+def _lift_omp_limit():
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU legs are the reference's path with every host
+    # thread it can use, so the setting is lifted before the oracle library (and its OpenMP runtime) is loaded
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
+
 def run_reference(args):
     """The reference's CPU path (oracle port) on the host cores, same workload and metric."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    # torchrun exports OMP_NUM_THREADS=1 to its workers; this arm is the CPU path with every host thread it can
-    # use, so the setting is lifted before the oracle library (and with it the OpenMP runtime) is loaded
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
-        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
-    factory = cpu_c1_step_factory if args.gpus == 1 else cpu_c4_step_factory
-    workload = "c1_q6k_ffn_pair" if args.gpus == 1 else "c4_70b_layer_matvec"
+    _lift_omp_limit()
     # Size the per-step sample so that warmup + steps end within ~2 minutes.
-    probe, cores, pbytes, _ = factory(1.0 / 16)
+    probe, cores, pbytes, _ = cpu_c4_step_factory(1.0 / 32)
     probe()
     t0 = time.perf_counter()
     probe()
     t_probe = time.perf_counter() - t0
     budget = 120.0 / max(1, args.steps + args.warmup)
-    frac = min(1.0, (1.0 / 16) * budget / max(t_probe, 1e-6))
-    step, cores, nbytes, sample = factory(frac)
+    frac = min(1.0, (1.0 / 32) * budget / max(t_probe, 1e-6))
+    step, cores, nbytes, sample = cpu_c4_step_factory(frac)
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
@@ -182,10 +195,10 @@ def run_reference(args):
     dt = time.perf_counter() - t0
     gbs = args.steps * nbytes / dt / 1e9
     line = {
-        "impl": "reference", "metric": "quantized_matvec_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload, "note": "C restatement of ullm-model's CPU path (rayon -> OpenMP over rows); the Rust reference cannot be built here"},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c4_70b_layer_matvec", "note": "C restatement of ullm-model's CPU path (rayon -> OpenMP over rows); the Rust reference cannot be built here"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": f"{args.steps} steps, each over {sample}"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -196,331 +209,463 @@ def run_reference(args):
 # ---------------------------------------------------------------------------
 # CUDA arm
 # ---------------------------------------------------------------------------
-def run_single(args):
-    import torch
-
-    from ullm_b200 import backend
-
-    torch.cuda.set_device(0)
-    ctx = backend.CudaContext(0)
-    stream = torch.cuda.current_stream().cuda_stream
-    dev = torch.device("cuda:0")
-
-    w_up_h = synth.gen_q6k(*C1_UP, synth.seed_for(1, 0))
-    w_dn_h = synth.gen_q6k(*C1_DOWN, synth.seed_for(1, 1))
-    x_h = synth.normal(synth.seed_for(1, 2), C1_UP[1])
-    ncopies = args.copies  # 2 * 48 MB per copy; the walk must exceed L2 (126 MB) several times
-    # resident weight objects (what GpuForward::new builds from a GpuWeight): one device copy each
-    ups = [backend.Weight(ctx, backend.Q6_K, w_up_h, *C1_UP) for _ in range(ncopies)]
-    dns = [backend.Weight(ctx, backend.Q6_K, w_dn_h, *C1_DOWN) for _ in range(ncopies)]
-    x = torch.from_numpy(x_h).to(dev)
-    h = torch.empty(C1_UP[0], dtype=torch.float32, device=dev)
-    y = torch.empty(C1_DOWN[0], dtype=torch.float32, device=dev)
-
-    # the pair as one persistent launch (up, then down behind a grid barrier) or as two launches
-    chains = [backend.WeightChain(ctx, [dict(w=ups[c], x=x.data_ptr(), y=h.data_ptr()),
-                                        dict(w=dns[c], x=h.data_ptr(), y=y.data_ptr(), dep=True)]) for c in range(ncopies)]
-
-    def step(i):
-        c = i % ncopies
-        if args.chain:
-            chains[c].launch(stream)
-        else:
-            ups[c].matvec_dev(x.data_ptr(), h.data_ptr(), stream)
-            dns[c].matvec_dev(h.data_ptr(), y.data_ptr(), stream)
-
-    if args.pdl:
-        ctx.debug_set("pdl", 1)
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    plan = ctx.last_plan()
-
-    # The K timed steps are captured into one CUDA graph and replayed, so the host's
-    # launch rate (a few microseconds per call from Python) is not what is measured.
+def time_graph(torch, step, steps, warmup, replays, before_timing=None):
+    """``step(i, stream)`` enqueues step i.  The ``steps`` timed steps are captured in one CUDA graph on a
+    non-default stream and replayed ``replays`` times back to back with an event between replays; returns the
+    per-replay times in ms.  (A NULL stream handle would mean "the context's own stream" to the library, so the
+    default stream is never used.)"""
     side = torch.cuda.Stream()
-    graph = None
-    if not args.eager:
-        stream = side.cuda_stream
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(args.steps):
-                step(args.warmup + i)
-        graph.replay()  # one untimed replay
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(0)
-    sampler.start()
-    time.sleep(0.3)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
     with torch.cuda.stream(side):
-        ev0.record()
-        if graph is not None:
-            graph.replay()
-        else:
-            stream = side.cuda_stream
-            for i in range(args.steps):
-                step(args.warmup + i)
-        ev1.record()
-    torch.cuda.synchronize()
-    ctx.synchronize()  # surfaces a device-side timeout status
-    ms = ev0.elapsed_time(ev1)
-
-    # end to end: host buffers in, host buffers out, through matvec_resident
-    xp = torch.from_numpy(x_h).pin_memory().numpy()
-    hp = torch.empty(C1_UP[0], dtype=torch.float32).pin_memory().numpy()
-    yp = torch.empty(C1_DOWN[0], dtype=torch.float32).pin_memory().numpy()
-
-    def e2e_step(i):
-        c = i % ncopies
-        ups[c].matvec(xp, out=hp)
-        dns[c].matvec(hp, out=yp)
-
-    for i in range(args.warmup):
-        e2e_step(i)
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(args.warmup + i)
-    e2e_s = time.perf_counter() - t0
-    clocks = sampler.stop()
-
-    # parity spot check of what was timed (64 rows of the final output)
-    y_host = y.cpu().numpy()
-    check = {"rel_err_vs_e2e": synth.rel_err(y_host, yp)}
-
-    step_bytes = 2 * C1_BYTES_PER_LAUNCH
-    value = args.steps * step_bytes / (ms * 1e-3) / 1e9
-    per_launch = 2 if args.chain else 1  # matrices streamed by one launch
-    launch_us = ms * 1e3 / (2 * args.steps) * per_launch
-    peak, peak_kind = measured_peak_gbs()
-    achieved = per_launch * C1_BYTES_PER_LAUNCH / (launch_us * 1e-6) / 1e9
-
-    cpu = None
-    if not args.no_cpu:
-        cstep, cores, _, _ = cpu_c1_step_factory()
-        cstep()
-        t0 = time.perf_counter()
-        n = 0
-        while n < 3 or (time.perf_counter() - t0 < 10.0 and n < 200):
-            ref = cstep()
-            n += 1
-        cdt = (time.perf_counter() - t0) / n
-        check["rel_err_vs_cpu"] = synth.rel_err(y_host, ref)
-        cpu = {"value": step_bytes / cdt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-               "sample": f"{n} full steps of c1_q6k_ffn_pair, {cdt * 1e3:.1f} ms each"}
-
-    line = {
-        "metric": "quantized_matvec_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8 dot products (16-bit fixed-point x) + f32 accumulate", "data": "synthetic",
-        "config": {"workload": "c1_q6k_ffn_pair", "shapes": "Q6_K [14336,4096] then Q6_K [4096,14336], batch 1",
-                   "l2": f"{ncopies} distinct weight copies ({ncopies * 96} MB) walked round-robin: inputs larger than L2",
-                   "plan": plan, "pdl": bool(args.pdl), "launch": "eager" if args.eager else "one CUDA graph of all timed steps",
-                   "frac_of_8000": value / 8000.0},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": per_launch * NCU_TRAFFIC_PER_LAUNCH["c1_q6k_ffn_pair"], "peak_kind": f"of {peak_kind}",
-                     "kernel": "matvec_chain_kernel (both matrices, one persistent launch)" if args.chain else "matvec_stream_kernel<Q6_K prepared>",
-                     "launch_us": launch_us, "algorithmic_bytes_per_launch": per_launch * C1_BYTES_PER_LAUNCH},
-        "cpu_baseline": cpu,
-        "e2e": {"value": args.steps * step_bytes / e2e_s / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": 4 * (C1_UP[1] + C1_DOWN[1]), "d2h_bytes_per_step": 4 * (C1_UP[0] + C1_DOWN[0]),
-                "us_per_step": e2e_s / args.steps * 1e6, "api": "ullm_cuda_weight_matvec (resident weight, pinned host x / y)"},
-        "gpu_launches": (1 if args.chain else 2) * args.steps,
-        "clocks": clocks,
-        "check": check,
-    }
-    print(json.dumps(line), flush=True)
-    return 0
-
-
-def _time_steps(torch, step, steps, warmup):
-    """step(i, stream) enqueues step i; the timed steps run as one CUDA graph."""
-    cur = torch.cuda.current_stream().cuda_stream
-    for i in range(warmup):
-        step(i, cur)
-    torch.cuda.synchronize()
-    side = torch.cuda.Stream()
+        for i in range(warmup):
+            step(i, side.cuda_stream)
+    side.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=side):
         for i in range(steps):
             step(warmup + i, side.cuda_stream)
-    graph.replay()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(side):
-        ev0.record()
-        graph.replay()
-        ev1.record()
+        graph.replay()  # one untimed replay
     torch.cuda.synchronize()
-    return ev0.elapsed_time(ev1)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+    if before_timing:
+        before_timing()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        evs[0].record()
+        for r in range(replays):
+            graph.replay()
+            evs[r + 1].record()
+    torch.cuda.synchronize()
+    return [evs[r].elapsed_time(evs[r + 1]) for r in range(replays)]
 
 
-def run_other(args):
-    """Single-GPU measurements of the other benchmark configurations (parity-test
-    cases; reported for the design notes, not the headline line)."""
-    import torch
+def spread(ms_list, steps):
+    per = sorted(m / steps for m in ms_list)
+    return {"median": statistics.median(per), "min": per[0], "max": per[-1], "replays": len(per)}
 
-    from ullm_b200 import backend
 
-    torch.cuda.set_device(0)
-    ctx = backend.CudaContext(0)
-    stream = torch.cuda.current_stream().cuda_stream
-    dev = torch.device("cuda:0")
-    peak, peak_kind = measured_peak_gbs()
-    if args.pdl:
-        ctx.debug_set("pdl", 1)
-    out = {"workload": args.workload, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "pdl": bool(args.pdl)}
+def oracle_rows(dt, w, cols, r0, n, x):
+    """The oracle's product for rows [r0, r0 + n) of a row-major quantized matrix."""
+    import oracle
 
-    if args.workload == "c0":
-        shape = (4096, 4096)
-        w = synth.gen_q4k(*shape, synth.seed_for(0, 0))
-        n = 40  # 9.4 MB each: 377 MB walked round-robin
-        ws = [backend.Weight(ctx, backend.Q4_K, w, *shape) for _ in range(n)]
-        x = torch.from_numpy(synth.normal(synth.seed_for(0, 1), shape[1])).to(dev)
-        y = torch.empty(shape[0], dtype=torch.float32, device=dev)
-        ms = _time_steps(torch, lambda i, st: ws[i % n].matvec_dev(x.data_ptr(), y.data_ptr(), st), args.steps, args.warmup)
-        nbytes = weight_bytes(synth.Q4_K, *shape) + 4 * sum(shape)
-        out.update(us_per_launch=ms * 1e3 / args.steps, gbs=args.steps * nbytes / ms / 1e6, bytes_per_launch=nbytes, plan=ctx.last_plan())
-    elif args.workload == "c4":
-        mats = []
-        for i, (name, dt, o, c) in enumerate(C4_MATS):
-            w = synth.gen_weight(dt, o, c, synth.seed_for(4, i))
-            mats.append((backend.Weight(ctx, dt, w, o, c), torch.from_numpy(synth.normal(synth.seed_for(4, 8 + i), c)).to(dev),
-                         torch.empty(o, dtype=torch.float32, device=dev)))
+    rb = cols // 256 * (144 if dt == synth.Q4_K else 210)
+    blk = np.ascontiguousarray(np.asarray(w).reshape(-1).view(np.uint8)[r0 * rb:(r0 + n) * rb])
+    return oracle.matvec_q(oracle.Weight(dt, blk, n, cols), x)
 
-        def step(_i, st):
-            for w, xv, yv in mats:
-                w.matvec_dev(xv.data_ptr(), yv.data_ptr(), st)
 
-        ms = _time_steps(torch, step, args.steps, args.warmup)
-        nbytes = sum(weight_bytes(dt, o, c) + 4 * (o + c) for _, dt, o, c in C4_MATS)
-        out.update(us_per_step=ms * 1e3 / args.steps, gbs=args.steps * nbytes / ms / 1e6, bytes_per_step=nbytes)
-    elif args.workload == "c4gemm":
-        # the same block as a prefill GEMM: 512 tokens through every matrix (tcgen05 path)
-        S = args.tokens
-        tf_peak = measured_peak_tflops()
-        per, total_ms, total_flop = {}, 0.0, 0.0
-        for i, (name, dt, o, c) in enumerate(C4_MATS):
-            if args.only and name != args.only:
-                continue
-            w = backend.Weight(ctx, dt, synth.gen_weight(dt, o, c, synth.seed_for(4, i)), o, c)
-            xs = torch.randn(S * c, dtype=torch.float32, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i))
-            ys = torch.empty(S * o, dtype=torch.float32, device=dev)
-            ms = _time_steps(torch, lambda _i, st: w.matmul_dev(xs.data_ptr(), ys.data_ptr(), S, st), args.steps, args.warmup)
-            flop = 2.0 * S * o * c
-            per[name] = {"us": round(ms * 1e3 / args.steps, 2), "tflops": round(args.steps * flop / ms / 1e9, 1)}
-            total_ms += ms / args.steps
-            total_flop += flop
-            assert ctx.last_plan()["grid"] == -1, "tensor-core GEMM did not run"
-            w.free()
-            del xs, ys
-        out.update(tokens=S, us_per_step=total_ms * 1e3, tflops=total_flop / total_ms / 1e9, peak_tflops=tf_peak,
-                   frac=total_flop / total_ms / 1e9 / tf_peak, per_matrix=per,
-                   note="includes the f32->bf16 activation cast kernel of every call")
-    elif args.workload == "c2":
-        ne, hid, inter, gs, ntok, k = 128, 2048, 768, 64, 8, 8
-        g = synth.gen_mlx4(ne * inter, hid, gs, synth.seed_for(2, 0))
-        u = synth.gen_mlx4(ne * inter, hid, gs, synth.seed_for(2, 1))
-        d = synth.gen_mlx4(ne * hid, inter, gs, synth.seed_for(2, 2))
-        exs = [backend.Experts(ctx, g, u, d, ne, hid, inter, gs) for _ in range(2)]  # 2 x 340 MB
-        x = torch.from_numpy(synth.normal(synth.seed_for(2, 4), ntok * hid)).to(dev)
-        lgs, dist = [], []
-        for j in range(4):
-            lg = synth.router_logits(ntok, ne, k, synth.seed_for(2, 5) + 977 * j)
-            dist.append(len(np.unique(np.argsort(-lg, axis=1)[:, :k])))
-            lgs.append(torch.from_numpy(lg).to(dev))
-        y = torch.empty(ntok * hid, dtype=torch.float32, device=dev)
-        ms = _time_steps(torch, lambda i, st: exs[i % 2].moe_ffn_dev(x.data_ptr(), lgs[i % 4].data_ptr(), ntok, k, y.data_ptr(), stream=st), args.steps, args.warmup)
-        D = sum(dist) / len(dist)
-        nbytes = D * 2_654_208 + 131_072
-        out.update(us_per_step=ms * 1e3 / args.steps, distinct_experts=D, gbs=args.steps * nbytes / ms / 1e6,
-                   bytes_per_step=nbytes, launches_per_step=4)
-    elif args.workload == "c3":
-        p = dict(synth.LLAMA_1B)
-        m = synth.gen_llama_model(p, synth.seed_for(3, 0))
-        kk, vv = synth.gen_kv_prefill(p, 1024, synth.seed_for(3, 1))
-        gf = backend.GpuForward(ctx, m, kv_f16=True)
-        gf.set_kv(0, kk, vv)
-        embd = ctx.upload(m["tok_embd"][1])
-        prompt = synth.rand_ints(synth.seed_for(3, 2), 16, 0, p["vocab"] - 1)
-        import oracle  # embedding rows for the prompt (host-side lookup, as the reference does)
+# ---- secondary workloads (N = 1): the other benchmark configurations, GPU legs only ----
+def sec_c1(torch, backend, ctx, dev, args, peak):
+    w_up_h = synth.gen_q6k(*C1_UP, synth.seed_for(1, 0))
+    w_dn_h = synth.gen_q6k(*C1_DOWN, synth.seed_for(1, 1))
+    x_h = synth.normal(synth.seed_for(1, 2), C1_UP[1])
+    n = 4  # 4 x 96 MB walked round-robin: larger than L2
+    ups = [backend.Weight(ctx, backend.Q6_K, w_up_h, *C1_UP) for _ in range(n)]
+    dns = [backend.Weight(ctx, backend.Q6_K, w_dn_h, *C1_DOWN) for _ in range(n)]
+    x = torch.from_numpy(x_h).to(dev)
+    h = torch.empty(C1_UP[0], dtype=torch.float32, device=dev)
+    y = torch.empty(C1_DOWN[0], dtype=torch.float32, device=dev)
 
-        emb_w = oracle.Weight(m["tok_embd"][0], m["tok_embd"][1], p["vocab"], p["n_embd"])
-        t0 = time.perf_counter()
-        for i, t in enumerate(prompt):
-            row = oracle.dequantize(m["tok_embd"][0], m["tok_embd"][1][int(t)], p["n_embd"])
-            lg = gf.forward(row, 1024 + i)
-        t_prompt = time.perf_counter() - t0
-        tok = int(np.argmax(lg))
-        n_gen = 128 if args.steps == 500 else args.steps  # 128 tokens unless --steps is given
-        gf.greedy(embd, m["tok_embd"][0], tok, 1040, min(8, n_gen))  # warm the greedy graph
+    def step(i, st):
+        ups[i % n].matvec_dev(x.data_ptr(), h.data_ptr(), st)
+        dns[i % n].matvec_dev(h.data_ptr(), y.data_ptr(), st)
+
+    sp = spread(time_graph(torch, step, args.steps, args.warmup, args.replays), args.steps)
+    ref_h = oracle_rows(synth.Q6_K, w_up_h, C1_UP[1], 0, C1_UP[0], x_h)
+    ref = oracle_rows(synth.Q6_K, w_dn_h, C1_DOWN[1], 0, 256, ref_h)
+    err = synth.rel_err(y.cpu().numpy()[:256], ref)
+    out = {"workload": "c1_q6k_ffn_pair", "us_per_launch": sp["median"] * 1e3 / 2, "gbs": 2 * C1_BYTES_PER_LAUNCH / (sp["median"] * 1e-3) / 1e9,
+           "ms_per_step": sp, "rel_err_vs_cpu": err}
+    out["frac"] = out["gbs"] / peak
+    for w in ups + dns:
+        w.free()
+    return out
+
+
+def sec_c0(torch, backend, ctx, dev, args, peak):
+    shape = (4096, 4096)
+    w = synth.gen_q4k(*shape, synth.seed_for(0, 0))
+    x_h = synth.normal(synth.seed_for(0, 1), shape[1])
+    n = 40  # 9.4 MB each: 377 MB walked round-robin
+    ws = [backend.Weight(ctx, backend.Q4_K, w, *shape) for _ in range(n)]
+    x = torch.from_numpy(x_h).to(dev)
+    y = torch.empty(shape[0], dtype=torch.float32, device=dev)
+    sp = spread(time_graph(torch, lambda i, st: ws[i % n].matvec_dev(x.data_ptr(), y.data_ptr(), st), args.steps, args.warmup, args.replays), args.steps)
+    nbytes = weight_bytes(synth.Q4_K, *shape) + 4 * sum(shape)
+    err = synth.rel_err(y.cpu().numpy()[:256], oracle_rows(synth.Q4_K, w, shape[1], 0, 256, x_h))
+    out = {"workload": "c0_q4k_4096", "us_per_launch": sp["median"] * 1e3, "gbs": nbytes / (sp["median"] * 1e-3) / 1e9, "ms_per_step": sp, "rel_err_vs_cpu": err}
+    out["frac"] = out["gbs"] / peak
+    for w_ in ws:
+        w_.free()
+    return out
+
+
+def sec_c2(torch, backend, ctx, dev, args, peak):
+    ne, hid, inter, gs, ntok, k = 128, 2048, 768, 64, 8, 8
+    g = synth.gen_mlx4(ne * inter, hid, gs, synth.seed_for(2, 0))
+    u = synth.gen_mlx4(ne * inter, hid, gs, synth.seed_for(2, 1))
+    d = synth.gen_mlx4(ne * hid, inter, gs, synth.seed_for(2, 2))
+    exs = [backend.Experts(ctx, g, u, d, ne, hid, inter, gs) for _ in range(2)]  # 2 x 340 MB
+    x = torch.from_numpy(synth.normal(synth.seed_for(2, 4), ntok * hid)).to(dev)
+    lgs, dist = [], []
+    for j in range(4):
+        lg = synth.router_logits(ntok, ne, k, synth.seed_for(2, 5) + 977 * j)
+        dist.append(len(np.unique(np.argsort(-lg, axis=1)[:, :k])))
+        lgs.append(torch.from_numpy(lg).to(dev))
+    y = torch.empty(ntok * hid, dtype=torch.float32, device=dev)
+    sp = spread(time_graph(torch, lambda i, st: exs[i % 2].moe_ffn_dev(x.data_ptr(), lgs[i % 4].data_ptr(), ntok, k, y.data_ptr(), stream=st),
+                           args.steps, args.warmup, args.replays), args.steps)
+    D = sum(dist) / len(dist)
+    nbytes = D * 2_654_208 + 131_072
+    out = {"workload": "c2_moe_mlx4", "us_per_step": sp["median"] * 1e3, "distinct_experts": D, "gbs": nbytes / (sp["median"] * 1e-3) / 1e9,
+           "ms_per_step": sp}
+    out["frac"] = out["gbs"] / peak
+    for e in exs:
+        e.free()
+    return out
+
+
+def sec_c3(torch, backend, ctx, dev, args, peak):
+    """Llama-3.2-1B-shaped decode: 16 prompt tokens one by one, then 128 greedy tokens kept on the device; the
+    tokens are compared with the oracle's, stored beside the tests."""
+    import oracle  # embedding rows of the prompt: host-side lookup, as the reference does (lib.rs:692-710)
+
+    p = dict(synth.LLAMA_1B)
+    m = synth.gen_llama_model(p, synth.seed_for(3, 0))
+    kk, vv = synth.gen_kv_prefill(p, 1024, synth.seed_for(3, 1))
+    gf = backend.GpuForward(ctx, m, kv_f16=True)
+    gf.set_kv(0, kk, vv)
+    embd = ctx.upload(m["tok_embd"][1])
+    prompt = synth.rand_ints(synth.seed_for(3, 2), 16, 0, p["vocab"] - 1)
+    rb = p["n_embd"] // 256 * 144
+    tab = np.asarray(m["tok_embd"][1]).reshape(-1).view(np.uint8)
+    for i, t in enumerate(prompt):
+        row = oracle.dequantize(m["tok_embd"][0], tab[int(t) * rb:(int(t) + 1) * rb], p["n_embd"])
+        lg = gf.forward(row, 1024 + i)
+    tok = int(np.argmax(lg))
+    n_gen = 128
+    gf.greedy(embd, m["tok_embd"][0], tok, 1040, 8)  # warm the greedy graph
+    times = []
+    for _ in range(3):
         t0 = time.perf_counter()
         toks = gf.greedy(embd, m["tok_embd"][0], tok, 1040, n_gen)
-        dt = time.perf_counter() - t0
-        wbytes = 16 * 38_805_504 + 215_470_080
-        kvbytes = 32_768 * (1040 + 64)
-        out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, prompt_ms_per_token=t_prompt / 16 * 1e3, tokens=n_gen,
-                   bytes_per_token=wbytes + kvbytes + 513_024, gbs=(wbytes + kvbytes + 513_024) * n_gen / dt / 1e9,
-                   first_tokens=toks[:8].tolist())
-    elif args.workload == "c2decode":
-        # Decode step of the Qwen3-30B-A3B shape (MLX 4-bit, 128 experts, 8 per token): the model the reference
-        # quotes its MoE decode rate on.  One seeded layer's weights are uploaded once per layer (separate device
-        # copies, so every layer streams its own bytes from HBM); tokens are produced by the on-device greedy loop.
-        p = dict(synth.QWEN3MOE_30B)
-        p["n_layer"] = args.layers or p["n_layer"]
-        one = synth.gen_qwen3moe_model(dict(p, n_layer=1), synth.seed_for(2, 8))
-        m = dict(one, params=p, layers=[one["layers"][0]] * p["n_layer"])
-        gf = backend.GpuForward(ctx, m, kv_f16=True, rope_neox=1, qk_norm=1)
-        t = m["tok_embd"]
-        embd = backend.Weight(ctx, t[0], t[1], t[2], t[3], t[4], t[5], t[6])
-        n_gen = 128 if args.steps == 500 else args.steps
-        gf.greedy_weight(embd, 11, 0, min(8, n_gen))  # warm the greedy graph
+        times.append(time.perf_counter() - t0)
+    dt = statistics.median(times)
+    wbytes = 16 * 38_805_504 + 215_470_080
+    kvbytes = 32_768 * (1040 + 64)
+    out = {"workload": "c3_llama1b_decode", "tok_per_s": n_gen / dt, "us_per_token": dt / n_gen * 1e6, "tokens": n_gen,
+           "gbs": (wbytes + kvbytes + 513_024) * n_gen / dt / 1e9, "runs_s": times,
+           "note": "one blocking call generates the 128 tokens on the device (argmax feeds the next embedding lookup); host wall clock"}
+    out["frac"] = out["gbs"] / peak
+    gold = os.path.join(ROOT, "tests", "golden", "c3_decode_128.npz")
+    if os.path.exists(gold):
+        g = np.load(gold)
+        same = int(np.sum(np.cumprod(toks == g["tokens"])))
+        out["check"] = {"first_token_matches": bool(tok == int(g["first"])), "leading_tokens_equal_to_oracle": same, "of": n_gen}
+    gf.free()
+    return out
+
+
+def c4_weights(backend, ctx):
+    mats = []
+    for i, (name, dt, o, c) in enumerate(C4_MATS):
+        w = synth.gen_weight(dt, o, c, synth.seed_for(4, i))
+        mats.append(dict(name=name, dt=dt, out=o, cols=c, host=w, w=backend.Weight(ctx, dt, w, o, c), xh=synth.normal(synth.seed_for(4, 8 + i), c)))
+    return mats
+
+
+def sec_c4gemm(torch, backend, ctx, dev, args, mats):
+    """The block as a 512-token prefill GEMM (tcgen05 path) on the weights already resident."""
+    S = args.tokens
+    tf_peak = measured_peak_tflops()
+    per, total_ms, total_flop, worst = {}, 0.0, 0.0, 0.0
+    for i, m in enumerate(mats):
+        o, c = m["out"], m["cols"]
+        xs = torch.randn(S * c, dtype=torch.float32, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i))
+        xs = xs.to(torch.bfloat16).to(torch.float32)  # bf16-representable activations, as the configuration states
+        ys = torch.empty(S * o, dtype=torch.float32, device=dev)
+        sp = spread(time_graph(torch, lambda _i, st: m["w"].matmul_dev(xs.data_ptr(), ys.data_ptr(), S, st), max(4, args.steps // 4), 3, args.replays),
+                    max(4, args.steps // 4))
+        assert ctx.last_plan()["grid"] == -1, "tensor-core GEMM did not run"
+        flop = 2.0 * S * o * c
+        per[m["name"]] = {"us": round(sp["median"] * 1e3, 2), "tflops": round(flop / sp["median"] / 1e9, 1)}
+        total_ms += sp["median"]
+        total_flop += flop
+        # 64 rows of the result against the oracle's f32 product of the same inputs (the 2e-2 bf16 bar)
+        import oracle
+        r0 = (o // 2) // 64 * 64
+        rb = c // 256 * (144 if m["dt"] == synth.Q4_K else 210)
+        blk = np.ascontiguousarray(np.asarray(m["host"]).reshape(-1).view(np.uint8)[r0 * rb:(r0 + 64) * rb])
+        xs_h = xs[:8 * c].cpu().numpy().reshape(8, c)
+        ref = oracle.matmul_q(oracle.Weight(m["dt"], blk, 64, c), xs_h, 8).reshape(8, 64)
+        got = ys.view(S, o)[:8, r0:r0 + 64].cpu().numpy()
+        worst = max(worst, synth.rel_err(got, ref))
+        del xs, ys
+    return {"workload": "c4_70b_layer_gemm", "tokens": S, "us_per_step": total_ms * 1e3, "tflops": total_flop / total_ms / 1e9, "peak_tflops": tf_peak,
+            "frac": total_flop / total_ms / 1e9 / tf_peak, "per_matrix": per, "rel_err_vs_cpu_64_rows_8_tokens": worst,
+            "note": "includes the f32->bf16 activation cast kernel of every call; frac of the measured cuBLAS bf16 burst"}
+
+
+def run_c4(args):
+    """The headline arm at every N."""
+    import torch
+
+    from ullm_b200 import backend
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = backend.CudaContext(local)
+    ctx.set_option(backend.OPT_PDL, 1 if args.pdl else 0)
+    peak, peak_kind = measured_peak_gbs()
+    total_bytes = c4_step_bytes()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(vals):
+        if dist is None:
+            return list(vals)
+        t = torch.tensor(list(vals), dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    check = {}
+    secondary = None
+    if world == 1:
+        mats = c4_weights(backend, ctx)
+        for m in mats:
+            m["x"] = torch.from_numpy(m["xh"]).to(dev)
+            m["y"] = torch.empty(m["out"], dtype=torch.float32, device=dev)
+        batch = backend.WeightBatch(ctx, [m["w"] for m in mats], [m["x"].data_ptr() for m in mats], [m["y"].data_ptr() for m in mats])
+        ctx.debug_set("prefer_chain", 1 if args.launch == "chain" else 0)
+
+        def step(_i, st):
+            if args.launch == "separate":
+                for m in mats:
+                    m["w"].matvec_dev(m["x"].data_ptr(), m["y"].data_ptr(), st)
+            else:
+                batch.launch(st)  # the library picks: one persistent launch, or one launch per matrix
+
+        sampler = ClockSampler(local)
+        sampler.start()
+        time.sleep(0.2)
+        ms = time_graph(torch, step, args.steps, args.warmup, args.replays)
+        ctx.synchronize()  # surfaces a device-side time-out status
+        launches_per_step = 1 if ctx.last_plan()["grid"] == -2 else len(mats)
+        # end to end: pinned host vectors through the blocking batch call
+        xs_p = [torch.from_numpy(m["xh"]).pin_memory().numpy() for m in mats]
+        ys_p = [torch.empty(m["out"], dtype=torch.float32).pin_memory().numpy() for m in mats]
+        hb = backend.HostBatch(ctx, [m["w"] for m in mats], xs_p, ys_p)
+        for _ in range(max(3, args.warmup)):
+            hb.run()
+        n_e2e = max(args.steps, 20)
         t0 = time.perf_counter()
-        toks = gf.greedy_weight(embd, 11, 0, n_gen)
-        dt = time.perf_counter() - t0
-        e, hd, g = p["n_embd"], p["head_dim"], p["group"]
-        qd, kvd, ne, k, mi = p["n_head"] * hd, p["n_kv_head"] * hd, p["n_experts"], p["n_experts_used"], p["moe_inter"]
-        mlx = lambda o, c: o * c // 2 + 2 * 2 * o * (c // g)  # packed words + bf16 scale and bias tables
-        layer = mlx(qd, e) + 2 * mlx(kvd, e) + mlx(e, qd) + mlx(ne, e) + k * (2 * mlx(mi, e) + mlx(e, mi))
-        nbytes = p["n_layer"] * layer + mlx(p["vocab"], e) + 2 * 2 * kvd * p["n_layer"] * (n_gen // 2)
-        out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, tokens=n_gen, layers=p["n_layer"], bytes_per_token=nbytes,
-                   gbs=nbytes * n_gen / dt / 1e9, first_tokens=toks[:8].tolist(),
-                   note="weights of one seeded layer repeated per layer (distinct device copies); greedy loop on the device")
-    elif args.workload == "c3prefill":
-        # time to first token on the Llama-3.2-1B shape: all prompt tokens in one batched pass
-        # (tensor-core GEMMs on the quantized weights), against the same prompt token by token
-        p = dict(synth.LLAMA_1B)
-        m = synth.gen_llama_model(p, synth.seed_for(3, 0))
-        gf = backend.GpuForward(ctx, m, kv_f16=True)
-        S = args.tokens
-        emb = synth.normal(synth.seed_for(3, 5), S * p["n_embd"]).reshape(S, p["n_embd"]) * np.float32(0.02)
-        gf.forward_batch(emb, S)  # allocates the chunk buffers
-        reps = max(3, min(args.steps, 20))
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            lg = gf.forward_batch(emb, S)
-        dt = (time.perf_counter() - t0) / reps
-        n_seq = min(S, 32)
-        t0 = time.perf_counter()
-        for i in range(n_seq):
-            gf.forward(emb[i], i)
-        dt_seq = (time.perf_counter() - t0) / n_seq
-        params = 16 * (2560 * 2048 + 512 * 2048 + 2048 * 2048 + 2 * 8192 * 2048 + 2048 * 8192)
-        flop = 2.0 * S * params
-        out.update(tokens=S, ms_prefill=dt * 1e3, prefill_tok_per_s=S / dt, gemm_tflops=flop / dt / 1e12,
-                   ms_per_token_stepwise=dt_seq * 1e3, speedup_vs_stepwise=dt_seq * S / dt, last_logit_argmax=int(np.argmax(lg)),
-                   note="host embeddings in, last-token logits out; projections as bf16 tensor-core GEMMs, attention f32")
-    if "gbs" in out:
-        out["frac_of_measured_peak"] = out["gbs"] / peak
-    out["peak_kind"] = peak_kind
-    print(json.dumps(out), flush=True)
+        for _ in range(n_e2e):
+            hb.run()
+        e2e_s = (time.perf_counter() - t0) / n_e2e
+        clocks = sampler.stop()
+        # parity of what was timed: 64 rows per matrix (the last ones: the ragged end of the row walk) against the oracle
+        worst = 0.0
+        for m, yp in zip(mats, ys_p):
+            r0 = m["out"] - 64
+            ref = oracle_rows(m["dt"], m["host"], m["cols"], r0, 64, m["xh"])
+            worst = max(worst, synth.rel_err(m["y"].cpu().numpy()[r0:], ref), synth.rel_err(yp[r0:], ref))
+        check["rel_err_vs_cpu_64_rows_per_matrix"] = worst
+        e2e_api = "ullm_cuda_weight_matvec_batch (7 resident weights, pinned host x / y, one blocking call per step)"
+        h2d, d2h = 4 * sum(m["cols"] for m in mats), 4 * sum(m["out"] for m in mats)
+        l2 = "every step streams 542 MB of weights once: inputs larger than L2"
+        launch = "one CUDA graph of the K timed steps, replayed; seven launches per step" if launches_per_step > 1 else "one CUDA graph of the K timed steps, replayed; one persistent launch per step"
+        kernel = "matvec_stream_kernel<Q4_K | Q6_K prepared>" if launches_per_step > 1 else "matvec_chain_kernel"
+        parallelism = "single GPU"
+        cpu = None
+        if not args.no_cpu:
+            cpu = cpu_leg(check, [m["y"].cpu().numpy() for m in mats])
+        if not args.no_secondary:
+            secondary = {}
+            for name, fn in (("c4gemm", lambda: sec_c4gemm(torch, backend, ctx, dev, args, mats)),):
+                secondary[name] = fn()
+            for m in mats:
+                m["w"].free()
+            torch.cuda.empty_cache()
+            for name, fn in (("c1", sec_c1), ("c0", sec_c0), ("c2", sec_c2), ("c3", sec_c3)):
+                secondary[name] = fn(torch, backend, ctx, dev, args, peak)
+    else:
+        # ---- N > 1: rows / N of every matrix per rank ----
+        outs = [o for _, _, o, _ in C4_MATS]
+        offs = shard.vector_offsets(outs)  # where each full-length result starts in the gather buffer
+        total = offs[-1]
+        slice_bytes = sum(weight_bytes(dt, o // world, c) for _, dt, o, c in C4_MATS)
+        ncopies = max(1, -(-400_000_000 // slice_bytes))  # distinct device copies walked round-robin: more than L2
+        sh = backend.Shard(ctx, world, rank, 2 * total)  # two regions, used by alternate steps
+        handles = [None] * world
+        dist.all_gather_object(handles, sh.export())
+        sh.connect(handles)
+        mats = []
+        for i, (name, dt, out, cols) in enumerate(C4_MATS):
+            r0, rows = sh.row_range(out)
+            w = synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1))  # each rank generates only its rows
+            xv = synth.normal(synth.seed_for(4, 8 + i), cols)
+            mats.append(dict(name=name, dt=dt, out=out, cols=cols, row0=r0, rows=rows, host=w, xh=xv, x=torch.from_numpy(xv).to(dev),
+                             ws=[backend.Weight(ctx, dt, w, rows, cols) for _ in range(ncopies)]))
+        ops = [[sh.ops([dict(w=m["ws"][c], x=m["x"].data_ptr(), y_offset=par * total + o, row0=m["row0"]) for m, o in zip(mats, offs)])
+                for par in range(2)] for c in range(ncopies)]
+        launches_per_step = 1
+        if args.exchange == "nccl":
+            ident = [sh.nccl_id() if rank == 0 else None]
+            dist.broadcast_object_list(ident, src=0)
+            sh.nccl_init(ident[0])
+            rows_total = sum(m["rows"] for m in mats)
+            y_cat = torch.empty(rows_total, dtype=torch.float32, device=dev)
+            y_all = torch.empty(world * rows_total, dtype=torch.float32, device=dev)
+            loff = shard.local_offsets(outs, world)
+            batches = [backend.WeightBatch(ctx, [m["ws"][c] for m in mats], [m["x"].data_ptr() for m in mats],
+                                           [y_cat.data_ptr() + 4 * o for o in loff[:-1]]) for c in range(ncopies)]
+            ctx.debug_set("prefer_chain", 1)
+            launches_per_step = 2
+
+        def step(i, st):
+            if args.exchange == "nccl":
+                batches[i % ncopies].launch(st)
+                sh.allgather_nccl_dev(y_cat.data_ptr(), y_all.data_ptr(), rows_total, st)
+            else:
+                sh.matvec_dev(ops[i % ncopies][i & 1], st)
+
+        barrier()  # every rank is connected before any rank runs a step
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.2)
+        if args.exchange == "nccl":  # comparison arm: host launches, as NCCL is not captured here
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for i in range(max(args.warmup, 3)):
+                    step(i, side.cuda_stream)
+            torch.cuda.synchronize()
+            barrier()
+            ms = []
+            for r in range(args.replays):
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(side):
+                    ev0.record()
+                    for i in range(args.steps):
+                        step(args.warmup + i, side.cuda_stream)
+                    ev1.record()
+                torch.cuda.synchronize()
+                ms.append(ev0.elapsed_time(ev1))
+            sh.nccl_check()
+        else:
+            ms = time_graph(torch, step, args.steps, args.warmup, args.replays, before_timing=barrier)
+        ctx.synchronize()
+        ms = max_over_ranks(ms)
+        barrier()
+        # end to end: pinned host x in, the gathered vectors back to pinned host memory, one blocking call per step
+        xs_p = [torch.from_numpy(m["xh"]).pin_memory().numpy() for m in mats]
+        y_p = torch.empty(total, dtype=torch.float32).pin_memory().numpy()
+        e2e_api = "ullm_cuda_shard_matvec (pinned host x -> this rank's row slices -> peer stores + step flags -> pinned host y of all 7 full vectors)"
+        if args.exchange == "nccl":
+            e2e_s = float("nan")
+        else:
+            for i in range(4):
+                sh.matvec_host(ops[i % ncopies][i & 1], xs_p, y_p, (i & 1) * total)
+            barrier()
+            n_e2e = max(args.steps, 20) // 2 * 2
+            t0 = time.perf_counter()
+            for i in range(n_e2e):
+                sh.matvec_host(ops[i % ncopies][i & 1], xs_p, y_p, (i & 1) * total)
+            e2e_s = max_over_ranks([(time.perf_counter() - t0) / n_e2e])[0]
+        clocks = sampler.stop() if rank == 0 else None
+        # parity on every rank's copy: each rank computes 64 rows of its own slice of every matrix with the oracle,
+        # the values travel to all ranks, and every rank compares them with what lies in ITS gather buffer at those rows
+        _lift_omp_limit()
+        mine = []
+        for m in mats:
+            l0 = max(0, m["rows"] - 64)
+            mine.append((m["row0"] + l0, oracle_rows(m["dt"], m["host"], m["cols"], l0, m["rows"] - l0, m["xh"])))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        if args.exchange == "nccl":
+            got_all = shard.split_gathered(y_all.cpu().numpy(), outs, world)
+        else:
+            last = (args.warmup + args.steps - 1) & 1 if n_e2e == 0 else (n_e2e - 1) & 1
+            got = sh.read_y(last * total, total)
+            got_all = [got[o:o + n] for o, n in zip(offs, outs)]
+        worst = 0.0
+        for r in range(world):
+            for i, (g0, ref) in enumerate(everyone[r]):
+                worst = max(worst, synth.rel_err(got_all[i][g0:g0 + len(ref)], ref))
+        check["rel_err_vs_cpu_64_rows_per_matrix_per_rank"] = max_over_ranks([worst])[0]
+        h2d, d2h = 4 * sum(m["cols"] for m in mats), 4 * total
+        l2 = f"{ncopies} distinct copies of the per-rank slice set ({slice_bytes // 1000000} MB each) walked round-robin: inputs larger than L2"
+        if args.exchange == "nccl":
+            launch, kernel = "host launches: one persistent launch + ncclAllGather per step (comparison arm)", "matvec_chain_kernel + ncclAllGather"
+            parallelism = f"rows/{world} per matrix; NCCL all-gather of the ranks' output rows"
+        else:
+            launch, kernel = "one CUDA graph of the K timed steps, replayed; one persistent launch per step", "matvec_chain_kernel (peer-store epilogue, step flags)"
+            parallelism = f"rows/{world} per matrix; every rank's kernel stores its rows into all ranks' result vectors over NVLink, a published step number replaces the all-gather"
+        cpu = None
+        if rank == 0 and not args.no_cpu:
+            cpu = cpu_leg({}, None)
+        barrier()
+
+    sp = spread(ms, args.steps)
+    step_ms = sp["median"]
+    if rank == 0:
+        value = total_bytes / (step_ms * 1e-3) / 1e9
+        per_rank = value / world
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": step_ms, "ms_per_step_spread": sp, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": DTYPE, "data": "synthetic",
+            "config": {"workload": "c4_70b_layer_matvec", "shapes": "Q4_K q,o [8192,8192] k,v [1024,8192] gate,up [28672,8192]; Q6_K down [8192,28672]; batch 1",
+                       "parallelism": parallelism, "l2": l2, "launch": launch, "pdl": bool(args.pdl), "frac_of_8000": per_rank / 8000.0},
+            "roofline": {"bound": "hbm", "achieved": per_rank, "peak": peak, "unit": "GB/s", "frac": per_rank / peak,
+                         "traffic": NCU_TRAFFIC_PER_STEP["c4_70b_layer_matvec"] if world == 1 else None, "peak_kind": f"of {peak_kind}", "kernel": kernel,
+                         "launch_us": step_ms * 1e3 / launches_per_step, "launches_per_step": launches_per_step,
+                         "algorithmic_bytes_per_step_per_gpu": total_bytes / world,
+                         "note": "per GPU: algorithmic bytes of a rank's share of the step / step time (N > 1: the exchange is inside the step)"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "us_per_step": e2e_s * 1e6, "api": e2e_api},
+            "gpu_launches": launches_per_step * args.steps * len(ms),
+            "clocks": clocks,
+            "check": check,
+        }
+        if secondary is not None:
+            line["secondary"] = secondary
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
     return 0
 
 
-def run_multi_gemm(args):
-    """N>1, --workload c4gemm: the 70B block as a 512-token prefill GEMM, rows/N of every matrix per
-    rank (tcgen05 kernel on the slice), one all-gather of the ranks' [tokens, rows/N] outputs per step."""
+def cpu_leg(check, gpu_outputs):
+    """The oracle port on the same workload, on the host cores: full steps for about ten seconds."""
+    _lift_omp_limit()
+    cstep, cores, nbytes, _ = cpu_c4_step_factory()
+    refs = cstep()
+    t0 = time.perf_counter()
+    n = 0
+    while n < 3 or (time.perf_counter() - t0 < 10.0 and n < 400):
+        refs = cstep()
+        n += 1
+    cdt = (time.perf_counter() - t0) / n
+    if gpu_outputs is not None:
+        check["rel_err_vs_cpu_full_vectors"] = max(synth.rel_err(g, r) for g, r in zip(gpu_outputs, refs))
+    return {"value": nbytes / cdt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{n} full steps of c4_70b_layer_matvec, {cdt * 1e3:.1f} ms each"}
+
+
+def run_c4gemm_multi(args):
+    """N > 1, --workload c4gemm: the block as a 512-token prefill GEMM, rows / N of every matrix per rank; the
+    GEMM's epilogue stores each rank's [tokens, rows / N] block into its columns of [tokens, out] on every rank."""
     import torch
     import torch.distributed as dist
 
@@ -529,193 +674,65 @@ def run_multi_gemm(args):
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    ctx = backend.CudaContext(local)
     dev = torch.device(f"cuda:{local}")
+    dist.init_process_group("nccl", device_id=dev)
+    ctx = backend.CudaContext(local)
     S = args.tokens
-    rows_total = shard.local_offsets([o for _, _, o, _ in C4_MATS], world)[-1]
+    outs = [o for _, _, o, _ in C4_MATS]
+    offs = [S * o for o in shard.vector_offsets(outs)]  # [tokens, out] matrices one after the other
+    sh = backend.Shard(ctx, world, rank, offs[-1])
+    handles = [None] * world
+    dist.all_gather_object(handles, sh.export())
+    sh.connect(handles)
     mats = []
     for i, (name, dt, out, cols) in enumerate(C4_MATS):
-        rows = out // world
-        w = backend.Weight(ctx, dt, synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1)), rows, cols)
+        r0, rows = sh.row_range(out)
+        w = synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1))
         xs = torch.randn(S * cols, dtype=torch.float32, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i))
-        y_r = torch.empty(S * rows, dtype=torch.float32, device=dev)             # this rank's [token][rows/N]
-        y_g = torch.empty(world * S * rows, dtype=torch.float32, device=dev)     # [rank][token][rows/N]
-        mats.append((w, xs, y_r, y_g))
-    side = torch.cuda.Stream()
-    ctx.debug_set("pdl", 0)
+        xs = xs.to(torch.bfloat16).to(torch.float32)
+        mats.append(dict(dt=dt, out=out, cols=cols, row0=r0, rows=rows, host=w, w=backend.Weight(ctx, dt, w, rows, cols), xs=xs))
 
-    def step():
-        # the gather of one matrix' output overlaps the GEMM of the next (NCCL runs on its own stream)
-        works = []
-        for w, xs, y_r, y_g in mats:
-            w.matmul_dev(xs.data_ptr(), y_r.data_ptr(), S, side.cuda_stream)
-            works.append(dist.all_gather_into_tensor(y_g, y_r, async_op=True))
-        for wk in works:
-            wk.wait()
+    def step(_i, st):
+        for k, (m, off) in enumerate(zip(mats, offs)):
+            last = k + 1 == len(mats)  # the step waits for the other ranks once, after its last matrix
+            sh.matmul_dev(m["w"], m["xs"].data_ptr(), S, off, m["row0"], m["out"], st, 0 if last else backend.SHARD_NO_WAIT)
 
-    with torch.cuda.stream(side):
-        for _ in range(max(args.warmup, 3)):
-            step()
-    torch.cuda.synchronize()
     dist.barrier()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(side):
-        ev0.record()
-        for _ in range(args.steps):
-            step()
-        ev1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms_t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
-    dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
-    ms = float(ms_t.item()) / args.steps
+    ms = time_graph(torch, step, max(2, args.steps // 4), 3, args.replays, before_timing=dist.barrier)
+    ctx.synchronize()
+    t = torch.tensor(ms, dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sp = spread(t.tolist(), max(2, args.steps // 4))
+    # parity: 64 rows x 8 tokens of every rank's block, read from this rank's copy of the full result
+    import oracle
+
+    _lift_omp_limit()
+    mine = []
+    for m in mats:
+        l0 = max(0, m["rows"] - 64)
+        rb = m["cols"] // 256 * (144 if m["dt"] == synth.Q4_K else 210)
+        blk = np.ascontiguousarray(np.asarray(m["host"]).reshape(-1).view(np.uint8)[l0 * rb:m["rows"] * rb])
+        xs_h = m["xs"][:8 * m["cols"]].cpu().numpy().reshape(8, m["cols"])
+        mine.append((m["row0"] + l0, oracle.matmul_q(oracle.Weight(m["dt"], blk, m["rows"] - l0, m["cols"]), xs_h, 8).reshape(8, -1)))
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine)
+    worst = 0.0
+    for i, (m, off) in enumerate(zip(mats, offs)):
+        got = sh.read_y(off, 8 * m["out"]).reshape(8, m["out"])
+        for r in range(world):
+            g0, ref = everyone[r][i]
+            worst = max(worst, synth.rel_err(got[:, g0:g0 + ref.shape[1]], ref))
+    wt = torch.tensor([worst], dtype=torch.float64, device=dev)
+    dist.all_reduce(wt, op=dist.ReduceOp.MAX)
     if rank == 0:
         flop = 2.0 * S * sum(o * c for _, _, o, c in C4_MATS)
-        tf = flop / ms / 1e9
-        print(json.dumps({"workload": "c4gemm", "n_gpus": world, "tokens": S, "steps": args.steps, "us_per_step": ms * 1e3,
+        tf = flop / sp["median"] / 1e9
+        print(json.dumps({"workload": "c4_70b_layer_gemm", "n_gpus": world, "tokens": S, "us_per_step": sp["median"] * 1e3, "ms_per_step_spread": sp,
                           "tflops": tf, "tflops_per_gpu": tf / world, "peak_tflops": measured_peak_tflops(),
                           "frac_per_gpu": tf / world / measured_peak_tflops(), "scaling": "strong",
-                          "gather_bytes_per_step": 4 * world * S * rows_total,
-                          "parallelism": f"rows/{world} per matrix; each matrix' [token][rows/N] output is all-gathered while the next matrix is multiplied",
-                          "launch": "host launches + NCCL"}), flush=True)
-    dist.destroy_process_group()
-    return 0
-
-
-def run_multi(args):
-    import torch
-    import torch.distributed as dist
-
-    from ullm_b200 import backend
-
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    ctx = backend.CudaContext(local)
-    dev = torch.device(f"cuda:{local}")
-    stream = torch.cuda.current_stream().cuda_stream
-
-    # Row slices: rank r owns rows [r*out/N, (r+1)*out/N) of every matrix and generates
-    # only those (rows are self-contained byte ranges).  Enough distinct device copies of
-    # the slice set are walked round-robin that a step never finds its weights in L2.
-    slice_bytes = sum(weight_bytes(dt, o // world, c) for _, dt, o, c in C4_MATS)
-    ncopies = max(1, -(-400_000_000 // slice_bytes))
-    rows_total = shard.local_offsets([o for _, _, o, _ in C4_MATS], world)[-1]
-    y_cat = torch.empty(rows_total, dtype=torch.float32, device=dev)       # this rank's rows of all 7 outputs
-    y_all = torch.empty(world * rows_total, dtype=torch.float32, device=dev)  # [rank][matrix][rows]
-    mats, off = [], 0
-    for i, (name, dt, out, cols) in enumerate(C4_MATS):
-        assert out % world == 0
-        rows = out // world
-        w = synth.gen_weight(dt, rows, cols, synth.seed_for(4, i) + 0x100000 * (rank + 1))
-        xv = synth.normal(synth.seed_for(4, 8 + i), cols)
-        mats.append(dict(rows=rows, cols=cols, off=off, ws=[backend.Weight(ctx, dt, w, rows, cols) for _ in range(ncopies)],
-                         x=torch.from_numpy(xv).to(dev), xh=torch.from_numpy(xv).pin_memory()))
-        off += rows
-    y_host = torch.empty(world * rows_total, dtype=torch.float32).pin_memory()
-
-    # Kernels and the NCCL collective share one non-default stream (a NULL handle would
-    # send the kernels to the context's own stream, unordered with NCCL).
-    side = torch.cuda.Stream()
-    stream = side.cuda_stream
-    use_pdl = bool(args.pdl) and args.multi_graph
-    ctx.debug_set("pdl", 1 if use_pdl else 0)
-    batches = [backend.WeightBatch(ctx, [m["ws"][c] for m in mats], [m["x"].data_ptr() for m in mats],
-                                   [y_cat.data_ptr() + 4 * m["off"] for m in mats]) for c in range(ncopies)]
-
-    def step(i):
-        batches[i % ncopies].launch(stream)  # the seven matvecs of this rank, one host call
-        # the one exchange of the path: every rank's output rows to every rank
-        dist.all_gather_into_tensor(y_all, y_cat)
-
-    torch.cuda.synchronize()
-    with torch.cuda.stream(side):
-        for i in range(max(args.warmup, 3)):
-            step(i)
-    torch.cuda.synchronize()
-    # the batch call is one persistent launch when the chain kernel takes the list, else one launch per matrix
-    launches_per_step = 1 if ctx.last_plan()["grid"] == -2 else len(mats)
-    graph = None
-    if args.multi_graph:
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(args.steps):
-                    step(args.warmup + i)
-            graph.replay()
-            torch.cuda.synchronize()
-        except Exception as e:  # fall back to host launches, say so in the line
-            graph = None
-            print(f"graph capture failed on rank {rank}: {e}", file=sys.stderr)
-            torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    dist.barrier()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(side):
-        ev0.record()
-        if graph is not None:
-            graph.replay()
-        else:
-            for i in range(args.steps):
-                step(args.warmup + i)
-        ev1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ctx.synchronize()
-
-    # end to end: x vectors from pinned host memory, gathered outputs back to the host
-    def e2e_step(i):
-        with torch.cuda.stream(side):
-            for m in mats:
-                m["x"].copy_(m["xh"], non_blocking=True)
-            step(i)
-            y_host.copy_(y_all, non_blocking=True)
-        side.synchronize()
-
-    for i in range(3):
-        e2e_step(i)
-    dist.barrier()
-    t0 = time.perf_counter()
-    n_e2e = min(args.steps, 200)
-    for i in range(n_e2e):
-        e2e_step(i)
-    e2e_t = torch.tensor([time.perf_counter() - t0], device=dev)
-    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
-    e2e_s = float(e2e_t.item()) / n_e2e
-    ms_t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
-    dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
-    ms = float(ms_t.item())
-    clocks = sampler.stop() if rank == 0 else None
-
-    total_bytes = sum(weight_bytes(dt, o, c) + 4 * (o + c) for _, dt, o, c in C4_MATS)
-    if rank == 0:
-        value = args.steps * total_bytes / (ms * 1e-3) / 1e9
-        peak, peak_kind = measured_peak_gbs()
-        line = {
-            "metric": "quantized_matvec_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "int8 dot products (16-bit fixed-point x) + f32 accumulate", "data": "synthetic",
-            "config": {"workload": "c4_70b_layer_matvec", "shapes": "Q4_K q,o [8192,8192] k,v [1024,8192] gate,up [28672,8192]; Q6_K down [8192,28672]",
-                       "parallelism": f"rows/{world} per matrix, one NCCL all-gather of the ranks' output rows per step",
-                       "l2": f"{ncopies} distinct copies of the per-rank slice set ({slice_bytes // 1000000} MB each) walked round-robin: inputs larger than L2",
-                       "launch": "one CUDA graph of all timed steps" if graph is not None else "host launches (one C call per step) + NCCL", "pdl": use_pdl},
-            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
-                         "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "matvec_stream_kernel (per rank, incl. all-gather time)"},
-            "cpu_baseline": None,
-            "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * sum(c for _, _, _, c in C4_MATS),
-                    "d2h_bytes_per_step": 4 * world * rows_total, "us_per_step": e2e_s * 1e6,
-                    "api": "pinned host x -> ullm_cuda_weight_matvec_dev x7 -> NCCL all-gather -> pinned host y"},
-            "gpu_launches": launches_per_step * args.steps,
-            "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
+                          "peer_store_bytes_per_rank_per_step": 4 * S * sum(outs) // world * (world - 1),
+                          "parallelism": f"rows/{world} per matrix; the GEMM epilogue stores each tile into all ranks' [tokens, out] over NVLink",
+                          "launch": "one CUDA graph of the timed steps, replayed", "check": {"rel_err_vs_cpu_64_rows_8_tokens_per_rank": float(wt.item())}}), flush=True)
     dist.destroy_process_group()
     return 0
 
@@ -723,30 +740,25 @@ def run_multi(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=500)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--copies", type=int, default=8)
-    ap.add_argument("--tokens", type=int, default=512, help="prefill length of the c4gemm workload")
-    ap.add_argument("--layers", type=int, default=0, help="c2decode: number of layers (default: the model's 48)")
-    ap.add_argument("--only", default="", help="c4gemm: run just this matrix of the block (q, k, v, o, gate, up, down)")
-    ap.add_argument("--pdl", type=int, default=1, help="launch the kernels with programmatic dependent launch (weight prefetch of the next kernel overlaps the tail of the previous one)")
-    ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--chain", type=int, default=0,
-                    help="c1: run the pair as one persistent launch (ullm_cuda_weight_matvec_chain_dev); measured slower than "
-                         "two programmatically chained launches for this pair, so off by default")
-    ap.add_argument("--multi-graph", action="store_true", help="N>1: capture kernels + NCCL in a CUDA graph (off by default)")
-    ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c2decode", "c3", "c3prefill", "c4", "c4gemm"],
-                    help="single-GPU only: c1 is the headline workload, the others are auxiliary measurements")
+    ap.add_argument("--replays", type=int, default=15, help="timed replays of the K-step graph (median / min / max reported)")
+    ap.add_argument("--tokens", type=int, default=512, help="prefill length of the GEMM workloads")
+    ap.add_argument("--pdl", type=int, default=1, help="ULLM_OPT_PDL: launch kernels programmatically dependent on their predecessor")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-secondary", action="store_true", help="N = 1: skip the other configurations")
+    ap.add_argument("--launch", default="auto", choices=["auto", "separate", "chain"],
+                    help="N = 1: the library's choice, seven launches per step, or one persistent launch per step")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: fused peer stores (default) or the NCCL all-gather comparison arm")
+    ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm"], help="N > 1 only: c4gemm runs the block as a sharded prefill GEMM")
     args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
-    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        return run_multi_gemm(args) if args.workload == "c4gemm" else run_multi(args)
-    if args.workload != "c1":
-        return run_other(args)
-    return run_single(args)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and args.workload == "c4gemm":
+        return run_c4gemm_multi(args)
+    return run_c4(args)
 
 
 if __name__ == "__main__":

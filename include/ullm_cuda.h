@@ -68,6 +68,14 @@ typedef struct ullm_cuda_weight ullm_cuda_weight;
 int ullm_cuda_ctx_create(int device, ullm_cuda_ctx **out);
 void ullm_cuda_ctx_destroy(ullm_cuda_ctx *ctx);
 const char *ullm_cuda_last_error(const ullm_cuda_ctx *ctx);
+/* Per-context switches (no counterpart in the reference, whose backend has none).
+ *  ULLM_OPT_PDL (default 1): the library's kernels are launched "programmatically dependent" on
+ *    their predecessor in the stream, so a kernel's weight stream starts while the previous kernel
+ *    drains; results are the same either way.
+ *  ULLM_OPT_SHARD_TIMEOUT_MS (default 2000): how long a rank of a row-sharded group waits for the
+ *    other ranks' rows before the call fails with ULLM_ERR_TIMEOUT. */
+enum { ULLM_OPT_PDL = 1, ULLM_OPT_SHARD_TIMEOUT_MS = 2 };
+int ullm_cuda_ctx_set_option(ullm_cuda_ctx *ctx, int option, int value);
 int ullm_cuda_device_name(const ullm_cuda_ctx *ctx, char *name, size_t cap);
 int ullm_cuda_sm_count(const ullm_cuda_ctx *ctx);
 /* Blocks until everything enqueued on the context's stream has finished and
@@ -131,6 +139,12 @@ int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, c
  * share no data: q/k/v, gate/up): y[i] = W[i] x[i], device vectors. */
 int ullm_cuda_weight_matvec_batch_dev(ullm_cuda_ctx *ctx, size_t n, const ullm_cuda_weight *const *w,
                                       const float *const *d_x, float *const *d_y, void *stream);
+/* The same from host vectors in ONE blocking call (a layer's independent projections): copies the
+ * n input vectors in, runs the n matvecs, copies the n results out and waits once.  The reference
+ * makes one submission per token (forward.rs:513-515); per-matrix calls of ullm_cuda_weight_matvec
+ * pay one copy-in / launch / copy-out / wait round trip each. */
+int ullm_cuda_weight_matvec_batch(ullm_cuda_ctx *ctx, size_t n, const ullm_cuda_weight *const *w, const float *const *x,
+                                  float *const *y);
 /* A list of matvecs on resident weights run as ONE persistent launch: the weight stream
  * of op i+1 follows that of op i without a gap, and the grid synchronises only where
  * `dep` says an op consumes what an earlier op of the list produced (x or res).  With the
@@ -180,6 +194,95 @@ int ullm_cuda_matmul_mlx4(ullm_cuda_ctx *ctx, const void *w, const float *scales
 int ullm_cuda_matmul_dev(ullm_cuda_ctx *ctx, int dtype, const void *d_w, const void *d_scales, const void *d_biases,
                          int table_dtype, size_t group, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
                          size_t s, void *stream);
+
+/* ---- row-sharded matrices over the GPUs of one node ----
+ * No counterpart in the reference (multi-device scale-out is an open item of its roadmap,
+ * docs/roadmap.md:83).  The split is the one its CPU path already uses: output rows are
+ * independent (crates/ullm-model/src/math.rs:11-21), and a row of a quantized matrix is a
+ * self-contained byte range (math.rs:29-31).  Rank r of N keeps rows [r*out/N, (r+1)*out/N) of a
+ * matrix; every rank has the whole input vector; the one exchange of the path is that each rank's
+ * output rows must reach every rank.
+ *
+ * A `ullm_cuda_shard` is one rank's end of such a group: a "gather buffer" of `y_floats` floats on
+ * its GPU, laid out identically on every rank, in which the caller places the full-length result
+ * vectors (by offset).  The kernels of rank r store the rows they computed at the same offset into
+ * EVERY rank's gather buffer (plain stores over NVLink through peer mappings; nothing is read from
+ * a peer), then publish a step number to every rank; the step is complete on a rank when it has
+ * seen every rank's number.  No NCCL call is involved, so a step can be captured in a CUDA graph
+ * like any other kernel.
+ *
+ * Set-up, one process per GPU (rank = that process' index): ullm_cuda_shard_create, exchange the
+ * ULLM_SHARD_HANDLE_BYTES handles of ullm_cuda_shard_export between the processes by any means
+ * (they are plain bytes), ullm_cuda_shard_connect with all N handles in rank order.  One process
+ * that owns several GPUs: create one context and one shard per GPU, then
+ * ullm_cuda_shard_connect_local.  All ranks must be connected before any of them runs a step.
+ *
+ * Rules for the caller:
+ *  - Every rank must run the same sequence of sharded calls (steps are counted per rank).
+ *  - A rank waits at most ULLM_OPT_SHARD_TIMEOUT_MS for the others; then the call (or the next
+ *    ullm_cuda_synchronize) reports ULLM_ERR_TIMEOUT instead of hanging — this is how a dead or
+ *    stalled peer shows.  After a time-out the group is out of step: every rank calls
+ *    ullm_cuda_shard_reset (with a host-side barrier of the caller's before the next step).
+ *  - A region of the gather buffer that step s filled may be filled again by step s+2 at the
+ *    earliest, and must have been read by then (a rank can run one step ahead of a peer, not
+ *    two): alternate between two regions when consecutive steps produce the same vector. */
+typedef struct ullm_cuda_shard ullm_cuda_shard;
+#define ULLM_SHARD_HANDLE_BYTES 64
+#define ULLM_SHARD_MAX_RANKS 8
+int ullm_cuda_shard_create(ullm_cuda_ctx *ctx, int world, int rank, size_t y_floats, ullm_cuda_shard **out);
+void ullm_cuda_shard_destroy(ullm_cuda_shard *s);
+int ullm_cuda_shard_export(const ullm_cuda_shard *s, void *handle /* ULLM_SHARD_HANDLE_BYTES */);
+int ullm_cuda_shard_connect(ullm_cuda_shard *s, const void *handles /* world x ULLM_SHARD_HANDLE_BYTES, rank order */);
+int ullm_cuda_shard_connect_local(ullm_cuda_shard *const *shards, int world);
+int ullm_cuda_shard_reset(ullm_cuda_shard *s);
+/* Device address of this rank's gather buffer (y_floats floats). */
+float *ullm_cuda_shard_y(const ullm_cuda_shard *s);
+/* Copies `n` floats at `offset` of this rank's gather buffer to the host.  Waits for the context's
+ * own stream; a caller that ran the step on another stream synchronises that stream first. */
+int ullm_cuda_shard_read(ullm_cuda_shard *s, size_t offset, float *host, size_t n);
+/* Rows [*row0, *row0 + *rows) of a matrix of `out` rows that `rank` of `world` keeps; FORMAT-style
+ * failure (non-zero) when `out` does not divide evenly. */
+int ullm_cuda_shard_row_range(size_t out, int world, int rank, size_t *row0, size_t *rows);
+/* A resident weight holding only this rank's rows of `full` (a host description of the WHOLE
+ * matrix, as ullm_cuda_weight_create takes it); MLX tables are sliced with the rows. */
+int ullm_cuda_shard_weight_create(ullm_cuda_shard *s, const struct ullm_gpu_weight_s *full, int mlx_table_dtype,
+                                  ullm_cuda_weight **out);
+/* One step of `n` sharded matvecs: for every op, y[y_offset + row0 + i] = (W_rows x)[i] in every
+ * rank's gather buffer, where W_rows is this rank's slice.  `w` is either a weight made by
+ * ullm_cuda_shard_weight_create (row0 is known) or any resident weight holding the slice, with
+ * `row0` given here.  Q4_K and prepared Q6_K slices run as one persistent launch whose epilogue
+ * stores to all ranks; other weights run the ordinary kernels followed by a copy to the peers.
+ * flags: ULLM_SHARD_NO_WAIT publishes without waiting (pair with ullm_cuda_shard_wait_dev). */
+typedef struct ullm_shard_op {
+    const ullm_cuda_weight *w;
+    const float *d_x;  /* [in] device, this rank's copy of the full input vector */
+    size_t y_offset;   /* where the full-length result starts in the gather buffer (floats) */
+    size_t row0;       /* first row of the slice; ignored for weights made by ullm_cuda_shard_weight_create */
+} ullm_shard_op;
+enum { ULLM_SHARD_NO_WAIT = 1 };
+int ullm_cuda_shard_matvec_dev(ullm_cuda_shard *s, size_t n, const ullm_shard_op *ops, int flags, void *stream);
+/* The same step from host vectors, blocking: x_host[i] (may be NULL: the op's d_x is already filled) is
+ * copied into op i's d_x, the step runs with its wait, and floats [y_offset, y_offset + y_count) of
+ * this rank's gather buffer — the gathered results — are copied to y_host. */
+int ullm_cuda_shard_matvec(ullm_cuda_shard *s, size_t n, const ullm_shard_op *ops, const float *const *x_host, float *y_host,
+                           size_t y_offset, size_t y_count);
+/* Enqueues the bounded wait for every rank's latest step. */
+int ullm_cuda_shard_wait_dev(ullm_cuda_shard *s, void *stream);
+/* Prefill form: this rank's [tokens, rows] block of Y = X W^T goes to columns [row0, row0 + rows)
+ * of the token-major [tokens, out_total] matrix at `y_offset` in every rank's gather buffer; the
+ * tensor-core GEMM's epilogue stores to all ranks.  d_x: [tokens, in] f32 on this rank. */
+int ullm_cuda_shard_matmul_dev(ullm_cuda_shard *s, const ullm_cuda_weight *w, const float *d_x, size_t tokens, size_t y_offset,
+                               size_t row0, size_t out_total, int flags, void *stream);
+/* Comparison arm: the same exchange as an NCCL all-gather (libnccl.so.2 is loaded at run time;
+ * UNSUPPORTED when it is absent).  Rank 0 makes the 128-byte id, the caller hands it to every rank,
+ * every rank calls _nccl_init.  _allgather_nccl_dev gathers `count` floats per rank from d_send into
+ * d_recv ([world][count]) on `stream`; _nccl_check reports an asynchronous communicator error
+ * (ncclCommGetAsyncError) as ULLM_ERR_CUDA. */
+#define ULLM_SHARD_NCCL_ID_BYTES 128
+int ullm_cuda_shard_nccl_id(void *id /* ULLM_SHARD_NCCL_ID_BYTES */);
+int ullm_cuda_shard_nccl_init(ullm_cuda_shard *s, const void *id);
+int ullm_cuda_shard_allgather_nccl_dev(ullm_cuda_shard *s, const float *d_send, float *d_recv, size_t count, void *stream);
+int ullm_cuda_shard_nccl_check(ullm_cuda_shard *s);
 
 /* ---- mixture-of-experts FFN (MLX 4-bit stacked experts) ----
  * GpuExperts (forward.rs:67-75): `n_experts` matrices concatenated, gate/up

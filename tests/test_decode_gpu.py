@@ -79,35 +79,54 @@ def test_decode_rejects_unbuilt_variants(ctx):
 
 
 def test_llama_1b_shape_greedy_sequence(ctx):
-    """Benchmark configuration 3: Llama-3.2-1B-shaped, Q4_K_M mix, f16 KV prefilled
-    with 1024 positions, 16-token prompt processed token by token, then greedy
-    tokens; the CUDA sequence must equal the oracle's (f16-rounding KV)."""
+    """Benchmark configuration 3 at its stated length: Llama-3.2-1B-shaped, Q4_K_M mix, f16 KV prefilled
+    with 1024 positions, a 16-token prompt processed token by token, then 128 greedy tokens.
+
+    The oracle's 128 tokens, each step's runner-up and the gap between their logits (relative to the
+    largest |logit|, the unit of the 1e-3 logit bar) are a committed fixture
+    (tests/golden/c3_decode_128.npz, made by tests/golden/make_c3_decode.py).  Two comparisons:
+    the sequence the device generates on its own, and a teacher-forced pass that feeds the oracle's
+    tokens so that all 128 steps are compared even if the free-running sequence leaves the oracle's
+    at a near-tie.  A step may differ from the oracle only where the oracle's own gap is inside the
+    logit tolerance, and then only by picking the runner-up."""
+    import os
+
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "c3_decode_128.npz"))
     p = dict(synth.LLAMA_1B)
     m = synth.gen_llama_model(p, synth.seed_for(3, 0))
-    n_pre, n_prompt, n_gen = 1024, 16, 16
+    n_pre, n_prompt, n_gen = 1024, 16, 128
     k, v = synth.gen_kv_prefill(p, n_pre, synth.seed_for(3, 1))
     prompt = synth.rand_ints(synth.seed_for(3, 2), n_prompt, 0, p["vocab"] - 1)
+    assert prompt.tolist() == gold["prompt"].tolist()
     om = oracle_model(m, True)
     om.key_cache[:, :n_pre] = k
     om.val_cache[:, :n_pre] = v
     gf = backend.GpuForward(ctx, m, kv_f16=True)
     gf.set_kv(0, k, v)
     for i, t in enumerate(prompt):
-        ref = om.forward(int(t), n_pre + i)
         got = gf.forward(om.embed(int(t)), n_pre + i)
-        assert synth.rel_err(got, ref) < 1e-3, i
-    tok = oracle.argmax(ref)
-    assert int(np.argmax(got)) == tok
+        if i < 3:  # logits against the oracle's forward at the first prompt positions (about a second of CPU each)
+            assert synth.rel_err(got, om.forward(int(t), n_pre + i)) < 1e-3, i
+    first = int(np.argmax(got))
+    assert first == int(gold["first"])
+    tokens, second, gap = gold["tokens"].tolist(), gold["second"].tolist(), gold["rel_gap"]
+    tie = 2e-3  # a GPU logit may be off by 1e-3 of the largest |logit| on either candidate
+
     embd = ctx.upload(m["tok_embd"][1])
-    ref_tokens, margins, t = [], [], tok
-    for i in range(n_gen):
-        lg = om.forward(t, n_pre + n_prompt + i)
-        s = np.partition(lg, -2)
-        margins.append(float(s[-1] - s[-2]))
-        t = oracle.argmax(lg)
-        ref_tokens.append(t)
-    got_tokens = gf.greedy(embd, m["tok_embd"][0], tok, n_pre + n_prompt, n_gen)
-    assert got_tokens.tolist() == ref_tokens, (got_tokens.tolist(), ref_tokens, margins)
+    free = gf.greedy(embd, m["tok_embd"][0], first, n_pre + n_prompt, n_gen).tolist()
+    same = next((i for i in range(n_gen) if free[i] != tokens[i]), n_gen)
+    if same < n_gen:
+        assert gap[same] < tie and free[same] == second[same], (same, free[same], tokens[same], second[same], float(gap[same]))
+
+    prev, swaps = first, []
+    for i in range(n_gen):  # teacher-forced: the oracle's token goes in, whatever the device would have picked
+        lg = gf.forward(om.embed(prev), n_pre + n_prompt + i)
+        a = int(np.argmax(lg))
+        if a != tokens[i]:
+            assert gap[i] < tie and a == second[i], (i, a, tokens[i], second[i], float(gap[i]))
+            swaps.append(i)
+        prev = tokens[i]
+    assert len(swaps) <= int(np.sum(gap < tie))
     gf.free()
 
 

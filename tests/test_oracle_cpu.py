@@ -204,3 +204,26 @@ def test_tiny_llama_decode_runs_and_kv_f16_matters_little():
         assert np.isfinite(la).all()
         assert synth.rel_err(lb, la) < 2e-2
         tok = oracle.argmax(la)
+
+
+# ---- third-party pin: ggml's own numpy dequantizer ------------------------------
+def test_q4k_q6k_equal_ggmls_reference_dequantizer_bit_for_bit():
+    """The reference's k-quant routines are a port of ggml's (crates/ullm-core/src/dequant.rs:3-5) and hold no
+    known-answer vector for Q4_K / Q6_K.  The `gguf` Python package ships ggml's own numpy dequantizer: an
+    implementation independent of this repository.  The oracle must reproduce it bit for bit on the benchmark's
+    block distribution and on arbitrary random bytes (with a finite f16 scale)."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import GGMLQuantizationType as T
+    from gguf import quants
+
+    for dt, qt, gen, bb, d_off in ((oracle.Q4_K, T.Q4_K, synth.gen_q4k, 144, (0, 2)), (oracle.Q6_K, T.Q6_K, synth.gen_q6k, 210, (208,))):
+        cases = [np.asarray(gen(64, 4096, 77)).reshape(-1).view(np.uint8)]
+        rnd = synth.rand_bytes(78, 512 * bb).reshape(512, bb).copy()
+        for o in d_off:  # keep the f16 scale fields finite: clear the top exponent bit of their high byte
+            rnd[:, o + 1] &= 0xBF
+        cases.append(rnd.reshape(-1))
+        for blob in cases:
+            n = blob.size // bb * 256
+            ours = oracle.dequantize(dt, blob, n)
+            theirs = quants.dequantize(blob.reshape(-1, bb), qt).astype(np.float32).reshape(-1)
+            assert np.array_equal(ours.view(np.uint32), theirs.view(np.uint32)), (dt, "oracle differs from ggml's dequantizer")

@@ -62,6 +62,116 @@ def test_row_sharded_matvecs_gather_to_the_unsharded_result():
     assert res == [(0, True), (1, True)]
 
 
+def _peer_worker(rank, world, port, out_q, silent_rank):
+    """The exchange the library's kernels perform, with gloo messages standing in for stores over NVLink: every
+    rank writes its rows into the same place of every rank's full-length result vectors (laid out by
+    shard.vector_offsets, two regions used by alternate steps), then publishes its step number to every rank;
+    a step is complete on a rank when it holds every rank's number.  Messages between two ranks arrive in order,
+    like a rank's stores followed by its release store of the number."""
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        outs = [m[1] for m in MATS]
+        offs = shard.vector_offsets(outs, align=16)
+        total = offs[-1]
+        buf = np.full(2 * total, np.nan, np.float32)  # this rank's gather buffer
+        seen = [0] * world                            # this rank's control block: rank r's published step
+        ok, timed_out = True, False
+        for step in range(1, 4):
+            base = shard.step_region(step, total)
+            rows, pending = [], []
+            if rank != silent_rank:
+                for i, (dt, out, cols) in enumerate(MATS):
+                    gen = synth.gen_q4k if dt == oracle.Q4_K else synth.gen_q6k
+                    mine = shard.slice_rows(dt, gen(out, cols, 100 + i), out, cols, world, rank)
+                    x = synth.normal(200 + i + 10 * step, cols)
+                    rows.append(oracle.matvec_q(oracle.Weight(dt, mine, out // world, cols), x))
+                for peer in range(world):
+                    payload = torch.from_numpy(np.concatenate(rows + [np.float32([step])]))
+                    if peer == rank:
+                        mine_payload = payload
+                    else:
+                        pending.append(dist.isend(payload, dst=peer))  # posted, not waited for: like a store
+            for peer in range(world):
+                n_rows = sum(o // world for o in outs)
+                if peer == rank:
+                    if rank == silent_rank:
+                        continue
+                    payload = mine_payload
+                else:
+                    payload = torch.empty(n_rows + 1)
+                    try:
+                        dist.recv(payload, src=peer)
+                    except Exception:  # the bounded wait ran out: the peer never published
+                        timed_out = True
+                        break
+                p, at = payload.numpy(), 0
+                for i, o in enumerate(outs):
+                    lo, hi = shard.row_range(o, world, peer)
+                    buf[base + offs[i] + lo: base + offs[i] + hi] = p[at:at + hi - lo]
+                    at += hi - lo
+                seen[peer] = int(p[at])
+            if timed_out:
+                break
+            for h in pending:
+                h.wait()
+            ok = ok and all(v >= step for v in seen)
+            for i, (dt, out, cols) in enumerate(MATS):
+                gen = synth.gen_q4k if dt == oracle.Q4_K else synth.gen_q6k
+                ref = oracle.matvec_q(oracle.Weight(dt, gen(out, cols, 100 + i), out, cols), synth.normal(200 + i + 10 * step, cols))
+                ok = ok and np.array_equal(buf[base + offs[i]: base + offs[i] + out], ref)
+        out_q.put((rank, ok, timed_out))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def _run_peers(silent_rank):
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_peer_worker, args=(r, world, port, q, silent_rank)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    return res
+
+
+def test_peer_store_exchange_fills_every_ranks_vectors_step_after_step():
+    assert _run_peers(silent_rank=-1) == [(0, True, False), (1, True, False)]
+
+
+def test_a_rank_that_never_publishes_ends_the_others_wait_with_a_timeout():
+    """Failure detection, made on the host: rank 1 computes and sends nothing; rank 0's wait for rank 1's step
+    number is bounded and reports the expiry instead of hanging."""
+    res = dict((r, (ok, to)) for r, ok, to in _run_peers(silent_rank=1))
+    assert res[0][1] is True  # rank 0 saw the time-out
+
+
+def test_library_row_split_agrees_with_the_index_math():
+    import ctypes as C
+
+    from ullm_b200 import backend
+
+    lib = backend.load_library()
+    for out, world in ((28672, 8), (8192, 4), (1024, 2), (7, 1)):
+        for rank in range(world):
+            r0, n = C.c_size_t(), C.c_size_t()
+            assert lib.ullm_cuda_shard_row_range(out, world, rank, C.byref(r0), C.byref(n)) == 0
+            assert (r0.value, r0.value + n.value) == shard.row_range(out, world, rank)
+    r0, n = C.c_size_t(), C.c_size_t()
+    assert lib.ullm_cuda_shard_row_range(10, 4, 0, C.byref(r0), C.byref(n)) == backend.ERR_FORMAT
+    assert shard.vector_offsets([8192, 1024, 28672]) == [0, 8192, 9216, 37888]
+    assert shard.vector_offsets([100, 7], align=64) == [0, 128, 192]
+    assert shard.step_region(4, 1000) == 0 and shard.step_region(5, 1000) == 1000
+
+
 def test_shard_index_math():
     assert shard.row_range(28672, 8, 3) == (3 * 3584, 4 * 3584)
     with pytest.raises(ValueError):

@@ -42,6 +42,9 @@ class FormatError(UllmError):
     pass
 
 
+OPT_PDL, OPT_SHARD_TIMEOUT_MS = 1, 2
+SHARD_HANDLE_BYTES, SHARD_NCCL_ID_BYTES, SHARD_NO_WAIT = 64, 128, 1
+
 _lib = None
 
 _vp, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
@@ -51,6 +54,7 @@ SIGNATURES = {
     "ullm_cuda_ctx_create": (_i, [_i, C.POINTER(_vp)]),
     "ullm_cuda_ctx_destroy": (None, [_vp]),
     "ullm_cuda_last_error": (C.c_char_p, [_vp]),
+    "ullm_cuda_ctx_set_option": (_i, [_vp, _i, _i]),
     "ullm_cuda_device_name": (_i, [_vp, C.c_char_p, _sz]),
     "ullm_cuda_sm_count": (_i, [_vp]),
     "ullm_cuda_synchronize": (_i, [_vp]),
@@ -71,6 +75,7 @@ SIGNATURES = {
     "ullm_cuda_weight_matvec": (_i, [_vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_dev": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_batch_dev": (_i, [_vp, _sz, _vp, _vp, _vp, _vp]),
+    "ullm_cuda_weight_matvec_batch": (_i, [_vp, _sz, _vp, _vp, _vp]),
     "ullm_cuda_weight_matvec_chain_dev": (_i, [_vp, _sz, _vp, _vp]),
     "ullm_cuda_weight_matmul": (_i, [_vp, _vp, _vp, _vp, _sz]),
     "ullm_cuda_weight_matmul_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
@@ -80,6 +85,24 @@ SIGNATURES = {
     "ullm_cuda_matmul_quant": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "ullm_cuda_matmul_mlx4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),
     "ullm_cuda_matmul_dev": (_i, [_vp, _i, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _sz, _sz, _vp]),
+    "ullm_cuda_shard_create": (_i, [_vp, _i, _i, _sz, C.POINTER(_vp)]),
+    "ullm_cuda_shard_destroy": (None, [_vp]),
+    "ullm_cuda_shard_export": (_i, [_vp, _vp]),
+    "ullm_cuda_shard_connect": (_i, [_vp, _vp]),
+    "ullm_cuda_shard_connect_local": (_i, [_vp, _i]),
+    "ullm_cuda_shard_reset": (_i, [_vp]),
+    "ullm_cuda_shard_y": (_vp, [_vp]),
+    "ullm_cuda_shard_read": (_i, [_vp, _sz, _vp, _sz]),
+    "ullm_cuda_shard_row_range": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
+    "ullm_cuda_shard_weight_create": (_i, [_vp, _vp, _i, C.POINTER(_vp)]),
+    "ullm_cuda_shard_matvec_dev": (_i, [_vp, _sz, _vp, _i, _vp]),
+    "ullm_cuda_shard_matvec": (_i, [_vp, _sz, _vp, _vp, _vp, _sz, _sz]),
+    "ullm_cuda_shard_wait_dev": (_i, [_vp, _vp]),
+    "ullm_cuda_shard_matmul_dev": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _i, _vp]),
+    "ullm_cuda_shard_nccl_id": (_i, [_vp]),
+    "ullm_cuda_shard_nccl_init": (_i, [_vp, _vp]),
+    "ullm_cuda_shard_allgather_nccl_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "ullm_cuda_shard_nccl_check": (_i, [_vp]),
     "ullm_cuda_experts_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "ullm_cuda_experts_create_st": (_i, [_vp, _vp, C.c_char_p, _sz, _sz, _sz, _sz, C.POINTER(_vp)]),
     "ullm_cuda_experts_destroy": (None, [_vp, _vp]),
@@ -101,7 +124,6 @@ SIGNATURES = {
 DEBUG_SIGNATURES = {
     "ullm_cuda_debug_set": (_i, [_vp, C.c_char_p, _i]),
     "ullm_cuda_debug_last_plan": (_i, [_vp, _vp, _i]),
-    "ullm_cuda_debug_trace": (_i, [_vp]),
 }
 
 
@@ -275,7 +297,11 @@ class CudaContext:
             self._lib.ullm_cuda_matmul_dev(self._h, dtype, d_w, d_scales, d_biases, table_dtype, group, d_x, d_y, out_dim, in_dim, s, stream)
         )
 
-    # -- knobs used by tests and benchmarks ---------------------------------
+    def set_option(self, option: int, value: int):
+        """``ullm_cuda_ctx_set_option``: ``OPT_PDL`` or ``OPT_SHARD_TIMEOUT_MS``."""
+        self._check(self._lib.ullm_cuda_ctx_set_option(self._h, option, value))
+
+    # -- knobs used by tests --------------------------------------------------
     def debug_set(self, key: str, value: int):
         self._check(self._lib.ullm_cuda_debug_set(self._h, key.encode(), value))
 
@@ -372,6 +398,143 @@ class WeightBatch:
     def launch(self, stream=None):
         c = self._ctx
         c._check(c._lib.ullm_cuda_weight_matvec_batch_dev(c._h, self._n, self._w, self._x, self._y, stream))
+
+
+class HostBatch:
+    """The same list from host vectors in one blocking call (``ullm_cuda_weight_matvec_batch``):
+    ``xs`` / ``ys`` are float32 numpy arrays (page-locked ones are moved without the copy engines)."""
+
+    def __init__(self, ctx: CudaContext, weights, xs, ys):
+        n = len(weights)
+        self._ctx, self._n, self._keep = ctx, n, (weights, xs, ys)
+        self._w = (_vp * n)(*[w._h for w in weights])
+        self._x = (_vp * n)(*[x.ctypes.data for x in xs])
+        self._y = (_vp * n)(*[y.ctypes.data for y in ys])
+
+    def run(self):
+        c = self._ctx
+        c._check(c._lib.ullm_cuda_weight_matvec_batch(c._h, self._n, self._w, self._x, self._y))
+
+
+class ShardOpC(C.Structure):
+    """``ullm_shard_op``."""
+
+    _fields_ = [("w", _vp), ("d_x", _vp), ("y_offset", _sz), ("row0", _sz)]
+
+
+class Shard:
+    """One rank's end of a row-sharded group (``ullm_cuda_shard``): a gather buffer of
+    ``y_floats`` floats with the same layout on every rank, into which every rank's kernels
+    store the rows they computed.  Connect the ranks with :meth:`export` / :meth:`connect`
+    (one process per GPU; the handles are plain bytes to be exchanged by any means) or with
+    :func:`connect_local` (one process, several GPUs)."""
+
+    def __init__(self, ctx: CudaContext, world: int, rank: int, y_floats: int):
+        self._ctx, self.world, self.rank, self.y_floats = ctx, world, rank, y_floats
+        h = _vp()
+        ctx._check(ctx._lib.ullm_cuda_shard_create(ctx._h, world, rank, y_floats, C.byref(h)))
+        self._h = h.value
+
+    def export(self) -> bytes:
+        buf = C.create_string_buffer(SHARD_HANDLE_BYTES)
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_export(self._h, buf))
+        return buf.raw
+
+    def connect(self, handles):
+        """``handles``: the ``world`` exported handles in rank order."""
+        blob = b"".join(handles)
+        assert len(blob) == self.world * SHARD_HANDLE_BYTES
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_connect(self._h, C.c_char_p(blob)))
+
+    @staticmethod
+    def connect_local(shards):
+        arr = (_vp * len(shards))(*[s._h for s in shards])
+        shards[0]._ctx._check(shards[0]._ctx._lib.ullm_cuda_shard_connect_local(arr, len(shards)))
+
+    def reset(self):
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_reset(self._h))
+
+    @property
+    def y_ptr(self) -> int:
+        return self._ctx._lib.ullm_cuda_shard_y(self._h)
+
+    def read_y(self, offset: int, n: int) -> np.ndarray:
+        """``n`` floats of this rank's gather buffer (``ullm_cuda_shard_read``: blocking; the step that
+        wrote them must have finished)."""
+        out = np.empty(n, np.float32)
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_read(self._h, offset, _ptr(out), n))
+        return out
+
+    def row_range(self, out_dim: int) -> tuple[int, int]:
+        r0, n = _sz(), _sz()
+        rc = self._ctx._lib.ullm_cuda_shard_row_range(out_dim, self.world, self.rank, C.byref(r0), C.byref(n))
+        if rc:
+            raise FormatError(rc, f"{out_dim} rows do not split evenly over {self.world} ranks")
+        return r0.value, n.value
+
+    def weight(self, dtype: int, data, out_dim: int, cols: int, scales=None, biases=None, group: int = 0) -> "Weight":
+        """This rank's rows of the full host matrix (``ullm_cuda_shard_weight_create``)."""
+        b = _bytes(data)
+        tdt, s, bi = F32, None, None
+        if scales is not None:
+            if np.asarray(scales).dtype == np.uint16:
+                tdt, s, bi = BF16, np.ascontiguousarray(scales, np.uint16), np.ascontiguousarray(biases, np.uint16)
+            else:
+                s, bi = _f32(scales), _f32(biases)
+        gw = GpuWeight(dtype, b.ctypes.data, b.size, out_dim, cols, _ptr(s), _ptr(bi), group)
+        h = _vp()
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_weight_create(self._h, C.byref(gw), tdt, C.byref(h)))
+        w = Weight.__new__(Weight)
+        w._ctx, w._h, w.out, w.cols, w.dtype = self._ctx, h.value, out_dim // self.world, cols, dtype
+        return w
+
+    def ops(self, items):
+        """``items``: dicts ``w`` (:class:`Weight`), ``x`` (device address), ``y_offset`` and optionally ``row0``."""
+        arr = (ShardOpC * len(items))()
+        for c, o in zip(arr, items):
+            c.w, c.d_x, c.y_offset, c.row0 = o["w"]._h, o["x"], o["y_offset"], o.get("row0", 0)
+        arr._keep = [o["w"] for o in items]
+        return arr
+
+    def matvec_dev(self, ops, stream=None, flags: int = 0):
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_matvec_dev(self._h, len(ops), ops, flags, stream))
+
+    def matvec_host(self, ops, xs_host, y_host: np.ndarray, y_offset: int):
+        """One blocking step from host vectors (``ullm_cuda_shard_matvec``); ``y_host`` receives the gathered floats."""
+        xp = (_vp * len(ops))(*[x.ctypes.data if x is not None else None for x in xs_host])
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_matvec(self._h, len(ops), ops, xp, y_host.ctypes.data, y_offset, y_host.size))
+
+    def wait_dev(self, stream=None):
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_wait_dev(self._h, stream))
+
+    def matmul_dev(self, w: "Weight", d_x: int, tokens: int, y_offset: int, row0: int, out_total: int, stream=None, flags: int = 0):
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_matmul_dev(self._h, w._h, d_x, tokens, y_offset, row0, out_total, flags, stream))
+
+    # NCCL comparison arm
+    def nccl_id(self) -> bytes:
+        buf = C.create_string_buffer(SHARD_NCCL_ID_BYTES)
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_nccl_id(buf))
+        return buf.raw
+
+    def nccl_init(self, ident: bytes):
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_nccl_init(self._h, C.c_char_p(ident)))
+
+    def allgather_nccl_dev(self, d_send: int, d_recv: int, count: int, stream=None):
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_allgather_nccl_dev(self._h, d_send, d_recv, count, stream))
+
+    def nccl_check(self):
+        self._ctx._check(self._ctx._lib.ullm_cuda_shard_nccl_check(self._h))
+
+    def free(self):
+        if getattr(self, "_h", None):
+            self._ctx._lib.ullm_cuda_shard_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
 
 
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2

@@ -72,6 +72,18 @@ void ullm_cuda_ctx_destroy(ullm_cuda_ctx *c) {
 
 const char *ullm_cuda_last_error(const ullm_cuda_ctx *c) { return c ? c->err : "null context"; }
 
+int ullm_cuda_ctx_set_option(ullm_cuda_ctx *c, int option, int value) {
+    if (!c) return ULLM_ERR_INVALID;
+    switch (option) {
+    case ULLM_OPT_PDL: c->use_pdl = value != 0; return ULLM_OK;
+    case ULLM_OPT_SHARD_TIMEOUT_MS:
+        if (value < 1) return ctx_fail(c, ULLM_ERR_INVALID, "the time limit must be at least 1 ms");
+        c->shard_timeout_ms = value;
+        return ULLM_OK;
+    default: return ctx_fail(c, ULLM_ERR_INVALID, "unknown option %d", option);
+    }
+}
+
 int ullm_cuda_device_name(const ullm_cuda_ctx *c, char *name, size_t cap) {
     if (!c || !name || cap == 0) return ULLM_ERR_INVALID;
     snprintf(name, cap, "%s", c->name);
@@ -221,6 +233,7 @@ int ullm_cuda_matvec_dev(ullm_cuda_ctx *c, int dtype, const void *d_w, const voi
     cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
     MatvecOpts mo;
     mo.force_generic = c->force_generic, mo.pdl = c->use_pdl, mo.plan_out = &c->last_plan;
+    mo.plan_wr = c->plan_wr, mo.plan_rw = c->plan_rw, mo.plan_stages = c->plan_stages;
     ULLM_CUDA_TRY(c, launch_matvec(c->dev, fmt, d_w, tb, d_x, d_y, out_dim, in_dim, c->d_status, st, mo));
     return ULLM_OK;
 }
@@ -286,14 +299,6 @@ int ullm_cuda_matvec_mlx4(ullm_cuda_ctx *c, const void *w, const float *scales, 
 }
 
 // ---- resident weights ------------------------------------------------------
-struct ullm_cuda_weight {
-    int fmt = 0;          // kernel format, FMT_Q6KR when the rows were prepared
-    int dtype = 0;        // ullm_dtype the caller gave
-    void *w = nullptr;
-    void *scales = nullptr, *biases = nullptr;
-    int table_bytes = 4;
-    size_t group = 0, out = 0, cols = 0, nbytes = 0, tbytes = 0;
-};
 
 int ullm_cuda_weight_create(ullm_cuda_ctx *c, const ullm_gpu_weight *gw, int mlx_table_dtype, ullm_cuda_weight **out) {
     if (!c || !gw || !out || !gw->bytes) return ULLM_ERR_INVALID;
@@ -375,6 +380,7 @@ int ullm_cuda_weight_matvec_dev(ullm_cuda_ctx *c, const ullm_cuda_weight *w, con
     tb.scales = w->scales, tb.biases = w->biases, tb.elem_bytes = w->table_bytes, tb.group = w->group;
     MatvecOpts mo;
     mo.force_generic = c->force_generic && w->fmt != FMT_Q6KR, mo.pdl = c->use_pdl, mo.plan_out = &c->last_plan;
+    mo.plan_wr = c->plan_wr, mo.plan_rw = c->plan_rw, mo.plan_stages = c->plan_stages;
     cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
     ULLM_CUDA_TRY(c, launch_matvec(c->dev, w->fmt, w->w, tb, d_x, d_y, w->out, w->cols, c->d_status, st, mo));
     return ULLM_OK;
@@ -411,6 +417,15 @@ int ullm_cuda_weight_matvec_chain_dev(ullm_cuda_ctx *c, size_t n, const ullm_cha
         m.fmt = o.w->fmt, m.w = o.w->w, m.x = o.d_x, m.y = o.d_y, m.out_dim = o.w->out, m.in_dim = o.w->cols;
         m.norm_w = o.d_norm_w, m.eps = o.eps, m.epi = o.epi, m.res = o.d_res, m.dep = o.dep != 0;
         chain_ok = chain_ok && matvec_chain_supported(m.fmt, m.out_dim, m.in_dim, m.epi);
+    }
+    // Independent ops on large matrices run faster as separate programmatically chained launches (each with the
+    // tile plan that suits its shape) than through one ring sized for the largest of them; the persistent launch
+    // pays off where the per-launch fixed cost matters: small matrices, or ops that depend on each other.
+    if (chain_ok && c->use_pdl && !c->prefer_chain) {
+        bool any_dep = false;
+        size_t bytes = 0;
+        for (size_t i = 0; i < n; ++i) any_dep = any_dep || v[i].dep, bytes += ops[i].w->nbytes;
+        if (!any_dep && bytes / n >= ((size_t)48 << 20)) chain_ok = false;
     }
     // one persistent launch per run of at most 12 ops; anything it cannot take goes op by op
     if (chain_ok) {
@@ -508,6 +523,40 @@ int ullm_cuda_weight_matvec(ullm_cuda_ctx *c, const ullm_cuda_weight *w, const f
     if ((rc = ullm_cuda_weight_matvec_dev(c, w, (const float *)d_x, (float *)d_y, nullptr))) return rc;
     if (yv) ULLM_CUDA_TRY(c, vec_copy((const float *)d_y, yv, w->out, c->stream));
     else ULLM_CUDA_TRY(c, cudaMemcpyAsync(y, d_y, w->out * 4, cudaMemcpyDeviceToHost, c->stream));
+    ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return ctx_check_status(c);
+}
+
+int ullm_cuda_weight_matvec_batch(ullm_cuda_ctx *c, size_t n, const ullm_cuda_weight *const *w, const float *const *x, float *const *y) {
+    if (!c || (n && (!w || !x || !y))) return ULLM_ERR_INVALID;
+    if (n == 0) return ULLM_OK;
+    ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
+    // one staging area for all inputs and one for all outputs, every vector 16-byte aligned inside it
+    size_t xin = 0, yout = 0;
+    for (size_t i = 0; i < n; ++i) {
+        if (!w[i] || !x[i] || !y[i]) return ULLM_ERR_INVALID;
+        xin += (w[i]->cols + 3) & ~(size_t)3, yout += (w[i]->out + 3) & ~(size_t)3;
+    }
+    void *d_x = nullptr, *d_y = nullptr;
+    int rc;
+    if ((rc = ctx_scratch(c, 4, xin * 4, &d_x)) || (rc = ctx_scratch(c, 5, yout * 4, &d_y))) return rc;
+    std::vector<ullm_chain_op> ops(n);
+    size_t xo = 0, yo = 0;
+    for (size_t i = 0; i < n; ++i) {
+        float *dx = (float *)d_x + xo, *dy = (float *)d_y + yo;
+        const float *xv = c->no_host_kernels ? nullptr : device_view_of_host(x[i]);
+        if (xv) ULLM_CUDA_TRY(c, vec_copy(xv, dx, w[i]->cols, c->stream));
+        else ULLM_CUDA_TRY(c, cudaMemcpyAsync(dx, x[i], w[i]->cols * 4, cudaMemcpyHostToDevice, c->stream));
+        ops[i] = ullm_chain_op{};
+        ops[i].w = w[i], ops[i].d_x = dx, ops[i].d_y = dy;
+        xo += (w[i]->cols + 3) & ~(size_t)3, yo += (w[i]->out + 3) & ~(size_t)3;
+    }
+    if ((rc = ullm_cuda_weight_matvec_chain_dev(c, n, ops.data(), nullptr))) return rc;
+    for (size_t i = 0; i < n; ++i) {
+        float *yv = c->no_host_kernels ? nullptr : (float *)device_view_of_host(y[i]);
+        if (yv) ULLM_CUDA_TRY(c, vec_copy(ops[i].d_y, yv, w[i]->out, c->stream));
+        else ULLM_CUDA_TRY(c, cudaMemcpyAsync(y[i], ops[i].d_y, w[i]->out * 4, cudaMemcpyDeviceToHost, c->stream));
+    }
     ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     return ctx_check_status(c);
 }
@@ -660,30 +709,19 @@ int ullm_cuda_matmul_mlx4(ullm_cuda_ctx *c, const void *w, const float *scales, 
     return matmul_host(c, ULLM_DTYPE_MLX_U32, d_w, d_s, d_b, ULLM_DTYPE_F32, group, x, y, out_dim, in_dim, s);
 }
 
-// ---- test / tuning knobs (not part of the mirrored surface) ------------------
+// ---- test knobs (not part of the mirrored surface; every one is per context) ----
 extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value) {
     if (!c || !key) return ULLM_ERR_INVALID;
     if (!strcmp(key, "force_generic")) c->force_generic = value != 0;
-    else if (!strcmp(key, "pdl")) c->use_pdl = value != 0;
     else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
     else if (!strcmp(key, "gemm_min_s")) c->gemm_min_s = value;
     else if (!strcmp(key, "no_chain")) c->no_chain = value != 0;
+    else if (!strcmp(key, "prefer_chain")) c->prefer_chain = value != 0;
     else if (!strcmp(key, "no_host_kernels")) c->no_host_kernels = value != 0;
-    else if (!strcmp(key, "gemm_mode")) gemm_set_debug_mode(value);
-    else if (!strcmp(key, "skip_compute")) matvec_set_skip_compute(value);
-    else if (!strcmp(key, "chunk")) matvec_set_chunk(value);
-    else if (!strcmp(key, "stagger")) matvec_set_stagger(value);
-    else if (!strcmp(key, "slices")) matvec_set_slices(value);
-    else if (!strcmp(key, "ctas_per_sm")) matvec_set_ctas_per_sm(value);
-    else if (!strcmp(key, "plan_wr")) c->plan_wr = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
-    else if (!strcmp(key, "plan_rw")) c->plan_rw = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
-    else if (!strcmp(key, "plan_stages")) c->plan_stages = value, matvec_set_plan_override(c->plan_wr, c->plan_rw, c->plan_stages);
+    else if (!strcmp(key, "plan_wr")) c->plan_wr = value;
+    else if (!strcmp(key, "plan_rw")) c->plan_rw = value;
+    else if (!strcmp(key, "plan_stages")) c->plan_stages = value;
     else return ULLM_ERR_INVALID;
-    return ULLM_OK;
-}
-extern "C" int ullm_cuda_debug_trace(void *d_buf) {
-    matvec_set_trace(d_buf);
-    gemm_set_trace(d_buf);
     return ULLM_OK;
 }
 extern "C" int ullm_cuda_debug_last_plan(const ullm_cuda_ctx *c, int *vals, int n) {

@@ -28,14 +28,29 @@ struct ullm_cuda_ctx {
         size_t cap = 0;
     } scratch[8];
     bool force_generic = false;
-    bool use_pdl = false;
+    bool use_pdl = true;  // programmatic dependent launch between the library's kernels (ULLM_OPT_PDL)
     bool no_prepare = false; // keep Q6_K weights in their verbatim bytes (tests)
     bool no_chain = false;   // run op lists one kernel per op (tests, comparisons)
+    bool prefer_chain = false; // always take the persistent launch when the ops allow it (comparisons)
     bool no_host_kernels = false; // host vectors always through cudaMemcpyAsync (comparisons)
     unsigned *d_sync = nullptr; // grid-barrier counter of the chain kernel
     int plan_wr = 0, plan_rw = 0, plan_stages = 0;
+    int shard_timeout_ms = 2000; // ULLM_OPT_SHARD_TIMEOUT_MS
     int gemm_min_s = 32; // batches below this many tokens use per-token matvecs
     ullm::MatvecPlan last_plan;
+};
+
+// A weight matrix resident on the device (the `WBuf` of the reference, forward.rs:119-126).
+struct ullm_cuda_weight {
+    int fmt = 0;          // kernel format, FMT_Q6KR when the rows were prepared
+    int dtype = 0;        // ullm_dtype the caller gave
+    void *w = nullptr;
+    void *scales = nullptr, *biases = nullptr;
+    int table_bytes = 4;
+    size_t group = 0, out = 0, cols = 0, nbytes = 0, tbytes = 0;
+    // Row-sharded weights (ullm_cuda_shard_weight_create): this object holds rows
+    // [row0, row0 + out) of a matrix of out_total rows; out_total == 0 for ordinary weights.
+    size_t row0 = 0, out_total = 0;
 };
 
 inline int ctx_fail(ullm_cuda_ctx *c, int code, const char *fmt, ...) {

@@ -25,15 +25,12 @@
 // Every mbarrier wait is bounded; on expiry the CTA records a status, stops issuing
 // work, still frees its tensor memory and leaves.
 //
-// Measured on B200 (cycle stamps of every warp's arrival): with one warp per (row quarter, column part)
-// the two dequantization warps that share a warp scheduler with the MMA-issuing thread finished each
-// chunk last and set the pace: a warp's chain wait -> unpack -> tcgen05.st -> wait::st -> arrive is
-// long against the chunk period, and any slot lost to the service warp shows.  Two phases give every
-// warp two chunk periods for that chain (857 -> 938 TFLOP/s on the 70B block at 512 tokens); three
-// phases (Q4_K fits in 72 registers) bring nothing more.  The service warps sit on four different
-// schedulers.
+// Why two phases: a dequantization warp's chain wait -> unpack -> tcgen05.st -> wait::st -> arrive is long
+// against the chunk period; with two phases every warp has two chunk periods for it.  The service warps
+// (TMA, allocation, MMA issue) sit on four different warp schedulers.
 #include "kernels.h"
 #include "matvec_core.cuh"
+#include "shard_dev.cuh"
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -139,8 +136,12 @@ struct GemmParams {
     int epi;                   // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU, applied here only when there is one k slice
     const float *res;          // EPI_RESIDUAL: y = res + W x (may alias y)
     uint32_t ldy;              // elements between two tokens in y / res (the full matrix' rows when this launch covers a row range)
+    int sh_world;              // > 0: every output element goes to the same place in all ranks' gather buffers (EPI_STORE)
+    long long sh_delta[SHARD_MAX_RANKS];
+#ifdef ULLM_TUNING
     long long *trace; // measurement only: cycle stamps of CTA (0, 0)
     uint32_t mode; // measurement only: bit 0 skips the dequantization, bit 1 the activation loads, bit 2 the MMAs
+#endif
 };
 // x: bf16 activations [s, in], 128-byte swizzle.  w0..w2: the packed weight bytes as plain
 // 2-D byte tensors [out rows, row bytes] — Q4_K: w0 = whole 144-byte blocks; prepared
@@ -332,8 +333,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
     const uint32_t kb0 = blockIdx.z * p.blocks_per_split;
     const uint32_t nb = min(p.blocks_per_split, p.in_dim / QK_K - kb0), nchunks = nb * 4;
     float *const yout = p.y + (size_t)blockIdx.z * p.s * p.out_dim;
+#ifdef ULLM_TUNING
     const bool traced = DBG && p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
     const uint32_t mode = DBG ? p.mode : 0u; // stages switched off for measurement
+    long long *const trace = p.trace;
+    const bool traced_any = DBG && p.trace;
+#else
+    constexpr bool traced_any = false;
+    constexpr bool traced = false;
+    constexpr uint32_t mode = 0u;
+    long long *const trace = nullptr;
+#endif
 
     if (tid == 0) {
         for (int i = 0; i < G_STAGES; ++i) {
@@ -374,7 +384,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
                 }
                 if (rank == 0) mbar_arrive_expect_tx(&full[c], 2 * G_B_BYTES); // both halves land on the leader's barrier
                 tma_load_2d(b_tiles + c * G_B_BYTES, &maps.x, (int)((kb0 * 4 + g) * GKC), (int)(n0 + rank * GNH), lead_full);
-                if (traced && g < 500) p.trace[6000 + g] = clock64();
+                if (traced && g < 500) trace[6000 + g] = clock64();
             }
         }
     } else if (warp == (uint32_t)g_raw_warp(PH)) {
@@ -423,11 +433,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
                     const uint32_t g = g0 + c;
                     if (g >= nchunks || !ok) break;
                     const bool tr = traced && g < 1024 && lane == 0;
-                    if (tr) p.trace[4 * g] = clock64();
+                    if (tr) trace[4 * g] = clock64();
                     if (tr && g >= 96 && g < 112) {
                         unsigned long long gt;
                         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-                        p.trace[7000 + 16 * 32 + (g - 96)] = (long long)gt;
+                        trace[7000 + 16 * 32 + (g - 96)] = (long long)gt;
                     }
                     const uint32_t cn = (c + 1) % G_STAGES, parn = (c + 1 == G_STAGES ? it + 1 : it) & 1;
                     const bool has_next = g + 1 < nchunks && !(mode & 8u);
@@ -471,9 +481,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
                           "r"(smem_u32(&freeb[c])), "h"((uint16_t)3)
                         : "memory");
                     if (!has_next) next_ready = 1;
-                    if (tr) p.trace[4 * g + 1] = clock64();
+                    if (tr) trace[4 * g + 1] = clock64();
                     if (!__all_sync(0xffffffffu, next_ready != 0)) ok = warp_wait(&full[cn], parn, lane);
-                    if (tr) p.trace[4 * g + 3] = clock64();
+                    if (tr) trace[4 * g + 3] = clock64();
                 }
             }
             if (lane == 0) {
@@ -500,9 +510,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
                 const uint32_t g = 4 * kb + c, ca = g % G_STAGES;
                 if (g % PH != phase) continue; // another phase's chunk
                 const bool tr = traced && g < 1024 && dt == 0;
-                if (tr) p.trace[4096 + 4 * g] = clock64();
+                if (tr) trace[4096 + 4 * g] = clock64();
                 if (g >= G_STAGES && !(mode & 16u)) ok = ok && warp_wait(&freeb[ca], ((g / G_STAGES) - 1) & 1, lane);
-                if (tr) p.trace[4096 + 4 * g + 1] = clock64();
+                if (tr) trace[4096 + 4 * g + 1] = clock64();
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); // the MMAs that read this stage are done
                 if (!(mode & 1u)) chunk_store(blk, c, part, ta_lane + ca * G_A_COLS);
@@ -510,12 +520,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&full[ca]), 0));
-                if (DBG && p.trace && blockIdx.x < 2 && blockIdx.y == 0 && lane == 0 && g >= 96 && g < 112) {
+                if (DBG && traced_any && blockIdx.x < 2 && blockIdx.y == 0 && lane == 0 && g >= 96 && g < 112) {
                     unsigned long long gt;
                     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-                    p.trace[7000 + (g - 96) * 32 + rank * 16 + (warp - 2)] = (long long)gt;
+                    trace[7000 + (g - 96) * 32 + rank * 16 + (warp - 2)] = (long long)gt;
                 }
-                if (tr) p.trace[4096 + 4 * g + 2] = clock64();
+                if (tr) trace[4096 + 4 * g + 2] = clock64();
             }
         }
         if (!ok) *(volatile int *)p.status = DEV_TIMEOUT;
@@ -552,7 +562,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
                         const uint32_t tok = n0 + col0 + j;
                         if (tok < p.s) {
                             const size_t at = (size_t)tok * p.ldy + orow;
-                            yout[at] = p.epi == EPI_RESIDUAL ? p.res[at] + __uint_as_float(v[j]) : __uint_as_float(v[j]);
+                            if (p.sh_world) {
+                                for (int r = 0; r < p.sh_world; ++r) *(float *)((char *)(yout + at) + p.sh_delta[r]) = __uint_as_float(v[j]);
+                            } else {
+                                yout[at] = p.epi == EPI_RESIDUAL ? p.res[at] + __uint_as_float(v[j]) : __uint_as_float(v[j]);
+                            }
                         }
                     }
                 }
@@ -587,8 +601,12 @@ __global__ void cast_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__r
 
 // split-K: the [s, rows] partial sums of the k slices added in slice order (deterministic), then the
 // epilogue; y / res have `ldy` elements between tokens
+struct ShardDeltas {
+    int world;
+    long long delta[SHARD_MAX_RANKS];
+};
 __global__ void splitk_reduce_kernel(const float *__restrict__ part, float *y, size_t s, size_t rows, size_t ldy, int splits, int epi,
-                                     const float *res) {
+                                     const float *res, const ShardDeltas sd) {
     const size_t n = s * rows, i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
     float a[4] = {0.f, 0.f, 0.f, 0.f};
@@ -610,7 +628,11 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ part, float *y, s
     } else {
         for (int k = 0; k < cnt; ++k) {
             const size_t tok = (i + k) / rows, r = (i + k) % rows, at = tok * ldy + r;
-            y[at] = epi == EPI_RESIDUAL ? res[at] + a[k] : a[k];
+            if (sd.world) {
+                for (int q = 0; q < sd.world; ++q) *(float *)((char *)(y + at) + sd.delta[q]) = a[k];
+            } else {
+                y[at] = epi == EPI_RESIDUAL ? res[at] + a[k] : a[k];
+            }
         }
     }
 }
@@ -640,10 +662,12 @@ static bool encode_2d(EncodeTiledFn enc, CUtensorMap *map, CUtensorMapDataType d
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+#ifdef ULLM_TUNING
 static uint32_t g_gemm_mode = 0;
 static long long *g_gemm_trace = nullptr;
 void gemm_set_trace(void *d_buf) { g_gemm_trace = (long long *)d_buf; }
 void gemm_set_debug_mode(int mode) { g_gemm_mode = (uint32_t)mode; }
+#endif
 
 bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s) {
     if (fmt != FMT_Q4K && fmt != FMT_Q6KR) return false;
@@ -708,7 +732,8 @@ template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, 
 // One launch (plus the split-K reduction) over `rows` weight rows starting at `w`; y / res point at the
 // first of these rows' outputs, `ldy` elements between tokens.
 static cudaError_t gemm_part(EncodeTiledFn enc, int fmt, const uint8_t *w, size_t rows, size_t in_dim, size_t s, int z, GemmMaps maps,
-                             float *y, const float *res, size_t ldy, int epi, float *part, int *d_status, cudaStream_t st) {
+                             float *y, const float *res, size_t ldy, int epi, float *part, int *d_status, cudaStream_t st,
+                             const ShardDev *shard) {
     const size_t nb = in_dim / QK_K;
     bool ok = true;
     if (fmt == FMT_Q4K) {
@@ -728,21 +753,35 @@ static cudaError_t gemm_part(EncodeTiledFn enc, int fmt, const uint8_t *w, size_
     p.y = gz > 1 ? part : y, p.status = d_status;
     p.epi = gz > 1 ? EPI_STORE : epi, p.res = res, p.ldy = gz > 1 ? (uint32_t)rows : (uint32_t)ldy;
     p.out_dim = (uint32_t)rows, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
-    p.mode = g_gemm_mode, p.trace = g_gemm_trace;
+    // sharded: the launch that produces the final values stores them into every rank's buffer
+    ShardDeltas sd{};
+    if (shard) {
+        sd.world = shard->world;
+        for (int r = 0; r < shard->world; ++r) sd.delta[r] = shard->delta[r];
+    }
+    p.sh_world = gz > 1 ? 0 : sd.world;
+    for (int r = 0; r < SHARD_MAX_RANKS; ++r) p.sh_delta[r] = sd.delta[r];
     const dim3 grid(2 * (unsigned)((rows + 2 * GM - 1) / (2 * GM)), (unsigned)((s + GN - 1) / GN), gz);
     cudaError_t e;
+#ifdef ULLM_TUNING
+    p.mode = g_gemm_mode, p.trace = g_gemm_trace;
     if (p.mode || p.trace) e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, true>(p, maps, grid, st) : launch_one<FMT_Q6KR, true>(p, maps, grid, st);
-    else e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
+    else
+#endif
+    e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
     if (e != cudaSuccess || gz == 1) return e;
     const size_t ny = s * rows;
-    splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, y, s, rows, ldy, (int)gz, epi, res);
+    splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, y, s, rows, ldy, (int)gz, epi, res, sd);
     return cudaGetLastError();
 }
 
 // d_w: FMT_Q4K verbatim rows or FMT_Q6KR prepared rows (16-byte aligned).  d_x f32 [s, in],
 // d_y f32 [s, out], d_xb16: scratch of gemm_tc_scratch_bytes (256-byte aligned).
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_xb16, size_t out_dim, size_t in_dim,
-                           size_t s, int sm_count, int *d_status, cudaStream_t st, int epi, const float *d_res) {
+                           size_t s, int sm_count, int *d_status, cudaStream_t st, int epi, const float *d_res, size_t ldy,
+                           const ShardDev *shard) {
+    if (ldy == 0) ldy = out_dim;
+    if (shard && (epi != EPI_STORE || shard->world < 1 || shard->world > SHARD_MAX_RANKS)) return cudaErrorInvalidValue;
     if (epi == EPI_SWIGLU && (out_dim & 1)) return cudaErrorInvalidValue;
     if (epi == EPI_RESIDUAL && !d_res) return cudaErrorInvalidValue;
     if (!gemm_tc_supported(fmt, out_dim, in_dim, s) || ((uintptr_t)d_w & 15)) return cudaErrorNotSupported;
@@ -759,10 +798,10 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
     const GemmPlan pl = gemm_plan(out_dim, in_dim, s, sm_count);
     const uint8_t *w = (const uint8_t *)d_w;
     const size_t ydiv = epi == EPI_SWIGLU ? 2 : 1; // SwiGLU halves the output rows
-    e = gemm_part(enc, fmt, w, pl.rows_main, in_dim, s, pl.z_main, maps, d_y, d_res, out_dim, epi, part, d_status, st);
+    e = gemm_part(enc, fmt, w, pl.rows_main, in_dim, s, pl.z_main, maps, d_y, d_res, ldy, epi, part, d_status, st, shard);
     if (e != cudaSuccess || pl.rows_tail == 0) return e;
     return gemm_part(enc, fmt, w + pl.rows_main * row_bytes, pl.rows_tail, in_dim, s, pl.z_tail, maps, d_y + pl.rows_main / ydiv,
-                     d_res ? d_res + pl.rows_main : nullptr, out_dim, epi, part, d_status, st);
+                     d_res ? d_res + pl.rows_main : nullptr, ldy, epi, part, d_status, st, shard);
 }
 
 } // namespace ullm

@@ -44,6 +44,7 @@ struct MatvecOpts {
     bool force_generic = false;
     bool pdl = false; // launch with programmatic stream serialization
     MatvecPlan *plan_out = nullptr;
+    int plan_wr = 0, plan_rw = 0, plan_stages = 0; // plan override (tests): row slices, rows per warp, ring depth; 0 = automatic
     // Fusions (streamed kernel only; cudaErrorNotSupported when the shape needs the
     // plain kernel):
     const float *norm_w = nullptr; // x <- rmsnorm(x, norm_w, eps) before the product
@@ -55,6 +56,40 @@ struct MatvecOpts {
 cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const MlxTables &tb, const float *d_x,
                           float *d_y, size_t out_dim, size_t in_dim, int *d_status, cudaStream_t st,
                           const MatvecOpts &opts = MatvecOpts());
+// Row-sharded output exchange (shard.cu).  Every rank of a group owns a gather buffer of the same
+// layout; a rank's kernels store the rows they computed at the same offset into EVERY rank's buffer
+// (plain stores through peer mappings over NVLink) and then publish a step number in every rank's
+// control block; a bounded wait on the ranks' step numbers tells a rank that all rows have arrived.
+constexpr int SHARD_MAX_RANKS = 8;
+constexpr int SHARD_CTL_STRIDE = 32;                 // unsigned words between control words: one 128-byte line each
+constexpr int SHARD_CTL_DONE = 8 * SHARD_CTL_STRIDE; // CTAs of the current launch that have stored all their rows
+constexpr int SHARD_CTL_STEP = 9 * SHARD_CTL_STRIDE; // number of exchanges this rank has published
+constexpr int SHARD_CTL_ABORT = 10 * SHARD_CTL_STRIDE;
+constexpr size_t SHARD_CTL_BYTES = 4096;             // control block in front of the gather buffer
+struct ShardDev {
+    int world = 0;                          // 0: not a sharded launch
+    int rank = 0;
+    long long delta[SHARD_MAX_RANKS] = {};  // bytes from an address in this rank's buffer to the same place in rank r's
+    unsigned *ctl = nullptr;                // this rank's control block: word r * SHARD_CTL_STRIDE = rank r's published step
+    unsigned *peer_flag[SHARD_MAX_RANKS] = {}; // this rank's word inside rank r's control block
+    int signal = 1;                         // publish when the launch is done (0: a later launch of the same exchange does)
+    int wait = 1;                           // ... and wait (bounded) for every rank's publication before the kernel ends
+    unsigned long long timeout_ns = 2000000000ull;
+};
+// Publishes the exchange whose rows earlier launches on `st` stored (and waits when sh.wait).
+cudaError_t launch_shard_signal(const ShardDev &sh, int *d_status, cudaStream_t st);
+// Waits (bounded) until every rank has published as many exchanges as this rank.
+cudaError_t launch_shard_wait(const ShardDev &sh, int *d_status, cudaStream_t st);
+// Copies `n` 2-D regions of this rank's buffer (first element, row length, rows, elements between rows; all in
+// floats) to the same places in every other rank's buffer, then publishes (and waits when sh.wait).
+struct ShardRegion {
+    float *ptr;
+    unsigned width, height;
+    size_t stride;
+};
+cudaError_t launch_shard_scatter(const DeviceInfo &dev, const ShardDev &sh, int n, const ShardRegion *regions, int *d_status,
+                                 cudaStream_t st);
+
 // A list of matvecs in one persistent launch (matvec_chain.cu).  `dep` marks an op whose x or
 // res was written by an earlier op of the same list.  d_sync: one zero-able unsigned in device memory.
 struct MatvecChainOp {
@@ -70,33 +105,21 @@ struct MatvecChainOp {
     bool dep = false;
 };
 bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi);
+// `shard` (optional): every op stores its rows into all ranks' gather buffers and the launch publishes the exchange.
 cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainOp *ops, unsigned *d_sync, int *d_status,
-                                cudaStream_t st, bool pdl);
-// Tuning override for tests / sweeps: force the row-slice count, rows per warp and
-// ring depth of the streamed plan (0 = automatic).
-void matvec_set_plan_override(int wr, int rw, int stages);
-// Tuning aid: device buffer (64 x u64 per CTA) receiving %globaltimer stamps of CTA
-// thread 0 (start, before / after x prep, before / after each tile wait, end); null = off.
-void matvec_set_trace(void *d_buf);
-// Tuning aid: stream the weight tiles but skip the arithmetic (memory-side ceiling).
-void matvec_set_skip_compute(int v);
-// Tuning aid: bytes per bulk copy of the tile stream (0 = default).
-void matvec_set_chunk(int v);
-void matvec_set_stagger(int v);
-void matvec_set_slices(int v); // 0: one barrier pair per tile instead of one per row slice (comparisons)
-// Tuning override: CTAs per SM of the streamed plan (0 = automatic, 1 or 2).
-void matvec_set_ctas_per_sm(int v);
+                                cudaStream_t st, bool pdl, const ShardDev *shard = nullptr);
 // prepare.cu — Q6_K rows <-> the prepared layout (FMT_Q6KR)
 bool q6k_can_prepare(size_t in_dim);
 cudaError_t launch_q6k_prepare(const void *d_src, void *d_dst, size_t rows, size_t in_dim, bool inverse, cudaStream_t st);
 // gemm.cu — tcgen05 / TMEM prefill GEMM on Q4_K (verbatim) or prepared Q6_K rows.
-void gemm_set_trace(void *d_buf); // >= 8192 int64: cycle stamps of CTA (0, 0)'s MMA and dequantization loops
-void gemm_set_debug_mode(int mode); // measurement only: stages of the GEMM kernel switched off
 bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s);
 size_t gemm_tc_scratch_bytes(size_t out_dim, size_t in_dim, size_t s, int sm_count); // bf16 activations + split-K partial sums
 // epi / d_res: the matvec's epilogues on the [s, out] result (EPI_SWIGLU writes [s, out / 2]; d_res may alias d_y)
+// ldy: elements between two tokens in d_y / d_res (0 = out_dim).  `shard` (optional, EPI_STORE only): every output element is
+// stored into all ranks' gather buffers (d_y points into this rank's); the caller publishes afterwards (launch_shard_signal).
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_scratch, size_t out_dim, size_t in_dim,
-                           size_t s, int sm_count, int *d_status, cudaStream_t st, int epi = EPI_STORE, const float *d_res = nullptr);
+                           size_t s, int sm_count, int *d_status, cudaStream_t st, int epi = EPI_STORE, const float *d_res = nullptr,
+                           size_t ldy = 0, const ShardDev *shard = nullptr);
 bool matvec_is_streamed(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
                         int epi);
 // Returns a static message when the shape cannot be computed at all.

@@ -138,12 +138,9 @@ struct StreamParams {
     uint32_t w_stage_bytes, tbl_stage_bytes, stage_bytes; // regions inside one stage (128-B multiples)
     uint32_t ncg;
     uint32_t off_part, off_prep, off_ring; // byte offsets in dynamic smem
-    unsigned long long *trace; // optional per-CTA timestamps (tuning aid), 64 slots per CTA
-    int skip_compute;          // tuning aid: stream the tiles but skip the arithmetic
-    uint32_t chunk;            // bytes per bulk copy (multiple of 16)
     int pdl;                   // launched with programmatic stream serialization
-    int stagger;               // request the first S tiles one after the other
 };
+constexpr uint32_t STREAM_CHUNK = 4096; // bytes per bulk copy (multiple of 16)
 
 constexpr int STREAM_MAX_THREADS = 800; // 24 consumer warps + the producer warp
 
@@ -162,15 +159,6 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool producer = warp == p.NW;
-    uint32_t tr = 0;
-    auto stamp = [&]() {
-        if (p.trace && tid == 0 && tr < 64) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[(size_t)blockIdx.x * 64 + tr++] = t;
-        }
-    };
-    stamp();
 
     // Rows are dealt to the CTAs as contiguous, balanced ranges (to within `gran`
     // rows); each CTA walks its range in tiles of R rows, the last one ragged.
@@ -216,7 +204,7 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
                 uint64_t *fb = &full[s * p.NSL + j];
                 if (lane == 0) {
                     if (k >= p.S) ok = wait_or_timeout(&empty[s * p.NSL + j], ph ^ 1u);
-                    else if (k > 0 && j == 0 && p.stagger) ok = wait_or_timeout(&full[(k - 1) * p.NSL + p.NSL - 1], 0);
+                    else if (k > 0 && j == 0) ok = wait_or_timeout(&full[(k - 1) * p.NSL + p.NSL - 1], 0);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
@@ -230,8 +218,8 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
                 __syncwarp();
                 const uint8_t *src = p.w + (size_t)(r0 + row0) * p.row_bytes;
                 uint8_t *d = dst + (size_t)row0 * p.row_bytes;
-                for (uint32_t off = lane * p.chunk; off < wb; off += 32 * p.chunk)
-                    bulk_g2s(d + off, src + off, min(p.chunk, wb - off), fb);
+                for (uint32_t off = lane * STREAM_CHUNK; off < wb; off += 32 * STREAM_CHUNK)
+                    bulk_g2s(d + off, src + off, min(STREAM_CHUNK, wb - off), fb);
                 if (FMT == FMT_MLX4 && lane < 2 && tb) {
                     const uint8_t *t = (lane ? p.biases : p.scales) + (size_t)(r0 + row0) * p.tbl_row_bytes;
                     bulk_g2s(dst + p.w_stage_bytes + lane * p.tbl_stage_bytes + (size_t)row0 * p.tbl_row_bytes, t, tb, fb);
@@ -271,10 +259,8 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
         asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // part is reused by the row reduction below
     }
     // x -> fixed-point register images, built once per CTA in shared memory
-    stamp();
     prep_image<FMT>(src, p.in_dim, prep, tid, nthr_c, &pre);
     asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
-    stamp();
 
     const uint32_t rs = warp / p.WC, cgw = warp % p.WC;
     uint32_t X[G][XR];
@@ -316,10 +302,8 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
     uint32_t slot = 0; // k mod 2S: stage s = slot mod S, mbarrier phase = slot / S
     for (uint32_t k = 0; k < ntiles; ++k, slot = slot + 1 == 2 * p.S ? 0 : slot + 1) {
         const uint32_t ph = slot >= p.S ? 1u : 0u, s = slot - ph * p.S;
-        stamp();
-        if (!aborted && !wait_or_timeout(&full[s * p.NSL + bslice], ph)) aborted = true;
-        stamp();
-        if (p.WC > 1 && k >= p.S) flush(k - p.S, ph ? s : s + p.S);
+            if (!aborted && !wait_or_timeout(&full[s * p.NSL + bslice], ph)) aborted = true;
+            if (p.WC > 1 && k >= p.S) flush(k - p.S, ph ? s : s + p.S);
         const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
         const uint32_t r0 = rbeg + k * p.R;
         float v[RW];
@@ -327,7 +311,7 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
         for (int rr = 0; rr < RW; ++rr) {
             v[rr] = 0.f;
             const uint32_t rl = rs * RW + rr;
-            if (!aborted && !p.skip_compute && r0 + rl < rend) {
+            if (!aborted && r0 + rl < rend) {
                 const uint32_t row_addr = stage + rl * p.row_bytes;
                 uint32_t ts, tb2;
                 if (FMT == FMT_Q6KR) ts = row_addr + 192u * nb, tb2 = row_addr + 208u * nb;
@@ -358,12 +342,10 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s * p.NSL + bslice]); // partials written, the slice may be refilled
     }
-    stamp();
     if (p.WC > 1) {
         asm volatile("bar.sync 1, %0;" ::"r"(p.NW * 32) : "memory"); // all partials of the last tiles are in
         for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt, kt % (2 * p.S));
     }
-    stamp();
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
 }
 
@@ -403,23 +385,9 @@ struct Plan {
     double score = 0;
 };
 
-// Tuning overrides (tests / sweeps): 0 = choose automatically.
-static int g_force_wr = 0, g_force_rw = 0, g_force_stages = 0, g_force_cpsm = 0;
-void matvec_set_ctas_per_sm(int v) { g_force_cpsm = v; }
-static unsigned long long *g_trace = nullptr;
-static int g_skip_compute = 0;
-static int g_chunk = 0;
-static int g_stagger = 1;
-static int g_slices = 1;
-void matvec_set_slices(int v) { g_slices = v; }
-void matvec_set_stagger(int v) { g_stagger = v; }
-void matvec_set_chunk(int v) { g_chunk = v; }
-void matvec_set_trace(void *p) { g_trace = (unsigned long long *)p; }
-void matvec_set_skip_compute(int v) { g_skip_compute = v; }
-void matvec_set_plan_override(int wr, int rw, int stages) { g_force_wr = wr, g_force_rw = rw, g_force_stages = stages; }
-
+// force_wr / force_rw / force_stages: the caller's plan override (tests), 0 = choose automatically.
 static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
-                        int epi) {
+                        int epi, int force_wr = 0, int force_rw = 0, int force_stages = 0) {
     Plan best;
     const uint32_t cg_elems = (fmt == FMT_Q4K || fmt == FMT_Q6KR) ? 2048u : 1024u;
     const uint32_t xregs = fmt == FMT_Q4K ? XREGS_Q4K : (fmt == FMT_Q6K ? XREGS_Q6K : (fmt == FMT_Q6KR ? XREGS_Q6KR : XREGS_MLX));
@@ -438,24 +406,22 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
     if (epi == EPI_SWIGLU) gran = std::max(gran, 2u);
     if (out_dim % gran) return best;
     const uint32_t ncg = (uint32_t)((in_dim + cg_elems - 1) / cg_elems);
-    // Two CTAs per SM (half the warps and half the ring each) let the CTAs of the next
-    // kernel of a programmatic-dependent chain move in and prefetch while this one runs.
-    const uint32_t cpsm = g_force_cpsm ? (uint32_t)g_force_cpsm : 1u;
-    const uint32_t max_warps = cpsm == 2 ? 12 : 24;
+    const uint32_t cpsm = 1u; // one CTA per SM
+    const uint32_t max_warps = 24;
     const uint32_t G = (ncg + 15) / 16;
     if (G > 2) return best;
     const uint32_t WC = (ncg + G - 1) / G;
     if (WC > max_warps) return best;
-    const int budget = cpsm == 2 ? (dev.max_smem_sm - 2048) / 2 - 1024 : dev.max_smem_optin - 1024;
+    const int budget = dev.max_smem_optin - 1024;
     const uint32_t units = (uint32_t)(out_dim / gran);
     const uint32_t grid = std::min<uint32_t>((uint32_t)dev.sm_count * cpsm, units);
     const uint32_t rows_cta = ((units + grid - 1) / grid) * gran; // the largest range
     for (uint32_t WR = 1; WR <= 15; ++WR) {
         if (WC * WR > max_warps) break;
         if (WC == 1 && WR > 24) break;
-        if (g_force_wr && (int)WR != g_force_wr) continue;
+        if (force_wr && (int)WR != force_wr) continue;
         for (uint32_t RW = (epi == EPI_SWIGLU ? 2 : 1); RW <= 4; RW *= 2) {
-            if (g_force_rw && (int)RW != g_force_rw) continue;
+            if (force_rw && (int)RW != force_rw) continue;
             const uint32_t R = WR * RW;
             if (R % gran) continue;
             const uint32_t wst = align_up(R * row_bytes, 128), tst = align_up(R * tbl_row_bytes, 128);
@@ -463,7 +429,7 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
             if (stage > 100 * 1024) continue;
             // one barrier pair per row slice when the slices are large (measured: slices of 47 KB, [4096,14336]
             // Q6_K, 13.7 -> 13.0 us; slices of 13-18 KB lose 10-20 %) and start 16-byte aligned, else one per tile
-            const uint32_t NSL = (g_slices && WR > 1 && RW * row_bytes >= 32768 && (RW * row_bytes) % 16 == 0 &&
+            const uint32_t NSL = (WR > 1 && RW * row_bytes >= 32768 && (RW * row_bytes) % 16 == 0 &&
                                   (RW * tbl_row_bytes) % 16 == 0) ? WR : 1u;
             const uint32_t off_part = align_up(2 * 8 * NSL * 8, 128); // up to 8 stages x NSL slices x (full, empty)
             const uint32_t off_prep = align_up(off_part + std::max(2 * 8 * R * WC * 4, 128u), 128);
@@ -472,7 +438,7 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
             const uint32_t tiles = (rows_cta + R - 1) / R;
             uint32_t S = std::min<uint32_t>(8, (budget - off_ring) / stage);
             S = std::min(S, std::max(2u, tiles));
-            if (g_force_stages) S = std::min<uint32_t>(S, (uint32_t)g_force_stages);
+            if (force_stages) S = std::min<uint32_t>(S, (uint32_t)force_stages);
             // Measured on B200 (plan sweeps on [28672,8192] and [8192,8192] Q4_K, [14336,4096] and [4096,14336]
             // Q6_K): the kernels are bound by instruction issue, not by HBM (about 200 warp instructions per
             // 2048 weights; streaming alone runs at 5.2 TB/s where the full kernel reached 3.9), so four rows per
@@ -480,9 +446,9 @@ static Plan plan_stream(const DeviceInfo &dev, int fmt, size_t out_dim, size_t i
             // the transposed reduction costs less per row), as many warps as the tile allows beat fewer, and two
             // stages of 70-95 KB are enough when that is what four rows per warp cost.
             const double eff = (double)rows_cta / ((double)tiles * R); // idle warps in the ragged tile
-            const double f_warps = std::sqrt(std::min(1.0, (WC * WR) / (cpsm == 2 ? 10.0 : 14.0)));
+            const double f_warps = std::sqrt(std::min(1.0, (WC * WR) / 14.0));
             const double f_rw = RW == 1 ? 0.75 : (RW == 2 ? 0.84 : 1.0);
-            const double f_stage = std::sqrt(std::min(1.0, stage / (cpsm == 2 ? 28672.0 : 45056.0)));
+            const double f_stage = std::sqrt(std::min(1.0, stage / 45056.0));
             const double f_depth = (S >= 3 || tiles <= S) ? 1.0 : 0.97;
             const double score = eff * f_warps * f_rw * f_stage * f_depth;
             if (score > best.score) {
@@ -555,7 +521,7 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
                          (!o.norm_w || (uintptr_t)o.norm_w % 16 == 0) &&
                          (fmt != FMT_MLX4 || ((uintptr_t)tb.scales % 16 == 0 && (uintptr_t)tb.biases % 16 == 0));
     if (o.epi == EPI_SWIGLU && (out_dim & 1)) return cudaErrorInvalidValue;
-    if (!o.force_generic && aligned) pl = plan_stream(dev, fmt, out_dim, in_dim, tb.group, tb.elem_bytes, o.epi);
+    if (!o.force_generic && aligned) pl = plan_stream(dev, fmt, out_dim, in_dim, tb.group, tb.elem_bytes, o.epi, o.plan_wr, o.plan_rw, o.plan_stages);
     if (o.plan_out) {
         o.plan_out->streamed = pl.ok;
         o.plan_out->rows_per_tile = pl.ok ? (int)pl.p.R : 8;
@@ -568,10 +534,7 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
         pl.p.w = (const uint8_t *)d_w, pl.p.scales = (const uint8_t *)tb.scales, pl.p.biases = (const uint8_t *)tb.biases;
         pl.p.x = d_x, pl.p.y = d_y, pl.p.status = d_status;
         pl.p.norm_w = o.norm_w, pl.p.eps = o.eps, pl.p.epi = o.epi, pl.p.res = o.res;
-        pl.p.trace = g_trace, pl.p.skip_compute = g_skip_compute;
         pl.p.pdl = o.pdl ? 1 : 0;
-        pl.p.stagger = g_stagger;
-        pl.p.chunk = g_chunk > 0 ? (uint32_t)g_chunk / 16 * 16 : 4096u;
         if (fmt == FMT_Q4K) return launch_stream_f<FMT_Q4K, float>(pl, st, o.pdl);
         if (fmt == FMT_Q6K) return launch_stream_f<FMT_Q6K, float>(pl, st, o.pdl);
         if (fmt == FMT_Q6KR) return launch_stream_f<FMT_Q6KR, float>(pl, st, o.pdl);

@@ -13,12 +13,13 @@
 //     image of x in registers, dp4a row sums, optional RMSNorm prologue and residual / SwiGLU
 //     epilogue — and wait at a grid-wide barrier only where an op reads what an earlier op
 //     of the same launch wrote;
-//   * that barrier is an atomic counter in global memory with a bounded, sleeping spin
-//     (the grid never exceeds the SM count and every CTA takes a whole SM, so all CTAs are
-//     resident; if the wait still expires the kernel records DEV_TIMEOUT, stops computing
-//     and walks out through its barriers).
+//   * that barrier is an atomic counter in global memory with a bounded, sleeping spin; a list
+//     that uses it is launched cooperatively, so the driver guarantees that all CTAs (one per SM)
+//     are resident together (if the wait still expires the kernel records DEV_TIMEOUT, stops
+//     computing and walks out through its barriers).
 #include "kernels.h"
 #include "matvec_core.cuh"
+#include "shard_dev.cuh"
 
 #include <algorithm>
 
@@ -44,6 +45,7 @@ struct ChainParams {
     unsigned *sync; // {arrival count, generation}: zero once, self-restoring
     int *status;
     uint32_t NW, S, stage_bytes, off_part, off_prep, off_ring, chunk;
+    ShardDev sh; // sh.world > 0: rows go to every rank's gather buffer and the launch publishes the exchange
 };
 
 __device__ __forceinline__ void chain_row_range(const ChainOpDev &o, uint32_t &rbeg, uint32_t &rend) {
@@ -141,8 +143,10 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
         if (gr >= rend || aborted) return;
         float acc = 0.f;
         for (uint32_t c = 0; c < o.WC; ++c) acc += pt[row * o.WC + c];
-        if (o.epi == EPI_STORE) o.y[gr] = acc;
-        else if (o.epi == EPI_RESIDUAL) o.y[gr] = __ldcg(o.res + gr) + acc;
+        if (o.epi == EPI_STORE) {
+            if (p.sh.world) shard_store_all(p.sh, o.y + gr, acc);
+            else o.y[gr] = acc;
+        } else if (o.epi == EPI_RESIDUAL) o.y[gr] = __ldcg(o.res + gr) + acc;
         else if ((lane & 1) == 0) {
             float up = 0.f;
             for (uint32_t c = 0; c < o.WC; ++c) up += pt[(row + 1) * o.WC + c];
@@ -182,8 +186,10 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
                 if (RW >= 2) other = __shfl_xor_sync(0xffffffffu, r, RW == 2 ? 16 : 8);
                 const bool writer = (lane & 7) == 0 && (RW == 4 || (lane & 8) == 0) && (RW > 1 || lane == 0);
                 if (writer && r0 + rl < rend && !aborted) {
-                    if (o.epi == EPI_STORE) o.y[r0 + rl] = r;
-                    else if (o.epi == EPI_RESIDUAL) o.y[r0 + rl] = __ldcg(o.res + r0 + rl) + r;
+                    if (o.epi == EPI_STORE) {
+                        if (p.sh.world) shard_store_all(p.sh, o.y + r0 + rl, r);
+                        else o.y[r0 + rl] = r;
+                    } else if (o.epi == EPI_RESIDUAL) o.y[r0 + rl] = __ldcg(o.res + r0 + rl) + r;
                     else if ((myrow & 1) == 0) o.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
                 }
             } else {
@@ -267,6 +273,10 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
         asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // prep / part areas are free for the next op
     }
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
+    // Sharded launch: the consumer threads have passed a barrier after their last store, so one
+    // thread orders the CTA's stores (system scope) and counts the CTA in; the last CTA publishes
+    // the exchange to every rank and waits, bounded, for theirs.
+    if (p.sh.world && tid == 0 && !shard_cta_done(p.sh, aborted)) *(volatile int *)p.status = DEV_TIMEOUT;
 }
 
 // ---------------------------------------------------------------------------
@@ -290,9 +300,15 @@ bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi) {
 }
 
 cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainOp *ops, unsigned *d_sync, int *d_status,
-                                cudaStream_t st, bool pdl) {
+                                cudaStream_t st, bool pdl, const ShardDev *shard) {
     if (n <= 0 || n > CHAIN_MAX_OPS) return cudaErrorInvalidValue;
     ChainParams p{};
+    if (shard) {
+        if (shard->world < 1 || shard->world > SHARD_MAX_RANKS) return cudaErrorInvalidValue;
+        for (int i = 0; i < n; ++i)
+            if (ops[i].epi != EPI_STORE) return cudaErrorNotSupported; // fused epilogues stay on one GPU
+        p.sh = *shard;
+    }
     p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 20, p.chunk = 4096;
     const int budget = dev.max_smem_optin - 1024;
     uint32_t max_stage = 0, max_part = 128, max_prep = 0;
@@ -354,10 +370,29 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid), cfg.blockDim = dim3((p.NW + 1) * 32), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    // A list with a dependent op meets at the grid-wide barrier, which needs every CTA resident at once: such a
+    // list is a cooperative launch (the driver refuses it when the grid does not fit beside what else is running,
+    // and the caller then runs the ops one by one).  Independent ops never wait for another CTA and may instead
+    // be launched programmatically dependent on the previous kernel.
+    bool any_dep = false;
+    for (int i = 0; i < n; ++i) any_dep = any_dep || ops[i].dep;
     cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
+    if (any_dep) {
+        at[0].id = cudaLaunchAttributeCooperative;
+        at[0].val.cooperative = 1;
+    } else {
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+    }
+    cfg.attrs = at, cfg.numAttrs = (any_dep || pdl) ? 1 : 0;
+    if (any_dep) {
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, matvec_chain_kernel, p);
+        if (e == cudaErrorCooperativeLaunchTooLarge) {
+            cudaGetLastError();
+            return cudaErrorNotSupported;
+        }
+        return e;
+    }
     return cudaLaunchKernelEx(&cfg, matvec_chain_kernel, p);
 }
 

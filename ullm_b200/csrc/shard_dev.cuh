@@ -1,0 +1,72 @@
+// Device side of the row-sharded output exchange: stores into every rank's gather buffer and the
+// publish / bounded-wait protocol on the ranks' control blocks (see ShardDev in kernels.h).
+#pragma once
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ullm {
+
+__device__ __forceinline__ unsigned long long shard_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned shard_ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void shard_st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// One value to the same place in every rank's gather buffer (`addr` is the place in this rank's).
+// Plain stores: the peers' buffers are mapped into this GPU's address space; nothing is read remotely.
+__device__ __forceinline__ void shard_store_all(const ShardDev &sh, float *addr, float v) {
+    for (int r = 0; r < sh.world; ++r) *(float *)((char *)addr + sh.delta[r]) = v;
+}
+
+// Waits until every rank has published exchange `step` (wrap-around safe); false when the time limit ran out.
+__device__ __forceinline__ bool shard_wait_all(const ShardDev &sh, unsigned step) {
+    const unsigned long long t0 = shard_now_ns();
+    for (int r = 0; r < sh.world; ++r) {
+        const unsigned *f = sh.ctl + r * SHARD_CTL_STRIDE;
+        for (;;) {
+            if ((int)(shard_ld_acquire_sys(f) - step) >= 0) break;
+            asm volatile("nanosleep.u32 32;" ::: "memory");
+            if (shard_now_ns() - t0 > sh.timeout_ns) return false;
+        }
+    }
+    return true;
+}
+
+// Called by ONE thread of the launch, after every store of the exchange is ordered before it (see
+// shard_cta_done): counts the exchange, tells every rank, and waits for theirs when asked to.
+// Returns false when the wait ran out of time.
+__device__ __forceinline__ bool shard_publish(const ShardDev &sh) {
+    unsigned *stepw = sh.ctl + SHARD_CTL_STEP;
+    const unsigned step = *(volatile unsigned *)stepw + 1u;
+    *(volatile unsigned *)stepw = step;
+    __threadfence_system();
+    for (int r = 0; r < sh.world; ++r) shard_st_release_sys(sh.peer_flag[r], step);
+    return sh.wait ? shard_wait_all(sh, step) : true;
+}
+
+// Called by one thread per CTA once the CTA's stores have been issued and a CTA-wide barrier has
+// passed.  The last CTA of the grid to arrive publishes.  `aborted`: this CTA gave up on a bounded
+// wait, its rows are missing, so the exchange must not be published.
+// Returns false only in the publishing thread, when its wait for the other ranks ran out of time.
+__device__ __forceinline__ bool shard_cta_done(const ShardDev &sh, bool aborted) {
+    unsigned *done = sh.ctl + SHARD_CTL_DONE, *abortw = sh.ctl + SHARD_CTL_ABORT;
+    if (aborted) atomicExch(abortw, 1u);
+    __threadfence_system(); // this CTA's stores into the peers' buffers are ordered before the arrival
+    if (atomicAdd(done, 1u) != gridDim.x * gridDim.y * gridDim.z - 1) return true;
+    __threadfence_system();
+    atomicExch(done, 0u);
+    const bool any_abort = atomicExch(abortw, 0u) != 0u;
+    if (any_abort || !sh.signal) return true;
+    return shard_publish(sh);
+}
+
+} // namespace ullm

@@ -1,13 +1,14 @@
-"""Row sharding of a quantized matrix over the ranks of one node.
+"""Row sharding of a quantized matrix over the ranks of one node: the index arithmetic.
 
 Output rows of ``y = W x`` are independent (the reference parallelises its CPU
 matvec over them, crates/ullm-model/src/math.rs:11-21), and a row of a GGUF /
 MLX matrix is a self-contained byte range, so rank ``r`` of ``N`` keeps rows
-``[r*out/N, (r+1)*out/N)`` and the path has one exchange: an all-gather of the
-ranks' output rows.  Several matrices that share a step are gathered together:
-each rank concatenates its rows of all of them, one all-gather produces the
-``[rank][matrix][rows]`` layout, and :func:`split_gathered` gives the per-matrix
-vectors back.
+``[r*out/N, (r+1)*out/N)`` and the path has one exchange: every rank's output
+rows must reach every rank.  The library does that inside its kernels
+(``ullm_cuda_shard_*``: each rank stores its rows into all ranks' full-length
+result vectors, laid out by :func:`vector_offsets`); the NCCL comparison arm
+all-gathers the ranks' concatenated rows instead, which produces the
+``[rank][matrix][rows]`` layout that :func:`split_gathered` undoes.
 """
 from __future__ import annotations
 
@@ -35,6 +36,22 @@ def slice_rows(dtype: int, w_bytes, out_dim: int, cols: int, world: int, rank: i
         raise ValueError("weight buffer shorter than out_dim rows")
     lo, hi = row_range(out_dim, world, rank)
     return b[lo * rb : hi * rb]
+
+
+def vector_offsets(out_dims, align: int = 64) -> list[int]:
+    """Where the full-length result vector of each matrix starts inside a rank's gather buffer (floats), every
+    vector on an ``align``-float boundary; the last entry is the total length.  Identical on all ranks."""
+    offs, o = [], 0
+    for d in out_dims:
+        offs.append(o)
+        o += -(-d // align) * align
+    return offs + [o]
+
+
+def step_region(step: int, total: int) -> int:
+    """Offset of the region of the gather buffer that step ``step`` fills: two regions, used by alternate steps,
+    because a rank may run one step ahead of a peer that is still reading the previous result."""
+    return (step & 1) * total
 
 
 def local_offsets(out_dims, world: int) -> list[int]:
