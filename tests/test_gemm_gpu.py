@@ -33,9 +33,10 @@ def expected(dtype, w, xs, out_dim, in_dim, s):
     return y_oracle, (xb @ wd.T)
 
 
-def check(got, y_oracle, y_path):
+def check(got, y_oracle, y_path, in_dim=2048):
     assert synth.rel_err(got, y_oracle) < TOL_BF16
-    assert synth.rel_err(got, y_path.astype(np.float32)) < TOL_PATH
+    # what the accumulation order leaves grows with the square root of the number of terms
+    assert synth.rel_err(got, y_path.astype(np.float32)) < TOL_PATH * max(1.0, (in_dim / 2048.0) ** 0.5)
 
 
 SHAPES = [
@@ -103,7 +104,7 @@ def test_c4_shapes_at_512_tokens_row_bands_match_oracle(ctx, dtype, out_dim, in_
     wb = np.asarray(w).reshape(-1).view(np.uint8)
     for r0 in (0, (out_dim // 2) // 64 * 64 + 64, out_dim - 64):
         blk = np.ascontiguousarray(wb[r0 * rb:(r0 + 64) * rb])
-        check(got[:, r0:r0 + 64].cpu().numpy(), *expected(dtype, blk, xs, 64, in_dim, s))
+        check(got[:, r0:r0 + 64].cpu().numpy(), *expected(dtype, blk, xs, 64, in_dim, s), in_dim=in_dim)
     wo.free()
 
 
