@@ -663,6 +663,49 @@ def cpu_leg(check, gpu_outputs):
             "sample": f"{n} full steps of c4_70b_layer_matvec, {cdt * 1e3:.1f} ms each"}
 
 
+def run_slice(args):
+    """Single-GPU diagnostic: what ONE rank of a `--slice-of W` group computes per step (rows / W of every matrix),
+    without any peer: the sharded entry point on a group of one (the kernel and its epilogue, no exchange), and the
+    same slices through the ordinary batch call.  The difference to the N = W line is what the exchange costs."""
+    import torch
+
+    from ullm_b200 import backend
+
+    W = args.slice_of
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    ctx = backend.CudaContext(0)
+    ctx.set_option(backend.OPT_PDL, 1 if args.pdl else 0)
+    outs = [o for _, _, o, _ in C4_MATS]
+    offs = shard.vector_offsets(outs)
+    total = offs[-1]
+    slice_bytes = sum(weight_bytes(dt, o // W, c) for _, dt, o, c in C4_MATS)
+    ncopies = max(1, -(-400_000_000 // slice_bytes))
+    sh = backend.Shard(ctx, 1, 0, 2 * total)
+    mats = []
+    for i, (name, dt, out, cols) in enumerate(C4_MATS):
+        rows = out // W
+        w = synth.gen_weight(dt, rows, cols, synth.seed_for(4, i))
+        mats.append(dict(rows=rows, cols=cols, x=torch.from_numpy(synth.normal(synth.seed_for(4, 8 + i), cols)).to(dev),
+                         y=torch.empty(rows, dtype=torch.float32, device=dev), ws=[backend.Weight(ctx, dt, w, rows, cols) for _ in range(ncopies)]))
+    ops = [[sh.ops([dict(w=m["ws"][c], x=m["x"].data_ptr(), y_offset=par * total + o, row0=0) for m, o in zip(mats, offs)]) for par in range(2)]
+           for c in range(ncopies)]
+    batches = [backend.WeightBatch(ctx, [m["ws"][c] for m in mats], [m["x"].data_ptr() for m in mats], [m["y"].data_ptr() for m in mats])
+               for c in range(ncopies)]
+    res = {"workload": f"one rank's share of c4 split {W} ways, on one GPU", "slice_mb": slice_bytes / 1e6, "copies": ncopies}
+    sp = spread(time_graph(torch, lambda i, st: sh.matvec_dev(ops[i % ncopies][i & 1], st), args.steps, args.warmup, args.replays), args.steps)
+    res["sharded_entry_us"] = sp["median"] * 1e3
+    for name, pc in (("batch_chain_us", 1), ("batch_separate_us", 0)):
+        ctx.debug_set("prefer_chain", pc)
+        ctx.debug_set("no_chain", 0 if pc else 1)
+        sp = spread(time_graph(torch, lambda i, st: batches[i % ncopies].launch(st), args.steps, args.warmup, args.replays), args.steps)
+        res[name] = sp["median"] * 1e3
+    ctx.synchronize()
+    res["gbs_sharded_entry"] = (slice_bytes + 4 * sum(m["rows"] + m["cols"] for m in mats)) / res["sharded_entry_us"] / 1e3
+    print(json.dumps(res), flush=True)
+    return 0
+
+
 def run_c4gemm_multi(args):
     """N > 1, --workload c4gemm: the block as a 512-token prefill GEMM, rows / N of every matrix per rank; the
     GEMM's epilogue stores each rank's [tokens, rows / N] block into its columns of [tokens, out] on every rank."""
@@ -752,10 +795,13 @@ def main():
                     help="N = 1: the library's choice, seven launches per step, or one persistent launch per step")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: fused peer stores (default) or the NCCL all-gather comparison arm")
     ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm"], help="N > 1 only: c4gemm runs the block as a sharded prefill GEMM")
+    ap.add_argument("--slice-of", type=int, default=0, help="N = 1 diagnostic: time one rank's share of a W-way split without peers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
+    if args.slice_of:
+        return run_slice(args)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1 and args.workload == "c4gemm":
         return run_c4gemm_multi(args)
     return run_c4(args)

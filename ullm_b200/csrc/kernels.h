@@ -64,7 +64,6 @@ constexpr int SHARD_MAX_RANKS = 8;
 constexpr int SHARD_CTL_STRIDE = 32;                 // unsigned words between control words: one 128-byte line each
 constexpr int SHARD_CTL_DONE = 8 * SHARD_CTL_STRIDE; // CTAs of the current launch that have stored all their rows
 constexpr int SHARD_CTL_STEP = 9 * SHARD_CTL_STRIDE; // number of exchanges this rank has published
-constexpr int SHARD_CTL_ABORT = 10 * SHARD_CTL_STRIDE;
 constexpr size_t SHARD_CTL_BYTES = 4096;             // control block in front of the gather buffer
 struct ShardDev {
     int world = 0;                          // 0: not a sharded launch

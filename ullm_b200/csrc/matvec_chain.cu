@@ -9,6 +9,11 @@
 //   * the producer warp of every CTA streams the tiles of op 0, op 1, ... back to back
 //     through one shared-memory ring — weights do not depend on activations, so the stream
 //     never stops at an op boundary;
+//   * ops that do not depend on each other are not walked by every CTA: the CTAs are dealt out to
+//     the ops in proportion to their bytes, so a CTA prepares the image of one activation vector
+//     and streams one matrix' rows for the whole launch (an op's input vector has to be read and
+//     converted by every CTA that touches the op, whatever its share of the rows, which is what a
+//     launch over many small row slices otherwise spends its time on);
 //   * the consumer warps do, per op, what matvec_stream_kernel does (matvec.cu): fixed-point
 //     image of x in registers, dp4a row sums, optional RMSNorm prologue and residual / SwiGLU
 //     epilogue — and wait at a grid-wide barrier only where an op reads what an earlier op
@@ -38,6 +43,7 @@ struct ChainOpDev {
     int dep;             // x / res come from an earlier op of this launch: grid barrier first
     uint32_t out_dim, in_dim, row_bytes, gran, ncg;
     uint32_t R, WC, WR, rw, g; // tile rows, column-group warps, row-slice warps, rows per warp, groups per warp
+    uint32_t cta0, ncta;       // the CTAs [cta0, cta0 + ncta) share this op's rows; the others skip it
 };
 struct ChainParams {
     ChainOpDev op[CHAIN_MAX_OPS];
@@ -49,9 +55,14 @@ struct ChainParams {
 };
 
 __device__ __forceinline__ void chain_row_range(const ChainOpDev &o, uint32_t &rbeg, uint32_t &rend) {
+    const uint32_t b = blockIdx.x - o.cta0; // wraps to a large value for CTAs in front of the op's group
+    if (b >= o.ncta) {
+        rbeg = rend = 0;
+        return;
+    }
     const uint32_t units = o.out_dim / o.gran;
-    rbeg = (uint32_t)(((uint64_t)units * blockIdx.x) / gridDim.x) * o.gran;
-    rend = blockIdx.x + 1 == gridDim.x ? o.out_dim : (uint32_t)(((uint64_t)units * (blockIdx.x + 1)) / gridDim.x) * o.gran;
+    rbeg = (uint32_t)(((uint64_t)units * b) / o.ncta) * o.gran;
+    rend = b + 1 == o.ncta ? o.out_dim : (uint32_t)(((uint64_t)units * (b + 1)) / o.ncta) * o.gran;
 }
 
 // Grid-wide barrier of the consumer threads.  sync[0] counts arrivals, sync[1] is the generation:
@@ -262,13 +273,14 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
     for (int i = 0; i < p.n_ops; ++i) {
         const ChainOpDev &o = p.op[i];
         if (o.dep && !chain_grid_sync(p.sync, nthr_c, tid, &sync_ok)) aborted = true;
+        uint32_t rbeg, rend;
+        chain_row_range(o, rbeg, rend);
+        if (rbeg == rend) continue; // no rows of this op here (another group of CTAs has them): no image of its x either
 #define ULLM_CHAIN_CASE(F, RWv, Gv) \
     if (o.fmt == F && o.rw == RWv && o.g == Gv) chain_consume<F, RWv, Gv>(o, p, smem, kbase, tid, aborted);
         ULLM_CHAIN_CASE(FMT_Q4K, 1, 1) ULLM_CHAIN_CASE(FMT_Q4K, 2, 1) ULLM_CHAIN_CASE(FMT_Q4K, 4, 1)
         ULLM_CHAIN_CASE(FMT_Q6KR, 1, 1) ULLM_CHAIN_CASE(FMT_Q6KR, 2, 1) ULLM_CHAIN_CASE(FMT_Q6KR, 4, 1)
 #undef ULLM_CHAIN_CASE
-        uint32_t rbeg, rend;
-        chain_row_range(o, rbeg, rend);
         kbase += (rend - rbeg + o.R - 1) / o.R;
         asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // prep / part areas are free for the next op
     }
@@ -313,6 +325,47 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     const int budget = dev.max_smem_optin - 1024;
     uint32_t max_stage = 0, max_part = 128, max_prep = 0;
     const uint32_t grid = (uint32_t)dev.sm_count;
+    // Independent ops: the CTAs are dealt out to the ops in proportion to their weight bytes (largest
+    // remainders first, at least one CTA each, never more CTAs than the op has row units).
+    uint32_t cta0[CHAIN_MAX_OPS], ncta[CHAIN_MAX_OPS];
+    bool dealt = n > 1 && (uint32_t)n <= grid;
+    for (int i = 0; i < n; ++i) dealt = dealt && !ops[i].dep;
+    if (dealt) {
+        double cost[CHAIN_MAX_OPS], total = 0, frac[CHAIN_MAX_OPS];
+        for (int i = 0; i < n; ++i) {
+            const double rb = (double)(ops[i].in_dim / QK_K) * (ops[i].fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+            // the fixed part stands for reading and converting the op's input vector, which every CTA of the op does
+            cost[i] = (double)ops[i].out_dim * rb + 3.0 * (double)ops[i].in_dim * 4.0;
+            total += cost[i];
+        }
+        uint32_t used = 0;
+        for (int i = 0; i < n; ++i) {
+            const double share = cost[i] / total * grid;
+            ncta[i] = std::max<uint32_t>(1, (uint32_t)share);
+            frac[i] = share - (double)(uint32_t)share;
+            used += ncta[i];
+        }
+        while (used < grid) { // hand the remaining CTAs to the largest remainders
+            int best = 0;
+            for (int i = 1; i < n; ++i)
+                if (frac[i] > frac[best]) best = i;
+            ++ncta[best], frac[best] = -1.0, ++used;
+            bool any = false;
+            for (int i = 0; i < n; ++i) any = any || frac[i] >= 0.0;
+            if (!any)
+                for (int i = 0; i < n; ++i) frac[i] = cost[i] / total;
+        }
+        while (used > grid) { // the minimum of one CTA per op overshot: take from the largest groups
+            int best = 0;
+            for (int i = 1; i < n; ++i)
+                if (ncta[i] > ncta[best]) best = i;
+            --ncta[best], --used;
+        }
+        uint32_t at = 0;
+        for (int i = 0; i < n; ++i) cta0[i] = at, at += ncta[i];
+    } else {
+        for (int i = 0; i < n; ++i) cta0[i] = 0, ncta[i] = grid;
+    }
     // tiles of up to 100 KB (four rows per warp on wide matrices) when ring, partials and activation images then
     // still fit; else the plan is redone with tiles of up to 56 KB
     for (uint32_t tile_cap : {100u * 1024u, 56u * 1024u}) {
@@ -334,7 +387,8 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         o.WR = p.NW / o.WC;
         // rows per warp: the largest of 4, 2, 1 whose tile stays within 56 KB, unless a tile of
         // half the rows already covers this CTA's whole share (then the rest would be padding)
-        const uint32_t rows_cta = (o.out_dim / o.gran + grid - 1) / grid * o.gran;
+        o.cta0 = cta0[i], o.ncta = std::min<uint32_t>(ncta[i], std::max<uint32_t>(1, o.out_dim / o.gran));
+        const uint32_t rows_cta = (o.out_dim / o.gran + o.ncta - 1) / o.ncta * o.gran;
         const uint32_t rw_min = h.epi == EPI_SWIGLU ? 2u : 1u;
         o.rw = 0;
         for (uint32_t rw = 4; rw >= rw_min; rw /= 2) {

@@ -30,10 +30,7 @@ namespace ullm {
 
 __global__ void shard_signal_kernel(const ShardDev sh, int *status) {
     pdl_wait_prior();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        if (!shard_publish(sh)) *(volatile int *)status = DEV_TIMEOUT;
-    }
+    if (threadIdx.x == 0 && !shard_publish(sh)) *(volatile int *)status = DEV_TIMEOUT;
 }
 
 __global__ void shard_wait_kernel(const ShardDev sh, int *status) {

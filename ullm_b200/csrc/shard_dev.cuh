@@ -41,31 +41,33 @@ __device__ __forceinline__ bool shard_wait_all(const ShardDev &sh, unsigned step
     return true;
 }
 
-// Called by ONE thread of the launch, after every store of the exchange is ordered before it (see
+// Called by ONE thread of the launch, once every store of the exchange happens-before it (see
 // shard_cta_done): counts the exchange, tells every rank, and waits for theirs when asked to.
 // Returns false when the wait ran out of time.
 __device__ __forceinline__ bool shard_publish(const ShardDev &sh) {
-    unsigned *stepw = sh.ctl + SHARD_CTL_STEP;
-    const unsigned step = *(volatile unsigned *)stepw + 1u;
-    *(volatile unsigned *)stepw = step;
+    // System-scope fence: the other CTAs' stores into the peers' buffers were ordered before their
+    // arrival (gpu scope), this thread has observed every arrival, and fences are cumulative - so all
+    // of those stores are ordered before the release stores below, as seen from the other GPUs.
     __threadfence_system();
+    unsigned *stepw = sh.ctl + SHARD_CTL_STEP;
+    const unsigned step = *(volatile unsigned *)stepw + 1u; // touched by one thread per launch; launches are stream-ordered
+    *(volatile unsigned *)stepw = step;
     for (int r = 0; r < sh.world; ++r) shard_st_release_sys(sh.peer_flag[r], step);
     return sh.wait ? shard_wait_all(sh, step) : true;
 }
 
 // Called by one thread per CTA once the CTA's stores have been issued and a CTA-wide barrier has
 // passed.  The last CTA of the grid to arrive publishes.  `aborted`: this CTA gave up on a bounded
-// wait, its rows are missing, so the exchange must not be published.
+// wait, its rows are missing, so the exchange must not be published.  One atomic per CTA: the low
+// 16 bits of the word count arrivals, the high bits count aborted CTAs.
 // Returns false only in the publishing thread, when its wait for the other ranks ran out of time.
 __device__ __forceinline__ bool shard_cta_done(const ShardDev &sh, bool aborted) {
-    unsigned *done = sh.ctl + SHARD_CTL_DONE, *abortw = sh.ctl + SHARD_CTL_ABORT;
-    if (aborted) atomicExch(abortw, 1u);
-    __threadfence_system(); // this CTA's stores into the peers' buffers are ordered before the arrival
-    if (atomicAdd(done, 1u) != gridDim.x * gridDim.y * gridDim.z - 1) return true;
-    __threadfence_system();
-    atomicExch(done, 0u);
-    const bool any_abort = atomicExch(abortw, 0u) != 0u;
-    if (any_abort || !sh.signal) return true;
+    unsigned *done = sh.ctl + SHARD_CTL_DONE;
+    __threadfence(); // this CTA's stores (the barrier made them this thread's business) before its arrival
+    const unsigned old = atomicAdd(done, aborted ? 0x10001u : 1u);
+    if ((old & 0xffffu) != gridDim.x * gridDim.y * gridDim.z - 1) return true;
+    *(volatile unsigned *)done = 0u; // for the next launch, which the stream orders after this one
+    if ((old >> 16) != 0u || aborted || !sh.signal) return true;
     return shard_publish(sh);
 }
 
