@@ -445,14 +445,13 @@ def run_c4(args):
             m["x"] = torch.from_numpy(m["xh"]).to(dev)
             m["y"] = torch.empty(m["out"], dtype=torch.float32, device=dev)
         batch = backend.WeightBatch(ctx, [m["w"] for m in mats], [m["x"].data_ptr() for m in mats], [m["y"].data_ptr() for m in mats])
-        ctx.debug_set("prefer_chain", 1 if args.launch == "chain" else 0)
 
         def step(_i, st):
             if args.launch == "separate":
                 for m in mats:
                     m["w"].matvec_dev(m["x"].data_ptr(), m["y"].data_ptr(), st)
             else:
-                batch.launch(st)  # the library picks: one persistent launch, or one launch per matrix
+                batch.launch(st)  # one persistent launch: the CTAs are dealt out to the seven matrices
 
         sampler = ClockSampler(local)
         sampler.start()
@@ -528,7 +527,6 @@ def run_c4(args):
             loff = shard.local_offsets(outs, world)
             batches = [backend.WeightBatch(ctx, [m["ws"][c] for m in mats], [m["x"].data_ptr() for m in mats],
                                            [y_cat.data_ptr() + 4 * o for o in loff[:-1]]) for c in range(ncopies)]
-            ctx.debug_set("prefer_chain", 1)
             launches_per_step = 2
 
         def step(i, st):
@@ -696,10 +694,21 @@ def run_slice(args):
     sp = spread(time_graph(torch, lambda i, st: sh.matvec_dev(ops[i % ncopies][i & 1], st), args.steps, args.warmup, args.replays), args.steps)
     res["sharded_entry_us"] = sp["median"] * 1e3
     for name, pc in (("batch_chain_us", 1), ("batch_separate_us", 0)):
-        ctx.debug_set("prefer_chain", pc)
         ctx.debug_set("no_chain", 0 if pc else 1)
         sp = spread(time_graph(torch, lambda i, st: batches[i % ncopies].launch(st), args.steps, args.warmup, args.replays), args.steps)
         res[name] = sp["median"] * 1e3
+    # every matrix alone (its own launches, copies walked round-robin)
+    ctx.debug_set("no_chain", 0)
+    per = {}
+    for (name, dt, out, cols), m in zip(C4_MATS, mats):
+        sp = spread(time_graph(torch, lambda i, st: m["ws"][i % ncopies].matvec_dev(m["x"].data_ptr(), m["y"].data_ptr(), st), args.steps, args.warmup, 5), args.steps)
+        nb = weight_bytes(dt, m["rows"], cols)
+        per[name] = {"us": round(sp["median"] * 1e3, 2), "gbs": round(nb / sp["median"] / 1e6, 1)}
+    res["per_matrix_alone"] = per
+    if args.q6k_cost:
+        ctx.debug_set("q6k_cost_permille", args.q6k_cost)
+        sp = spread(time_graph(torch, lambda i, st: batches[i % ncopies].launch(st), args.steps, args.warmup, args.replays), args.steps)
+        res[f"batch_chain_us_q6k_cost_{args.q6k_cost}"] = sp["median"] * 1e3
     ctx.synchronize()
     res["gbs_sharded_entry"] = (slice_bytes + 4 * sum(m["rows"] + m["cols"] for m in mats)) / res["sharded_entry_us"] / 1e3
     print(json.dumps(res), flush=True)
@@ -791,10 +800,11 @@ def main():
     ap.add_argument("--pdl", type=int, default=1, help="ULLM_OPT_PDL: launch kernels programmatically dependent on their predecessor")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-secondary", action="store_true", help="N = 1: skip the other configurations")
-    ap.add_argument("--launch", default="auto", choices=["auto", "separate", "chain"],
-                    help="N = 1: the library's choice, seven launches per step, or one persistent launch per step")
+    ap.add_argument("--launch", default="auto", choices=["auto", "separate"],
+                    help="N = 1: the batch call (one persistent launch for the seven matrices) or seven launches per step")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: fused peer stores (default) or the NCCL all-gather comparison arm")
     ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm"], help="N > 1 only: c4gemm runs the block as a sharded prefill GEMM")
+    ap.add_argument("--q6k-cost", type=int, default=0, help="--slice-of diagnostic: also time the persistent launch with this per-byte cost (permille) of Q6_K rows")
     ap.add_argument("--slice-of", type=int, default=0, help="N = 1 diagnostic: time one rank's share of a W-way split without peers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

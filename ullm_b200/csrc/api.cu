@@ -418,15 +418,6 @@ int ullm_cuda_weight_matvec_chain_dev(ullm_cuda_ctx *c, size_t n, const ullm_cha
         m.norm_w = o.d_norm_w, m.eps = o.eps, m.epi = o.epi, m.res = o.d_res, m.dep = o.dep != 0;
         chain_ok = chain_ok && matvec_chain_supported(m.fmt, m.out_dim, m.in_dim, m.epi);
     }
-    // Independent ops on large matrices run faster as separate programmatically chained launches (each with the
-    // tile plan that suits its shape) than through one ring sized for the largest of them; the persistent launch
-    // pays off where the per-launch fixed cost matters: small matrices, or ops that depend on each other.
-    if (chain_ok && c->use_pdl && !c->prefer_chain) {
-        bool any_dep = false;
-        size_t bytes = 0;
-        for (size_t i = 0; i < n; ++i) any_dep = any_dep || v[i].dep, bytes += ops[i].w->nbytes;
-        if (!any_dep && bytes / n >= ((size_t)48 << 20)) chain_ok = false;
-    }
     // one persistent launch per run of at most 12 ops; anything it cannot take goes op by op
     if (chain_ok) {
         unsigned *d_sync = nullptr;
@@ -497,6 +488,31 @@ __global__ void __launch_bounds__(256) host_vec_copy_kernel(const float *__restr
         for (size_t j = i; j < n && j < i + 4; ++j) dst[j] = src[j];
     }
 }
+// Several vectors in one launch: segment i is n[i] floats from src[i] to dst[i]; blockIdx.y picks the segment.
+constexpr int VEC_COPY_MAX = 16;
+struct VecCopyList {
+    const float *src[VEC_COPY_MAX];
+    float *dst[VEC_COPY_MAX];
+    unsigned n[VEC_COPY_MAX];
+};
+__global__ void __launch_bounds__(256) host_vec_copy_multi_kernel(const __grid_constant__ VecCopyList l) {
+    const float *src = l.src[blockIdx.y];
+    float *dst = l.dst[blockIdx.y];
+    const size_t n = l.n[blockIdx.y];
+    const bool vec = ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+        if (vec && i + 3 < n) *(float4 *)(dst + i) = *(const float4 *)(src + i);
+        else
+            for (size_t j = i; j < n && j < i + 4; ++j) dst[j] = src[j];
+    }
+}
+static cudaError_t vec_copy_multi(const VecCopyList &l, int count, cudaStream_t st) {
+    unsigned most = 0;
+    for (int i = 0; i < count; ++i) most = std::max(most, l.n[i]);
+    const unsigned gx = std::max(1u, std::min(32u, (most + 1023) / 1024));
+    host_vec_copy_multi_kernel<<<dim3(gx, (unsigned)count), 256, 0, st>>>(l);
+    return cudaGetLastError();
+}
 static const float *device_view_of_host(const void *p) {
     cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
@@ -541,21 +557,39 @@ int ullm_cuda_weight_matvec_batch(ullm_cuda_ctx *c, size_t n, const ullm_cuda_we
     int rc;
     if ((rc = ctx_scratch(c, 4, xin * 4, &d_x)) || (rc = ctx_scratch(c, 5, yout * 4, &d_y))) return rc;
     std::vector<ullm_chain_op> ops(n);
+    std::vector<const float *> xv(n);
+    std::vector<float *> yv(n);
     size_t xo = 0, yo = 0;
+    bool all_mapped = !c->no_host_kernels;
     for (size_t i = 0; i < n; ++i) {
-        float *dx = (float *)d_x + xo, *dy = (float *)d_y + yo;
-        const float *xv = c->no_host_kernels ? nullptr : device_view_of_host(x[i]);
-        if (xv) ULLM_CUDA_TRY(c, vec_copy(xv, dx, w[i]->cols, c->stream));
-        else ULLM_CUDA_TRY(c, cudaMemcpyAsync(dx, x[i], w[i]->cols * 4, cudaMemcpyHostToDevice, c->stream));
         ops[i] = ullm_chain_op{};
-        ops[i].w = w[i], ops[i].d_x = dx, ops[i].d_y = dy;
+        ops[i].w = w[i], ops[i].d_x = (float *)d_x + xo, ops[i].d_y = (float *)d_y + yo;
         xo += (w[i]->cols + 3) & ~(size_t)3, yo += (w[i]->out + 3) & ~(size_t)3;
+        xv[i] = all_mapped ? device_view_of_host(x[i]) : nullptr;
+        yv[i] = all_mapped ? (float *)device_view_of_host(y[i]) : nullptr;
+        all_mapped = all_mapped && xv[i] && yv[i] && w[i]->cols <= 0xffffffffull && w[i]->out <= 0xffffffffull;
+    }
+    // page-locked vectors move in one small kernel per direction (up to 16 vectors each); pageable ones by the copy engines
+    if (all_mapped) {
+        for (size_t i = 0; i < n; i += VEC_COPY_MAX) {
+            VecCopyList l{};
+            const int m = (int)std::min<size_t>(VEC_COPY_MAX, n - i);
+            for (int k = 0; k < m; ++k) l.src[k] = xv[i + k], l.dst[k] = (float *)ops[i + k].d_x, l.n[k] = (unsigned)w[i + k]->cols;
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream));
+        }
+    } else {
+        for (size_t i = 0; i < n; ++i) ULLM_CUDA_TRY(c, cudaMemcpyAsync((void *)ops[i].d_x, x[i], w[i]->cols * 4, cudaMemcpyHostToDevice, c->stream));
     }
     if ((rc = ullm_cuda_weight_matvec_chain_dev(c, n, ops.data(), nullptr))) return rc;
-    for (size_t i = 0; i < n; ++i) {
-        float *yv = c->no_host_kernels ? nullptr : (float *)device_view_of_host(y[i]);
-        if (yv) ULLM_CUDA_TRY(c, vec_copy(ops[i].d_y, yv, w[i]->out, c->stream));
-        else ULLM_CUDA_TRY(c, cudaMemcpyAsync(y[i], ops[i].d_y, w[i]->out * 4, cudaMemcpyDeviceToHost, c->stream));
+    if (all_mapped) {
+        for (size_t i = 0; i < n; i += VEC_COPY_MAX) {
+            VecCopyList l{};
+            const int m = (int)std::min<size_t>(VEC_COPY_MAX, n - i);
+            for (int k = 0; k < m; ++k) l.src[k] = ops[i + k].d_y, l.dst[k] = yv[i + k], l.n[k] = (unsigned)w[i + k]->out;
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream));
+        }
+    } else {
+        for (size_t i = 0; i < n; ++i) ULLM_CUDA_TRY(c, cudaMemcpyAsync(y[i], ops[i].d_y, w[i]->out * 4, cudaMemcpyDeviceToHost, c->stream));
     }
     ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     return ctx_check_status(c);
@@ -716,7 +750,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     else if (!strcmp(key, "no_prepare")) c->no_prepare = value != 0;
     else if (!strcmp(key, "gemm_min_s")) c->gemm_min_s = value;
     else if (!strcmp(key, "no_chain")) c->no_chain = value != 0;
-    else if (!strcmp(key, "prefer_chain")) c->prefer_chain = value != 0;
+    else if (!strcmp(key, "q6k_cost_permille")) matvec_chain_set_q6k_cost(value / 1000.0);
     else if (!strcmp(key, "no_host_kernels")) c->no_host_kernels = value != 0;
     else if (!strcmp(key, "plan_wr")) c->plan_wr = value;
     else if (!strcmp(key, "plan_rw")) c->plan_rw = value;

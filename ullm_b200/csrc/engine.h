@@ -31,7 +31,6 @@ struct ullm_cuda_ctx {
     bool use_pdl = true;  // programmatic dependent launch between the library's kernels (ULLM_OPT_PDL)
     bool no_prepare = false; // keep Q6_K weights in their verbatim bytes (tests)
     bool no_chain = false;   // run op lists one kernel per op (tests, comparisons)
-    bool prefer_chain = false; // always take the persistent launch when the ops allow it (comparisons)
     bool no_host_kernels = false; // host vectors always through cudaMemcpyAsync (comparisons)
     unsigned *d_sync = nullptr; // grid-barrier counter of the chain kernel
     int plan_wr = 0, plan_rw = 0, plan_stages = 0;

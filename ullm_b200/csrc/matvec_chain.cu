@@ -31,6 +31,9 @@
 namespace ullm {
 
 constexpr int CHAIN_MAX_OPS = 12;
+constexpr int CHAIN_MAX_STAGES = 8;
+static double g_q6k_cost = 1.3; // relative cost per byte of prepared Q6_K rows when CTAs are dealt out to ops
+void matvec_chain_set_q6k_cost(double v) { g_q6k_cost = v; }
 
 struct ChainOpDev {
     const uint8_t *w;
@@ -44,13 +47,16 @@ struct ChainOpDev {
     uint32_t out_dim, in_dim, row_bytes, gran, ncg;
     uint32_t R, WC, WR, rw, g; // tile rows, column-group warps, row-slice warps, rows per warp, groups per warp
     uint32_t cta0, ncta;       // the CTAs [cta0, cta0 + ncta) share this op's rows; the others skip it
+    // shared-memory layout while this op runs: the same for every op when all CTAs walk the whole list (the ring
+    // then runs on across ops), the op's own when the CTAs are dealt out (a CTA then sees one op only)
+    uint32_t S, stage_bytes, off_part, off_prep, off_ring;
 };
 struct ChainParams {
     ChainOpDev op[CHAIN_MAX_OPS];
     int n_ops;
     unsigned *sync; // {arrival count, generation}: zero once, self-restoring
     int *status;
-    uint32_t NW, S, stage_bytes, off_part, off_prep, off_ring, chunk;
+    uint32_t NW, chunk;
     ShardDev sh; // sh.world > 0: rows go to every rank's gather buffer and the launch publishes the exchange
 };
 
@@ -105,10 +111,10 @@ template <int FMT, int RW, int G>
 __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainParams &p, uint8_t *smem, uint32_t kbase,
                                               uint32_t tid, bool &aborted) {
     constexpr int XR = FmtTraits<FMT>::XREGS;
-    uint64_t *full = (uint64_t *)smem, *empty = full + p.S;
-    float *part = (float *)(smem + p.off_part);
-    uint32_t *prep = (uint32_t *)(smem + p.off_prep);
-    uint8_t *ring = smem + p.off_ring;
+    uint64_t *full = (uint64_t *)smem, *empty = full + CHAIN_MAX_STAGES;
+    float *part = (float *)(smem + o.off_part);
+    uint32_t *prep = (uint32_t *)(smem + o.off_prep);
+    uint8_t *ring = smem + o.off_ring;
     const uint32_t warp = tid >> 5, lane = tid & 31, nthr_c = p.NW * 32;
     uint32_t rbeg, rend;
     chain_row_range(o, rbeg, rend);
@@ -154,10 +160,8 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
         if (gr >= rend || aborted) return;
         float acc = 0.f;
         for (uint32_t c = 0; c < o.WC; ++c) acc += pt[row * o.WC + c];
-        if (o.epi == EPI_STORE) {
-            if (p.sh.world) shard_store_all(p.sh, o.y + gr, acc);
-            else o.y[gr] = acc;
-        } else if (o.epi == EPI_RESIDUAL) o.y[gr] = __ldcg(o.res + gr) + acc;
+        if (o.epi == EPI_STORE) o.y[gr] = acc;
+        else if (o.epi == EPI_RESIDUAL) o.y[gr] = __ldcg(o.res + gr) + acc;
         else if ((lane & 1) == 0) {
             float up = 0.f;
             for (uint32_t c = 0; c < o.WC; ++c) up += pt[(row + 1) * o.WC + c];
@@ -166,14 +170,14 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
     };
     // ring stage and mbarrier phase of the op's first tile (the ring runs on across ops), then carried along;
     // slot = k mod 2S for the partial areas, which are the op's own
-    uint32_t s = kbase % p.S, ph = (kbase / p.S) & 1u, slot = 0;
-    for (uint32_t k = 0; k < ntiles; ++k, slot = slot + 1 == 2 * p.S ? 0 : slot + 1) {
+    uint32_t s = kbase % o.S, ph = (kbase / o.S) & 1u, slot = 0;
+    for (uint32_t k = 0; k < ntiles; ++k, slot = slot + 1 == 2 * o.S ? 0 : slot + 1) {
         if (k) {
-            if (++s == p.S) s = 0, ph ^= 1u;
+            if (++s == o.S) s = 0, ph ^= 1u;
         }
         if (!aborted && !wait_or_timeout(&full[s], ph)) aborted = true;
-        if (o.WC > 1 && k >= p.S) flush(k - p.S, slot >= p.S ? slot - p.S : slot + p.S);
-        const uint32_t stage = smem_u32(ring + (size_t)s * p.stage_bytes);
+        if (o.WC > 1 && k >= o.S) flush(k - o.S, slot >= o.S ? slot - o.S : slot + o.S);
+        const uint32_t stage = smem_u32(ring + (size_t)s * o.stage_bytes);
         const uint32_t r0 = rbeg + k * o.R;
         if (active) {
             float v[RW];
@@ -197,10 +201,8 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
                 if (RW >= 2) other = __shfl_xor_sync(0xffffffffu, r, RW == 2 ? 16 : 8);
                 const bool writer = (lane & 7) == 0 && (RW == 4 || (lane & 8) == 0) && (RW > 1 || lane == 0);
                 if (writer && r0 + rl < rend && !aborted) {
-                    if (o.epi == EPI_STORE) {
-                        if (p.sh.world) shard_store_all(p.sh, o.y + r0 + rl, r);
-                        else o.y[r0 + rl] = r;
-                    } else if (o.epi == EPI_RESIDUAL) o.y[r0 + rl] = __ldcg(o.res + r0 + rl) + r;
+                    if (o.epi == EPI_STORE) o.y[r0 + rl] = r;
+                    else if (o.epi == EPI_RESIDUAL) o.y[r0 + rl] = __ldcg(o.res + r0 + rl) + r;
                     else if ((myrow & 1) == 0) o.y[(r0 + rl) >> 1] = r / (1.0f + expf(-r)) * other;
                 }
             } else {
@@ -213,7 +215,7 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
     }
     if (o.WC > 1) {
         asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // all partials of the last tiles are in
-        for (uint32_t kt = ntiles > p.S ? ntiles - p.S : 0; kt < ntiles; ++kt) flush(kt, kt % (2 * p.S));
+        for (uint32_t kt = ntiles > o.S ? ntiles - o.S : 0; kt < ntiles; ++kt) flush(kt, kt % (2 * o.S));
     }
 }
 
@@ -221,13 +223,13 @@ constexpr int CHAIN_MAX_THREADS = 21 * 32; // 20 consumer warps + the producer w
 
 __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(const __grid_constant__ ChainParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *full = (uint64_t *)smem, *empty = full + p.S;
+    uint64_t *full = (uint64_t *)smem, *empty = full + CHAIN_MAX_STAGES;
     int &sync_ok = *(int *)(smem + 128); // after the 2 x 8 mbarriers; static shared memory would eat into the opt-in maximum
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool producer = warp == p.NW;
     pdl_launch_dependents();
     if (tid == 0) {
-        for (uint32_t s = 0; s < p.S; ++s) {
+        for (uint32_t s = 0; s < CHAIN_MAX_STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], p.NW);
         }
@@ -238,23 +240,23 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
 
     if (producer) {
         // the weight tiles of every op, back to back: one tile = one contiguous byte range
-        uint8_t *ring = smem + p.off_ring;
         uint32_t kg = 0, s = 0, ph = 0; // tile count, ring stage and phase of the stage's current use, carried along
         for (int i = 0; i < p.n_ops; ++i) {
             const ChainOpDev &o = p.op[i];
+            uint8_t *ring = smem + o.off_ring;
             uint32_t rbeg, rend;
             chain_row_range(o, rbeg, rend);
             const uint32_t ntiles = (rend - rbeg + o.R - 1) / o.R;
-            for (uint32_t k = 0; k < ntiles; ++k, ++kg, s = s + 1 == p.S ? 0 : s + 1, ph ^= (s == 0)) {
+            for (uint32_t k = 0; k < ntiles; ++k, ++kg, s = s + 1 == o.S ? 0 : s + 1, ph ^= (s == 0)) {
                 bool ok = true;
-                if (lane == 0 && kg >= p.S) ok = wait_or_timeout(&empty[s], ph ^ 1u);
+                if (lane == 0 && kg >= o.S) ok = wait_or_timeout(&empty[s], ph ^ 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     if (lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
                     return;
                 }
                 const uint32_t r0 = rbeg + k * o.R, rows = min(o.R, rend - r0), wb = rows * o.row_bytes;
-                uint8_t *dst = ring + (size_t)s * p.stage_bytes;
+                uint8_t *dst = ring + (size_t)s * o.stage_bytes;
                 if (lane == 0) mbar_arrive_expect_tx(&full[s], wb);
                 __syncwarp();
                 const uint8_t *src = o.w + (size_t)r0 * o.row_bytes;
@@ -283,12 +285,24 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
 #undef ULLM_CHAIN_CASE
         kbase += (rend - rbeg + o.R - 1) / o.R;
         asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // prep / part areas are free for the next op
+        // Sharded launch: this CTA's rows of the op, just written to this rank's result vector, go to the same
+        // place in every other rank's (the barrier above makes them visible to all threads of the CTA; they are
+        // read back past the L1 and sent as plain stores through the peer mappings, a warp's worth contiguous).
+        if (p.sh.world > 1 && !aborted) {
+            for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
+                const float v = __ldcg(o.y + e);
+                for (int r = 0; r < p.sh.world; ++r)
+                    if (r != p.sh.rank) *(float *)((char *)(o.y + e) + p.sh.delta[r]) = v;
+            }
+        }
     }
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
-    // Sharded launch: the consumer threads have passed a barrier after their last store, so one
-    // thread orders the CTA's stores (system scope) and counts the CTA in; the last CTA publishes
-    // the exchange to every rank and waits, bounded, for theirs.
-    if (p.sh.world && tid == 0 && !shard_cta_done(p.sh, aborted)) *(volatile int *)p.status = DEV_TIMEOUT;
+    // Sharded launch: once every consumer thread has issued its stores to the peers, one thread orders them
+    // and counts the CTA in; the last CTA publishes the exchange to every rank and waits, bounded, for theirs.
+    if (p.sh.world) {
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+        if (tid == 0 && !shard_cta_done(p.sh, aborted)) *(volatile int *)p.status = DEV_TIMEOUT;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -323,7 +337,6 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     }
     p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 20, p.chunk = 4096;
     const int budget = dev.max_smem_optin - 1024;
-    uint32_t max_stage = 0, max_part = 128, max_prep = 0;
     const uint32_t grid = (uint32_t)dev.sm_count;
     // Independent ops: the CTAs are dealt out to the ops in proportion to their weight bytes (largest
     // remainders first, at least one CTA each, never more CTAs than the op has row units).
@@ -335,7 +348,8 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         for (int i = 0; i < n; ++i) {
             const double rb = (double)(ops[i].in_dim / QK_K) * (ops[i].fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
             // the fixed part stands for reading and converting the op's input vector, which every CTA of the op does
-            cost[i] = (double)ops[i].out_dim * rb + 3.0 * (double)ops[i].in_dim * 4.0;
+            // (prepared Q6_K rows cost more instructions per byte than Q4_K rows: measured rates on B200)
+            cost[i] = (double)ops[i].out_dim * rb * (ops[i].fmt == FMT_Q4K ? 1.0 : g_q6k_cost) + 3.0 * (double)ops[i].in_dim * 4.0;
             total += cost[i];
         }
         uint32_t used = 0;
@@ -366,10 +380,6 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     } else {
         for (int i = 0; i < n; ++i) cta0[i] = 0, ncta[i] = grid;
     }
-    // tiles of up to 100 KB (four rows per warp on wide matrices) when ring, partials and activation images then
-    // still fit; else the plan is redone with tiles of up to 56 KB
-    for (uint32_t tile_cap : {100u * 1024u, 56u * 1024u}) {
-    max_stage = 0, max_part = 128, max_prep = 0;
     for (int i = 0; i < n; ++i) {
         const MatvecChainOp &h = ops[i];
         if (!matvec_chain_supported(h.fmt, h.out_dim, h.in_dim, h.epi)) return cudaErrorNotSupported;
@@ -385,11 +395,13 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         o.g = (o.ncg + 15) / 16;
         o.WC = (o.ncg + o.g - 1) / o.g;
         o.WR = p.NW / o.WC;
-        // rows per warp: the largest of 4, 2, 1 whose tile stays within 56 KB, unless a tile of
-        // half the rows already covers this CTA's whole share (then the rest would be padding)
         o.cta0 = cta0[i], o.ncta = std::min<uint32_t>(ncta[i], std::max<uint32_t>(1, o.out_dim / o.gran));
+    }
+    // Rows per warp of op i: the largest of 4, 2, 1 whose tile stays within `tile_cap`, unless a tile of half the
+    // rows already covers a CTA's whole share of the op (then the rest would be padding).
+    auto pick_rows = [&](ChainOpDev &o, uint32_t tile_cap) -> bool {
         const uint32_t rows_cta = (o.out_dim / o.gran + o.ncta - 1) / o.ncta * o.gran;
-        const uint32_t rw_min = h.epi == EPI_SWIGLU ? 2u : 1u;
+        const uint32_t rw_min = o.epi == EPI_SWIGLU ? 2u : 1u;
         o.rw = 0;
         for (uint32_t rw = 4; rw >= rw_min; rw /= 2) {
             const uint32_t R = o.WR * rw;
@@ -398,22 +410,60 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
             o.rw = rw;
             break;
         }
-        if (!o.rw) return cudaErrorNotSupported;
         o.R = o.WR * o.rw;
-        max_stage = std::max(max_stage, align_up_u32(o.R * o.row_bytes, 128));
-        max_part = std::max(max_part, 2u * 8u * o.R * o.WC * 4u);
-        max_prep = std::max(max_prep, o.ncg * (uint32_t)(h.fmt == FMT_Q4K ? XREGS_Q4K : XREGS_Q6KR) * 32u * 4u);
+        return o.rw != 0;
+    };
+    auto part_bytes = [](const ChainOpDev &o) { return std::max(128u, 2u * 8u * o.R * o.WC * 4u); };
+    auto prep_bytes = [](const ChainOpDev &o) { return o.ncg * (uint32_t)(o.fmt == FMT_Q4K ? XREGS_Q4K : XREGS_Q6KR) * 32u * 4u; };
+    // Tiles of up to 100 KB (four rows per warp on wide matrices) when the ring of at least two of them still fits
+    // beside the partial sums and the activation image; else tiles of up to 56 KB.
+    uint32_t smem = 0;
+    if (dealt) { // a CTA meets one op: every op has the layout that suits it
+        for (int i = 0; i < n; ++i) {
+            ChainOpDev &o = p.op[i];
+            bool fits = false;
+            for (uint32_t tile_cap : {100u * 1024u, 56u * 1024u}) {
+                if (!pick_rows(o, tile_cap)) continue;
+                o.stage_bytes = align_up_u32(o.R * o.row_bytes, 128);
+                o.off_part = 256;
+                o.off_prep = align_up_u32(o.off_part + part_bytes(o), 128);
+                o.off_ring = align_up_u32(o.off_prep + prep_bytes(o), 128);
+                if ((int)o.off_ring + 2 * (int)o.stage_bytes <= budget) {
+                    fits = true;
+                    break;
+                }
+            }
+            if (!fits) return cudaErrorNotSupported;
+            o.S = std::min<uint32_t>(CHAIN_MAX_STAGES, (uint32_t)(budget - (int)o.off_ring) / o.stage_bytes);
+            smem = std::max(smem, o.off_ring + o.S * o.stage_bytes);
+        }
+    } else { // all CTAs walk the list: one layout, sized for the largest op, so that the ring runs on across ops
+        bool fits = false;
+        uint32_t max_stage = 0, max_part = 128, max_prep = 0;
+        for (uint32_t tile_cap : {100u * 1024u, 56u * 1024u}) {
+            max_stage = 0, max_part = 128, max_prep = 0;
+            bool ok = true;
+            for (int i = 0; i < n && ok; ++i) {
+                ChainOpDev &o = p.op[i];
+                ok = pick_rows(o, tile_cap);
+                max_stage = std::max(max_stage, align_up_u32(o.R * o.row_bytes, 128));
+                max_part = std::max(max_part, part_bytes(o));
+                max_prep = std::max(max_prep, prep_bytes(o));
+            }
+            if (ok && 256 + (int)align_up_u32(max_part, 128) + (int)align_up_u32(max_prep, 128) + 2 * (int)max_stage <= budget) {
+                fits = true;
+                break;
+            }
+        }
+        if (!fits) return cudaErrorNotSupported;
+        const uint32_t off_part = 256, off_prep = align_up_u32(off_part + max_part, 128), off_ring = align_up_u32(off_prep + max_prep, 128);
+        const uint32_t S = std::min<uint32_t>(CHAIN_MAX_STAGES, (uint32_t)(budget - (int)off_ring) / max_stage);
+        for (int i = 0; i < n; ++i) {
+            ChainOpDev &o = p.op[i];
+            o.S = S, o.stage_bytes = max_stage, o.off_part = off_part, o.off_prep = off_prep, o.off_ring = off_ring;
+        }
+        smem = off_ring + S * max_stage;
     }
-    // CTAs whose share of an op is empty stream nothing for it, but still take part in the barriers
-    p.off_part = 256;
-    p.off_prep = align_up_u32(p.off_part + max_part, 128);
-    p.off_ring = align_up_u32(p.off_prep + max_prep, 128);
-    p.stage_bytes = max_stage;
-    if ((int)p.off_ring + 2 * (int)max_stage <= budget) break;
-    if (tile_cap == 56u * 1024u) return cudaErrorNotSupported;
-    }
-    p.S = std::min<uint32_t>(8, (uint32_t)(budget - (int)p.off_ring) / max_stage);
-    const uint32_t smem = p.off_ring + p.S * max_stage;
     static bool attr_set[64] = {};
     int devid = 0;
     cudaGetDevice(&devid);
