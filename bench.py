@@ -705,6 +705,26 @@ def run_slice(args):
         nb = weight_bytes(dt, m["rows"], cols)
         per[name] = {"us": round(sp["median"] * 1e3, 2), "gbs": round(nb / sp["median"] / 1e6, 1)}
     res["per_matrix_alone"] = per
+    if args.tokens:
+        # the same slices as a prefill GEMM: plain calls, and the sharded entry point on a group of one
+        S = args.tokens
+        goffs = [S * o for o in shard.vector_offsets(outs)]
+        shg = backend.Shard(ctx, 1, 0, goffs[-1])
+        xs = [torch.randn(S * m["cols"], dtype=torch.float32, device=dev) for m in mats]
+        ys = [torch.empty(S * m["rows"], dtype=torch.float32, device=dev) for m in mats]
+        gper = {}
+        for (name, dt, out, cols), m, x_, y_ in zip(C4_MATS, mats, xs, ys):
+            sp = spread(time_graph(torch, lambda i, st: m["ws"][0].matmul_dev(x_.data_ptr(), y_.data_ptr(), S, st), 4, 3, 5), 4)
+            gper[name] = round(sp["median"] * 1e3, 1)
+        res["gemm_plain_us_per_matrix"] = gper
+        res["gemm_plain_us"] = sum(gper.values())
+
+        def gstep(_i, st):
+            for k, (m, off, x_) in enumerate(zip(mats, goffs, xs)):
+                shg.matmul_dev(m["ws"][0], x_.data_ptr(), S, off, 0, m["rows"] * 1, st, 0 if k + 1 == len(mats) else backend.SHARD_NO_WAIT)
+
+        sp = spread(time_graph(torch, gstep, 4, 3, 5), 4)
+        res["gemm_sharded_entry_us"] = sp["median"] * 1e3
     if args.q6k_cost:
         ctx.debug_set("q6k_cost_permille", args.q6k_cost)
         sp = spread(time_graph(torch, lambda i, st: batches[i % ncopies].launch(st), args.steps, args.warmup, args.replays), args.steps)

@@ -401,6 +401,19 @@ int ullm_cuda_forward_create_st(ullm_cuda_ctx *ctx, const struct ullm_st *st, in
 void ullm_cuda_forward_destroy(ullm_cuda_fwd *f);
 /* GpuForward::forward (forward.rs:384): one token at `pos`, returns vocab logits. */
 int ullm_cuda_forward(ullm_cuda_fwd *f, const float *x_init, size_t pos, float *logits);
+/* GpuForward::forward_debug (forward.rs:530-635; reached from `ULLM_GPU_DBG`, crates/ullm-cli/src/main.rs:387):
+ * steps through layer 0 one op at a time, unfused, and reports for every intermediate the number of NaNs and
+ * infinities and the largest finite magnitude, in the reference's order and under its labels: x_init, attn_norm,
+ * wq, wk, [q_norm, k_norm,] rope_q, rope_k, attn_scores, attn_out, wo, ffn_norm, gate, up, glu, w_down.  As there,
+ * the residual is not added between the two halves, projection biases are not applied, and K / V of `pos` are
+ * written to the cache.  `out` has room for `cap` entries (32 is enough); `*n_out` receives the count.
+ * UNSUPPORTED when layer 0 is a mixture-of-experts layer (the reference walks the dense FFN only). */
+typedef struct ullm_debug_stat {
+    char label[16];
+    uint64_t nan, inf;
+    float maxabs;
+} ullm_debug_stat;
+int ullm_cuda_forward_debug(ullm_cuda_fwd *f, const float *x_init, size_t pos, ullm_debug_stat *out, size_t cap, size_t *n_out);
 /* Fills KV cache positions [pos0, pos0+n) of every layer from host f32 arrays
  * laid out [n_layer][n][kv_dim] (test / benchmark set-up: the reference fills
  * the cache by running tokens). */

@@ -298,6 +298,19 @@ class LlamaModel:
         lib().uo_forward_llama(C.byref(self.c), token, pos, _p(logits))
         return logits
 
+    def forward_debug(self, x_init, pos: int):
+        """``[(label, maxabs), ...]`` of layer 0's intermediates (GpuForward::forward_debug, forward.rs:530-635)."""
+        x = np.ascontiguousarray(x_init, np.float32)
+        idx = (C.c_int * 16)()
+        mx = (C.c_float * 16)()
+        L = lib()
+        L.uo_debug_label.restype = C.c_char_p
+        L.uo_forward_debug.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int]
+        n = L.uo_forward_debug(C.byref(self.c), _p(x), pos, idx, mx, 16)
+        if n < 0:
+            raise OracleError("forward_debug: layer 0 is a mixture-of-experts layer")
+        return [(L.uo_debug_label(idx[i]).decode(), float(mx[i])) for i in range(n)]
+
     def forward_embd(self, x_init, pos: int) -> np.ndarray:
         x = np.ascontiguousarray(x_init, np.float32)
         logits = np.zeros(self.p["vocab"], np.float32)

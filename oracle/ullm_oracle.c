@@ -447,6 +447,98 @@ void uo_forward_llama_embd(uo_model *m, const float *x_init, size_t pos, float *
     uo_matvec_q(&m->output, xb, logits);
     free(x); free(xb); free(q); free(k); free(v); free(att); free(proj); free(gate); free(up); free(scores);
 }
+/* GpuForward::forward_debug (crates/ullm-metal/src/forward.rs:530-635) on the CPU: layer 0 one op at a time, the
+ * largest finite magnitude of every intermediate in the order the reference prints them.  As there, the residual is
+ * not added between the attention and the FFN half (ffn_norm normalises x_init), projection biases are not applied,
+ * and K / V of `pos` go into the cache.  Returns the number of entries (labels: uo_debug_label). */
+static const char *const UO_DEBUG_LABELS[] = {"x_init", "attn_norm", "wq", "wk", "q_norm", "k_norm", "rope_q", "rope_k", "attn_scores",
+                                              "attn_out", "wo", "ffn_norm", "gate", "up", "glu", "w_down"};
+const char *uo_debug_label(int i) { return i >= 0 && i < 16 ? UO_DEBUG_LABELS[i] : ""; }
+static float maxabs_finite(const float *v, size_t n) {
+    float mx = 0.0f;
+    for (size_t i = 0; i < n; i++)
+        if (isfinite(v[i]) && fabsf(v[i]) > mx) mx = fabsf(v[i]);
+    return mx;
+}
+int uo_forward_debug(uo_model *m, const float *x_init, size_t pos, int *label_idx, float *maxabs, int cap) {
+    size_t n_embd = m->n_embd, hd = m->head_dim, n_ff = m->n_ff;
+    size_t kv_dim = m->n_kv_head * hd, q_dim = m->n_head * hd, kv_mul = m->n_head / m->n_kv_head;
+    float scale = 1.0f / sqrtf((float)hd);
+    const uo_layer *lw = &m->layers[0];
+    if (lw->experts || cap < 16) return -1;
+    float *xb = (float *)malloc(n_embd * 4), *q = (float *)malloc(q_dim * 4), *k = (float *)malloc(kv_dim * 4), *v = (float *)malloc(kv_dim * 4);
+    float *att = (float *)malloc(q_dim * 4), *proj = (float *)malloc(n_embd * 4);
+    float *gate = (float *)malloc((n_ff + 1) * 4), *up = (float *)malloc((n_ff + 1) * 4);
+    float *scores = (float *)malloc(m->n_head * (pos + 1) * 4);
+    int n = 0;
+#define UO_PUT(idx, ptr, cnt) (label_idx[n] = (idx), maxabs[n] = maxabs_finite((ptr), (cnt)), n++)
+    UO_PUT(0, x_init, n_embd);
+    uo_rmsnorm(x_init, lw->attn_norm, n_embd, m->eps, xb);
+    UO_PUT(1, xb, n_embd);
+    uo_matvec_q(&lw->wq, xb, q);
+    UO_PUT(2, q, q_dim);
+    uo_matvec_q(&lw->wk, xb, k);
+    UO_PUT(3, k, kv_dim);
+    uo_matvec_q(&lw->wv, xb, v);
+    float tmp[512];
+    if (lw->q_norm) {
+        for (size_t h = 0; h < m->n_head; h++) {
+            uo_rmsnorm(q + h * hd, lw->q_norm, hd, m->eps, tmp);
+            memcpy(q + h * hd, tmp, hd * 4);
+        }
+        UO_PUT(4, q, q_dim);
+    }
+    if (lw->k_norm) {
+        for (size_t h = 0; h < m->n_kv_head; h++) {
+            uo_rmsnorm(k + h * hd, lw->k_norm, hd, m->eps, tmp);
+            memcpy(k + h * hd, tmp, hd * 4);
+        }
+        UO_PUT(5, k, kv_dim);
+    }
+    if (m->rope_neox) {
+        uo_rope_neox(q, m->n_head, hd, hd, pos, m->rope_theta);
+        uo_rope_neox(k, m->n_kv_head, hd, hd, pos, m->rope_theta);
+    } else {
+        uo_rope(q, m->n_head, hd, hd, pos, m->rope_theta);
+        uo_rope(k, m->n_kv_head, hd, hd, pos, m->rope_theta);
+    }
+    UO_PUT(6, q, q_dim);
+    UO_PUT(7, k, kv_dim);
+    size_t off = pos * kv_dim;
+    for (size_t i = 0; i < kv_dim; i++) {
+        m->key_cache[off + i] = m->kv_f16 ? uo_round_f16(k[i]) : k[i];
+        m->val_cache[off + i] = m->kv_f16 ? uo_round_f16(v[i]) : v[i];
+    }
+    for (size_t h = 0; h < m->n_head; h++)
+        for (size_t t = 0; t <= pos; t++)
+            scores[h * (pos + 1) + t] = dot_seq(q + h * hd, m->key_cache + t * kv_dim + (h / kv_mul) * hd, hd) * scale;
+    UO_PUT(8, scores, m->n_head * (pos + 1));
+    for (size_t i = 0; i < q_dim; i++) att[i] = 0.0f;
+    for (size_t h = 0; h < m->n_head; h++) {
+        float *sc = scores + h * (pos + 1), *ao = att + h * hd;
+        uo_softmax(sc, pos + 1);
+        for (size_t t = 0; t <= pos; t++) {
+            const float *vt = m->val_cache + t * kv_dim + (h / kv_mul) * hd;
+            for (size_t d = 0; d < hd; d++) ao[d] += sc[t] * vt[d];
+        }
+    }
+    UO_PUT(9, att, q_dim);
+    uo_matvec_q(&lw->wo, att, proj);
+    UO_PUT(10, proj, n_embd);
+    uo_rmsnorm(x_init, lw->ffn_norm, n_embd, m->eps, xb);
+    UO_PUT(11, xb, n_embd);
+    uo_matvec_q(&lw->w_gate, xb, gate);
+    UO_PUT(12, gate, n_ff);
+    uo_matvec_q(&lw->w_up, xb, up);
+    UO_PUT(13, up, n_ff);
+    for (size_t i = 0; i < n_ff; i++) gate[i] = uo_silu(gate[i]) * up[i];
+    UO_PUT(14, gate, n_ff);
+    uo_matvec_q(&lw->w_down, gate, proj);
+    UO_PUT(15, proj, n_embd);
+#undef UO_PUT
+    free(xb); free(q); free(k); free(v); free(att); free(proj); free(gate); free(up); free(scores);
+    return n;
+}
 void uo_forward_llama(uo_model *m, uint32_t token, size_t pos, float *logits) {
     float *x = (float *)malloc(m->n_embd * 4);
     uo_embed(m, token, x);

@@ -135,6 +135,10 @@ void uo_forward_llama(uo_model *m, uint32_t token, size_t pos, float *logits);
  * crates/ullm-metal/src/forward.rs:384). */
 void uo_forward_llama_embd(uo_model *m, const float *x_init, size_t pos, float *logits);
 
+/* GpuForward::forward_debug (forward.rs:530-635) restated: largest finite |value| of every intermediate of layer 0. */
+const char *uo_debug_label(int i);
+int uo_forward_debug(uo_model *m, const float *x_init, size_t pos, int *label_idx, float *maxabs, int cap);
+
 /* IEEE half round-trip used for the f16 KV cache (round to nearest even). */
 float uo_round_f16(float v);
 

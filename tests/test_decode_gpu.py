@@ -268,3 +268,35 @@ def test_attention_head_shapes_with_a_multi_split_context(ctx, hd, n_head, n_kv_
             assert synth.rel_err(got, ref) < 1e-3, (kv_f16, pos)
             tok = oracle.argmax(ref)
         gf.free()
+
+
+@pytest.mark.parametrize("variant", ["llama", "qk_norm_neox"])
+def test_forward_debug_walks_layer_0_like_the_reference(ctx, variant):
+    """``GpuForward::forward_debug`` (crates/ullm-metal/src/forward.rs:530-635): layer 0 op by op.  Labels and order are
+    the reference's; every intermediate's largest magnitude must agree with the oracle's walk of the same ops, and a
+    NaN planted in the input must show up in the counts instead of disappearing."""
+    p = dict(synth.LLAMA_TINY)
+    m = synth.gen_llama_model(p, 13)
+    flags = {}
+    if variant == "qk_norm_neox":
+        for i, l in enumerate(m["layers"]):
+            l["q_norm"] = 1.0 + 0.1 * synth.normal(900 + i, p["head_dim"])
+            l["k_norm"] = 1.0 + 0.1 * synth.normal(950 + i, p["head_dim"])
+        flags = dict(rope_neox=1, qk_norm=1)
+    mk = lambda t: oracle.Weight(t[0], t[1], t[2], t[3])
+    layers = [{k: (mk(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in m["layers"]]
+    om = oracle.LlamaModel(m["params"], mk(m["tok_embd"]), mk(m["output"]), m["final_norm"], layers, True, rope_neox=bool(flags))
+    gf = backend.GpuForward(ctx, m, kv_f16=True, **flags)
+    x = om.embed(5)
+    for pos in (0, 1, 2):  # each walk writes K / V of its position, so later positions attend to earlier ones
+        ref = om.forward_debug(x, pos)
+        got = gf.forward_debug(x, pos)
+        assert [g[0] for g in got] == [r[0] for r in ref]
+        for (label, nan, inf, mx), (_, rmx) in zip(got, ref):
+            assert nan == 0 and inf == 0, label
+            assert abs(mx - rmx) <= 1e-3 * max(rmx, 1e-6), (pos, label, mx, rmx)
+    bad = x.copy()
+    bad[3] = np.nan
+    got = dict((g[0], g) for g in gf.forward_debug(bad, 3))
+    assert got["x_init"][1] == 1 and got["attn_norm"][1] == p["n_embd"] and got["w_down"][1] > 0
+    gf.free()

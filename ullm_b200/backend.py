@@ -116,6 +116,7 @@ SIGNATURES = {
     "ullm_cuda_forward_destroy": (None, [_vp]),
     "ullm_cuda_forward": (_i, [_vp, _vp, _sz, _vp]),
     "ullm_cuda_forward_set_kv": (_i, [_vp, _sz, _sz, _vp, _vp]),
+    "ullm_cuda_forward_debug": (_i, [_vp, _vp, _sz, _vp, _sz, C.POINTER(_sz)]),
     "ullm_cuda_forward_supports_batched_prefill": (_i, [_vp]),
     "ullm_cuda_forward_greedy": (_i, [_vp, _vp, _i, C.c_uint32, _sz, _sz, _vp]),
     "ullm_cuda_forward_greedy_weight": (_i, [_vp, _vp, C.c_uint32, _sz, _sz, _vp]),
@@ -647,8 +648,14 @@ class GpuModelInput(C.Structure):
     _fields_ = [("params", GpuParams), ("output", GpuWeight), ("final_norm", _vp), ("layers", _vp), ("mlx_table_dtype", _i)]
 
 
+class DebugStatC(C.Structure):
+    """``ullm_debug_stat``."""
+
+    _fields_ = [("label", C.c_char * 16), ("nan", C.c_uint64), ("inf", C.c_uint64), ("maxabs", C.c_float)]
+
+
 class GpuForward:
-    """``GpuForward::{new, forward, supports_batched_prefill}`` on the B200.
+    """``GpuForward::{new, forward, forward_batch, supports_batched_prefill, forward_debug}`` on the B200.
 
     ``model`` is the dict :func:`ullm_b200.synth.gen_llama_model` builds (or the
     same structure filled from a real file): weights as ``(dtype, bytes, out,
@@ -751,6 +758,14 @@ class GpuForward:
         out = np.empty(self.params["vocab"], np.float32)
         self._ctx._check(self._ctx._lib.ullm_cuda_forward(self._h, _ptr(x), pos, _ptr(out)))
         return out
+
+    def forward_debug(self, x_init, pos: int):
+        """``GpuForward::forward_debug`` (forward.rs:530-635): ``[(label, nan, inf, maxabs), ...]`` of layer 0, op by op."""
+        x = _f32(x_init)
+        recs = (DebugStatC * 32)()
+        n = _sz()
+        self._ctx._check(self._ctx._lib.ullm_cuda_forward_debug(self._h, _ptr(x), pos, recs, 32, C.byref(n)))
+        return [(recs[i].label.decode(), int(recs[i].nan), int(recs[i].inf), float(recs[i].maxabs)) for i in range(n.value)]
 
     def set_kv(self, pos0: int, k, v):
         k, v = _f32(k), _f32(v)

@@ -1086,6 +1086,18 @@ int ullm_cuda_forward(ullm_cuda_fwd *f, const float *x_init, size_t pos, float *
     return fwd_status(f);
 }
 
+int ullm_cuda_forward_debug(ullm_cuda_fwd *f, const float *x_init, size_t pos, ullm_debug_stat *out, size_t cap, size_t *n_out) {
+    if (!f || !x_init || !out || !n_out) return ULLM_ERR_INVALID;
+    *n_out = 0;
+    if (pos >= f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "position %zu is outside the context of %zu", pos, f->f.P.n_ctx);
+    static_assert(sizeof(ullm_debug_stat) == sizeof(DebugStat), "debug record layout");
+    cudaError_t e = f->f.debug_layer0(x_init, pos, (DebugStat *)out, cap, n_out);
+    if (e == cudaErrorNotSupported) return ctx_fail(f->ctx, ULLM_ERR_UNSUPPORTED, "forward_debug walks a dense layer 0 only");
+    if (e == cudaErrorInvalidValue) return ctx_fail(f->ctx, ULLM_ERR_INVALID, "room for %zu entries is not enough", cap);
+    if (e != cudaSuccess) return fwd_fail(f, e, "forward_debug");
+    return fwd_status(f);
+}
+
 int ullm_cuda_forward_set_kv(ullm_cuda_fwd *f, size_t pos0, size_t n, const float *k, const float *v) {
     if (!f || !k || !v) return ULLM_ERR_INVALID;
     if (pos0 + n > f->f.P.n_ctx) return ctx_fail(f->ctx, ULLM_ERR_FORMAT, "positions beyond the context");

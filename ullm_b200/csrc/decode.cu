@@ -20,6 +20,7 @@
 #include "decode.h"
 
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -961,6 +962,173 @@ cudaError_t Forward::set_kv(size_t pos0, size_t n, const float *k, const float *
     cudaError_t e2 = cudaStreamSynchronize(stream);
     cudaFree(tmp);
     return e != cudaSuccess ? e : e2;
+}
+
+// ---------------------------------------------------------------------------
+// forward_debug: layer 0 one op at a time (crates/ullm-metal/src/forward.rs:530-635)
+// ---------------------------------------------------------------------------
+// Non-finite counts and the largest finite magnitude of n values `stride` apart (one CTA).
+__global__ void __launch_bounds__(256) debug_stat_kernel(const float *__restrict__ v, size_t n, size_t stride, DebugStat *out) {
+    __shared__ unsigned long long s_nan[8], s_inf[8];
+    __shared__ float s_mx[8];
+    unsigned long long nan = 0, inf = 0;
+    float mx = 0.f;
+    for (size_t i = threadIdx.x; i < n; i += 256) {
+        const float x = v[i * stride];
+        if (isnan(x)) ++nan;
+        else if (isinf(x)) ++inf;
+        else mx = fmaxf(mx, fabsf(x));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        nan += __shfl_xor_sync(0xffffffffu, nan, o);
+        inf += __shfl_xor_sync(0xffffffffu, inf, o);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) s_nan[threadIdx.x >> 5] = nan, s_inf[threadIdx.x >> 5] = inf, s_mx[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; ++i) nan += s_nan[i], inf += s_inf[i], mx = fmaxf(mx, s_mx[i]);
+        out->nan = nan, out->inf = inf, out->maxabs = mx;
+    }
+}
+// Per-head RMSNorm (math.rs:82-86) and RoPE (math.rs:116-162) of `n_heads` heads of `hd` values, unfused: the
+// normalised heads go to `normed` (when norm_w is given), the rotated ones to `roped`.  One warp per head.
+__global__ void debug_heads_kernel(const float *__restrict__ src, const float *__restrict__ norm_w, float eps, const float2 *__restrict__ rp,
+                                   int neox, int hd, float *__restrict__ normed, float *__restrict__ roped) {
+    const int h = blockIdx.x, lane = threadIdx.x;
+    const float *s = src + (size_t)h * hd;
+    float *nd = normed + (size_t)h * hd, *rd = roped + (size_t)h * hd;
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) ss += s[d] * s[d];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+    for (int d = lane; d < hd; d += 32) nd[d] = norm_w ? s[d] * inv * norm_w[d] : s[d];
+    __syncwarp();
+    for (int j = lane; j < hd / 2; j += 32) {
+        const int ia = neox ? j : 2 * j, ib = neox ? j + hd / 2 : 2 * j + 1;
+        const float a = nd[ia], b = nd[ib];
+        const float2 cs = rp[j];
+        rd[ia] = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+        rd[ib] = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+    }
+}
+// scores[h][t] = scale * q[h] . K[t][h / kv_mul] for t <= pos, keys read from the cache.  One warp per (h, t).
+template <typename KV_T>
+__global__ void debug_scores_kernel(const float *__restrict__ q, const KV_T *__restrict__ kcache, int hd, int kv_dim, int kv_mul, int seqlen,
+                                    float scale, float *__restrict__ scores) {
+    const int h = blockIdx.y, t = blockIdx.x, lane = threadIdx.x;
+    const KV_T *k = kcache + (size_t)t * kv_dim + (size_t)(h / kv_mul) * hd;
+    float acc = 0.f;
+    for (int d = lane; d < hd; d += 32) acc += q[(size_t)h * hd + d] * kv_f(k[d]);
+    acc = warp_sum(acc);
+    if (lane == 0) scores[(size_t)h * seqlen + t] = acc * scale;
+}
+__global__ void debug_glu_kernel(const float *__restrict__ gu, int n_ff, float *__restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_ff) {
+        const float g = gu[2 * i], u = gu[2 * i + 1];
+        out[i] = g / (1.0f + expf(-g)) * u; // silu(g) * u (math.rs:103-105)
+    }
+}
+
+cudaError_t Forward::debug_layer0(const float *x_init, size_t pos, DebugStat *out, size_t cap, size_t *n_out) {
+    cudaError_t e;
+#define TRY(x) \
+    if ((e = (x)) != cudaSuccess) return e;
+    TRY(cudaSetDevice(device));
+    const Layer &L = layers[0];
+    if (L.moe || !L.gu_fused) return cudaErrorNotSupported;
+    const size_t hd = P.head_dim, qd = P.n_head * hd, kvd = P.n_kv_head * hd, ne = P.n_embd, nf = P.n_ff, seqlen = pos + 1;
+    // scratch: normed x | q k v projections | normed heads | rotated heads | scores | wo out | gate,up | glu | down | stats
+    const size_t proj = qd + 2 * kvd;
+    const size_t floats = ne + proj + proj + proj + P.n_head * P.n_ctx + ne + 2 * nf + nf + ne;
+    if (!dbg) TRY(dev_alloc((void **)&dbg, floats * 4 + 32 * sizeof(DebugStat)));
+    float *xn = dbg, *pr = xn + ne, *hn = pr + proj, *hr = hn + proj, *sc = hr + proj, *wo_out = sc + P.n_head * P.n_ctx, *gu = wo_out + ne,
+          *glu = gu + 2 * nf, *down = glu + nf;
+    DebugStat *d_stats = (DebugStat *)(down + ne);
+    std::vector<DebugStat> host;
+    auto stat = [&](const char *label, const float *v, size_t n, size_t stride) -> cudaError_t {
+        if (host.size() >= cap || host.size() >= 32) return cudaErrorInvalidValue;
+        DebugStat s{};
+        snprintf(s.label, sizeof s.label, "%s", label);
+        debug_stat_kernel<<<1, 256, 0, stream>>>(v, n, stride, d_stats + host.size());
+        host.push_back(s);
+        return cudaGetLastError();
+    };
+    auto plain = [&](const Mat &m, const float *in, float *o) -> cudaError_t {
+        MlxTables tb;
+        tb.scales = m.scales, tb.biases = m.biases, tb.elem_bytes = m.tbl_bytes, tb.group = m.group;
+        return launch_matvec(dev, m.fmt, m.w, tb, in, o, m.out, m.cols, d_status, stream, MatvecOpts());
+    };
+    ((int *)h_pin)[0] = (int)pos;
+    TRY(cudaMemcpyAsync(state, h_pin, 4, cudaMemcpyHostToDevice, stream));
+    memcpy(h_x, x_init, ne * 4);
+    TRY(cudaMemcpyAsync(x, h_x, ne * 4, cudaMemcpyHostToDevice, stream));
+    TRY(stat("x_init", x, ne, 1));
+    rmsnorm_vec_kernel<<<1, 256, 0, stream>>>(x, L.attn_norm, P.eps, (int)ne, xn);
+    TRY(stat("attn_norm", xn, ne, 1));
+    // projections, stored q | k | v in `pr` whatever way the engine keeps the matrices
+    if (L.qkv_fused) {
+        TRY(plain(L.wqk, xn, pr));
+    } else {
+        if (L.qk_fused) {
+            TRY(plain(L.wqk, xn, pr));
+        } else {
+            TRY(plain(L.wq, xn, pr));
+            TRY(plain(L.wk, xn, pr + qd));
+        }
+        TRY(plain(L.wv, xn, pr + qd + kvd));
+    }
+    TRY(stat("wq", pr, qd, 1));
+    TRY(stat("wk", pr + qd, kvd, 1));
+    const float2 *rp = rope + pos * (hd / 2);
+    debug_heads_kernel<<<(unsigned)P.n_head, 32, 0, stream>>>(pr, L.q_norm, P.eps, rp, P.rope_neox, (int)hd, hn, hr);
+    debug_heads_kernel<<<(unsigned)P.n_kv_head, 32, 0, stream>>>(pr + qd, L.k_norm, P.eps, rp, P.rope_neox, (int)hd, hn + qd, hr + qd);
+    if (L.q_norm) TRY(stat("q_norm", hn, qd, 1));
+    if (L.k_norm) TRY(stat("k_norm", hn + qd, kvd, 1));
+    TRY(stat("rope_q", hr, qd, 1));
+    TRY(stat("rope_k", hr + qd, kvd, 1));
+    // the engine's own attention kernel (it rotates q / k itself and writes K / V of `pos` into the cache); as in the
+    // reference's debug walk the projection biases are left out
+    AttnParams ap;
+    ap.q = pr, ap.knew = pr + qd, ap.vnew = pr + qd + kvd;
+    ap.kcache = kcache, ap.vcache = vcache;
+    ap.rope = rope, ap.pos_ptr = (int *)state, ap.scale = 1.0f / sqrtf((float)hd);
+    ap.partial = partial, ap.counters = counters, ap.out = attn, ap.kv_dim = (int)kvd, ap.n_split = n_split;
+    ap.q_bias = ap.k_bias = ap.v_bias = nullptr, ap.q_norm = L.q_norm, ap.k_norm = L.k_norm;
+    ap.eps = P.eps, ap.neox = P.rope_neox;
+    TRY(launch_attn(ap, (int)hd, (int)(P.n_head / P.n_kv_head), (int)P.n_kv_head, P.kv_f16 != 0, stream, false));
+    const dim3 sg((unsigned)seqlen, (unsigned)P.n_head);
+    if (P.kv_f16)
+        debug_scores_kernel<__half><<<sg, 32, 0, stream>>>(hr, (const __half *)kcache, (int)hd, (int)kvd, (int)(P.n_head / P.n_kv_head), (int)seqlen,
+                                                          ap.scale, sc);
+    else
+        debug_scores_kernel<float><<<sg, 32, 0, stream>>>(hr, (const float *)kcache, (int)hd, (int)kvd, (int)(P.n_head / P.n_kv_head), (int)seqlen,
+                                                         ap.scale, sc);
+    TRY(stat("attn_scores", sc, P.n_head * seqlen, 1));
+    TRY(stat("attn_out", attn, qd, 1));
+    TRY(plain(L.wo, attn, wo_out));
+    TRY(stat("wo", wo_out, ne, 1));
+    rmsnorm_vec_kernel<<<1, 256, 0, stream>>>(x, L.ffn_norm, P.eps, (int)ne, xn); // x is still x_init, as in the reference's walk
+    TRY(stat("ffn_norm", xn, ne, 1));
+    TRY(plain(L.wgu, xn, gu)); // rows interleaved (gate_j, up_j)
+    TRY(stat("gate", gu, nf, 2));
+    TRY(stat("up", gu + 1, nf, 2));
+    debug_glu_kernel<<<(unsigned)((nf + 255) / 256), 256, 0, stream>>>(gu, (int)nf, glu);
+    TRY(stat("glu", glu, nf, 1));
+    TRY(plain(L.wd, glu, down));
+    TRY(stat("w_down", down, ne, 1));
+    std::vector<DebugStat> got(host.size());
+    TRY(cudaMemcpyAsync(got.data(), d_stats, host.size() * sizeof(DebugStat), cudaMemcpyDeviceToHost, stream));
+    TRY(cudaStreamSynchronize(stream));
+    for (size_t i = 0; i < host.size(); ++i) {
+        out[i] = got[i];
+        memcpy(out[i].label, host[i].label, sizeof host[i].label);
+    }
+    *n_out = host.size();
+#undef TRY
+    return cudaSuccess;
 }
 
 } // namespace ullm

@@ -38,6 +38,13 @@ struct HostModel {
     std::vector<HostLayer> layers;
 };
 
+// One line of GpuForward::forward_debug's report (crates/ullm-metal/src/forward.rs:566-580).
+struct DebugStat {
+    char label[16];
+    unsigned long long nan, inf;
+    float maxabs; // largest finite magnitude
+};
+
 struct Forward {
     static constexpr size_t MAX_GREEDY = 4096; // tokens kept on the device between host reads
     struct Mat {
@@ -94,6 +101,10 @@ struct Forward {
     cudaError_t greedy(const void *embd_table, int embd_dtype, uint32_t first_token, size_t pos, size_t n,
                        uint32_t *tokens_host);
     cudaError_t set_kv(size_t pos0, size_t n, const float *k, const float *v);
+    // GpuForward::forward_debug (forward.rs:530-635): layer 0 one op at a time, unfused, with the non-finite counts and
+    // the largest magnitude of every intermediate.  cudaErrorNotSupported when layer 0 is a mixture-of-experts layer.
+    cudaError_t debug_layer0(const float *x_init, size_t pos, DebugStat *out, size_t cap, size_t *n_out);
+    float *dbg = nullptr; // scratch of debug_layer0, allocated on first use
     // batched prefill (prefill.cu): all s prompt tokens in one pass, KV cache filled for 0..s-1,
     // logits of the last token
     bool batch_supported() const;
