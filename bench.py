@@ -764,10 +764,12 @@ def run_c4gemm_multi(args):
         xs = xs.to(torch.bfloat16).to(torch.float32)
         mats.append(dict(dt=dt, out=out, cols=cols, row0=r0, rows=rows, host=w, w=backend.Weight(ctx, dt, w, rows, cols), xs=xs))
 
+    fused = backend.SHARD_FUSED_STORES if args.gemm_exchange == "fused" else 0
+
     def step(_i, st):
         for k, (m, off) in enumerate(zip(mats, offs)):
             last = k + 1 == len(mats)  # the step waits for the other ranks once, after its last matrix
-            sh.matmul_dev(m["w"], m["xs"].data_ptr(), S, off, m["row0"], m["out"], st, 0 if last else backend.SHARD_NO_WAIT)
+            sh.matmul_dev(m["w"], m["xs"].data_ptr(), S, off, m["row0"], m["out"], st, (0 if last else backend.SHARD_NO_WAIT) | fused)
 
     dist.barrier()
     ms = time_graph(torch, step, max(2, args.steps // 4), 3, args.replays, before_timing=dist.barrier)
@@ -803,7 +805,8 @@ def run_c4gemm_multi(args):
                           "tflops": tf, "tflops_per_gpu": tf / world, "peak_tflops": measured_peak_tflops(),
                           "frac_per_gpu": tf / world / measured_peak_tflops(), "scaling": "strong",
                           "peer_store_bytes_per_rank_per_step": 4 * S * sum(outs) // world * (world - 1),
-                          "parallelism": f"rows/{world} per matrix; the GEMM epilogue stores each tile into all ranks' [tokens, out] over NVLink",
+                          "parallelism": (f"rows/{world} per matrix; the GEMM epilogue stores each tile into all ranks' [tokens, out] over NVLink" if fused else
+                                          f"rows/{world} per matrix; each finished [tokens, rows/{world}] block is pushed to all ranks' [tokens, out] by the copy engines while the next matrix is multiplied; step flags instead of an all-gather"),
                           "launch": "one CUDA graph of the timed steps, replayed", "check": {"rel_err_vs_cpu_64_rows_8_tokens_per_rank": float(wt.item())}}), flush=True)
     dist.destroy_process_group()
     return 0
@@ -825,6 +828,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: fused peer stores (default) or the NCCL all-gather comparison arm")
     ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm"], help="N > 1 only: c4gemm runs the block as a sharded prefill GEMM")
     ap.add_argument("--q6k-cost", type=int, default=0, help="--slice-of diagnostic: also time the persistent launch with this per-byte cost (permille) of Q6_K rows")
+    ap.add_argument("--gemm-exchange", default="copy", choices=["copy", "fused"], help="c4gemm at N > 1: copy engines on a side stream, or stores from the GEMM epilogue")
     ap.add_argument("--slice-of", type=int, default=0, help="N = 1 diagnostic: time one rank's share of a W-way split without peers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

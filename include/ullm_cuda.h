@@ -5,7 +5,7 @@
  * The reference has no C ABI: its GPU backend is the Rust crate `ullm-metal`,
  * used concretely by `ullm-model`.  Every entry point below replaces one method
  * of that crate's public surface (cited as file:line inside the reference
- * project); a Rust `ullm-cuda` crate binds them one to one.
+ * project); the Rust crate `crates/ullm-cuda` binds them one to one.
  *
  * Conventions
  *  - All functions return an `ullm_status`; 0 is success.  A human-readable
@@ -259,7 +259,7 @@ typedef struct ullm_shard_op {
     size_t y_offset;   /* where the full-length result starts in the gather buffer (floats) */
     size_t row0;       /* first row of the slice; ignored for weights made by ullm_cuda_shard_weight_create */
 } ullm_shard_op;
-enum { ULLM_SHARD_NO_WAIT = 1 };
+enum { ULLM_SHARD_NO_WAIT = 1, ULLM_SHARD_FUSED_STORES = 2 };
 int ullm_cuda_shard_matvec_dev(ullm_cuda_shard *s, size_t n, const ullm_shard_op *ops, int flags, void *stream);
 /* The same step from host vectors, blocking: x_host[i] (may be NULL: the op's d_x is already filled) is
  * copied into op i's d_x, the step runs with its wait, and floats [y_offset, y_offset + y_count) of
@@ -269,8 +269,16 @@ int ullm_cuda_shard_matvec(ullm_cuda_shard *s, size_t n, const ullm_shard_op *op
 /* Enqueues the bounded wait for every rank's latest step. */
 int ullm_cuda_shard_wait_dev(ullm_cuda_shard *s, void *stream);
 /* Prefill form: this rank's [tokens, rows] block of Y = X W^T goes to columns [row0, row0 + rows)
- * of the token-major [tokens, out_total] matrix at `y_offset` in every rank's gather buffer; the
- * tensor-core GEMM's epilogue stores to all ranks.  d_x: [tokens, in] f32 on this rank. */
+ * of the token-major [tokens, out_total] matrix at `y_offset` in every rank's gather buffer.
+ * d_x: [tokens, in] f32 on this rank.  The tensor-core GEMM writes the block into this rank's
+ * buffer and the copy engines push it to the peers on a stream of the group's own, followed there
+ * by the publication; with ULLM_SHARD_NO_WAIT the call returns to the caller's stream at once, so
+ * the next matrix' GEMM overlaps the transfer, and the last call of a step (without the flag) or
+ * ullm_cuda_shard_wait_dev joins the transfers and waits for the other ranks.  Inside a stream
+ * capture a step must therefore end with such a joining call.  ULLM_SHARD_FUSED_STORES makes the
+ * GEMM's epilogue store every tile to all ranks itself instead (one kernel, no copy engine);
+ * at prefill sizes that is the slower form, because a tile's stores over NVLink then run in series
+ * with the tile's own arithmetic. */
 int ullm_cuda_shard_matmul_dev(ullm_cuda_shard *s, const ullm_cuda_weight *w, const float *d_x, size_t tokens, size_t y_offset,
                                size_t row0, size_t out_total, int flags, void *stream);
 /* Comparison arm: the same exchange as an NCCL all-gather (libnccl.so.2 is loaded at run time;

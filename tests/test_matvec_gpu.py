@@ -235,6 +235,23 @@ def test_matvec_per_row_error_with_outlier_channels(ctx, dtype, mag):
     assert (err[rows] / np.abs(exact)[rows]).max() < TOL
 
 
+@pytest.mark.parametrize("dtype", [backend.Q4_K, backend.Q6_K])
+@pytest.mark.parametrize("poison", [np.nan, np.inf])
+def test_matvec_non_finite_activations_stay_non_finite(ctx, dtype, poison):
+    """A NaN or an infinity in x reaches every output row in the reference's f32 product (math.rs:17); the
+    fixed-point re-expression of x must not round it away (resident weights, streamed kernel; raw bytes too)."""
+    out, cols = 256, 4096
+    w = GEN[dtype](out, cols, 41)
+    x = synth.normal(42, cols)
+    x[1234] = poison
+    wo = backend.Weight(ctx, dtype, w, out, cols)
+    y = wo.matvec(x)
+    assert ctx.last_plan()["streamed"] == 1
+    assert not np.isfinite(y).any()
+    assert not np.isfinite(ctx.matvec_quant(dtype, w, x, out, cols)).any()
+    wo.free()
+
+
 def test_matvec_linearity_at_full_size(ctx):
     """Size-independent property on the largest single matrices: W(a+b) = Wa + Wb."""
     for dtype, out, cols in ((backend.Q4_K, 28672, 8192), (backend.Q6_K, 8192, 28672)):

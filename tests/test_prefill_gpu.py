@@ -9,7 +9,7 @@ import oracle
 from ullm_b200 import backend, synth
 
 pytestmark = pytest.mark.gpu
-TOL = 2e-2  # BASELINE north_star tolerance for bf16 tensor-core products
+TOL = 2e-2  # the tolerance stated for bf16 tensor-core products
 SMALL = dict(n_embd=2048, n_layer=2, n_head=8, n_kv_head=2, head_dim=64, n_ff=2048, n_ctx=640, vocab=1024, rope_theta=500000.0,
              eps=1e-5)
 

@@ -44,6 +44,13 @@ template <> struct FmtTraits<FMT_Q6KR> { static constexpr int XREGS = XREGS_Q6KR
 
 // 16-bit fixed point of up to 32 values sharing one scale.  X = rint(v/s) with
 // s = max|v|/32767; returned as byte planes: hi = X >> 8 (signed), lo = X & 255.
+// max(|a|, |b|) that keeps a NaN once it has seen one (fmaxf drops NaNs): a group that holds a NaN gets a NaN
+// scale, so the NaN reaches every output row the way it does in the reference's f32 product
+// (crates/ullm-model/src/math.rs:17) instead of being rounded to an integer.
+__device__ __forceinline__ float absmax_nan(float mx, float v) {
+    const float a = fabsf(v);
+    return (a > mx || a != a) ? a : mx;
+}
 __device__ __forceinline__ int quant16(float v, float inv) {
     int q = __float2int_rn(v * inv);
     return max(-32767, min(32767, q));
@@ -148,14 +155,14 @@ __device__ __forceinline__ void prep_image(const ActSrc &src, uint32_t in_dim, u
         const float v[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
         float mx = 0.f, sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i])), sum += v[i];
+        for (int i = 0; i < 8; ++i) mx = absmax_nan(mx, v[i]), sum += v[i];
         if (FMT == FMT_Q6KR) { // 64 values share a scale: task bits 0 (8 of 16), 2-3 (group)
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = absmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = absmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = absmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
         } else if (FMT != FMT_Q6K) { // 32 values share a scale: four neighbouring tasks
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            mx = absmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = absmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         }

@@ -167,6 +167,11 @@ struct ullm_cuda_shard {
     bool connected = false;
     ShardDev dev;
     void *nccl_comm = nullptr;
+    // the prefill form pushes finished blocks to the peers with the copy engines on a stream of its own, so that
+    // the transfer of one matrix' block overlaps the next matrix' GEMM
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool copies_pending = false; // copy_stream has work the compute stream has not been joined with
 };
 
 static float *shard_y(const ullm_cuda_shard *s) { return (float *)((uint8_t *)s->base + SHARD_CTL_BYTES); }
@@ -210,6 +215,14 @@ int ullm_cuda_shard_create(ullm_cuda_ctx *c, int world, int rank, size_t y_float
         delete s;
         return ctx_fail(c, e == cudaErrorMemoryAllocation ? ULLM_ERR_OOM : ULLM_ERR_CUDA, "gather buffer: %s", cudaGetErrorString(e));
     }
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->copy_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        ullm_cuda_shard_destroy(s);
+        return ctx_fail(c, ULLM_ERR_CUDA, "copy stream: %s", cudaGetErrorString(e));
+    }
     s->peer_base[rank] = s->base;
     if (world == 1) shard_wire(s);
     *out = s;
@@ -220,6 +233,12 @@ void ullm_cuda_shard_destroy(ullm_cuda_shard *s) {
     if (!s) return;
     cudaSetDevice(s->ctx->device);
     cudaStreamSynchronize(s->ctx->stream);
+    if (s->copy_stream) {
+        cudaStreamSynchronize(s->copy_stream);
+        cudaStreamDestroy(s->copy_stream);
+    }
+    if (s->ev_fork) cudaEventDestroy(s->ev_fork);
+    if (s->ev_join) cudaEventDestroy(s->ev_join);
     if (s->nccl_comm && nccl_api().ok) nccl_api().CommDestroy(s->nccl_comm);
     for (int r = 0; r < s->world; ++r)
         if (r != s->rank && s->peer_ipc[r] && s->peer_base[r]) cudaIpcCloseMemHandle(s->peer_base[r]);
@@ -443,7 +462,13 @@ int ullm_cuda_shard_wait_dev(ullm_cuda_shard *s, void *stream) {
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
     ShardDev sh = s->dev;
     shard_timeout(s, sh);
-    ULLM_CUDA_TRY(c, launch_shard_wait(sh, c->d_status, stream ? (cudaStream_t)stream : c->stream));
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    if (s->copies_pending) { // blocks still on their way to the peers: their publications come first
+        ULLM_CUDA_TRY(c, cudaEventRecord(s->ev_join, s->copy_stream));
+        ULLM_CUDA_TRY(c, cudaStreamWaitEvent(st, s->ev_join, 0));
+        s->copies_pending = false;
+    }
+    ULLM_CUDA_TRY(c, launch_shard_wait(sh, c->d_status, st));
     return ULLM_OK;
 }
 
@@ -467,9 +492,27 @@ int ullm_cuda_shard_matmul_dev(ullm_cuda_shard *s, const ullm_cuda_weight *w, co
     if (!c->force_generic && tokens >= (size_t)c->gemm_min_s && gemm_tc_supported(w->fmt, w->out, w->cols, tokens)) {
         void *xb = nullptr;
         if ((rc = ctx_scratch(c, 7, gemm_tc_scratch_bytes(w->out, w->cols, tokens, c->dev.sm_count), &xb))) return rc;
+        const bool fused = (flags & ULLM_SHARD_FUSED_STORES) != 0 || s->world == 1;
         cudaError_t e = launch_gemm_tc(w->fmt, w->w, d_x, y, xb, w->out, w->cols, tokens, c->dev.sm_count, c->d_status, st, EPI_STORE, nullptr,
-                                       out_total, &sh);
-        if (e == cudaSuccess) e = launch_shard_signal(sh, c->d_status, st);
+                                       out_total, fused ? &sh : nullptr);
+        if (e == cudaSuccess && fused) e = launch_shard_signal(sh, c->d_status, st);
+        if (e == cudaSuccess && !fused) {
+            // The block is complete in this rank's buffer.  The copy engines push it to the peers on the copy stream
+            // (strided: `tokens` rows of `rows` floats, out_total apart), the publication follows them there, and the
+            // compute stream joins only when the caller wants the step to be complete.
+            e = cudaEventRecord(s->ev_fork, st);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(s->copy_stream, s->ev_fork, 0);
+            for (int r = 0; r < s->world && e == cudaSuccess; ++r)
+                if (r != s->rank)
+                    e = cudaMemcpy2DAsync((char *)y + sh.delta[r], out_total * 4, y, out_total * 4, w->out * 4, tokens, cudaMemcpyDefault, s->copy_stream);
+            if (e == cudaSuccess) e = launch_shard_signal(sh, c->d_status, s->copy_stream);
+            s->copies_pending = true;
+            if (e == cudaSuccess && sh.wait) {
+                e = cudaEventRecord(s->ev_join, s->copy_stream);
+                if (e == cudaSuccess) e = cudaStreamWaitEvent(st, s->ev_join, 0);
+                s->copies_pending = false;
+            }
+        }
         if (e != cudaSuccess) {
             cudaGetLastError();
             return ctx_fail(c, ULLM_ERR_CUDA, "sharded GEMM launch: %s", cudaGetErrorString(e));

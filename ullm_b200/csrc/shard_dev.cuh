@@ -12,13 +12,16 @@ __device__ __forceinline__ unsigned long long shard_now_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ unsigned shard_ld_acquire_sys(const unsigned *p) {
+// Relaxed system-scope accesses to the step words; the ordering comes from ONE system-scope fence before the
+// stores of a publication and one after the last load of a wait (a release store / acquire load per word would
+// each carry a fence of its own: one per rank, in series, on the step's critical path).
+__device__ __forceinline__ unsigned shard_ld_relaxed_sys(const unsigned *p) {
     unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void shard_st_release_sys(unsigned *p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void shard_st_relaxed_sys(unsigned *p, unsigned v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // One value to the same place in every rank's gather buffer (`addr` is the place in this rank's).
@@ -33,11 +36,12 @@ __device__ __forceinline__ bool shard_wait_all(const ShardDev &sh, unsigned step
     for (int r = 0; r < sh.world; ++r) {
         const unsigned *f = sh.ctl + r * SHARD_CTL_STRIDE;
         for (;;) {
-            if ((int)(shard_ld_acquire_sys(f) - step) >= 0) break;
+            if ((int)(shard_ld_relaxed_sys(f) - step) >= 0) break;
             asm volatile("nanosleep.u32 32;" ::: "memory");
             if (shard_now_ns() - t0 > sh.timeout_ns) return false;
         }
     }
+    __threadfence_system(); // acquire: the ranks' rows, stored before their publications, are visible from here on
     return true;
 }
 
@@ -48,11 +52,11 @@ __device__ __forceinline__ bool shard_publish(const ShardDev &sh) {
     // System-scope fence: the other CTAs' stores into the peers' buffers were ordered before their
     // arrival (gpu scope), this thread has observed every arrival, and fences are cumulative - so all
     // of those stores are ordered before the release stores below, as seen from the other GPUs.
-    __threadfence_system();
     unsigned *stepw = sh.ctl + SHARD_CTL_STEP;
     const unsigned step = *(volatile unsigned *)stepw + 1u; // touched by one thread per launch; launches are stream-ordered
+    __threadfence_system();                                 // (the load above is in flight while the fence drains)
     *(volatile unsigned *)stepw = step;
-    for (int r = 0; r < sh.world; ++r) shard_st_release_sys(sh.peer_flag[r], step);
+    for (int r = 0; r < sh.world; ++r) shard_st_relaxed_sys(sh.peer_flag[r], step);
     return sh.wait ? shard_wait_all(sh, step) : true;
 }
 
