@@ -209,6 +209,9 @@ def run_reference(args):
 # ---------------------------------------------------------------------------
 # CUDA arm
 # ---------------------------------------------------------------------------
+EAGER = False  # --eager: launch the timed steps from the host instead of replaying a graph (for profilers)
+
+
 def time_graph(torch, step, steps, warmup, replays, before_timing=None):
     """``step(i, stream)`` enqueues step i.  The ``steps`` timed steps are captured in one CUDA graph on a
     non-default stream and replayed ``replays`` times back to back with an event between replays; returns the
@@ -219,10 +222,17 @@ def time_graph(torch, step, steps, warmup, replays, before_timing=None):
         for i in range(warmup):
             step(i, side.cuda_stream)
     side.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        for i in range(steps):
-            step(warmup + i, side.cuda_stream)
+    if EAGER:
+        class _Eager:
+            def replay(self):
+                for i in range(steps):
+                    step(warmup + i, side.cuda_stream)
+        graph = _Eager()
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(steps):
+                step(warmup + i, side.cuda_stream)
     with torch.cuda.stream(side):
         graph.replay()  # one untimed replay
     torch.cuda.synchronize()
@@ -423,6 +433,8 @@ def run_c4(args):
         dist.init_process_group("nccl", device_id=dev)
     ctx = backend.CudaContext(local)
     ctx.set_option(backend.OPT_PDL, 1 if args.pdl else 0)
+    for kv in args.knob:
+        ctx.debug_set(kv.split("=")[0], int(kv.split("=")[1]))
     peak, peak_kind = measured_peak_gbs()
     total_bytes = c4_step_bytes()
 
@@ -674,6 +686,8 @@ def run_slice(args):
     dev = torch.device("cuda:0")
     ctx = backend.CudaContext(0)
     ctx.set_option(backend.OPT_PDL, 1 if args.pdl else 0)
+    for kv in args.knob:
+        ctx.debug_set(kv.split("=")[0], int(kv.split("=")[1]))
     outs = [o for _, _, o, _ in C4_MATS]
     offs = shard.vector_offsets(outs)
     total = offs[-1]
@@ -830,8 +844,12 @@ def main():
     ap.add_argument("--q6k-cost", type=int, default=0, help="--slice-of diagnostic: also time the persistent launch with this per-byte cost (permille) of Q6_K rows")
     ap.add_argument("--gemm-exchange", default="copy", choices=["copy", "fused"], help="c4gemm at N > 1: copy engines on a side stream, or stores from the GEMM epilogue")
     ap.add_argument("--slice-of", type=int, default=0, help="N = 1 diagnostic: time one rank's share of a W-way split without peers")
+    ap.add_argument("--knob", action="append", default=[], help="test knob key=value passed to the library (sweeps; not used by any default run)")
+    ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global EAGER
+    EAGER = args.eager
     if args.impl == "reference":
         return run_reference(args)
     if args.slice_of:

@@ -93,6 +93,14 @@ __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint3
                  : "memory");
 }
 
+// Asks the L2 to fetch `bytes` (a multiple of 16, 16-byte aligned) from global memory: no destination, no completion.
+// (The tile ring in shared memory holds two to three tiles, which bounds the bytes a CTA can have in flight from
+// DRAM; prefetching the tiles after those into the L2 is the obvious way around that bound - see the note at its
+// one use for what it measured.)
+__device__ __forceinline__ void bulk_prefetch_l2(const void *gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
+
 // Programmatic dependent launch: lets the next kernel in the stream start its
 // prologue early / wait for the previous kernel's results.
 __device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

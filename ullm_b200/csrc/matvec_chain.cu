@@ -32,6 +32,10 @@ namespace ullm {
 
 constexpr int CHAIN_MAX_OPS = 12;
 constexpr int CHAIN_MAX_STAGES = 8;
+// L2 prefetch distance in tiles.  Off: measured on B200 it slows the c4 step (121 us without, 136 / 149 / 155 us at
+// 2 / 4 / 8 tiles ahead): the prefetches compete with the ring's own copies for DRAM and do not come back as hits.
+static int g_pf_tiles = 0;
+void matvec_chain_set_prefetch(int v) { g_pf_tiles = v < 0 ? 0 : v; }
 static double g_q6k_cost = 1.3; // relative cost per byte of prepared Q6_K rows when CTAs are dealt out to ops
 void matvec_chain_set_q6k_cost(double v) { g_q6k_cost = v; }
 
@@ -57,6 +61,7 @@ struct ChainParams {
     unsigned *sync; // {arrival count, generation}: zero once, self-restoring
     int *status;
     uint32_t NW, chunk;
+    uint32_t pf_tiles; // tiles the producer keeps requested in the L2 ahead of the ring's own copies
     ShardDev sh; // sh.world > 0: rows go to every rank's gather buffer and the launch publishes the exchange
 };
 
@@ -247,7 +252,18 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
             uint32_t rbeg, rend;
             chain_row_range(o, rbeg, rend);
             const uint32_t ntiles = (rend - rbeg + o.R - 1) / o.R;
+            // this CTA's rows of the op are one contiguous byte range; the L2 prefetch runs pf_tiles tiles ahead of the ring
+            const uint8_t *range0 = o.w + (size_t)rbeg * o.row_bytes;
+            const size_t range_bytes = (size_t)(rend - rbeg) * o.row_bytes, tile_bytes = (size_t)o.R * o.row_bytes;
+            auto prefetch_tile = [&](uint32_t kt) {
+                const size_t b0 = (size_t)kt * tile_bytes;
+                if (b0 >= range_bytes) return;
+                const uint32_t nb = (uint32_t)min(tile_bytes, range_bytes - b0);
+                for (uint32_t off = lane * p.chunk; off < nb; off += 32 * p.chunk) bulk_prefetch_l2(range0 + b0 + off, min(p.chunk, nb - off));
+            };
+            for (uint32_t kt = o.S; kt < o.S + p.pf_tiles && p.pf_tiles; ++kt) prefetch_tile(kt); // tiles 0 .. S-1 are requested by the ring at once
             for (uint32_t k = 0; k < ntiles; ++k, ++kg, s = s + 1 == o.S ? 0 : s + 1, ph ^= (s == 0)) {
+                if (p.pf_tiles) prefetch_tile(k + o.S + p.pf_tiles);
                 bool ok = true;
                 if (lane == 0 && kg >= o.S) ok = wait_or_timeout(&empty[s], ph ^ 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -335,7 +351,7 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
             if (ops[i].epi != EPI_STORE) return cudaErrorNotSupported; // fused epilogues stay on one GPU
         p.sh = *shard;
     }
-    p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 20, p.chunk = 4096;
+    p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 20, p.chunk = 4096, p.pf_tiles = (uint32_t)g_pf_tiles;
     const int budget = dev.max_smem_optin - 1024;
     const uint32_t grid = (uint32_t)dev.sm_count;
     // Independent ops: the CTAs are dealt out to the ops in proportion to their weight bytes (largest
