@@ -849,7 +849,7 @@ cudaError_t Forward::enqueue_step(int mode, const void *embd_table, int embd_dty
                                    false, use_pdl, nullptr, x);
             }
             TRY(e);
-            launches += 3; // route, gate|up, down with the combine (+ residual) in its epilogue
+            launches += 4; // route, gate|up, down, combine (+ residual)
             TRY(cudaGetLastError());
             continue;
         }

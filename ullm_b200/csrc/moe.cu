@@ -2,19 +2,20 @@
 // at once (CPU form: crates/ullm-model/src/lib.rs:1453-1488; GPU form:
 // crates/ullm-metal/src/forward.rs:484-494 with shader.metal:301-444).
 //
-// Three launches (four on the plain fallback):
+// Four launches:
 //   1. route   : per token, top-k experts by descending router logit (ties: lower
 //                index first) and softmax over the selected logits; then the
 //                (token, slot) pairs are grouped by expert so each distinct
 //                expert's weights are read from HBM once for all tokens that
 //                picked it.
 //   2. gate_up : expert-gathered  hidden[pair] = silu(W_gate[e] x_t) * (W_up[e] x_t)
-//   3. down    : expert-gathered  down[pair]   = W_down[e] hidden[pair], and in its epilogue
-//      combine : y[t] = sum over slots, in descending-logit order, of w * down (the order the
-//                reference accumulates in, lib.rs:1479-1488): the CTA that finishes the LAST of a
-//                token's k slots for a row tile (a counter per token and row tile tells) adds the
-//                k partial rows in slot order and writes y, so the result does not depend on
-//                which CTA that was.  (The plain fallback keeps combine as a fourth launch.)
+//   3. down    : expert-gathered  down[pair]   = W_down[e] hidden[pair]
+//   4. combine : y[t] = sum over slots, in descending-logit order, of w * down
+//                (the order the reference accumulates in, lib.rs:1479-1488).  A launch of its own on purpose:
+//                folded into the down kernel's epilogue (a counter per token and row tile, the CTA that
+//                finishes a token's last slot sums the k rows in slot order) it was measured slower on
+//                B200, 90 us against 63 us for the benchmark's 8-token step, because every (expert, row tile)
+//                unit then pays two CTA barriers and an atomic round trip.
 // Kernels 2 and 3 are streamed like the dense matvec: persistent CTAs, each
 // owning a contiguous range of (expert, row-tile) units so that it meets one or
 // two experts only, weights and group tables arriving through a TMA-bulk ring;
@@ -44,7 +45,7 @@ __host__ __device__ inline int route_off_pairs(int E) { return 2 + 2 * E; }
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict__ logits, int n_tok, int n_exp, int k,
                                                        uint32_t *__restrict__ idx, float *__restrict__ wts,
-                                                       int *__restrict__ route, int *__restrict__ slot_cnt, int n_cnt) {
+                                                       int *__restrict__ route) {
     __shared__ __align__(16) float lg[MOE_MAX_TOK][MOE_MAX_EXPERTS];
     __shared__ int sel[MOE_MAX_TOK * MOE_MAX_K];
     __shared__ int cnt[MOE_MAX_EXPERTS];
@@ -52,7 +53,6 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait_prior();
-    for (int i = threadIdx.x; i < n_cnt; i += blockDim.x) slot_cnt[i] = 0; // slot counters of the down kernel's combine
     // one warp per token (n_tok <= 8 = warps of the block)
     if (warp < n_tok) {
         const int t = warp;
@@ -162,11 +162,6 @@ struct MoeStreamParams {
     uint32_t R, NW, S, tiles_per_expert, ncg;
     uint32_t w_stage_bytes, tbl_stage_bytes, stage_bytes; // one matrix' regions; stage = NM * (w + 2 tbl)
     uint32_t off_route, off_q, off_ring; // byte offsets in dynamic shared memory
-    // down kernel only, y != null: combine in the epilogue
-    float *y;            // [n_tok, rows]
-    const float *res;    // added to y when set (may alias y)
-    const float *wts;    // [n_tok, k] softmax weights in slot order
-    int *cnt;            // [n_tok, tiles_per_expert] slots finished, zeroed by the routing kernel
 };
 
 // GATE_UP: two matrices, x indexed by token, epilogue silu(g)*u.
@@ -371,33 +366,6 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-        if (!GATE_UP && p.y) {
-            // combine (lib.rs:1479-1488): count this unit's pairs in; whoever completes a token's k-th slot for this
-            // row tile sums the k partial rows in slot order
-            int *fl = (int *)(u_s + 2 + 32); // up to MOE_MAX_TOK tokens completed by this unit
-            asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory"); // every warp's rows of the unit are stored
-            if ((int)tid < np) {
-                const int t = pairs[pb + (int)tid] / (int)p.k;
-                __threadfence();
-                int *c = p.cnt + (size_t)t * p.tiles_per_expert + rt;
-                const bool last = !aborted && atomicAdd(c, 1) == (int)p.k - 1;
-                fl[tid] = last ? t : -1;
-                __threadfence();
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(nthr_c) : "memory");
-            const uint32_t nr = min(p.R, p.rows - r0);
-            for (int j = 0; j < np; ++j) {
-                const int t = fl[j];
-                if (t < 0) continue;
-                for (uint32_t r = tid; r < nr; r += nthr_c) {
-                    float acc = 0.f;
-                    for (uint32_t sl = 0; sl < p.k; ++sl)
-                        acc += p.wts[(size_t)t * p.k + sl] * __ldcg(p.out + ((size_t)t * p.k + sl) * p.rows + r0 + r);
-                    const size_t at = (size_t)t * p.rows + r0 + r;
-                    p.y[at] = p.res ? p.res[at] + acc : acc; // the residual stream's `x += down` (lib.rs:959-961) when asked for
-                }
-            }
-        }
     }
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
 }
@@ -481,7 +449,7 @@ static MoePlanInt plan_moe(const DeviceInfo &dev, bool gate_up, uint32_t rows, u
     const uint32_t NW = 16;
     const int budget = dev.max_smem_optin - 1024;
     const uint32_t off_route = 128; // routing table + the CTA's two unit bounds
-    const uint32_t off_q = align_up(off_route + ((uint32_t)route_off_pairs((int)n_exp) + MOE_MAX_TOK * MOE_MAX_K + 2 + 32 + MOE_MAX_TOK) * 4, 128); // + per-warp sums of squares + combine flags
+    const uint32_t off_q = align_up(off_route + ((uint32_t)route_off_pairs((int)n_exp) + MOE_MAX_TOK * MOE_MAX_K + 2 + 32) * 4, 128); // + per-warp sums of squares
     const uint32_t off_ring = align_up(off_q + n_vec * ncg * XREGS_MLX * 32 * 4, 128);
     for (uint32_t RW = 1; RW <= 4; RW *= 2) {
         const uint32_t R = NW * RW;
@@ -542,7 +510,7 @@ size_t moe_scratch_bytes(const MoeExperts &e) {
     const size_t pairs = (size_t)MOE_MAX_TOK * MOE_MAX_K;
     size_t route = (size_t)(route_off_pairs((int)e.n_experts) + pairs) * 4;
     route = (route + 255) / 256 * 256;
-    return route + pairs * e.inter * 4 + pairs * e.hidden * 4 + pairs * 8 + 1024 + (size_t)MOE_MAX_TOK * ((e.hidden + 15) / 16) * 4; // + slot counters
+    return route + pairs * e.inter * 4 + pairs * e.hidden * 4 + pairs * 8 + 1024;
 }
 
 const char *moe_shape_error(const MoeExperts &e, size_t n_tok, size_t k) {
@@ -567,8 +535,6 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
     float *down = hidden + pairs_cap * e.inter;
     uint32_t *idx_s = (uint32_t *)(down + pairs_cap * e.hidden);
     float *wts_s = (float *)(idx_s + pairs_cap);
-    int *cnt = (int *)(wts_s + pairs_cap + 256); // [MOE_MAX_TOK][row tiles of the down kernel]
-    const int n_cnt = (int)(MOE_MAX_TOK * ((e.hidden + 15) / 16));
     const uint32_t tb = (uint32_t)e.table_bytes;
     // both the streamed and the plain kernels read x with 128-bit loads: callers check this before launching
     if ((uintptr_t)d_x % 16 || (uintptr_t)d_y % 4 || (uintptr_t)d_logits % 4) return cudaErrorMisalignedAddress;
@@ -587,7 +553,7 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
         cudaLaunchConfig_t rc_cfg = {};
         rc_cfg.gridDim = dim3(1), rc_cfg.blockDim = dim3(256), rc_cfg.stream = st, rc_cfg.attrs = pat, rc_cfg.numAttrs = pdl ? 1 : 0;
         cudaError_t err = cudaLaunchKernelEx(&rc_cfg, moe_route_kernel, d_logits + t0 * e.n_experts, (int)nt, (int)e.n_experts, (int)k, idx,
-                                             wts, route, cnt, n_cnt);
+                                             wts, route);
         if (err != cudaSuccess) return err;
 
         MoePlanInt pg, pd;
@@ -601,7 +567,6 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
             a.w[0] = (const uint8_t *)e.gate_w, a.sc[0] = (const uint8_t *)e.gate_s, a.bi[0] = (const uint8_t *)e.gate_b;
             a.w[1] = (const uint8_t *)e.up_w, a.sc[1] = (const uint8_t *)e.up_s, a.bi[1] = (const uint8_t *)e.up_b;
             a.act = x, a.norm_w = d_norm_w, a.eps = eps, a.out = hidden, a.route = route, a.status = d_status;
-            a.y = nullptr, a.res = nullptr, a.wts = nullptr, a.cnt = nullptr;
             a.n_exp = (uint32_t)e.n_experts, a.k = (uint32_t)k, a.n_tok = nt;
             err = tb == 2 ? launch_moe_g<true, uint16_t>(pg, st, pdl) : launch_moe_g<true, float>(pg, st, pdl);
             if (err != cudaSuccess) return err;
@@ -610,10 +575,8 @@ cudaError_t launch_moe_ffn(const DeviceInfo &dev, const MoeExperts &e, const flo
             b.w[1] = nullptr, b.sc[1] = nullptr, b.bi[1] = nullptr;
             b.act = hidden, b.norm_w = nullptr, b.eps = 0.f, b.out = down, b.route = route, b.status = d_status;
             b.n_exp = (uint32_t)e.n_experts, b.k = (uint32_t)k, b.n_tok = nt;
-            b.y = d_y + t0 * e.hidden, b.res = d_res ? d_res + t0 * e.hidden : nullptr, b.wts = wts, b.cnt = cnt;
             err = tb == 2 ? launch_moe_g<false, uint16_t>(pd, st, pdl) : launch_moe_g<false, float>(pd, st, pdl);
             if (err != cudaSuccess) return err;
-            continue; // the down kernel has written y
         } else {
             if (d_norm_w) return cudaErrorNotSupported; // the plain kernels take the vector as it is
             dim3 g1((unsigned)((e.inter + 7) / 8), npairs), g2((unsigned)((e.hidden + 7) / 8), npairs);
