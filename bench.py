@@ -54,7 +54,7 @@ METRIC = "quantized_matvec_hbm_gbs"
 DTYPE = "u8 x s16 integer dot products (x as 16-bit fixed point per 32/64 values), f32 scale and accumulate"
 # dram__bytes_read.sum + dram__bytes_write.sum of one step's kernels at N = 1, from an ncu capture of this
 # workload (None until one has been taken)
-NCU_TRAFFIC_PER_STEP = {"c4_70b_layer_matvec": None}
+NCU_TRAFFIC_PER_STEP = {"c4_70b_layer_matvec": 543_680_000 + 6_027_520}
 
 
 def weight_bytes(dtype, out, cols):
@@ -373,6 +373,88 @@ def sec_c3(torch, backend, ctx, dev, args, peak):
         out["check"] = {"first_token_matches": bool(tok == int(g["first"])), "leading_tokens_equal_to_oracle": same, "of": n_gen}
     gf.free()
     return out
+
+
+def aux_c2decode(torch, backend, ctx, dev, args, peak):
+    out = {"workload": "c2decode"}
+    if True:
+        # Decode step of the Qwen3-30B-A3B shape (MLX 4-bit, 128 experts, 8 per token): the model the reference
+        # quotes its MoE decode rate on.  One seeded layer's weights are uploaded once per layer (separate device
+        # copies, so every layer streams its own bytes from HBM); tokens are produced by the on-device greedy loop.
+        p = dict(synth.QWEN3MOE_30B)
+        p["n_layer"] = args.layers or p["n_layer"]
+        one = synth.gen_qwen3moe_model(dict(p, n_layer=1), synth.seed_for(2, 8))
+        m = dict(one, params=p, layers=[one["layers"][0]] * p["n_layer"])
+        gf = backend.GpuForward(ctx, m, kv_f16=True, rope_neox=1, qk_norm=1)
+        t = m["tok_embd"]
+        embd = backend.Weight(ctx, t[0], t[1], t[2], t[3], t[4], t[5], t[6])
+        n_gen = args.steps if args.steps > 20 else 128
+        gf.greedy_weight(embd, 11, 0, min(8, n_gen))  # warm the greedy graph
+        t0 = time.perf_counter()
+        toks = gf.greedy_weight(embd, 11, 0, n_gen)
+        dt = time.perf_counter() - t0
+        e, hd, g = p["n_embd"], p["head_dim"], p["group"]
+        qd, kvd, ne, k, mi = p["n_head"] * hd, p["n_kv_head"] * hd, p["n_experts"], p["n_experts_used"], p["moe_inter"]
+        mlx = lambda o, c: o * c // 2 + 2 * 2 * o * (c // g)  # packed words + bf16 scale and bias tables
+        layer = mlx(qd, e) + 2 * mlx(kvd, e) + mlx(e, qd) + mlx(ne, e) + k * (2 * mlx(mi, e) + mlx(e, mi))
+        nbytes = p["n_layer"] * layer + mlx(p["vocab"], e) + 2 * 2 * kvd * p["n_layer"] * (n_gen // 2)
+        out.update(tok_per_s=n_gen / dt, us_per_token=dt / n_gen * 1e6, tokens=n_gen, layers=p["n_layer"], bytes_per_token=nbytes,
+                   gbs=nbytes * n_gen / dt / 1e9, first_tokens=toks[:8].tolist(),
+                   note="weights of one seeded layer repeated per layer (distinct device copies); greedy loop on the device")
+    return out
+
+
+def aux_c3prefill(torch, backend, ctx, dev, args, peak):
+    out = {"workload": "c3prefill"}
+    if True:
+        # time to first token on the Llama-3.2-1B shape: all prompt tokens in one batched pass
+        # (tensor-core GEMMs on the quantized weights), against the same prompt token by token
+        p = dict(synth.LLAMA_1B)
+        m = synth.gen_llama_model(p, synth.seed_for(3, 0))
+        gf = backend.GpuForward(ctx, m, kv_f16=True)
+        S = args.tokens
+        emb = synth.normal(synth.seed_for(3, 5), S * p["n_embd"]).reshape(S, p["n_embd"]) * np.float32(0.02)
+        gf.forward_batch(emb, S)  # allocates the chunk buffers
+        reps = max(3, min(args.steps, 20))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            lg = gf.forward_batch(emb, S)
+        dt = (time.perf_counter() - t0) / reps
+        n_seq = min(S, 32)
+        t0 = time.perf_counter()
+        for i in range(n_seq):
+            gf.forward(emb[i], i)
+        dt_seq = (time.perf_counter() - t0) / n_seq
+        params = 16 * (2560 * 2048 + 512 * 2048 + 2048 * 2048 + 2 * 8192 * 2048 + 2048 * 8192)
+        flop = 2.0 * S * params
+        out.update(tokens=S, ms_prefill=dt * 1e3, prefill_tok_per_s=S / dt, gemm_tflops=flop / dt / 1e12,
+                   ms_per_token_stepwise=dt_seq * 1e3, speedup_vs_stepwise=dt_seq * S / dt, last_logit_argmax=int(np.argmax(lg)),
+                   note="host embeddings in, last-token logits out; projections as bf16 tensor-core GEMMs, attention f32")
+    return out
+
+
+def run_aux(args):
+    """Single-GPU runs of one of the other configurations on its own (the figures the N = 1 line carries in
+    `secondary`, plus the Qwen3-MoE decode step and the batched prefill), for profiling one workload at a time."""
+    import torch
+
+    from ullm_b200 import backend
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    ctx = backend.CudaContext(0)
+    ctx.set_option(backend.OPT_PDL, 1 if args.pdl else 0)
+    peak, _ = measured_peak_gbs()
+    if args.workload == "c4gemm":
+        mats = [m for m in c4_weights(backend, ctx) if not args.only or m["name"] == args.only]
+        out = sec_c4gemm(torch, backend, ctx, dev, args, mats)
+    else:
+        fn = {"c0": sec_c0, "c1": sec_c1, "c2": sec_c2, "c3": sec_c3, "c2decode": aux_c2decode, "c3prefill": aux_c3prefill}[args.workload]
+        out = fn(torch, backend, ctx, dev, args, peak)
+    if "gbs" in out:
+        out["frac_of_measured_peak"] = out["gbs"] / peak
+    print(json.dumps(out), flush=True)
+    return 0
 
 
 def c4_weights(backend, ctx):
@@ -840,7 +922,11 @@ def main():
     ap.add_argument("--launch", default="auto", choices=["auto", "separate"],
                     help="N = 1: the batch call (one persistent launch for the seven matrices) or seven launches per step")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: fused peer stores (default) or the NCCL all-gather comparison arm")
-    ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm"], help="N > 1 only: c4gemm runs the block as a sharded prefill GEMM")
+    ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm", "c0", "c1", "c2", "c3", "c2decode", "c3prefill"],
+                    help="c4 is the benchmark.  N > 1: c4gemm runs the block as a sharded prefill GEMM.  N = 1: any other choice runs that "
+                         "configuration alone and prints its figures (what `secondary` holds, plus the MoE decode step and the batched prefill)")
+    ap.add_argument("--layers", type=int, default=0, help="c2decode: number of layers (default: the model's 48)")
+    ap.add_argument("--only", default="", help="c4gemm at N = 1: just this matrix of the block (q, k, v, o, gate, up, down)")
     ap.add_argument("--q6k-cost", type=int, default=0, help="--slice-of diagnostic: also time the persistent launch with this per-byte cost (permille) of Q6_K rows")
     ap.add_argument("--gemm-exchange", default="copy", choices=["copy", "fused"], help="c4gemm at N > 1: copy engines on a side stream, or stores from the GEMM epilogue")
     ap.add_argument("--slice-of", type=int, default=0, help="N = 1 diagnostic: time one rank's share of a W-way split without peers")
@@ -856,6 +942,8 @@ def main():
         return run_slice(args)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1 and args.workload == "c4gemm":
         return run_c4gemm_multi(args)
+    if args.workload != "c4":
+        return run_aux(args)
     return run_c4(args)
 
 

@@ -167,8 +167,10 @@ typedef struct ullm_chain_op {
 } ullm_chain_op;
 int ullm_cuda_weight_matvec_chain_dev(ullm_cuda_ctx *ctx, size_t n, const ullm_chain_op *ops, void *stream);
 /* GpuForward::matmul (forward.rs:679-725) on a resident weight: x [s, in] f32
- * token-major -> y [s, out].  Prefill-sized batches run on the tensor cores
- * (activations and dequantized weights rounded to bf16, f32 accumulation). */
+ * token-major -> y [s, out].  Prefill-sized batches (32 tokens or more) run on the tensor
+ * cores (activations and dequantized weights rounded to bf16, f32 accumulation): Q4_K,
+ * Q6_K with in % 2048 == 0, and MLX 4-bit with group 64; other shapes form the product
+ * one token at a time with the matvec kernels. */
 int ullm_cuda_weight_matmul(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *x, float *y, size_t s);
 int ullm_cuda_weight_matmul_dev(ullm_cuda_ctx *ctx, const ullm_cuda_weight *w, const float *d_x, float *d_y, size_t s,
                                 void *stream);

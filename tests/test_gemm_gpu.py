@@ -128,3 +128,43 @@ def test_gemm_check_pattern(ctx):
     finally:
         ctx.debug_set("gemm_min_s", 32)
     check(got, *expected(backend.Q4_K, w, xs, out_dim, in_dim, s))
+
+
+# ---- MLX 4-bit (matmul_mlx4, crates/ullm-metal/src/shader.metal:568; CPU form math.rs:38-79) on the tensor cores ----
+def expected_mlx(w, s32, b32, xs, out_dim, in_dim, group, s):
+    ow = oracle.Weight(oracle.MLX_U32, w, out_dim, in_dim, s32, b32, group)
+    y_oracle = oracle.matmul_q(ow, xs, s)
+    wd = bf16_round(oracle.dequantize_mlx_q4(w, s32, b32, out_dim, in_dim, group)).astype(np.float64)
+    xb = bf16_round(xs).reshape(s, in_dim).astype(np.float64)
+    return y_oracle, (xb @ wd.T)
+
+
+@pytest.mark.parametrize("out_dim,in_dim,s", [(128, 256, 32), (768, 2048, 100), (2048, 768, 512), (300, 1024, 300), (200, 8192, 64)])
+def test_matmul_mlx4_tensor_core_path(ctx, out_dim, in_dim, s):
+    """f32 tables through the host entry point (what the reference passes) and bf16 tables on a resident weight;
+    ragged rows and tokens, a split-K shape, the Qwen3-30B-A3B expert shapes."""
+    gs = 64
+    w, sc, bi = synth.gen_mlx4(out_dim, in_dim, gs, 61)
+    s32, b32 = synth.bf16_to_f32(sc), synth.bf16_to_f32(bi)
+    xs = synth.normal(62, s * in_dim)
+    want = expected_mlx(w, s32, b32, xs, out_dim, in_dim, gs, s)
+    got = ctx.matmul_mlx4(w, s32, b32, xs, out_dim, in_dim, gs, s)
+    assert ctx.last_plan()["grid"] == -1, "the tensor-core GEMM did not run"
+    check(got, *want, in_dim=in_dim)
+    wo = backend.Weight(ctx, backend.MLX_U32, w, out_dim, in_dim, sc, bi, gs)  # bf16 tables as stored on disk
+    got2 = wo.matmul(xs, s)
+    assert ctx.last_plan()["grid"] == -1
+    check(got2, *want, in_dim=in_dim)
+    assert np.array_equal(got, got2)  # the same values whichever width the tables are kept in
+    wo.free()
+
+
+def test_matmul_mlx4_other_groups_keep_the_matvec_path(ctx):
+    out_dim, in_dim, s, gs = 96, 512, 40, 32
+    w, sc, bi = synth.gen_mlx4(out_dim, in_dim, gs, 63)
+    s32, b32 = synth.bf16_to_f32(sc), synth.bf16_to_f32(bi)
+    xs = synth.normal(64, s * in_dim)
+    got = ctx.matmul_mlx4(w, s32, b32, xs, out_dim, in_dim, gs, s)
+    assert ctx.last_plan()["grid"] != -1
+    ref = oracle.matmul_q(oracle.Weight(oracle.MLX_U32, w, out_dim, in_dim, s32, b32, gs), xs, s)
+    assert synth.rel_err(got, ref) < 1e-3

@@ -64,11 +64,13 @@ def build(verbose: bool = False, force: bool = False) -> str:
                 raise RuntimeError(f"nvcc failed on {src}")
     objs = [os.path.join(OBJ, s[:-3] + ".o") for s in sources()]
     if jobs or not os.path.exists(SO):
-        cmd = [nvcc(), *ARCH, "-shared", "-o", SO, *objs, "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+        tmp = SO + ".tmp"  # linked beside the target and renamed, so a reader never maps a half-written library
+        cmd = [nvcc(), *ARCH, "-shared", "-o", tmp, *objs, "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+        os.replace(tmp, SO)
     return SO
 
 

@@ -617,12 +617,13 @@ int ullm_cuda_weight_export(ullm_cuda_ctx *c, const ullm_cuda_weight *w, void *b
 // FMT_Q6KR prepared); ULLM_ERR_UNSUPPORTED (silently, no message) when the shape or
 // the batch is outside what it takes, so callers can fall back to per-token matvecs.
 static int gemm_try(ullm_cuda_ctx *c, int fmt, const void *d_w, const float *d_x, float *d_y, size_t out_dim, size_t in_dim,
-                    size_t s, cudaStream_t st) {
-    if (c->force_generic || s < (size_t)c->gemm_min_s || !gemm_tc_supported(fmt, out_dim, in_dim, s)) return ULLM_ERR_UNSUPPORTED;
+                    size_t s, cudaStream_t st, const MlxTables *mlx = nullptr) {
+    if (c->force_generic || s < (size_t)c->gemm_min_s) return ULLM_ERR_UNSUPPORTED;
+    if (fmt == FMT_MLX4 ? !(mlx && gemm_tc_supported_mlx4(out_dim, in_dim, s, *mlx)) : !gemm_tc_supported(fmt, out_dim, in_dim, s)) return ULLM_ERR_UNSUPPORTED;
     void *xb = nullptr;
     int rc = ctx_scratch(c, 7, gemm_tc_scratch_bytes(out_dim, in_dim, s, c->dev.sm_count), &xb);
     if (rc) return rc;
-    cudaError_t e = launch_gemm_tc(fmt, d_w, d_x, d_y, xb, out_dim, in_dim, s, c->dev.sm_count, c->d_status, st);
+    cudaError_t e = launch_gemm_tc(fmt, d_w, d_x, d_y, xb, out_dim, in_dim, s, c->dev.sm_count, c->d_status, st, EPI_STORE, nullptr, 0, nullptr, mlx);
     if (e == cudaErrorNotSupported) {
         cudaGetLastError();
         return ULLM_ERR_UNSUPPORTED;
@@ -660,6 +661,14 @@ int ullm_cuda_matmul_dev(ullm_cuda_ctx *c, int dtype, const void *d_w, const voi
         rc = gemm_try(c, gfmt, gw, d_x, d_y, out_dim, in_dim, s, st);
         if (rc != ULLM_ERR_UNSUPPORTED) return rc;
     }
+    // MLX 4-bit words with group 64 (matmul_mlx4, crates/ullm-metal/src/shader.metal:568): the same tensor-core kernel,
+    // values q * scale + bias formed in its dequantization stage
+    if (fmt == FMT_MLX4 && d_scales && d_biases && (table_dtype == ULLM_DTYPE_F32 || table_dtype == ULLM_DTYPE_BF16)) {
+        MlxTables tb;
+        tb.scales = d_scales, tb.biases = d_biases, tb.group = group, tb.elem_bytes = table_dtype == ULLM_DTYPE_F32 ? 4 : 2;
+        int rc = gemm_try(c, FMT_MLX4, d_w, d_x, d_y, out_dim, in_dim, s, st, &tb);
+        if (rc != ULLM_ERR_UNSUPPORTED) return rc;
+    }
     // Otherwise the product is formed one token column at a time with the matvec kernel
     // (same arithmetic, weights re-read per token).
     for (size_t t = 0; t < s; ++t) {
@@ -674,7 +683,9 @@ int ullm_cuda_weight_matmul_dev(ullm_cuda_ctx *c, const ullm_cuda_weight *w, con
     if (!c || !w || !d_x || !d_y) return ULLM_ERR_INVALID;
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
     cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
-    int rc = gemm_try(c, w->fmt, w->w, d_x, d_y, w->out, w->cols, s, st);
+    MlxTables tb;
+    tb.scales = w->scales, tb.biases = w->biases, tb.elem_bytes = w->table_bytes, tb.group = w->group;
+    int rc = gemm_try(c, w->fmt, w->w, d_x, d_y, w->out, w->cols, s, st, w->fmt == FMT_MLX4 ? &tb : nullptr);
     if (rc != ULLM_ERR_UNSUPPORTED) return rc;
     for (size_t t = 0; t < s; ++t)
         if ((rc = ullm_cuda_weight_matvec_dev(c, w, d_x + t * w->cols, d_y + t * w->out, stream))) return rc;

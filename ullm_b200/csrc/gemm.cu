@@ -136,6 +136,7 @@ struct GemmParams {
     int epi;                   // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU, applied here only when there is one k slice
     const float *res;          // EPI_RESIDUAL: y = res + W x (may alias y)
     uint32_t ldy;              // elements between two tokens in y / res (the full matrix' rows when this launch covers a row range)
+    uint32_t tbl_bytes;        // MLX 4-bit: bytes per table entry (4 = f32, 2 = bf16 bits); group size is 64
     int sh_world;              // > 0: every output element goes to the same place in all ranks' gather buffers (EPI_STORE)
     long long sh_delta[SHARD_MAX_RANKS];
 #ifdef ULLM_TUNING
@@ -145,7 +146,9 @@ struct GemmParams {
 };
 // x: bf16 activations [s, in], 128-byte swizzle.  w0..w2: the packed weight bytes as plain
 // 2-D byte tensors [out rows, row bytes] — Q4_K: w0 = whole 144-byte blocks; prepared
-// Q6_K: w0 = 48-byte records, w1 = the 16 scale bytes of a block, w2 = eight blocks' f16 d.
+// Q6_K: w0 = 48-byte records, w1 = the 16 scale bytes of a block, w2 = eight blocks' f16 d;
+// MLX 4-bit (group 64): w0 = the 128 bytes of packed words of a 256-k block, w1 / w2 = 16 bytes of the row's
+// scale / bias table around the block's four entries.
 struct GemmMaps {
     CUtensorMap x, w0, w1, w2;
 };
@@ -157,6 +160,11 @@ template <int FMT> struct GemmCfg;
 template <> struct GemmCfg<FMT_Q4K> {
     static constexpr int RAW_BYTES = GM * Q4K_BYTES; // [128 rows][144 B]: 16-byte reads one row apart hit distinct banks
     static constexpr int PHASES = PHASES_Q4K;
+    static constexpr int RAW_STAGES = 4;
+};
+template <> struct GemmCfg<FMT_MLX4> {
+    static constexpr int RAW_BYTES = GM * 128 + 2 * GM * 16; // [128 rows][128 B of words], [128][16 B] scales, [128][16 B] biases
+    static constexpr int PHASES = 2;
     static constexpr int RAW_STAGES = 4;
 };
 template <> struct GemmCfg<FMT_Q6KR> {
@@ -267,6 +275,54 @@ __device__ __forceinline__ void chunk_store(const BlkQ6KR &b, int c, uint32_t tp
     tmem_st8(ta + 16 + 8 * tp, oB);  // second group
 }
 
+// MLX 4-bit, group 64 (crates/ullm-core/src/dequant.rs:297-317): a 64-k chunk is one group; thread (row, q) owns the
+// chunk's words 4q .. 4q+3 = k 32q .. 32q+31, nibble n of word j being element 8j + n.
+struct BlkMLX {
+    uint4 qs[4];      // per chunk: the thread's four words
+    float sc[4], bi[4]; // per chunk: the group's scale and bias
+};
+__device__ __forceinline__ void blk_load_mlx(BlkMLX &b, uint32_t raw, uint32_t row, uint32_t q, uint32_t kb, uint32_t tbl_bytes) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) b.qs[c] = lds128(raw + row * 128 + 32 * c + 16 * q);
+    const uint32_t ts = raw + GM * 128 + row * 16, tb = ts + GM * 16;
+    if (tbl_bytes == 4) {
+        const uint4 s4 = lds128(ts), b4 = lds128(tb);
+        b.sc[0] = __uint_as_float(s4.x), b.sc[1] = __uint_as_float(s4.y), b.sc[2] = __uint_as_float(s4.z), b.sc[3] = __uint_as_float(s4.w);
+        b.bi[0] = __uint_as_float(b4.x), b.bi[1] = __uint_as_float(b4.y), b.bi[2] = __uint_as_float(b4.z), b.bi[3] = __uint_as_float(b4.w);
+    } else { // bf16 bits: the 16 staged bytes hold two blocks' entries, this block's four at (kb & 1) * 8
+        const uint32_t o = (kb & 1u) * 8u;
+        const uint32_t s01 = lds32(ts + o), s23 = lds32(ts + o + 4), b01 = lds32(tb + o), b23 = lds32(tb + o + 4);
+        b.sc[0] = __uint_as_float(s01 << 16), b.sc[1] = __uint_as_float(s01 & 0xffff0000u);
+        b.sc[2] = __uint_as_float(s23 << 16), b.sc[3] = __uint_as_float(s23 & 0xffff0000u);
+        b.bi[0] = __uint_as_float(b01 << 16), b.bi[1] = __uint_as_float(b01 & 0xffff0000u);
+        b.bi[2] = __uint_as_float(b23 << 16), b.bi[3] = __uint_as_float(b23 & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void blk_load(BlkMLX &, uint32_t, uint32_t, uint32_t, uint32_t) {} // (the MLX path loads with its table width)
+// value = q * scale + bias (dequant.rs:311-314; the product is exact for bf16-derived scales, so the fused
+// multiply-add rounds where the reference's addition does), then rounded to bf16
+__device__ __forceinline__ void chunk_store(const BlkMLX &b, int c, uint32_t q, uint32_t ta) {
+    const __half2 k1024 = h2_const(1024.f);
+    const float s = b.sc[c], bias = b.bi[c];
+    uint32_t o[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w = word_of(b.qs[c], i);
+        // nibbles (0, 4), (1, 5), (2, 6), (3, 7) of the word as exact halves
+        const __half2 a0 = __hsub2(h2_bits((w & 0x000f000fu) | 0x64006400u), k1024);
+        const __half2 a1 = __hsub2(h2_bits(((w >> 4) & 0x000f000fu) | 0x64006400u), k1024);
+        const __half2 a2 = __hsub2(h2_bits(((w >> 8) & 0x000f000fu) | 0x64006400u), k1024);
+        const __half2 a3 = __hsub2(h2_bits(((w >> 12) & 0x000f000fu) | 0x64006400u), k1024);
+        o[4 * i + 0] = pack_bf16x2(__fmaf_rn(s, __low2float(a0), bias), __fmaf_rn(s, __low2float(a1), bias));   // elements 0, 1
+        o[4 * i + 1] = pack_bf16x2(__fmaf_rn(s, __low2float(a2), bias), __fmaf_rn(s, __low2float(a3), bias));   // 2, 3
+        o[4 * i + 2] = pack_bf16x2(__fmaf_rn(s, __high2float(a0), bias), __fmaf_rn(s, __high2float(a1), bias)); // 4, 5
+        o[4 * i + 3] = pack_bf16x2(__fmaf_rn(s, __high2float(a2), bias), __fmaf_rn(s, __high2float(a3), bias)); // 6, 7
+    }
+    const uint32_t lo[8] = {o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]}, hi[8] = {o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]};
+    tmem_st8(ta + 16 * q, lo);     // k 32q .. 32q+15
+    tmem_st8(ta + 16 * q + 8, hi); // k 32q+16 .. 32q+31
+}
+
 // A waiting thread must stay off the warp scheduler: a thread parked in try_wait (or spinning on
 // it) takes issue slots from the dequantization warps of its scheduler, which then finish last and
 // make everyone wait longer.  So waits test the barrier once (test_wait never blocks) and sleep
@@ -306,6 +362,7 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32
 template <int FMT> struct BlkOf;
 template <> struct BlkOf<FMT_Q4K> { using type = BlkQ4K; };
 template <> struct BlkOf<FMT_Q6KR> { using type = BlkQ6KR; };
+template <> struct BlkOf<FMT_MLX4> { using type = BlkMLX; };
 
 // grid (2 * ceil(out / 256), ceil(s / 256)) in clusters of 2 along x, 352 threads
 template <int FMT, bool DBG>
@@ -401,6 +458,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
                 mbar_arrive_expect_tx(&raw_full[st], Cfg::RAW_BYTES);
                 if constexpr (FMT == FMT_Q4K) {
                     tma_load_2d(dst, &maps.w0, (int)(kg * Q4K_BYTES), (int)m0, bar);
+                } else if constexpr (FMT == FMT_MLX4) {
+                    // four table entries per block: 16 bytes of f32, or the aligned 16 bytes around 8 bytes of bf16
+                    const int tx = p.tbl_bytes == 4 ? (int)(kg * 16) : (int)((kg >> 1) * 16);
+                    tma_load_2d(dst, &maps.w0, (int)(kg * 128), (int)m0, bar);
+                    tma_load_2d(dst + GM * 128, &maps.w1, tx, (int)m0, bar);
+                    tma_load_2d(dst + GM * 128 + GM * 16, &maps.w2, tx, (int)m0, bar);
                 } else {
 #pragma unroll
                     for (int r = 0; r < 4; ++r) tma_load_2d(dst + r * Cfg::REC_BYTES, &maps.w0, (int)((kg * 4 + r) * 48), (int)m0, bar);
@@ -502,7 +565,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g_threads(GemmCfg<FM
             ok = warp_wait(&raw_full[st], (kb / RS) & 1, lane);
             if (!ok) break;
             Blk blk;
-            blk_load(blk, smem_u32(raw + st * Cfg::RAW_BYTES), row, part, kb0 + kb);
+            if constexpr (FMT == FMT_MLX4) blk_load_mlx(blk, smem_u32(raw + st * Cfg::RAW_BYTES), row, part, kb0 + kb, p.tbl_bytes);
+            else blk_load(blk, smem_u32(raw + st * Cfg::RAW_BYTES), row, part, kb0 + kb);
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_free[st]); // the block's bytes are in registers: its stage can be refilled
 #pragma unroll
@@ -669,6 +733,14 @@ void gemm_set_trace(void *d_buf) { g_gemm_trace = (long long *)d_buf; }
 void gemm_set_debug_mode(int mode) { g_gemm_mode = (uint32_t)mode; }
 #endif
 
+bool gemm_tc_supported_mlx4(size_t out_dim, size_t in_dim, size_t s, const MlxTables &tb) {
+    if (tb.group != 64 || (tb.elem_bytes != 2 && tb.elem_bytes != 4) || !tb.scales || !tb.biases) return false;
+    if (in_dim % QK_K || in_dim < QK_K || out_dim == 0 || s == 0) return false;
+    if (((in_dim / 64) * tb.elem_bytes) % 16) return false; // table rows are TMA rows: strides in multiples of 16 bytes
+    if (((uintptr_t)tb.scales | (uintptr_t)tb.biases) & 15) return false;
+    return in_dim <= (1u << 24) && out_dim <= (1u << 30) && s <= (1u << 30);
+}
+
 bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s) {
     if (fmt != FMT_Q4K && fmt != FMT_Q6KR) return false;
     if (in_dim % QK_K || in_dim < QK_K || out_dim == 0 || s == 0) return false;
@@ -733,10 +805,16 @@ template <int FMT, bool DBG> static cudaError_t launch_one(const GemmParams &p, 
 // first of these rows' outputs, `ldy` elements between tokens.
 static cudaError_t gemm_part(EncodeTiledFn enc, int fmt, const uint8_t *w, size_t rows, size_t in_dim, size_t s, int z, GemmMaps maps,
                              float *y, const float *res, size_t ldy, int epi, float *part, int *d_status, cudaStream_t st,
-                             const ShardDev *shard) {
+                             const ShardDev *shard, const MlxTables *mlx = nullptr, size_t mlx_row0 = 0) {
     const size_t nb = in_dim / QK_K;
     bool ok = true;
-    if (fmt == FMT_Q4K) {
+    if (fmt == FMT_MLX4) {
+        const size_t rb = in_dim / 2, trb = (in_dim / 64) * mlx->elem_bytes;
+        const uint8_t *sc = (const uint8_t *)mlx->scales + mlx_row0 * trb, *bi = (const uint8_t *)mlx->biases + mlx_row0 * trb;
+        ok = encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, rb, rows, rb, 128, GM, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+             encode_2d(enc, &maps.w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, sc, trb, rows, trb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+             encode_2d(enc, &maps.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, bi, trb, rows, trb, 16, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else if (fmt == FMT_Q4K) {
         const size_t rb = nb * Q4K_BYTES;
         ok = encode_2d(enc, &maps.w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, rb, rows, rb, Q4K_BYTES, GM, CU_TENSOR_MAP_SWIZZLE_NONE);
         maps.w1 = maps.w0, maps.w2 = maps.w0;
@@ -753,6 +831,7 @@ static cudaError_t gemm_part(EncodeTiledFn enc, int fmt, const uint8_t *w, size_
     p.y = gz > 1 ? part : y, p.status = d_status;
     p.epi = gz > 1 ? EPI_STORE : epi, p.res = res, p.ldy = gz > 1 ? (uint32_t)rows : (uint32_t)ldy;
     p.out_dim = (uint32_t)rows, p.in_dim = (uint32_t)in_dim, p.s = (uint32_t)s;
+    p.tbl_bytes = mlx ? (uint32_t)mlx->elem_bytes : 0u;
     // sharded: the launch that produces the final values stores them into every rank's buffer
     ShardDeltas sd{};
     if (shard) {
@@ -768,7 +847,8 @@ static cudaError_t gemm_part(EncodeTiledFn enc, int fmt, const uint8_t *w, size_
     if (p.mode || p.trace) e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, true>(p, maps, grid, st) : launch_one<FMT_Q6KR, true>(p, maps, grid, st);
     else
 #endif
-    e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st);
+    e = fmt == FMT_Q4K ? launch_one<FMT_Q4K, false>(p, maps, grid, st)
+                       : (fmt == FMT_MLX4 ? launch_one<FMT_MLX4, false>(p, maps, grid, st) : launch_one<FMT_Q6KR, false>(p, maps, grid, st));
     if (e != cudaSuccess || gz == 1) return e;
     const size_t ny = s * rows;
     splitk_reduce_kernel<<<(unsigned)((ny / 4 + 255) / 256 + 1), 256, 0, st>>>(part, y, s, rows, ldy, (int)gz, epi, res, sd);
@@ -779,15 +859,16 @@ static cudaError_t gemm_part(EncodeTiledFn enc, int fmt, const uint8_t *w, size_
 // d_y f32 [s, out], d_xb16: scratch of gemm_tc_scratch_bytes (256-byte aligned).
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_xb16, size_t out_dim, size_t in_dim,
                            size_t s, int sm_count, int *d_status, cudaStream_t st, int epi, const float *d_res, size_t ldy,
-                           const ShardDev *shard) {
+                           const ShardDev *shard, const MlxTables *mlx) {
     if (ldy == 0) ldy = out_dim;
     if (shard && (epi != EPI_STORE || shard->world < 1 || shard->world > SHARD_MAX_RANKS)) return cudaErrorInvalidValue;
     if (epi == EPI_SWIGLU && (out_dim & 1)) return cudaErrorInvalidValue;
     if (epi == EPI_RESIDUAL && !d_res) return cudaErrorInvalidValue;
-    if (!gemm_tc_supported(fmt, out_dim, in_dim, s) || ((uintptr_t)d_w & 15)) return cudaErrorNotSupported;
+    const bool supported = fmt == FMT_MLX4 ? (mlx && gemm_tc_supported_mlx4(out_dim, in_dim, s, *mlx)) : gemm_tc_supported(fmt, out_dim, in_dim, s);
+    if (!supported || ((uintptr_t)d_w & 15)) return cudaErrorNotSupported;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
-    const size_t n = s * in_dim, row_bytes = in_dim / QK_K * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    const size_t n = s * in_dim, row_bytes = fmt == FMT_MLX4 ? in_dim / 2 : in_dim / QK_K * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
     cast_bf16_kernel<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, st>>>(d_x, (__nv_bfloat16 *)d_xb16, n);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -798,10 +879,10 @@ cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_
     const GemmPlan pl = gemm_plan(out_dim, in_dim, s, sm_count);
     const uint8_t *w = (const uint8_t *)d_w;
     const size_t ydiv = epi == EPI_SWIGLU ? 2 : 1; // SwiGLU halves the output rows
-    e = gemm_part(enc, fmt, w, pl.rows_main, in_dim, s, pl.z_main, maps, d_y, d_res, ldy, epi, part, d_status, st, shard);
+    e = gemm_part(enc, fmt, w, pl.rows_main, in_dim, s, pl.z_main, maps, d_y, d_res, ldy, epi, part, d_status, st, shard, mlx, 0);
     if (e != cudaSuccess || pl.rows_tail == 0) return e;
     return gemm_part(enc, fmt, w + pl.rows_main * row_bytes, pl.rows_tail, in_dim, s, pl.z_tail, maps, d_y + pl.rows_main / ydiv,
-                     d_res ? d_res + pl.rows_main : nullptr, ldy, epi, part, d_status, st, shard);
+                     d_res ? d_res + pl.rows_main : nullptr, ldy, epi, part, d_status, st, shard, mlx, pl.rows_main);
 }
 
 } // namespace ullm

@@ -112,15 +112,16 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
 // prepare.cu — Q6_K rows <-> the prepared layout (FMT_Q6KR)
 bool q6k_can_prepare(size_t in_dim);
 cudaError_t launch_q6k_prepare(const void *d_src, void *d_dst, size_t rows, size_t in_dim, bool inverse, cudaStream_t st);
-// gemm.cu — tcgen05 / TMEM prefill GEMM on Q4_K (verbatim) or prepared Q6_K rows.
+// gemm.cu — tcgen05 / TMEM prefill GEMM on Q4_K (verbatim) rows, prepared Q6_K rows, or MLX 4-bit words (fmt FMT_MLX4 with `mlx`).
 bool gemm_tc_supported(int fmt, size_t out_dim, size_t in_dim, size_t s);
+bool gemm_tc_supported_mlx4(size_t out_dim, size_t in_dim, size_t s, const MlxTables &tb); // MLX 4-bit words, group 64, 16-byte aligned tables
 size_t gemm_tc_scratch_bytes(size_t out_dim, size_t in_dim, size_t s, int sm_count); // bf16 activations + split-K partial sums
 // epi / d_res: the matvec's epilogues on the [s, out] result (EPI_SWIGLU writes [s, out / 2]; d_res may alias d_y)
 // ldy: elements between two tokens in d_y / d_res (0 = out_dim).  `shard` (optional, EPI_STORE only): every output element is
 // stored into all ranks' gather buffers (d_y points into this rank's); the caller publishes afterwards (launch_shard_signal).
 cudaError_t launch_gemm_tc(int fmt, const void *d_w, const float *d_x, float *d_y, void *d_scratch, size_t out_dim, size_t in_dim,
                            size_t s, int sm_count, int *d_status, cudaStream_t st, int epi = EPI_STORE, const float *d_res = nullptr,
-                           size_t ldy = 0, const ShardDev *shard = nullptr);
+                           size_t ldy = 0, const ShardDev *shard = nullptr, const MlxTables *mlx = nullptr);
 bool matvec_is_streamed(const DeviceInfo &dev, int fmt, size_t out_dim, size_t in_dim, size_t group, int tbl_bytes,
                         int epi);
 // Returns a static message when the shape cannot be computed at all.
