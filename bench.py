@@ -581,10 +581,28 @@ def run_c4(args):
         cpu = None
         if not args.no_cpu:
             cpu = cpu_leg(check, [m["y"].cpu().numpy() for m in mats])
+        fp32_path = None
         if not args.no_secondary:
             secondary = {}
             for name, fn in (("c4gemm", lambda: sec_c4gemm(torch, backend, ctx, dev, args, mats)),):
                 secondary[name] = fn()
+            # The same step through the plain fp32-FMA kernel (one warp per row, f32 x, no fixed-point image): what the
+            # integer formulation buys.  Test knobs select it (raw Q6_K rows, generic kernel); nothing timed above uses them.
+            ctx.debug_set("no_prepare", 1)
+            plain = [backend.Weight(ctx, m["dt"], m["host"], m["out"], m["cols"]) for m in mats]
+            ctx.debug_set("no_prepare", 0)
+            ctx.debug_set("force_generic", 1)
+
+            def fstep(_i, st):
+                for w_, m in zip(plain, mats):
+                    w_.matvec_dev(m["x"].data_ptr(), m["y"].data_ptr(), st)
+
+            fsp = spread(time_graph(torch, fstep, 4, 3, 3), 4)
+            ctx.debug_set("force_generic", 0)
+            ferr = max(synth.rel_err(m["y"].cpu().numpy()[m["out"] - 64:], oracle_rows(m["dt"], m["host"], m["cols"], m["out"] - 64, 64, m["xh"])) for m in mats)
+            fp32_path = {"gbs": total_bytes / (fsp["median"] * 1e-3) / 1e9, "us_per_step": fsp["median"] * 1e3, "rel_err_vs_cpu": ferr}
+            for w_ in plain:
+                w_.free()
             for m in mats:
                 m["w"].free()
             torch.cuda.empty_cache()
@@ -709,6 +727,8 @@ def run_c4(args):
 
     sp = spread(ms, args.steps)
     step_ms = sp["median"]
+    if world > 1:
+        fp32_path = None
     if rank == 0:
         value = total_bytes / (step_ms * 1e-3) / 1e9
         per_rank = value / world
@@ -730,6 +750,9 @@ def run_c4(args):
             "clocks": clocks,
             "check": check,
         }
+        if fp32_path is not None:
+            line["roofline"]["fp32_path_gbs"] = fp32_path["gbs"]
+            line["roofline"]["fp32_path"] = fp32_path
         if secondary is not None:
             line["secondary"] = secondary
         print(json.dumps(line), flush=True)

@@ -153,9 +153,13 @@ def test_matmul_mlx4_tensor_core_path(ctx, out_dim, in_dim, s):
     check(got, *want, in_dim=in_dim)
     wo = backend.Weight(ctx, backend.MLX_U32, w, out_dim, in_dim, sc, bi, gs)  # bf16 tables as stored on disk
     got2 = wo.matmul(xs, s)
-    assert ctx.last_plan()["grid"] == -1
-    check(got2, *want, in_dim=in_dim)
-    assert np.array_equal(got, got2)  # the same values whichever width the tables are kept in
+    if (in_dim // gs * 2) % 16 == 0:  # bf16 table rows are TMA rows only when their length is a multiple of 16 bytes
+        assert ctx.last_plan()["grid"] == -1
+        check(got2, *want, in_dim=in_dim)
+        assert np.array_equal(got, got2)  # the same values whichever width the tables are kept in
+    else:  # per-token matvecs: the f32 bar
+        assert ctx.last_plan()["grid"] != -1
+        assert synth.rel_err(got2, want[0]) < 1e-3
     wo.free()
 
 

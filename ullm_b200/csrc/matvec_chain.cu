@@ -360,19 +360,34 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     bool dealt = n > 1 && (uint32_t)n <= grid;
     for (int i = 0; i < n; ++i) dealt = dealt && !ops[i].dep;
     if (dealt) {
-        double cost[CHAIN_MAX_OPS], total = 0, frac[CHAIN_MAX_OPS];
+        // Model of an op's time with m CTAs: fixed_i + work_i / m, where work_i is its weight bytes at the rate a CTA
+        // streams them (prepared Q6_K rows weigh g_q6k_cost: more instructions per byte; measured rates on B200) and
+        // fixed_i is what every CTA of the op spends before its first tile: reading and converting the op's whole
+        // input vector.  The launch ends when the slowest group does, so the CTAs are dealt out such that all groups
+        // end together: find T with sum_i work_i / (T - fixed_i) = grid, then round (largest remainders, at least one
+        // CTA per op).
+        double work[CHAIN_MAX_OPS], fixed[CHAIN_MAX_OPS], share[CHAIN_MAX_OPS], frac[CHAIN_MAX_OPS];
+        double lo = 0, hi = 0;
         for (int i = 0; i < n; ++i) {
             const double rb = (double)(ops[i].in_dim / QK_K) * (ops[i].fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
-            // the fixed part stands for reading and converting the op's input vector, which every CTA of the op does
-            // (prepared Q6_K rows cost more instructions per byte than Q4_K rows: measured rates on B200)
-            cost[i] = (double)ops[i].out_dim * rb * (ops[i].fmt == FMT_Q4K ? 1.0 : g_q6k_cost) + 3.0 * (double)ops[i].in_dim * 4.0;
-            total += cost[i];
+            work[i] = (double)ops[i].out_dim * rb * (ops[i].fmt == FMT_Q4K ? 1.0 : g_q6k_cost) / 33000.0; // us of one CTA
+            fixed[i] = 0.5 + (double)ops[i].in_dim * 7.0e-5;                                             // us
+            lo = std::max(lo, fixed[i]);
+            hi = std::max(hi, fixed[i] + work[i]);
+        }
+        hi += 1.0;
+        for (int it = 0; it < 60; ++it) {
+            const double T = 0.5 * (lo + hi);
+            double need = 0;
+            for (int i = 0; i < n; ++i) need += work[i] / (T - fixed[i]);
+            if (need > grid) lo = T;
+            else hi = T;
         }
         uint32_t used = 0;
         for (int i = 0; i < n; ++i) {
-            const double share = cost[i] / total * grid;
-            ncta[i] = std::max<uint32_t>(1, (uint32_t)share);
-            frac[i] = share - (double)(uint32_t)share;
+            share[i] = work[i] / (hi - fixed[i]);
+            ncta[i] = std::max<uint32_t>(1, (uint32_t)share[i]);
+            frac[i] = share[i] - (double)(uint32_t)share[i];
             used += ncta[i];
         }
         while (used < grid) { // hand the remaining CTAs to the largest remainders
@@ -383,7 +398,7 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
             bool any = false;
             for (int i = 0; i < n; ++i) any = any || frac[i] >= 0.0;
             if (!any)
-                for (int i = 0; i < n; ++i) frac[i] = cost[i] / total;
+                for (int i = 0; i < n; ++i) frac[i] = share[i] / grid;
         }
         while (used > grid) { // the minimum of one CTA per op overshot: take from the largest groups
             int best = 0;
