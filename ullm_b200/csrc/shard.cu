@@ -11,6 +11,7 @@
 // comparison arm (libnccl loaded at run time).
 #include "../../include/ullm_cuda.h"
 #include "engine.h"
+#include "host_copy.cuh"
 #include "shard_dev.cuh"
 
 #include <dlfcn.h>
@@ -444,12 +445,37 @@ int ullm_cuda_shard_matvec(ullm_cuda_shard *s, size_t n, const ullm_shard_op *op
     ullm_cuda_ctx *c = s->ctx;
     if (y_offset > s->y_floats || y_count > s->y_floats - y_offset) return ctx_fail(c, ULLM_ERR_FORMAT, "result range outside the gather buffer");
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
-    for (size_t i = 0; i < n && x_host; ++i)
-        if (x_host[i] && ops[i].w && ops[i].d_x)
-            ULLM_CUDA_TRY(c, cudaMemcpyAsync((void *)ops[i].d_x, x_host[i], ops[i].w->cols * 4, cudaMemcpyHostToDevice, c->stream));
+    // page-locked host vectors move in one small kernel per direction (no copy-engine hand-over); others by cudaMemcpyAsync
+    if (x_host) {
+        VecCopyList l{};
+        int m = 0;
+        bool mapped = !c->no_host_kernels;
+        for (size_t i = 0; i < n && mapped; ++i) {
+            if (!x_host[i] || !ops[i].w || !ops[i].d_x) continue;
+            const float *v = device_view_of_host(x_host[i]);
+            if (!v || m == VEC_COPY_MAX) mapped = false;
+            else l.src[m] = v, l.dst[m] = (float *)ops[i].d_x, l.n[m] = (unsigned)ops[i].w->cols, ++m;
+        }
+        if (mapped && m) {
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream));
+        } else if (!mapped) {
+            for (size_t i = 0; i < n; ++i)
+                if (x_host[i] && ops[i].w && ops[i].d_x)
+                    ULLM_CUDA_TRY(c, cudaMemcpyAsync((void *)ops[i].d_x, x_host[i], ops[i].w->cols * 4, cudaMemcpyHostToDevice, c->stream));
+        }
+    }
     int rc = ullm_cuda_shard_matvec_dev(s, n, ops, 0, nullptr);
     if (rc) return rc;
-    if (y_count) ULLM_CUDA_TRY(c, cudaMemcpyAsync(y_host, shard_y(s) + y_offset, y_count * 4, cudaMemcpyDeviceToHost, c->stream));
+    if (y_count) {
+        float *yv = c->no_host_kernels ? nullptr : (float *)device_view_of_host(y_host);
+        if (yv && y_count <= 0xffffffffull) {
+            VecCopyList l{};
+            l.src[0] = shard_y(s) + y_offset, l.dst[0] = yv, l.n[0] = (unsigned)y_count;
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, 1, c->stream));
+        } else {
+            ULLM_CUDA_TRY(c, cudaMemcpyAsync(y_host, shard_y(s) + y_offset, y_count * 4, cudaMemcpyDeviceToHost, c->stream));
+        }
+    }
     ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     return ctx_check_status(c);
 }
