@@ -444,6 +444,8 @@ def run_aux(args):
     dev = torch.device("cuda:0")
     ctx = backend.CudaContext(0)
     ctx.set_option(backend.OPT_PDL, 1 if args.pdl else 0)
+    for kv in args.knob:
+        ctx.debug_set(kv.split("=")[0], int(kv.split("=")[1]))
     peak, _ = measured_peak_gbs()
     if args.workload == "c4gemm":
         mats = [m for m in c4_weights(backend, ctx) if not args.only or m["name"] == args.only]
@@ -720,9 +722,7 @@ def run_c4(args):
         else:
             launch, kernel = "one CUDA graph of the K timed steps, replayed; one persistent launch per step", "matvec_chain_kernel (peer-store epilogue, step flags)"
             parallelism = f"rows/{world} per matrix; every rank's kernel stores its rows into all ranks' result vectors over NVLink, a published step number replaces the all-gather"
-        cpu = None
-        if rank == 0 and not args.no_cpu:
-            cpu = cpu_leg({}, None)
+        cpu = None  # the CPU baseline is an N = 1 figure: one process then has the host's cores to itself
         barrier()
 
     sp = spread(ms, args.steps)

@@ -139,8 +139,10 @@ struct StreamParams {
     uint32_t ncg;
     uint32_t off_part, off_prep, off_ring; // byte offsets in dynamic smem
     int pdl;                   // launched with programmatic stream serialization
+    uint32_t chunk;            // bytes per bulk copy (multiple of 16)
 };
-constexpr uint32_t STREAM_CHUNK = 4096; // bytes per bulk copy (multiple of 16)
+static int g_stream_chunk = 4096;
+void matvec_stream_set_chunk(int bytes) { g_stream_chunk = bytes >= 1024 ? bytes / 16 * 16 : 4096; }
 
 constexpr int STREAM_MAX_THREADS = 800; // 24 consumer warps + the producer warp
 
@@ -218,8 +220,8 @@ __global__ void __launch_bounds__(STREAM_MAX_THREADS, 1) matvec_stream_kernel(co
                 __syncwarp();
                 const uint8_t *src = p.w + (size_t)(r0 + row0) * p.row_bytes;
                 uint8_t *d = dst + (size_t)row0 * p.row_bytes;
-                for (uint32_t off = lane * STREAM_CHUNK; off < wb; off += 32 * STREAM_CHUNK)
-                    bulk_g2s(d + off, src + off, min(STREAM_CHUNK, wb - off), fb);
+                for (uint32_t off = lane * p.chunk; off < wb; off += 32 * p.chunk)
+                    bulk_g2s(d + off, src + off, min(p.chunk, wb - off), fb);
                 if (FMT == FMT_MLX4 && lane < 2 && tb) {
                     const uint8_t *t = (lane ? p.biases : p.scales) + (size_t)(r0 + row0) * p.tbl_row_bytes;
                     bulk_g2s(dst + p.w_stage_bytes + lane * p.tbl_stage_bytes + (size_t)row0 * p.tbl_row_bytes, t, tb, fb);
@@ -535,6 +537,7 @@ cudaError_t launch_matvec(const DeviceInfo &dev, int fmt, const void *d_w, const
         pl.p.x = d_x, pl.p.y = d_y, pl.p.status = d_status;
         pl.p.norm_w = o.norm_w, pl.p.eps = o.eps, pl.p.epi = o.epi, pl.p.res = o.res;
         pl.p.pdl = o.pdl ? 1 : 0;
+        pl.p.chunk = (uint32_t)g_stream_chunk;
         if (fmt == FMT_Q4K) return launch_stream_f<FMT_Q4K, float>(pl, st, o.pdl);
         if (fmt == FMT_Q6K) return launch_stream_f<FMT_Q6K, float>(pl, st, o.pdl);
         if (fmt == FMT_Q6KR) return launch_stream_f<FMT_Q6KR, float>(pl, st, o.pdl);

@@ -36,7 +36,11 @@ constexpr int CHAIN_MAX_STAGES = 8;
 // 2 / 4 / 8 tiles ahead): the prefetches compete with the ring's own copies for DRAM and do not come back as hits.
 static int g_pf_tiles = 0;
 void matvec_chain_set_prefetch(int v) { g_pf_tiles = v < 0 ? 0 : v; }
-static double g_q6k_cost = 1.3; // relative cost per byte of prepared Q6_K rows when CTAs are dealt out to ops
+// Bytes per bulk copy of the producer warp (a tile is copied as pieces of this size, one per lane and round).
+// 16 KB: the 70B block measured 127.5 / 111.4 / 107.5 / 107.0 / 106.9 / 106.8 us per step at 2 / 4 / 8 / 16 / 32 / 128 KB.
+static int g_chain_chunk = 16384;
+void matvec_chain_set_chunk(int bytes) { g_chain_chunk = bytes >= 1024 ? bytes / 16 * 16 : 16384; }
+static double g_q6k_cost = 1.4; // relative cost per byte of prepared Q6_K rows when CTAs are dealt out to ops
 void matvec_chain_set_q6k_cost(double v) { g_q6k_cost = v; }
 
 struct ChainOpDev {
@@ -226,6 +230,10 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
 
 constexpr int CHAIN_MAX_THREADS = 21 * 32; // 20 consumer warps + the producer warp
 
+// 20 consumer warps at 80 registers.  Measured against it on the 70B block (B200, us per step): 28 warps at 64
+// registers, which would keep every warp busy on rows of 14 column groups (28,672 columns; 14 of 20 warps work
+// there), 135-156 instead of 107: a row slice then has to drop to one or two rows per warp, and that costs more
+// than the idle warps; tiles capped at 56 KB (two rows per warp, four stages) 139.
 __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(const __grid_constant__ ChainParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = (uint64_t *)smem, *empty = full + CHAIN_MAX_STAGES;
@@ -351,60 +359,38 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
             if (ops[i].epi != EPI_STORE) return cudaErrorNotSupported; // fused epilogues stay on one GPU
         p.sh = *shard;
     }
-    p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 20, p.chunk = 4096, p.pf_tiles = (uint32_t)g_pf_tiles;
+    p.n_ops = n, p.sync = d_sync, p.status = d_status, p.NW = 20, p.chunk = (uint32_t)g_chain_chunk, p.pf_tiles = (uint32_t)g_pf_tiles;
     const int budget = dev.max_smem_optin - 1024;
     const uint32_t grid = (uint32_t)dev.sm_count;
-    // Independent ops: the CTAs are dealt out to the ops in proportion to their weight bytes (largest
-    // remainders first, at least one CTA each, never more CTAs than the op has row units).
+    // Independent ops: the CTAs are dealt out to the ops (at least one CTA each, never more CTAs than the op has
+    // pairs of rows), so that every group of CTAs is expected to finish at the same time.
     uint32_t cta0[CHAIN_MAX_OPS], ncta[CHAIN_MAX_OPS];
     bool dealt = n > 1 && (uint32_t)n <= grid;
     for (int i = 0; i < n; ++i) dealt = dealt && !ops[i].dep;
     if (dealt) {
         // Model of an op's time with m CTAs: fixed_i + work_i / m, where work_i is its weight bytes at the rate a CTA
-        // streams them (prepared Q6_K rows weigh g_q6k_cost: more instructions per byte; measured rates on B200) and
+        // streams them (prepared Q6_K rows weigh g_q6k_cost: on the 28,672-column matrix 14 of the 20 warps work; the 70B block measured 129.5 / 121.7 / 117.7 / 111.7 / 107.0 / 108.7 / 121.7 us per step at 1.0 / 1.1 / 1.2 / 1.3 / 1.4 / 1.5 / 1.7) and
         // fixed_i is what every CTA of the op spends before its first tile: reading and converting the op's whole
-        // input vector.  The launch ends when the slowest group does, so the CTAs are dealt out such that all groups
-        // end together: find T with sum_i work_i / (T - fixed_i) = grid, then round (largest remainders, at least one
-        // CTA per op).
-        double work[CHAIN_MAX_OPS], fixed[CHAIN_MAX_OPS], share[CHAIN_MAX_OPS], frac[CHAIN_MAX_OPS];
-        double lo = 0, hi = 0;
+        // input vector.  The launch ends when the slowest group does, so the CTAs are dealt out to minimise the
+        // largest group time: one CTA each, then every further CTA to the group that is slowest at that moment
+        // (optimal for this model; rounding shares to the nearest count instead left the 1024-row matrices of the
+        // 70B block with one CTA each, and those two CTAs then set the time of the whole step).
+        double work[CHAIN_MAX_OPS], fixed[CHAIN_MAX_OPS];
         for (int i = 0; i < n; ++i) {
             const double rb = (double)(ops[i].in_dim / QK_K) * (ops[i].fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
             work[i] = (double)ops[i].out_dim * rb * (ops[i].fmt == FMT_Q4K ? 1.0 : g_q6k_cost) / 33000.0; // us of one CTA
             fixed[i] = 0.5 + (double)ops[i].in_dim * 7.0e-5;                                             // us
-            lo = std::max(lo, fixed[i]);
-            hi = std::max(hi, fixed[i] + work[i]);
+            ncta[i] = 1;
         }
-        hi += 1.0;
-        for (int it = 0; it < 60; ++it) {
-            const double T = 0.5 * (lo + hi);
-            double need = 0;
-            for (int i = 0; i < n; ++i) need += work[i] / (T - fixed[i]);
-            if (need > grid) lo = T;
-            else hi = T;
-        }
-        uint32_t used = 0;
-        for (int i = 0; i < n; ++i) {
-            share[i] = work[i] / (hi - fixed[i]);
-            ncta[i] = std::max<uint32_t>(1, (uint32_t)share[i]);
-            frac[i] = share[i] - (double)(uint32_t)share[i];
-            used += ncta[i];
-        }
-        while (used < grid) { // hand the remaining CTAs to the largest remainders
-            int best = 0;
-            for (int i = 1; i < n; ++i)
-                if (frac[i] > frac[best]) best = i;
-            ++ncta[best], frac[best] = -1.0, ++used;
-            bool any = false;
-            for (int i = 0; i < n; ++i) any = any || frac[i] >= 0.0;
-            if (!any)
-                for (int i = 0; i < n; ++i) frac[i] = share[i] / grid;
-        }
-        while (used > grid) { // the minimum of one CTA per op overshot: take from the largest groups
-            int best = 0;
-            for (int i = 1; i < n; ++i)
-                if (ncta[i] > ncta[best]) best = i;
-            --ncta[best], --used;
+        for (uint32_t used = (uint32_t)n; used < grid; ++used) {
+            int slow = 0;
+            double worst = -1.0;
+            for (int i = 0; i < n; ++i) {
+                const uint32_t units = std::max<uint32_t>(1, (uint32_t)(ops[i].out_dim / 2)); // no more CTAs than pairs of rows
+                const double t = ncta[i] >= units ? -1.0 : fixed[i] + work[i] / ncta[i];
+                if (t > worst) worst = t, slow = i;
+            }
+            ++ncta[slow];
         }
         uint32_t at = 0;
         for (int i = 0; i < n; ++i) cta0[i] = at, at += ncta[i];
