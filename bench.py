@@ -450,6 +450,8 @@ def run_aux(args):
     if args.workload == "c4gemm":
         mats = [m for m in c4_weights(backend, ctx) if not args.only or m["name"] == args.only]
         out = sec_c4gemm(torch, backend, ctx, dev, args, mats)
+    elif args.workload == "readprobe":
+        out = read_only_ceiling(ctx, c4_step_bytes())
     else:
         fn = {"c0": sec_c0, "c1": sec_c1, "c2": sec_c2, "c3": sec_c3, "c2decode": aux_c2decode, "c3prefill": aux_c3prefill}[args.workload]
         out = fn(torch, backend, ctx, dev, args, peak)
@@ -583,7 +585,7 @@ def run_c4(args):
         cpu = None
         if not args.no_cpu:
             cpu = cpu_leg(check, [m["y"].cpu().numpy() for m in mats])
-        fp32_path = None
+        fp32_path = read_ceiling = None
         if not args.no_secondary:
             secondary = {}
             for name, fn in (("c4gemm", lambda: sec_c4gemm(torch, backend, ctx, dev, args, mats)),):
@@ -608,6 +610,7 @@ def run_c4(args):
             for m in mats:
                 m["w"].free()
             torch.cuda.empty_cache()
+            read_ceiling = read_only_ceiling(ctx, total_bytes)
             for name, fn in (("c1", sec_c1), ("c0", sec_c0), ("c2", sec_c2), ("c3", sec_c3)):
                 secondary[name] = fn(torch, backend, ctx, dev, args, peak)
     else:
@@ -728,7 +731,7 @@ def run_c4(args):
     sp = spread(ms, args.steps)
     step_ms = sp["median"]
     if world > 1:
-        fp32_path = None
+        fp32_path = read_ceiling = None
     if rank == 0:
         value = total_bytes / (step_ms * 1e-3) / 1e9
         per_rank = value / world
@@ -753,12 +756,26 @@ def run_c4(args):
         if fp32_path is not None:
             line["roofline"]["fp32_path_gbs"] = fp32_path["gbs"]
             line["roofline"]["fp32_path"] = fp32_path
+        if read_ceiling is not None:
+            line["roofline"]["read_only_ceiling"] = read_ceiling
         if secondary is not None:
             line["secondary"] = secondary
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
     return 0
+
+
+def read_only_ceiling(ctx, nbytes):
+    """What a kernel that only READS `nbytes` (one launch, L2 flushed before it) reaches on this GPU: plain
+    16-byte loads, and a bulk-copy ring with nothing consuming it (the streaming side of the matvec kernels
+    alone, two stages of 92 KB as the Q4_K matrices use).  `peak` in the roofline stays the copy bandwidth;
+    these two rates say how much of the gap to it a pure reader can close at all."""
+    nbytes = nbytes // (1 << 20) * (1 << 20)
+    ld = ctx.read_probe(0, nbytes)
+    ring = ctx.read_probe(1, nbytes, 94208, 2, 16384)
+    return {"bytes": nbytes, "plain_loads_gbs": ld["gbs"], "plain_loads_us": ld["us"], "bulk_copy_ring_gbs": ring["gbs"], "bulk_copy_ring_us": ring["us"],
+            "note": "one launch over the same number of bytes as a step, 256 MB written before each launch; median of 8"}
 
 
 def cpu_leg(check, gpu_outputs):
@@ -945,7 +962,7 @@ def main():
     ap.add_argument("--launch", default="auto", choices=["auto", "separate"],
                     help="N = 1: the batch call (one persistent launch for the seven matrices) or seven launches per step")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: fused peer stores (default) or the NCCL all-gather comparison arm")
-    ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm", "c0", "c1", "c2", "c3", "c2decode", "c3prefill"],
+    ap.add_argument("--workload", default="c4", choices=["c4", "c4gemm", "c0", "c1", "c2", "c3", "c2decode", "c3prefill", "readprobe"],
                     help="c4 is the benchmark.  N > 1: c4gemm runs the block as a sharded prefill GEMM.  N = 1: any other choice runs that "
                          "configuration alone and prints its figures (what `secondary` holds, plus the MoE decode step and the batched prefill)")
     ap.add_argument("--layers", type=int, default=0, help="c2decode: number of layers (default: the model's 48)")

@@ -125,6 +125,7 @@ SIGNATURES = {
 DEBUG_SIGNATURES = {
     "ullm_cuda_debug_set": (_i, [_vp, C.c_char_p, _i]),
     "ullm_cuda_debug_last_plan": (_i, [_vp, _vp, _i]),
+    "ullm_cuda_debug_read_probe": (_i, [_vp, _i, _sz, _i, _i, _i, _i, _vp]),
 }
 
 
@@ -305,6 +306,13 @@ class CudaContext:
     # -- knobs used by tests --------------------------------------------------
     def debug_set(self, key: str, value: int):
         self._check(self._lib.ullm_cuda_debug_set(self._h, key.encode(), value))
+
+    def read_probe(self, mode: int, nbytes: int, stage_bytes: int = 94208, stages: int = 2, chunk: int = 16384, reps: int = 8) -> dict:
+        """Read-only bandwidth of this GPU over ``nbytes``: ``mode`` 0 = plain 16-byte loads, 1 = a bulk-copy ring
+        without a consumer (the streaming side of the matvec kernels alone).  Median / min / max microseconds."""
+        us = (C.c_float * 3)()
+        self._check(self._lib.ullm_cuda_debug_read_probe(self._h, mode, nbytes, stage_bytes, stages, chunk, reps, us))
+        return {"us": us[0], "us_min": us[1], "us_max": us[2], "gbs": nbytes / (us[0] * 1e-6) / 1e9}
 
     def last_plan(self) -> dict:
         v = (C.c_int * 6)()
