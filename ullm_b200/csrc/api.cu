@@ -715,6 +715,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     else if (!strcmp(key, "q6k_cost_permille")) matvec_chain_set_q6k_cost(value / 1000.0);
     else if (!strcmp(key, "chain_prefetch_tiles")) matvec_chain_set_prefetch(value);
     else if (!strcmp(key, "chain_chunk")) matvec_chain_set_chunk(value);
+    else if (!strcmp(key, "chain_overlap_image")) matvec_chain_set_overlap(value);
     else if (!strcmp(key, "stream_chunk")) matvec_stream_set_chunk(value);
     else if (!strcmp(key, "no_host_kernels")) c->no_host_kernels = value != 0;
     else if (!strcmp(key, "plan_wr")) c->plan_wr = value;

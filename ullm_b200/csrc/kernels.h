@@ -107,6 +107,7 @@ bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi);
 void matvec_chain_set_q6k_cost(double v);
 void matvec_chain_set_prefetch(int tiles);
 void matvec_chain_set_chunk(int bytes);
+void matvec_chain_set_overlap(int on);
 void matvec_stream_set_chunk(int bytes);
 // `shard` (optional): every op stores its rows into all ranks' gather buffers and the launch publishes the exchange.
 cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainOp *ops, unsigned *d_sync, int *d_status,

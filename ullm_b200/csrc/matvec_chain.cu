@@ -38,9 +38,11 @@ static int g_pf_tiles = 0;
 void matvec_chain_set_prefetch(int v) { g_pf_tiles = v < 0 ? 0 : v; }
 // Bytes per bulk copy of the producer warp (a tile is copied as pieces of this size, one per lane and round).
 // 16 KB: the 70B block measured 127.5 / 111.4 / 107.5 / 107.0 / 106.9 / 106.8 us per step at 2 / 4 / 8 / 16 / 32 / 128 KB.
+static int g_overlap_image = 1;
+void matvec_chain_set_overlap(int v) { g_overlap_image = v; }
 static int g_chain_chunk = 16384;
 void matvec_chain_set_chunk(int bytes) { g_chain_chunk = bytes >= 1024 ? bytes / 16 * 16 : 16384; }
-static double g_q6k_cost = 1.4; // relative cost per byte of prepared Q6_K rows when CTAs are dealt out to ops
+static double g_q6k_cost = 1.05; // relative cost per byte of prepared Q6_K rows when CTAs are dealt out to ops
 void matvec_chain_set_q6k_cost(double v) { g_q6k_cost = v; }
 
 struct ChainOpDev {
@@ -58,6 +60,9 @@ struct ChainOpDev {
     // shared-memory layout while this op runs: the same for every op when all CTAs walk the whole list (the ring
     // then runs on across ops), the op's own when the CTAs are dealt out (a CTA then sees one op only)
     uint32_t S, stage_bytes, off_part, off_prep, off_ring;
+    // Dealt CTAs only: ring stages from this one on lie over the activation image (which is dead once the consumers
+    // hold it in registers); the producer fills them for the first time after the consumers have said so.  S: none.
+    uint32_t late_stage;
 };
 struct ChainParams {
     ChainOpDev op[CHAIN_MAX_OPS];
@@ -160,6 +165,11 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
         for (int k = 0; k < XR; ++k) X[g][k] = live[g] ? prep[((size_t)cg * XR + k) * 32 + lane] : 0u;
     }
     const uint32_t nb = o.in_dim / QK_K;
+    if (o.late_stage < o.S) { // the image may be overwritten by weight tiles from here on
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic accesses to the image before the bulk copies over it
+        __syncwarp();
+        if (lane == 0) mbar_arrive((uint64_t *)(smem + 136));
+    }
 
     // sums the column-group partials of tile kt (see matvec.cu); slot = kt mod 2S names its partial area
     auto flush = [&](uint32_t kt, uint32_t slot) {
@@ -246,6 +256,7 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], p.NW);
         }
+        mbar_init((uint64_t *)(smem + 136), p.NW); // "activation image is in registers" (see ChainOpDev::late_stage)
         sync_ok = 1;
         mbar_fence_init();
     }
@@ -274,6 +285,7 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
                 if (p.pf_tiles) prefetch_tile(k + o.S + p.pf_tiles);
                 bool ok = true;
                 if (lane == 0 && kg >= o.S) ok = wait_or_timeout(&empty[s], ph ^ 1u);
+                else if (lane == 0 && s >= o.late_stage) ok = wait_or_timeout((uint64_t *)(smem + 136), 0);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     if (lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
@@ -369,7 +381,7 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     for (int i = 0; i < n; ++i) dealt = dealt && !ops[i].dep;
     if (dealt) {
         // Model of an op's time with m CTAs: fixed_i + work_i / m, where work_i is its weight bytes at the rate a CTA
-        // streams them (prepared Q6_K rows weigh g_q6k_cost: on the 28,672-column matrix 14 of the 20 warps work; the 70B block measured 129.5 / 121.7 / 117.7 / 111.7 / 107.0 / 108.7 / 121.7 us per step at 1.0 / 1.1 / 1.2 / 1.3 / 1.4 / 1.5 / 1.7) and
+        // streams them (prepared Q6_K rows weigh g_q6k_cost: on the 28,672-column matrix 14 of the 20 warps work; the 70B block measured 111.7 / 107.0 / 108.7 us per step at 1.3 / 1.4 / 1.5, and 129.5 / 121.7 at 1.0 / 1.7 with 4 KB copies) and
         // fixed_i is what every CTA of the op spends before its first tile: reading and converting the op's whole
         // input vector.  The launch ends when the slowest group does, so the CTAs are dealt out to minimise the
         // largest group time: one CTA each, then every further CTA to the group that is slowest at that moment
@@ -439,19 +451,31 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         for (int i = 0; i < n; ++i) {
             ChainOpDev &o = p.op[i];
             bool fits = false;
-            for (uint32_t tile_cap : {100u * 1024u, 56u * 1024u}) {
-                if (!pick_rows(o, tile_cap)) continue;
+            // 1: large tiles beside the image; 2: large tiles, the last stages laid over the image (the consumers hold
+            // it in registers by the time the ring needs them: the 66 KB image of a 28,672-column vector otherwise
+            // forces tiles of two rows); 3: small tiles beside the image
+            for (int form = 1; form <= 3 && !fits; ++form) {
+                if (form == 2 && !g_overlap_image) continue;
+                if (!pick_rows(o, form == 3 ? 56u * 1024u : 100u * 1024u)) continue;
                 o.stage_bytes = align_up_u32(o.R * o.row_bytes, 128);
                 o.off_part = 256;
-                o.off_prep = align_up_u32(o.off_part + part_bytes(o), 128);
-                o.off_ring = align_up_u32(o.off_prep + prep_bytes(o), 128);
-                if ((int)o.off_ring + 2 * (int)o.stage_bytes <= budget) {
-                    fits = true;
-                    break;
+                const uint32_t after_part = align_up_u32(o.off_part + part_bytes(o), 128), pb = align_up_u32(prep_bytes(o), 128);
+                if (form != 2) {
+                    o.off_prep = after_part;
+                    o.off_ring = o.off_prep + pb;
+                    if ((int)o.off_ring + 2 * (int)o.stage_bytes > budget) continue;
+                    o.S = std::min<uint32_t>(CHAIN_MAX_STAGES, (uint32_t)(budget - (int)o.off_ring) / o.stage_bytes);
+                    o.late_stage = o.S;
+                } else {
+                    o.off_ring = after_part;
+                    if ((int)o.off_ring + 2 * (int)o.stage_bytes > budget || pb > o.stage_bytes) continue;
+                    o.S = std::min<uint32_t>(CHAIN_MAX_STAGES, (uint32_t)(budget - (int)o.off_ring) / o.stage_bytes);
+                    o.off_prep = o.off_ring + o.S * o.stage_bytes - pb; // inside the last stage
+                    o.late_stage = o.S - 1;
                 }
+                fits = true;
             }
             if (!fits) return cudaErrorNotSupported;
-            o.S = std::min<uint32_t>(CHAIN_MAX_STAGES, (uint32_t)(budget - (int)o.off_ring) / o.stage_bytes);
             smem = std::max(smem, o.off_ring + o.S * o.stage_bytes);
         }
     } else { // all CTAs walk the list: one layout, sized for the largest op, so that the ring runs on across ops
@@ -477,7 +501,7 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         const uint32_t S = std::min<uint32_t>(CHAIN_MAX_STAGES, (uint32_t)(budget - (int)off_ring) / max_stage);
         for (int i = 0; i < n; ++i) {
             ChainOpDev &o = p.op[i];
-            o.S = S, o.stage_bytes = max_stage, o.off_part = off_part, o.off_prep = off_prep, o.off_ring = off_ring;
+            o.S = S, o.stage_bytes = max_stage, o.off_part = off_part, o.off_prep = off_prep, o.off_ring = off_ring, o.late_stage = S;
         }
         smem = off_ring + S * max_stage;
     }
