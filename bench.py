@@ -54,7 +54,7 @@ METRIC = "quantized_matvec_hbm_gbs"
 DTYPE = "u8 x s16 integer dot products (x as 16-bit fixed point per 32/64 values), f32 scale and accumulate"
 # dram__bytes_read.sum + dram__bytes_write.sum of one step's kernels at N = 1, from an ncu capture of this
 # workload (None until one has been taken)
-NCU_TRAFFIC_PER_STEP = {"c4_70b_layer_matvec": 543_680_000 + 6_027_520}
+NCU_TRAFFIC_PER_STEP = {"c4_70b_layer_matvec": 543_715_328 + 6_088_192}
 
 
 def weight_bytes(dtype, out, cols):

@@ -187,11 +187,16 @@ def test_shard_argument_errors(ctx):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_devices_one_process():
+@pytest.mark.parametrize("tagged", [1, 0])
+def test_two_devices_one_process(tagged):
     """A real two-GPU group inside one process (``ullm_cuda_shard_connect_local``): both ranks launch their
-    step with the wait inside the kernel; the launches are asynchronous, so both kernels are in flight."""
+    step with the wait inside the kernel; the launches are asynchronous, so both kernels are in flight.
+    Both exchanges: rows as {value, step} pairs that the receiving kernel polls and unpacks (the default of a
+    waiting launch), and plain stores followed by published step numbers."""
     ws, xs, refs, offs, total = full_problem(700)
     ctxs = [backend.CudaContext(d) for d in range(2)]
+    for c in ctxs:
+        c.debug_set("shard_no_tagged", 0 if tagged else 1)
     shards = [backend.Shard(c, 2, r, 2 * total) for r, c in enumerate(ctxs)]
     backend.Shard.connect_local(shards)
     try:

@@ -74,6 +74,14 @@ struct ShardDev {
     int signal = 1;                         // publish when the launch is done (0: a later launch of the same exchange does)
     int wait = 1;                           // ... and wait (bounded) for every rank's publication before the kernel ends
     unsigned long long timeout_ns = 2000000000ull;
+    // Tagged exchange (matvec_chain_kernel, `tagged` != 0): rows travel as 8-byte {value, step} pairs into the
+    // receivers' pair areas, and every rank's kernel polls the pairs it is owed and writes the values into its own
+    // gather buffer - no fence, flag or second round trip between the last row and the end of the step.
+    // pairs[(step & 1) * pair_floats + e] belongs to float e of the gather buffer `ybase`.
+    int tagged = 0;
+    float *ybase = nullptr;
+    uint2 *pairs = nullptr;
+    unsigned pair_floats = 0;
 };
 // Publishes the exchange whose rows earlier launches on `st` stored (and waits when sh.wait).
 cudaError_t launch_shard_signal(const ShardDev &sh, int *d_status, cudaStream_t st);
@@ -102,6 +110,9 @@ struct MatvecChainOp {
     int epi = EPI_STORE;
     const float *res = nullptr;
     bool dep = false;
+    // sharded launch: [gather_off, gather_off + gather_len) is the whole vector in the gather buffer (floats), of
+    // which y .. y + out_dim is this rank's part
+    size_t gather_off = 0, gather_len = 0;
 };
 bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi);
 void matvec_chain_set_q6k_cost(double v);

@@ -63,6 +63,7 @@ struct ChainOpDev {
     // Dealt CTAs only: ring stages from this one on lie over the activation image (which is dead once the consumers
     // hold it in registers); the producer fills them for the first time after the consumers have said so.  S: none.
     uint32_t late_stage;
+    uint32_t gather_off, gather_len; // sharded launch: the op's whole vector in the gather buffer (floats)
 };
 struct ChainParams {
     ChainOpDev op[CHAIN_MAX_OPS];
@@ -325,17 +326,50 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
         // place in every other rank's (the barrier above makes them visible to all threads of the CTA; they are
         // read back past the L1 and sent as plain stores through the peer mappings, a warp's worth contiguous).
         if (p.sh.world > 1 && !aborted) {
-            for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
-                const float v = __ldcg(o.y + e);
-                for (int r = 0; r < p.sh.world; ++r)
-                    if (r != p.sh.rank) *(float *)((char *)(o.y + e) + p.sh.delta[r]) = v;
+            if (p.sh.tagged) { // {value, step} pairs into the receivers' pair areas
+                const unsigned step = shard_this_step(p.sh);
+                uint2 *mine = p.sh.pairs + (size_t)(step & 1u) * p.sh.pair_floats + (o.y - p.sh.ybase);
+                for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
+                    const float v = __ldcg(o.y + e);
+                    for (int r = 0; r < p.sh.world; ++r)
+                        if (r != p.sh.rank) shard_st_pair((uint2 *)((char *)(mine + e) + p.sh.delta[r]), v, step);
+                }
+            } else {
+                for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
+                    const float v = __ldcg(o.y + e);
+                    for (int r = 0; r < p.sh.world; ++r)
+                        if (r != p.sh.rank) *(float *)((char *)(o.y + e) + p.sh.delta[r]) = v;
+                }
             }
         }
     }
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
     // Sharded launch: once every consumer thread has issued its stores to the peers, one thread orders them
     // and counts the CTA in; the last CTA publishes the exchange to every rank and waits, bounded, for theirs.
-    if (p.sh.world) {
+    if (p.sh.world && p.sh.tagged) {
+        // Tagged exchange: the rows the other ranks owe this one arrive as pairs; all CTAs share the polling (a
+        // few elements per thread), whichever op they worked on, and write the values into this rank's vector.
+        const unsigned step = shard_this_step(p.sh);
+        int &failed = *(int *)(smem + 132);
+        if (tid == 0) failed = aborted ? 1 : 0;
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+        if (!aborted && p.sh.world > 1) {
+            const unsigned long long t0 = shard_now_ns();
+            bool ok = true;
+            for (int i = 0; i < p.n_ops && ok; ++i) {
+                const ChainOpDev &o = p.op[i];
+                const uint32_t own = (uint32_t)(o.y - p.sh.ybase) - o.gather_off, remote = o.gather_len - o.out_dim;
+                for (uint32_t j = blockIdx.x * nthr_c + tid; j < remote && ok; j += gridDim.x * nthr_c)
+                    ok = shard_take_pair(p.sh, step, (size_t)o.gather_off + (j < own ? j : j + o.out_dim), t0);
+            }
+            if (!ok) {
+                failed = 1;
+                *(volatile int *)p.status = DEV_TIMEOUT;
+            }
+        }
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+        if (tid == 0) shard_cta_done_tagged(p.sh, step, failed != 0);
+    } else if (p.sh.world) {
         asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
         if (tid == 0 && !shard_cta_done(p.sh, aborted)) *(volatile int *)p.status = DEV_TIMEOUT;
     }
@@ -416,6 +450,8 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
         ChainOpDev &o = p.op[i];
         o.w = (const uint8_t *)h.w, o.x = h.x, o.y = h.y, o.norm_w = h.norm_w, o.res = h.res, o.eps = h.eps, o.epi = h.epi;
         o.fmt = h.fmt, o.dep = h.dep ? 1 : 0, o.out_dim = (uint32_t)h.out_dim, o.in_dim = (uint32_t)h.in_dim;
+        o.gather_off = (uint32_t)h.gather_off, o.gather_len = (uint32_t)h.gather_len;
+        if (shard && shard->tagged && (h.gather_len < h.out_dim || h.gather_off + h.gather_len > 0xffffffffull)) return cudaErrorInvalidValue;
         o.row_bytes = (uint32_t)(h.in_dim / QK_K) * (h.fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
         o.gran = 16 / gcd_u(o.row_bytes, 16);
         if (h.epi == EPI_SWIGLU) o.gran = std::max(o.gran, 2u);

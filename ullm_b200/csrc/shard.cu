@@ -161,8 +161,9 @@ constexpr int kNcclFloat = 7; // ncclFloat32
 struct ullm_cuda_shard {
     ullm_cuda_ctx *ctx = nullptr;
     int world = 0, rank = 0;
-    void *base = nullptr; // [control block SHARD_CTL_BYTES][y_floats floats]
+    void *base = nullptr; // [control block SHARD_CTL_BYTES][y_floats floats][pair area: 2 x y_floats pairs, when pair_bytes]
     size_t y_floats = 0;
+    size_t pair_bytes = 0; // 0: no pair area (gather buffers beyond kPairMaxFloats, i.e. prefill-sized ones)
     void *peer_base[SHARD_MAX_RANKS] = {};
     bool peer_ipc[SHARD_MAX_RANKS] = {}; // opened with cudaIpcOpenMemHandle: closed on destroy
     bool connected = false;
@@ -176,6 +177,10 @@ struct ullm_cuda_shard {
 };
 
 static float *shard_y(const ullm_cuda_shard *s) { return (float *)((uint8_t *)s->base + SHARD_CTL_BYTES); }
+static size_t shard_y_bytes(const ullm_cuda_shard *s) { return (s->y_floats * 4 + 255) & ~(size_t)255; }
+// The tagged exchange of the batch-1 form needs 16 bytes of pair area per float of the gather buffer: kept to
+// buffers of vector size (a prefill-sized buffer of [tokens, out] floats uses the flag protocol and copy engines).
+constexpr size_t kPairMaxFloats = (size_t)1 << 22;
 
 static void shard_wire(ullm_cuda_shard *s) {
     ShardDev &d = s->dev;
@@ -185,6 +190,9 @@ static void shard_wire(ullm_cuda_shard *s) {
         d.delta[r] = (long long)((intptr_t)s->peer_base[r] - (intptr_t)s->base);
         d.peer_flag[r] = (unsigned *)s->peer_base[r] + s->rank * SHARD_CTL_STRIDE;
     }
+    d.ybase = shard_y(s);
+    d.pairs = s->pair_bytes ? (uint2 *)((uint8_t *)s->base + SHARD_CTL_BYTES + shard_y_bytes(s)) : nullptr;
+    d.pair_floats = (unsigned)s->y_floats;
     s->connected = true;
 }
 static void shard_timeout(ullm_cuda_shard *s, ShardDev &d) { d.timeout_ns = (unsigned long long)s->ctx->shard_timeout_ms * 1000000ull; }
@@ -207,7 +215,8 @@ int ullm_cuda_shard_create(ullm_cuda_ctx *c, int world, int rank, size_t y_float
     ullm_cuda_shard *s = new (std::nothrow) ullm_cuda_shard();
     if (!s) return ULLM_ERR_OOM;
     s->ctx = c, s->world = world, s->rank = rank, s->y_floats = y_floats;
-    const size_t bytes = SHARD_CTL_BYTES + ((y_floats * 4 + 255) & ~(size_t)255);
+    s->pair_bytes = y_floats <= kPairMaxFloats ? 2 * y_floats * sizeof(uint2) : 0;
+    const size_t bytes = SHARD_CTL_BYTES + shard_y_bytes(s) + s->pair_bytes;
     cudaError_t e = cudaMalloc(&s->base, bytes);
     if (e == cudaSuccess) e = cudaMemset(s->base, 0, bytes);
     if (e != cudaSuccess) {
@@ -324,6 +333,7 @@ int ullm_cuda_shard_reset(ullm_cuda_shard *s) {
     ULLM_CUDA_TRY(c, cudaSetDevice(c->device));
     ULLM_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     ULLM_CUDA_TRY(c, cudaMemset(s->base, 0, SHARD_CTL_BYTES));
+    if (s->pair_bytes) ULLM_CUDA_TRY(c, cudaMemset((uint8_t *)s->base + SHARD_CTL_BYTES + shard_y_bytes(s), 0, s->pair_bytes)); // stale tags
     *c->h_status = DEV_OK;
     return ULLM_OK;
 }
@@ -374,6 +384,8 @@ int ullm_cuda_shard_matvec_dev(ullm_cuda_shard *s, size_t n, const ullm_shard_op
     sh.wait = (flags & ULLM_SHARD_NO_WAIT) ? 0 : 1;
     std::vector<MatvecChainOp> v(n);
     bool fused = !c->force_generic && !c->no_chain;
+    // The tagged exchange: one launch that waits for the other ranks itself, every op an even split by rank.
+    bool tagged = sh.wait && s->pair_bytes && n <= 12 && !c->shard_no_tagged;
     for (size_t i = 0; i < n; ++i) {
         const ullm_shard_op &o = ops[i];
         if (!o.w || !o.d_x) return ULLM_ERR_INVALID;
@@ -384,6 +396,8 @@ int ullm_cuda_shard_matvec_dev(ullm_cuda_shard *s, size_t n, const ullm_shard_op
                             row0 + o.w->out, o.y_offset, s->y_floats);
         MatvecChainOp &m = v[i];
         m.fmt = o.w->fmt, m.w = o.w->w, m.x = o.d_x, m.y = shard_y(s) + o.y_offset + row0, m.out_dim = o.w->out, m.in_dim = o.w->cols;
+        m.gather_off = o.y_offset, m.gather_len = o.w->out * (size_t)s->world;
+        tagged = tagged && row0 == o.w->out * (size_t)s->rank && m.gather_len <= s->y_floats - o.y_offset;
         fused = fused && matvec_chain_supported(m.fmt, m.out_dim, m.in_dim, EPI_STORE) && ((uintptr_t)m.w % 16 == 0);
     }
     if (fused) {
@@ -404,6 +418,7 @@ int ullm_cuda_shard_matvec_dev(ullm_cuda_shard *s, size_t n, const ullm_shard_op
             const size_t m = std::min<size_t>(12, n - i);
             ShardDev part = sh;
             part.signal = i + m == n ? 1 : 0; // the last launch of the step publishes for all of them
+            part.tagged = tagged ? 1 : 0;
             cudaError_t e = launch_matvec_chain(c->dev, (int)m, v.data() + i, d_sync, c->d_status, st, c->use_pdl, &part);
             if (e == cudaErrorNotSupported && i == 0) {
                 cudaGetLastError();

@@ -75,4 +75,43 @@ __device__ __forceinline__ bool shard_cta_done(const ShardDev &sh, bool aborted)
     return shard_publish(sh);
 }
 
+// ---- tagged exchange (see ShardDev::tagged) ----
+// An aligned 8-byte store / load is one access, so a pair is never seen half written (what NCCL's LL protocol
+// relies on as well); volatile keeps both out of the L1.
+__device__ __forceinline__ void shard_st_pair(uint2 *p, float v, unsigned step) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(step) : "memory");
+}
+__device__ __forceinline__ uint2 shard_ld_pair(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// The step this launch belongs to: one more than the rank has completed.  Read by every thread that needs it
+// before its CTA arrives; the word changes only after every CTA of the launch has arrived.
+__device__ __forceinline__ unsigned shard_this_step(const ShardDev &sh) { return *(volatile unsigned *)(sh.ctl + SHARD_CTL_STEP) + 1u; }
+// Polls (bounded) the pair of gather-buffer float e for `step`; false when the time limit ran out.
+__device__ __forceinline__ bool shard_take_pair(const ShardDev &sh, unsigned step, size_t e, unsigned long long t0) {
+    const uint2 *slot = sh.pairs + (size_t)(step & 1u) * sh.pair_floats + e;
+    for (unsigned spin = 0;; ++spin) {
+        const uint2 v = shard_ld_pair(slot);
+        if (v.y == step) {
+            sh.ybase[e] = __uint_as_float(v.x);
+            return true;
+        }
+        if ((spin & 63u) == 63u && shard_now_ns() - t0 > sh.timeout_ns) return false;
+    }
+}
+// End of a tagged launch, one thread per CTA after a CTA-wide barrier: counts the CTA in; the last one completes
+// the step (step word, and the ranks' flag words so that the flag protocol of other entry points stays in
+// step).  `failed`: this CTA gave up on a bounded wait: the step is not completed.
+__device__ __forceinline__ void shard_cta_done_tagged(const ShardDev &sh, unsigned step, bool failed) {
+    unsigned *done = sh.ctl + SHARD_CTL_DONE;
+    const unsigned old = atomicAdd(done, failed ? 0x10001u : 1u);
+    if ((old & 0xffffu) != gridDim.x * gridDim.y * gridDim.z - 1) return;
+    *(volatile unsigned *)done = 0u;
+    if ((old >> 16) != 0u || failed) return;
+    *(volatile unsigned *)(sh.ctl + SHARD_CTL_STEP) = step;
+    for (int r = 0; r < sh.world; ++r) shard_st_relaxed_sys(sh.peer_flag[r], step);
+}
+
 } // namespace ullm
