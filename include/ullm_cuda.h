@@ -210,8 +210,11 @@ int ullm_cuda_matmul_dev(ullm_cuda_ctx *ctx, int dtype, const void *d_w, const v
  * vectors (by offset).  The kernels of rank r store the rows they computed at the same offset into
  * EVERY rank's gather buffer (plain stores over NVLink through peer mappings; nothing is read from
  * a peer), then publish a step number to every rank; the step is complete on a rank when it has
- * seen every rank's number.  No NCCL call is involved, so a step can be captured in a CUDA graph
- * like any other kernel.
+ * seen every rank's number.  A matvec step that waits for the other ranks itself (no
+ * ULLM_SHARD_NO_WAIT) sends its rows as {value, step} pairs instead, which the receiving rank's
+ * kernel polls and writes into its gather buffer: the same result without the publication round
+ * trips (the shard then holds 16 more bytes per float of `y_floats`, for buffers up to 4 M floats).
+ * No NCCL call is involved, so a step can be captured in a CUDA graph like any other kernel.
  *
  * Set-up, one process per GPU (rank = that process' index): ullm_cuda_shard_create, exchange the
  * ULLM_SHARD_HANDLE_BYTES handles of ullm_cuda_shard_export between the processes by any means
@@ -220,7 +223,8 @@ int ullm_cuda_matmul_dev(ullm_cuda_ctx *ctx, int dtype, const void *d_w, const v
  * ullm_cuda_shard_connect_local.  All ranks must be connected before any of them runs a step.
  *
  * Rules for the caller:
- *  - Every rank must run the same sequence of sharded calls (steps are counted per rank).
+ *  - Every rank must run the same sequence of sharded calls with the same flags (steps are counted
+ *    per rank, and the flags select how rows travel).
  *  - A rank waits at most ULLM_OPT_SHARD_TIMEOUT_MS for the others; then the call (or the next
  *    ullm_cuda_synchronize) reports ULLM_ERR_TIMEOUT instead of hanging — this is how a dead or
  *    stalled peer shows.  After a time-out the group is out of step: every rank calls

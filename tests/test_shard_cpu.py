@@ -154,6 +154,98 @@ def test_a_rank_that_never_publishes_ends_the_others_wait_with_a_timeout():
     assert res[0][1] is True  # rank 0 saw the time-out
 
 
+def _tagged_worker(rank, world, port, out_q):
+    """The tagged exchange of a waiting launch (``matvec_chain_kernel`` with ``ShardDev::tagged``), gloo messages
+    standing in for 8-byte stores over NVLink: a rank's rows reach the others as {value, step} pairs in the half
+    of the pair area that ``step`` selects; a rank polls the pairs it is owed for the step's tag and writes the
+    values into its own vectors.  Rank 1 is made slow on purpose: before it takes the pairs of step s it has
+    already been sent rank 0's pairs of step s + 1 (rank 0 only needed rank 1's rows of step s to go on), which
+    land in the other half and must not disturb step s."""
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        outs = [m[1] for m in MATS]
+        offs = shard.vector_offsets(outs, align=16)
+        total = offs[-1]
+        vec = np.full(total, np.nan, np.float32)       # this rank's result vectors
+        pair_val = np.zeros(2 * total, np.float32)     # pair area: values ...
+        pair_tag = np.zeros(2 * total, np.int64)       # ... and step tags (0: never written)
+        peer, n_rows, last = 1 - rank, sum(o // world for o in outs), 4
+        ok, early, applied, pending = True, 0, 0, []
+
+        def apply_one_message():
+            msg = torch.empty(n_rows + 1)
+            dist.recv(msg, src=peer)
+            m, at = msg.numpy(), 0
+            step = int(m[-1])
+            for i, o in enumerate(outs):
+                lo, hi = shard.row_range(o, world, peer)
+                for e in range(offs[i] + lo, offs[i] + hi):  # the peer's stores: its own rows, tagged
+                    slot = shard.pair_slot(step, total, e)
+                    pair_val[slot], pair_tag[slot] = m[at], step
+                    at += 1
+            return step
+
+        for step in range(1, last + 1):
+            rows = []
+            for i, (dt, out, cols) in enumerate(MATS):
+                gen = synth.gen_q4k if dt == oracle.Q4_K else synth.gen_q6k
+                mine = shard.slice_rows(dt, gen(out, cols, 100 + i), out, cols, world, rank)
+                y = oracle.matvec_q(oracle.Weight(dt, mine, out // world, cols), synth.normal(200 + i + 10 * step, cols))
+                lo, hi = shard.row_range(out, world, rank)
+                vec[offs[i] + lo: offs[i] + hi] = y      # own rows: plain stores into the own vector
+                rows.append(y)
+            pending.append(dist.isend(torch.from_numpy(np.concatenate(rows + [np.float32([step])])), dst=peer))
+            # what has arrived when this rank starts polling: the fast rank has exactly its peer's current step,
+            # the slow rank has let the peer run ahead by one step
+            want = step if rank == 0 else min(step + 1, last)
+            while applied < want:
+                early += apply_one_message() > step
+                applied += 1
+            for i, (dt, out, cols) in enumerate(MATS):
+                for j in range(out - out // world):
+                    e = shard.owed_element(j, offs[i], out, world, rank)
+                    slot = shard.pair_slot(step, total, e)
+                    ok = ok and pair_tag[slot] == step  # a real kernel polls here, bounded
+                    vec[e] = pair_val[slot]
+                gen = synth.gen_q4k if dt == oracle.Q4_K else synth.gen_q6k
+                ref = oracle.matvec_q(oracle.Weight(dt, gen(out, cols, 100 + i), out, cols), synth.normal(200 + i + 10 * step, cols))
+                ok = ok and np.array_equal(vec[offs[i]: offs[i] + out], ref)
+        for h in pending:
+            h.wait()
+        out_q.put((rank, bool(ok), early))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_tagged_exchange_survives_a_rank_that_runs_one_step_ahead():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_tagged_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    assert [(r, ok) for r, ok, _ in res] == [(0, True), (1, True)]
+    assert res[1][2] == 3  # rank 1 held rank 0's next step before it took the current one, in three of four steps
+
+
+def test_owed_elements_and_pair_slots():
+    # rank 1 of 4 on a 16-row vector at offset 100 computes rows 4..7 and is owed the other twelve
+    got = [shard.owed_element(j, 100, 16, 4, 1) for j in range(12)]
+    assert got == [100, 101, 102, 103, 108, 109, 110, 111, 112, 113, 114, 115]
+    with pytest.raises(ValueError):
+        shard.owed_element(12, 100, 16, 4, 1)
+    assert shard.pair_slot(6, 1000, 7) == 7 and shard.pair_slot(7, 1000, 7) == 1007
+
+
 def test_library_row_split_agrees_with_the_index_math():
     import ctypes as C
 

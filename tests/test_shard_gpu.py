@@ -169,6 +169,41 @@ def test_a_silent_peer_ends_in_a_timeout_status_and_the_group_recovers(ctx):
             s.free()
 
 
+def test_a_silent_peer_ends_the_tagged_exchange_in_a_timeout_too(ctx):
+    """The same failure in a launch that waits itself: rank 0's kernel polls the {value, step} pairs rank 1 owes
+    it, rank 1 never runs, the poll's time limit (50 ms) runs out in every polling thread, the kernel returns and
+    the host sees ULLM_ERR_TIMEOUT.  After a reset (which also clears stale tags) the group works again."""
+    out, cols = 512, 1024
+    w = synth.gen_q4k(out, cols, 621)
+    x = synth.normal(622, cols)
+    ref = oracle.matvec_q(oracle.Weight(backend.Q4_K, w, out, cols), x)
+    shards = group(ctx, 2, out)
+    xd = dev_f32(x)
+    ctx.set_option(backend.OPT_SHARD_TIMEOUT_MS, 50)
+    try:
+        w0 = shards[0].weight(backend.Q4_K, w, out, cols)
+        shards[0].matvec_dev(shards[0].ops([dict(w=w0, x=xd.data_ptr(), y_offset=0)]))  # waits inside the kernel
+        assert ctx.last_plan()["grid"] == -3
+        with pytest.raises(backend.UllmError) as e:
+            ctx.synchronize()
+        assert e.value.code == backend.ERR_TIMEOUT
+        for s in shards:
+            s.reset()
+        ctx.set_option(backend.OPT_SHARD_TIMEOUT_MS, 2000)
+        for s in shards:
+            wt = s.weight(backend.Q4_K, w, out, cols)
+            s.matvec_dev(s.ops([dict(w=wt, x=xd.data_ptr(), y_offset=0)]), None, backend.SHARD_NO_WAIT)
+        for s in shards:
+            s.wait_dev()
+        ctx.synchronize()
+        for s in shards:
+            assert synth.rel_err(s.read_y(0, out), ref) < TOL
+    finally:
+        ctx.set_option(backend.OPT_SHARD_TIMEOUT_MS, 2000)
+        for s in shards:
+            s.free()
+
+
 def test_shard_argument_errors(ctx):
     with pytest.raises(backend.UllmError):
         backend.Shard(ctx, 9, 0, 16)  # more than 8 ranks

@@ -239,6 +239,63 @@ __device__ __forceinline__ void chain_consume(const ChainOpDev &o, const ChainPa
     }
 }
 
+// Sharded launch, after an op: this CTA's rows [rbeg, rend) of the op, just written to this rank's result vector,
+// go to every other rank (the CTA barrier before the call made them visible to all its threads; they are read back
+// past the L1 and sent as plain stores through the peer mappings, a warp's worth contiguous): as {value, step}
+// pairs into the receivers' pair areas, or as plain floats into the same place of their vectors.
+// Kept out of line, like chain_shard_finish: the sharded tail must not weigh on the registers of the row loop.
+__device__ __noinline__ void chain_shard_send(const ChainOpDev &o, const ShardDev &sh, uint32_t rbeg, uint32_t rend, uint32_t tid,
+                                              uint32_t nthr_c) {
+    if (sh.tagged) {
+        const unsigned step = shard_this_step(sh);
+        uint2 *mine = sh.pairs + (size_t)(step & 1u) * sh.pair_floats + (o.y - sh.ybase);
+        for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
+            const float v = __ldcg(o.y + e);
+            for (int r = 0; r < sh.world; ++r)
+                if (r != sh.rank) shard_st_pair((uint2 *)((char *)(mine + e) + sh.delta[r]), v, step);
+        }
+    } else {
+        for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
+            const float v = __ldcg(o.y + e);
+            for (int r = 0; r < sh.world; ++r)
+                if (r != sh.rank) *(float *)((char *)(o.y + e) + sh.delta[r]) = v;
+        }
+    }
+}
+
+// Sharded launch, after the last op (all consumer threads).
+__device__ __noinline__ void chain_shard_finish(const ChainParams &p, uint8_t *smem, uint32_t tid, uint32_t nthr_c, bool aborted) {
+    if (p.sh.tagged) {
+        // Tagged exchange: the rows the other ranks owe this one arrive as pairs; all CTAs share the polling (a
+        // few elements per thread), whichever op they worked on, and write the values into this rank's vector.
+        const unsigned step = shard_this_step(p.sh);
+        int &failed = *(int *)(smem + 132);
+        if (tid == 0) failed = aborted ? 1 : 0;
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+        if (!aborted && p.sh.world > 1) {
+            const unsigned long long t0 = shard_now_ns();
+            bool ok = true;
+            for (int i = 0; i < p.n_ops && ok; ++i) {
+                const ChainOpDev &o = p.op[i];
+                const uint32_t own = (uint32_t)(o.y - p.sh.ybase) - o.gather_off, remote = o.gather_len - o.out_dim;
+                for (uint32_t j = blockIdx.x * nthr_c + tid; j < remote && ok; j += gridDim.x * nthr_c)
+                    ok = shard_take_pair(p.sh, step, (size_t)o.gather_off + (j < own ? j : j + o.out_dim), t0);
+            }
+            if (!ok) {
+                failed = 1;
+                *(volatile int *)p.status = DEV_TIMEOUT;
+            }
+        }
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+        if (tid == 0) shard_cta_done_tagged(p.sh, step, failed != 0);
+    } else {
+        // Plain stores: once every consumer thread has issued its stores to the peers, one thread orders them and
+        // counts the CTA in; the last CTA publishes the exchange to every rank and waits, bounded, for theirs.
+        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
+        if (tid == 0 && !shard_cta_done(p.sh, aborted)) *(volatile int *)p.status = DEV_TIMEOUT;
+    }
+}
+
 constexpr int CHAIN_MAX_THREADS = 21 * 32; // 20 consumer warps + the producer warp
 
 // 20 consumer warps at 80 registers.  Measured against it on the 70B block (B200, us per step): 28 warps at 64
@@ -322,57 +379,10 @@ __global__ void __launch_bounds__(CHAIN_MAX_THREADS, 1) matvec_chain_kernel(cons
 #undef ULLM_CHAIN_CASE
         kbase += (rend - rbeg + o.R - 1) / o.R;
         asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory"); // prep / part areas are free for the next op
-        // Sharded launch: this CTA's rows of the op, just written to this rank's result vector, go to the same
-        // place in every other rank's (the barrier above makes them visible to all threads of the CTA; they are
-        // read back past the L1 and sent as plain stores through the peer mappings, a warp's worth contiguous).
-        if (p.sh.world > 1 && !aborted) {
-            if (p.sh.tagged) { // {value, step} pairs into the receivers' pair areas
-                const unsigned step = shard_this_step(p.sh);
-                uint2 *mine = p.sh.pairs + (size_t)(step & 1u) * p.sh.pair_floats + (o.y - p.sh.ybase);
-                for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
-                    const float v = __ldcg(o.y + e);
-                    for (int r = 0; r < p.sh.world; ++r)
-                        if (r != p.sh.rank) shard_st_pair((uint2 *)((char *)(mine + e) + p.sh.delta[r]), v, step);
-                }
-            } else {
-                for (uint32_t e = rbeg + tid; e < rend; e += nthr_c) {
-                    const float v = __ldcg(o.y + e);
-                    for (int r = 0; r < p.sh.world; ++r)
-                        if (r != p.sh.rank) *(float *)((char *)(o.y + e) + p.sh.delta[r]) = v;
-                }
-            }
-        }
+        if (p.sh.world > 1 && !aborted) chain_shard_send(o, p.sh, rbeg, rend, tid, nthr_c);
     }
     if (aborted && lane == 0) *(volatile int *)p.status = DEV_TIMEOUT;
-    // Sharded launch: once every consumer thread has issued its stores to the peers, one thread orders them
-    // and counts the CTA in; the last CTA publishes the exchange to every rank and waits, bounded, for theirs.
-    if (p.sh.world && p.sh.tagged) {
-        // Tagged exchange: the rows the other ranks owe this one arrive as pairs; all CTAs share the polling (a
-        // few elements per thread), whichever op they worked on, and write the values into this rank's vector.
-        const unsigned step = shard_this_step(p.sh);
-        int &failed = *(int *)(smem + 132);
-        if (tid == 0) failed = aborted ? 1 : 0;
-        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
-        if (!aborted && p.sh.world > 1) {
-            const unsigned long long t0 = shard_now_ns();
-            bool ok = true;
-            for (int i = 0; i < p.n_ops && ok; ++i) {
-                const ChainOpDev &o = p.op[i];
-                const uint32_t own = (uint32_t)(o.y - p.sh.ybase) - o.gather_off, remote = o.gather_len - o.out_dim;
-                for (uint32_t j = blockIdx.x * nthr_c + tid; j < remote && ok; j += gridDim.x * nthr_c)
-                    ok = shard_take_pair(p.sh, step, (size_t)o.gather_off + (j < own ? j : j + o.out_dim), t0);
-            }
-            if (!ok) {
-                failed = 1;
-                *(volatile int *)p.status = DEV_TIMEOUT;
-            }
-        }
-        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
-        if (tid == 0) shard_cta_done_tagged(p.sh, step, failed != 0);
-    } else if (p.sh.world) {
-        asm volatile("bar.sync 2, %0;" ::"r"(nthr_c) : "memory");
-        if (tid == 0 && !shard_cta_done(p.sh, aborted)) *(volatile int *)p.status = DEV_TIMEOUT;
-    }
+    if (p.sh.world) chain_shard_finish(p, smem, tid, nthr_c, aborted);
 }
 
 // ---------------------------------------------------------------------------

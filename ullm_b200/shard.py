@@ -54,6 +54,22 @@ def step_region(step: int, total: int) -> int:
     return (step & 1) * total
 
 
+def owed_element(j: int, gather_off: int, out_dim: int, world: int, rank: int) -> int:
+    """Tagged exchange: the ``j``-th float of a matrix' full-length vector that rank ``rank`` does NOT compute
+    itself (0 <= j < out_dim - out_dim/world), as an index into the gather buffer.  The receiving kernel's threads
+    share these out: each polls the {value, step} pair of its elements and writes the value into the vector."""
+    lo, hi = row_range(out_dim, world, rank)
+    if not 0 <= j < out_dim - (hi - lo):
+        raise ValueError("no such owed element")
+    return gather_off + (j if j < lo else j + (hi - lo))
+
+
+def pair_slot(step: int, gather_floats: int, e: int) -> int:
+    """Index of the {value, step} pair of gather-buffer float ``e`` in a rank's pair area: two halves used by
+    alternate steps, so that a rank one step ahead writes beside, not over, pairs its peer has yet to take."""
+    return (step & 1) * gather_floats + e
+
+
 def local_offsets(out_dims, world: int) -> list[int]:
     """Offsets of each matrix' rows inside a rank's concatenated output."""
     offs, o = [], 0
