@@ -526,7 +526,7 @@ int ullm_cuda_weight_matvec_batch(ullm_cuda_ctx *c, size_t n, const ullm_cuda_we
             VecCopyList l{};
             const int m = (int)std::min<size_t>(VEC_COPY_MAX, n - i);
             for (int k = 0; k < m; ++k) l.src[k] = xv[i + k], l.dst[k] = (float *)ops[i + k].d_x, l.n[k] = (unsigned)w[i + k]->cols;
-            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream));
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream, c->use_pdl));
         }
     } else {
         for (size_t i = 0; i < n; ++i) ULLM_CUDA_TRY(c, cudaMemcpyAsync((void *)ops[i].d_x, x[i], w[i]->cols * 4, cudaMemcpyHostToDevice, c->stream));
@@ -537,7 +537,7 @@ int ullm_cuda_weight_matvec_batch(ullm_cuda_ctx *c, size_t n, const ullm_cuda_we
             VecCopyList l{};
             const int m = (int)std::min<size_t>(VEC_COPY_MAX, n - i);
             for (int k = 0; k < m; ++k) l.src[k] = ops[i + k].d_y, l.dst[k] = yv[i + k], l.n[k] = (unsigned)w[i + k]->out;
-            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream));
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream, c->use_pdl));
         }
     } else {
         for (size_t i = 0; i < n; ++i) ULLM_CUDA_TRY(c, cudaMemcpyAsync(y[i], ops[i].d_y, w[i]->out * 4, cudaMemcpyDeviceToHost, c->stream));

@@ -26,7 +26,13 @@ struct VecCopyList {
     float *dst[VEC_COPY_MAX];
     unsigned n[VEC_COPY_MAX];
 };
+// Launched programmatically dependent on the kernel before it, and letting the kernel after it start at once:
+// between the copy-in, the matvec launch and the copy-out of a host-vector call there is then no launch gap (the
+// matvec kernel's producer warps stream weights while the inputs are still on their way; its consumers wait for
+// this grid with griddepcontrol.wait before they read them).
 static __global__ void __launch_bounds__(256) host_vec_copy_multi_kernel(const __grid_constant__ VecCopyList l) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory"); // the kernel before this one has written what is copied
     const float *src = l.src[blockIdx.y];
     float *dst = l.dst[blockIdx.y];
     const size_t n = l.n[blockIdx.y];
@@ -37,12 +43,17 @@ static __global__ void __launch_bounds__(256) host_vec_copy_multi_kernel(const _
             for (size_t j = i; j < n && j < i + 4; ++j) dst[j] = src[j];
     }
 }
-static cudaError_t vec_copy_multi(const VecCopyList &l, int count, cudaStream_t st) {
+static cudaError_t vec_copy_multi(const VecCopyList &l, int count, cudaStream_t st, bool pdl = false) {
     unsigned most = 0;
     for (int i = 0; i < count; ++i) most = std::max(most, l.n[i]);
     const unsigned gx = std::max(1u, std::min(32u, (most + 1023) / 1024));
-    host_vec_copy_multi_kernel<<<dim3(gx, (unsigned)count), 256, 0, st>>>(l);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(gx, (unsigned)count), cfg.blockDim = dim3(256), cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, host_vec_copy_multi_kernel, l);
 }
 static const float *device_view_of_host(const void *p) {
     cudaPointerAttributes a;

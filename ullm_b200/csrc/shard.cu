@@ -472,7 +472,7 @@ int ullm_cuda_shard_matvec(ullm_cuda_shard *s, size_t n, const ullm_shard_op *op
             else l.src[m] = v, l.dst[m] = (float *)ops[i].d_x, l.n[m] = (unsigned)ops[i].w->cols, ++m;
         }
         if (mapped && m) {
-            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream));
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, m, c->stream, c->use_pdl));
         } else if (!mapped) {
             for (size_t i = 0; i < n; ++i)
                 if (x_host[i] && ops[i].w && ops[i].d_x)
@@ -486,7 +486,7 @@ int ullm_cuda_shard_matvec(ullm_cuda_shard *s, size_t n, const ullm_shard_op *op
         if (yv && y_count <= 0xffffffffull) {
             VecCopyList l{};
             l.src[0] = shard_y(s) + y_offset, l.dst[0] = yv, l.n[0] = (unsigned)y_count;
-            ULLM_CUDA_TRY(c, vec_copy_multi(l, 1, c->stream));
+            ULLM_CUDA_TRY(c, vec_copy_multi(l, 1, c->stream, c->use_pdl));
         } else {
             ULLM_CUDA_TRY(c, cudaMemcpyAsync(y_host, shard_y(s) + y_offset, y_count * 4, cudaMemcpyDeviceToHost, c->stream));
         }
