@@ -142,3 +142,16 @@ def test_rank_shares_of_the_70b_block_in_one_launch(ctx, world):
     assert ctx.last_plan()["grid"] == -2, "the chain kernel did not run"
     for y, ref in zip(ys, refs):
         assert synth.rel_err(y.cpu().numpy(), ref) < TOL
+
+
+def test_read_probe_reports_both_ways_of_reading(ctx):
+    """The measurement tool behind ``roofline.read_only_ceiling``: both modes run, return ordered statistics and
+    a plausible rate (above 1 TB/s on any B200, below 20), and bad arguments are refused before any launch."""
+    for mode in (0, 1):
+        r = ctx.read_probe(mode, 256 << 20, 94208, 2, 16384, reps=3)
+        assert r["us_min"] <= r["us"] <= r["us_max"]
+        assert 1000.0 < r["gbs"] < 20000.0, r
+    with pytest.raises(backend.UllmError):
+        ctx.read_probe(1, 256 << 20, 94208, 3, 16384)  # three such stages do not fit in shared memory
+    with pytest.raises(backend.UllmError):
+        ctx.read_probe(2, 256 << 20)
