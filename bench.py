@@ -7,11 +7,12 @@ At every ``--gpus N`` the workload is ``c4_70b_layer_matvec``: the seven matrice
 Llama-3-70B-shaped block (Q4_K q, k, v, o, gate, up; Q6_K down) as batch-1 matvecs, each with its own
 seeded input vector — the largest configuration that fits one GPU and the one that shards.
 
-* N = 1: resident weight objects, seven launches per step through ``ullm_cuda_weight_matvec_dev``.
+* N = 1: resident weight objects, one persistent launch per step through
+  ``ullm_cuda_weight_matvec_batch_dev`` (``--launch separate``: seven launches).
 * N > 1 (one process per GPU under torchrun): output rows split evenly over the ranks
-  (``ullm_cuda_shard_*``); each rank runs its slices as one persistent launch whose epilogue stores
-  the rows into every rank's gather buffer over NVLink, then publishes a step number and waits for
-  the others' (no NCCL on the data path).  ``--exchange nccl`` runs the comparison arm instead:
+  (``ullm_cuda_shard_*``); each rank runs its slices as one persistent launch that stores its rows
+  into every rank's memory over NVLink as {value, step} pairs and takes the pairs the other ranks
+  owe it before it ends (no NCCL on the data path).  ``--exchange nccl`` runs the comparison arm instead:
   the same kernels followed by an ``ncclAllGather``.  torch.distributed only carries the set-up
   (handle exchange) and the max-over-ranks of the timings.
 
@@ -684,7 +685,7 @@ def run_c4(args):
         # end to end: pinned host x in, the gathered vectors back to pinned host memory, one blocking call per step
         xs_p = [torch.from_numpy(m["xh"]).pin_memory().numpy() for m in mats]
         y_p = torch.empty(total, dtype=torch.float32).pin_memory().numpy()
-        e2e_api = "ullm_cuda_shard_matvec (pinned host x -> this rank's row slices -> peer stores + step flags -> pinned host y of all 7 full vectors)"
+        e2e_api = "ullm_cuda_shard_matvec (pinned host x -> this rank's row slices -> rows to all ranks as tagged pairs -> pinned host y of all 7 full vectors)"
         if args.exchange == "nccl":
             e2e_s = float("nan")
         else:
@@ -723,8 +724,8 @@ def run_c4(args):
             launch, kernel = "host launches: one persistent launch + ncclAllGather per step (comparison arm)", "matvec_chain_kernel + ncclAllGather"
             parallelism = f"rows/{world} per matrix; NCCL all-gather of the ranks' output rows"
         else:
-            launch, kernel = "one CUDA graph of the K timed steps, replayed; one persistent launch per step", "matvec_chain_kernel (peer-store epilogue, step flags)"
-            parallelism = f"rows/{world} per matrix; every rank's kernel stores its rows into all ranks' result vectors over NVLink, a published step number replaces the all-gather"
+            launch, kernel = "one CUDA graph of the K timed steps, replayed; one persistent launch per step", "matvec_chain_kernel (rows to all ranks as {value, step} pairs)"
+            parallelism = f"rows/{world} per matrix; every rank's kernel stores its rows into all ranks' memory over NVLink as tagged pairs and takes the pairs it is owed: no all-gather"
         cpu = None  # the CPU baseline is an N = 1 figure: one process then has the host's cores to itself
         barrier()
 
