@@ -901,7 +901,9 @@ def run_c4gemm_multi(args):
         xs = xs.to(torch.bfloat16).to(torch.float32)
         mats.append(dict(dt=dt, out=out, cols=cols, row0=r0, rows=rows, host=w, w=backend.Weight(ctx, dt, w, rows, cols), xs=xs))
 
-    fused = backend.SHARD_FUSED_STORES if args.gemm_exchange == "fused" else 0
+    fused = {"fused": backend.SHARD_FUSED_STORES, "push": backend.SHARD_SM_PUSH, "copy": 0, "auto": 0}[args.gemm_exchange]
+    if args.gemm_exchange == "copy":
+        ctx.debug_set("shard_gemm_exchange", 1)  # comparison: copy engines whatever the block's shape
 
     def step(_i, st):
         for k, (m, off) in enumerate(zip(mats, offs)):
@@ -942,8 +944,11 @@ def run_c4gemm_multi(args):
                           "tflops": tf, "tflops_per_gpu": tf / world, "peak_tflops": measured_peak_tflops(),
                           "frac_per_gpu": tf / world / measured_peak_tflops(), "scaling": "strong",
                           "peer_store_bytes_per_rank_per_step": 4 * S * sum(outs) // world * (world - 1),
-                          "parallelism": (f"rows/{world} per matrix; the GEMM epilogue stores each tile into all ranks' [tokens, out] over NVLink" if fused else
-                                          f"rows/{world} per matrix; each finished [tokens, rows/{world}] block is pushed to all ranks' [tokens, out] by the copy engines while the next matrix is multiplied; step flags instead of an all-gather"),
+                          "exchange": args.gemm_exchange,
+                          "parallelism": {"fused": f"rows/{world} per matrix; the GEMM epilogue stores each tile into all ranks' [tokens, out] over NVLink",
+                                          "push": f"rows/{world} per matrix; each finished [tokens, rows/{world}] block is pushed to all ranks' [tokens, out] by a copy kernel on a side stream while the next matrix is multiplied; step flags instead of an all-gather",
+                                          "auto": f"rows/{world} per matrix; each finished [tokens, rows/{world}] block is pushed to all ranks' [tokens, out] on a side stream while the next matrix is multiplied (copy kernel for narrow blocks or more than four ranks, else copy engines); step flags instead of an all-gather",
+                                          "copy": f"rows/{world} per matrix; each finished [tokens, rows/{world}] block is pushed to all ranks' [tokens, out] by the copy engines (one stream per peer) while the next matrix is multiplied; step flags instead of an all-gather"}[args.gemm_exchange],
                           "launch": "one CUDA graph of the timed steps, replayed", "check": {"rel_err_vs_cpu_64_rows_8_tokens_per_rank": float(wt.item())}}), flush=True)
     dist.destroy_process_group()
     return 0
@@ -969,7 +974,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="c2decode: number of layers (default: the model's 48)")
     ap.add_argument("--only", default="", help="c4gemm at N = 1: just this matrix of the block (q, k, v, o, gate, up, down)")
     ap.add_argument("--q6k-cost", type=int, default=0, help="--slice-of diagnostic: also time the persistent launch with this per-byte cost (permille) of Q6_K rows")
-    ap.add_argument("--gemm-exchange", default="copy", choices=["copy", "fused"], help="c4gemm at N > 1: copy engines on a side stream, or stores from the GEMM epilogue")
+    ap.add_argument("--gemm-exchange", default="auto", choices=["auto", "copy", "fused", "push"],
+                    help="c4gemm at N > 1: the library's choice per block (default), or forced: copy engines on side streams, stores from the GEMM epilogue, a copy kernel on the side stream")
     ap.add_argument("--slice-of", type=int, default=0, help="N = 1 diagnostic: time one rank's share of a W-way split without peers")
     ap.add_argument("--knob", action="append", default=[], help="test knob key=value passed to the library (sweeps; not used by any default run)")
     ap.add_argument("--eager", action="store_true", help="launch the timed steps from the host instead of replaying a CUDA graph")

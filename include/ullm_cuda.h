@@ -265,7 +265,7 @@ typedef struct ullm_shard_op {
     size_t y_offset;   /* where the full-length result starts in the gather buffer (floats) */
     size_t row0;       /* first row of the slice; ignored for weights made by ullm_cuda_shard_weight_create */
 } ullm_shard_op;
-enum { ULLM_SHARD_NO_WAIT = 1, ULLM_SHARD_FUSED_STORES = 2 };
+enum { ULLM_SHARD_NO_WAIT = 1, ULLM_SHARD_FUSED_STORES = 2, ULLM_SHARD_SM_PUSH = 4 };
 int ullm_cuda_shard_matvec_dev(ullm_cuda_shard *s, size_t n, const ullm_shard_op *ops, int flags, void *stream);
 /* The same step from host vectors, blocking: x_host[i] (may be NULL: the op's d_x is already filled) is
  * copied into op i's d_x, the step runs with its wait, and floats [y_offset, y_offset + y_count) of
@@ -284,7 +284,10 @@ int ullm_cuda_shard_wait_dev(ullm_cuda_shard *s, void *stream);
  * capture a step must therefore end with such a joining call.  ULLM_SHARD_FUSED_STORES makes the
  * GEMM's epilogue store every tile to all ranks itself instead (one kernel, no copy engine);
  * at prefill sizes that is the slower form, because a tile's stores over NVLink then run in series
- * with the tile's own arithmetic. */
+ * with the tile's own arithmetic.  ULLM_SHARD_SM_PUSH moves the finished block with a copy kernel
+ * (vector loads, stores to every peer) on the group's stream instead of the copy engines, which the
+ * library also does by itself for narrow blocks (rows of less than 4 KB) and groups of more than
+ * four ranks: the engines handle such strided copies poorly, and a small slice's GEMM leaves SMs idle. */
 int ullm_cuda_shard_matmul_dev(ullm_cuda_shard *s, const ullm_cuda_weight *w, const float *d_x, size_t tokens, size_t y_offset,
                                size_t row0, size_t out_total, int flags, void *stream);
 /* Comparison arm: the same exchange as an NCCL all-gather (libnccl.so.2 is loaded at run time;

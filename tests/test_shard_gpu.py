@@ -105,12 +105,12 @@ def test_sharded_matvec_caller_made_slices_and_mlx(ctx):
             s.free()
 
 
-@pytest.mark.parametrize("fused", [0, 1])
+@pytest.mark.parametrize("fused", [0, backend.SHARD_FUSED_STORES, backend.SHARD_SM_PUSH])
 @pytest.mark.parametrize("dtype,out,cols,tokens", [(backend.Q4_K, 1024, 2048, 96), (backend.Q6_K, 512, 2048, 300), (backend.Q4_K, 256, 8192, 64)])
 def test_sharded_matmul_tiles_land_in_every_rank(ctx, dtype, out, cols, tokens, fused):
     """Prefill form: each rank's [tokens, rows] block goes to its columns of [tokens, out] on every rank
-    (bf16 tensor-core GEMM: the 2e-2 bar); the third case takes the split-K path.  Both ways of moving the
-    block: copy engines on the group's own stream (default) and stores from the GEMM's epilogue."""
+    (bf16 tensor-core GEMM: the 2e-2 bar); the third case takes the split-K path.  The three ways of moving the
+    block: copy engines on the group's own streams (default), stores from the GEMM's epilogue, a copy kernel."""
     world = 2
     w = GEN[dtype](out, cols, 520)
     xs = synth.f32_to_bf16(synth.normal(521, tokens * cols))
@@ -121,7 +121,7 @@ def test_sharded_matmul_tiles_land_in_every_rank(ctx, dtype, out, cols, tokens, 
     try:
         for s in shards:
             wt = s.weight(dtype, w, out, cols)
-            s.matmul_dev(wt, xd.data_ptr(), tokens, 64, 0, 0, None, backend.SHARD_NO_WAIT | (backend.SHARD_FUSED_STORES if fused else 0))
+            s.matmul_dev(wt, xd.data_ptr(), tokens, 64, 0, 0, None, backend.SHARD_NO_WAIT | fused)
             assert ctx.last_plan()["grid"] == -1, "the tensor-core GEMM did not run"
         for s in shards:
             s.wait_dev()

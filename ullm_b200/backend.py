@@ -43,7 +43,7 @@ class FormatError(UllmError):
 
 
 OPT_PDL, OPT_SHARD_TIMEOUT_MS = 1, 2
-SHARD_HANDLE_BYTES, SHARD_NCCL_ID_BYTES, SHARD_NO_WAIT, SHARD_FUSED_STORES = 64, 128, 1, 2
+SHARD_HANDLE_BYTES, SHARD_NCCL_ID_BYTES, SHARD_NO_WAIT, SHARD_FUSED_STORES, SHARD_SM_PUSH = 64, 128, 1, 2, 4
 
 _lib = None
 

@@ -713,6 +713,7 @@ extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value)
     else if (!strcmp(key, "gemm_min_s")) c->gemm_min_s = value;
     else if (!strcmp(key, "no_chain")) c->no_chain = value != 0;
     else if (!strcmp(key, "shard_no_tagged")) c->shard_no_tagged = value != 0;
+    else if (!strcmp(key, "shard_gemm_exchange")) c->shard_gemm_exchange = value;
     else if (!strcmp(key, "q6k_cost_permille")) matvec_chain_set_q6k_cost(value / 1000.0);
     else if (!strcmp(key, "chain_prefetch_tiles")) matvec_chain_set_prefetch(value);
     else if (!strcmp(key, "chain_chunk")) matvec_chain_set_chunk(value);

@@ -35,6 +35,7 @@ struct ullm_cuda_ctx {
     unsigned *d_sync = nullptr; // grid-barrier counter of the chain kernel
     int plan_wr = 0, plan_rw = 0, plan_stages = 0;
     int shard_timeout_ms = 2000; // ULLM_OPT_SHARD_TIMEOUT_MS
+    int shard_gemm_exchange = 0; // prefill form's block transfer: 0 chosen per block, 1 copy engines, 2 copy kernel (comparisons)
     bool shard_no_tagged = false; // sharded matvec steps through the flag protocol only (tests, comparisons)
     int gemm_min_s = 32; // batches below this many tokens use per-token matvecs
     ullm::MatvecPlan last_plan;

@@ -173,6 +173,10 @@ struct ullm_cuda_shard {
     // the transfer of one matrix' block overlaps the next matrix' GEMM
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    // one more stream per peer, made at the first use: the copies to different peers go over different links and
+    // can use different copy engines, so they are issued side by side and meet again on copy_stream
+    cudaStream_t peer_stream[SHARD_MAX_RANKS] = {};
+    cudaEvent_t ev_peer[SHARD_MAX_RANKS] = {};
     bool copies_pending = false; // copy_stream has work the compute stream has not been joined with
 };
 
@@ -189,6 +193,15 @@ static void shard_wire(ullm_cuda_shard *s) {
     for (int r = 0; r < s->world; ++r) {
         d.delta[r] = (long long)((intptr_t)s->peer_base[r] - (intptr_t)s->base);
         d.peer_flag[r] = (unsigned *)s->peer_base[r] + s->rank * SHARD_CTL_STRIDE;
+    }
+    for (int r = 0; r < s->world; ++r) { // made here, outside any stream capture; a failure is retried at the first use
+        if (r == s->rank || s->peer_stream[r]) continue;
+        if (cudaStreamCreateWithFlags(&s->peer_stream[r], cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->ev_peer[r], cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            if (s->peer_stream[r]) cudaStreamDestroy(s->peer_stream[r]);
+            s->peer_stream[r] = nullptr;
+        }
     }
     d.ybase = shard_y(s);
     d.pairs = s->pair_bytes ? (uint2 *)((uint8_t *)s->base + SHARD_CTL_BYTES + shard_y_bytes(s)) : nullptr;
@@ -249,6 +262,13 @@ void ullm_cuda_shard_destroy(ullm_cuda_shard *s) {
     }
     if (s->ev_fork) cudaEventDestroy(s->ev_fork);
     if (s->ev_join) cudaEventDestroy(s->ev_join);
+    for (int r = 0; r < SHARD_MAX_RANKS; ++r) {
+        if (s->peer_stream[r]) {
+            cudaStreamSynchronize(s->peer_stream[r]);
+            cudaStreamDestroy(s->peer_stream[r]);
+        }
+        if (s->ev_peer[r]) cudaEventDestroy(s->ev_peer[r]);
+    }
     if (s->nccl_comm && nccl_api().ok) nccl_api().CommDestroy(s->nccl_comm);
     for (int r = 0; r < s->world; ++r)
         if (r != s->rank && s->peer_ipc[r] && s->peer_base[r]) cudaIpcCloseMemHandle(s->peer_base[r]);
@@ -543,10 +563,32 @@ int ullm_cuda_shard_matmul_dev(ullm_cuda_shard *s, const ullm_cuda_weight *w, co
             // compute stream joins only when the caller wants the step to be complete.
             e = cudaEventRecord(s->ev_fork, st);
             if (e == cudaSuccess) e = cudaStreamWaitEvent(s->copy_stream, s->ev_fork, 0);
-            for (int r = 0; r < s->world && e == cudaSuccess; ++r)
-                if (r != s->rank)
-                    e = cudaMemcpy2DAsync((char *)y + sh.delta[r], out_total * 4, y, out_total * 4, w->out * 4, tokens, cudaMemcpyDefault, s->copy_stream);
-            if (e == cudaSuccess) e = launch_shard_signal(sh, c->d_status, s->copy_stream);
+            // Narrow blocks, or many peers: one copy kernel (the block to every peer, then the publication) - strided
+            // copies of rows of a few hundred floats to seven peers kept the engines busy for longer than the GEMMs
+            // of a 1/8 slice take (70B block, 512 tokens, N = 8: 965 us through one copy stream, 835 with a stream
+            // per peer, 574 with the kernel; N = 4: 615 against 619).  Otherwise the copy engines, which need no SM.
+            const bool push = (flags & ULLM_SHARD_SM_PUSH) || c->shard_gemm_exchange == 2 ||
+                              (c->shard_gemm_exchange == 0 && (s->world > 4 || w->out * 4 < 4096));
+            if (push) {
+                const ShardRegion reg{y, (unsigned)w->out, (unsigned)tokens, out_total};
+                if (e == cudaSuccess) e = launch_shard_scatter(c->dev, sh, 1, &reg, c->d_status, s->copy_stream);
+            } else {
+                for (int r = 0; r < s->world && e == cudaSuccess; ++r) {
+                    if (r == s->rank) continue;
+                    if (!s->peer_stream[r]) {
+                        e = cudaStreamCreateWithFlags(&s->peer_stream[r], cudaStreamNonBlocking);
+                        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->ev_peer[r], cudaEventDisableTiming);
+                        if (e != cudaSuccess) break;
+                    }
+                    e = cudaStreamWaitEvent(s->peer_stream[r], s->ev_fork, 0);
+                    if (e == cudaSuccess)
+                        e = cudaMemcpy2DAsync((char *)y + sh.delta[r], out_total * 4, y, out_total * 4, w->out * 4, tokens, cudaMemcpyDefault,
+                                              s->peer_stream[r]);
+                    if (e == cudaSuccess) e = cudaEventRecord(s->ev_peer[r], s->peer_stream[r]);
+                    if (e == cudaSuccess) e = cudaStreamWaitEvent(s->copy_stream, s->ev_peer[r], 0);
+                }
+                if (e == cudaSuccess) e = launch_shard_signal(sh, c->d_status, s->copy_stream);
+            }
             s->copies_pending = true;
             if (e == cudaSuccess && sh.wait) {
                 e = cudaEventRecord(s->ev_join, s->copy_stream);
