@@ -371,7 +371,8 @@ __device__ __forceinline__ float row_partial(uint32_t row_addr, const uint32_t (
             ol = dp4a_uu(od, X[12 + j], ol);
         }
         int isum16 = 16 * (eh * 256 + el) + (oh * 256 + ol);
-        uint32_t g = (widx * 32u) / group;
+        // group sizes are powers of two in every MLX checkpoint (32, 64, 128): a shift, not a division, per row
+        const uint32_t g = (group & (group - 1u)) == 0u ? (widx * 32u) >> (31 - __clz((int)group)) : (widx * 32u) / group;
         float sc, bi;
         if constexpr (sizeof(TBL) == 4) {
             sc = __uint_as_float(lds32(tbl_s + 4 * g));
