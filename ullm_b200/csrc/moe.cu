@@ -294,6 +294,7 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
     bool aborted = false;
     int cur_d = -1;
     uint32_t kk = 0;
+    const int kshift = (p.k & (p.k - 1u)) == 0u ? 31 - __clz((int)p.k) : -1; // experts per token is usually a power of two
     // The register image of the current activation vector survives from tile to tile: most experts
     // are picked by a single pair, and then all row tiles of the expert use the same vector.
     uint32_t X[G][XR];
@@ -318,7 +319,7 @@ __global__ void __launch_bounds__(544, 1) moe_stream_kernel(const MoeStreamParam
         const uint32_t mstride = p.w_stage_bytes + 2 * p.tbl_stage_bytes;
         for (int j = 0; j < np && !aborted; ++j) {
             const int pair = pairs[pb + j];
-            const uint32_t vec = GATE_UP ? (uint32_t)pair / p.k : (uint32_t)j;
+            const uint32_t vec = GATE_UP ? (kshift >= 0 ? (uint32_t)pair >> kshift : (uint32_t)pair / p.k) : (uint32_t)j; // the pair's token
             if ((int)vec != loaded_vec) {
 #pragma unroll
                 for (int g = 0; g < G; ++g)
