@@ -426,3 +426,96 @@ impl Drop for GpuForward {
         unsafe { ffi::ullm_cuda_forward_destroy(self.raw) }
     }
 }
+
+// ---------------------------------------------------------------------------
+// Row-sharded matrices over the GPUs of one node (no counterpart in ullm-metal; the reference's
+// roadmap lists multi-device scale-out as open, docs/roadmap.md:83).  The split is the one the CPU
+// path already uses: output rows are independent (crates/ullm-model/src/math.rs:11-21).
+// ---------------------------------------------------------------------------
+
+/// One rank's end of a group of `world` GPUs: a gather buffer of `y_floats` floats with the same
+/// layout on every rank, in which the caller places full-length result vectors by offset.
+pub struct ShardGroup {
+    ctx: *mut ffi::ullm_cuda_ctx,
+    raw: *mut ffi::ullm_cuda_shard,
+    world: usize,
+    rank: usize,
+}
+unsafe impl Send for ShardGroup {}
+
+/// This rank's rows of a matrix, resident on its GPU.
+pub struct ShardedWeight {
+    ctx: *mut ffi::ullm_cuda_ctx,
+    raw: *mut ffi::ullm_cuda_weight,
+    pub out_total: usize,
+    pub cols: usize,
+}
+impl Drop for ShardedWeight {
+    fn drop(&mut self) {
+        unsafe { ffi::ullm_cuda_weight_destroy(self.ctx, self.raw) }
+    }
+}
+
+/// One matvec of a step: `y[y_offset .. y_offset + out_total] = W x` in every rank's gather buffer.
+pub struct ShardOp<'a> {
+    pub w: &'a ShardedWeight,
+    /// this rank's copy of the whole input vector, on the device
+    pub x: &'a Buffer,
+    pub y_offset: usize,
+}
+
+impl ShardGroup {
+    pub fn new(ctx: &CudaContext, world: usize, rank: usize, y_floats: usize) -> Result<Self> {
+        let mut raw = ptr::null_mut();
+        check(unsafe { ffi::ullm_cuda_shard_create(ctx.raw, world as c_int, rank as c_int, y_floats, &mut raw) }, ctx.raw)?;
+        Ok(Self { ctx: ctx.raw, raw, world, rank })
+    }
+    /// The bytes the other ranks' processes need to reach this rank's buffer (plain data: send them by any means).
+    pub fn export(&self) -> Result<[u8; ffi::ULLM_SHARD_HANDLE_BYTES]> {
+        let mut h = [0u8; ffi::ULLM_SHARD_HANDLE_BYTES];
+        check(unsafe { ffi::ullm_cuda_shard_export(self.raw, h.as_mut_ptr().cast()) }, self.ctx)?;
+        Ok(h)
+    }
+    /// `handles`: every rank's `export()`, in rank order.  All ranks connect before any runs a step.
+    pub fn connect(&mut self, handles: &[[u8; ffi::ULLM_SHARD_HANDLE_BYTES]]) -> Result<()> {
+        if handles.len() != self.world {
+            return Err(Error::Format(format!("need {} handles, got {}", self.world, handles.len())));
+        }
+        check(unsafe { ffi::ullm_cuda_shard_connect(self.raw, handles.as_ptr().cast()) }, self.ctx)
+    }
+    pub fn rank(&self) -> usize {
+        self.rank
+    }
+    /// Uploads this rank's rows of `full` (a description of the WHOLE matrix).
+    pub fn weight(&self, full: &GpuWeight) -> Result<ShardedWeight> {
+        let cw = c_weight(full)?;
+        let mut raw = ptr::null_mut();
+        check(unsafe { ffi::ullm_cuda_shard_weight_create(self.raw, &cw, ffi::ULLM_DTYPE_F32, &mut raw) }, self.ctx)?;
+        Ok(ShardedWeight { ctx: self.ctx, raw, out_total: full.out, cols: full.cols })
+    }
+    /// One step: every op's rows are computed here and stored into every rank's gather buffer; returns
+    /// (in stream order) when every rank's rows are in this rank's buffer.  A rank that does not answer within
+    /// the context's limit ends the step with an error instead of a hang.  Every rank runs the same steps.
+    pub fn matvec(&self, ops: &[ShardOp]) -> Result<()> {
+        let c: Vec<ffi::ullm_shard_op> = ops
+            .iter()
+            .map(|o| ffi::ullm_shard_op { w: o.w.raw, d_x: unsafe { ffi::ullm_cuda_buf_ptr(o.x.raw) }.cast(), y_offset: o.y_offset, row0: 0 })
+            .collect();
+        check(unsafe { ffi::ullm_cuda_shard_matvec_dev(self.raw, c.len(), c.as_ptr(), 0, ptr::null_mut()) }, self.ctx)
+    }
+    /// `n` gathered floats at `offset` of this rank's buffer (waits for the context's stream).
+    pub fn read(&self, offset: usize, n: usize) -> Result<Vec<f32>> {
+        let mut v = vec![0f32; n];
+        check(unsafe { ffi::ullm_cuda_shard_read(self.raw, offset, v.as_mut_ptr(), n) }, self.ctx)?;
+        Ok(v)
+    }
+    /// After a time-out the ranks are out of step: every rank resets, with a barrier of the caller's in between.
+    pub fn reset(&mut self) -> Result<()> {
+        check(unsafe { ffi::ullm_cuda_shard_reset(self.raw) }, self.ctx)
+    }
+}
+impl Drop for ShardGroup {
+    fn drop(&mut self) {
+        unsafe { ffi::ullm_cuda_shard_destroy(self.raw) }
+    }
+}
