@@ -126,6 +126,7 @@ DEBUG_SIGNATURES = {
     "ullm_cuda_debug_set": (_i, [_vp, C.c_char_p, _i]),
     "ullm_cuda_debug_last_plan": (_i, [_vp, _vp, _i]),
     "ullm_cuda_debug_read_probe": (_i, [_vp, _i, _sz, _i, _i, _i, _i, _vp]),
+    "ullm_cuda_debug_chain_deal": (_i, [_i, _vp, _vp, _vp, _i, _vp]),
 }
 
 
@@ -318,6 +319,20 @@ class CudaContext:
         v = (C.c_int * 6)()
         self._lib.ullm_cuda_debug_last_plan(self._h, v, 6)
         return dict(zip(("streamed", "rows_per_tile", "warps", "stages", "smem_bytes", "grid"), list(v)))
+
+
+def chain_deal(mats, grid: int = 148) -> list[int]:
+    """CTAs per matrix when the persistent matvec launch deals ``grid`` CTAs out to the independent matrices
+    ``[(dtype, out, cols), ...]`` (host arithmetic of the library; no device needed)."""
+    n = len(mats)
+    dt = (C.c_int * n)(*[m[0] for m in mats])
+    out = (C.c_size_t * n)(*[m[1] for m in mats])
+    cols = (C.c_size_t * n)(*[m[2] for m in mats])
+    res = (C.c_uint * n)()
+    rc = load_library().ullm_cuda_debug_chain_deal(n, dt, out, cols, grid, res)
+    if rc:
+        raise UllmError(rc, "ullm_cuda_debug_chain_deal")
+    return list(res)
 
 
 class GpuWeight(C.Structure):

@@ -705,6 +705,19 @@ int ullm_cuda_matmul_mlx4(ullm_cuda_ctx *c, const void *w, const float *scales, 
     return matmul_host(c, ULLM_DTYPE_MLX_U32, d_w, d_s, d_b, ULLM_DTYPE_F32, group, x, y, out_dim, in_dim, s);
 }
 
+// How the persistent matvec launch would deal `grid` CTAs out to `n` independent matrices (dtype: ULLM_DTYPE_Q4_K
+// or ULLM_DTYPE_Q6_K; at most 12; n <= grid).  Host arithmetic only: needs no device, so the CPU tests can pin it.
+extern "C" int ullm_cuda_debug_chain_deal(int n, const int *dtype, const size_t *out_dim, const size_t *in_dim, int grid, unsigned *ncta) {
+    if (n < 1 || n > 12 || grid < n || !dtype || !out_dim || !in_dim || !ncta) return ULLM_ERR_INVALID;
+    MatvecChainOp ops[12];
+    for (int i = 0; i < n; ++i) {
+        if (dtype[i] != ULLM_DTYPE_Q4_K && dtype[i] != ULLM_DTYPE_Q6_K) return ULLM_ERR_UNSUPPORTED;
+        ops[i].fmt = dtype[i] == ULLM_DTYPE_Q4_K ? FMT_Q4K : FMT_Q6KR, ops[i].out_dim = out_dim[i], ops[i].in_dim = in_dim[i];
+    }
+    matvec_chain_deal(n, ops, (uint32_t)grid, ncta);
+    return ULLM_OK;
+}
+
 // ---- test knobs (not part of the mirrored surface; every one is per context) ----
 extern "C" int ullm_cuda_debug_set(ullm_cuda_ctx *c, const char *key, int value) {
     if (!c || !key) return ULLM_ERR_INVALID;

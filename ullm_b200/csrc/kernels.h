@@ -116,6 +116,7 @@ struct MatvecChainOp {
 };
 bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi);
 void matvec_chain_set_q6k_cost(double v);
+void matvec_chain_deal(int n, const MatvecChainOp *ops, uint32_t grid, uint32_t *ncta); // CTAs per op of a list of independent ops
 void matvec_chain_set_prefetch(int tiles);
 void matvec_chain_set_chunk(int bytes);
 void matvec_chain_set_overlap(int on);

@@ -405,6 +405,35 @@ bool matvec_chain_supported(int fmt, size_t out_dim, size_t in_dim, int epi) {
     return (in_dim + 2047) / 2048 <= 16; // one column group (2048 columns) per warp; up to 16 of the 20 consumer warps form a row slice
 }
 
+// How `grid` CTAs are dealt out to `n` independent ops (n <= grid): ncta[i] CTAs share op i's rows.
+// Model of an op's time with m CTAs: fixed_i + work_i / m, where work_i is its weight bytes at the rate a CTA
+// streams them (prepared Q6_K rows weigh g_q6k_cost, fitted on the 70B block: 111.7 / 107.0 / 108.7 us per step at
+// 1.3 / 1.4 / 1.5 before, 100.9 / 98.6 / 95.7 / 98.0 / 100.5 at 1.2 / 1.1 / 1.05 / 1.0 / 0.95 after four rows per
+// warp came to its widest matrix) and fixed_i is what every CTA of the op spends before its first tile: reading
+// and converting the op's whole input vector.  The launch ends when the slowest group does, so the CTAs are dealt
+// out to minimise the largest group time: one CTA each, then every further CTA to the group that is slowest at
+// that moment (optimal for this model; rounding byte shares to the nearest count instead left the 1024-row
+// matrices of the 70B block with one CTA each, and those two CTAs then set the time of the whole step).
+void matvec_chain_deal(int n, const MatvecChainOp *ops, uint32_t grid, uint32_t *ncta) {
+    double work[CHAIN_MAX_OPS], fixed[CHAIN_MAX_OPS];
+    for (int i = 0; i < n; ++i) {
+        const double rb = (double)(ops[i].in_dim / QK_K) * (ops[i].fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+        work[i] = (double)ops[i].out_dim * rb * (ops[i].fmt == FMT_Q4K ? 1.0 : g_q6k_cost) / 33000.0; // us of one CTA
+        fixed[i] = 0.5 + (double)ops[i].in_dim * 7.0e-5;                                             // us
+        ncta[i] = 1;
+    }
+    for (uint32_t used = (uint32_t)n; used < grid; ++used) {
+        int slow = 0;
+        double worst = -1.0;
+        for (int i = 0; i < n; ++i) {
+            const uint32_t units = std::max<uint32_t>(1, (uint32_t)(ops[i].out_dim / 2)); // no more CTAs than pairs of rows
+            const double t = ncta[i] >= units ? -1.0 : fixed[i] + work[i] / ncta[i];
+            if (t > worst) worst = t, slow = i;
+        }
+        ++ncta[slow];
+    }
+}
+
 cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainOp *ops, unsigned *d_sync, int *d_status,
                                 cudaStream_t st, bool pdl, const ShardDev *shard) {
     if (n <= 0 || n > CHAIN_MAX_OPS) return cudaErrorInvalidValue;
@@ -424,30 +453,7 @@ cudaError_t launch_matvec_chain(const DeviceInfo &dev, int n, const MatvecChainO
     bool dealt = n > 1 && (uint32_t)n <= grid;
     for (int i = 0; i < n; ++i) dealt = dealt && !ops[i].dep;
     if (dealt) {
-        // Model of an op's time with m CTAs: fixed_i + work_i / m, where work_i is its weight bytes at the rate a CTA
-        // streams them (prepared Q6_K rows weigh g_q6k_cost: on the 28,672-column matrix 14 of the 20 warps work; the 70B block measured 111.7 / 107.0 / 108.7 us per step at 1.3 / 1.4 / 1.5, and 129.5 / 121.7 at 1.0 / 1.7 with 4 KB copies) and
-        // fixed_i is what every CTA of the op spends before its first tile: reading and converting the op's whole
-        // input vector.  The launch ends when the slowest group does, so the CTAs are dealt out to minimise the
-        // largest group time: one CTA each, then every further CTA to the group that is slowest at that moment
-        // (optimal for this model; rounding shares to the nearest count instead left the 1024-row matrices of the
-        // 70B block with one CTA each, and those two CTAs then set the time of the whole step).
-        double work[CHAIN_MAX_OPS], fixed[CHAIN_MAX_OPS];
-        for (int i = 0; i < n; ++i) {
-            const double rb = (double)(ops[i].in_dim / QK_K) * (ops[i].fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
-            work[i] = (double)ops[i].out_dim * rb * (ops[i].fmt == FMT_Q4K ? 1.0 : g_q6k_cost) / 33000.0; // us of one CTA
-            fixed[i] = 0.5 + (double)ops[i].in_dim * 7.0e-5;                                             // us
-            ncta[i] = 1;
-        }
-        for (uint32_t used = (uint32_t)n; used < grid; ++used) {
-            int slow = 0;
-            double worst = -1.0;
-            for (int i = 0; i < n; ++i) {
-                const uint32_t units = std::max<uint32_t>(1, (uint32_t)(ops[i].out_dim / 2)); // no more CTAs than pairs of rows
-                const double t = ncta[i] >= units ? -1.0 : fixed[i] + work[i] / ncta[i];
-                if (t > worst) worst = t, slow = i;
-            }
-            ++ncta[slow];
-        }
+        matvec_chain_deal(n, ops, grid, ncta);
         uint32_t at = 0;
         for (int i = 0; i < n; ++i) cta0[i] = at, at += ncta[i];
     } else {
