@@ -57,3 +57,10 @@ def test_spread_reports_median_min_max_per_step():
     sp = bench.spread([2.0, 1.0, 4.0], 2)
     assert sp == {"median": 1.0, "min": 0.5, "max": 2.0, "replays": 3}
     assert np.isclose(bench.spread([3.0], 3)["median"], 1.0)
+
+
+def test_roofline_denominators_come_from_the_measured_file_or_the_stated_fallback(monkeypatch, tmp_path):
+    monkeypatch.setattr(bench, "ROOT", str(tmp_path))
+    assert bench.measured_peak_gbs() == (6650.0, "fallback") and bench.measured_peak_tflops() == 1590.0
+    (tmp_path / "MEASURED_PEAKS.json").write_text(json.dumps({"hbm_gbs": 6545.0, "bf16_tflops": 1699.0}))
+    assert bench.measured_peak_gbs() == (6545.0, "measured") and bench.measured_peak_tflops() == 1699.0
